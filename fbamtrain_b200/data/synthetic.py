@@ -1,0 +1,55 @@
+"""Vectorised synthetic batch source for benchmarks and smoke runs.
+
+Produces whole training batches with the statistics the benchmark configurations prescribe:
+frames are ``rows x cols`` grids of cell ids drawn uniformly from ``[0, cell_vocab)`` (plus a
+uniform colour-attribute id in ``[0, 16)`` mapped through the ANSI palette to fg/bg RGB); every
+later frame copies its predecessor and redraws ``resample`` (5 %) of the cells; the target action
+of each frame is uniform in ``[0, action_vocab)``.  Output lives in *pinned host memory* in the
+cell-state layout the model consumes — ``uint32 (B, T, rows*cols, 3)`` — so a training step can
+upload it with one asynchronous copy.
+"""
+from __future__ import annotations
+
+from typing import Tuple
+
+import numpy as np
+import torch
+
+from .palette import ANSI_PALETTE
+
+
+class SyntheticBatchSource:
+    def __init__(self, rows: int, cols: int, cell_vocab: int, action_vocab: int, seed: int = 0,
+                 resample: float = 0.05, attr_ids: int = 16, pin: bool = True):
+        self.rows, self.cols = rows, cols
+        self.cell_vocab, self.action_vocab = cell_vocab, action_vocab
+        self.resample, self.attr_ids = resample, attr_ids
+        self.seed = seed
+        self.pin = pin and torch.cuda.is_available()
+        self._calls = 0
+
+    def next_batch(self, batch: int, seq: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Returns ``(cells uint32-as-int32 (B, T, P, 3), targets int64 (B, T))`` on the host."""
+        rng = np.random.default_rng([self.seed, self._calls])
+        self._calls += 1
+        n = self.rows * self.cols
+        pal = np.asarray(ANSI_PALETTE, dtype=np.uint32)
+        cp = rng.integers(0, self.cell_vocab, size=(batch, n), dtype=np.uint32)
+        attr = rng.integers(0, self.attr_ids, size=(batch, n), dtype=np.uint32)
+        k = max(1, int(round(self.resample * n)))
+        cells = torch.empty((batch, seq, n, 3), dtype=torch.int32, pin_memory=self.pin)
+        out = cells.numpy().view(np.uint32)
+        rows_ix = np.arange(batch)[:, None]
+        for t in range(seq):
+            if t > 0:
+                # k distinct cells per batch row: argpartition of random keys
+                idx = np.argpartition(rng.random((batch, n), dtype=np.float32), k, axis=1)[:, :k]
+                cp[rows_ix, idx] = rng.integers(0, self.cell_vocab, size=(batch, k), dtype=np.uint32)
+                attr[rows_ix, idx] = rng.integers(0, self.attr_ids, size=(batch, k), dtype=np.uint32)
+            out[:, t, :, 0] = cp
+            out[:, t, :, 1] = pal[attr % 16]
+            out[:, t, :, 2] = pal[(15 - attr) % 16]
+        tg = torch.from_numpy(rng.integers(0, self.action_vocab, size=(batch, seq), dtype=np.int64))
+        if self.pin:
+            tg = tg.pin_memory()
+        return cells, tg

@@ -1,0 +1,100 @@
+"""Building blocks shared by the frame head and the action model.
+
+``Linear`` keeps its weight as ``(out, in)`` — the K-major operand layout of the GEMM kernels —
+and the checkpoint layer transposes to the reference's ``(in, out)`` storage (reference:
+``tensorlib/include/linear.h:30-33``).  ``FullMhaAttention`` is a fused-QKV projection, a split
+into strided q/k/v views, scaled-dot-product attention and an output projection (reference:
+``tensorlib/include/attention.h:95-114``); the block wiring ``x += attn(norm(x)); x += mlp(norm(x))``
+follows ``src/framehead_model.cpp:339-398``.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from .. import ops
+from .init_utils import SeedSequence, fill_uniform_fan_
+
+
+class RmsNorm(nn.Module):
+    def __init__(self, dim: int, eps: float, dtype: torch.dtype):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.rms_norm(x, self.weight, self.eps)
+
+
+class LayerNorm(nn.Module):
+    """Forward-complete LayerNorm (the reference ships it but no model uses it;
+    reference: ``tensorlib/include/layer_norm.h:12-78``)."""
+
+    def __init__(self, dim: int, eps: float, dtype: torch.dtype, bias: bool = True):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype))
+        self.bias = nn.Parameter(torch.zeros(dim, dtype=dtype)) if bias else None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.layer_norm(x, self.weight, self.bias, self.eps)
+
+
+class Linear(nn.Module):
+    def __init__(self, fan_in: int, fan_out: int, bias: bool, dtype: torch.dtype, seeds: SeedSequence,
+                 act: str = "none"):
+        super().__init__()
+        self.act = act
+        self.weight = nn.Parameter(torch.empty(fan_out, fan_in, dtype=dtype))
+        fill_uniform_fan_(self.weight.data, fan_in, seeds)
+        if bias:
+            self.bias = nn.Parameter(torch.empty(fan_out, dtype=dtype))
+            fill_uniform_fan_(self.bias.data, fan_in, seeds)
+        else:
+            self.bias = None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.linear(x, self.weight, self.bias, self.act)
+
+
+class MlpBlock(nn.Module):
+    def __init__(self, dim: int, hidden: int, bias: bool, dtype: torch.dtype, seeds: SeedSequence):
+        super().__init__()
+        self.fc1 = Linear(dim, hidden, bias, dtype, seeds, act="gelu")
+        self.fc2 = Linear(hidden, dim, bias, dtype, seeds)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.fc2(self.fc1(x))
+
+
+class FullMhaAttention(nn.Module):
+    def __init__(self, dim: int, n_head: int, bias: bool, causal: bool, dtype: torch.dtype, seeds: SeedSequence):
+        super().__init__()
+        if dim % n_head != 0:
+            raise ValueError("n_embed must be divisible by n_head")
+        self.n_head, self.causal = n_head, causal
+        self.qkv = Linear(dim, 3 * dim, bias, dtype, seeds)
+        self.proj = Linear(dim, dim, bias, dtype, seeds)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        b, t, e = x.shape
+        d = e // self.n_head
+        qkv = self.qkv(x.reshape(b * t, e)).view(b, t, 3, self.n_head, d)
+        o = ops.attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], self.causal)
+        return self.proj(o.reshape(b * t, e)).view(b, t, e)
+
+
+class AttentionBlock(nn.Module):
+    def __init__(self, dim: int, n_head: int, mlp_dim: int, bias: bool, causal: bool, eps: float,
+                 dtype: torch.dtype, seeds: SeedSequence):
+        super().__init__()
+        self.ln1 = RmsNorm(dim, eps, dtype)
+        self.attn = FullMhaAttention(dim, n_head, bias, causal, dtype, seeds)
+        self.ln2 = RmsNorm(dim, eps, dtype)
+        self.mlp = MlpBlock(dim, mlp_dim, bias, dtype, seeds)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x = x + self.attn(self.ln1(x))
+        b, t, e = x.shape
+        x = x + self.mlp(self.ln2(x).reshape(b * t, e)).view(b, t, e)
+        return x

@@ -1,0 +1,114 @@
+"""Backend selection for the functional ops (see the package docstring)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import reference as ref
+
+_BACKEND = "auto"  # "auto": native kernels for CUDA tensors, PyTorch on CPU; "torch": PyTorch everywhere
+
+
+def set_backend(name: str) -> None:
+    global _BACKEND
+    if name not in ("auto", "torch"):
+        raise ValueError("backend must be 'auto' or 'torch'")
+    _BACKEND = name
+
+
+def get_backend() -> str:
+    return _BACKEND
+
+
+def _native(t: torch.Tensor) -> bool:
+    return t.is_cuda and _BACKEND == "auto"
+
+
+def cell_embed(cells, cp_embed, pos_embed, colour_embed, out_dtype):
+    if _native(cells):
+        from .native_ops import cell_embed as f
+        return f(cells, cp_embed, pos_embed, colour_embed, out_dtype)
+    return ref.cell_embed(cells, cp_embed, pos_embed, colour_embed, out_dtype)
+
+
+def conv2d_nhwc(x, w_ohwi, stride: int, padding: int, dilation: int):
+    if _native(x):
+        from .native_ops import conv2d_nhwc as f
+        return f(x, w_ohwi, stride, padding, dilation)
+    return ref.conv2d_nhwc(x, w_ohwi, stride, padding, dilation)
+
+
+def rms_norm(x, weight, eps: float):
+    if _native(x):
+        from .native_ops import rms_norm as f
+        return f(x, weight, eps)
+    return ref.rms_norm(x, weight, eps)
+
+
+def layer_norm(x, weight, bias, eps: float):
+    if _native(x):
+        from .native_ops import layer_norm as f
+        return f(x, weight, bias, eps)
+    return ref.layer_norm(x, weight, bias, eps)
+
+
+def gelu(x):
+    if _native(x):
+        from .native_ops import gelu as f
+        return f(x)
+    return ref.gelu(x)
+
+
+def geglu(x):
+    if _native(x):
+        from .native_ops import geglu as f
+        return f(x)
+    return ref.geglu(x)
+
+
+def avg_pool2x2_nhwc(x):
+    if _native(x):
+        from .native_ops import avg_pool2x2_nhwc as f
+        return f(x)
+    return ref.avg_pool2x2_nhwc(x)
+
+
+def global_avg_pool_nhwc(x):
+    """``(N, H, W, C)`` → ``(N, C)`` mean over the spatial positions (fp32 accumulate)."""
+    if _native(x):
+        from .native_ops import global_avg_pool_nhwc as f
+        return f(x)
+    return x.float().mean(dim=(1, 2)).to(x.dtype)
+
+
+def linear(x, weight, bias: Optional[torch.Tensor] = None, act: str = "none"):
+    if _native(x):
+        from .native_ops import linear as f
+        return f(x, weight, bias, act)
+    return ref.linear(x, weight, bias, act)
+
+
+def attention(q, k, v, causal: bool):
+    if _native(q):
+        from .native_ops import attention as f
+        return f(q, k, v, causal)
+    if q.is_cuda:  # PyTorch baseline on GPU: library flash attention
+        import torch.nn.functional as F
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal)
+        return o.transpose(1, 2).contiguous()
+    return ref.attention(q, k, v, causal)
+
+
+def lstm_sequence(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype):
+    if _native(x):
+        from .native_ops import lstm_sequence as f
+        return f(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype)
+    return ref.lstm_sequence(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype)
+
+
+def lm_head_ce(x, w_head, targets, vocab: int, scale: float):
+    if _native(x):
+        from .native_ops import lm_head_ce as f
+        return f(x, w_head, targets, vocab, scale)
+    return ref.lm_head_ce(x, w_head, targets, vocab, scale)

@@ -1,0 +1,348 @@
+"""Training engine: builds the model, optimizers and flat buffers from a run configuration and runs
+steps.
+
+Step structure of the reference (reference: ``src/main.cpp:3016-3869``): zero gradients → for every
+micro-batch run frame head, action model forward/backward and frame-head backward → accumulate the
+loss → reduce gradients across data-parallel ranks (sum; the loss is pre-divided by
+``T · total_batch_size``) → step the frame-head and action-model optimizers → commit the dataset
+cursor → enqueue step metrics → periodic validation → periodic checkpoint.
+
+``Trainer.train_step(cells, targets)`` is the public per-step call.  It accepts host tensors
+(pinned or not): frames are uploaded chunk by chunk on a copy stream while the frame head already
+works on earlier chunks, and the step loss leaves the device through the loss ring buffer without
+blocking the loop.
+"""
+from __future__ import annotations
+
+import os
+import time
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from .checkpoint import CheckpointManager
+from .config import ParallelConfiguration, RunConfiguration
+from .data import (DatasetCursorCommitter, DatasetCursorSnapshot, RecordingDatasetIterator,
+                   StreamTokenizationContext, SyntheticBatchSource, consume_next_token, prepare_cell_states)
+from .models import FbamModel
+from .optim import AdamwOptimizer, MuonWithAuxAdam, Optimizer, create_optimizer
+from .tokenizer import Tokenizer
+from .utils.flat import FlatGroup, build_groups
+from .utils.logging import LOG
+from .utils.metrics import AsyncStepLogger, LossRingBuffer, StepRecord
+from .utils.nvtx import gputx_range
+
+
+def _is_muon_param(name: str, p: torch.nn.Parameter) -> bool:
+    """Matrices go to Muon; embeddings, the LM head, gains, biases and initial states to AdamW."""
+    if p.dim() < 2:
+        return False
+    return not any(k in name for k in ("embed", "head_weight", "position_embedding"))
+
+
+class Trainer:
+    def __init__(self, cfg: RunConfiguration, parallel: Optional[ParallelConfiguration] = None,
+                 device: Optional[torch.device] = None, dp=None, tokenizer: Optional[Tokenizer] = None,
+                 frame_chunk: int = 0, working_dir: str = "."):
+        self.cfg, self.parallel, self.working_dir = cfg, parallel, working_dir
+        self.device = device or torch.device("cuda" if torch.cuda.is_available() else "cpu")
+        self.dp = dp
+        self.world = dp.world_size if dp is not None else 1
+        self.rank = dp.rank if dp is not None else 0
+        if cfg.total_batch_size % (cfg.micro_batch_size * self.world) != 0:
+            raise ValueError("total_batch_size must be a multiple of micro_batch_size x data-parallel world size")
+        self.grad_accum_steps = cfg.total_batch_size // (cfg.micro_batch_size * self.world)
+
+        self.tokenizer = tokenizer
+        if tokenizer is None and cfg.tokenizer_file_path:
+            self.tokenizer = Tokenizer.from_file(os.path.join(working_dir, cfg.tokenizer_file_path))
+        vocab = cfg.model_config.action_vocab or (len(self.tokenizer) if self.tokenizer else 0)
+        if vocab <= 0:
+            raise ValueError("action vocabulary unknown: give a tokenizer file or 'action_vocab'")
+        self.vocab = vocab
+
+        self.model = FbamModel(cfg.model_config, vocab).to(self.device)
+        self.model.frame_chunk = frame_chunk
+        self.frame_chunk = frame_chunk
+
+        # flat parameter / gradient buffers, grouped by scope, optimizer kind and dtype
+        shard_multiple = self.world
+        self.groups: Dict[str, List[FlatGroup]] = {}
+        self.optimizers: Dict[str, Optimizer] = {}
+        for scope, module in (("frame_head", self.model.frame_head), ("action_model", self.model.action_model)):
+            named = [(f"{scope}.{n}", p) for n, p in module.named_parameters()]
+            ocfg = cfg.optimizer_config
+            prefix = f"optim/{scope}"
+            if ocfg.type == "adamw":
+                gs = build_groups(scope, named, shard_multiple)
+                self.groups[scope] = gs
+                self.optimizers[scope] = AdamwOptimizer(named, prefix, ocfg.learning_rate, ocfg.beta1, ocfg.beta2,
+                                                        ocfg.eps, ocfg.weight_decay, groups=gs)
+            elif ocfg.type == "muon":
+                muon_named = [(n, p) for n, p in named if _is_muon_param(n, p)]
+                adam_named = [(n, p) for n, p in named if not _is_muon_param(n, p)]
+                g_muon = build_groups(scope + "/muon", muon_named, shard_multiple) if muon_named else []
+                g_adam = build_groups(scope + "/adam", adam_named, shard_multiple) if adam_named else []
+                self.groups[scope] = g_muon + g_adam
+                opt = MuonWithAuxAdam(named, prefix, ocfg.learning_rate, ocfg.momentum, ocfg.nesterov,
+                                      ocfg.weight_decay, ocfg.beta1, ocfg.beta2, ocfg.eps,
+                                      adam_names=lambda n, _m=dict(named): not _is_muon_param(n, _m[n]))
+                if g_adam:
+                    opt.adam = AdamwOptimizer(adam_named, prefix + "/adam", ocfg.learning_rate, ocfg.beta1,
+                                              ocfg.beta2, ocfg.eps, ocfg.weight_decay, groups=g_adam)
+                self.optimizers[scope] = opt
+            else:
+                self.groups[scope] = build_groups(scope, named, shard_multiple)
+                self.optimizers[scope] = create_optimizer(ocfg, named, prefix)
+        if self.dp is not None:
+            self.dp.attach(self)
+
+        self.step_count = 0
+        self.ring = LossRingBuffer(self.device)
+        self.logger = AsyncStepLogger(self.ring)
+        self.ckpt = CheckpointManager(os.path.join(working_dir, cfg.checkpointing.checkpoint_directory),
+                                      cfg.max_training_steps)
+        self.cursor: Optional[DatasetCursorCommitter] = None
+        self._cuda = self.device.type == "cuda"
+        if self._cuda:
+            self.h2d_stream = torch.cuda.Stream(device=self.device)
+        self._staging: Dict[Tuple, torch.Tensor] = {}
+
+    # ------------------------------------------------------------------------------------------
+    def all_groups(self) -> List[FlatGroup]:
+        return [g for gs in self.groups.values() for g in gs]
+
+    def zero_grad(self) -> None:
+        with gputx_range("fbamtrain::zero_grad"):
+            for g in self.all_groups():
+                g.grad.zero_()
+
+    def _device_buffer(self, key, shape, dtype) -> torch.Tensor:
+        buf = self._staging.get(key)
+        if buf is None or tuple(buf.shape) != tuple(shape) or buf.dtype != dtype:
+            buf = torch.empty(shape, dtype=dtype, device=self.device)
+            self._staging[key] = buf
+        return buf
+
+    def _upload(self, cells: torch.Tensor, targets: torch.Tensor):
+        """Starts the host→device copies; returns device tensors and per-chunk ready events."""
+        if cells.device == self.device or not self._cuda:
+            return cells.to(self.device), targets.to(self.device), None, None
+        b, t, p, _ = cells.shape
+        frames = b * t
+        chunk = self.frame_chunk or frames
+        dev_cells = self._device_buffer(("cells",), (frames, p, 3), cells.dtype)
+        dev_targets = self._device_buffer(("targets",), tuple(targets.shape), targets.dtype)
+        flat = cells.reshape(frames, p, 3)
+        events = []
+        self.h2d_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.h2d_stream):
+            dev_targets.copy_(targets, non_blocking=True)
+            for lo in range(0, frames, chunk):
+                hi = min(frames, lo + chunk)
+                dev_cells[lo:hi].copy_(flat[lo:hi], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record()
+                events.append(ev)
+        return dev_cells.view(b, t, p, 3), dev_targets, events, chunk
+
+    def _forward_backward(self, cells: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        loss_scale = 1.0 / (cells.shape[1] * cfg.total_batch_size)
+        dev_cells, dev_targets, events, chunk = self._upload(cells, targets)
+        b, t, p, _ = dev_cells.shape
+        with gputx_range("fbamtrain::forward"):
+            if events is None:
+                emb = self.model.frame_embeddings(dev_cells)
+            else:
+                flat = dev_cells.view(b * t, p, 3)
+                parts = []
+                with gputx_range("fbamtrain::frame_head_fwd"):
+                    for i, lo in enumerate(range(0, b * t, chunk)):
+                        torch.cuda.current_stream().wait_event(events[i])
+                        parts.append(self.model.frame_head(flat[lo:lo + chunk]))
+                emb = (parts[0] if len(parts) == 1 else torch.cat(parts, 0)).view(b, t, -1)
+            with gputx_range("fbamtrain::action_model_fwd_bwd"):
+                loss = self.model.action_model(emb, dev_targets, loss_scale)
+        with gputx_range("fbamtrain::backward"):
+            loss.backward()
+        return loss.detach()
+
+    def train_step(self, cells: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """One optimizer step.  ``cells`` int32 ``(B_local, T, P, 3)`` and ``targets`` int64 ``(B_local, T)``
+        hold this rank's share of the batch (``grad_accum_steps`` micro-batches).  Returns the step
+        loss as a device scalar (this rank's share of the global mean)."""
+        cfg = self.cfg
+        micro = cfg.micro_batch_size
+        if cells.shape[0] != micro * self.grad_accum_steps:
+            raise ValueError(f"expected {micro * self.grad_accum_steps} sequences per rank, got {cells.shape[0]}")
+        step = self.step_count
+        start_ev = end_ev = None
+        wall0 = time.perf_counter()
+        if self._cuda:
+            start_ev = torch.cuda.Event(enable_timing=True)
+            start_ev.record()
+        self.zero_grad()
+        self.ring.begin(step)
+        total = None
+        for k in range(self.grad_accum_steps):
+            loss = self._forward_backward(cells[k * micro:(k + 1) * micro], targets[k * micro:(k + 1) * micro])
+            self.ring.accumulate(step, loss)
+            total = loss if total is None else total + loss
+        committed = True
+        if self.dp is not None:
+            committed = self.dp.reduce_and_step(self)
+        else:
+            with gputx_range("fbamtrain::action_model_optim_step"):
+                self.optimizers["action_model"].step()
+            with gputx_range("fbamtrain::frame_head_optim_step"):
+                self.optimizers["frame_head"].step()
+        loss_ev = self.ring.finalize(step)
+        if self._cuda:
+            end_ev = torch.cuda.Event(enable_timing=True)
+            end_ev.record()
+        self.logger.submit(StepRecord(step, start_ev, end_ev, loss_ev, cells.shape[1], cfg.total_batch_size,
+                                      dropped=not committed, wall_start=wall0, wall_end=time.perf_counter()))
+        if committed:
+            self.step_count += 1
+        return total
+
+    # ------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def validation_loss(self, cells: torch.Tensor, targets: torch.Tensor) -> float:
+        cells, targets = cells.to(self.device), targets.to(self.device)
+        scale = 1.0 / (cells.shape[0] * cells.shape[1])
+        return float(self.model(cells, targets, scale))
+
+    def validation_dump(self, cells: torch.Tensor, targets: torch.Tensor) -> Dict[str, torch.Tensor]:
+        """Tensors of one forward/backward pass for numerics comparison: ``output`` (LSTM-stack
+        hidden states), ``h_n``, ``c_n``, ``loss``, ``frame_embeddings``, ``logits``, ``grad_*`` and
+        ``param_*`` (reference: ``src/main.cpp:3492-3564``)."""
+        cells, targets = cells.to(self.device), targets.to(self.device)
+        self.zero_grad()
+        scale = 1.0 / (cells.shape[1] * cells.shape[0])
+        emb = self.model.frame_embeddings(cells)
+        emb.retain_grad()
+        hidden, (h_n, c_n) = self.model.action_model.features(emb)
+        logits = self.model.action_model.logits(hidden)
+        loss = self.model.action_model(emb, targets, scale)
+        loss.backward()
+        out = {"output": hidden.detach(), "h_n": h_n.detach(), "c_n": c_n.detach(), "loss": loss.detach().reshape(1),
+               "frame_embeddings": emb.detach(), "logits": logits.detach()}
+        for n, p in self.model.named_parameters():
+            out["param_" + n] = p.detach().clone()
+            if p.grad is not None:
+                out["grad_" + n] = p.grad.detach().clone()
+        return {k: v.float().cpu().contiguous() for k, v in out.items()}
+
+    # ------------------------------------------------------------------------------------------
+    def save_checkpoint(self, dataset_state=None) -> str:
+        if self._cuda:
+            torch.cuda.synchronize()
+        if self.dp is not None:
+            self.dp.gather_optimizer_state(self)
+        return self.ckpt.save(self.step_count, self.model, self.optimizers, dataset_state)
+
+    def load_latest_checkpoint(self):
+        """Returns the restored dataset-iterator state, or None when nothing was loaded."""
+        if self.cfg.checkpointing.resume_behavior != "load_latest":
+            return None
+        latest = self.ckpt.find_latest()
+        if latest is None:
+            return None
+        step, ds = self.ckpt.load(latest[1], self.model, self.optimizers,
+                                  self.cfg.micro_batch_size * self.grad_accum_steps)
+        self.step_count = step
+        LOG("INFO", f"Resumed from {latest[1]} at step {step}")
+        return ds
+
+    def close(self) -> None:
+        self.logger.drain()
+        self.logger.close()
+        if self.cursor is not None:
+            self.cursor.close()
+
+
+# ----------------------------------------------------------------------------------------------
+# batches from recordings
+# ----------------------------------------------------------------------------------------------
+def build_batch_from_recordings(batch, tokenizer: Tokenizer, seq_len: int, rows: int, cols: int, vocab: int,
+                                max_code_point: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Walks each stream's keystrokes with the tokenizer and pairs every token with the frame that
+    was on screen when it started; exhausted streams pad with zero frames and target 0
+    (reference: ``src/main.cpp:1812-1884``)."""
+    b = len(batch.recordings)
+    cells = np.zeros((b, seq_len, rows * cols, 3), dtype=np.uint32)
+    targets = np.zeros((b, seq_len), dtype=np.int64)
+    for i, (rec, start) in enumerate(zip(batch.recordings, batch.start_positions)):
+        if rec.rows != rows or rec.cols != cols:
+            raise RuntimeError(f"Obtained input frame from dataset with size different from configuration: "
+                               f"Expected {rows}x{cols} according to configuration, got {rec.rows}x{rec.cols}")
+        ctx = StreamTokenizationContext(rec, tokenizer, int(start))
+        for pos in range(seq_len):
+            res = None if ctx.exhausted else consume_next_token(ctx)
+            if res is None:
+                ctx.exhausted = True
+                continue
+            token_id, frame_idx = res
+            frame, _ = rec.frame(frame_idx)
+            prepare_cell_states(frame, max_code_point, cells[i, pos])
+            targets[i, pos] = token_id % vocab
+    return torch.from_numpy(cells.view(np.int32)), torch.from_numpy(targets)
+
+
+def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None) -> List[dict]:
+    """The outer loop: data → ``train_step`` → cursor commit → validation → checkpoint."""
+    cfg = trainer.cfg
+    local_batch = cfg.micro_batch_size * trainer.grad_accum_steps
+    iterator = None
+    if source is None:
+        if cfg.train_data_config.recordings_directory_path:
+            iterator = RecordingDatasetIterator(
+                os.path.join(trainer.working_dir, cfg.train_data_config.recordings_directory_path), local_batch,
+                cfg.train_sequence_length, cfg.train_data_config.iteration_seed + trainer.rank)
+        else:
+            source = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point,
+                                          trainer.vocab, seed=cfg.train_data_config.iteration_seed + trainer.rank)
+    restored = trainer.load_latest_checkpoint()
+    if iterator is not None and restored is not None and restored.batch_size:
+        iterator.restore(restored)
+    cursor_path = cfg.checkpointing.dataset_cursor_path
+    if cursor_path:
+        cursor_path = os.path.join(trainer.working_dir, cursor_path)
+        snap = DatasetCursorCommitter.load(cursor_path)
+        if snap is not None and iterator is not None:
+            if snap.step_count != trainer.step_count:
+                LOG("WARN", f"dataset cursor is at step {snap.step_count}, checkpoint at {trainer.step_count}")
+            from .data.iterator import DatasetIteratorState
+            iterator.restore(DatasetIteratorState(rng_state=snap.rng_state, batch_size=local_batch))
+        trainer.cursor = DatasetCursorCommitter(cursor_path)
+    limit = cfg.max_training_steps if max_steps is None else min(cfg.max_training_steps, trainer.step_count + max_steps)
+    mc = cfg.model_config
+    while trainer.step_count < limit:
+        with gputx_range("fbamtrain::next_batch_wait"):
+            if iterator is not None:
+                batch = iterator.next_batch()
+                cells, targets = build_batch_from_recordings(batch, trainer.tokenizer, cfg.train_sequence_length,
+                                                             cfg.frame_rows, cfg.frame_cols, trainer.vocab,
+                                                             mc.max_code_point)
+            else:
+                cells, targets = source.next_batch(local_batch, cfg.train_sequence_length)
+        trainer.train_step(cells, targets)
+        if trainer.cursor is not None and iterator is not None:
+            st = iterator.cursor_checkpoint()
+            trainer.cursor.commit(DatasetCursorSnapshot(trainer.step_count, st.rng_state, local_batch,
+                                                        cfg.train_sequence_length))
+        if cfg.enable_validation and cfg.validation_interval and trainer.step_count % cfg.validation_interval == 0:
+            with gputx_range("fbamtrain::validation"):
+                vsrc = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, mc.max_code_point, trainer.vocab,
+                                            seed=cfg.validation_data_config.iteration_seed, pin=False)
+                vc, vt = vsrc.next_batch(cfg.micro_batch_size, cfg.validation_sequence_length)
+                trainer.logger.log_validation(trainer.step_count, trainer.validation_loss(vc, vt))
+        if trainer.step_count % cfg.checkpointing.checkpoint_interval == 0 and trainer.rank == 0:
+            trainer.save_checkpoint(iterator.checkpoint() if iterator is not None else None)
+    trainer.logger.drain()
+    if iterator is not None:
+        iterator.close()
+    return list(trainer.logger.history)

@@ -1,0 +1,46 @@
+"""Debug switches that stand in for a sanitizer on shared GPUs.
+
+* ``FBAMTRAIN_SYNC_EVERY_OP=1`` — synchronise the device after every custom-op launch so an
+  asynchronous failure is attributed to the op that caused it (reference:
+  ``tensorlib/src/execution_backend.cpp:39-43, 619-622``).
+* ``FBAMTRAIN_POISON_ALLOC=1`` — fill every buffer obtained through :func:`fresh` with NaN (floats)
+  or 0xFF bytes so reads of uninitialised memory surface in the numerics (the reference bisects the
+  same class of bug by zero-filling op ranges, ``execution_backend.cpp:77-155``).
+* ``FBAMTRAIN_DEBUG_KERNEL_LAUNCH=1`` — print one line per custom-kernel launch with its
+  arguments (reference: ``execution_backend.cpp:796-803``).
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import torch
+
+
+def _flag(name: str) -> bool:
+    return os.environ.get(name, "0") not in ("", "0", "false", "False")
+
+
+SYNC_EVERY_OP = _flag("FBAMTRAIN_SYNC_EVERY_OP")
+POISON_ALLOC = _flag("FBAMTRAIN_POISON_ALLOC")
+DEBUG_KERNEL_LAUNCH = _flag("FBAMTRAIN_DEBUG_KERNEL_LAUNCH")
+
+
+def fresh(shape, dtype, device) -> torch.Tensor:
+    """``torch.empty`` that honours the poison switch."""
+    t = torch.empty(shape, dtype=dtype, device=device)
+    if POISON_ALLOC and t.numel():
+        if t.is_floating_point():
+            t.fill_(float("nan"))
+        else:
+            t.view(torch.uint8).fill_(0xFF)
+    return t
+
+
+def after_launch(name: str, *args) -> None:
+    if DEBUG_KERNEL_LAUNCH:
+        desc = ", ".join(f"{tuple(a.shape)}:{str(a.dtype).replace('torch.', '')}" if isinstance(a, torch.Tensor)
+                         else repr(a) for a in args)
+        sys.stdout.write(f"[launch] {name}({desc})\n")
+    if SYNC_EVERY_OP and torch.cuda.is_available():
+        torch.cuda.synchronize()

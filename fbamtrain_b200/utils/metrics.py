@@ -1,0 +1,132 @@
+"""Step metrics without host synchronisation in the training loop.
+
+``LossRingBuffer`` keeps 128 device scalars; micro-batch losses are added on the device, and when a
+step is finalised its slot is copied to pinned host memory on a side stream behind an event.
+``AsyncStepLogger`` is a thread that consumes finished steps: it waits on the step's end event,
+reads the loss slot, and emits ``Step N took s seconds; seqlen/time = …; loss/train = …`` plus — when
+``FBAMTRAIN_METRICS_JSON`` is set — one JSON object per line
+(``{"step": N, "step_time_sec": …, "loss/train": …}``; validation lines use ``loss/validation``).
+Dropped steps discard their slot.  (reference: ``src/loss_accumulation_ring_buffer.cpp:67-189``,
+``src/async_step_logger.cpp:71-186``, ``include/async_step_logger.h:15-123``.)
+"""
+from __future__ import annotations
+
+import json
+import os
+import queue
+import sys
+import threading
+import time
+from dataclasses import dataclass
+from typing import Callable, List, Optional
+
+import torch
+
+from .logging import LOG
+
+RING_SLOTS = 128
+
+
+class LossRingBuffer:
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.ring = torch.zeros(RING_SLOTS, dtype=torch.float32, device=device)
+        self.host = torch.zeros(RING_SLOTS, dtype=torch.float32)
+        self.cuda = device.type == "cuda"
+        if self.cuda:
+            self.host = self.host.pin_memory()
+            self.d2h = torch.cuda.Stream(device=device)
+
+    def begin(self, step: int) -> None:
+        self.ring[step % RING_SLOTS].zero_()
+
+    def accumulate(self, step: int, loss: torch.Tensor) -> None:
+        self.ring[step % RING_SLOTS].add_(loss.detach().float())
+
+    def finalize(self, step: int):
+        """Starts the device→host copy of the step's slot; returns an event to wait on (or None on CPU)."""
+        slot = step % RING_SLOTS
+        if not self.cuda:
+            self.host[slot] = self.ring[slot]
+            return None
+        ready = torch.cuda.Event()
+        ready.record()
+        with torch.cuda.stream(self.d2h):
+            self.d2h.wait_event(ready)
+            self.host[slot].copy_(self.ring[slot], non_blocking=True)
+            done = torch.cuda.Event()
+            done.record()
+        return done
+
+    def read(self, step: int) -> float:
+        return float(self.host[step % RING_SLOTS])
+
+
+@dataclass
+class StepRecord:
+    step: int
+    start_event: object
+    end_event: object
+    loss_event: object
+    seq_len: int
+    batch: int
+    dropped: bool = False
+    wall_start: float = 0.0
+    wall_end: float = 0.0
+
+
+class AsyncStepLogger:
+    def __init__(self, ring: LossRingBuffer, sink: Optional[Callable[[dict], None]] = None):
+        self.ring = ring
+        self.sink = sink
+        self.json_lines = bool(os.environ.get("FBAMTRAIN_METRICS_JSON"))
+        self.history: List[dict] = []
+        self._q: "queue.Queue[Optional[StepRecord]]" = queue.Queue()
+        self._thread = threading.Thread(target=self._loop, name="fbam-step-logger", daemon=True)
+        self._thread.start()
+
+    def submit(self, rec: StepRecord) -> None:
+        self._q.put(rec)
+
+    def log_validation(self, step: int, loss: float) -> None:
+        LOG("INFO", f"Step {step} validation loss = {loss:.6f}")
+        if self.json_lines:
+            sys.stdout.write(json.dumps({"step": step, "loss/validation": loss}) + "\n")
+            sys.stdout.flush()
+
+    def _loop(self) -> None:
+        while True:
+            rec = self._q.get()
+            if rec is None:
+                return
+            try:
+                if rec.end_event is not None:
+                    rec.end_event.synchronize()
+                    seconds = rec.start_event.elapsed_time(rec.end_event) / 1e3
+                else:
+                    seconds = rec.wall_end - rec.wall_start
+                if rec.dropped:
+                    LOG("WARN", f"Step {rec.step} dropped after {seconds:.4f} seconds")
+                    continue
+                if rec.loss_event is not None:
+                    rec.loss_event.synchronize()
+                loss = self.ring.read(rec.step)
+                rate = rec.seq_len * rec.batch / seconds if seconds > 0 else float("inf")
+                entry = {"step": rec.step, "step_time_sec": seconds, "loss/train": loss, "frames_per_sec": rate}
+                self.history.append(entry)
+                LOG("INFO", f"Step {rec.step} took {seconds:.4f} seconds; seqlen/time = "
+                            f"{rec.seq_len / seconds if seconds > 0 else float('inf'):.2f}; loss/train = {loss:.6f}")
+                if self.json_lines:
+                    sys.stdout.write(json.dumps({"step": rec.step, "step_time_sec": seconds, "loss/train": loss}) + "\n")
+                    sys.stdout.flush()
+                if self.sink is not None:
+                    self.sink(entry)
+            finally:
+                self._q.task_done()
+
+    def drain(self) -> None:
+        self._q.join()
+
+    def close(self) -> None:
+        self._q.put(None)
+        self._thread.join()
