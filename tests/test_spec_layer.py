@@ -1,0 +1,188 @@
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from fbamtrain_b200.data import (ArrayRecording, DatasetCursorCommitter, DatasetCursorSnapshot,
+                                 RecordingDatasetIterator, StreamTokenizationContext, SyntheticBatchSource,
+                                 SyntheticRecording, consume_next_token, prepare_cell_states)
+from fbamtrain_b200.data.iterator import DatasetIteratorState
+from fbamtrain_b200.rng import SplitMix64
+from fbamtrain_b200.tokenizer import Tokenizer
+from fbamtrain_b200.utils import safetensors_io as st
+from fbamtrain_b200.utils.testing import assert_similar
+
+
+def test_splitmix64_known_vectors():
+    # First outputs of SplitMix64 seeded with 0 and with 1234567 (published test vectors of the algorithm).
+    r = SplitMix64(0)
+    assert [r.randu64() for _ in range(3)] == [0xE220A8397B1DCDAF, 0x6E789E6AA1B965F4, 0x06C45D188009454F]
+    r = SplitMix64(1234567)
+    assert [r.randu64() for _ in range(2)] == [6457827717110365317, 3203168211198807973]
+    r = SplitMix64(42)
+    v = [r.randint(3, 10) for _ in range(100)]
+    assert min(v) >= 3 and max(v) < 10
+    with pytest.raises(ValueError):
+        r.randint(5, 5)
+
+
+def test_tokenizer_sort_trie_and_longest_match(tmp_path):
+    lines = ["# FBAM_TOK v1.0\n", '"a"\n', '"ab"\n', '"\\u001b[A"\n', '"b"\n', "\n", '"abc"\n']
+    p = tmp_path / "tok.txt"
+    p.write_text("".join(lines), encoding="utf-8")
+    tok = Tokenizer.from_file(str(p))
+    # stable sort by length, longest first: "\x1b[A", "abc" (len 3), "ab", then "a", "b" in file order
+    assert tok.tokens == ["\x1b[A", "abc", "ab", "a", "b"]
+    h = tok.new_handle()
+    h.add_char(ord("a"))
+    assert h.current_token_id() == 3 and h.has_continuation()
+    h.add_char(ord("b"))
+    assert h.current_token_id() == 2
+    h.add_char(ord("x"))
+    assert h.is_dead() and h.current_token_id() is None
+    h.reset()
+    assert not h.is_dead()
+    assert [t for t, _ in tok.encode_longest_match("abcabz\x1b[Ab")] == [1, 2, 0, 4]
+    with pytest.raises(ValueError, match="header"):
+        Tokenizer.from_lines(["# WRONG\n"])
+    with pytest.raises(ValueError, match="line 2"):
+        Tokenizer.from_lines(["# FBAM_TOK v1.0\n", "not json\n"])
+
+
+def test_reference_tokenizer_file_if_present():
+    path = "/root/reference/working_dir/tokenizer.txt"
+    if not os.path.exists(path):
+        pytest.skip("reference tree not mounted")
+    tok = Tokenizer.from_file(path)
+    assert len(tok) == 20351
+    lens = [len(t) for t in tok.tokens]
+    assert lens == sorted(lens, reverse=True)
+
+
+def test_token_stream_consumption_pairs_token_with_start_frame():
+    tok = Tokenizer(["abc", "ab", "a", "b", "c"])
+    cells = np.zeros((5, 2, 3, 3), dtype=np.uint32)
+    rec = ArrayRecording(cells, ["a", "b", "", "ca", "z"])
+    ctx = StreamTokenizationContext(rec, tok, 0)
+    out = []
+    while True:
+        r = consume_next_token(ctx)
+        if r is None:
+            break
+        out.append(r)
+    # "a","b","c" spread over frames 0,1,3 form the longest token "abc" which started on frame 0
+    assert out == [(0, 0), (2, 3)]
+
+
+def test_prepare_cell_states_clamps_codepoints():
+    frame = np.array([[[300, 0x112233, 0xFF445566], [5, 1, 2]]], dtype=np.uint32)
+    cs = prepare_cell_states(frame, 256)
+    assert cs.tolist() == [[255, 0x112233, 0x445566], [5, 1, 2]]
+
+
+def test_synthetic_recording_resamples_five_percent():
+    rec = SyntheticRecording(24, 80, 6, seed=0, cell_vocab=256)
+    a, _ = rec.frame(0)
+    b, _ = rec.frame(1)
+    changed = (a.reshape(-1, 3) != b.reshape(-1, 3)).any(-1).sum()
+    assert 0 < changed <= round(0.05 * 24 * 80)
+    src = SyntheticBatchSource(8, 16, 512, 64, seed=3, pin=False)
+    cells, tg = src.next_batch(2, 5)
+    assert cells.shape == (2, 5, 128, 3) and tg.shape == (2, 5)
+    assert int(cells[..., 0].max()) < 512 and int(tg.max()) < 64
+    frac = (cells[:, 1:, :, 0] != cells[:, :-1, :, 0]).float().mean()
+    assert frac <= 0.05 + 1e-6
+
+
+def _recs(n=3):
+    return [SyntheticRecording(4, 6, 40 + 7 * i, seed=i) for i in range(n)]
+
+
+def test_iterator_sampling_matches_rng_contract_and_restores():
+    it = RecordingDatasetIterator(None, batch_size=4, sequence_length=16, seed=99, recordings=_recs())
+    rng = SplitMix64(99)
+    totals = [40, 47, 54]
+    b1 = it.next_batch()
+    exp_idx, exp_start = [], []
+    for _ in range(4):
+        i = rng.randint(0, 3)
+        exp_idx.append(i)
+        exp_start.append(rng.randint(0, max(0, totals[i] - 16) + 1))
+    assert b1.indices == exp_idx and b1.start_positions == exp_start
+    state = it.checkpoint()              # describes the *prepared* (next) batch
+    cursor = it.cursor_checkpoint()      # RNG after the batch handed out
+    b2 = it.next_batch()
+    assert state.prepared_indices == b2.indices and state.prepared_start_positions == b2.start_positions
+    b3 = it.next_batch()
+    it.restore(state)
+    r2 = it.next_batch()
+    r3 = it.next_batch()
+    assert (r2.indices, r2.start_positions) == (b2.indices, b2.start_positions)
+    assert (r3.indices, r3.start_positions) == (b3.indices, b3.start_positions)
+    it.restore(DatasetIteratorState(rng_state=cursor.rng_state, batch_size=4))  # RNG-only form
+    c2 = it.next_batch()
+    assert (c2.indices, c2.start_positions) == (b2.indices, b2.start_positions)
+    with pytest.raises(RuntimeError, match="batch size"):
+        it.restore(DatasetIteratorState(rng_state=1, batch_size=5))
+    it.close()
+
+
+def test_iterator_reads_directory_sorted(tmp_path):
+    for i, name in enumerate(["b", "a", "c"]):
+        r = SyntheticRecording(2, 3, 10, seed=i)
+        ArrayRecording(np.stack([r.frame(t)[0] for t in range(10)]), [r.frame(t)[1] for t in range(10)]).save(
+            str(tmp_path / f"{name}.fbrec.npz"))
+    it = RecordingDatasetIterator(str(tmp_path), 2, 4, seed=1)
+    assert [os.path.basename(p) for p in it._paths] == ["a.fbrec.npz", "b.fbrec.npz", "c.fbrec.npz"]
+    it.close()
+    with pytest.raises(RuntimeError):
+        RecordingDatasetIterator(str(tmp_path / "nope"), 2, 4, seed=1)
+
+
+def test_cursor_durable_roundtrip(tmp_path):
+    path = str(tmp_path / "ck" / "cursor.json")
+    assert DatasetCursorCommitter.load(path) is None
+    c = DatasetCursorCommitter(path)
+    for s in range(20):
+        c.commit(DatasetCursorSnapshot(s, 2 ** 63 + s, 8, 1024))
+    assert c.flush()
+    c.close()
+    snap = DatasetCursorCommitter.load(path)
+    assert snap == DatasetCursorSnapshot(19, 2 ** 63 + 19, 8, 1024)
+    d = json.load(open(path))
+    assert d["version"] == 1 and set(d) == {"version", "step_count", "rng_state", "batch_size", "sequence_length"}
+    assert not os.path.exists(path + ".tmp")
+
+
+def test_safetensors_roundtrip_and_validation(tmp_path):
+    tensors = {"a": torch.randn(3, 4), "b": torch.randn(5).to(torch.bfloat16), "c": torch.randn(2, 2).half(),
+               "u64": torch.tensor([2 ** 63 + 1], dtype=torch.uint64), "u32": torch.tensor([1, 2], dtype=torch.uint32),
+               "empty": torch.zeros(0, dtype=torch.uint32)}
+    p = str(tmp_path / "x.safetensors")
+    st.save_file(tensors, p)
+    back = st.load_file(p)
+    assert set(back) == set(tensors)
+    for k in tensors:
+        assert back[k].dtype == tensors[k].dtype and back[k].shape == tensors[k].shape
+        assert torch.equal(back[k].view(torch.uint8), tensors[k].view(torch.uint8))
+    header, _ = st.read_header(p)
+    assert header["u64"]["dtype"] == "U64" and header["b"]["dtype"] == "BF16"
+    with pytest.raises(ValueError):
+        st.load_inplace(p, {"a": torch.zeros(4, 3)})
+    dst = {"a": torch.zeros(3, 4)}
+    st.load_inplace(p, dst)
+    assert torch.equal(dst["a"], tensors["a"])
+
+
+def test_assert_similar_rules():
+    e = torch.tensor([1.0, 2.0]).bfloat16()
+    a = torch.tensor([1.0078125, 2.0]).bfloat16()  # one bf16 ulp above 1.0
+    assert_similar(e, a, 1e-6)
+    with pytest.raises(AssertionError):
+        assert_similar(e.float(), a.float(), 1e-6)
+    with pytest.raises(AssertionError, match="non-finite"):
+        assert_similar(torch.tensor([float("nan")]), torch.tensor([0.0]), 1.0)
+    with pytest.raises(AssertionError, match="shape"):
+        assert_similar(torch.zeros(2), torch.zeros(3), 1.0)
