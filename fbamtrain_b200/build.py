@@ -1,0 +1,92 @@
+"""In-tree build of the native libraries.
+
+``build_all()`` compiles every ``csrc/*.cu`` for ``sm_100a`` with ``nvcc`` and links them into
+``lib/libfbam_kernels.so``; ``csrc/runtime/*.cpp`` (host-only runtime: tokenizer trie, SplitMix64,
+safetensors, durable cursor writer, TCP rendezvous, membership master) goes into
+``lib/libfbam_runtime.so`` with ``g++``.  Objects are rebuilt only when their source (or a header)
+is newer.  Run as ``python -m fbamtrain_b200.build``.
+"""
+from __future__ import annotations
+
+import glob
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from typing import List
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "lib")
+OBJ = os.path.join(LIB, "obj")
+KERNELS_SO = os.path.join(LIB, "libfbam_kernels.so")
+RUNTIME_SO = os.path.join(LIB, "libfbam_runtime.so")
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread"]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _newest(paths: List[str]) -> float:
+    return max((os.path.getmtime(p) for p in paths), default=0.0)
+
+
+def _compile(cmd: List[str], log_path: str) -> None:
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    with open(log_path, "w") as f:
+        f.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+    if r.returncode != 0:
+        raise RuntimeError(f"build failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+
+
+def build_kernels(force: bool = False, verbose: bool = False) -> str:
+    os.makedirs(OBJ, exist_ok=True)
+    sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+    headers = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh"))
+    hdr_time = _newest(headers)
+    nvcc = _nvcc()
+    jobs, objs = [], []
+    for src in sources:
+        obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
+        objs.append(obj)
+        if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_time):
+            jobs.append(([nvcc] + NVCC_FLAGS + ["-I", CSRC, "-c", src, "-o", obj], obj + ".log"))
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            list(ex.map(lambda j: _compile(*j), jobs))
+    if jobs or not os.path.exists(KERNELS_SO) or os.path.getmtime(KERNELS_SO) < _newest(objs):
+        _compile([nvcc, "-shared", "-o", KERNELS_SO] + objs + ["-lcudart"], os.path.join(OBJ, "link_kernels.log"))
+    if verbose:
+        for _, log in jobs:
+            sys.stdout.write(open(log).read())
+    return KERNELS_SO
+
+
+def build_runtime(force: bool = False) -> str:
+    os.makedirs(OBJ, exist_ok=True)
+    sources = sorted(glob.glob(os.path.join(CSRC, "runtime", "*.cpp")))
+    if not sources:
+        return ""
+    headers = glob.glob(os.path.join(CSRC, "runtime", "*.h"))
+    if force or not os.path.exists(RUNTIME_SO) or os.path.getmtime(RUNTIME_SO) < _newest(sources + headers):
+        cxx = shutil.which("g++") or "g++"
+        _compile([cxx] + CXX_FLAGS + ["-shared", "-o", RUNTIME_SO] + sources, os.path.join(OBJ, "link_runtime.log"))
+    return RUNTIME_SO
+
+
+def build_all(force: bool = False, verbose: bool = False) -> None:
+    build_kernels(force, verbose)
+    build_runtime(force)
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print("built:", KERNELS_SO, RUNTIME_SO if os.path.exists(RUNTIME_SO) else "")

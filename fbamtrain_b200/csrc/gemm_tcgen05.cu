@@ -1,0 +1,490 @@
+// Persistent, warp-specialised bf16 GEMM / implicit-GEMM convolution for sm_100a.
+//
+//   D[M, N] = epilogue( A[M, K] · B[N, K]ᵀ )        fp32 accumulation in tensor memory
+//
+// One CTA per SM loops over 128 x BN output tiles.  Warp 0 streams operand tiles into a 4-stage
+// shared-memory ring with TMA (128-byte swizzle); warp 1 issues tcgen05.mma (one elected thread)
+// into one of two TMEM accumulators; warps 2-5 drain the other accumulator with tcgen05.ld, apply the
+// fused epilogue and store — so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Operand sources (template MODE):
+//   GEMM   A and B are 2-D matrices.  Each may be K-major (row = M/N index, K contiguous) or MN-major
+//          (row = K index, M/N contiguous); MN-major tiles are fetched as 64-wide column panels and
+//          consumed through the transposed-operand form of the UMMA descriptor, so weight-gradient
+//          products (Xᵀ·dY) need no explicit transposes.
+//   CONV   A is an NHWC activation tensor reached through a 4-D tensor map; a K block is one filter
+//          tap x 64 input channels, and the tile's 128 rows are a TN x TH x TW brick of output pixels,
+//          so the im2col gather is done by TMA (element strides give the convolution stride, out-of-
+//          range coordinates give zero padding).  Forward and data-gradient convolutions both map
+//          onto this mode (the data gradient of a stride-2 convolution is four parity classes, each a
+//          stride-1 gather over the taps that reach that parity).
+//
+// Epilogue (runtime flags): + bias[n], GELU (optionally storing the pre-activation), + residual[m, n],
+// x gelu'(aux[m, n]) (fuses the activation gradient into the GEMM that produces dH), C += (fp32
+// accumulate-into-output), bf16 or fp32 output.
+//
+// Every mbarrier wait is bounded; on timeout the CTA writes an error code to `status` and unwinds.
+#include "gemm_tcgen05.h"
+#include "tc05.cuh"
+
+namespace {
+
+using namespace tc05;
+
+constexpr int BM = 128;
+constexpr int BK = 64;       // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kNumEpilogueWarps = 4;
+constexpr int kThreads = 32 * (2 + kNumEpilogueWarps);
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024: manual alignment slack
+};
+
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_grad_f(float x) {
+  return 0.5f * (1.0f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+
+// Row of the output tile -> element offset of that row in D (or -1 when the row is out of range).
+__device__ __forceinline__ long long row_offset(const GemmParams& p, int tile_m, int row) {
+  if (p.mode == GEMM_MODE_PLAIN) {
+    int m = tile_m * BM + row;
+    return m < p.M ? (long long)m * p.ldd : -1;
+  }
+  // CONV: tile_m enumerates (n-brick, h-brick, w-brick)
+  const ConvGeom& g = p.conv;
+  int wb = tile_m % g.tiles_w;
+  int hb = (tile_m / g.tiles_w) % g.tiles_h;
+  int nb = tile_m / (g.tiles_w * g.tiles_h);
+  int wl = row % g.tw, hl = (row / g.tw) % g.th, nl = row / (g.tw * g.th);
+  int n = nb * g.tn + nl, h = hb * g.th + hl, w = wb * g.tw + wl;
+  if (n >= g.batch || h >= g.grid_h || w >= g.grid_w) return -1;
+  int oh = h * g.out_mul + g.out_off_h, ow = w * g.out_mul + g.out_off_w;
+  if (oh >= g.out_h || ow >= g.out_w) return -1;
+  return (((long long)n * g.out_h + oh) * g.out_w + ow) * p.ldd;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const GemmParams p) {
+  using L = SmemLayout<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);
+  uint64_t* empty_bar = full_bar + L::kStages;
+  uint64_t* tmem_full = empty_bar + L::kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = p.tiles_m * tiles_n;
+  const int k_blocks = p.k_blocks;
+  constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+    for (int s = 0; s < L::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], kNumEpilogueWarps);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int tile_m = tile / tiles_n, tile_n = tile % tiles_n;
+        int cn = 0, ch = 0, cw = 0;
+        if (p.mode == GEMM_MODE_CONV) {
+          const ConvGeom& g = p.conv;
+          cw = (tile_m % g.tiles_w) * g.tw * g.in_mul;
+          ch = ((tile_m / g.tiles_w) % g.tiles_h) * g.th * g.in_mul;
+          cn = (tile_m / (g.tiles_w * g.tiles_h)) * g.tn;
+        }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          if (p.mode == GEMM_MODE_CONV) {
+            const ConvGeom& g = p.conv;
+            const int tap = kb / g.c_blocks, cb = kb % g.c_blocks;
+            tma_load_4d(sa, &map_a, &full_bar[stage], cb * BK, cw + g.tap_dw[tap], ch + g.tap_dh[tap], cn);
+          } else if (p.a_mn_major) {
+            tma_load_2d(sa, &map_a, &full_bar[stage], tile_m * BM, kb * BK);
+            tma_load_2d(sa + BK * 128, &map_a, &full_bar[stage], tile_m * BM + 64, kb * BK);
+          } else {
+            tma_load_2d(sa, &map_a, &full_bar[stage], kb * BK, tile_m * BM);
+          }
+          if (p.b_mn_major) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * BK * 128, &map_b, &full_bar[stage], tile_n * BN + j * 64, kb * BK);
+          } else {
+            tma_load_2d(sb, &map_b, &full_bar[stage], kb * BK, tile_n * BN);
+          }
+          if (++stage == L::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) atomicExch(p.status, GEMM_ERR_PRODUCER_TIMEOUT);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn_major != 0, p.b_mn_major != 0);
+      // K-major: 8-row groups are 1024 B apart (SBO); one UMMA_K step = 32 B inside the swizzle row.
+      // MN-major: 64-wide column panels are BK*128 B apart (LBO), 8-row K groups 1024 B apart (SBO);
+      //           one UMMA_K step = 16 rows = 2048 B.
+      const uint32_t a_lbo = p.a_mn_major ? BK * 128 : 16, b_lbo = p.b_mn_major ? BK * 128 : 16;
+      const uint32_t a_kstep = p.a_mn_major ? UMMA_K * 128 : UMMA_K * 2;
+      const uint32_t b_kstep = p.b_mn_major ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { ok = false; break; }
+        fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
+          fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
+            const uint64_t db = make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
+            mma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0);
+          }
+          mma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
+          if (++stage == L::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit(&tmem_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (!ok) atomicExch(p.status, GEMM_ERR_MMA_TIMEOUT);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int lane_group = warp % 4;  // TMEM lanes [32*lane_group, +32) are visible to this warp
+    const int row = lane_group * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int tile_m = tile / tiles_n, tile_n = tile % tiles_n;
+      if (!mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
+      fence_after_sync();
+      const long long roff = row_offset(p, tile_m, row);
+      const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c0, r);
+        tmem_ld_wait();
+        const int n0 = tile_n * BN + c0;
+        if (roff < 0 || n0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        const bool full_vec = (n0 + 32 <= p.N) && p.vec_ok;
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (n0 + j < p.N)
+              v[j] += p.bias_fp32 ? reinterpret_cast<const float*>(p.bias)[n0 + j]
+                                  : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n0 + j]);
+        }
+        if (p.preact_out != nullptr) {
+          __nv_bfloat16* po = p.preact_out + roff + n0;
+          if (full_vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              __align__(16) __nv_bfloat162 h[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+              *reinterpret_cast<uint4*>(po + j) = *reinterpret_cast<uint4*>(h);
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) po[j] = __float2bfloat16(v[j]);
+          }
+        }
+        if (p.act == GEMM_ACT_GELU) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
+        } else if (p.act == GEMM_ACT_RELU) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+        }
+        if (p.gelu_grad_in != nullptr) {
+          const __nv_bfloat16* gi = p.gelu_grad_in + roff + n0;
+          if (full_vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 raw = *reinterpret_cast<const uint4*>(gi + j);
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                float2 f = __bfloat1622float2(h[q]);
+                v[j + 2 * q] *= gelu_grad_f(f.x);
+                v[j + 2 * q + 1] *= gelu_grad_f(f.y);
+              }
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) v[j] *= gelu_grad_f(__bfloat162float(gi[j]));
+          }
+        }
+        if (p.residual != nullptr) {
+          const __nv_bfloat16* ri = p.residual + roff / p.ldd * p.ldr + n0;
+          if (full_vec && (p.ldr % 8 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 raw = *reinterpret_cast<const uint4*>(ri + j);
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                float2 f = __bfloat1622float2(h[q]);
+                v[j + 2 * q] += f.x;
+                v[j + 2 * q + 1] += f.y;
+              }
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) v[j] += __bfloat162float(ri[j]);
+          }
+        }
+        if (p.out_fp32) {
+          float* out = reinterpret_cast<float*>(p.D) + roff + n0;
+          if (p.accumulate == GEMM_ACC_ATOMIC) {
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) atomicAdd(out + j, v[j]);
+          } else if (full_vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              if (p.accumulate) {
+                float4 c = *reinterpret_cast<const float4*>(out + j);
+                o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+              }
+              *reinterpret_cast<float4*>(out + j) = o;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) out[j] = p.accumulate ? out[j] + v[j] : v[j];
+          }
+        } else {
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + roff + n0;
+          if (full_vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (p.accumulate) {
+                uint4 raw = *reinterpret_cast<const uint4*>(out + j);
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  float2 f = __bfloat1622float2(h[q]);
+                  v[j + 2 * q] += f.x;
+                  v[j + 2 * q + 1] += f.y;
+                }
+              }
+              __align__(16) __nv_bfloat162 h[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+              *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N)
+                out[j] = __float2bfloat16(p.accumulate ? __bfloat162float(out[j]) + v[j] : v[j]);
+          }
+        }
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (!ok && lane == 0) atomicExch(p.status, GEMM_ERR_EPILOGUE_TIMEOUT);
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// -------------------------------------------------------------------------------------------------
+// host side
+// -------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// 2-D bf16 matrix [rows, cols] with row pitch `ld` elements; box = 64 columns x `box_rows` rows.
+int encode_2d(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return GEMM_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld * 2) % 16) return GEMM_ERR_ALIGNMENT;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : GEMM_ERR_TENSORMAP;
+}
+
+// NHWC bf16 tensor [n, h, w, c]; box = 64 channels x (tw, th, tn) pixels visited with `stride`.
+int encode_nhwc(CUtensorMap* map, const void* base, int n, int h, int w, int c, int tn, int th, int tw, int stride) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return GEMM_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (c * 2) % 16) return GEMM_ERR_ALIGNMENT;
+  cuuint64_t dims[4] = {(cuuint64_t)c, (cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)n};
+  cuuint64_t strides[3] = {(cuuint64_t)c * 2, (cuuint64_t)w * c * 2, (cuuint64_t)h * w * c * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)((tw - 1) * stride + 1), (cuuint32_t)((th - 1) * stride + 1), (cuuint32_t)tn};
+  cuuint32_t estr[4] = {1, (cuuint32_t)stride, (cuuint32_t)stride, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : GEMM_ERR_TENSORMAP;
+}
+
+int g_num_sms = 0;
+
+template <int BN>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess)
+      return GEMM_ERR_LAUNCH;
+    configured = true;
+  }
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int tiles = p.tiles_m * ((p.N + BN - 1) / BN);
+  int grid = tiles < g_num_sms ? tiles : g_num_sms;
+  if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
+  gemm_kernel<BN><<<grid, kThreads, L::kTotal, stream>>>(ma, mb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : GEMM_ERR_LAUNCH;
+}
+
+int pick_bn(int n, int requested) {
+  if (requested == 64 || requested == 128 || requested == 256) return requested;
+  if (n <= 64) return 64;
+  if (n <= 128) return 128;
+  return 256;
+}
+
+}  // namespace
+
+extern "C" int fbam_gemm_bf16(const void* A, long long lda, int a_mn_major, const void* B, long long ldb,
+                              int b_mn_major, int M, int N, int K, GemmParams* params, void* stream) {
+  GemmParams p = *params;
+  if (M <= 0 || N <= 0 || K <= 0) return GEMM_ERR_SHAPE;
+  p.mode = GEMM_MODE_PLAIN;
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.k_blocks = (K + BK - 1) / BK;
+  const int bn = pick_bn(N, p.bn);
+  const int elt = p.out_fp32 ? 4 : 2;
+  p.vec_ok = (p.ldd % (16 / elt) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&
+             (p.preact_out == nullptr || (reinterpret_cast<uintptr_t>(p.preact_out) & 15) == 0) &&
+             (p.gelu_grad_in == nullptr || (reinterpret_cast<uintptr_t>(p.gelu_grad_in) & 15) == 0) &&
+             (p.residual == nullptr || (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) && (p.ldd % 8 == 0);
+  CUtensorMap ma, mb;
+  int e;
+  if (a_mn_major) e = encode_2d(&ma, A, K, M, lda, 64);  // rows = K, cols = M, panels of 64 columns
+  else e = encode_2d(&ma, A, M, K, lda, BM);
+  if (e) return e;
+  if (b_mn_major) e = encode_2d(&mb, B, K, N, ldb, 64);
+  else e = encode_2d(&mb, B, N, K, ldb, bn);
+  if (e) return e;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 64) return launch<64>(ma, mb, p, s);
+  if (bn == 128) return launch<128>(ma, mb, p, s);
+  return launch<256>(ma, mb, p, s);
+}
+
+// Implicit-GEMM convolution pass.  `X` is the gathered NHWC tensor [batch, in_h, in_w, C]; `Wmat` is the
+// filter matrix [N, taps*C] (K-major; tap-major then channel).  See ConvGeom for the tiling fields.
+extern "C" int fbam_conv_bf16(const void* X, int in_h, int in_w, int C, const void* Wmat, long long ldw, int N,
+                              GemmParams* params, void* stream) {
+  GemmParams p = *params;
+  ConvGeom& g = p.conv;
+  if (C % 64 != 0 || g.tn * g.th * g.tw != BM || g.num_taps < 1 || g.num_taps > 9) return GEMM_ERR_SHAPE;
+  p.mode = GEMM_MODE_CONV;
+  p.a_mn_major = 0; p.b_mn_major = 0;
+  g.c_blocks = C / 64;
+  g.tiles_w = (g.grid_w + g.tw - 1) / g.tw;
+  g.tiles_h = (g.grid_h + g.th - 1) / g.th;
+  const int tiles_nb = (g.batch + g.tn - 1) / g.tn;
+  p.tiles_m = g.tiles_w * g.tiles_h * tiles_nb;
+  p.M = p.tiles_m * BM;
+  p.N = N; p.K = g.num_taps * C;
+  p.k_blocks = g.num_taps * g.c_blocks;
+  const int bn = pick_bn(N, p.bn);
+  const int elt = p.out_fp32 ? 4 : 2;
+  p.vec_ok = (p.ldd % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) && (p.ldd % (16 / elt) == 0);
+  CUtensorMap ma, mb;
+  int e = encode_nhwc(&ma, X, g.batch, in_h, in_w, C, g.tn, g.th, g.tw, g.in_mul);
+  if (e) return e;
+  e = encode_2d(&mb, Wmat, N, p.K, ldw, bn);
+  if (e) return e;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 64) return launch<64>(ma, mb, p, s);
+  if (bn == 128) return launch<128>(ma, mb, p, s);
+  return launch<256>(ma, mb, p, s);
+}

@@ -1,0 +1,46 @@
+// Parameter blocks of the tcgen05 GEMM / implicit-GEMM convolution entry points.  The Python side
+// mirrors these structs field for field with ctypes (fbamtrain_b200/ops/native.py).
+#pragma once
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+enum { GEMM_MODE_PLAIN = 0, GEMM_MODE_CONV = 1 };
+enum { GEMM_ACT_NONE = 0, GEMM_ACT_GELU = 1, GEMM_ACT_RELU = 2 };
+enum { GEMM_ACC_NONE = 0, GEMM_ACC_RMW = 1, GEMM_ACC_ATOMIC = 2 };
+enum {
+  GEMM_ERR_SHAPE = 1, GEMM_ERR_ALIGNMENT = 2, GEMM_ERR_TENSORMAP = 3, GEMM_ERR_DRIVER = 4, GEMM_ERR_LAUNCH = 5,
+  GEMM_ERR_PRODUCER_TIMEOUT = 101, GEMM_ERR_MMA_TIMEOUT = 102, GEMM_ERR_EPILOGUE_TIMEOUT = 103
+};
+
+// Geometry of one implicit-GEMM convolution pass.  The 128 rows of an output tile are a brick of
+// tn x th x tw positions of a (batch, grid_h, grid_w) iteration grid.  Grid position (h, w) gathers
+// input pixel (h*in_mul + tap_dh[t], w*in_mul + tap_dw[t]) for tap t and writes output pixel
+// (h*out_mul + out_off_h, w*out_mul + out_off_w) of an (out_h, out_w) image.
+struct ConvGeom {
+  int batch, grid_h, grid_w;
+  int tn, th, tw;
+  int in_mul;
+  int out_mul, out_off_h, out_off_w, out_h, out_w;
+  int num_taps;
+  int tap_dh[9], tap_dw[9];
+  // derived by the launcher
+  int c_blocks, tiles_w, tiles_h;
+};
+
+struct GemmParams {
+  void* D;                          // output, bf16 or fp32, row pitch ldd elements
+  long long ldd;
+  const void* bias;                 // [N] or null
+  const __nv_bfloat16* residual;    // [M, N] pitch ldr, added after the activation, or null
+  long long ldr;
+  __nv_bfloat16* preact_out;        // [M, N] pitch ldd: value before the activation, or null
+  const __nv_bfloat16* gelu_grad_in;  // [M, N] pitch ldd: result is multiplied by gelu'(this), or null
+  int* status;                      // device word, receives an error code on a timed-out wait
+  float alpha;
+  int out_fp32, bias_fp32, act, accumulate;
+  int bn;                           // 0 = choose from N; else 64 / 128 / 256
+  int max_ctas;                     // 0 = one per SM
+  // filled by the launcher
+  int mode, M, N, K, tiles_m, k_blocks, a_mn_major, b_mn_major, vec_ok;
+  ConvGeom conv;
+};

@@ -1,0 +1,695 @@
+// Bandwidth-bound kernels (no tensor cores): normalisation, activations, pooling, cell embedding,
+// cross-entropy, bias-gradient reductions and the fused optimizer update.  All are written for
+// 16-byte vector accesses on bf16 data with fp32 arithmetic, one pass over memory per tensor, grids
+// sized from the problem (rows or 16-byte packets), and predicated tails.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide sum; `scratch` holds 32 floats.  Result is valid in every thread.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < nwarps) ? scratch[threadIdx.x] : 0.0f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) scratch[0] = t;
+  }
+  __syncthreads();
+  return scratch[0];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < nwarps) ? scratch[threadIdx.x] : -INFINITY;
+  if (warp == 0) {
+    t = warp_max(t);
+    if (lane == 0) scratch[0] = t;
+  }
+  __syncthreads();
+  return scratch[0];
+}
+
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_grad_f(float x) {
+  return 0.5f * (1.0f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+
+struct alignas(16) Pack8 { __nv_bfloat162 h[4]; };
+__device__ __forceinline__ void unpack8(const Pack8& p, float* f) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(p.h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ Pack8 pack8(const float* f) {
+  Pack8 p;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p.h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return p;
+}
+
+// ------------------------------------------------------------------------------------------------
+// RMSNorm: one warp per row for dim <= 2048 (kept in registers), bf16 IO, fp32 math.
+// ------------------------------------------------------------------------------------------------
+template <int VEC_PER_LANE>  // dim = VEC_PER_LANE * 32 * 8 at most
+__global__ void rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
+                                   float* __restrict__ rstd, long long rows, int dim, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const bf16* xr = x + row * dim;
+  float v[VEC_PER_LANE][8];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VEC_PER_LANE; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < dim) {
+      unpack8(*reinterpret_cast<const Pack8*>(xr + c), v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+    }
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / dim + eps);
+  if (lane == 0 && rstd != nullptr) rstd[row] = r;
+#pragma unroll
+  for (int i = 0; i < VEC_PER_LANE; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < dim) {
+      float g[8], o[8];
+      unpack8(*reinterpret_cast<const Pack8*>(w + c), g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = v[i][j] * r * g[j];
+      *reinterpret_cast<Pack8*>(y + row * dim + c) = pack8(o);
+    }
+  }
+}
+
+// dx = rstd * (g*dy - xhat * mean(g*dy*xhat));  dgamma[c] += sum_rows dy*xhat (fp32 atomics, one per
+// column per block after an in-block reduction over the block's rows).
+template <int VEC_PER_LANE>
+__global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                   const float* __restrict__ rstd, bf16* __restrict__ dx, float* __restrict__ dgamma,
+                                   long long rows, int dim, int rows_per_warp) {
+  extern __shared__ float sm_dg[];  // [dim]
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) sm_dg[c] = 0.0f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warps = blockDim.x >> 5;
+  float acc[VEC_PER_LANE][8];
+#pragma unroll
+  for (int i = 0; i < VEC_PER_LANE; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+  float g[VEC_PER_LANE][8];
+#pragma unroll
+  for (int i = 0; i < VEC_PER_LANE; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < dim) unpack8(*reinterpret_cast<const Pack8*>(w + c), g[i]);
+  }
+  const long long first = ((long long)blockIdx.x * warps + (threadIdx.x >> 5)) * rows_per_warp;
+  for (int rr = 0; rr < rows_per_warp; ++rr) {
+    const long long row = first + rr;
+    if (row >= rows) break;
+    const float r = rstd[row];
+    float xv[VEC_PER_LANE][8], dv[VEC_PER_LANE][8];
+    float dot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VEC_PER_LANE; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < dim) {
+        unpack8(*reinterpret_cast<const Pack8*>(x + row * dim + c), xv[i]);
+        unpack8(*reinterpret_cast<const Pack8*>(dy + row * dim + c), dv[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xv[i][j] *= r;  // xhat
+          acc[i][j] += dv[i][j] * xv[i][j];
+          dot += dv[i][j] * g[i][j] * xv[i][j];
+        }
+      }
+    }
+    dot = warp_sum(dot) / dim;
+#pragma unroll
+    for (int i = 0; i < VEC_PER_LANE; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < dim) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = r * (dv[i][j] * g[i][j] - xv[i][j] * dot);
+        *reinterpret_cast<Pack8*>(dx + row * dim + c) = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VEC_PER_LANE; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < dim)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) atomicAdd(&sm_dg[c + j], acc[i][j]);
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) atomicAdd(&dgamma[c], sm_dg[c]);
+}
+
+// LayerNorm forward (block per row).
+__global__ void layernorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ b,
+                                     bf16* __restrict__ y, int dim, float eps) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const bf16* xr = x + row * dim;
+  float s = 0.0f;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) s += __bfloat162float(xr[c]);
+  const float mean = block_sum(s, scratch) / dim;
+  float q = 0.0f;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    const float d = __bfloat162float(xr[c]) - mean;
+    q += d * d;
+  }
+  const float r = rsqrtf(block_sum(q, scratch) / dim + eps);
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    float o = (__bfloat162float(xr[c]) - mean) * r * __bfloat162float(w[c]);
+    if (b != nullptr) o += __bfloat162float(b[c]);
+    y[row * dim + c] = __float2bfloat16(o);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// element-wise
+// ------------------------------------------------------------------------------------------------
+// mode 0: y = gelu(x); mode 1: dx = dy * gelu'(x)
+__global__ void gelu_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, bf16* __restrict__ out,
+                            long long n8, int mode) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  float a[8], o[8];
+  unpack8(reinterpret_cast<const Pack8*>(x)[i], a);
+  if (mode == 0) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = gelu_f(a[j]);
+  } else {
+    float d[8];
+    unpack8(reinterpret_cast<const Pack8*>(dy)[i], d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = d[j] * gelu_grad_f(a[j]);
+  }
+  reinterpret_cast<Pack8*>(out)[i] = pack8(o);
+}
+
+// GeGLU over the channel dimension: x [rows, 2C] -> y [rows, C] = value * gelu(gate).
+__global__ void geglu_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long rows, int c) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int c8 = c / 8;
+  if (i >= rows * c8) return;
+  const long long row = i / c8;
+  const int col = (int)(i % c8) * 8;
+  float v[8], g[8], o[8];
+  unpack8(*reinterpret_cast<const Pack8*>(x + row * 2 * c + col), v);
+  unpack8(*reinterpret_cast<const Pack8*>(x + row * 2 * c + c + col), g);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = v[j] * gelu_f(g[j]);
+  *reinterpret_cast<Pack8*>(y + row * c + col) = pack8(o);
+}
+__global__ void geglu_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, bf16* __restrict__ dx,
+                                 long long rows, int c) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int c8 = c / 8;
+  if (i >= rows * c8) return;
+  const long long row = i / c8;
+  const int col = (int)(i % c8) * 8;
+  float v[8], g[8], d[8], dv[8], dg[8];
+  unpack8(*reinterpret_cast<const Pack8*>(x + row * 2 * c + col), v);
+  unpack8(*reinterpret_cast<const Pack8*>(x + row * 2 * c + c + col), g);
+  unpack8(*reinterpret_cast<const Pack8*>(dy + row * c + col), d);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    dv[j] = d[j] * gelu_f(g[j]);
+    dg[j] = d[j] * v[j] * gelu_grad_f(g[j]);
+  }
+  *reinterpret_cast<Pack8*>(dx + row * 2 * c + col) = pack8(dv);
+  *reinterpret_cast<Pack8*>(dx + row * 2 * c + c + col) = pack8(dg);
+}
+
+// 2x2 stride-2 average pool, NHWC.  bwd=1 scatters dy/4 back.
+__global__ void avgpool2x2_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, long long n, int oh, int ow,
+                                  int c, int bwd) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int c8 = c / 8;
+  const long long total = n * oh * ow * c8;
+  if (i >= total) return;
+  const int col = (int)(i % c8) * 8;
+  long long pix = i / c8;
+  const int x = (int)(pix % ow);
+  pix /= ow;
+  const int y = (int)(pix % oh);
+  const long long b = pix / oh;
+  const int ih = oh * 2, iw = ow * 2;
+  const long long obase = ((b * oh + y) * ow + x) * c + col;
+  if (!bwd) {
+    float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int dy = 0; dy < 2; ++dy)
+#pragma unroll
+      for (int dx = 0; dx < 2; ++dx) {
+        float v[8];
+        unpack8(*reinterpret_cast<const Pack8*>(in + ((b * ih + 2 * y + dy) * iw + 2 * x + dx) * c + col), v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[j] += v[j];
+      }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[j] *= 0.25f;
+    *reinterpret_cast<Pack8*>(out + obase) = pack8(s);
+  } else {
+    float v[8];
+    unpack8(*reinterpret_cast<const Pack8*>(in + obase), v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= 0.25f;
+    const Pack8 p = pack8(v);
+#pragma unroll
+    for (int dy = 0; dy < 2; ++dy)
+#pragma unroll
+      for (int dx = 0; dx < 2; ++dx)
+        *reinterpret_cast<Pack8*>(out + ((b * ih + 2 * y + dy) * iw + 2 * x + dx) * c + col) = p;
+  }
+}
+
+// Global average pool over `pix` positions: x [n, pix, c] -> y [n, c].  One block per (n, 8-channel-group
+// slab of 32 groups); threads stride over positions.
+__global__ void global_avgpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, int pix, int c) {
+  __shared__ float red[8][33][8];
+  const long long n = blockIdx.x;
+  const int cg = blockIdx.y * 32 + (threadIdx.x & 31);  // 8-channel group
+  const int slice = threadIdx.x >> 5;                   // 8 slices over positions
+  float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (cg * 8 < c) {
+    for (int p = slice; p < pix; p += 8) {
+      float v[8];
+      unpack8(*reinterpret_cast<const Pack8*>(x + (n * pix + p) * c + cg * 8), v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[slice][threadIdx.x & 31][j] = s[j];
+  __syncthreads();
+  if (slice == 0 && cg * 8 < c) {
+    float o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float t = 0.0f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) t += red[k][threadIdx.x & 31][j];
+      o[j] = t / pix;
+    }
+    *reinterpret_cast<Pack8*>(y + n * c + cg * 8) = pack8(o);
+  }
+}
+__global__ void global_avgpool_bwd_kernel(const bf16* __restrict__ dy, bf16* __restrict__ dx, long long n, int pix,
+                                          int c) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int c8 = c / 8;
+  if (i >= n * pix * c8) return;
+  const int col = (int)(i % c8) * 8;
+  const long long b = i / c8 / pix;
+  float v[8];
+  unpack8(*reinterpret_cast<const Pack8*>(dy + b * c + col), v);
+  const float inv = 1.0f / pix;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] *= inv;
+  reinterpret_cast<Pack8*>(dx)[i] = pack8(v);
+}
+
+// Column sums of a bf16 matrix [rows, cols] into fp32 (bias gradients): out[c] += sum_r x[r, c].
+__global__ void colsum_kernel(const bf16* __restrict__ x, float* __restrict__ out, long long rows, int cols,
+                              int rows_per_block) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= cols) return;
+  const long long r0 = (long long)blockIdx.y * rows_per_block;
+  const long long r1 = min(rows, r0 + rows_per_block);
+  float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (long long r = r0; r < r1; ++r) {
+    float v[8];
+    unpack8(*reinterpret_cast<const Pack8*>(x + r * cols + c), v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[j] += v[j];
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) atomicAdd(out + c + j, s[j]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// cell embedding
+// ------------------------------------------------------------------------------------------------
+// out[n, p, :] = cp_embed[cp] (0 if out of range) + pos_embed[p] + sum_c chan_c/255 * colour[c]
+// One thread per 8 output channels; the six colour vectors and the position row come from L1/L2.
+__global__ void cell_embed_fwd_kernel(const int* __restrict__ cells, const float* __restrict__ cp_embed,
+                                      const float* __restrict__ pos_embed, const float* __restrict__ colour,
+                                      bf16* __restrict__ out, long long total_cells, int positions, int e, int vocab) {
+  const int e8 = e / 8;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total_cells * e8) return;
+  const long long cell = i / e8;
+  const int col = (int)(i % e8) * 8;
+  const int cp = cells[cell * 3 + 0];
+  const uint32_t fg = (uint32_t)cells[cell * 3 + 1], bg = (uint32_t)cells[cell * 3 + 2];
+  const int p = (int)(cell % positions);
+  const float ch[6] = {((fg >> 16) & 255) * (1.0f / 255.0f), ((fg >> 8) & 255) * (1.0f / 255.0f),
+                       (fg & 255) * (1.0f / 255.0f),         ((bg >> 16) & 255) * (1.0f / 255.0f),
+                       ((bg >> 8) & 255) * (1.0f / 255.0f),  (bg & 255) * (1.0f / 255.0f)};
+  float o[8];
+  const float4* pe = reinterpret_cast<const float4*>(pos_embed + (long long)p * e + col);
+  float4 a = pe[0], b = pe[1];
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+  if (cp >= 0 && cp < vocab) {
+    const float4* ce = reinterpret_cast<const float4*>(cp_embed + (long long)cp * e + col);
+    a = ce[0]; b = ce[1];
+    o[0] += a.x; o[1] += a.y; o[2] += a.z; o[3] += a.w; o[4] += b.x; o[5] += b.y; o[6] += b.z; o[7] += b.w;
+  }
+#pragma unroll
+  for (int k = 0; k < 6; ++k) {
+    const float4* cv = reinterpret_cast<const float4*>(colour + k * e + col);
+    a = cv[0]; b = cv[1];
+    o[0] += ch[k] * a.x; o[1] += ch[k] * a.y; o[2] += ch[k] * a.z; o[3] += ch[k] * a.w;
+    o[4] += ch[k] * b.x; o[5] += ch[k] * b.y; o[6] += ch[k] * b.z; o[7] += ch[k] * b.w;
+  }
+  *reinterpret_cast<Pack8*>(out + cell * e + col) = pack8(o);
+}
+
+// Backward, position and colour tables.  Frames of a batch share positions, so a thread that owns
+// (position p, 8 channels) walks a slice of the frames: the position gradient is a plain running sum
+// (one atomic per slice at the end), and the six colour gradients are reduced over the block in shared
+// memory before one atomic per (colour, channel) per block.
+__global__ void cell_embed_bwd_pos_colour_kernel(const int* __restrict__ cells, const bf16* __restrict__ dout,
+                                                 float* __restrict__ d_pos, float* __restrict__ d_colour,
+                                                 long long frames, int positions, int e, int frames_per_block) {
+  extern __shared__ float sm_col[];  // [6][e]
+  for (int i = threadIdx.x; i < 6 * e; i += blockDim.x) sm_col[i] = 0.0f;
+  __syncthreads();
+  const int e8 = e / 8;
+  const int g = threadIdx.x % e8, pl = threadIdx.x / e8;
+  const int p = blockIdx.x * (blockDim.x / e8) + pl;
+  const long long f0 = (long long)blockIdx.y * frames_per_block;
+  const long long f1 = min(frames, f0 + frames_per_block);
+  const int col = g * 8;
+  if (p < positions && pl < blockDim.x / e8) {
+    float pos_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    float col_acc[6][8];
+#pragma unroll
+    for (int k = 0; k < 6; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) col_acc[k][j] = 0.0f;
+    for (long long f = f0; f < f1; ++f) {
+      const long long cell = f * positions + p;
+      float d[8];
+      unpack8(*reinterpret_cast<const Pack8*>(dout + cell * e + col), d);
+      const uint32_t fg = (uint32_t)cells[cell * 3 + 1], bg = (uint32_t)cells[cell * 3 + 2];
+      const float ch[6] = {((fg >> 16) & 255) * (1.0f / 255.0f), ((fg >> 8) & 255) * (1.0f / 255.0f),
+                           (fg & 255) * (1.0f / 255.0f),         ((bg >> 16) & 255) * (1.0f / 255.0f),
+                           ((bg >> 8) & 255) * (1.0f / 255.0f),  (bg & 255) * (1.0f / 255.0f)};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) pos_acc[j] += d[j];
+#pragma unroll
+      for (int k = 0; k < 6; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) col_acc[k][j] += ch[k] * d[j];
+    }
+    float* dp = d_pos + (long long)p * e + col;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(dp + j, pos_acc[j]);
+#pragma unroll
+    for (int k = 0; k < 6; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) atomicAdd(&sm_col[k * e + col + j], col_acc[k][j]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 6 * e; i += blockDim.x) atomicAdd(d_colour + i, sm_col[i]);
+}
+
+// Backward, code-point table: d_cp[v, :] = sum over cells with code point v of dout[cell, :].  Each block
+// owns a 32-channel slab and a contiguous run of cells; it accumulates into a private [vocab][32] table in
+// shared memory (one warp per cell, lane = channel, so the shared atomics are bank-conflict free) and
+// flushes the non-zero rows with global atomics once.
+__global__ void cell_embed_bwd_cp_kernel(const int* __restrict__ cells, const bf16* __restrict__ dout,
+                                         float* __restrict__ d_cp, long long total_cells, int e, int vocab,
+                                         int cells_per_block) {
+  extern __shared__ float table[];  // [vocab][32]
+  for (int i = threadIdx.x; i < vocab * 32; i += blockDim.x) table[i] = 0.0f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int c = blockIdx.y * 32 + lane;
+  const long long c0 = (long long)blockIdx.x * cells_per_block;
+  const long long c1 = min(total_cells, c0 + cells_per_block);
+  if (c < e) {
+    for (long long cell = c0 + warp; cell < c1; cell += warps) {
+      const int cp = cells[cell * 3];
+      if (cp >= 0 && cp < vocab) atomicAdd(&table[cp * 32 + lane], __bfloat162float(dout[cell * e + c]));
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < vocab * 32; i += blockDim.x) {
+    const float v = table[i];
+    const int ch = blockIdx.y * 32 + (i & 31);
+    if (v != 0.0f && ch < e) atomicAdd(d_cp + (long long)(i >> 5) * e + ch, v);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// cross-entropy on bf16 logits, forward + backward in one pass over the row
+// ------------------------------------------------------------------------------------------------
+// logits [rows, ld] (first `vocab` columns valid).  loss_sum += scale * sum_rows (lse - logit[target]);
+// logits are overwritten with scale * (softmax - onehot); padding columns get 0.
+__global__ void ce_fwd_bwd_kernel(bf16* __restrict__ logits, const long long* __restrict__ targets,
+                                  float* __restrict__ loss_sum, int vocab, int ld, float scale, int write_grad) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  bf16* lr = logits + row * ld;
+  float mx = -INFINITY;
+  for (int c = threadIdx.x; c < vocab; c += blockDim.x) mx = fmaxf(mx, __bfloat162float(lr[c]));
+  mx = block_max(mx, scratch);
+  float s = 0.0f;
+  for (int c = threadIdx.x; c < vocab; c += blockDim.x) s += __expf(__bfloat162float(lr[c]) - mx);
+  s = block_sum(s, scratch);
+  const int t = (int)targets[row];
+  if (threadIdx.x == 0) {
+    const float lt = (t >= 0 && t < vocab) ? __bfloat162float(lr[t]) : 0.0f;
+    atomicAdd(loss_sum, scale * (logf(s) + mx - lt));
+  }
+  if (!write_grad) return;
+  const float inv = 1.0f / s;
+  for (int c = threadIdx.x; c < ld; c += blockDim.x) {
+    float g = 0.0f;
+    if (c < vocab) g = scale * (__expf(__bfloat162float(lr[c]) - mx) * inv - (c == t ? 1.0f : 0.0f));
+    lr[c] = __float2bfloat16(g);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// fused AdamW over a flat range: reads g (bf16 or fp32), updates m, v, fp32 master and writes the
+// rounded parameter.  4 elements per thread.
+// ------------------------------------------------------------------------------------------------
+template <typename PT>
+__global__ void adamw_kernel(PT* __restrict__ param, const PT* __restrict__ grad, float* __restrict__ m,
+                             float* __restrict__ v, float* __restrict__ master, long long n, float lr, float b1,
+                             float b2, float eps, float wd, float inv_bc1, float inv_bc2, float grad_scale) {
+  const long long i0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const long long i = i0 + k;
+    if (i >= n) return;
+    float g, w;
+    if constexpr (sizeof(PT) == 2) g = __bfloat162float(grad[i]); else g = grad[i];
+    g *= grad_scale;
+    if (master != nullptr) w = master[i];
+    else if constexpr (sizeof(PT) == 2) w = __bfloat162float(param[i]); else w = param[i];
+    w *= 1.0f - lr * wd;
+    const float mi = b1 * m[i] + (1.0f - b1) * g;
+    const float vi = b2 * v[i] + (1.0f - b2) * g * g;
+    m[i] = mi;
+    v[i] = vi;
+    w -= lr * (mi * inv_bc1) / (sqrtf(vi * inv_bc2) + eps);
+    if (master != nullptr) master[i] = w;
+    if constexpr (sizeof(PT) == 2) param[i] = __float2bfloat16(w); else param[i] = w;
+  }
+}
+
+template <int V>
+int launch_rms_fwd(const bf16* x, const bf16* w, bf16* y, float* rstd, long long rows, int dim, float eps,
+                   cudaStream_t s) {
+  const int warps = 8;
+  rmsnorm_fwd_kernel<V><<<(unsigned)((rows + warps - 1) / warps), warps * 32, 0, s>>>(x, w, y, rstd, rows, dim, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+template <int V>
+int launch_rms_bwd(const bf16* dy, const bf16* x, const bf16* w, const float* rstd, bf16* dx, float* dg, long long rows,
+                   int dim, cudaStream_t s) {
+  const int warps = 8, rpw = 8;
+  const long long blocks = (rows + warps * rpw - 1) / (warps * rpw);
+  rmsnorm_bwd_kernel<V><<<(unsigned)blocks, warps * 32, dim * sizeof(float), s>>>(dy, x, w, rstd, dx, dg, rows, dim, rpw);
+  return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+
+}  // namespace
+
+#define STREAM(s) reinterpret_cast<cudaStream_t>(s)
+#define CHECK_LAUNCH() (cudaGetLastError() == cudaSuccess ? 0 : 5)
+
+extern "C" {
+
+int fbam_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int dim, float eps,
+                     void* stream) {
+  if (dim % 8 != 0 || dim > 8192) return 1;
+  const bf16 *X = (const bf16*)x, *W = (const bf16*)w;
+  if (dim <= 256) return launch_rms_fwd<1>(X, W, (bf16*)y, rstd, rows, dim, eps, STREAM(stream));
+  if (dim <= 512) return launch_rms_fwd<2>(X, W, (bf16*)y, rstd, rows, dim, eps, STREAM(stream));
+  if (dim <= 1024) return launch_rms_fwd<4>(X, W, (bf16*)y, rstd, rows, dim, eps, STREAM(stream));
+  if (dim <= 2048) return launch_rms_fwd<8>(X, W, (bf16*)y, rstd, rows, dim, eps, STREAM(stream));
+  if (dim <= 4096) return launch_rms_fwd<16>(X, W, (bf16*)y, rstd, rows, dim, eps, STREAM(stream));
+  return launch_rms_fwd<32>(X, W, (bf16*)y, rstd, rows, dim, eps, STREAM(stream));
+}
+
+int fbam_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dgamma,
+                     long long rows, int dim, void* stream) {
+  if (dim % 8 != 0 || dim > 4096) return 1;
+  const bf16 *DY = (const bf16*)dy, *X = (const bf16*)x, *W = (const bf16*)w;
+  if (dim <= 256) return launch_rms_bwd<1>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
+  if (dim <= 512) return launch_rms_bwd<2>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
+  if (dim <= 1024) return launch_rms_bwd<4>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
+  if (dim <= 2048) return launch_rms_bwd<8>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
+  return launch_rms_bwd<16>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
+}
+
+int fbam_layernorm_fwd(const void* x, const void* w, const void* b, void* y, long long rows, int dim, float eps,
+                       void* stream) {
+  layernorm_fwd_kernel<<<(unsigned)rows, 256, 0, STREAM(stream)>>>((const bf16*)x, (const bf16*)w, (const bf16*)b,
+                                                                   (bf16*)y, dim, eps);
+  return CHECK_LAUNCH();
+}
+
+int fbam_gelu(const void* x, const void* dy, void* out, long long n, int mode, void* stream) {
+  if (n % 8 != 0) return 1;
+  const long long n8 = n / 8;
+  gelu_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16*)x, (const bf16*)dy, (bf16*)out,
+                                                                        n8, mode);
+  return CHECK_LAUNCH();
+}
+
+int fbam_geglu(const void* x, const void* dy, void* out, long long rows, int c, int bwd, void* stream) {
+  if (c % 8 != 0) return 1;
+  const long long n = rows * (c / 8);
+  if (!bwd) geglu_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16*)x, (bf16*)out, rows, c);
+  else geglu_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16*)x, (const bf16*)dy,
+                                                                                (bf16*)out, rows, c);
+  return CHECK_LAUNCH();
+}
+
+int fbam_avgpool2x2(const void* in, void* out, long long n, int oh, int ow, int c, int bwd, void* stream) {
+  if (c % 8 != 0) return 1;
+  const long long total = n * oh * ow * (c / 8);
+  avgpool2x2_kernel<<<(unsigned)((total + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16*)in, (bf16*)out, n, oh, ow,
+                                                                                 c, bwd);
+  return CHECK_LAUNCH();
+}
+
+int fbam_global_avgpool(const void* in, void* out, long long n, int pix, int c, int bwd, void* stream) {
+  if (c % 8 != 0) return 1;
+  if (!bwd) {
+    dim3 grid((unsigned)n, (c / 8 + 31) / 32);
+    global_avgpool_fwd_kernel<<<grid, 256, 0, STREAM(stream)>>>((const bf16*)in, (bf16*)out, pix, c);
+  } else {
+    const long long total = n * pix * (c / 8);
+    global_avgpool_bwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16*)in, (bf16*)out,
+                                                                                           n, pix, c);
+  }
+  return CHECK_LAUNCH();
+}
+
+int fbam_colsum(const void* x, float* out, long long rows, int cols, void* stream) {
+  if (cols % 8 != 0) return 1;
+  const int threads = 128, rpb = 256;
+  dim3 grid((cols / 8 + threads - 1) / threads, (unsigned)((rows + rpb - 1) / rpb));
+  colsum_kernel<<<grid, threads, 0, STREAM(stream)>>>((const bf16*)x, out, rows, cols, rpb);
+  return CHECK_LAUNCH();
+}
+
+int fbam_cell_embed_fwd(const int* cells, const float* cp_embed, const float* pos_embed, const float* colour,
+                        void* out, long long total_cells, int positions, int e, int vocab, void* stream) {
+  if (e % 8 != 0) return 1;
+  const long long total = total_cells * (e / 8);
+  cell_embed_fwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, STREAM(stream)>>>(
+      cells, cp_embed, pos_embed, colour, (bf16*)out, total_cells, positions, e, vocab);
+  return CHECK_LAUNCH();
+}
+
+int fbam_cell_embed_bwd(const int* cells, const void* dout, float* d_cp, float* d_pos, float* d_colour,
+                        long long frames, int positions, int e, int vocab, void* stream) {
+  if (e % 8 != 0 || e / 8 > 256) return 1;
+  const int e8 = e / 8;
+  const int threads = 256 / e8 * e8 < 32 ? e8 : 256 / e8 * e8;
+  const int pos_per_block = threads / e8;
+  const int fpb = 64;
+  dim3 grid((positions + pos_per_block - 1) / pos_per_block, (unsigned)((frames + fpb - 1) / fpb));
+  cell_embed_bwd_pos_colour_kernel<<<grid, threads, 6 * e * sizeof(float), STREAM(stream)>>>(
+      cells, (const bf16*)dout, d_pos, d_colour, frames, positions, e, fpb);
+  if (cudaGetLastError() != cudaSuccess) return 5;
+  // code-point table: vocab x 32 fp32 slab per block in shared memory
+  const size_t smem = (size_t)vocab * 32 * sizeof(float);
+  if (smem > 200 * 1024) return 1;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(cell_embed_bwd_cp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+        cudaSuccess)
+      return 5;
+    configured = true;
+  }
+  const long long total_cells = frames * positions;
+  const int cpb = 32768;
+  dim3 grid2((unsigned)((total_cells + cpb - 1) / cpb), (e + 31) / 32);
+  cell_embed_bwd_cp_kernel<<<grid2, 512, smem, STREAM(stream)>>>(cells, (const bf16*)dout, d_cp, total_cells, e, vocab,
+                                                                 cpb);
+  return CHECK_LAUNCH();
+}
+
+int fbam_ce_fwd_bwd(void* logits, const long long* targets, float* loss_sum, long long rows, int vocab, int ld,
+                    float scale, int write_grad, void* stream) {
+  ce_fwd_bwd_kernel<<<(unsigned)rows, 256, 0, STREAM(stream)>>>((bf16*)logits, targets, loss_sum, vocab, ld, scale,
+                                                                write_grad);
+  return CHECK_LAUNCH();
+}
+
+int fbam_adamw(void* param, const void* grad, float* m, float* v, float* master, long long n, int param_bf16,
+               float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
+               void* stream) {
+  if (n <= 0) return 0;
+  const unsigned blocks = (unsigned)((n + 1023) / 1024);
+  if (param_bf16)
+    adamw_kernel<bf16><<<blocks, 256, 0, STREAM(stream)>>>((bf16*)param, (const bf16*)grad, m, v, master, n, lr, b1, b2,
+                                                           eps, wd, 1.0f / bc1, 1.0f / bc2, grad_scale);
+  else
+    adamw_kernel<float><<<blocks, 256, 0, STREAM(stream)>>>((float*)param, (const float*)grad, m, v, master, n, lr, b1,
+                                                            b2, eps, wd, 1.0f / bc1, 1.0f / bc2, grad_scale);
+  return CHECK_LAUNCH();
+}
+
+}  // extern "C"

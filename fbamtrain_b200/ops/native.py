@@ -1,0 +1,107 @@
+"""ctypes binding of ``lib/libfbam_kernels.so`` (hand-written sm_100a kernels).
+
+The library exports plain C entry points that take device pointers, sizes and a CUDA stream; this
+module loads it, mirrors its parameter structs, and converts non-zero return codes and device-side
+status words into Python exceptions.  If the library is absent on a machine that has a GPU, loading
+raises — CUDA tensors never fall back to a PyTorch implementation silently.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libfbam_kernels.so")
+_lib: Optional[C.CDLL] = None
+
+GEMM_ACT = {"none": 0, "gelu": 1, "relu": 2}
+GEMM_ACC_NONE, GEMM_ACC_RMW, GEMM_ACC_ATOMIC = 0, 1, 2
+_ERRORS = {1: "unsupported shape", 2: "operand not 16-byte aligned", 3: "tensor-map encode failed",
+           4: "driver entry point unavailable", 5: "kernel launch failed",
+           101: "TMA producer wait timed out", 102: "MMA wait timed out", 103: "epilogue wait timed out"}
+
+
+class ConvGeom(C.Structure):
+    _fields_ = [("batch", C.c_int), ("grid_h", C.c_int), ("grid_w", C.c_int),
+                ("tn", C.c_int), ("th", C.c_int), ("tw", C.c_int),
+                ("in_mul", C.c_int),
+                ("out_mul", C.c_int), ("out_off_h", C.c_int), ("out_off_w", C.c_int), ("out_h", C.c_int), ("out_w", C.c_int),
+                ("num_taps", C.c_int),
+                ("tap_dh", C.c_int * 9), ("tap_dw", C.c_int * 9),
+                ("c_blocks", C.c_int), ("tiles_w", C.c_int), ("tiles_h", C.c_int)]
+
+
+class GemmParams(C.Structure):
+    _fields_ = [("D", C.c_void_p), ("ldd", C.c_longlong),
+                ("bias", C.c_void_p),
+                ("residual", C.c_void_p), ("ldr", C.c_longlong),
+                ("preact_out", C.c_void_p),
+                ("gelu_grad_in", C.c_void_p),
+                ("status", C.c_void_p),
+                ("alpha", C.c_float),
+                ("out_fp32", C.c_int), ("bias_fp32", C.c_int), ("act", C.c_int), ("accumulate", C.c_int),
+                ("bn", C.c_int), ("max_ctas", C.c_int),
+                ("mode", C.c_int), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("tiles_m", C.c_int),
+                ("k_blocks", C.c_int), ("a_mn_major", C.c_int), ("b_mn_major", C.c_int), ("vec_ok", C.c_int),
+                ("conv", ConvGeom)]
+
+
+def available() -> bool:
+    return os.path.exists(LIB_PATH)
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"native kernel library missing: {LIB_PATH} (run `python -m fbamtrain_b200.build`)")
+        _lib = C.CDLL(LIB_PATH)
+        _lib.fbam_gemm_bf16.restype = C.c_int
+        _lib.fbam_conv_bf16.restype = C.c_int
+    return _lib
+
+
+_launches = 0
+
+
+def launches() -> int:
+    """Number of native entry-point calls that launched kernels since import."""
+    return _launches
+
+
+def check(code: int, what: str) -> None:
+    global _launches
+    if code != 0:
+        raise RuntimeError(f"{what}: {_ERRORS.get(code, 'error')} (code {code})")
+    _launches += 1
+
+
+def stream_ptr() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+_status = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word that kernels set when a bounded wait expires."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device: torch.device) -> None:
+    """Synchronises and raises if any kernel reported a timed-out wait since the last check."""
+    w = status_word(device)
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise RuntimeError(f"device-side wait expired: {_ERRORS.get(code, 'error')} (code {code})")

@@ -1,0 +1,522 @@
+"""CUDA implementations of the functional ops: autograd Functions over the native kernels.
+
+Tensor-core work (linear layers, convolutions, LM head) goes through the tcgen05 GEMM /
+implicit-GEMM entry points; everything else through the bandwidth-bound kernels.  Model dtype on
+this path is bf16 (fp32 parameters — embeddings, LSTM — are handled where noted).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from ..utils import debug
+from . import native as nv
+from . import reference as ref
+
+BF16 = torch.bfloat16
+# Weight-gradient and data-gradient GEMMs read their operands in place through the transposed
+# (MN-major) operand form of the tensor-core descriptors.  False = materialise transposes instead.
+USE_MN_MAJOR = True
+
+
+def _need_bf16(*ts):
+    for t in ts:
+        if t is not None and t.dtype != BF16:
+            raise TypeError(f"native kernels take bf16 tensors, got {t.dtype}")
+
+
+# =================================================================================================
+# GEMM
+# =================================================================================================
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = BF16, bias: Optional[torch.Tensor] = None,
+         act: str = "none", residual: Optional[torch.Tensor] = None, preact_out: Optional[torch.Tensor] = None,
+         gelu_grad_in: Optional[torch.Tensor] = None, accumulate: int = 0, alpha: float = 1.0,
+         bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
+    """``D[M, N] = epilogue(A · Bᵀ)``.
+
+    ``a``: ``(M, K)`` (or ``(K, M)`` when ``a_mn``); ``b``: ``(N, K)`` (or ``(K, N)`` when ``b_mn``).
+    Operands must be bf16 with unit inner stride, 16-byte aligned rows.  ``accumulate``: 0 overwrite,
+    1 read-modify-write ``D +=``, 2 atomic adds (fp32 output only)."""
+    _need_bf16(a, b)
+    if a.stride(-1) != 1 or b.stride(-1) != 1:
+        raise ValueError("GEMM operands need unit inner stride")
+    m, k = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    n, kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if k != kb:
+        raise ValueError(f"inner dimensions differ: {k} vs {kb}")
+    if out is None:
+        out = debug.fresh((m, n), out_dtype, a.device)
+    if out.shape != (m, n) or out.stride(1) != 1:
+        raise ValueError("output has the wrong shape or layout")
+    p = nv.GemmParams()
+    p.D, p.ldd = out.data_ptr(), out.stride(0)
+    p.bias = 0 if bias is None else bias.data_ptr()
+    p.bias_fp32 = int(bias is not None and bias.dtype == torch.float32)
+    if residual is not None:
+        _need_bf16(residual)
+        p.residual, p.ldr = residual.data_ptr(), residual.stride(0)
+    if preact_out is not None:
+        if preact_out.stride(0) != out.stride(0):
+            raise ValueError("preact_out must share the output's row pitch")
+        p.preact_out = preact_out.data_ptr()
+    if gelu_grad_in is not None:
+        if gelu_grad_in.stride(0) != out.stride(0):
+            raise ValueError("gelu_grad_in must share the output's row pitch")
+        p.gelu_grad_in = gelu_grad_in.data_ptr()
+    p.status = nv.status_word(a.device).data_ptr()
+    p.alpha = alpha
+    p.out_fp32 = int(out.dtype == torch.float32)
+    p.act = nv.GEMM_ACT[act]
+    p.accumulate = accumulate
+    p.bn, p.max_ctas = bn, max_ctas
+    code = nv.lib().fbam_gemm_bf16(nv.ptr(a), C.c_longlong(a.stride(0)), int(a_mn), nv.ptr(b),
+                                   C.c_longlong(b.stride(0)), int(b_mn), m, n, k, C.byref(p), nv.stream_ptr())
+    nv.check(code, "fbam_gemm_bf16")
+    debug.after_launch("gemm", a, b, out)
+    return out
+
+
+def _t(x: torch.Tensor) -> torch.Tensor:
+    return x.t().contiguous()
+
+
+def gemm_nt(a, b, **kw):
+    """``A (M,K) · B (N,K)ᵀ``."""
+    return gemm(a, b, **kw)
+
+
+def gemm_nn(a, b_kn, **kw):
+    """``A (M,K) · B (K,N)``."""
+    if USE_MN_MAJOR:
+        return gemm(a, b_kn, b_mn=True, **kw)
+    return gemm(a, _t(b_kn), **kw)
+
+
+def gemm_tn(a_km, b_kn, **kw):
+    """``A (K,M)ᵀ · B (K,N)`` — weight gradients."""
+    if USE_MN_MAJOR:
+        return gemm(a_km, b_kn, a_mn=True, b_mn=True, **kw)
+    return gemm(_t(a_km), _t(b_kn), **kw)
+
+
+def _colsum(x2d: torch.Tensor) -> torch.Tensor:
+    out = torch.zeros(x2d.shape[1], dtype=torch.float32, device=x2d.device)
+    nv.check(nv.lib().fbam_colsum(nv.ptr(x2d), nv.ptr(out), C.c_longlong(x2d.shape[0]), x2d.shape[1],
+                                  nv.stream_ptr()), "fbam_colsum")
+    return out
+
+
+def _gelu_bwd(preact: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
+    out = torch.empty_like(dy)
+    nv.check(nv.lib().fbam_gelu(nv.ptr(preact), nv.ptr(dy), nv.ptr(out), C.c_longlong(dy.numel()), 1,
+                                nv.stream_ptr()), "fbam_gelu")
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, act):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        preact = None
+        if act == "gelu" and (x.requires_grad or weight.requires_grad):
+            preact = torch.empty((x2.shape[0], weight.shape[0]), dtype=BF16, device=x.device)
+        y = gemm(x2, weight, bias=bias, act=act, preact_out=preact)
+        ctx.save_for_backward(x2, weight, preact)
+        ctx.act, ctx.has_bias, ctx.in_shape = act, bias is not None, x.shape
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, preact = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        if ctx.act == "gelu":
+            dy2 = _gelu_bwd(preact, dy2)
+        elif ctx.act == "relu":
+            raise NotImplementedError("relu backward is not wired on the native path")
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm_nn(dy2, weight).view(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm_tn(dy2, x2)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = _colsum(dy2).to(BF16)
+        return dx, dw, db, None
+
+
+def linear(x, weight, bias=None, act="none"):
+    _need_bf16(x, weight, bias)
+    return _Linear.apply(x, weight, bias, act)
+
+
+# =================================================================================================
+# convolution (implicit GEMM)
+# =================================================================================================
+def _brick(n: int, h: int, w: int) -> Tuple[int, int, int]:
+    """Splits the 128 rows of a tile into (tn, th, tw) positions with the least padding waste."""
+    best, best_cost = (1, 1, 128), None
+    for tw in (1, 2, 4, 8, 16, 32, 64, 128):
+        for th in (1, 2, 4, 8, 16, 32, 64, 128):
+            if tw * th > 128:
+                continue
+            tn = 128 // (tw * th)
+            cost = (math.ceil(w / tw) * tw) * (math.ceil(h / th) * th) * (math.ceil(n / tn) * tn)
+            # prefer wide bricks on ties: longer contiguous runs per TMA box row
+            key = (cost, -tw, -th)
+            if best_cost is None or key < best_cost:
+                best, best_cost = (tn, th, tw), key
+    return best
+
+
+def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor, *, grid_hw, in_mul, taps,
+              out_mul=1, out_off=(0, 0), accumulate=0, bn: int = 0) -> None:
+    """One implicit-GEMM pass (see ``ConvGeom`` in csrc/gemm_tcgen05.h).  ``x`` NHWC bf16, ``wmat``
+    ``(n_out, taps·C)`` bf16, ``out`` NHWC with ``n_out`` channels."""
+    b, ih, iw, c = x.shape
+    p = nv.GemmParams()
+    g = p.conv
+    g.batch, g.grid_h, g.grid_w = b, grid_hw[0], grid_hw[1]
+    g.tn, g.th, g.tw = _brick(b, grid_hw[0], grid_hw[1])
+    g.in_mul, g.out_mul = in_mul, out_mul
+    g.out_off_h, g.out_off_w = out_off
+    g.out_h, g.out_w = out.shape[1], out.shape[2]
+    g.num_taps = len(taps)
+    for i, (dh, dw) in enumerate(taps):
+        g.tap_dh[i], g.tap_dw[i] = dh, dw
+    p.D, p.ldd = out.data_ptr(), out.shape[3]
+    p.status = nv.status_word(x.device).data_ptr()
+    p.alpha = 1.0
+    p.out_fp32 = int(out.dtype == torch.float32)
+    p.accumulate = accumulate
+    p.bn = bn
+    code = nv.lib().fbam_conv_bf16(nv.ptr(x), ih, iw, c, nv.ptr(wmat), C.c_longlong(wmat.stride(0)), n_out,
+                                   C.byref(p), nv.stream_ptr())
+    nv.check(code, "fbam_conv_bf16")
+    debug.after_launch("conv_pass", x, wmat, out)
+
+
+def conv2d_fprop(x, w_ohwi, stride, padding, dilation):
+    b, ih, iw, c = x.shape
+    o = w_ohwi.shape[0]
+    oh = (ih + 2 * padding - 2 * dilation - 1) // stride + 1
+    ow = (iw + 2 * padding - 2 * dilation - 1) // stride + 1
+    out = debug.fresh((b, oh, ow, o), BF16, x.device)
+    taps = [(r * dilation - padding, s * dilation - padding) for r in range(3) for s in range(3)]
+    conv_pass(x, w_ohwi.reshape(o, 9 * c), o, out, grid_hw=(oh, ow), in_mul=stride, taps=taps)
+    return out
+
+
+def conv2d_dgrad(dy, w_ohwi, in_hw, stride, padding, dilation):
+    """dX[n, h, w, :] = Σ_taps dY[n, (h + pad − r·dil)/stride, (w + pad − s·dil)/stride, :] · W[:, r, s, :]
+    over the taps for which the division is exact.  Output pixels are split into stride x stride
+    parity classes; each class is one stride-1 gather over its own tap subset."""
+    b, oh, ow, o = dy.shape
+    c = w_ohwi.shape[3]
+    ih, iw = in_hw
+    dx = debug.fresh((b, ih, iw, c), BF16, dy.device)
+    covered = 0
+    for ph in range(stride):
+        for pw in range(stride):
+            taps, mats = [], []
+            for r in range(3):
+                if (ph + padding - r * dilation) % stride != 0:
+                    continue
+                for s in range(3):
+                    if (pw + padding - s * dilation) % stride != 0:
+                        continue
+                    taps.append(((ph + padding - r * dilation) // stride, (pw + padding - s * dilation) // stride))
+                    mats.append(w_ohwi[:, r, s, :])                       # (O, C)
+            gh, gw = (ih - ph + stride - 1) // stride, (iw - pw + stride - 1) // stride
+            if gh <= 0 or gw <= 0:
+                continue
+            if not taps:
+                dx[:, ph::stride, pw::stride, :].zero_()
+                continue
+            # filter matrix for this class: (C, taps·O), K ordered tap-major then output channel
+            wmat = torch.stack(mats, 0).permute(2, 0, 1).reshape(c, len(taps) * o).contiguous()
+            conv_pass(dy, wmat, c, dx, grid_hw=(gh, gw), in_mul=1, taps=taps, out_mul=stride, out_off=(ph, pw))
+            covered += 1
+    return dx
+
+
+class _Conv2d(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, stride, padding, dilation):
+        ctx.save_for_backward(x, w)
+        ctx.cfg = (stride, padding, dilation)
+        return conv2d_fprop(x, w, stride, padding, dilation)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        stride, padding, dilation = ctx.cfg
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            if dy.shape[3] % 64 == 0:
+                dx = conv2d_dgrad(dy, w, (x.shape[1], x.shape[2]), stride, padding, dilation)
+            else:
+                dx = torch.nn.grad.conv2d_input(x.permute(0, 3, 1, 2).shape, w.permute(0, 3, 1, 2),
+                                                dy.permute(0, 3, 1, 2), stride, padding, dilation).permute(0, 2, 3, 1).contiguous()
+        if ctx.needs_input_grad[1]:
+            from .conv_wgrad import conv2d_wgrad
+            dw = conv2d_wgrad(x, dy, w.shape, stride, padding, dilation)
+        return dx, dw, None, None, None
+
+
+def conv2d_nhwc(x, w_ohwi, stride, padding, dilation):
+    _need_bf16(x, w_ohwi)
+    if x.shape[3] % 64 != 0:
+        raise ValueError("native convolution needs input channels in multiples of 64")
+    return _Conv2d.apply(x.contiguous(), w_ohwi, stride, padding, dilation)
+
+
+# =================================================================================================
+# normalisation / activations / pooling
+# =================================================================================================
+class _RmsNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        y = torch.empty_like(x2)
+        rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+        nv.check(nv.lib().fbam_rmsnorm_fwd(nv.ptr(x2), nv.ptr(weight), nv.ptr(y), nv.ptr(rstd),
+                                           C.c_longlong(x2.shape[0]), x2.shape[1], C.c_float(eps), nv.stream_ptr()),
+                 "fbam_rmsnorm_fwd")
+        ctx.save_for_backward(x2, weight, rstd)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, rstd = ctx.saved_tensors
+        dy2 = dy.reshape(x2.shape).contiguous()
+        dx = torch.empty_like(x2)
+        dg = torch.zeros(x2.shape[1], dtype=torch.float32, device=x2.device)
+        nv.check(nv.lib().fbam_rmsnorm_bwd(nv.ptr(dy2), nv.ptr(x2), nv.ptr(weight), nv.ptr(rstd), nv.ptr(dx), nv.ptr(dg),
+                                           C.c_longlong(x2.shape[0]), x2.shape[1], nv.stream_ptr()), "fbam_rmsnorm_bwd")
+        return dx.view(dy.shape), dg.to(weight.dtype), None
+
+
+def rms_norm(x, weight, eps):
+    _need_bf16(x, weight)
+    return _RmsNorm.apply(x, weight, eps)
+
+
+def layer_norm(x, weight, bias, eps):
+    _need_bf16(x, weight, bias)
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    y = torch.empty_like(x2)
+    nv.check(nv.lib().fbam_layernorm_fwd(nv.ptr(x2), nv.ptr(weight), nv.ptr(bias), nv.ptr(y), C.c_longlong(x2.shape[0]),
+                                         x2.shape[1], C.c_float(eps), nv.stream_ptr()), "fbam_layernorm_fwd")
+    return y.view(x.shape)
+
+
+class _Gelu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        x = x.contiguous()
+        y = torch.empty_like(x)
+        nv.check(nv.lib().fbam_gelu(nv.ptr(x), None, nv.ptr(y), C.c_longlong(x.numel()), 0, nv.stream_ptr()), "fbam_gelu")
+        ctx.save_for_backward(x)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        return _gelu_bwd(x, dy.contiguous())
+
+
+def gelu(x):
+    _need_bf16(x)
+    return _Gelu.apply(x)
+
+
+class _Geglu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        x = x.contiguous()
+        c = x.shape[-1] // 2
+        rows = x.numel() // (2 * c)
+        y = torch.empty(*x.shape[:-1], c, dtype=BF16, device=x.device)
+        nv.check(nv.lib().fbam_geglu(nv.ptr(x), None, nv.ptr(y), C.c_longlong(rows), c, 0, nv.stream_ptr()), "fbam_geglu")
+        ctx.save_for_backward(x)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        c = x.shape[-1] // 2
+        dx = torch.empty_like(x)
+        nv.check(nv.lib().fbam_geglu(nv.ptr(x), nv.ptr(dy.contiguous()), nv.ptr(dx), C.c_longlong(x.numel() // (2 * c)),
+                                     c, 1, nv.stream_ptr()), "fbam_geglu")
+        return dx
+
+
+def geglu(x):
+    _need_bf16(x)
+    return _Geglu.apply(x)
+
+
+class _AvgPool2x2(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        n, h, w, c = x.shape
+        y = torch.empty(n, h // 2, w // 2, c, dtype=BF16, device=x.device)
+        nv.check(nv.lib().fbam_avgpool2x2(nv.ptr(x.contiguous()), nv.ptr(y), C.c_longlong(n), h // 2, w // 2, c, 0,
+                                          nv.stream_ptr()), "fbam_avgpool2x2")
+        ctx.shape = x.shape
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        n, h, w, c = ctx.shape
+        dx = torch.zeros(ctx.shape, dtype=BF16, device=dy.device) if (h % 2 or w % 2) else \
+            torch.empty(ctx.shape, dtype=BF16, device=dy.device)
+        nv.check(nv.lib().fbam_avgpool2x2(nv.ptr(dy.contiguous()), nv.ptr(dx), C.c_longlong(n), h // 2, w // 2, c, 1,
+                                          nv.stream_ptr()), "fbam_avgpool2x2")
+        return dx
+
+
+def avg_pool2x2_nhwc(x):
+    _need_bf16(x)
+    if x.shape[1] % 2 or x.shape[2] % 2:
+        raise ValueError("2x2 pooling needs even height and width")
+    return _AvgPool2x2.apply(x)
+
+
+class _GlobalAvgPool(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        n, h, w, c = x.shape
+        y = torch.empty(n, c, dtype=BF16, device=x.device)
+        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(x.contiguous()), nv.ptr(y), C.c_longlong(n), h * w, c, 0,
+                                              nv.stream_ptr()), "fbam_global_avgpool")
+        ctx.shape = x.shape
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        n, h, w, c = ctx.shape
+        dx = torch.empty(ctx.shape, dtype=BF16, device=dy.device)
+        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(dy.contiguous()), nv.ptr(dx), C.c_longlong(n), h * w, c, 1,
+                                              nv.stream_ptr()), "fbam_global_avgpool")
+        return dx
+
+
+def global_avg_pool_nhwc(x):
+    _need_bf16(x)
+    return _GlobalAvgPool.apply(x)
+
+
+# =================================================================================================
+# cell embedding
+# =================================================================================================
+class _CellEmbed(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, cells, cp_embed, pos_embed, colour):
+        n, p, _ = cells.shape
+        e = cp_embed.shape[1]
+        cells = cells.contiguous()
+        out = debug.fresh((n, p, e), BF16, cells.device)
+        nv.check(nv.lib().fbam_cell_embed_fwd(nv.ptr(cells), nv.ptr(cp_embed), nv.ptr(pos_embed), nv.ptr(colour),
+                                              nv.ptr(out), C.c_longlong(n * p), p, e, cp_embed.shape[0],
+                                              nv.stream_ptr()), "fbam_cell_embed_fwd")
+        ctx.save_for_backward(cells)
+        ctx.dims = (n, p, e, cp_embed.shape[0])
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (cells,) = ctx.saved_tensors
+        n, p, e, vocab = ctx.dims
+        d_cp = torch.zeros(vocab, e, dtype=torch.float32, device=dout.device)
+        d_pos = torch.zeros(p, e, dtype=torch.float32, device=dout.device)
+        d_col = torch.zeros(6, e, dtype=torch.float32, device=dout.device)
+        nv.check(nv.lib().fbam_cell_embed_bwd(nv.ptr(cells), nv.ptr(dout.contiguous()), nv.ptr(d_cp), nv.ptr(d_pos),
+                                              nv.ptr(d_col), C.c_longlong(n), p, e, vocab, nv.stream_ptr()),
+                 "fbam_cell_embed_bwd")
+        return None, d_cp, d_pos, d_col
+
+
+def cell_embed(cells, cp_embed, pos_embed, colour, out_dtype):
+    if out_dtype != BF16:
+        raise TypeError("native cell embedding writes bf16")
+    if pos_embed.shape[0] != cells.shape[1]:
+        raise ValueError("position table must have one row per cell")
+    return _CellEmbed.apply(cells, cp_embed, pos_embed, colour)
+
+
+# =================================================================================================
+# LM head + cross-entropy, chunked over rows so the (rows x vocab) logits never exist at once
+# =================================================================================================
+LM_HEAD_CHUNK_ROWS = 4096
+
+
+class _LmHeadCe(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_head, targets, vocab, scale):
+        rows, h = x.shape
+        vpad = w_head.shape[0]
+        loss = torch.zeros(1, dtype=torch.float32, device=x.device)
+        need_grad = x.requires_grad or w_head.requires_grad
+        dx = torch.empty_like(x) if need_grad else None
+        dw = torch.zeros(vpad, h, dtype=torch.float32, device=x.device) if need_grad else None
+        targets = targets.contiguous()
+        for lo in range(0, rows, LM_HEAD_CHUNK_ROWS):
+            hi = min(rows, lo + LM_HEAD_CHUNK_ROWS)
+            xc = x[lo:hi]
+            logits = gemm(xc, w_head)                                    # (chunk, vpad) bf16
+            nv.check(nv.lib().fbam_ce_fwd_bwd(nv.ptr(logits), nv.ptr(targets[lo:hi]), nv.ptr(loss),
+                                              C.c_longlong(hi - lo), vocab, vpad, C.c_float(scale), int(need_grad),
+                                              nv.stream_ptr()), "fbam_ce_fwd_bwd")
+            if need_grad:                                                # logits now hold scale·(softmax − onehot)
+                gemm_nn(logits, w_head, out=dx[lo:hi])
+                gemm_tn(logits, xc, out=dw, accumulate=nv.GEMM_ACC_RMW)
+        ctx.save_for_backward(dx, dw)
+        return loss.reshape(())
+
+    @staticmethod
+    def backward(ctx, dloss):
+        dx, dw = ctx.saved_tensors
+        return (dx * dloss.to(dx.dtype)), (dw * dloss).to(BF16), None, None, None
+
+
+def lm_head_ce(x, w_head, targets, vocab, scale):
+    _need_bf16(x, w_head)
+    return _LmHeadCe.apply(x.contiguous(), w_head, targets, vocab, scale)
+
+
+# =================================================================================================
+# fused AdamW on a flat range
+# =================================================================================================
+def adamw_flat(param, grad, m, v, master, lo, hi, lr, b1, b2, eps, wd, bc1, bc2, grad_scale=1.0):
+    n = hi - lo
+    if n <= 0:
+        return
+    is_bf16 = param.dtype == BF16
+    if not is_bf16 and param.dtype != torch.float32:
+        raise TypeError("fused AdamW handles bf16 and fp32 parameters")
+    nv.check(nv.lib().fbam_adamw(nv.ptr(param[lo:hi]), nv.ptr(grad[lo:hi]), nv.ptr(m[lo:hi]), nv.ptr(v[lo:hi]),
+                                 nv.ptr(None if master is None else master[lo:hi]), C.c_longlong(n), int(is_bf16),
+                                 C.c_float(lr), C.c_float(b1), C.c_float(b2), C.c_float(eps), C.c_float(wd),
+                                 C.c_float(bc1), C.c_float(bc2), C.c_float(grad_scale), nv.stream_ptr()), "fbam_adamw")
+
+
+# =================================================================================================
+# attention and LSTM sequence
+# =================================================================================================
+def attention(q, k, v, causal):
+    from .attention import flash_attention
+    return flash_attention(q, k, v, causal)
+
+
+def lstm_sequence(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype):
+    from .lstm import lstm_sequence as f
+    return f(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype)

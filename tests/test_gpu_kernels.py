@@ -1,0 +1,254 @@
+"""Numerics of the native sm_100a kernels against plain PyTorch fp32 definitions of the same ops."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from fbamtrain_b200.ops import reference as ref  # noqa: E402
+from fbamtrain_b200.utils.testing import assert_similar  # noqa: E402
+
+DEV = "cuda"
+BF = torch.bfloat16
+
+
+def _nops():
+    from fbamtrain_b200.ops import native, native_ops
+    return native, native_ops
+
+
+def _rel_err(a, b):
+    return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 256, 512), (4096, 4096, 4096), (300, 200, 136),
+                                   (1000, 72, 256), (64, 64, 64), (8192, 1024, 4096)])
+def test_gemm_k_major(m, n, k):
+    nv, no = _nops()
+    torch.manual_seed(0)
+    a = torch.randn(m, k, device=DEV).to(BF)
+    b = torch.randn(n, k, device=DEV).to(BF)
+    d = no.gemm(a, b)
+    nv.check_status(a.device)
+    expect = a.float() @ b.float().t()
+    assert _rel_err(d, expect) < 5e-3
+    assert_similar(expect.to(BF), d, 0.02 * math.sqrt(k))
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 512, 320), (1024, 4096, 8192), (200, 264, 136)])
+def test_gemm_mn_major_operands(a_mn, b_mn, m, n, k):
+    nv, no = _nops()
+    torch.manual_seed(1)
+    a = torch.randn(m, k, device=DEV).to(BF)
+    b = torch.randn(n, k, device=DEV).to(BF)
+    a_in = a.t().contiguous() if a_mn else a
+    b_in = b.t().contiguous() if b_mn else b
+    d = no.gemm(a_in, b_in, a_mn=a_mn, b_mn=b_mn)
+    nv.check_status(a.device)
+    expect = a.float() @ b.float().t()
+    assert _rel_err(d, expect) < 5e-3
+
+
+def test_gemm_epilogues():
+    nv, no = _nops()
+    torch.manual_seed(2)
+    m, n, k = 512, 384, 256
+    a = torch.randn(m, k, device=DEV).to(BF)
+    b = (torch.randn(n, k, device=DEV) / math.sqrt(k)).to(BF)
+    bias = torch.randn(n, device=DEV).to(BF)
+    res = torch.randn(m, n, device=DEV).to(BF)
+    pre = torch.empty(m, n, device=DEV, dtype=BF)
+    z = a.float() @ b.float().t() + bias.float()
+    d = no.gemm(a, b, bias=bias, act="gelu", residual=res, preact_out=pre)
+    assert_similar((torch.nn.functional.gelu(z) + res.float()).to(BF), d, 3e-2)
+    assert_similar(z.to(BF), pre, 3e-2)
+    # gelu-gradient epilogue
+    aux = torch.randn(m, n, device=DEV).to(BF)
+    d2 = no.gemm(a, b, gelu_grad_in=aux)
+    assert_similar(((a.float() @ b.float().t()) * ref.gelu_grad(aux)).to(BF), d2, 3e-2)
+    # fp32 output, accumulate (read-modify-write and atomic), alpha, fp32 bias
+    c0 = torch.randn(m, n, device=DEV)
+    out = c0.clone()
+    no.gemm(a, b, out=out, accumulate=nv.GEMM_ACC_RMW, alpha=0.5)
+    assert_similar(c0 + 0.5 * (a.float() @ b.float().t()), out, 2e-3)
+    out = c0.clone()
+    no.gemm(a, b, out=out, accumulate=nv.GEMM_ACC_ATOMIC)
+    assert_similar(c0 + a.float() @ b.float().t(), out, 2e-3)
+    out = no.gemm(a, b, out_dtype=torch.float32, bias=bias.float())
+    assert_similar(z, out, 2e-3)
+    nv.check_status(a.device)
+
+
+@pytest.mark.parametrize("stride,pad,dil", [(1, 1, 1), (2, 1, 1), (1, 2, 2)])
+@pytest.mark.parametrize("shape", [(4, 24, 80, 64, 128), (3, 12, 40, 128, 64), (16, 48, 160, 128, 256)])
+def test_conv_fprop_and_dgrad(stride, pad, dil, shape):
+    nv, no = _nops()
+    n, h, w, c, o = shape
+    torch.manual_seed(3)
+    x = torch.randn(n, h, w, c, device=DEV).to(BF)
+    wt = (torch.randn(o, 3, 3, c, device=DEV) / math.sqrt(9 * c)).to(BF)
+    y = no.conv2d_fprop(x, wt, stride, pad, dil)
+    expect = ref.conv2d_nhwc(x.float(), wt.float(), stride, pad, dil)
+    assert y.shape == expect.shape
+    assert _rel_err(y, expect) < 5e-3
+    dy = torch.randn_like(expect).to(BF)
+    dx = no.conv2d_dgrad(dy, wt, (h, w), stride, pad, dil)
+    xf = x.float().requires_grad_(True)
+    ref.conv2d_nhwc(xf, wt.float(), stride, pad, dil).backward(dy.float())
+    assert _rel_err(dx, xf.grad) < 5e-3
+    nv.check_status(x.device)
+
+
+def test_linear_autograd_matches_reference():
+    nv, no = _nops()
+    torch.manual_seed(4)
+    x = torch.randn(6, 50, 256, device=DEV).to(BF).requires_grad_(True)
+    w = (torch.randn(512, 256, device=DEV) / 16).to(BF).requires_grad_(True)
+    b = torch.randn(512, device=DEV).to(BF).requires_grad_(True)
+    for act in ("none", "gelu"):
+        y = no.linear(x, w, b, act)
+        g = torch.randn_like(y)
+        gx, gw, gb = torch.autograd.grad(y, (x, w, b), g)
+        xf, wf, bf = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+        yf = ref.linear(xf, wf, bf, act)
+        ex, ew, eb = torch.autograd.grad(yf, (xf, wf, bf), g.float())
+        assert_similar(yf.to(BF), y, 3e-2)
+        assert _rel_err(gx, ex) < 1e-2 and _rel_err(gw, ew) < 1e-2 and _rel_err(gb, eb) < 1e-2
+    nv.check_status(x.device)
+
+
+@pytest.mark.parametrize("dim", [64, 256, 1024, 2048])
+def test_rmsnorm_fwd_bwd(dim):
+    nv, no = _nops()
+    torch.manual_seed(5)
+    x = torch.randn(777, dim, device=DEV).to(BF).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(dim, device=DEV)).to(BF).requires_grad_(True)
+    y = no.rms_norm(x, w, 1e-5)
+    g = torch.randn_like(y)
+    gx, gw = torch.autograd.grad(y, (x, w), g)
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yf = ref.rms_norm(xf, wf, 1e-5)
+    ex, ew = torch.autograd.grad(yf, (xf, wf), g.float())
+    assert_similar(yf.to(BF), y, 2e-2)
+    assert_similar(ex.to(BF), gx, 3e-2)
+    assert _rel_err(gw, ew) < 1e-2
+
+
+def test_layernorm_gelu_geglu_pools():
+    nv, no = _nops()
+    torch.manual_seed(6)
+    x = torch.randn(100, 320, device=DEV).to(BF)
+    w, b = torch.randn(320, device=DEV).to(BF), torch.randn(320, device=DEV).to(BF)
+    assert_similar(ref.layer_norm(x.float(), w.float(), b.float(), 1e-5).to(BF), no.layer_norm(x, w, b, 1e-5), 3e-2)
+    xg = torch.randn(64, 512, device=DEV).to(BF).requires_grad_(True)
+    for fn, rf in ((no.gelu, ref.gelu), (no.geglu, ref.geglu)):
+        y = fn(xg)
+        g = torch.randn_like(y)
+        (gx,) = torch.autograd.grad(y, xg, g)
+        xf = xg.detach().float().requires_grad_(True)
+        yf = rf(xf)
+        (ex,) = torch.autograd.grad(yf, xf, g.float())
+        assert_similar(yf.to(BF), y, 2e-2)
+        assert_similar(ex.to(BF), gx, 3e-2)
+    xp = torch.randn(3, 8, 12, 64, device=DEV).to(BF).requires_grad_(True)
+    for fn, rf in ((no.avg_pool2x2_nhwc, ref.avg_pool2x2_nhwc),
+                   (no.global_avg_pool_nhwc, lambda t: t.float().mean(dim=(1, 2)))):
+        y = fn(xp)
+        g = torch.randn_like(y)
+        (gx,) = torch.autograd.grad(y, xp, g)
+        xf = xp.detach().float().requires_grad_(True)
+        yf = rf(xf)
+        (ex,) = torch.autograd.grad(yf, xf, g.float())
+        assert_similar(yf.to(BF), y, 2e-2)
+        assert_similar(ex.to(BF), gx, 2e-2)
+
+
+def test_cell_embed_fwd_bwd():
+    nv, no = _nops()
+    torch.manual_seed(7)
+    n, p, e, vocab = 20, 96, 128, 50
+    cells = torch.stack([torch.randint(0, vocab + 5, (n, p)), torch.randint(0, 1 << 24, (n, p)),
+                         torch.randint(0, 1 << 24, (n, p))], -1).to(torch.int32).to(DEV)
+    cp = torch.randn(vocab, e, device=DEV, requires_grad=True)
+    pos = torch.randn(p, e, device=DEV, requires_grad=True)
+    col = torch.randn(6, e, device=DEV, requires_grad=True)
+    y = no.cell_embed(cells, cp, pos, col, BF)
+    g = torch.randn_like(y)
+    got = torch.autograd.grad(y, (cp, pos, col), g)
+    yf = ref.cell_embed(cells, cp, pos, col, torch.float32)
+    exp = torch.autograd.grad(yf, (cp, pos, col), g.float())
+    assert_similar(yf.to(BF), y, 3e-2)
+    for a, b_ in zip(got, exp):
+        assert _rel_err(a, b_) < 1e-2
+
+
+def test_lm_head_ce_fwd_bwd():
+    nv, no = _nops()
+    torch.manual_seed(8)
+    rows, h, vocab = 1000, 256, 250
+    vpad = 256
+    x = torch.randn(rows, h, device=DEV).to(BF).requires_grad_(True)
+    w = (torch.randn(vpad, h, device=DEV) / 16).to(BF).requires_grad_(True)
+    t = torch.randint(0, vocab, (rows,), device=DEV)
+    old = no.LM_HEAD_CHUNK_ROWS
+    no.LM_HEAD_CHUNK_ROWS = 384          # exercise several chunks and a ragged tail
+    try:
+        loss = no.lm_head_ce(x, w, t, vocab, 1.0 / rows)
+        gx, gw = torch.autograd.grad(loss, (x, w))
+    finally:
+        no.LM_HEAD_CHUNK_ROWS = old
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    lf = ref.lm_head_ce(xf, wf, t, vocab, 1.0 / rows)
+    ex, ew = torch.autograd.grad(lf, (xf, wf))
+    assert abs(float(loss) - float(lf)) < 2e-2
+    assert _rel_err(gx, ex) < 3e-2 and _rel_err(gw, ew) < 3e-2
+    assert float(gw[vocab:].abs().max()) == 0.0
+    nv.check_status(x.device)
+
+
+def test_fused_adamw_matches_reference_rule():
+    nv, no = _nops()
+    torch.manual_seed(9)
+    n = 10_000 + 3
+    for dtype in (torch.float32, BF):
+        master = torch.randn(n, device=DEV)
+        p = master.to(dtype)
+        g = torch.randn(n, device=DEV).to(dtype)
+        m, v = torch.rand(n, device=DEV) * 0.1, torch.rand(n, device=DEV) * 0.01
+        em, ev, ew = m.clone(), v.clone(), master.clone()
+        lr, b1, b2, eps, wd, step = 1e-2, 0.9, 0.99, 1e-8, 0.1, 3
+        bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
+        no.adamw_flat(p, g, m, v, master if dtype == BF else None, 0, n, lr, b1, b2, eps, wd, bc1, bc2)
+        gf = g.float()
+        ew.mul_(1 - lr * wd)
+        em.mul_(b1).add_(gf, alpha=1 - b1)
+        ev.mul_(b2).addcmul_(gf, gf, value=1 - b2)
+        ew.addcdiv_(em / bc1, (ev / bc2).sqrt() + eps, value=-lr)
+        assert_similar(em, m, 1e-6)
+        assert_similar(ev, v, 1e-6)
+        assert_similar(ew, master if dtype == BF else p, 2e-6)
+        if dtype == BF:
+            assert torch.equal(p, master.to(BF))
+
+
+def test_model_step_native_vs_reference_path():
+    """One training step of the tiny model in bf16: native kernels against the PyTorch op definitions."""
+    from fbamtrain_b200 import RunConfiguration, Trainer, ops, presets
+    from fbamtrain_b200.data import SyntheticBatchSource
+    d = presets.tiny("bf16")
+    d["model_config"].update({"cell_embed_dim": 64, "downsample_channels": [64], "n_embed": 64})
+    cfg = RunConfiguration.from_json(d)
+    src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=0, pin=False)
+    cells, tg = src.next_batch(2, 16)
+    losses = {}
+    for backend in ("auto", "torch"):
+        ops.set_backend(backend)
+        try:
+            tr = Trainer(cfg, device=torch.device(DEV))
+            losses[backend] = [float(tr.train_step(cells, tg)) for _ in range(3)]
+            tr.close()
+        finally:
+            ops.set_backend("auto")
+    assert losses["auto"] == pytest.approx(losses["torch"], abs=5e-2)
