@@ -54,7 +54,7 @@ __device__ __forceinline__ float gelu_grad_f(float x) {
 
 // Row of the output tile -> element offset of that row in D (or -1 when the row is out of range).
 __device__ __forceinline__ long long row_offset(const GemmParams& p, int tile_m, int row) {
-  if (p.mode == GEMM_MODE_PLAIN) {
+  if (p.mode != GEMM_MODE_CONV) {
     int m = tile_m * BM + row;
     return m < p.M ? (long long)m * p.ldd : -1;
   }
@@ -69,6 +69,23 @@ __device__ __forceinline__ long long row_offset(const GemmParams& p, int tile_m,
   int oh = h * g.out_mul + g.out_off_h, ow = w * g.out_mul + g.out_off_w;
   if (oh >= g.out_h || ow >= g.out_w) return -1;
   return (((long long)n * g.out_h + oh) * g.out_w + ow) * p.ldd;
+}
+
+// Work item = (split, tile_m, tile_n): output tile plus the range of K blocks this CTA accumulates.
+struct Work {
+  int tile_m, tile_n, k_begin, k_end;
+};
+__device__ __forceinline__ Work decode_work(const GemmParams& p, int item, int tiles_n) {
+  Work w;
+  const int tiles = p.tiles_m * tiles_n;
+  const int split = item / tiles;
+  const int t = item % tiles;
+  w.tile_m = t / tiles_n;
+  w.tile_n = t % tiles_n;
+  const int per = (p.k_blocks + p.splits - 1) / p.splits;
+  w.k_begin = split * per;
+  w.k_end = min(p.k_blocks, w.k_begin + per);
+  return w;
 }
 
 template <int BN>
@@ -87,8 +104,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
   const int tiles_n = (p.N + BN - 1) / BN;
-  const int num_tiles = p.tiles_m * tiles_n;
-  const int k_blocks = p.k_blocks;
+  const int num_tiles = p.tiles_m * tiles_n * p.splits;
   constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators
 
   if (threadIdx.x == 0) {
@@ -120,7 +136,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int tile_m = tile / tiles_n, tile_n = tile % tiles_n;
+        const Work wk = decode_work(p, tile, tiles_n);
+        const int tile_m = wk.tile_m, tile_n = wk.tile_n;
         int cn = 0, ch = 0, cw = 0;
         if (p.mode == GEMM_MODE_CONV) {
           const ConvGeom& g = p.conv;
@@ -128,11 +145,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           ch = ((tile_m / g.tiles_w) % g.tiles_h) * g.th * g.in_mul;
           cn = (tile_m / (g.tiles_w * g.tiles_h)) * g.tn;
         }
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = wk.k_begin; kb < wk.k_end; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
           mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          if (p.mode == GEMM_MODE_WGRAD) {
+            // K block = brick of 64 output pixels; A = dY panel pair, B = gathered input for this tile's tap
+            const ConvGeom& g = p.conv;
+            const int bw = (kb % g.tiles_w) * g.tw;
+            const int bh = ((kb / g.tiles_w) % g.tiles_h) * g.th;
+            const int bn = (kb / (g.tiles_w * g.tiles_h)) * g.tn;
+            const int nb_per_tap = g.c_blocks * 64 / BN;  // N tiles per tap
+            const int tap = tile_n / nb_per_tap, c0 = (tile_n % nb_per_tap) * BN;
+            tma_load_4d(sa, &map_a, &full_bar[stage], tile_m * BM, bw, bh, bn);
+            tma_load_4d(sa + BK * 128, &map_a, &full_bar[stage], tile_m * BM + 64, bw, bh, bn);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_4d(sb + j * BK * 128, &map_b, &full_bar[stage], c0 + j * 64,
+                          bw * g.in_mul + g.tap_dw[tap], bh * g.in_mul + g.tap_dh[tap], bn);
+            if (++stage == L::kStages) { stage = 0; phase ^= 1; }
+            continue;
+          }
           if (p.mode == GEMM_MODE_CONV) {
             const ConvGeom& g = p.conv;
             const int tap = kb / g.c_blocks, cb = kb % g.c_blocks;
@@ -171,10 +205,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const Work wk = decode_work(p, tile, tiles_n);
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { ok = false; break; }
         fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = wk.k_begin; kb < wk.k_end; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
           fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
@@ -183,7 +218,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t da = make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
             const uint64_t db = make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
-            mma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0);
+            mma_f16_ss(d_tmem, da, db, idesc, ((kb - wk.k_begin) | k) != 0);
           }
           mma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
           if (++stage == L::kStages) { stage = 0; phase ^= 1; }
@@ -202,7 +237,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int tile_m = tile / tiles_n, tile_n = tile % tiles_n;
+      const Work wk = decode_work(p, tile, tiles_n);
+      const int tile_m = wk.tile_m, tile_n = wk.tile_n;
       if (!mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
       fence_after_sync();
       const long long roff = row_offset(p, tile_m, row);
@@ -213,7 +249,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         tmem_ld_32x32(taddr + c0, r);
         tmem_ld_wait();
         const int n0 = tile_n * BN + c0;
-        if (roff < 0 || n0 >= p.N) continue;
+        if (roff < 0 || n0 >= p.N || wk.k_end <= wk.k_begin) continue;
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
@@ -413,7 +449,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStre
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const int tiles = p.tiles_m * ((p.N + BN - 1) / BN);
+  const int tiles = p.tiles_m * ((p.N + BN - 1) / BN) * p.splits;
   int grid = tiles < g_num_sms ? tiles : g_num_sms;
   if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
   gemm_kernel<BN><<<grid, kThreads, L::kTotal, stream>>>(ma, mb, p);
@@ -438,6 +474,9 @@ extern "C" int fbam_gemm_bf16(const void* A, long long lda, int a_mn_major, cons
   p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
   p.tiles_m = (M + BM - 1) / BM;
   p.k_blocks = (K + BK - 1) / BK;
+  if (p.splits < 1) p.splits = 1;
+  if (p.splits > p.k_blocks) p.splits = p.k_blocks;
+  if (p.splits > 1 && !(p.out_fp32 && p.accumulate == GEMM_ACC_ATOMIC)) return GEMM_ERR_SHAPE;
   const int bn = pick_bn(N, p.bn);
   const int elt = p.out_fp32 ? 4 : 2;
   p.vec_ok = (p.ldd % (16 / elt) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&
@@ -475,6 +514,7 @@ extern "C" int fbam_conv_bf16(const void* X, int in_h, int in_w, int C, const vo
   p.M = p.tiles_m * BM;
   p.N = N; p.K = g.num_taps * C;
   p.k_blocks = g.num_taps * g.c_blocks;
+  p.splits = 1;
   const int bn = pick_bn(N, p.bn);
   const int elt = p.out_fp32 ? 4 : 2;
   p.vec_ok = (p.ldd % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) && (p.ldd % (16 / elt) == 0);
@@ -482,6 +522,50 @@ extern "C" int fbam_conv_bf16(const void* X, int in_h, int in_w, int C, const vo
   int e = encode_nhwc(&ma, X, g.batch, in_h, in_w, C, g.tn, g.th, g.tw, g.in_mul);
   if (e) return e;
   e = encode_2d(&mb, Wmat, N, p.K, ldw, bn);
+  if (e) return e;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 64) return launch<64>(ma, mb, p, s);
+  if (bn == 128) return launch<128>(ma, mb, p, s);
+  return launch<256>(ma, mb, p, s);
+}
+
+// Convolution weight gradient as a split-K GEMM over output pixels:
+//   dW[o, tap, c] += sum_pixels dY[pixel, o] * X[gather(pixel, tap), c]
+// dY: NHWC [batch, out_h, out_w, O]; X: NHWC [batch, in_h, in_w, C]; dW: fp32 [O, taps*C], must be zeroed by
+// the caller (CTAs add their partial sums atomically).  conv.{tn,th,tw} describe the 64-pixel K brick.
+extern "C" int fbam_conv_wgrad_bf16(const void* dY, int O, const void* X, int in_h, int in_w, int C,
+                                    GemmParams* params, void* stream) {
+  GemmParams p = *params;
+  ConvGeom& g = p.conv;
+  if (C % 64 != 0 || O % 8 != 0 || g.tn * g.th * g.tw != BK || g.num_taps < 1 || g.num_taps > 9) return GEMM_ERR_SHAPE;
+  if (!p.out_fp32) return GEMM_ERR_SHAPE;
+  p.mode = GEMM_MODE_WGRAD;
+  p.a_mn_major = 1; p.b_mn_major = 1;
+  p.accumulate = GEMM_ACC_ATOMIC;
+  g.c_blocks = C / 64;
+  g.tiles_w = (g.grid_w + g.tw - 1) / g.tw;
+  g.tiles_h = (g.grid_h + g.th - 1) / g.th;
+  const int bricks = g.tiles_w * g.tiles_h * ((g.batch + g.tn - 1) / g.tn);
+  p.M = O; p.N = g.num_taps * C; p.K = bricks * BK;
+  p.tiles_m = (O + BM - 1) / BM;
+  p.k_blocks = bricks;
+  int bn = (C % 256 == 0) ? 256 : (C % 128 == 0 ? 128 : 64);
+  if (p.bn == 64 || (p.bn == 128 && C % 128 == 0)) bn = p.bn;
+  if (p.splits < 1) {
+    if (g_num_sms == 0) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const int tiles = p.tiles_m * (p.N / bn);
+    p.splits = (g_num_sms + tiles - 1) / tiles;
+  }
+  if (p.splits > bricks) p.splits = bricks;
+  p.vec_ok = 0;
+  CUtensorMap ma, mb;
+  int e = encode_nhwc(&ma, dY, g.batch, g.grid_h, g.grid_w, O, g.tn, g.th, g.tw, 1);
+  if (e) return e;
+  e = encode_nhwc(&mb, X, g.batch, in_h, in_w, C, g.tn, g.th, g.tw, g.in_mul);
   if (e) return e;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (bn == 64) return launch<64>(ma, mb, p, s);

@@ -4,7 +4,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
-enum { GEMM_MODE_PLAIN = 0, GEMM_MODE_CONV = 1 };
+enum { GEMM_MODE_PLAIN = 0, GEMM_MODE_CONV = 1, GEMM_MODE_WGRAD = 2 };
 enum { GEMM_ACT_NONE = 0, GEMM_ACT_GELU = 1, GEMM_ACT_RELU = 2 };
 enum { GEMM_ACC_NONE = 0, GEMM_ACC_RMW = 1, GEMM_ACC_ATOMIC = 2 };
 enum {
@@ -40,6 +40,7 @@ struct GemmParams {
   int out_fp32, bias_fp32, act, accumulate;
   int bn;                           // 0 = choose from N; else 64 / 128 / 256
   int max_ctas;                     // 0 = one per SM
+  int splits;                       // split-K factor (needs fp32 output with atomic accumulation); 0/1 = none
   // filled by the launcher
   int mode, M, N, K, tiles_m, k_blocks, a_mn_major, b_mn_major, vec_ok;
   ConvGeom conv;

@@ -1,0 +1,303 @@
+// Persistent recurrent LSTM kernels.
+//
+// The input projection X·W_ihᵀ for the whole sequence is one large tensor-core GEMM done elsewhere; what
+// remains per time step is a (batch ≤ 8) x H · H x 4H product plus the gate arithmetic — far too small to
+// launch as kernels 1024 times.  These kernels run the whole sequence in one cooperative launch:
+//
+//  * forward: CTA j owns 8 hidden units (32 gate rows of W_hh).  Its W_hh slice is loaded ONCE into
+//    registers as mma.sync A-fragments (8 warps split K) and stays there for all T steps.  Per step
+//    every warp multiplies its K-slice with h_{t-1} (read from a double-buffered global vector through
+//    L2), partial sums are reduced through shared memory, 64 threads apply the gate non-linearities,
+//    keep the cell state in registers, and publish the CTA's 8 new h values; one grid-wide barrier
+//    (monotonic counter, bounded spin) separates steps.  The buffer of gate pre-activations is
+//    overwritten in place with the activated gates, which is exactly what the backward pass needs.
+//  * backward (BPTT): CTA j owns 16 hidden units: it keeps the matching 16 rows of W_hhᵀ (K = 4H) in
+//    registers, does the point-wise gate gradient for its units, writes dGates[t] (bf16 — the big
+//    dX / dW GEMMs consume it later), and after the barrier multiplies all of dGates[t] with its
+//    W_hhᵀ rows to obtain dh_{t-1} for its own units, which never leaves the CTA.
+//
+// (The batch dimension is the 8-wide N of mma.sync.m16n8k16; the legacy tensor path is the right tool
+// here: tcgen05 tiles start at M = 64 rows per CTA and would be ≥ 87 % padding for this shape.)
+#include <cooperative_groups.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr unsigned kBarrierSpinLimit = 1u << 22;
+enum { LSTM_ERR_BARRIER_TIMEOUT = 201 };
+
+__device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// All CTAs arrive; returns false (in every thread) if the wait ran out.
+__device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target, int* status) {
+  __syncthreads();
+  int ok = 1;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(counter, 1u);
+    unsigned spins = 0;
+    while (ld_acquire(counter) < target) {
+      if (++spins > kBarrierSpinLimit) { ok = 0; break; }
+      __nanosleep(20);
+    }
+    if (!ok) atomicExch(status, LSTM_ERR_BARRIER_TIMEOUT);
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+// -------------------------------------------------------------------------------------------------
+// forward
+// -------------------------------------------------------------------------------------------------
+template <int MAXKS>  // k-steps (of 16) per warp: H <= MAXKS * 8 * 16
+__global__ void __launch_bounds__(kThreads, 1)
+lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const float* __restrict__ h0,
+                const float* __restrict__ c0, bf16* __restrict__ y, float* __restrict__ c_all, bf16* hbuf,
+                unsigned* counter, int* status, int T, int B, int H) {
+  __shared__ float part[kWarps][2][16][8];
+  __shared__ float pre[32][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int unit0 = blockIdx.x * 8;
+  const int nks = H / 16;
+
+  // W_hh slice -> registers (A fragments).  Tile 0 rows: gate i (0-7), gate f (8-15); tile 1: g, o.
+  uint32_t afrag[2][MAXKS][4];
+#pragma unroll
+  for (int tile = 0; tile < 2; ++tile)
+#pragma unroll
+    for (int j = 0; j < MAXKS; ++j) {
+      const int ks = warp + kWarps * j;
+      const bool on = ks < nks;
+      const int k = ks * 16 + q * 2;
+      const bf16* r_lo = whh + ((long long)(tile * 2) * H + unit0 + g) * H;      // row g   of the tile
+      const bf16* r_hi = whh + ((long long)(tile * 2 + 1) * H + unit0 + g) * H;  // row g+8 of the tile
+      afrag[tile][j][0] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k) : 0u;
+      afrag[tile][j][1] = on ? *reinterpret_cast<const uint32_t*>(r_hi + k) : 0u;
+      afrag[tile][j][2] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k + 8) : 0u;
+      afrag[tile][j][3] = on ? *reinterpret_cast<const uint32_t*>(r_hi + k + 8) : 0u;
+    }
+
+  // initial state: threads 0..63 own (unit u, batch b)
+  const int u = threadIdx.x >> 3, b = threadIdx.x & 7;
+  float c = 0.0f;
+  if (threadIdx.x < 64) {
+    c = c0[unit0 + u];
+    hbuf[(long long)b * H + unit0 + u] = __float2bfloat16(h0[unit0 + u]);
+  }
+  unsigned bar = 0;
+  if (!grid_barrier(counter, ++bar * gridDim.x, status)) return;
+
+  for (int t = 0; t < T; ++t) {
+    const bf16* hprev = hbuf + (long long)(t & 1) * 8 * H;
+    bf16* hnext = hbuf + (long long)((t + 1) & 1) * 8 * H;
+    float acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+#pragma unroll
+    for (int j = 0; j < MAXKS; ++j) {
+      const int ks = warp + kWarps * j;
+      if (ks < nks) {
+        const bf16* hp = hprev + (long long)g * H + ks * 16 + q * 2;  // B fragment: n = g (batch), k pairs
+        const uint32_t b0 = __ldcg(reinterpret_cast<const unsigned int*>(hp));
+        const uint32_t b1 = __ldcg(reinterpret_cast<const unsigned int*>(hp + 8));
+        mma_16816(acc[0], afrag[0][j], b0, b1);
+        mma_16816(acc[1], afrag[1][j], b0, b1);
+      }
+    }
+#pragma unroll
+    for (int tile = 0; tile < 2; ++tile) {
+      part[warp][tile][g][q * 2] = acc[tile][0];
+      part[warp][tile][g][q * 2 + 1] = acc[tile][1];
+      part[warp][tile][g + 8][q * 2] = acc[tile][2];
+      part[warp][tile][g + 8][q * 2 + 1] = acc[tile][3];
+    }
+    __syncthreads();
+    {
+      const int row = threadIdx.x >> 3, bb = threadIdx.x & 7;  // 32 rows x 8 batch = 256 threads
+      const int tile = row >> 4, r = row & 15;
+      float s = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) s += part[w][tile][r][bb];
+      const int gate = tile * 2 + (r >> 3), uu = r & 7;
+      if (bb < B) s += gates[((long long)t * B + bb) * 4 * H + (long long)gate * H + unit0 + uu];
+      pre[row][bb] = s;
+    }
+    __syncthreads();
+    if (threadIdx.x < 64) {
+      const float ig = sigmoid_f(pre[u][b]), fg = sigmoid_f(pre[8 + u][b]);
+      const float gg = tanhf(pre[16 + u][b]), og = sigmoid_f(pre[24 + u][b]);
+      c = fg * c + ig * gg;
+      const float h = og * tanhf(c);
+      const bf16 hb = __float2bfloat16(h);
+      if (b < B) {
+        float* gt = gates + ((long long)t * B + b) * 4 * H + unit0 + u;
+        gt[0] = ig; gt[H] = fg; gt[2 * (long long)H] = gg; gt[3 * (long long)H] = og;
+        y[((long long)t * B + b) * H + unit0 + u] = hb;
+        c_all[((long long)t * B + b) * H + unit0 + u] = c;
+        hnext[(long long)b * H + unit0 + u] = hb;
+      } else {
+        hnext[(long long)b * H + unit0 + u] = __float2bfloat16(0.0f);
+      }
+    }
+    if (!grid_barrier(counter, ++bar * gridDim.x, status)) return;
+  }
+}
+
+// -------------------------------------------------------------------------------------------------
+// backward
+// -------------------------------------------------------------------------------------------------
+template <int MAXKS>  // k-steps per warp: 4H <= MAXKS * 8 * 16
+__global__ void __launch_bounds__(kThreads, 1)
+lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all, const float* __restrict__ c0,
+                const bf16* __restrict__ dy, const bf16* __restrict__ whh_t, bf16* dgates, float* __restrict__ dh0,
+                float* __restrict__ dc0, const float* __restrict__ dh_last, const float* __restrict__ dc_last,
+                unsigned* counter, int* status, int T, int B, int H) {
+  __shared__ float part[kWarps][16][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int unit0 = blockIdx.x * 16;
+  const int K = 4 * H, nks = K / 16;
+
+  uint32_t afrag[MAXKS][4];
+#pragma unroll
+  for (int j = 0; j < MAXKS; ++j) {
+    const int ks = warp + kWarps * j;
+    const bool on = ks < nks;
+    const int k = ks * 16 + q * 2;
+    const bf16* r_lo = whh_t + (long long)(unit0 + g) * K;
+    const bf16* r_hi = whh_t + (long long)(unit0 + g + 8) * K;
+    afrag[j][0] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k) : 0u;
+    afrag[j][1] = on ? *reinterpret_cast<const uint32_t*>(r_hi + k) : 0u;
+    afrag[j][2] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k + 8) : 0u;
+    afrag[j][3] = on ? *reinterpret_cast<const uint32_t*>(r_hi + k + 8) : 0u;
+  }
+
+  const int u = threadIdx.x >> 3, b = threadIdx.x & 7;  // threads 0..127 own (unit u of 16, batch b)
+  const bool owner = threadIdx.x < 128 && b < B;
+  const int unit = unit0 + u;
+  float dh_next = 0.0f, dc_next = 0.0f;
+  if (owner) {
+    if (dh_last != nullptr) dh_next = dh_last[(long long)b * H + unit];
+    if (dc_last != nullptr) dc_next = dc_last[(long long)b * H + unit];
+  }
+  unsigned bar = 0;
+
+  for (int t = T - 1; t >= 0; --t) {
+    if (owner) {
+      const float* gt = gates + ((long long)t * B + b) * K + unit;
+      const float ig = gt[0], fg = gt[H], gg = gt[2 * (long long)H], og = gt[3 * (long long)H];
+      const float ct = c_all[((long long)t * B + b) * H + unit];
+      const float cp = t > 0 ? c_all[((long long)(t - 1) * B + b) * H + unit] : c0[unit];
+      const float dh = __bfloat162float(dy[((long long)t * B + b) * H + unit]) + dh_next;
+      const float tc = tanhf(ct);
+      const float d_o = dh * tc * og * (1.0f - og);
+      const float dc = dh * og * (1.0f - tc * tc) + dc_next;
+      const float d_i = dc * gg * ig * (1.0f - ig);
+      const float d_f = dc * cp * fg * (1.0f - fg);
+      const float d_g = dc * ig * (1.0f - gg * gg);
+      dc_next = dc * fg;
+      bf16* dg = dgates + ((long long)t * B + b) * K + unit;
+      dg[0] = __float2bfloat16(d_i);
+      dg[H] = __float2bfloat16(d_f);
+      dg[2 * (long long)H] = __float2bfloat16(d_g);
+      dg[3 * (long long)H] = __float2bfloat16(d_o);
+    }
+    if (!grid_barrier(counter, ++bar * gridDim.x, status)) return;
+    // dh_{t-1}[b, unit] = sum_k dGates[t][b, k] * W_hh[k, unit]
+    float acc[4] = {0, 0, 0, 0};
+    const bf16* dgt = dgates + (long long)t * B * K;
+#pragma unroll
+    for (int j = 0; j < MAXKS; ++j) {
+      const int ks = warp + kWarps * j;
+      if (ks < nks) {
+        uint32_t b0 = 0, b1 = 0;
+        if (g < B) {
+          const bf16* p = dgt + (long long)g * K + ks * 16 + q * 2;
+          b0 = __ldcg(reinterpret_cast<const unsigned int*>(p));
+          b1 = __ldcg(reinterpret_cast<const unsigned int*>(p + 8));
+        }
+        mma_16816(acc, afrag[j], b0, b1);
+      }
+    }
+    part[warp][g][q * 2] = acc[0];
+    part[warp][g][q * 2 + 1] = acc[1];
+    part[warp][g + 8][q * 2] = acc[2];
+    part[warp][g + 8][q * 2 + 1] = acc[3];
+    __syncthreads();
+    if (threadIdx.x < 128) {
+      float s = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) s += part[w][u][b];
+      dh_next = s;
+    }
+    __syncthreads();
+  }
+  if (owner) {
+    dh0[(long long)b * H + unit] = dh_next;
+    dc0[(long long)b * H + unit] = dc_next;
+  }
+}
+
+template <typename K>
+int coop_launch(K kernel, int grid, void** args, cudaStream_t stream) {
+  int dev = 0, sms = 0, per_sm = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess) return 5;
+  if (grid > sms * per_sm) return 1;  // all CTAs must be co-resident
+  return cudaLaunchCooperativeKernel((void*)kernel, dim3(grid), dim3(kThreads), args, 0, stream) == cudaSuccess ? 0 : 5;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Largest hidden size the register-resident kernels accept (and the batch limit is 8).
+int fbam_lstm_persistent_max_hidden() { return 1024; }
+
+// gates: (T, B, 4H) fp32, pre-activations incl. bias on entry, activated gates on exit.
+// hbuf: 2*8*H bf16 scratch; counter: one zeroed unsigned.
+int fbam_lstm_fwd(float* gates, const void* whh, const float* h0, const float* c0, void* y, float* c_all,
+                  void* hbuf, unsigned* counter, int* status, int T, int B, int H, void* stream) {
+  if (B < 1 || B > 8 || H % 16 != 0 || H > 1024 || T < 1) return 1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(counter, 0, sizeof(unsigned), s) != cudaSuccess) return 5;
+  void* args[] = {&gates, &whh, &h0, &c0, &y, &c_all, &hbuf, &counter, &status, &T, &B, &H};
+  const int grid = H / 8;
+  if (H <= 256) return coop_launch(lstm_fwd_kernel<2>, grid, args, s);
+  if (H <= 512) return coop_launch(lstm_fwd_kernel<4>, grid, args, s);
+  return coop_launch(lstm_fwd_kernel<8>, grid, args, s);
+}
+
+// whh_t: (H, 4H) bf16 = W_hh transposed.  dgates: (T, B, 4H) bf16 out.  dh0/dc0: (B, H) fp32 out.
+int fbam_lstm_bwd(const float* gates, const float* c_all, const float* c0, const void* dy, const void* whh_t,
+                  void* dgates, float* dh0, float* dc0, const float* dh_last, const float* dc_last, unsigned* counter,
+                  int* status, int T, int B, int H, void* stream) {
+  if (B < 1 || B > 8 || H % 16 != 0 || H > 1024 || T < 1) return 1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(counter, 0, sizeof(unsigned), s) != cudaSuccess) return 5;
+  void* args[] = {&gates, &c_all, &c0, &dy, &whh_t, &dgates, &dh0, &dc0, &dh_last, &dc_last, &counter, &status,
+                  &T, &B, &H};
+  const int grid = H / 16;
+  if (H <= 256) return coop_launch(lstm_bwd_kernel<8>, grid, args, s);
+  if (H <= 512) return coop_launch(lstm_bwd_kernel<16>, grid, args, s);
+  return coop_launch(lstm_bwd_kernel<32>, grid, args, s);
+}
+
+}  // extern "C"

@@ -1,12 +1,43 @@
-"""Convolution weight gradient ``dW[o, r, s, c] = Σ_{n,oh,ow} dY[n,oh,ow,o] · X[n, oh·stride + r·dil − pad, …, c]``."""
+"""Convolution weight gradient ``dW[o, r, s, c] = Σ_{n,oh,ow} dY[n,oh,ow,o] · X[n, oh·stride + r·dil − pad, …, c]``.
+
+Run as a split-K tensor-core GEMM whose K dimension is the output pixels: both operands are read in
+place through 4-D TMA gathers (``dY`` bricks of 64 pixels as the transposed A operand, the input
+shifted by the filter tap as the transposed B operand), each CTA accumulates one ``128 x BN`` tile of
+``dW`` for one tap over its share of the pixels in tensor memory, and partial tiles are added into an
+fp32 ``dW`` with atomics.
+"""
 from __future__ import annotations
+
+import ctypes as C
 
 import torch
 
+from . import native as nv
 
-def conv2d_wgrad(x, dy, w_shape, stride, padding, dilation):
-    # Interim: library kernel.  The tcgen05 split-K wgrad replaces this.
+
+def conv2d_wgrad(x, dy, w_shape, stride, padding, dilation, out_dtype=torch.bfloat16, splits: int = 0, bn: int = 0):
+    from .native_ops import _brick
     o, _, _, c = w_shape
-    dw = torch.nn.grad.conv2d_weight(x.permute(0, 3, 1, 2), (o, c, 3, 3), dy.permute(0, 3, 1, 2), stride, padding,
-                                     dilation)
-    return dw.permute(0, 2, 3, 1).contiguous()
+    b, ih, iw, _ = x.shape
+    _, oh, ow, _ = dy.shape
+    if c % 64 != 0 or o % 8 != 0:
+        dw = torch.nn.grad.conv2d_weight(x.permute(0, 3, 1, 2), (o, c, 3, 3), dy.permute(0, 3, 1, 2), stride, padding,
+                                         dilation)
+        return dw.permute(0, 2, 3, 1).contiguous().to(out_dtype)
+    dw = torch.zeros(o, 9 * c, dtype=torch.float32, device=x.device)
+    p = nv.GemmParams()
+    g = p.conv
+    g.batch, g.grid_h, g.grid_w = b, oh, ow
+    g.tn, g.th, g.tw = _brick(b, oh, ow, 64)
+    g.in_mul = stride
+    g.num_taps = 9
+    for i in range(9):
+        g.tap_dh[i], g.tap_dw[i] = (i // 3) * dilation - padding, (i % 3) * dilation - padding
+    p.D, p.ldd = dw.data_ptr(), 9 * c
+    p.status = nv.status_word(x.device).data_ptr()
+    p.alpha = 1.0
+    p.out_fp32 = 1
+    p.splits, p.bn = splits, bn
+    code = nv.lib().fbam_conv_wgrad_bf16(nv.ptr(dy), o, nv.ptr(x), ih, iw, c, C.byref(p), nv.stream_ptr())
+    nv.check(code, "fbam_conv_wgrad_bf16")
+    return dw.view(o, 3, 3, c).to(out_dtype)

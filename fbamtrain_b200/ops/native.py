@@ -21,7 +21,8 @@ GEMM_ACT = {"none": 0, "gelu": 1, "relu": 2}
 GEMM_ACC_NONE, GEMM_ACC_RMW, GEMM_ACC_ATOMIC = 0, 1, 2
 _ERRORS = {1: "unsupported shape", 2: "operand not 16-byte aligned", 3: "tensor-map encode failed",
            4: "driver entry point unavailable", 5: "kernel launch failed",
-           101: "TMA producer wait timed out", 102: "MMA wait timed out", 103: "epilogue wait timed out"}
+           101: "TMA producer wait timed out", 102: "MMA wait timed out", 103: "epilogue wait timed out",
+           201: "LSTM grid barrier timed out"}
 
 
 class ConvGeom(C.Structure):
@@ -43,7 +44,7 @@ class GemmParams(C.Structure):
                 ("status", C.c_void_p),
                 ("alpha", C.c_float),
                 ("out_fp32", C.c_int), ("bias_fp32", C.c_int), ("act", C.c_int), ("accumulate", C.c_int),
-                ("bn", C.c_int), ("max_ctas", C.c_int),
+                ("bn", C.c_int), ("max_ctas", C.c_int), ("splits", C.c_int),
                 ("mode", C.c_int), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("tiles_m", C.c_int),
                 ("k_blocks", C.c_int), ("a_mn_major", C.c_int), ("b_mn_major", C.c_int), ("vec_ok", C.c_int),
                 ("conv", ConvGeom)]
@@ -61,6 +62,8 @@ def lib() -> C.CDLL:
         _lib = C.CDLL(LIB_PATH)
         _lib.fbam_gemm_bf16.restype = C.c_int
         _lib.fbam_conv_bf16.restype = C.c_int
+        _lib.fbam_conv_wgrad_bf16.restype = C.c_int
+        _lib.fbam_lstm_persistent_max_hidden.restype = C.c_int
     return _lib
 
 

@@ -159,14 +159,14 @@ def linear(x, weight, bias=None, act="none"):
 # =================================================================================================
 # convolution (implicit GEMM)
 # =================================================================================================
-def _brick(n: int, h: int, w: int) -> Tuple[int, int, int]:
-    """Splits the 128 rows of a tile into (tn, th, tw) positions with the least padding waste."""
-    best, best_cost = (1, 1, 128), None
+def _brick(n: int, h: int, w: int, total: int = 128) -> Tuple[int, int, int]:
+    """Splits the `total` rows of a tile into (tn, th, tw) positions with the least padding waste."""
+    best, best_cost = (1, 1, total), None
     for tw in (1, 2, 4, 8, 16, 32, 64, 128):
         for th in (1, 2, 4, 8, 16, 32, 64, 128):
-            if tw * th > 128:
+            if tw * th > total:
                 continue
-            tn = 128 // (tw * th)
+            tn = total // (tw * th)
             cost = (math.ceil(w / tw) * tw) * (math.ceil(h / th) * th) * (math.ceil(n / tn) * tn)
             # prefer wide bricks on ties: longer contiguous runs per TMA box row
             key = (cost, -tw, -th)
@@ -513,7 +513,7 @@ def adamw_flat(param, grad, m, v, master, lo, hi, lr, b1, b2, eps, wd, bc1, bc2,
 # attention and LSTM sequence
 # =================================================================================================
 def attention(q, k, v, causal):
-    from .attention import flash_attention
+    from .mha import flash_attention
     return flash_attention(q, k, v, causal)
 
 

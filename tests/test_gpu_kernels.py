@@ -252,3 +252,51 @@ def test_model_step_native_vs_reference_path():
         finally:
             ops.set_backend("auto")
     assert losses["auto"] == pytest.approx(losses["torch"], abs=5e-2)
+
+
+@pytest.mark.parametrize("t_len,b,i_dim,h", [(5, 2, 64, 64), (33, 8, 128, 256), (16, 3, 256, 1024)])
+def test_persistent_lstm_fwd_bwd(t_len, b, i_dim, h):
+    nv, no = _nops()
+    from fbamtrain_b200.ops import lstm as L
+    torch.manual_seed(10)
+    x = torch.randn(t_len, b, i_dim, device=DEV).to(BF).requires_grad_(True)
+    k = 1.0 / math.sqrt(h)
+    w_ih = ((torch.rand(4 * h, i_dim, device=DEV) * 2 - 1) * k).requires_grad_(True)
+    w_hh = ((torch.rand(4 * h, h, device=DEV) * 2 - 1) * k).requires_grad_(True)
+    b_ih = ((torch.rand(4 * h, device=DEV) * 2 - 1) * k).requires_grad_(True)
+    b_hh = ((torch.rand(4 * h, device=DEV) * 2 - 1) * k).requires_grad_(True)
+    h0 = (0.1 * torch.randn(h, device=DEV)).requires_grad_(True)
+    c0 = (0.1 * torch.randn(h, device=DEV)).requires_grad_(True)
+    params = (x, w_ih, w_hh, b_ih, b_hh, h0, c0)
+    assert L.persistent_ok(b, h)
+    y, hT, cT = L.lstm_sequence(*params, BF)
+    nv.check_status(x.device)
+    g = torch.randn_like(y)
+    got = torch.autograd.grad((y.float() * g.float()).sum() + cT.sum(), params)
+    nv.check_status(x.device)
+    fp = [p.detach().float().requires_grad_(True) for p in params]
+    yf, hf, cf = ref.lstm_sequence(*fp, torch.float32)
+    exp = torch.autograd.grad((yf * g.float()).sum() + cf.sum(), fp)
+    assert_similar(yf.to(BF), y, 3e-2)
+    assert_similar(cf, cT, 3e-2)
+    names = ["dx", "dw_ih", "dw_hh", "db_ih", "db_hh", "dh0", "dc0"]
+    for name, a, e in zip(names, got, exp):
+        assert _rel_err(a, e) < 4e-2, (name, _rel_err(a, e))
+
+
+@pytest.mark.parametrize("stride,pad,dil", [(1, 1, 1), (2, 1, 1), (1, 2, 2)])
+@pytest.mark.parametrize("shape", [(4, 24, 80, 64, 128), (3, 12, 40, 128, 64), (16, 48, 160, 128, 256),
+                                   (5, 10, 14, 256, 512)])
+def test_conv_wgrad(stride, pad, dil, shape):
+    nv, no = _nops()
+    from fbamtrain_b200.ops.conv_wgrad import conv2d_wgrad
+    n, h, w, c, o = shape
+    torch.manual_seed(11)
+    x = torch.randn(n, h, w, c, device=DEV).to(BF)
+    wt = torch.zeros(o, 3, 3, c, device=DEV, requires_grad=True)
+    yf = ref.conv2d_nhwc(x.float(), wt, stride, pad, dil)
+    dy = torch.randn_like(yf).to(BF)
+    (expect,) = torch.autograd.grad(yf, wt, dy.float())
+    got = conv2d_wgrad(x, dy, wt.shape, stride, pad, dil, out_dtype=torch.float32)
+    nv.check_status(x.device)
+    assert _rel_err(got, expect) < 5e-3
