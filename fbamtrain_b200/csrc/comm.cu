@@ -1,0 +1,395 @@
+// Kernels that fuse data-parallel communication with the arithmetic around it, over NVLink / NVSwitch peer
+// memory.  Every rank maps every peer's window (gradient buffers, parameter buffers, flag words) into its
+// own address space; kernels then load from and store to peers directly (or through an NVSwitch multicast
+// address with multimem instructions), so no NCCL call is on these paths.
+//
+//  * fbam_rs_adamw_ag     — gradient reduce-scatter + bf16→fp32 cast/scale + sharded AdamW + parameter
+//                           all-gather, one launch per flat bucket: each rank sums ITS slice of the bucket
+//                           over all peers' gradient buffers, updates its slice of the fp32 master / m / v,
+//                           and writes the rounded parameters into every peer's parameter buffer.
+//  * fbam_reduce_pull     — sum of all peers' gradients for a range (Muon: the owner of a matrix gathers its
+//                           gradient), fused with the momentum update and the Frobenius-norm partial sum.
+//  * fbam_push_shard      — copy a range of a local buffer into every peer's buffer and raise a per-source
+//                           ready flag (all-gather whose consumers wait per shard, e.g. the flag-gated GEMM).
+//  * fbam_peer_barrier    — stand-alone cross-GPU barrier on the flag words.
+//
+// Synchronisation is by epoch-tagged flag words in peer memory: a rank publishes epoch e by storing e into
+// its slot of every peer's flag array (st.release.sys after a system-scope fence) and waits until all slots
+// of its own array hold >= e (ld.acquire.sys).  Every wait is bounded; when it runs out the kernel records
+// COMM_ERR_PEER_TIMEOUT plus the rank it was waiting for in `status` and returns, leaving the context usable.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define FBAM_MAX_RANKS 8
+
+struct PeerPtrs {
+  void* p[FBAM_MAX_RANKS];
+};
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+enum { COMM_ERR_PEER_TIMEOUT = 301 };
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// Bounded wait until flags[slot*MAX + r] >= epoch for every r < world.  `spin_limit` polls per rank.
+__device__ __forceinline__ bool wait_all(const unsigned* my_flags, int slot, int world, unsigned epoch,
+                                         unsigned spin_limit, int* status) {
+  for (int r = 0; r < world; ++r) {
+    const unsigned* f = my_flags + slot * FBAM_MAX_RANKS + r;
+    unsigned spins = 0;
+    while ((int)(ld_acquire_sys(f) - epoch) < 0) {
+      if (++spins > spin_limit) {
+        atomicExch(status, COMM_ERR_PEER_TIMEOUT + 1000 * (r + 1));
+        return false;
+      }
+      __nanosleep(100);
+    }
+  }
+  return true;
+}
+
+// Grid-wide, cross-GPU barrier.  CTA 0 publishes this rank's arrival to every peer (after all CTAs of this
+// grid have arrived locally when `local_arrive` is given), and every CTA waits on the local flag array.
+__device__ bool signal_and_wait(const PeerPtrs& flags, int rank, int world, int slot, unsigned epoch,
+                                unsigned spin_limit, int* status, unsigned* local_arrive, unsigned arrive_target) {
+  __syncthreads();
+  int ok = 1;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    bool publish = (blockIdx.x == 0);
+    if (local_arrive != nullptr) {
+      // last CTA to arrive publishes, so that peers see the signal only after the whole grid's writes
+      const unsigned prev = atomicAdd(local_arrive, 1u);
+      publish = (prev + 1 == arrive_target);
+      if (publish) __threadfence_system();
+    }
+    if (publish) {
+      for (int r = 0; r < world; ++r)
+        st_release_sys(reinterpret_cast<unsigned*>(flags.p[r]) + slot * FBAM_MAX_RANKS + rank, epoch);
+    }
+    ok = wait_all(reinterpret_cast<const unsigned*>(flags.p[rank]), slot, world, epoch, spin_limit, status) ? 1 : 0;
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack_bf16x8(const float* f) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return raw;
+}
+
+struct AdamArgs {
+  float lr, b1, b2, eps, wd, inv_bc1, inv_bc2, grad_scale;
+};
+
+// -------------------------------------------------------------------------------------------------
+// reduce-scatter + AdamW + all-gather.  The shard [lo, hi) (element indices, multiples of 8) is this rank's.
+// BF16 = parameters/gradients are bf16 with an fp32 master copy; otherwise they are fp32 (no master).
+// MULTIMEM = gradients are summed by the switch (multimem.ld_reduce) and parameters broadcast by it
+// (multimem.st) through the multicast addresses mc_grad / mc_param.
+// -------------------------------------------------------------------------------------------------
+template <bool BF16, bool MULTIMEM>
+__global__ void __launch_bounds__(256)
+rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_grad, void* mc_param, float* m, float* v,
+                   float* master, long long lo, long long hi, AdamArgs a, int rank, int world, unsigned epoch,
+                   int sync, unsigned spin_limit, int* status, unsigned* arrive) {
+  // phase 0: every rank's gradients are complete (this kernel is stream-ordered after the local backward)
+  if (sync && !signal_and_wait(flags, rank, world, 0, epoch, spin_limit, status, nullptr, 0)) return;
+
+  constexpr int VEC = BF16 ? 8 : 4;  // elements per 16-byte packet
+  const long long packets = (hi - lo) / VEC;
+  for (long long pk = (long long)blockIdx.x * blockDim.x + threadIdx.x; pk < packets;
+       pk += (long long)gridDim.x * blockDim.x) {
+    const long long i = lo + pk * VEC;
+    float g[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) g[j] = 0.0f;
+    if constexpr (MULTIMEM) {
+      if constexpr (BF16) {
+        uint4 raw;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                     : "l"(reinterpret_cast<const bf16*>(mc_grad) + i)
+                     : "memory");
+        unpack_bf16x8(raw, g);
+      } else {
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=f"(g[0]), "=f"(g[1]), "=f"(g[2]), "=f"(g[3])
+                     : "l"(reinterpret_cast<const float*>(mc_grad) + i)
+                     : "memory");
+      }
+    } else {
+      // fixed summation order (rank 0, 1, ...) on every rank: results do not depend on who owns the shard
+      for (int r = 0; r < world; ++r) {
+        if constexpr (BF16) {
+          float t[8];
+          unpack_bf16x8(ld_cg_v4(reinterpret_cast<const bf16*>(grads.p[r]) + i), t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] += t[j];
+        } else {
+          const uint4 raw = ld_cg_v4(reinterpret_cast<const float*>(grads.p[r]) + i);
+          g[0] += __uint_as_float(raw.x); g[1] += __uint_as_float(raw.y);
+          g[2] += __uint_as_float(raw.z); g[3] += __uint_as_float(raw.w);
+        }
+      }
+    }
+    float w[VEC];
+    if constexpr (BF16) {
+      const float4 w0 = *reinterpret_cast<const float4*>(master + i), w1 = *reinterpret_cast<const float4*>(master + i + 4);
+      w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w; w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
+    } else {
+      const float4 w0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(params.p[rank]) + i);
+      w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w;
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const float gj = g[j] * a.grad_scale;
+      const float mj = a.b1 * m[i + j] + (1.0f - a.b1) * gj;
+      const float vj = a.b2 * v[i + j] + (1.0f - a.b2) * gj * gj;
+      m[i + j] = mj;
+      v[i + j] = vj;
+      w[j] = w[j] * (1.0f - a.lr * a.wd) - a.lr * (mj * a.inv_bc1) / (sqrtf(vj * a.inv_bc2) + a.eps);
+    }
+    uint4 out;
+    if constexpr (BF16) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) master[i + j] = w[j];
+      out = pack_bf16x8(w);
+    } else {
+      out = make_uint4(__float_as_uint(w[0]), __float_as_uint(w[1]), __float_as_uint(w[2]), __float_as_uint(w[3]));
+    }
+    // all-gather: the updated packet goes to every rank's parameter buffer
+    if constexpr (MULTIMEM) {
+      void* dst = BF16 ? static_cast<void*>(reinterpret_cast<bf16*>(mc_param) + i)
+                       : static_cast<void*>(reinterpret_cast<float*>(mc_param) + i);
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst),
+                   "f"(__uint_as_float(out.x)), "f"(__uint_as_float(out.y)), "f"(__uint_as_float(out.z)),
+                   "f"(__uint_as_float(out.w))
+                   : "memory");
+    } else {
+      for (int r = 0; r < world; ++r) {
+        void* dst = BF16 ? static_cast<void*>(reinterpret_cast<bf16*>(params.p[r]) + i)
+                         : static_cast<void*>(reinterpret_cast<float*>(params.p[r]) + i);
+        *reinterpret_cast<uint4*>(dst) = out;
+      }
+    }
+  }
+  // phase 1: every rank has written its shard everywhere (and has finished reading everyone's gradients)
+  if (sync) signal_and_wait(flags, rank, world, 1, epoch, spin_limit, status, arrive, gridDim.x);
+}
+
+// -------------------------------------------------------------------------------------------------
+// Sum of all peers' gradients over [lo, hi) -> momentum buffer update -> bf16 update direction + Σ x².
+// buf = mu*buf + g;  u = nesterov ? g + mu*buf : buf;  out_bf16 = u;  sumsq += Σ u²
+// -------------------------------------------------------------------------------------------------
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+reduce_pull_kernel(PeerPtrs grads, float* momentum_buf, bf16* out, float* sumsq, long long lo, long long hi, float mu,
+                   int nesterov, float grad_scale, int world) {
+  constexpr int VEC = BF16 ? 8 : 4;
+  const long long packets = (hi - lo) / VEC;
+  float local = 0.0f;
+  for (long long pk = (long long)blockIdx.x * blockDim.x + threadIdx.x; pk < packets;
+       pk += (long long)gridDim.x * blockDim.x) {
+    const long long i = lo + pk * VEC;
+    float g[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) g[j] = 0.0f;
+    for (int r = 0; r < world; ++r) {
+      if constexpr (BF16) {
+        float t[8];
+        unpack_bf16x8(ld_cg_v4(reinterpret_cast<const bf16*>(grads.p[r]) + i), t);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] += t[j];
+      } else {
+        const uint4 raw = ld_cg_v4(reinterpret_cast<const float*>(grads.p[r]) + i);
+        g[0] += __uint_as_float(raw.x); g[1] += __uint_as_float(raw.y);
+        g[2] += __uint_as_float(raw.z); g[3] += __uint_as_float(raw.w);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const float gj = g[j] * grad_scale;
+      const float bj = mu * momentum_buf[i - lo + j] + gj;
+      momentum_buf[i - lo + j] = bj;
+      const float u = nesterov ? gj + mu * bj : bj;
+      out[i - lo + j] = __float2bfloat16(u);
+      local += u * u;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+  if ((threadIdx.x & 31) == 0) atomicAdd(sumsq, local);
+}
+
+// Copy [lo_bytes, hi_bytes) of the local buffer into every peer's buffer, then raise flag `slot`/rank.
+__global__ void __launch_bounds__(256)
+push_shard_kernel(PeerPtrs bufs, PeerPtrs flags, long long lo_bytes, long long hi_bytes, int rank, int world, int slot,
+                  unsigned epoch, unsigned* arrive) {
+  const long long packets = (hi_bytes - lo_bytes) / 16;
+  const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(bufs.p[rank]) + lo_bytes);
+  for (long long pk = (long long)blockIdx.x * blockDim.x + threadIdx.x; pk < packets;
+       pk += (long long)gridDim.x * blockDim.x) {
+    const uint4 val = src[pk];
+    for (int r = 0; r < world; ++r)
+      if (r != rank) reinterpret_cast<uint4*>(reinterpret_cast<char*>(bufs.p[r]) + lo_bytes)[pk] = val;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned prev = atomicAdd(arrive, 1u);
+    if (prev + 1 == gridDim.x) {  // last CTA: all of this grid's stores are ordered before the flag
+      __threadfence_system();
+      for (int r = 0; r < world; ++r)
+        st_release_sys(reinterpret_cast<unsigned*>(flags.p[r]) + slot * FBAM_MAX_RANKS + rank, epoch);
+    }
+  }
+}
+
+__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int slot, unsigned epoch, unsigned spin_limit,
+                                    int* status) {
+  signal_and_wait(flags, rank, world, slot, epoch, spin_limit, status, nullptr, 0);
+}
+
+// Wait (bounded) until the local flags of `slot` reach `epoch`; sets status on timeout.
+__global__ void wait_flags_kernel(const unsigned* my_flags, int slot, int world, unsigned epoch, unsigned spin_limit,
+                                  int* status) {
+  if (threadIdx.x == 0) wait_all(my_flags, slot, world, epoch, spin_limit, status);
+}
+
+int num_sms() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return sms;
+}
+
+}  // namespace
+
+#define STREAM(s) reinterpret_cast<cudaStream_t>(s)
+
+extern "C" {
+
+int fbam_comm_max_ranks() { return FBAM_MAX_RANKS; }
+
+// grads/params/flags: arrays of `world` device pointers (peer-mapped).  mc_grad/mc_param: multicast addresses
+// or null (then plain peer loads/stores are used).  arrive: one zeroed unsigned in local memory.
+// sync = 0 skips the cross-rank barriers (single-process emulation of several ranks, one launch per rank).
+int fbam_rs_adamw_ag(void* const* grads, void* const* params, void* const* flags, void* mc_grad, void* mc_param,
+                     float* m, float* v, float* master, long long lo, long long hi, int is_bf16, float lr, float b1,
+                     float b2, float eps, float wd, float bc1, float bc2, float grad_scale, int rank, int world,
+                     unsigned epoch, int sync, unsigned spin_limit, int* status, unsigned* arrive, int max_ctas,
+                     void* stream) {
+  if (world < 1 || world > FBAM_MAX_RANKS || rank < 0 || rank >= world) return 1;
+  const int vec = is_bf16 ? 8 : 4;
+  if (lo % vec != 0 || hi % vec != 0 || hi < lo) return 1;
+  if (is_bf16 && master == nullptr) return 1;
+  PeerPtrs G{}, P{}, F{};
+  for (int r = 0; r < world; ++r) {
+    G.p[r] = grads[r];
+    P.p[r] = params[r];
+    F.p[r] = flags ? flags[r] : nullptr;
+  }
+  if (sync && flags == nullptr) return 1;
+  AdamArgs a{lr, b1, b2, eps, wd, 1.0f / bc1, 1.0f / bc2, grad_scale};
+  const long long packets = (hi - lo) / vec;
+  // Persistent-style grid: all CTAs must be co-resident because they spin on the end-of-kernel barrier.
+  int grid = (int)((packets + 255) / 256);
+  int cap = max_ctas > 0 ? max_ctas : num_sms() * 2;
+  if (grid > cap) grid = cap;
+  if (grid < 1) grid = 1;
+  cudaStream_t s = STREAM(stream);
+  if (cudaMemsetAsync(arrive, 0, sizeof(unsigned), s) != cudaSuccess) return 5;
+  const bool mm = mc_grad != nullptr && mc_param != nullptr;
+#define LAUNCH(BF, MM)                                                                                              \
+  rs_adamw_ag_kernel<BF, MM><<<grid, 256, 0, s>>>(G, P, F, mc_grad, mc_param, m, v, master, lo, hi, a, rank, world, \
+                                                  epoch, sync, spin_limit, status, arrive)
+  if (is_bf16) { if (mm) LAUNCH(true, true); else LAUNCH(true, false); }
+  else { if (mm) LAUNCH(false, true); else LAUNCH(false, false); }
+#undef LAUNCH
+  return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+
+int fbam_reduce_pull(void* const* grads, float* momentum_buf, void* out_bf16, float* sumsq, long long lo, long long hi,
+                     int is_bf16, float mu, int nesterov, float grad_scale, int world, void* stream) {
+  if (world < 1 || world > FBAM_MAX_RANKS) return 1;
+  const int vec = is_bf16 ? 8 : 4;
+  if (lo % vec != 0 || hi % vec != 0 || hi < lo) return 1;
+  PeerPtrs G{};
+  for (int r = 0; r < world; ++r) G.p[r] = grads[r];
+  const long long packets = (hi - lo) / vec;
+  int grid = (int)((packets + 255) / 256);
+  if (grid > num_sms() * 4) grid = num_sms() * 4;
+  if (grid < 1) grid = 1;
+  if (is_bf16)
+    reduce_pull_kernel<true><<<grid, 256, 0, STREAM(stream)>>>(G, momentum_buf, (bf16*)out_bf16, sumsq, lo, hi, mu,
+                                                               nesterov, grad_scale, world);
+  else
+    reduce_pull_kernel<false><<<grid, 256, 0, STREAM(stream)>>>(G, momentum_buf, (bf16*)out_bf16, sumsq, lo, hi, mu,
+                                                                nesterov, grad_scale, world);
+  return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+
+int fbam_push_shard(void* const* bufs, void* const* flags, long long lo_bytes, long long hi_bytes, int rank, int world,
+                    int slot, unsigned epoch, unsigned* arrive, void* stream) {
+  if (world < 1 || world > FBAM_MAX_RANKS || lo_bytes % 16 != 0 || hi_bytes % 16 != 0) return 1;
+  PeerPtrs B{}, F{};
+  for (int r = 0; r < world; ++r) {
+    B.p[r] = bufs[r];
+    F.p[r] = flags[r];
+  }
+  const long long packets = (hi_bytes - lo_bytes) / 16;
+  int grid = (int)((packets + 255) / 256);
+  if (grid > num_sms()) grid = num_sms();
+  if (grid < 1) grid = 1;
+  cudaStream_t s = STREAM(stream);
+  if (cudaMemsetAsync(arrive, 0, sizeof(unsigned), s) != cudaSuccess) return 5;
+  push_shard_kernel<<<grid, 256, 0, s>>>(B, F, lo_bytes, hi_bytes, rank, world, slot, epoch, arrive);
+  return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+
+int fbam_peer_barrier(void* const* flags, int rank, int world, int slot, unsigned epoch, unsigned spin_limit,
+                      int* status, void* stream) {
+  if (world < 1 || world > FBAM_MAX_RANKS) return 1;
+  PeerPtrs F{};
+  for (int r = 0; r < world; ++r) F.p[r] = flags[r];
+  peer_barrier_kernel<<<1, 32, 0, STREAM(stream)>>>(F, rank, world, slot, epoch, spin_limit, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+
+int fbam_wait_flags(const void* my_flags, int slot, int world, unsigned epoch, unsigned spin_limit, int* status,
+                    void* stream) {
+  wait_flags_kernel<<<1, 32, 0, STREAM(stream)>>>((const unsigned*)my_flags, slot, world, epoch, spin_limit, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+
+}  // extern "C"

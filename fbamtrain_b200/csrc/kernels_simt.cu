@@ -326,8 +326,10 @@ __global__ void global_avgpool_fwd_kernel(const bf16* __restrict__ x, bf16* __re
     *reinterpret_cast<Pack8*>(y + n * c + cg * 8) = pack8(o);
   }
 }
-__global__ void global_avgpool_bwd_kernel(const bf16* __restrict__ dy, bf16* __restrict__ dx, long long n, int pix,
-                                          int c) {
+// dx[n, p, :] = dy[n, :] / pix, optionally multiplied by gelu'(z[n, p, :]) (z = pre-activation of the
+// GELU that fed the pool), which folds the activation gradient into the same pass.
+__global__ void global_avgpool_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ z,
+                                          bf16* __restrict__ dx, long long n, int pix, int c) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int c8 = c / 8;
   if (i >= n * pix * c8) return;
@@ -336,8 +338,15 @@ __global__ void global_avgpool_bwd_kernel(const bf16* __restrict__ dy, bf16* __r
   float v[8];
   unpack8(*reinterpret_cast<const Pack8*>(dy + b * c + col), v);
   const float inv = 1.0f / pix;
+  if (z != nullptr) {
+    float zv[8];
+    unpack8(reinterpret_cast<const Pack8*>(z)[i], zv);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) v[j] *= inv;
+    for (int j = 0; j < 8; ++j) v[j] *= inv * gelu_grad_f(zv[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= inv;
+  }
   reinterpret_cast<Pack8*>(dx)[i] = pack8(v);
 }
 
@@ -362,48 +371,71 @@ __global__ void colsum_kernel(const bf16* __restrict__ x, float* __restrict__ ou
 // ------------------------------------------------------------------------------------------------
 // cell embedding
 // ------------------------------------------------------------------------------------------------
-// out[n, p, :] = cp_embed[cp] (0 if out of range) + pos_embed[p] + sum_c chan_c/255 * colour[c]
-// One thread per 8 output channels; the six colour vectors and the position row come from L1/L2.
+// out[f, p, :] = cp_embed[cp] (0 if out of range) + pos_embed[p] + sum_c chan_c/255 * colour[c]
+// A thread owns (position p, 8 channels) and walks a slice of the frames: its position row and the six
+// colour vectors stay in registers, so per cell it loads only the three cell words and one 32-byte slice
+// of the code-point table (L1/L2 resident) and stores 16 bytes.  The threads of a block cover 16
+// neighbouring positions x all channels, i.e. one contiguous 4 KB span of the output per frame.
 __global__ void cell_embed_fwd_kernel(const int* __restrict__ cells, const float* __restrict__ cp_embed,
                                       const float* __restrict__ pos_embed, const float* __restrict__ colour,
-                                      bf16* __restrict__ out, long long total_cells, int positions, int e, int vocab) {
+                                      bf16* __restrict__ out, long long frames, int positions, int e, int vocab,
+                                      int frames_per_block) {
   const int e8 = e / 8;
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total_cells * e8) return;
-  const long long cell = i / e8;
-  const int col = (int)(i % e8) * 8;
-  const int cp = cells[cell * 3 + 0];
-  const uint32_t fg = (uint32_t)cells[cell * 3 + 1], bg = (uint32_t)cells[cell * 3 + 2];
-  const int p = (int)(cell % positions);
-  const float ch[6] = {((fg >> 16) & 255) * (1.0f / 255.0f), ((fg >> 8) & 255) * (1.0f / 255.0f),
-                       (fg & 255) * (1.0f / 255.0f),         ((bg >> 16) & 255) * (1.0f / 255.0f),
-                       ((bg >> 8) & 255) * (1.0f / 255.0f),  (bg & 255) * (1.0f / 255.0f)};
-  float o[8];
-  const float4* pe = reinterpret_cast<const float4*>(pos_embed + (long long)p * e + col);
-  float4 a = pe[0], b = pe[1];
-  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
-  if (cp >= 0 && cp < vocab) {
-    const float4* ce = reinterpret_cast<const float4*>(cp_embed + (long long)cp * e + col);
-    a = ce[0]; b = ce[1];
-    o[0] += a.x; o[1] += a.y; o[2] += a.z; o[3] += a.w; o[4] += b.x; o[5] += b.y; o[6] += b.z; o[7] += b.w;
-  }
+  const int g = threadIdx.x % e8, pl = threadIdx.x / e8;
+  const int p = blockIdx.x * (blockDim.x / e8) + pl;
+  if (p >= positions) return;
+  const int col = g * 8;
+  float pos[8], cv[6][8];
+  {
+    const float4* pe = reinterpret_cast<const float4*>(pos_embed + (long long)p * e + col);
+    const float4 a = pe[0], b = pe[1];
+    pos[0] = a.x; pos[1] = a.y; pos[2] = a.z; pos[3] = a.w; pos[4] = b.x; pos[5] = b.y; pos[6] = b.z; pos[7] = b.w;
 #pragma unroll
-  for (int k = 0; k < 6; ++k) {
-    const float4* cv = reinterpret_cast<const float4*>(colour + k * e + col);
-    a = cv[0]; b = cv[1];
-    o[0] += ch[k] * a.x; o[1] += ch[k] * a.y; o[2] += ch[k] * a.z; o[3] += ch[k] * a.w;
-    o[4] += ch[k] * b.x; o[5] += ch[k] * b.y; o[6] += ch[k] * b.z; o[7] += ch[k] * b.w;
+    for (int k = 0; k < 6; ++k) {
+      const float4* c4 = reinterpret_cast<const float4*>(colour + k * e + col);
+      const float4 x = c4[0], y = c4[1];
+      cv[k][0] = x.x; cv[k][1] = x.y; cv[k][2] = x.z; cv[k][3] = x.w;
+      cv[k][4] = y.x; cv[k][5] = y.y; cv[k][6] = y.z; cv[k][7] = y.w;
+    }
   }
-  *reinterpret_cast<Pack8*>(out + cell * e + col) = pack8(o);
+  const long long f0 = (long long)blockIdx.y * frames_per_block;
+  const long long f1 = min(frames, f0 + frames_per_block);
+#pragma unroll 4
+  for (long long f = f0; f < f1; ++f) {
+    const long long cell = f * positions + p;
+    const int cp = cells[cell * 3 + 0];
+    const uint32_t fg = (uint32_t)cells[cell * 3 + 1], bg = (uint32_t)cells[cell * 3 + 2];
+    const float ch[6] = {((fg >> 16) & 255) * (1.0f / 255.0f), ((fg >> 8) & 255) * (1.0f / 255.0f),
+                         (fg & 255) * (1.0f / 255.0f),         ((bg >> 16) & 255) * (1.0f / 255.0f),
+                         ((bg >> 8) & 255) * (1.0f / 255.0f),  (bg & 255) * (1.0f / 255.0f)};
+    float o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = pos[j];
+    if (cp >= 0 && cp < vocab) {
+      const float4* ce = reinterpret_cast<const float4*>(cp_embed + (long long)cp * e + col);
+      const float4 a = ce[0], b = ce[1];
+      o[0] += a.x; o[1] += a.y; o[2] += a.z; o[3] += a.w; o[4] += b.x; o[5] += b.y; o[6] += b.z; o[7] += b.w;
+    }
+#pragma unroll
+    for (int k = 0; k < 6; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] += ch[k] * cv[k][j];
+    *reinterpret_cast<Pack8*>(out + cell * e + col) = pack8(o);
+  }
 }
 
-// Backward, position and colour tables.  Frames of a batch share positions, so a thread that owns
-// (position p, 8 channels) walks a slice of the frames: the position gradient is a plain running sum
-// (one atomic per slice at the end), and the six colour gradients are reduced over the block in shared
-// memory before one atomic per (colour, channel) per block.
-__global__ void cell_embed_bwd_pos_colour_kernel(const int* __restrict__ cells, const bf16* __restrict__ dout,
-                                                 float* __restrict__ d_pos, float* __restrict__ d_colour,
-                                                 long long frames, int positions, int e, int frames_per_block) {
+// Backward of the cell embedding, all three tables in one pass over dOut.  A thread owns (position p,
+// 8 channels) and walks a slice of the frames:
+//   * position gradient: running sum, one atomic per slice;
+//   * colour gradients: running weighted sums, reduced over the block in shared memory, then one atomic
+//     per (colour, channel) per block;
+//   * code-point gradient: consecutive frames mostly show the same glyph at a position, so the thread
+//     accumulates while the code point stays the same and issues its 8 atomics only when it changes
+//     (run-length flushing); worst case (every frame differs) this degenerates to one flush per cell.
+__global__ void cell_embed_bwd_kernel(const int* __restrict__ cells, const bf16* __restrict__ dout,
+                                      float* __restrict__ d_cp, float* __restrict__ d_pos,
+                                      float* __restrict__ d_colour, long long frames, int positions, int e, int vocab,
+                                      int frames_per_block) {
   extern __shared__ float sm_col[];  // [6][e]
   for (int i = threadIdx.x; i < 6 * e; i += blockDim.x) sm_col[i] = 0.0f;
   __syncthreads();
@@ -413,8 +445,10 @@ __global__ void cell_embed_bwd_pos_colour_kernel(const int* __restrict__ cells, 
   const long long f0 = (long long)blockIdx.y * frames_per_block;
   const long long f1 = min(frames, f0 + frames_per_block);
   const int col = g * 8;
-  if (p < positions && pl < blockDim.x / e8) {
+  if (p < positions) {
     float pos_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    float run_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int run_cp = -1;
     float col_acc[6][8];
 #pragma unroll
     for (int k = 0; k < 6; ++k)
@@ -424,16 +458,35 @@ __global__ void cell_embed_bwd_pos_colour_kernel(const int* __restrict__ cells, 
       const long long cell = f * positions + p;
       float d[8];
       unpack8(*reinterpret_cast<const Pack8*>(dout + cell * e + col), d);
+      const int cp = cells[cell * 3 + 0];
       const uint32_t fg = (uint32_t)cells[cell * 3 + 1], bg = (uint32_t)cells[cell * 3 + 2];
       const float ch[6] = {((fg >> 16) & 255) * (1.0f / 255.0f), ((fg >> 8) & 255) * (1.0f / 255.0f),
                            (fg & 255) * (1.0f / 255.0f),         ((bg >> 16) & 255) * (1.0f / 255.0f),
                            ((bg >> 8) & 255) * (1.0f / 255.0f),  (bg & 255) * (1.0f / 255.0f)};
+      if (cp != run_cp) {
+        if (run_cp >= 0 && run_cp < vocab) {
+          float* dst = d_cp + (long long)run_cp * e + col;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) pos_acc[j] += d[j];
+          for (int j = 0; j < 8; ++j) atomicAdd(dst + j, run_acc[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) run_acc[j] = 0.0f;
+        run_cp = cp;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        pos_acc[j] += d[j];
+        run_acc[j] += d[j];
+      }
 #pragma unroll
       for (int k = 0; k < 6; ++k)
 #pragma unroll
         for (int j = 0; j < 8; ++j) col_acc[k][j] += ch[k] * d[j];
+    }
+    if (run_cp >= 0 && run_cp < vocab) {
+      float* dst = d_cp + (long long)run_cp * e + col;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) atomicAdd(dst + j, run_acc[j]);
     }
     float* dp = d_pos + (long long)p * e + col;
 #pragma unroll
@@ -445,34 +498,6 @@ __global__ void cell_embed_bwd_pos_colour_kernel(const int* __restrict__ cells, 
   }
   __syncthreads();
   for (int i = threadIdx.x; i < 6 * e; i += blockDim.x) atomicAdd(d_colour + i, sm_col[i]);
-}
-
-// Backward, code-point table: d_cp[v, :] = sum over cells with code point v of dout[cell, :].  Each block
-// owns a 32-channel slab and a contiguous run of cells; it accumulates into a private [vocab][32] table in
-// shared memory (one warp per cell, lane = channel, so the shared atomics are bank-conflict free) and
-// flushes the non-zero rows with global atomics once.
-__global__ void cell_embed_bwd_cp_kernel(const int* __restrict__ cells, const bf16* __restrict__ dout,
-                                         float* __restrict__ d_cp, long long total_cells, int e, int vocab,
-                                         int cells_per_block) {
-  extern __shared__ float table[];  // [vocab][32]
-  for (int i = threadIdx.x; i < vocab * 32; i += blockDim.x) table[i] = 0.0f;
-  __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  const int c = blockIdx.y * 32 + lane;
-  const long long c0 = (long long)blockIdx.x * cells_per_block;
-  const long long c1 = min(total_cells, c0 + cells_per_block);
-  if (c < e) {
-    for (long long cell = c0 + warp; cell < c1; cell += warps) {
-      const int cp = cells[cell * 3];
-      if (cp >= 0 && cp < vocab) atomicAdd(&table[cp * 32 + lane], __bfloat162float(dout[cell * e + c]));
-    }
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < vocab * 32; i += blockDim.x) {
-    const float v = table[i];
-    const int ch = blockIdx.y * 32 + (i & 31);
-    if (v != 0.0f && ch < e) atomicAdd(d_cp + (long long)(i >> 5) * e + ch, v);
-  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -612,15 +637,16 @@ int fbam_avgpool2x2(const void* in, void* out, long long n, int oh, int ow, int 
   return CHECK_LAUNCH();
 }
 
-int fbam_global_avgpool(const void* in, void* out, long long n, int pix, int c, int bwd, void* stream) {
+int fbam_global_avgpool(const void* in, void* out, long long n, int pix, int c, int bwd, const void* gelu_z,
+                        void* stream) {
   if (c % 8 != 0) return 1;
   if (!bwd) {
     dim3 grid((unsigned)n, (c / 8 + 31) / 32);
     global_avgpool_fwd_kernel<<<grid, 256, 0, STREAM(stream)>>>((const bf16*)in, (bf16*)out, pix, c);
   } else {
     const long long total = n * pix * (c / 8);
-    global_avgpool_bwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16*)in, (bf16*)out,
-                                                                                           n, pix, c);
+    global_avgpool_bwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, STREAM(stream)>>>(
+        (const bf16*)in, (const bf16*)gelu_z, (bf16*)out, n, pix, c);
   }
   return CHECK_LAUNCH();
 }
@@ -633,41 +659,27 @@ int fbam_colsum(const void* x, float* out, long long rows, int cols, void* strea
   return CHECK_LAUNCH();
 }
 
+static int embed_threads(int e8) { return (256 / e8 > 0 ? 256 / e8 : 1) * e8; }
+
 int fbam_cell_embed_fwd(const int* cells, const float* cp_embed, const float* pos_embed, const float* colour,
-                        void* out, long long total_cells, int positions, int e, int vocab, void* stream) {
-  if (e % 8 != 0) return 1;
-  const long long total = total_cells * (e / 8);
-  cell_embed_fwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, STREAM(stream)>>>(
-      cells, cp_embed, pos_embed, colour, (bf16*)out, total_cells, positions, e, vocab);
+                        void* out, long long frames, int positions, int e, int vocab, void* stream) {
+  if (e % 8 != 0 || e / 8 > 256) return 1;
+  const int e8 = e / 8, threads = embed_threads(e8), ppb = threads / e8;
+  const int fpb = 64;
+  dim3 grid((positions + ppb - 1) / ppb, (unsigned)((frames + fpb - 1) / fpb));
+  cell_embed_fwd_kernel<<<grid, threads, 0, STREAM(stream)>>>(cells, cp_embed, pos_embed, colour, (bf16*)out, frames,
+                                                              positions, e, vocab, fpb);
   return CHECK_LAUNCH();
 }
 
 int fbam_cell_embed_bwd(const int* cells, const void* dout, float* d_cp, float* d_pos, float* d_colour,
                         long long frames, int positions, int e, int vocab, void* stream) {
   if (e % 8 != 0 || e / 8 > 256) return 1;
-  const int e8 = e / 8;
-  const int threads = 256 / e8 * e8 < 32 ? e8 : 256 / e8 * e8;
-  const int pos_per_block = threads / e8;
-  const int fpb = 64;
-  dim3 grid((positions + pos_per_block - 1) / pos_per_block, (unsigned)((frames + fpb - 1) / fpb));
-  cell_embed_bwd_pos_colour_kernel<<<grid, threads, 6 * e * sizeof(float), STREAM(stream)>>>(
-      cells, (const bf16*)dout, d_pos, d_colour, frames, positions, e, fpb);
-  if (cudaGetLastError() != cudaSuccess) return 5;
-  // code-point table: vocab x 32 fp32 slab per block in shared memory
-  const size_t smem = (size_t)vocab * 32 * sizeof(float);
-  if (smem > 200 * 1024) return 1;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(cell_embed_bwd_cp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
-        cudaSuccess)
-      return 5;
-    configured = true;
-  }
-  const long long total_cells = frames * positions;
-  const int cpb = 32768;
-  dim3 grid2((unsigned)((total_cells + cpb - 1) / cpb), (e + 31) / 32);
-  cell_embed_bwd_cp_kernel<<<grid2, 512, smem, STREAM(stream)>>>(cells, (const bf16*)dout, d_cp, total_cells, e, vocab,
-                                                                 cpb);
+  const int e8 = e / 8, threads = embed_threads(e8), ppb = threads / e8;
+  const int fpb = 256;
+  dim3 grid((positions + ppb - 1) / ppb, (unsigned)((frames + fpb - 1) / fpb));
+  cell_embed_bwd_kernel<<<grid, threads, 6 * e * sizeof(float), STREAM(stream)>>>(
+      cells, (const bf16*)dout, d_cp, d_pos, d_colour, frames, positions, e, vocab, fpb);
   return CHECK_LAUNCH();
 }
 

@@ -73,6 +73,9 @@ lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const f
                 unsigned* counter, int* status, int T, int B, int H) {
   __shared__ float part[kWarps][2][16][8];
   __shared__ float pre[32][8];
+  extern __shared__ uint4 dyn_smem[];
+  bf16* hs = reinterpret_cast<bf16*>(dyn_smem);  // [8][H + 8]: h_{t-1}, rows padded by 16 B against bank conflicts
+  const int hs_ld = H + 8;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
   const int unit0 = blockIdx.x * 8;
@@ -102,30 +105,46 @@ lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const f
     c = c0[unit0 + u];
     hbuf[(long long)b * H + unit0 + u] = __float2bfloat16(h0[unit0 + u]);
   }
+  // Each of the 256 threads owns one (gate row, batch) entry of the pre-activations; the value for the next
+  // step is fetched from HBM before the grid barrier so that its latency is hidden behind the wait.
+  const int prow = threadIdx.x >> 3, pbb = threadIdx.x & 7;
+  const int ptile = prow >> 4, pr = prow & 15;
+  const long long pre_off = (long long)(ptile * 2 + (pr >> 3)) * H + unit0 + (pr & 7);
+  float xg_next = 0.0f;
+  if (pbb < B) xg_next = gates[(long long)pbb * 4 * H + pre_off];
   unsigned bar = 0;
   if (!grid_barrier(counter, ++bar * gridDim.x, status)) return;
 
   for (int t = 0; t < T; ++t) {
+    const float xg = xg_next;
     const bf16* hprev = hbuf + (long long)(t & 1) * 8 * H;
     bf16* hnext = hbuf + (long long)((t + 1) & 1) * 8 * H;
-    float acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+    // h_{t-1} (8 x H bf16) -> shared memory with independent 16-byte loads (one L2 round trip in flight
+    // for all of them), then the B fragments come from shared memory.
+    for (int c = threadIdx.x; c < H; c += kThreads) {  // 8*H/8 packets of 8 elements
+      const int row = c / (H / 8), col = (c % (H / 8)) * 8;
+      *reinterpret_cast<uint4*>(hs + row * hs_ld + col) =
+          __ldcg(reinterpret_cast<const uint4*>(hprev + (long long)row * H + col));
+    }
+    __syncthreads();
+    float acc[2][2][4] = {{{0, 0, 0, 0}, {0, 0, 0, 0}}, {{0, 0, 0, 0}, {0, 0, 0, 0}}};
 #pragma unroll
     for (int j = 0; j < MAXKS; ++j) {
       const int ks = warp + kWarps * j;
       if (ks < nks) {
-        const bf16* hp = hprev + (long long)g * H + ks * 16 + q * 2;  // B fragment: n = g (batch), k pairs
-        const uint32_t b0 = __ldcg(reinterpret_cast<const unsigned int*>(hp));
-        const uint32_t b1 = __ldcg(reinterpret_cast<const unsigned int*>(hp + 8));
-        mma_16816(acc[0], afrag[0][j], b0, b1);
-        mma_16816(acc[1], afrag[1][j], b0, b1);
+        const bf16* hp = hs + g * hs_ld + ks * 16 + q * 2;  // B fragment: n = g (batch), k pairs
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(hp);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(hp + 8);
+        mma_16816(acc[0][j & 1], afrag[0][j], b0, b1);
+        mma_16816(acc[1][j & 1], afrag[1][j], b0, b1);
       }
     }
 #pragma unroll
     for (int tile = 0; tile < 2; ++tile) {
-      part[warp][tile][g][q * 2] = acc[tile][0];
-      part[warp][tile][g][q * 2 + 1] = acc[tile][1];
-      part[warp][tile][g + 8][q * 2] = acc[tile][2];
-      part[warp][tile][g + 8][q * 2 + 1] = acc[tile][3];
+      part[warp][tile][g][q * 2] = acc[tile][0][0] + acc[tile][1][0];
+      part[warp][tile][g][q * 2 + 1] = acc[tile][0][1] + acc[tile][1][1];
+      part[warp][tile][g + 8][q * 2] = acc[tile][0][2] + acc[tile][1][2];
+      part[warp][tile][g + 8][q * 2 + 1] = acc[tile][0][3] + acc[tile][1][3];
     }
     __syncthreads();
     {
@@ -134,9 +153,7 @@ lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const f
       float s = 0.0f;
 #pragma unroll
       for (int w = 0; w < kWarps; ++w) s += part[w][tile][r][bb];
-      const int gate = tile * 2 + (r >> 3), uu = r & 7;
-      if (bb < B) s += gates[((long long)t * B + bb) * 4 * H + (long long)gate * H + unit0 + uu];
-      pre[row][bb] = s;
+      pre[row][bb] = s + xg;
     }
     __syncthreads();
     if (threadIdx.x < 64) {
@@ -155,6 +172,9 @@ lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const f
         hnext[(long long)b * H + unit0 + u] = __float2bfloat16(0.0f);
       }
     }
+    // prefetch: the same thread wrote this location's activated gate for step t above only if it is one of
+    // the 64 gate threads; the value read here belongs to step t+1, which nobody has touched yet.
+    if (pbb < B && t + 1 < T) xg_next = gates[((long long)(t + 1) * B + pbb) * 4 * H + pre_off];
     if (!grid_barrier(counter, ++bar * gridDim.x, status)) return;
   }
 }
@@ -169,10 +189,14 @@ lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all
                 float* __restrict__ dc0, const float* __restrict__ dh_last, const float* __restrict__ dc_last,
                 unsigned* counter, int* status, int T, int B, int H) {
   __shared__ float part[kWarps][16][8];
+  extern __shared__ uint4 dyn_smem[];
+  bf16* ds = reinterpret_cast<bf16*>(dyn_smem);  // [8][4H + 8]: dGates[t], padded rows
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
   const int unit0 = blockIdx.x * 16;
   const int K = 4 * H, nks = K / 16;
+  const int ds_ld = K + 8;
+  for (int c = threadIdx.x; c < 8 * ds_ld / 8; c += kThreads) dyn_smem[c] = make_uint4(0, 0, 0, 0);  // rows >= B stay 0
 
   uint32_t afrag[MAXKS][4];
 #pragma unroll
@@ -197,14 +221,21 @@ lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all
     if (dc_last != nullptr) dc_next = dc_last[(long long)b * H + unit];
   }
   unsigned bar = 0;
+  // point-wise inputs of the step about to be processed (fetched one step ahead, before the barrier)
+  float n_ig = 0, n_fg = 0, n_gg = 0, n_og = 0, n_ct = 0, n_cp = 0, n_dy = 0;
+  if (owner) {
+    const int t = T - 1;
+    const float* gt = gates + ((long long)t * B + b) * K + unit;
+    n_ig = gt[0]; n_fg = gt[H]; n_gg = gt[2 * (long long)H]; n_og = gt[3 * (long long)H];
+    n_ct = c_all[((long long)t * B + b) * H + unit];
+    n_cp = t > 0 ? c_all[((long long)(t - 1) * B + b) * H + unit] : c0[unit];
+    n_dy = __bfloat162float(dy[((long long)t * B + b) * H + unit]);
+  }
 
   for (int t = T - 1; t >= 0; --t) {
     if (owner) {
-      const float* gt = gates + ((long long)t * B + b) * K + unit;
-      const float ig = gt[0], fg = gt[H], gg = gt[2 * (long long)H], og = gt[3 * (long long)H];
-      const float ct = c_all[((long long)t * B + b) * H + unit];
-      const float cp = t > 0 ? c_all[((long long)(t - 1) * B + b) * H + unit] : c0[unit];
-      const float dh = __bfloat162float(dy[((long long)t * B + b) * H + unit]) + dh_next;
+      const float ig = n_ig, fg = n_fg, gg = n_gg, og = n_og, ct = n_ct, cp = n_cp;
+      const float dh = n_dy + dh_next;
       const float tc = tanhf(ct);
       const float d_o = dh * tc * og * (1.0f - og);
       const float dc = dh * og * (1.0f - tc * tc) + dc_next;
@@ -217,28 +248,38 @@ lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all
       dg[H] = __float2bfloat16(d_f);
       dg[2 * (long long)H] = __float2bfloat16(d_g);
       dg[3 * (long long)H] = __float2bfloat16(d_o);
+      if (t > 0) {
+        const int tn = t - 1;
+        const float* gt = gates + ((long long)tn * B + b) * K + unit;
+        n_ig = gt[0]; n_fg = gt[H]; n_gg = gt[2 * (long long)H]; n_og = gt[3 * (long long)H];
+        n_ct = cp;
+        n_cp = tn > 0 ? c_all[((long long)(tn - 1) * B + b) * H + unit] : c0[unit];
+        n_dy = __bfloat162float(dy[((long long)tn * B + b) * H + unit]);
+      }
     }
     if (!grid_barrier(counter, ++bar * gridDim.x, status)) return;
     // dh_{t-1}[b, unit] = sum_k dGates[t][b, k] * W_hh[k, unit]
-    float acc[4] = {0, 0, 0, 0};
     const bf16* dgt = dgates + (long long)t * B * K;
+    for (int c = threadIdx.x; c < B * (K / 8); c += kThreads) {
+      const int row = c / (K / 8), col = (c % (K / 8)) * 8;
+      *reinterpret_cast<uint4*>(ds + row * ds_ld + col) =
+          __ldcg(reinterpret_cast<const uint4*>(dgt + (long long)row * K + col));
+    }
+    __syncthreads();
+    float acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
 #pragma unroll
     for (int j = 0; j < MAXKS; ++j) {
       const int ks = warp + kWarps * j;
       if (ks < nks) {
-        uint32_t b0 = 0, b1 = 0;
-        if (g < B) {
-          const bf16* p = dgt + (long long)g * K + ks * 16 + q * 2;
-          b0 = __ldcg(reinterpret_cast<const unsigned int*>(p));
-          b1 = __ldcg(reinterpret_cast<const unsigned int*>(p + 8));
-        }
-        mma_16816(acc, afrag[j], b0, b1);
+        const bf16* p = ds + g * ds_ld + ks * 16 + q * 2;
+        mma_16816(acc[j & 1], afrag[j], *reinterpret_cast<const uint32_t*>(p),
+                  *reinterpret_cast<const uint32_t*>(p + 8));
       }
     }
-    part[warp][g][q * 2] = acc[0];
-    part[warp][g][q * 2 + 1] = acc[1];
-    part[warp][g + 8][q * 2] = acc[2];
-    part[warp][g + 8][q * 2 + 1] = acc[3];
+    part[warp][g][q * 2] = acc[0][0] + acc[1][0];
+    part[warp][g][q * 2 + 1] = acc[0][1] + acc[1][1];
+    part[warp][g + 8][q * 2] = acc[0][2] + acc[1][2];
+    part[warp][g + 8][q * 2 + 1] = acc[0][3] + acc[1][3];
     __syncthreads();
     if (threadIdx.x < 128) {
       float s = 0.0f;
@@ -255,13 +296,17 @@ lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all
 }
 
 template <typename K>
-int coop_launch(K kernel, int grid, void** args, cudaStream_t stream) {
+int coop_launch(K kernel, int grid, void** args, size_t smem, cudaStream_t stream) {
   int dev = 0, sms = 0, per_sm = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess) return 5;
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return 5;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem) != cudaSuccess) return 5;
   if (grid > sms * per_sm) return 1;  // all CTAs must be co-resident
-  return cudaLaunchCooperativeKernel((void*)kernel, dim3(grid), dim3(kThreads), args, 0, stream) == cudaSuccess ? 0 : 5;
+  return cudaLaunchCooperativeKernel((void*)kernel, dim3(grid), dim3(kThreads), args, smem, stream) == cudaSuccess
+             ? 0 : 5;
 }
 
 }  // namespace
@@ -280,9 +325,10 @@ int fbam_lstm_fwd(float* gates, const void* whh, const float* h0, const float* c
   if (cudaMemsetAsync(counter, 0, sizeof(unsigned), s) != cudaSuccess) return 5;
   void* args[] = {&gates, &whh, &h0, &c0, &y, &c_all, &hbuf, &counter, &status, &T, &B, &H};
   const int grid = H / 8;
-  if (H <= 256) return coop_launch(lstm_fwd_kernel<2>, grid, args, s);
-  if (H <= 512) return coop_launch(lstm_fwd_kernel<4>, grid, args, s);
-  return coop_launch(lstm_fwd_kernel<8>, grid, args, s);
+  const size_t smem = (size_t)8 * (H + 8) * sizeof(bf16);
+  if (H <= 256) return coop_launch(lstm_fwd_kernel<2>, grid, args, smem, s);
+  if (H <= 512) return coop_launch(lstm_fwd_kernel<4>, grid, args, smem, s);
+  return coop_launch(lstm_fwd_kernel<8>, grid, args, smem, s);
 }
 
 // whh_t: (H, 4H) bf16 = W_hh transposed.  dgates: (T, B, 4H) bf16 out.  dh0/dc0: (B, H) fp32 out.
@@ -295,9 +341,10 @@ int fbam_lstm_bwd(const float* gates, const float* c_all, const float* c0, const
   void* args[] = {&gates, &c_all, &c0, &dy, &whh_t, &dgates, &dh0, &dc0, &dh_last, &dc_last, &counter, &status,
                   &T, &B, &H};
   const int grid = H / 16;
-  if (H <= 256) return coop_launch(lstm_bwd_kernel<8>, grid, args, s);
-  if (H <= 512) return coop_launch(lstm_bwd_kernel<16>, grid, args, s);
-  return coop_launch(lstm_bwd_kernel<32>, grid, args, s);
+  const size_t smem = (size_t)8 * (4 * H + 8) * sizeof(bf16);
+  if (H <= 256) return coop_launch(lstm_bwd_kernel<8>, grid, args, smem, s);
+  if (H <= 512) return coop_launch(lstm_bwd_kernel<16>, grid, args, smem, s);
+  return coop_launch(lstm_bwd_kernel<32>, grid, args, smem, s);
 }
 
 }  // extern "C"

@@ -82,6 +82,16 @@ def global_avg_pool_nhwc(x):
     return x.float().mean(dim=(1, 2)).to(x.dtype)
 
 
+def conv_gelu_stack_pool(x, weights, stride: int, paddings, dilations):
+    """``[conv3x3 (no bias) → GELU] x n → mean over positions``: ``(N, H, W, C)`` → ``(N, C_last)``."""
+    if _native(x) and all(w.shape[3] % 64 == 0 for w in weights):
+        from .native_ops import conv_gelu_stack_pool as f
+        return f(x, weights, stride, paddings, dilations)
+    for w, pad, dil in zip(weights, paddings, dilations):
+        x = gelu(conv2d_nhwc(x, w, stride, pad, dil))
+    return global_avg_pool_nhwc(x)
+
+
 def linear(x, weight, bias: Optional[torch.Tensor] = None, act: str = "none"):
     if _native(x):
         from .native_ops import linear as f

@@ -176,7 +176,8 @@ def _brick(n: int, h: int, w: int, total: int = 128) -> Tuple[int, int, int]:
 
 
 def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor, *, grid_hw, in_mul, taps,
-              out_mul=1, out_off=(0, 0), accumulate=0, bn: int = 0) -> None:
+              out_mul=1, out_off=(0, 0), accumulate=0, bn: int = 0, act: str = "none",
+              preact_out: Optional[torch.Tensor] = None, gelu_grad_in: Optional[torch.Tensor] = None) -> None:
     """One implicit-GEMM pass (see ``ConvGeom`` in csrc/gemm_tcgen05.h).  ``x`` NHWC bf16, ``wmat``
     ``(n_out, taps·C)`` bf16, ``out`` NHWC with ``n_out`` channels."""
     b, ih, iw, c = x.shape
@@ -196,24 +197,34 @@ def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor
     p.out_fp32 = int(out.dtype == torch.float32)
     p.accumulate = accumulate
     p.bn = bn
+    p.act = nv.GEMM_ACT[act]
+    if preact_out is not None:
+        p.preact_out = preact_out.data_ptr()
+    if gelu_grad_in is not None:
+        p.gelu_grad_in = gelu_grad_in.data_ptr()
     code = nv.lib().fbam_conv_bf16(nv.ptr(x), ih, iw, c, nv.ptr(wmat), C.c_longlong(wmat.stride(0)), n_out,
                                    C.byref(p), nv.stream_ptr())
     nv.check(code, "fbam_conv_bf16")
     debug.after_launch("conv_pass", x, wmat, out)
 
 
-def conv2d_fprop(x, w_ohwi, stride, padding, dilation):
+def conv2d_fprop(x, w_ohwi, stride, padding, dilation, act: str = "none", preact_out=None):
     b, ih, iw, c = x.shape
     o = w_ohwi.shape[0]
     oh = (ih + 2 * padding - 2 * dilation - 1) // stride + 1
     ow = (iw + 2 * padding - 2 * dilation - 1) // stride + 1
     out = debug.fresh((b, oh, ow, o), BF16, x.device)
     taps = [(r * dilation - padding, s * dilation - padding) for r in range(3) for s in range(3)]
-    conv_pass(x, w_ohwi.reshape(o, 9 * c), o, out, grid_hw=(oh, ow), in_mul=stride, taps=taps)
+    conv_pass(x, w_ohwi.reshape(o, 9 * c), o, out, grid_hw=(oh, ow), in_mul=stride, taps=taps, act=act,
+              preact_out=preact_out)
     return out
 
 
-def conv2d_dgrad(dy, w_ohwi, in_hw, stride, padding, dilation):
+def conv_out_hw(ih, iw, stride, padding, dilation):
+    return ((ih + 2 * padding - 2 * dilation - 1) // stride + 1, (iw + 2 * padding - 2 * dilation - 1) // stride + 1)
+
+
+def conv2d_dgrad(dy, w_ohwi, in_hw, stride, padding, dilation, gelu_grad_in=None):
     """dX[n, h, w, :] = Σ_taps dY[n, (h + pad − r·dil)/stride, (w + pad − s·dil)/stride, :] · W[:, r, s, :]
     over the taps for which the division is exact.  Output pixels are split into stride x stride
     parity classes; each class is one stride-1 gather over its own tap subset."""
@@ -239,11 +250,64 @@ def conv2d_dgrad(dy, w_ohwi, in_hw, stride, padding, dilation):
             if not taps:
                 dx[:, ph::stride, pw::stride, :].zero_()
                 continue
+            # (gelu_grad_in multiplies every written element, so zero-tap classes stay zero)
             # filter matrix for this class: (C, taps·O), K ordered tap-major then output channel
             wmat = torch.stack(mats, 0).permute(2, 0, 1).reshape(c, len(taps) * o).contiguous()
-            conv_pass(dy, wmat, c, dx, grid_hw=(gh, gw), in_mul=1, taps=taps, out_mul=stride, out_off=(ph, pw))
+            conv_pass(dy, wmat, c, dx, grid_hw=(gh, gw), in_mul=1, taps=taps, out_mul=stride, out_off=(ph, pw),
+                      gelu_grad_in=gelu_grad_in)
             covered += 1
     return dx
+
+
+class _ConvGeluStackPool(torch.autograd.Function):
+    """``[conv3x3 → GELU] x n → mean over positions`` with a hand-written backward in which every
+    activation gradient rides in the epilogue of the kernel that produces its input gradient: GELU is the
+    epilogue of each forward convolution (the pre-activation is stored alongside), the pool's backward
+    multiplies by gelu'(z_last), and the data-gradient convolution of block i multiplies by gelu'(z_{i-1})."""
+
+    @staticmethod
+    def forward(ctx, x, stride, paddings, dilations, *weights):
+        ys, zs = [x], []
+        for w, pad, dil in zip(weights, paddings, dilations):
+            oh, ow = conv_out_hw(ys[-1].shape[1], ys[-1].shape[2], stride, pad, dil)
+            z = debug.fresh((x.shape[0], oh, ow, w.shape[0]), BF16, x.device)
+            ys.append(conv2d_fprop(ys[-1], w, stride, pad, dil, act="gelu", preact_out=z))
+            zs.append(z)
+        last = ys[-1]
+        n, h, wd, c = last.shape
+        vec = torch.empty(n, c, dtype=BF16, device=x.device)
+        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(last), nv.ptr(vec), C.c_longlong(n), h * wd, c, 0, None,
+                                              nv.stream_ptr()), "fbam_global_avgpool")
+        ctx.save_for_backward(*ys[:-1], *zs, *weights)
+        ctx.cfg = (stride, tuple(paddings), tuple(dilations), len(weights))
+        return vec
+
+    @staticmethod
+    def backward(ctx, dvec):
+        stride, paddings, dilations, nb = ctx.cfg
+        saved = ctx.saved_tensors
+        ys, zs, weights = saved[:nb], saved[nb:2 * nb], saved[2 * nb:]
+        from .conv_wgrad import conv2d_wgrad
+        z_last = zs[-1]
+        n, h, wd, c = z_last.shape
+        dz = torch.empty_like(z_last)
+        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(dvec.contiguous()), nv.ptr(dz), C.c_longlong(n), h * wd, c, 1,
+                                              nv.ptr(z_last), nv.stream_ptr()), "fbam_global_avgpool")
+        dws = [None] * nb
+        for i in range(nb - 1, -1, -1):
+            x_in, w = ys[i], weights[i]
+            if ctx.needs_input_grad[4 + i]:
+                dws[i] = conv2d_wgrad(x_in, dz, w.shape, stride, paddings[i], dilations[i])
+            if i > 0 or ctx.needs_input_grad[0]:
+                dz = conv2d_dgrad(dz, w, (x_in.shape[1], x_in.shape[2]), stride, paddings[i], dilations[i],
+                                  gelu_grad_in=zs[i - 1] if i > 0 else None)
+        dx = dz if ctx.needs_input_grad[0] else None
+        return (dx, None, None, None, *dws)
+
+
+def conv_gelu_stack_pool(x, weights, stride, paddings, dilations):
+    _need_bf16(x, *weights)
+    return _ConvGeluStackPool.apply(x.contiguous(), stride, tuple(paddings), tuple(dilations), *weights)
 
 
 class _Conv2d(torch.autograd.Function):
@@ -396,7 +460,7 @@ class _GlobalAvgPool(torch.autograd.Function):
     def forward(ctx, x):
         n, h, w, c = x.shape
         y = torch.empty(n, c, dtype=BF16, device=x.device)
-        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(x.contiguous()), nv.ptr(y), C.c_longlong(n), h * w, c, 0,
+        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(x.contiguous()), nv.ptr(y), C.c_longlong(n), h * w, c, 0, None,
                                               nv.stream_ptr()), "fbam_global_avgpool")
         ctx.shape = x.shape
         return y
@@ -405,7 +469,7 @@ class _GlobalAvgPool(torch.autograd.Function):
     def backward(ctx, dy):
         n, h, w, c = ctx.shape
         dx = torch.empty(ctx.shape, dtype=BF16, device=dy.device)
-        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(dy.contiguous()), nv.ptr(dx), C.c_longlong(n), h * w, c, 1,
+        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(dy.contiguous()), nv.ptr(dx), C.c_longlong(n), h * w, c, 1, None,
                                               nv.stream_ptr()), "fbam_global_avgpool")
         return dx
 
@@ -426,7 +490,7 @@ class _CellEmbed(torch.autograd.Function):
         cells = cells.contiguous()
         out = debug.fresh((n, p, e), BF16, cells.device)
         nv.check(nv.lib().fbam_cell_embed_fwd(nv.ptr(cells), nv.ptr(cp_embed), nv.ptr(pos_embed), nv.ptr(colour),
-                                              nv.ptr(out), C.c_longlong(n * p), p, e, cp_embed.shape[0],
+                                              nv.ptr(out), C.c_longlong(n), p, e, cp_embed.shape[0],
                                               nv.stream_ptr()), "fbam_cell_embed_fwd")
         ctx.save_for_backward(cells)
         ctx.dims = (n, p, e, cp_embed.shape[0])

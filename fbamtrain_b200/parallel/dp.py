@@ -1,0 +1,229 @@
+"""Data parallelism over flat gradient buckets.
+
+Three ways to turn per-rank gradients into updated parameters, all with identical mathematics
+(sum of gradients, no averaging — the loss is already divided by the global batch; reference:
+``src/main.cpp:2501-2502, 3585-3659``):
+
+``allreduce``  NCCL all-reduce of every bucket, then every rank runs the full optimizer (what the
+               reference does; optimizer state is replicated).
+``zero1``      NCCL reduce-scatter → AdamW on this rank's slice of m / v / master → NCCL all-gather of
+               the parameters.  This is the library baseline of the fused path.
+``fused``      one hand-written kernel per bucket (``csrc/comm.cu``: ``fbam_rs_adamw_ag``) reads this rank's slice
+               of every peer's gradient bucket over NVLink, sums in fp32, applies AdamW to its slice and
+               stores the rounded parameters into every peer's parameter bucket.  Buckets live in
+               peer-memory windows; the action-model buckets are reduced on a side stream as soon as the
+               action model's backward has finished, i.e. while the frame head's backward (the bulk of
+               the step) is still running.
+
+The buckets are the trainer's flat groups (frame-head 16-bit, frame-head fp32 embeddings,
+action-model 16-bit, action-model fp32 LSTM), the grouping the reference uses for its all-reduces
+(reference: ``src/main.cpp:745-807``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..optim import AdamwOptimizer
+from ..utils.flat import FlatGroup
+from ..utils.nvtx import gputx_range
+
+
+class DataParallel:
+    def __init__(self, mode: str = "allreduce", group: Optional[dist.ProcessGroup] = None,
+                 use_multicast: bool = False, overlap: bool = True, spin_limit: int = 1 << 22):
+        if mode not in ("allreduce", "zero1", "fused"):
+            raise ValueError("mode must be allreduce, zero1 or fused")
+        self.mode, self.group = mode, group
+        self.rank = dist.get_rank(group)
+        self.world_size = dist.get_world_size(group)
+        self.use_multicast, self.overlap, self.spin_limit = use_multicast, overlap, spin_limit
+        self.peers = None
+        self._windows: Dict[str, tuple] = {}
+        self._side = None
+        self.stats = {"bytes_reduced": 0}
+
+    # ------------------------------------------------------------------------------------------
+    def attach(self, trainer) -> None:
+        """Called once by the trainer after the flat groups exist: broadcasts rank 0's parameters and,
+        for the fused mode, moves every bucket into a peer-memory window."""
+        for g in trainer.all_groups():
+            dist.broadcast(g.data, src=self._global(0), group=self.group)
+            if g.numel % self.world_size != 0:
+                raise ValueError("flat groups must be padded to a multiple of the world size")
+        for opt in self._adamw_optimizers(trainer):
+            for fs, g in zip(opt.flat_state, opt.groups):
+                if "master" in fs:
+                    fs["master"].copy_(g.data.float())
+        if self.mode == "fused":
+            if trainer.device.type != "cuda":
+                raise ValueError("the fused mode needs CUDA peer memory")
+            self._build_windows(trainer)
+            self._side = torch.cuda.Stream(device=trainer.device)
+
+    def _global(self, rank_in_group: int) -> int:
+        return rank_in_group if self.group is None else dist.get_global_rank(self.group, rank_in_group)
+
+    @staticmethod
+    def _adamw_optimizers(trainer) -> List[AdamwOptimizer]:
+        out = []
+        for opt in trainer.optimizers.values():
+            if isinstance(opt, AdamwOptimizer) and opt.groups is not None:
+                out.append(opt)
+            elif hasattr(opt, "adam") and isinstance(opt.adam, AdamwOptimizer) and opt.adam.groups is not None:
+                out.append(opt.adam)
+        return out
+
+    def _build_windows(self, trainer) -> None:
+        from .peer_window import PeerGroup
+        if self.peers is None:
+            self.peers = PeerGroup(self.group, trainer.device, self.use_multicast)
+        self._windows.clear()
+        for g in trainer.all_groups():
+            wg = self.peers.allocate(g.name + "/grad", g.numel, g.dtype)
+            wp = self.peers.allocate(g.name + "/param", g.numel, g.dtype)
+            wp.local.copy_(g.data)
+            wg.local.zero_()
+            g.data, g.grad = wp.local, wg.local
+            for n, p in g.named_params:                       # re-point parameters at the window
+                o = g.offsets[n]
+                p.data = g.data[o:o + p.numel()].view_as(p)
+            g.rebind_grads()
+            self._windows[g.name] = (wg, wp)
+        torch.cuda.synchronize(trainer.device)
+        dist.barrier(group=self.group)
+
+    def rebuild(self, trainer, group: Optional[dist.ProcessGroup]) -> None:
+        """After a membership change: adopt the new group and re-create the peer windows."""
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world_size = dist.get_world_size(group)
+        if self.mode == "fused":
+            saved = {g.name: g.data.clone() for g in trainer.all_groups()}
+            self.peers.rebuild(group)
+            self._build_windows(trainer)
+            for g in trainer.all_groups():
+                g.data.copy_(saved[g.name])
+
+    # ------------------------------------------------------------------------------------------
+    def reduce_and_step(self, trainer) -> bool:
+        """Reduces gradients over the group and applies the optimizers.  Returns True (step committed)."""
+        if self.mode == "fused":
+            self._fused_step(trainer)
+            return True
+        if self.mode == "zero1":
+            self._zero1_step(trainer)
+            return True
+        with gputx_range("fbamtrain::action_model_grad_allreduce"):
+            for g in trainer.groups["action_model"]:
+                dist.all_reduce(g.grad, group=self.group)
+                self.stats["bytes_reduced"] += g.grad.numel() * g.grad.element_size()
+        with gputx_range("fbamtrain::frame_head_grad_allreduce"):
+            for g in trainer.groups["frame_head"]:
+                dist.all_reduce(g.grad, group=self.group)
+                self.stats["bytes_reduced"] += g.grad.numel() * g.grad.element_size()
+        with gputx_range("fbamtrain::action_model_optim_step"):
+            trainer.optimizers["action_model"].step()
+        with gputx_range("fbamtrain::frame_head_optim_step"):
+            trainer.optimizers["frame_head"].step()
+        return True
+
+    def _zero1_step(self, trainer) -> None:
+        shard = (self.rank, self.world_size)
+        for opt in self._adamw_optimizers(trainer):
+            for g in opt.groups:
+                per = g.numel // self.world_size
+                mine = g.grad[self.rank * per:(self.rank + 1) * per]
+                dist.reduce_scatter_tensor(mine, g.grad, group=self.group)
+            opt.step(shard=shard)
+            for g in opt.groups:
+                per = g.numel // self.world_size
+                dist.all_gather_into_tensor(g.data, g.data[self.rank * per:(self.rank + 1) * per].clone(),
+                                            group=self.group)
+        self._step_non_adamw(trainer)
+
+    def _step_non_adamw(self, trainer) -> None:
+        """Optimizers without a sharded form (SGD, Muon matrices): all-reduce their buckets, step replicated."""
+        handled = {id(g) for opt in self._adamw_optimizers(trainer) for g in opt.groups}
+        for g in trainer.all_groups():
+            if id(g) not in handled:
+                dist.all_reduce(g.grad, group=self.group)
+        for opt in trainer.optimizers.values():
+            if isinstance(opt, AdamwOptimizer):
+                continue
+            if hasattr(opt, "muon"):
+                opt.step_count += 1
+                opt.muon.step()
+                if not (isinstance(opt.adam, AdamwOptimizer) and opt.adam.groups is not None):
+                    opt.adam.step()
+            else:
+                opt.step()
+
+    # -- fused path ----------------------------------------------------------------------------
+    def launch_fused_bucket(self, opt: AdamwOptimizer, g: FlatGroup, fs, bc1: float, bc2: float, device) -> None:
+        from ..ops import native as nv
+        wg, wp = self._windows[g.name]
+        per = g.numel // self.world_size
+        lo, hi = self.rank * per, (self.rank + 1) * per
+        epoch = self.peers.next_epoch()
+        is_bf16 = g.dtype == torch.bfloat16
+        if not is_bf16 and g.dtype != torch.float32:
+            raise TypeError("fused buckets are bf16 or fp32")
+        master = fs.get("master")
+        code = nv.lib().fbam_rs_adamw_ag(
+            wg.c_ptrs, wp.c_ptrs, self.peers.flags.c_ptrs,
+            C.c_void_p(wg.multicast_ptr), C.c_void_p(wp.multicast_ptr),
+            nv.ptr(fs["m"]), nv.ptr(fs["v"]), nv.ptr(master), C.c_longlong(lo), C.c_longlong(hi), int(is_bf16),
+            C.c_float(opt.lr), C.c_float(opt.beta1), C.c_float(opt.beta2), C.c_float(opt.eps),
+            C.c_float(opt.weight_decay), C.c_float(bc1), C.c_float(bc2), C.c_float(1.0), self.rank, self.world_size,
+            C.c_uint(epoch), 1, C.c_uint(self.spin_limit), nv.ptr(nv.status_word(device)), nv.ptr(self.peers.arrive),
+            0, nv.stream_ptr())
+        nv.check(code, "fbam_rs_adamw_ag")
+        self.stats["bytes_reduced"] += g.numel * g.grad.element_size()
+
+    def _fused_scope(self, trainer, scope: str) -> None:
+        opt = trainer.optimizers[scope]
+        adam = opt if isinstance(opt, AdamwOptimizer) else getattr(opt, "adam", None)
+        if not (isinstance(adam, AdamwOptimizer) and adam.groups is not None):
+            return
+        adam.step_count += 1
+        bc1 = 1.0 - adam.beta1 ** adam.step_count
+        bc2 = 1.0 - adam.beta2 ** adam.step_count
+        for g, fs in zip(adam.groups, adam.flat_state):
+            self.launch_fused_bucket(adam, g, fs, bc1, bc2, trainer.device)
+
+    def action_model_grads_ready(self, trainer) -> None:
+        """Hook: the action model's backward is complete while the frame head's is still to run.  Starts
+        the fused reduce-scatter / AdamW / all-gather of the action-model buckets on the side stream."""
+        if self.mode != "fused" or not self.overlap:
+            return
+        self._side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self._side), gputx_range("fbamtrain::action_model_grad_allreduce"):
+            self._fused_scope(trainer, "action_model")
+        self._early = True
+
+    def _fused_step(self, trainer) -> None:
+        cur = torch.cuda.current_stream()
+        if not getattr(self, "_early", False):
+            with gputx_range("fbamtrain::action_model_grad_allreduce"):
+                self._fused_scope(trainer, "action_model")
+        with gputx_range("fbamtrain::frame_head_grad_allreduce"):
+            self._fused_scope(trainer, "frame_head")
+        if getattr(self, "_early", False):
+            cur.wait_stream(self._side)
+            self._early = False
+        self._step_non_adamw(trainer)
+
+    # ------------------------------------------------------------------------------------------
+    def gather_optimizer_state(self, trainer) -> None:
+        """Before a checkpoint: make every rank's m / v / master complete (each rank only maintains its slice)."""
+        if self.mode == "allreduce":
+            return
+        for opt in self._adamw_optimizers(trainer):
+            for g, fs in zip(opt.groups, opt.flat_state):
+                per = g.numel // self.world_size
+                for t in fs.values():
+                    dist.all_gather_into_tensor(t, t[self.rank * per:(self.rank + 1) * per].clone(), group=self.group)

@@ -1,0 +1,115 @@
+"""Peer-memory windows: buffers that every rank of a group can load from and store to directly.
+
+A ``PeerWindow`` owns one symmetric allocation per rank (same size everywhere), the table of all
+ranks' device pointers to it, an optional NVSwitch multicast address, and is created collectively.
+``PeerGroup`` bundles the windows of one communicator with the flag words and the epoch counter the
+fused kernels synchronise on, and ``rebuild()`` re-creates everything after a membership change
+(new group → new allocations → new pointer tables; epochs keep counting so stale flags can never
+satisfy a wait).
+
+The allocation and handle exchange is ``torch.distributed``'s symmetric-memory facility (CUDA VMM /
+fabric handles exchanged through the group's store).  ``LocalPeerGroup`` lays the same interface
+over plain buffers of ONE device, so that a single process can play several ranks in turn — used to
+test the kernels' arithmetic without a second GPU (cross-rank waits are switched off there, because
+kernels that wait on one another must never be separate launches on one device).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+MAX_RANKS = 8
+FLAG_SLOTS = 16
+
+
+def _ptr_array(ptrs: List[int]):
+    arr = (C.c_void_p * MAX_RANKS)()
+    for i, p in enumerate(ptrs):
+        arr[i] = p
+    return arr
+
+
+class PeerWindow:
+    """One symmetric buffer.  ``local`` is this rank's tensor; ``ptrs[r]`` is rank r's buffer as seen from here."""
+
+    def __init__(self, local: torch.Tensor, ptrs: List[int], multicast_ptr: int = 0):
+        self.local = local
+        self.ptrs = ptrs
+        self.multicast_ptr = multicast_ptr
+        self.c_ptrs = _ptr_array(ptrs)
+
+    def offset_ptrs(self, byte_offset: int):
+        return _ptr_array([p + byte_offset for p in self.ptrs])
+
+
+class PeerGroup:
+    def __init__(self, group: Optional[dist.ProcessGroup], device: torch.device, use_multicast: bool = False):
+        self.group = group
+        self.device = device
+        self.rank = dist.get_rank(group)
+        self.world_size = dist.get_world_size(group)
+        if self.world_size > MAX_RANKS:
+            raise ValueError(f"peer windows support at most {MAX_RANKS} ranks per group")
+        self.use_multicast = use_multicast
+        self.epoch = 0
+        self.windows: Dict[str, PeerWindow] = {}
+        self._build_flags()
+
+    def _group_name(self) -> str:
+        pg = self.group if self.group is not None else dist.group.WORLD
+        return pg.group_name
+
+    def allocate(self, name: str, numel: int, dtype: torch.dtype) -> PeerWindow:
+        import torch.distributed._symmetric_memory as symm
+        t = symm.empty(numel, dtype=dtype, device=self.device)
+        t.zero_()
+        handle = symm.rendezvous(t, self._group_name())
+        ptrs = [int(p) for p in handle.buffer_ptrs]
+        mc = int(handle.multicast_ptr) if (self.use_multicast and handle.multicast_ptr) else 0
+        win = PeerWindow(t, ptrs, mc)
+        win.handle = handle
+        self.windows[name] = win
+        return win
+
+    def _build_flags(self) -> None:
+        self.flags = self.allocate("__flags__", FLAG_SLOTS * MAX_RANKS, torch.int32)
+        self.arrive = torch.zeros(4, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    def rebuild(self, group: Optional[dist.ProcessGroup]) -> None:
+        """Drops every window and re-creates the flag words for a new group; callers re-allocate their
+        buffers (and re-point parameter / gradient views) afterwards.  The epoch counter is kept."""
+        self.windows.clear()
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world_size = dist.get_world_size(group)
+        self._build_flags()
+
+
+class LocalPeerGroup:
+    """Several emulated ranks inside one process on one device (see the module docstring)."""
+
+    def __init__(self, world_size: int, device: torch.device):
+        self.world_size, self.device = world_size, device
+        self.epoch = 0
+        self.windows: Dict[str, List[PeerWindow]] = {}
+        self.arrive = torch.zeros(4, dtype=torch.int32, device=device)
+
+    def allocate(self, name: str, numel: int, dtype: torch.dtype) -> List[PeerWindow]:
+        bufs = [torch.zeros(numel, dtype=dtype, device=self.device) for _ in range(self.world_size)]
+        ptrs = [b.data_ptr() for b in bufs]
+        wins = [PeerWindow(b, ptrs, 0) for b in bufs]
+        self.windows[name] = wins
+        return wins
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch

@@ -300,3 +300,23 @@ def test_conv_wgrad(stride, pad, dil, shape):
     got = conv2d_wgrad(x, dy, wt.shape, stride, pad, dil, out_dtype=torch.float32)
     nv.check_status(x.device)
     assert _rel_err(got, expect) < 5e-3
+
+
+def test_conv_gelu_stack_pool_matches_unfused_reference():
+    nv, no = _nops()
+    torch.manual_seed(12)
+    x = torch.randn(6, 24, 40, 64, device=DEV).to(BF).requires_grad_(True)
+    w1 = (torch.randn(128, 3, 3, 64, device=DEV) / 24).to(BF).requires_grad_(True)
+    w2 = (torch.randn(256, 3, 3, 128, device=DEV) / 34).to(BF).requires_grad_(True)
+    v = no.conv_gelu_stack_pool(x, [w1, w2], 2, [1, 1], [1, 1])
+    g = torch.randn_like(v)
+    got = torch.autograd.grad(v, (x, w1, w2), g)
+    fx, f1, f2 = (t.detach().float().requires_grad_(True) for t in (x, w1, w2))
+    y = ref.gelu(ref.conv2d_nhwc(fx, f1, 2, 1, 1))
+    y = ref.gelu(ref.conv2d_nhwc(y, f2, 2, 1, 1))
+    vf = y.mean(dim=(1, 2))
+    exp = torch.autograd.grad(vf, (fx, f1, f2), g.float())
+    assert_similar(vf.to(BF), v, 2e-2)
+    for name, a, e in zip(("dx", "dw1", "dw2"), got, exp):
+        assert _rel_err(a, e) < 2e-2, (name, _rel_err(a, e))
+    nv.check_status(x.device)
