@@ -63,6 +63,23 @@ class DataParallel:
                 raise ValueError("the fused mode needs CUDA peer memory")
             self._build_windows(trainer)
             self._side = torch.cuda.Stream(device=trainer.device)
+            # Early start of the action-model buckets: count gradient accumulations of the action model's
+            # parameters during the last micro-batch; when all have landed, the frame head's backward is
+            # still ahead and the fused kernel can run beside it.
+            self._am_params = [p for _, p in trainer.model.action_model.named_parameters() if p.requires_grad]
+            self._pending = 0
+            self._armed = False
+
+            def _hook(_p, dp=self, tr=trainer):
+                if not dp._armed:
+                    return
+                dp._pending -= 1
+                if dp._pending == 0:
+                    dp._armed = False
+                    dp.action_model_grads_ready(tr)
+
+            for p in self._am_params:
+                p.register_post_accumulate_grad_hook(_hook)
 
     def _global(self, rank_in_group: int) -> int:
         return rank_in_group if self.group is None else dist.get_global_rank(self.group, rank_in_group)
@@ -136,8 +153,9 @@ class DataParallel:
         for opt in self._adamw_optimizers(trainer):
             for g in opt.groups:
                 per = g.numel // self.world_size
-                mine = g.grad[self.rank * per:(self.rank + 1) * per]
-                dist.reduce_scatter_tensor(mine, g.grad, group=self.group)
+                reduced = torch.empty(per, dtype=g.grad.dtype, device=g.grad.device)   # must not alias the input
+                dist.reduce_scatter_tensor(reduced, g.grad, group=self.group)
+                g.grad[self.rank * per:(self.rank + 1) * per].copy_(reduced)
             opt.step(shard=shard)
             for g in opt.groups:
                 per = g.numel // self.world_size
@@ -194,6 +212,12 @@ class DataParallel:
         bc2 = 1.0 - adam.beta2 ** adam.step_count
         for g, fs in zip(adam.groups, adam.flat_state):
             self.launch_fused_bucket(adam, g, fs, bc1, bc2, trainer.device)
+
+    def arm(self) -> None:
+        """Called by the trainer right before the backward pass of the step's last micro-batch."""
+        if self.mode == "fused" and self.overlap:
+            self._pending = len(self._am_params)
+            self._armed = True
 
     def action_model_grads_ready(self, trainer) -> None:
         """Hook: the action model's backward is complete while the frame head's is still to run.  Starts

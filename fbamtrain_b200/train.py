@@ -187,6 +187,8 @@ class Trainer:
         self.ring.begin(step)
         total = None
         for k in range(self.grad_accum_steps):
+            if self.dp is not None and k == self.grad_accum_steps - 1:
+                self.dp.arm()
             loss = self._forward_backward(cells[k * micro:(k + 1) * micro], targets[k * micro:(k + 1) * micro])
             self.ring.accumulate(step, loss)
             total = loss if total is None else total + loss

@@ -1,0 +1,145 @@
+"""Fused communication kernels: arithmetic on one GPU (several emulated ranks, no cross-rank waits) and the
+real peer-memory path on two GPUs when the machine has them."""
+import ctypes as C
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF = torch.bfloat16
+
+
+def _nv():
+    from fbamtrain_b200.ops import native
+    return native
+
+
+@pytest.mark.parametrize("dtype", [BF, torch.float32])
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_rs_adamw_ag_emulated_ranks(dtype, world):
+    from fbamtrain_b200.parallel.peer_window import LocalPeerGroup
+    nv = _nv()
+    torch.manual_seed(0)
+    n = 8 * 1024 * world + 8 * world * 3
+    peers = LocalPeerGroup(world, torch.device(DEV))
+    grads = peers.allocate("g", n, dtype)
+    params = peers.allocate("p", n, dtype)
+    master0 = torch.randn(n, device=DEV)
+    for w in params:
+        w.local.copy_(master0.to(dtype))
+    gsum = torch.zeros(n, device=DEV)
+    for w in grads:
+        g = torch.randn(n, device=DEV).to(dtype)
+        w.local.copy_(g)
+        gsum += g.float()
+    m = [torch.rand(n, device=DEV) * 0.1 for _ in range(world)]
+    v = [torch.rand(n, device=DEV) * 0.01 for _ in range(world)]
+    m[1:] = [m[0].clone() for _ in range(world - 1)]
+    v[1:] = [v[0].clone() for _ in range(world - 1)]
+    masters = [master0.to(dtype).float().clone() if dtype == BF else None for _ in range(world)]
+    em, ev = m[0].clone(), v[0].clone()
+    ew = master0.to(dtype).float().clone()
+    lr, b1, b2, eps, wd, step = 1e-2, 0.9, 0.99, 1e-8, 0.1, 2
+    bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
+    per = n // world
+    status = nv.status_word(torch.device(DEV))
+    for r in range(world):
+        code = nv.lib().fbam_rs_adamw_ag(
+            grads[r].c_ptrs, params[r].c_ptrs, None, None, None, nv.ptr(m[r]), nv.ptr(v[r]), nv.ptr(masters[r]),
+            C.c_longlong(r * per), C.c_longlong((r + 1) * per), int(dtype == BF), C.c_float(lr), C.c_float(b1),
+            C.c_float(b2), C.c_float(eps), C.c_float(wd), C.c_float(bc1), C.c_float(bc2), C.c_float(1.0), r, world,
+            C.c_uint(1), 0, C.c_uint(1000), nv.ptr(status), nv.ptr(peers.arrive), 0, nv.stream_ptr())
+        nv.check(code, "fbam_rs_adamw_ag")
+    nv.check_status(torch.device(DEV))
+    ew.mul_(1 - lr * wd)
+    em.mul_(b1).add_(gsum, alpha=1 - b1)
+    ev.mul_(b2).addcmul_(gsum, gsum, value=1 - b2)
+    ew.addcdiv_(em / bc1, (ev / bc2).sqrt() + eps, value=-lr)
+    expect = ew.to(dtype)
+    for r in range(world):
+        assert torch.allclose(params[r].local.float(), expect.float(), atol=1e-5 if dtype != BF else 8e-3), r
+        assert torch.equal(params[r].local, params[0].local)
+        sl = slice(r * per, (r + 1) * per)
+        assert torch.allclose(m[r][sl], em[sl], atol=1e-6) and torch.allclose(v[r][sl], ev[sl], atol=1e-6)
+
+
+def test_reduce_pull_and_push_shard_emulated():
+    from fbamtrain_b200.parallel.peer_window import LocalPeerGroup, FLAG_SLOTS, MAX_RANKS
+    nv = _nv()
+    torch.manual_seed(1)
+    world, n = 4, 4096
+    peers = LocalPeerGroup(world, torch.device(DEV))
+    grads = peers.allocate("g", n, BF)
+    total = torch.zeros(n, device=DEV)
+    for w in grads:
+        g = torch.randn(n, device=DEV).to(BF)
+        w.local.copy_(g)
+        total += g.float()
+    lo, hi = 512, 2048
+    buf = torch.randn(hi - lo, device=DEV)
+    expect_buf = 0.9 * buf + total[lo:hi]
+    out = torch.empty(hi - lo, device=DEV, dtype=BF)
+    sumsq = torch.zeros(1, device=DEV)
+    nv.check(nv.lib().fbam_reduce_pull(grads[0].c_ptrs, nv.ptr(buf), nv.ptr(out), nv.ptr(sumsq), C.c_longlong(lo),
+                                       C.c_longlong(hi), 1, C.c_float(0.9), 1, C.c_float(1.0), world,
+                                       nv.stream_ptr()), "fbam_reduce_pull")
+    u = total[lo:hi] + 0.9 * expect_buf
+    assert torch.allclose(buf, expect_buf, atol=1e-5)
+    assert torch.allclose(out.float(), u, atol=3e-2, rtol=1e-2)
+    assert abs(float(sumsq) - float((u * u).sum())) / float((u * u).sum()) < 1e-3
+    # push: rank 2's slice lands in every buffer and its flag is raised everywhere
+    bufs = peers.allocate("b", n, BF)
+    flags = peers.allocate("f", FLAG_SLOTS * MAX_RANKS, torch.int32)
+    bufs[2].local.copy_(torch.randn(n, device=DEV).to(BF))
+    nv.check(nv.lib().fbam_push_shard(bufs[2].c_ptrs, flags[2].c_ptrs, C.c_longlong(1024), C.c_longlong(4096), 2,
+                                      world, 3, C.c_uint(7), nv.ptr(peers.arrive), nv.stream_ptr()), "fbam_push_shard")
+    torch.cuda.synchronize()
+    for r in range(world):
+        assert torch.equal(bufs[r].local[512:2048], bufs[2].local[512:2048])
+        assert int(flags[r].local[3 * MAX_RANKS + 2]) == 7
+        if r != 2:
+            assert float(bufs[r].local[:512].abs().max()) == 0.0
+
+
+def test_bounded_wait_reports_timeout_and_context_survives():
+    """A wait on a flag that nobody sets must end in a status code, not a hang."""
+    from fbamtrain_b200.parallel.peer_window import FLAG_SLOTS, MAX_RANKS
+    nv = _nv()
+    dev = torch.device(DEV)
+    flags = torch.zeros(FLAG_SLOTS * MAX_RANKS, dtype=torch.int32, device=DEV)
+    status = nv.status_word(dev)
+    status.zero_()
+    nv.check(nv.lib().fbam_wait_flags(nv.ptr(flags), 0, 2, C.c_uint(5), C.c_uint(2000), nv.ptr(status),
+                                      nv.stream_ptr()), "fbam_wait_flags")
+    torch.cuda.synchronize()
+    code = int(status.item())
+    assert code % 1000 == 301 and code // 1000 == 1      # timed out waiting for rank 0
+    status.zero_()
+    x = torch.ones(8, device=DEV)
+    assert float((x * 2).sum()) == 16.0                  # the context is still usable
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("variant", ["p2p", "multicast"])
+def test_fused_dp_matches_nccl_zero1_on_two_gpus(tmp_path, variant):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = tmp_path / "result.txt"
+    worker = os.path.join(os.path.dirname(__file__), "workers", "dp_fused_worker.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), worker, str(out)]
+    if variant == "multicast":
+        cmd.append("multicast")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert out.read_text() == "ok"

@@ -1,0 +1,152 @@
+"""Data-parallel plumbing, rendezvous and the collective wrapper on CPU ranks (gloo, world size 2)."""
+import os
+import socket
+import threading
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from fbamtrain_b200 import RunConfiguration, Trainer, presets
+from fbamtrain_b200.data import SyntheticBatchSource
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _cfg(total=4, micro=2, opt="adamw"):
+    d = presets.tiny()
+    d["total_batch_size"], d["micro_batch_size"] = total, micro
+    d["optimizer"]["type"] = opt
+    return RunConfiguration.from_json(d)
+
+
+def _batches(cfg, n, batch):
+    src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=5, pin=False)
+    return [src.next_batch(batch, cfg.train_sequence_length) for _ in range(n)]
+
+
+def _dp_worker(rank, world, port, mode, opt, out_dir):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from fbamtrain_b200.parallel.dp import DataParallel
+    cfg = _cfg(opt=opt)
+    tr = Trainer(cfg, device=torch.device("cpu"), dp=DataParallel(mode=mode))
+    assert tr.grad_accum_steps == 1
+    batches = _batches(cfg, 3, 4)
+    losses = []
+    for cells, tg in batches:
+        lo = rank * 2
+        losses.append(float(tr.train_step(cells[lo:lo + 2], tg[lo:lo + 2])))
+    tr.dp.gather_optimizer_state(tr)
+    state = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+    for name, opt_ in tr.optimizers.items():
+        for k, v in opt_.state_tensors().items():
+            state["opt:" + k] = v.detach().clone()
+    torch.save({"params": state, "losses": losses}, os.path.join(out_dir, f"{mode}_{rank}.pt"))
+    tr.close()
+    dist.destroy_process_group()
+
+
+def _run(mode, opt, tmp_path, world=2):
+    port = _free_port()
+    mp.spawn(_dp_worker, args=(world, port, mode, opt, str(tmp_path)), nprocs=world, join=True)
+    return [torch.load(os.path.join(tmp_path, f"{mode}_{r}.pt")) for r in range(world)]
+
+
+def test_dp_allreduce_and_zero1_match_single_process(tmp_path):
+    ar = _run("allreduce", "adamw", tmp_path)
+    z1 = _run("zero1", "adamw", tmp_path)
+    # ranks agree with one another
+    for res in (ar, z1):
+        for k, v in res[0]["params"].items():
+            assert torch.equal(v, res[1]["params"][k]), k
+    # sharded optimizer == replicated optimizer (to rounding: CPU backward kernels are not run-to-run exact)
+    for k, v in ar[0]["params"].items():
+        if "qkv.bias" in k:   # the key bias has a zero gradient in exact arithmetic; Adam amplifies its rounding noise
+            continue
+        assert torch.allclose(v.float(), z1[0]["params"][k].float(), atol=1e-6), k
+    # and both equal one process training on the whole batch with two accumulation steps
+    cfg = _cfg()
+    tr = Trainer(cfg, device=torch.device("cpu"))
+    assert tr.grad_accum_steps == 2
+    for cells, tg in _batches(cfg, 3, 4):
+        tr.train_step(cells, tg)
+    for n, p in tr.model.named_parameters():
+        if "qkv.bias" in n:
+            continue
+        assert torch.allclose(p, ar[0]["params"][n], atol=2e-6), n
+    tr.close()
+    # loss reported per rank is that rank's share of the global mean
+    single = ar[0]["losses"][0] + ar[1]["losses"][0]
+    assert single > 0
+
+
+def test_dp_muon_replicated_matrices_sharded_adam(tmp_path):
+    res = _run("zero1", "muon", tmp_path)
+    for k, v in res[0]["params"].items():
+        assert torch.equal(v, res[1]["params"][k]), k
+
+
+def _rdv_worker(rank, world, port, q):
+    from fbamtrain_b200.parallel import ccl, rendezvous
+    comm = rendezvous.perform_ccl_rendezvous("127.0.0.1", port, rank, world, torch.device("cpu"), timeout_s=30)
+    ccl.barrier(comm)
+    t = torch.full((4,), float(rank + 1))
+    ccl.all_reduce_async(comm, t).wait()
+    out = torch.zeros(world * 2)
+    ccl.all_gather_async(comm, out, torch.full((2,), float(rank))).wait()
+    if rank == 0:
+        ccl.send_string(comm, "héllo from 0", 1)
+        msg = ""
+    else:
+        msg = ccl.recv_string(comm, 0)
+    b = torch.arange(3.0) if rank == 0 else torch.zeros(3)
+    ccl.broadcast_async(comm, b, 0).wait()
+    sub = ccl.create_subset_communicator(comm, [0])
+    q.put((rank, t.tolist(), out.tolist(), msg, b.tolist(), sub is not None))
+    rendezvous.teardown(comm)
+
+
+def test_rendezvous_and_ccl_ops():
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rdv_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert got[0][1] == [3.0] * 4 and got[1][1] == [3.0] * 4
+    assert got[0][2] == [0.0, 0.0, 1.0, 1.0]
+    assert got[1][3] == "héllo from 0"
+    assert got[1][4] == [0.0, 1.0, 2.0]
+    assert got[0][5] is True and got[1][5] is False
+
+
+def test_rendezvous_rejects_bad_ranks():
+    from fbamtrain_b200.parallel import rendezvous as rdv
+    port = _free_port()
+    blob = b"x" * rdv.BLOB_BYTES
+    err = {}
+
+    def serve():
+        try:
+            rdv.serve_blob("127.0.0.1", port, 3, blob, timeout_s=10)
+        except rdv.RendezvousError as ex:
+            err["e"] = str(ex)
+
+    th = threading.Thread(target=serve)
+    th.start()
+    with pytest.raises(rdv.RendezvousError):
+        rdv.fetch_blob("127.0.0.1", port, 7, timeout_s=5)   # out of range: server closes without a blob
+    th.join(20)
+    assert "out of range" in err["e"]
+    with pytest.raises(rdv.RendezvousError):
+        rdv.perform_ccl_rendezvous("127.0.0.1", port, 5, 2, torch.device("cpu"))
