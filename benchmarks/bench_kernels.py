@@ -1,0 +1,162 @@
+#!/usr/bin/env python
+"""Per-kernel benchmarks (device-timed with CUDA events, L2 flushed between iterations).
+
+    python benchmarks/bench_kernels.py gemm  [--m 4096 --n 4096 --k 4096] [--library]
+    python benchmarks/bench_kernels.py conv  [--batch 512 --h 48 --w 160 --cin 128 --cout 256 --stride 2]
+    python benchmarks/bench_kernels.py lstm  [--t 1024 --b 8 --hidden 1024]
+    python benchmarks/bench_kernels.py mha   [--b 8 --heads 8 --t 1024 --d 128] [--causal]
+
+Shapes default to the ones the reference's own benchmark programs use (GEMM 4096³ / 8192³, conv
+(32, 48, 160, 1024→1024), MHA (8, 8, 1024, 128), streaming LSTM; reference: ``benchmarks/`` and
+``benchmarks/common/benchmark_utils.h:59-71``) — ``BENCH_WARMUP`` / ``BENCH_ITERS`` are honoured as there.
+``--library`` times the cuBLAS / cuDNN / SDPA call for the same problem next to the native kernel.
+Each run prints one JSON line with milliseconds, TFLOP/s and the fraction of the measured peaks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+WARMUP = int(os.environ.get("BENCH_WARMUP", "5"))
+ITERS = int(os.environ.get("BENCH_ITERS", "20"))
+
+
+def timeit(fn, iters=ITERS, warmup=WARMUP):
+    for _ in range(max(3, warmup)):
+        fn()
+    torch.cuda.synchronize()
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")   # larger than the 126 MB L2
+    times = []
+    for _ in range(iters):
+        flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def report(name, ms, flops=None, bytes_moved=None, extra=None):
+    from fbamtrain_b200.utils.mfu import measured_peaks
+    peaks = measured_peaks()
+    out = {"bench": name, "ms": ms, "peaks": peaks["source"]}
+    if flops:
+        out["tflops"] = flops / ms / 1e9
+        out["frac_of_cublas_burst"] = out["tflops"] / peaks["bf16_tflops"]
+    if bytes_moved:
+        out["gbs"] = bytes_moved / ms / 1e6
+        out["frac_of_copy_bw"] = out["gbs"] / peaks["hbm_gbs"]
+    if extra:
+        out.update(extra)
+    print(json.dumps(out), flush=True)
+
+
+def bench_gemm(a):
+    from fbamtrain_b200.ops import native_ops as no
+    x = torch.randn(a.m, a.k, device="cuda").bfloat16()
+    w = torch.randn(a.n, a.k, device="cuda").bfloat16()
+    out = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+    flops = 2.0 * a.m * a.n * a.k
+    report(f"gemm_tcgen05 {a.m}x{a.n}x{a.k}", timeit(lambda: no.gemm(x, w, out=out)), flops)
+    if a.library:
+        report(f"gemm_cublas {a.m}x{a.n}x{a.k}", timeit(lambda: torch.matmul(x, w.t(), out=out)), flops)
+
+
+def bench_conv(a):
+    from fbamtrain_b200.ops import native_ops as no
+    from fbamtrain_b200.ops.conv_wgrad import conv2d_wgrad
+    x = torch.randn(a.batch, a.h, a.w, a.cin, device="cuda").bfloat16()
+    w = (torch.randn(a.cout, 3, 3, a.cin, device="cuda") / math.sqrt(9 * a.cin)).bfloat16()
+    pad = a.dilation
+    oh, ow = no.conv_out_hw(a.h, a.w, a.stride, pad, a.dilation)
+    flops = 2.0 * a.batch * oh * ow * a.cout * a.cin * 9
+    tag = f"n{a.batch} {a.h}x{a.w} {a.cin}->{a.cout} s{a.stride} d{a.dilation}"
+    report("conv_fprop " + tag, timeit(lambda: no.conv2d_fprop(x, w, a.stride, pad, a.dilation)), flops)
+    dy = torch.randn(a.batch, oh, ow, a.cout, device="cuda").bfloat16()
+    report("conv_dgrad " + tag, timeit(lambda: no.conv2d_dgrad(dy, w, (a.h, a.w), a.stride, pad, a.dilation)), flops)
+    report("conv_wgrad " + tag, timeit(lambda: conv2d_wgrad(x, dy, w.shape, a.stride, pad, a.dilation)), flops)
+    if a.library:
+        xc = x.permute(0, 3, 1, 2)
+        wc = w.permute(0, 3, 1, 2)
+        report("conv_fprop_cudnn " + tag,
+               timeit(lambda: torch.nn.functional.conv2d(xc, wc, None, a.stride, pad, a.dilation)), flops)
+
+
+def bench_lstm(a):
+    from fbamtrain_b200.ops import lstm as L
+    h = a.hidden
+    k = 1.0 / math.sqrt(h)
+    x = torch.randn(a.t, a.b, h, device="cuda").bfloat16().requires_grad_(True)
+    ps = [((torch.rand(4 * h, h, device="cuda") * 2 - 1) * k).requires_grad_(True) for _ in range(2)]
+    bs = [((torch.rand(4 * h, device="cuda") * 2 - 1) * k).requires_grad_(True) for _ in range(2)]
+    h0 = torch.zeros(h, device="cuda", requires_grad=True)
+    c0 = torch.zeros(h, device="cuda", requires_grad=True)
+    useful = 2.0 * a.t * a.b * 2 * h * 4 * h
+
+    def fwd():
+        return L.lstm_sequence(x, ps[0], ps[1], bs[0], bs[1], h0, c0, torch.bfloat16)
+
+    report(f"lstm_fwd T{a.t} B{a.b} H{h}", timeit(fwd, iters=10), useful,
+           extra={"us_per_step": None})
+    y, _, _ = fwd()
+    g = torch.randn_like(y)
+
+    def fwd_bwd():
+        yy, _, _ = fwd()
+        torch.autograd.grad(yy, [x] + ps + bs, g)
+
+    report(f"lstm_fwd_bwd T{a.t} B{a.b} H{h}", timeit(fwd_bwd, iters=10), 3 * useful)
+
+
+def bench_mha(a):
+    from fbamtrain_b200 import ops
+    q, k, v = (torch.randn(a.b, a.t, a.heads, a.d, device="cuda").bfloat16().requires_grad_(True) for _ in range(3))
+    flops = 4.0 * a.b * a.heads * a.t * a.t * a.d * (0.5 if a.causal else 1.0)
+    report(f"mha_fwd B{a.b} H{a.heads} T{a.t} D{a.d} causal={a.causal}",
+           timeit(lambda: ops.attention(q, k, v, a.causal)), flops)
+    o = ops.attention(q, k, v, a.causal)
+    g = torch.randn_like(o)
+
+    def fb():
+        torch.autograd.grad(ops.attention(q, k, v, a.causal), (q, k, v), g)
+
+    report(f"mha_fwd_bwd B{a.b} H{a.heads} T{a.t} D{a.d} causal={a.causal}", timeit(fb), 3.5 * flops)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=4096)
+    g.add_argument("--n", type=int, default=4096)
+    g.add_argument("--k", type=int, default=4096)
+    g.add_argument("--library", action="store_true")
+    c = sub.add_parser("conv")
+    for name, default in (("batch", 32), ("h", 48), ("w", 160), ("cin", 1024), ("cout", 1024), ("stride", 1),
+                          ("dilation", 2)):
+        c.add_argument("--" + name, type=int, default=default)
+    c.add_argument("--library", action="store_true")
+    l = sub.add_parser("lstm")
+    l.add_argument("--t", type=int, default=1024)
+    l.add_argument("--b", type=int, default=8)
+    l.add_argument("--hidden", type=int, default=1024)
+    m = sub.add_parser("mha")
+    for name, default in (("b", 8), ("heads", 8), ("t", 1024), ("d", 128)):
+        m.add_argument("--" + name, type=int, default=default)
+    m.add_argument("--causal", action="store_true")
+    a = ap.parse_args()
+    {"gemm": bench_gemm, "conv": bench_conv, "lstm": bench_lstm, "mha": bench_mha}[a.cmd](a)
+
+
+if __name__ == "__main__":
+    main()

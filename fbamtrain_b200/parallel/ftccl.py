@@ -1,0 +1,554 @@
+"""Fault-tolerant collective layer with dynamic peer membership.
+
+The reference wraps Prime Intellect's PCCL (reference: ``ftccl/include/ftccl.h:9-229``,
+``ftccl/src/ftccl_pccl.cpp:15-560``): a *master* process tracks membership; peers connect, are admitted at
+topology updates that all accepted peers vote for, keep a revisioned *shared state* (all parameters and
+optimizer tensors) consistent by hash comparison — outdated or newly joined peers receive the popular
+content — and all-reduce with retry, dropping the step when too few peers remain.  This module provides
+the same surface on top of plain TCP (control plane) and ``torch.distributed`` (data plane):
+
+* :class:`MembershipMaster` — the master: peers register, heartbeat, vote for topology updates; it admits
+  pending peers, evicts silent ones, numbers the topology *epoch* and hands out ranks and the address of the
+  epoch's bootstrap store.
+* :class:`FtPeer` — a peer: ``connect``, ``update_topology`` (re-rendezvous: tears the process group of the
+  old epoch down and initialises the new one), ``are_peers_pending``, ``optimize_topology`` (a no-op here:
+  behind NVSwitch every peer is equidistant, so there is no ring order to probe), ``synchronize_shared_state``,
+  ``all_reduce`` / ``all_reduce_multiple_with_retry`` and world-size attributes.
+
+Failures are detected on the host — a missed heartbeat at the master, or an exception from a collective — and
+every device-side wait in the fused kernels is bounded, so a lost peer costs a dropped step, never a hung GPU.
+``FtPeer.on_topology_change`` callbacks let owners of peer-memory windows rebuild them for the new group.
+"""
+from __future__ import annotations
+
+import datetime
+import hashlib
+import json
+import socket
+import threading
+import time
+from dataclasses import dataclass, field
+from enum import Enum
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..utils.logging import LOG
+
+
+class Result(Enum):
+    SUCCESS = 0
+    TOO_FEW_PEERS = 1
+    RANK_CONNECTION_LOST = 2
+    UPDATE_TOPOLOGY_FAILED = 3
+    MASTER_CONNECTION_FAILED = 4
+    INVALID_USAGE = 5
+
+
+class SharedStateSyncStrategy(Enum):
+    ENFORCE_POPULAR = 0
+    RECEIVE_ONLY = 1
+    SEND_ONLY = 2
+
+
+class Attribute(Enum):
+    GLOBAL_WORLD_SIZE = 0
+    PEER_GROUP_WORLD_SIZE = 1
+    NUM_DISTINCT_PEER_GROUPS = 2
+    LARGEST_PEER_GROUP_WORLD_SIZE = 3
+
+
+class QuantizationAlgorithm(Enum):
+    NONE = 0
+    MIN_MAX = 1
+    ZERO_POINT_SCALE = 2
+
+
+@dataclass
+class ReduceInfo:
+    world_size: int = 0
+    tx_bytes: int = 0
+    rx_bytes: int = 0
+
+
+@dataclass
+class SharedStateSyncInfo:
+    tx_bytes: int = 0
+    rx_bytes: int = 0
+    revision: int = 0
+
+
+@dataclass
+class TensorInfo:
+    name: str
+    tensor: torch.Tensor
+    allow_content_inequality: bool = False
+
+
+def _send_json(sock: socket.socket, obj) -> None:
+    sock.sendall((json.dumps(obj) + "\n").encode("utf-8"))
+
+
+class _LineReader:
+    def __init__(self, sock: socket.socket):
+        self.sock, self.buf = sock, b""
+
+    def read(self):
+        while b"\n" not in self.buf:
+            chunk = self.sock.recv(65536)
+            if not chunk:
+                raise ConnectionError("connection closed")
+            self.buf += chunk
+        line, self.buf = self.buf.split(b"\n", 1)
+        return json.loads(line.decode("utf-8"))
+
+
+# =================================================================================================
+# master
+# =================================================================================================
+@dataclass
+class _PeerRecord:
+    uid: int
+    peer_group: int
+    ip: str
+    last_seen: float
+    accepted: bool = False
+    vote: Optional[dict] = None
+    conn: Optional[socket.socket] = None
+
+
+class MembershipMaster:
+    """Runs in a thread (``start()``) or blocks (``run()``).  ``interrupt()`` stops it."""
+
+    def __init__(self, ip: str = "127.0.0.1", port: int = 0, heartbeat_timeout_s: float = 2.0):
+        self.ip, self.heartbeat_timeout_s = ip, heartbeat_timeout_s
+        self._srv = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+        self._srv.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+        self._srv.bind((ip, port))
+        self._srv.listen(64)
+        self.port = self._srv.getsockname()[1]
+        self._lock = threading.Condition()
+        self._peers: Dict[int, _PeerRecord] = {}
+        self._next_uid = 1
+        self.epoch = 0
+        self._stop = False
+        self._threads: List[threading.Thread] = []
+        self._round_result: Optional[dict] = None
+        self._round_id = 0
+
+    # -- lifecycle ----------------------------------------------------------------------------
+    def start(self) -> "MembershipMaster":
+        t = threading.Thread(target=self.run, name="ftccl-master", daemon=True)
+        t.start()
+        self._threads.append(t)
+        return self
+
+    def run(self) -> None:
+        self._srv.settimeout(0.2)
+        while not self._stop:
+            try:
+                conn, addr = self._srv.accept()
+            except socket.timeout:
+                self._reap()
+                continue
+            except OSError:
+                break
+            t = threading.Thread(target=self._serve, args=(conn, addr), daemon=True)
+            t.start()
+        try:
+            self._srv.close()
+        except OSError:
+            pass
+
+    def interrupt(self) -> None:
+        self._stop = True
+        with self._lock:
+            self._lock.notify_all()
+
+    def await_termination(self, timeout: float = 5.0) -> None:
+        for t in self._threads:
+            t.join(timeout)
+
+    # -- membership ---------------------------------------------------------------------------
+    def _alive(self, rec: _PeerRecord) -> bool:
+        return time.monotonic() - rec.last_seen <= self.heartbeat_timeout_s
+
+    def _reap(self) -> None:
+        with self._lock:
+            dead = [uid for uid, r in self._peers.items() if not self._alive(r)]
+            for uid in dead:
+                LOG("WARN", f"ftccl master: peer {uid} missed its heartbeats, evicting")
+                del self._peers[uid]
+            if dead:
+                self._lock.notify_all()
+
+    def snapshot(self) -> dict:
+        with self._lock:
+            return {"epoch": self.epoch,
+                    "accepted": sorted(u for u, r in self._peers.items() if r.accepted),
+                    "pending": sorted(u for u, r in self._peers.items() if not r.accepted)}
+
+    def _try_complete_round(self) -> None:
+        """With the lock held: if every live accepted peer (or, at start-up, every pending peer that voted)
+        has voted, admit the pending voters, renumber and publish the new topology."""
+        live = {u: r for u, r in self._peers.items() if self._alive(r)}
+        accepted = [r for r in live.values() if r.accepted]
+        voters = [r for r in live.values() if r.vote is not None]
+        if not voters:
+            return
+        if accepted and any(r.vote is None for r in accepted):
+            return
+        members = sorted((r for r in live.values() if r.accepted or r.vote is not None), key=lambda r: r.uid)
+        if any(r.vote is None for r in members):
+            return
+        min_world = max(r.vote.get("min_world", 1) for r in members)
+        if len(members) < min_world:
+            return    # keep waiting for more peers to join
+        self.epoch += 1
+        leader = members[0]
+        result = {"epoch": self.epoch, "world": len(members),
+                  "ranks": {str(r.uid): i for i, r in enumerate(members)},
+                  "store": {"ip": leader.ip, "port": leader.vote["free_port"]},
+                  "groups": {str(r.uid): r.peer_group for r in members}}
+        for r in members:
+            r.accepted, r.vote = True, None
+        self._round_id += 1
+        self._round_result = dict(result, round=self._round_id)
+        self._lock.notify_all()
+
+    def _serve(self, conn: socket.socket, addr) -> None:
+        reader = _LineReader(conn)
+        uid = None
+        try:
+            while not self._stop:
+                msg = reader.read()
+                op = msg.get("op")
+                with self._lock:
+                    if uid is not None and uid in self._peers:
+                        self._peers[uid].last_seen = time.monotonic()
+                if op == "connect":
+                    with self._lock:
+                        uid = self._next_uid
+                        self._next_uid += 1
+                        self._peers[uid] = _PeerRecord(uid, int(msg.get("peer_group", 0)), msg.get("ip", addr[0]),
+                                                       time.monotonic(), conn=conn)
+                        self._lock.notify_all()
+                    _send_json(conn, {"ok": True, "uid": uid})
+                elif op == "heartbeat":
+                    with self._lock:
+                        known = uid in self._peers
+                        snap = {"epoch": self.epoch,
+                                "pending": sum(1 for r in self._peers.values() if not r.accepted),
+                                "world": sum(1 for r in self._peers.values() if r.accepted and self._alive(r))}
+                    _send_json(conn, dict(snap, ok=known))
+                elif op == "pending":
+                    with self._lock:
+                        n = sum(1 for r in self._peers.values() if not r.accepted and self._alive(r))
+                    _send_json(conn, {"ok": True, "pending": n})
+                elif op == "vote":
+                    deadline = time.monotonic() + float(msg.get("timeout", 30.0))
+                    with self._lock:
+                        if uid not in self._peers:
+                            _send_json(conn, {"ok": False, "error": "evicted"})
+                            continue
+                        start_round = self._round_id
+                        self._peers[uid].vote = msg
+                        self._try_complete_round()
+                        while self._round_id == start_round and not self._stop:
+                            remaining = deadline - time.monotonic()
+                            if remaining <= 0:
+                                break
+                            self._lock.wait(min(0.2, remaining))
+                            if uid in self._peers:
+                                self._peers[uid].last_seen = time.monotonic()
+                            # evict silent peers so that a dead accepted peer cannot block the round
+                            for u in [u for u, r in self._peers.items() if not self._alive(r) and u != uid]:
+                                del self._peers[u]
+                            if self._round_id == start_round:
+                                self._try_complete_round()
+                        if self._round_id != start_round and str(uid) in self._round_result["ranks"]:
+                            res = dict(self._round_result, ok=True)
+                        else:
+                            if uid in self._peers:
+                                self._peers[uid].vote = None
+                            res = {"ok": False, "error": "timeout"}
+                    _send_json(conn, res)
+                elif op == "leave":
+                    with self._lock:
+                        self._peers.pop(uid, None)
+                        self._lock.notify_all()
+                    _send_json(conn, {"ok": True})
+                    break
+                else:
+                    _send_json(conn, {"ok": False, "error": f"unknown op {op}"})
+        except (ConnectionError, OSError, json.JSONDecodeError):
+            pass
+        finally:
+            try:
+                conn.close()
+            except OSError:
+                pass
+
+
+# =================================================================================================
+# peer
+# =================================================================================================
+def _free_port(ip: str) -> int:
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind((ip, 0))
+        return s.getsockname()[1]
+
+
+def tensor_hash(t: torch.Tensor) -> str:
+    data = t.detach().contiguous().cpu()
+    raw = data.view(torch.uint8).numpy().tobytes() if data.numel() else b""
+    return hashlib.blake2b(raw, digest_size=16).hexdigest()
+
+
+class FtPeer:
+    def __init__(self, master_ip: str, master_port: int, device: torch.device, peer_group: int = 0,
+                 my_ip: str = "127.0.0.1", heartbeat_interval_s: float = 0.25, collective_timeout_s: float = 30.0,
+                 p2p_connection_pool_size: int = 16):
+        self.master_addr = (master_ip, master_port)
+        self.device, self.peer_group, self.my_ip = device, peer_group, my_ip
+        self.heartbeat_interval_s, self.collective_timeout_s = heartbeat_interval_s, collective_timeout_s
+        self.p2p_connection_pool_size = p2p_connection_pool_size
+        self.uid: Optional[int] = None
+        self.epoch = 0
+        self.rank = 0
+        self.world_size = 0
+        self._groups: Dict[str, int] = {}
+        self._sock: Optional[socket.socket] = None
+        self._reader: Optional[_LineReader] = None
+        self._io = threading.Lock()
+        self._hb_stop = threading.Event()
+        self._hb_thread: Optional[threading.Thread] = None
+        self._master_view = {"epoch": 0, "pending": 0, "world": 0, "ok": True}
+        self.on_topology_change: List[Callable[["FtPeer"], None]] = []
+        self.alive = True
+
+    # -- control plane ------------------------------------------------------------------------
+    def _rpc(self, msg: dict, timeout: float = 10.0) -> dict:
+        with self._io:
+            if self._sock is None:
+                raise ConnectionError("not connected to the master")
+            self._sock.settimeout(timeout)
+            _send_json(self._sock, msg)
+            return self._reader.read()
+
+    def connect(self, retries: int = 50) -> Result:
+        last = None
+        for _ in range(retries):
+            try:
+                self._sock = socket.create_connection(self.master_addr, timeout=5.0)
+                self._reader = _LineReader(self._sock)
+                res = self._rpc({"op": "connect", "peer_group": self.peer_group, "ip": self.my_ip})
+                self.uid = int(res["uid"])
+                self._hb_stop.clear()
+                self._hb_thread = threading.Thread(target=self._heartbeat_loop, name="ftccl-heartbeat", daemon=True)
+                self._hb_thread.start()
+                return Result.SUCCESS
+            except OSError as ex:
+                last = ex
+                time.sleep(0.1)
+        LOG("ERR", f"ftccl: cannot reach the master at {self.master_addr}: {last}")
+        return Result.MASTER_CONNECTION_FAILED
+
+    def _heartbeat_loop(self) -> None:
+        while not self._hb_stop.wait(self.heartbeat_interval_s):
+            try:
+                self._master_view = self._rpc({"op": "heartbeat"}, timeout=5.0)
+            except (OSError, ConnectionError, json.JSONDecodeError):
+                self._master_view = dict(self._master_view, ok=False)
+                return
+
+    def are_peers_pending(self) -> bool:
+        try:
+            return int(self._rpc({"op": "pending"})["pending"]) > 0
+        except (OSError, ConnectionError):
+            return False
+
+    def membership_changed(self) -> bool:
+        """Host-side check before launching collectives: True when the master's view differs from the
+        topology this peer is running with (someone was evicted or waits to be admitted)."""
+        v = self._master_view
+        return (not v.get("ok", True)) or v.get("pending", 0) > 0 or (
+            self.world_size > 0 and v.get("world", self.world_size) != self.world_size)
+
+    def update_topology(self, min_world: int = 1, timeout_s: float = 30.0) -> Result:
+        """Votes for a topology update and, once all accepted peers have voted, re-rendezvouses: the old
+        process group is destroyed and the new epoch's group initialised with the ranks the master assigned."""
+        try:
+            res = self._rpc({"op": "vote", "free_port": _free_port(self.my_ip), "min_world": min_world,
+                             "timeout": timeout_s}, timeout=timeout_s + 10.0)
+        except (OSError, ConnectionError) as ex:
+            LOG("ERR", f"ftccl: topology vote failed: {ex}")
+            return Result.UPDATE_TOPOLOGY_FAILED
+        if not res.get("ok"):
+            return Result.UPDATE_TOPOLOGY_FAILED
+        self._teardown_group()
+        self.epoch = int(res["epoch"])
+        self.world_size = int(res["world"])
+        self.rank = int(res["ranks"][str(self.uid)])
+        self._groups = res.get("groups", {})
+        store = res["store"]
+        backend = "nccl" if self.device.type == "cuda" else "gloo"
+        kwargs = {"device_id": self.device} if self.device.type == "cuda" else {}
+        try:
+            dist.init_process_group(backend, init_method=f"tcp://{store['ip']}:{store['port']}", rank=self.rank,
+                                    world_size=self.world_size,
+                                    timeout=datetime.timedelta(seconds=self.collective_timeout_s), **kwargs)
+        except Exception as ex:  # noqa: BLE001
+            LOG("ERR", f"ftccl: process-group initialisation for epoch {self.epoch} failed: {ex}")
+            return Result.UPDATE_TOPOLOGY_FAILED
+        self._master_view = dict(self._master_view, world=self.world_size, pending=0, ok=True)
+        for cb in self.on_topology_change:
+            cb(self)
+        return Result.SUCCESS
+
+    def optimize_topology(self) -> Result:
+        """Ring-order optimisation by bandwidth probing has nothing to do behind an NVSwitch (every pair of
+        GPUs has the same bandwidth); kept for API parity."""
+        return Result.SUCCESS if self.world_size > 0 else Result.INVALID_USAGE
+
+    def get_attribute(self, attr: Attribute) -> int:
+        if attr == Attribute.GLOBAL_WORLD_SIZE:
+            return self.world_size
+        sizes: Dict[int, int] = {}
+        for g in self._groups.values():
+            sizes[g] = sizes.get(g, 0) + 1
+        if attr == Attribute.PEER_GROUP_WORLD_SIZE:
+            return sizes.get(self.peer_group, 0)
+        if attr == Attribute.NUM_DISTINCT_PEER_GROUPS:
+            return len(sizes)
+        return max(sizes.values()) if sizes else 0
+
+    def _teardown_group(self) -> None:
+        if dist.is_initialized():
+            try:
+                dist.destroy_process_group()
+            except Exception:  # noqa: BLE001
+                pass
+
+    # -- data plane ---------------------------------------------------------------------------
+    def all_reduce(self, tensor: torch.Tensor, tag: int = 0,
+                   quantization: QuantizationAlgorithm = QuantizationAlgorithm.NONE) -> Tuple[Result, ReduceInfo]:
+        """Sum all-reduce.  A failed collective (lost peer) returns RANK_CONNECTION_LOST and leaves
+        ``tensor`` unspecified: callers retry after a topology update or drop the step."""
+        if quantization != QuantizationAlgorithm.NONE:
+            LOG("WARN", "ftccl: quantised all-reduce is not implemented on NVLink transports; using full precision")
+        info = ReduceInfo(world_size=self.world_size)
+        if self.world_size <= 1:
+            return (Result.TOO_FEW_PEERS if self.world_size < 1 else Result.SUCCESS), info
+        try:
+            dist.all_reduce(tensor)
+            if tensor.is_cuda:
+                torch.cuda.synchronize(tensor.device)
+        except Exception as ex:  # noqa: BLE001
+            LOG("WARN", f"ftccl: all-reduce (tag {tag}) failed: {ex}")
+            return Result.RANK_CONNECTION_LOST, info
+        nbytes = tensor.numel() * tensor.element_size()
+        info.tx_bytes = info.rx_bytes = 2 * nbytes * (self.world_size - 1) // self.world_size
+        return Result.SUCCESS, info
+
+    def all_reduce_multiple_with_retry(self, tensors: Sequence[torch.Tensor], tags: Sequence[int],
+                                       min_world: int = 2, max_in_flight: int = 8,
+                                       max_retries: int = 3) -> Tuple[Result, ReduceInfo]:
+        """All-reduces every tensor; on a lost connection restores the inputs, re-rendezvouses and retries.
+        Returns TOO_FEW_PEERS when fewer than ``min_world`` peers remain (the caller drops the step)."""
+        backups = [t.clone() for t in tensors]
+        total = ReduceInfo(world_size=self.world_size)
+        for attempt in range(max_retries + 1):
+            if self.world_size < min_world:
+                return Result.TOO_FEW_PEERS, total
+            failed = False
+            for t, tag in zip(tensors, tags):
+                res, info = self.all_reduce(t, tag)
+                if res != Result.SUCCESS:
+                    failed = True
+                    break
+                total.tx_bytes += info.tx_bytes
+                total.rx_bytes += info.rx_bytes
+            if not failed:
+                total.world_size = self.world_size
+                return Result.SUCCESS, total
+            for t, b in zip(tensors, backups):
+                t.copy_(b)
+            if self.update_topology(min_world=1) != Result.SUCCESS:
+                return Result.UPDATE_TOPOLOGY_FAILED, total
+        return Result.RANK_CONNECTION_LOST, total
+
+    def synchronize_shared_state(self, revision: int, infos: Sequence[TensorInfo],
+                                 strategy: SharedStateSyncStrategy = SharedStateSyncStrategy.ENFORCE_POPULAR
+                                 ) -> Tuple[Result, SharedStateSyncInfo]:
+        """Makes every peer hold the same content for the named tensors.  Peers exchange (revision, hash of
+        all tensors); the donor is a peer with the highest revision whose hash is the most common one at that
+        revision (lowest rank on ties); every peer whose hash differs receives the donor's tensors."""
+        out = SharedStateSyncInfo(revision=revision)
+        if self.world_size <= 1:
+            return Result.SUCCESS, out
+        h = hashlib.blake2b(digest_size=16)
+        for ti in infos:
+            if not ti.allow_content_inequality:
+                h.update(ti.name.encode())
+                h.update(tensor_hash(ti.tensor).encode())
+        mine = (int(revision), h.hexdigest(), strategy.value)
+        try:
+            everyone: List[Optional[tuple]] = [None] * self.world_size
+            dist.all_gather_object(everyone, mine)
+            candidates = [(r, rev, hh) for r, (rev, hh, st) in enumerate(everyone)
+                          if st != SharedStateSyncStrategy.RECEIVE_ONLY.value]
+            if not candidates:
+                return Result.INVALID_USAGE, out
+            top = max(rev for _, rev, _ in candidates)
+            counts: Dict[str, int] = {}
+            for _, rev, hh in candidates:
+                if rev == top:
+                    counts[hh] = counts.get(hh, 0) + 1
+            popular = max(counts.items(), key=lambda kv: (kv[1], ))[0]
+            donor = min(r for r, rev, hh in candidates if rev == top and hh == popular)
+            differs = [(rev, hh) != (top, popular) for (rev, hh, _) in everyone]
+            out.revision = top
+            if any(differs):
+                for ti in infos:
+                    buf = ti.tensor if ti.tensor.is_contiguous() else ti.tensor.contiguous()
+                    dist.broadcast(buf, src=donor)
+                    if buf is not ti.tensor:
+                        ti.tensor.copy_(buf)
+                    nbytes = buf.numel() * buf.element_size()
+                    if self.rank == donor:
+                        out.tx_bytes += nbytes * sum(differs)
+                    elif differs[self.rank]:
+                        out.rx_bytes += nbytes
+        except Exception as ex:  # noqa: BLE001
+            LOG("WARN", f"ftccl: shared-state synchronisation failed: {ex}")
+            return Result.RANK_CONNECTION_LOST, out
+        return Result.SUCCESS, out
+
+    # -- leaving / failure injection ----------------------------------------------------------
+    def leave(self) -> None:
+        """Orderly departure between steps."""
+        self._hb_stop.set()
+        try:
+            self._rpc({"op": "leave"}, timeout=2.0)
+        except (OSError, ConnectionError):
+            pass
+        self._close()
+
+    def inject_failure(self) -> None:
+        """Host-side fault injection: the peer falls silent (no heartbeats, sockets closed) without telling
+        anyone, as a crashed process would.  The device context is untouched."""
+        self._hb_stop.set()
+        self._close()
+
+    def _close(self) -> None:
+        self.alive = False
+        self._teardown_group()
+        with self._io:
+            if self._sock is not None:
+                try:
+                    self._sock.close()
+                except OSError:
+                    pass
+                self._sock = None
