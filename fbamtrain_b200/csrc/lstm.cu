@@ -348,3 +348,71 @@ int fbam_lstm_bwd(const float* gates, const float* c_all, const float* c0, const
 }
 
 }  // extern "C"
+
+// -------------------------------------------------------------------------------------------------
+// Allocation-free variant of the forward entry point (see lstm_noalloc.h for who needs it and the contract).
+// The scratch lives in a device array that is part of this module: [0, 256) holds the grid-barrier counter,
+// the rest the double-buffered h vector for the largest supported hidden size.
+// -------------------------------------------------------------------------------------------------
+#include "lstm_noalloc.h"
+
+static __device__ __align__(256) unsigned char g_lstm_noalloc_scratch[FBAM_LSTM_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+// Device address of the scratch array per device ordinal.  In host code the array's name is only a handle for
+// the runtime; the address a kernel can use has to be asked for, once per device, with that device current.
+void* g_noalloc_scratch_addr[kMaxDevices] = {nullptr};
+
+int noalloc_scratch(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FBAM_LSTM_NOALLOC_ERR_SETUP;
+  if (g_noalloc_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_lstm_noalloc_scratch) != cudaSuccess || ptr == nullptr)
+      return FBAM_LSTM_NOALLOC_ERR_SETUP;
+    g_noalloc_scratch_addr[dev] = ptr;
+  }
+  *out = g_noalloc_scratch_addr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" {
+
+int fbam_lstm_fwd_noalloc_max_hidden(void) { return FBAM_LSTM_NOALLOC_MAX_HIDDEN; }
+
+const char* fbam_lstm_fwd_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case 1: return "unsupported shape: need 1 <= B <= 8, H a multiple of 16, T >= 1";
+    case 5: return "kernel launch failed";
+    case FBAM_LSTM_NOALLOC_ERR_TOO_LARGE:
+      return "hidden size exceeds FBAM_LSTM_NOALLOC_MAX_HIDDEN (1024): the built-in scratch array is too small; "
+             "use fbam_lstm_fwd with caller-provided scratch instead";
+    case FBAM_LSTM_NOALLOC_ERR_SETUP: return "could not obtain the device address of the built-in scratch array";
+    default: return "unknown error";
+  }
+}
+
+int fbam_lstm_fwd_noalloc(float* gates, const void* whh, const float* h0, const float* c0, void* y, float* c_all,
+                          int* status, int T, int B, int H, void* stream) {
+  if (H > FBAM_LSTM_NOALLOC_MAX_HIDDEN) return FBAM_LSTM_NOALLOC_ERR_TOO_LARGE;
+  if (B < 1 || B > 8 || H < 16 || H % 16 != 0 || T < 1) return 1;
+  void* base = nullptr;
+  const int rc = noalloc_scratch(&base);
+  if (rc != 0) return rc;
+  unsigned* counter = reinterpret_cast<unsigned*>(base);
+  void* hbuf = static_cast<unsigned char*>(base) + 256;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // the counter must start at zero; the h buffer is written (initial state) before any CTA reads it
+  if (cudaMemsetAsync(counter, 0, sizeof(unsigned), s) != cudaSuccess) return 5;
+  void* args[] = {&gates, &whh, &h0, &c0, &y, &c_all, &hbuf, &counter, &status, &T, &B, &H};
+  const int grid = H / 8;
+  const size_t smem = (size_t)8 * (H + 8) * sizeof(bf16);
+  if (H <= 256) return coop_launch(lstm_fwd_kernel<2>, grid, args, smem, s);
+  if (H <= 512) return coop_launch(lstm_fwd_kernel<4>, grid, args, smem, s);
+  return coop_launch(lstm_fwd_kernel<8>, grid, args, smem, s);
+}
+
+}  // extern "C"
