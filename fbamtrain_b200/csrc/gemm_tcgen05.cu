@@ -31,15 +31,18 @@ namespace {
 
 using namespace tc05;
 
-constexpr int BM = 128;
 constexpr int BK = 64;       // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kNumEpilogueWarps = 8;   // two warps per TMEM lane group, each draining half of the columns
 constexpr int kThreads = 32 * (2 + kNumEpilogueWarps);
 
-template <int BN>
+// BM = 128: two TMEM accumulators of BN columns alternate between tiles (epilogue overlaps the next main loop).
+// BM = 256: the tile is two stacked M = 128 halves that share every B fetch — 64 B of operand traffic per
+//           tensor-core cycle instead of 96 — at the price of using both accumulators for one tile.
+template <int BM, int BN>
 struct SmemLayout {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStageRaw = (BM + BN) * BK * 2;
+  static constexpr int kStages = (200 * 1024 / kStageRaw) > 6 ? 6 : (200 * 1024 / kStageRaw);
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
@@ -67,7 +70,7 @@ __device__ __forceinline__ float gelu_grad_f(float x) {
 }
 
 // Row of the output tile -> element offset of that row in D (or -1 when the row is out of range).
-__device__ __forceinline__ long long row_offset(const GemmParams& p, int tile_m, int row) {
+__device__ __forceinline__ long long row_offset(const GemmParams& p, int tile_m, int row, int BM) {
   if (p.mode != GEMM_MODE_CONV) {
     int m = tile_m * BM + row;
     return m < p.M ? (long long)m * p.ldd : -1;
@@ -102,11 +105,12 @@ __device__ __forceinline__ Work decode_work(const GemmParams& p, int item, int t
   return w;
 }
 
-template <int BN>
+template <int BM, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const GemmParams p) {
-  using L = SmemLayout<BN>;
+  using L = SmemLayout<BM, BN>;
+  constexpr int MH = BM / 128;  // M = 128 halves per tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);
@@ -170,14 +174,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const int bw = (kb % g.tiles_w) * g.tw;
             const int bh = ((kb / g.tiles_w) % g.tiles_h) * g.th;
             const int bn = (kb / (g.tiles_w * g.tiles_h)) * g.tn;
-            const int nb_per_tap = g.c_blocks * 64 / BN;  // N tiles per tap
-            const int tap = tile_n / nb_per_tap, c0 = (tile_n % nb_per_tap) * BN;
-            tma_load_4d(sa, &map_a, &full_bar[stage], tile_m * BM, bw, bh, bn);
-            tma_load_4d(sa + BK * 128, &map_a, &full_bar[stage], tile_m * BM + 64, bw, bh, bn);
+            const int C = g.c_blocks * 64;
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_4d(sb + j * BK * 128, &map_b, &full_bar[stage], c0 + j * 64,
-                          bw * g.in_mul + g.tap_dw[tap], bh * g.in_mul + g.tap_dh[tap], bn);
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_4d(sa + j * BK * 128, &map_a, &full_bar[stage], tile_m * BM + j * 64, bw, bh, bn);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) {
+              // column panel j of the tile: its filter tap and channel offset (past the last tap: channel
+              // coordinate C, i.e. out of range, which TMA fills with zeros)
+              const int col = tile_n * BN + j * 64;
+              int tap = col / C, c0 = col % C;
+              if (tap >= g.num_taps) { tap = 0; c0 = C; }
+              tma_load_4d(sb + j * BK * 128, &map_b, &full_bar[stage], c0, bw * g.in_mul + g.tap_dw[tap],
+                          bh * g.in_mul + g.tap_dh[tap], bn);
+            }
             if (++stage == L::kStages) { stage = 0; phase ^= 1; }
             continue;
           }
@@ -186,8 +196,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const int tap = kb / g.c_blocks, cb = kb % g.c_blocks;
             tma_load_4d(sa, &map_a, &full_bar[stage], cb * BK, cw + g.tap_dw[tap], ch + g.tap_dh[tap], cn);
           } else if (p.a_mn_major) {
-            tma_load_2d(sa, &map_a, &full_bar[stage], tile_m * BM, kb * BK);
-            tma_load_2d(sa + BK * 128, &map_a, &full_bar[stage], tile_m * BM + 64, kb * BK);
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * BK * 128, &map_a, &full_bar[stage], tile_m * BM + j * 64, kb * BK);
           } else {
             tma_load_2d(sa, &map_a, &full_bar[stage], kb * BK, tile_m * BM);
           }
@@ -206,7 +217,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn_major != 0, p.b_mn_major != 0);
+      const uint32_t idesc = make_idesc_bf16(128, BN, p.a_mn_major != 0, p.b_mn_major != 0);
       // K-major: 8-row groups are 1024 B apart (SBO); one UMMA_K step = 32 B inside the swizzle row.
       // MN-major: 64-wide column panels are BK*128 B apart (LBO), 8-row K groups 1024 B apart (SBO);
       //           one UMMA_K step = 16 rows = 2048 B.
@@ -222,7 +233,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const Work wk = decode_work(p, tile, tiles_n);
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { ok = false; break; }
         fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + (MH == 1 ? acc * BN : 0);
         for (int kb = wk.k_begin; kb < wk.k_end; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
           fence_after_sync();
@@ -230,24 +241,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           const uint32_t sb = sa + L::kABytes;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
             const uint64_t db = make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
-            mma_f16_ss(d_tmem, da, db, idesc, ((kb - wk.k_begin) | k) != 0);
+#pragma unroll
+            for (int h = 0; h < MH; ++h) {   // M half h: rows [128h, 128h+128) = 16 KB further in either layout
+              const uint64_t da = make_smem_desc_sw128(sa + h * 128 * 128 + k * a_kstep, a_lbo, 1024);
+              mma_f16_ss(d_tmem + h * BN, da, db, idesc, ((kb - wk.k_begin) | k) != 0);
+            }
           }
           mma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
           if (++stage == L::kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         mma_commit(&tmem_full[acc]);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        if (MH == 2) { acc_phase ^= 1; }
+        else if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
       if (!ok) atomicExch(p.status, GEMM_ERR_MMA_TIMEOUT);
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int lane_group = warp % 4;  // TMEM lanes [32*lane_group, +32) are visible to this warp
-    const int col_half = (warp - 2) / 4;
-    const int row = lane_group * 32 + lane;
+    const int second = (warp - 2) / 4;  // BM=128: second half of the columns; BM=256: second M half
+    const int row = (MH == 2 ? second * 128 : 0) + lane_group * 32 + lane;
+    const int c_begin = MH == 2 ? 0 : second * (BN / 2), c_end = MH == 2 ? BN : (second + 1) * (BN / 2);
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -256,10 +272,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const int tile_m = wk.tile_m, tile_n = wk.tile_n;
       if (!mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
       fence_after_sync();
-      const long long roff = row_offset(p, tile_m, row);
-      const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * BN;
+      const long long roff = row_offset(p, tile_m, row, BM);
+      const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + (MH == 2 ? second * BN : acc * BN);
 #pragma unroll 1
-      for (int c0 = col_half * (BN / 2); c0 < (col_half + 1) * (BN / 2); c0 += 32) {
+      for (int c0 = c_begin; c0 < c_end; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c0, r);
         tmem_ld_wait();
@@ -385,7 +401,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (MH == 2) { acc_phase ^= 1; }
+      else if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (!ok && lane == 0) atomicExch(p.status, GEMM_ERR_EPILOGUE_TIMEOUT);
   }
@@ -450,12 +467,13 @@ int encode_nhwc(CUtensorMap* map, const void* base, int n, int h, int w, int c, 
 
 int g_num_sms = 0;
 
-template <int BN>
+template <int BM, int BN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
-  using L = SmemLayout<BN>;
+  using L = SmemLayout<BM, BN>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_kernel<BM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
+        cudaSuccess)
       return GEMM_ERR_LAUNCH;
     configured = true;
   }
@@ -467,8 +485,26 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStre
   const int tiles = p.tiles_m * ((p.N + BN - 1) / BN) * p.splits;
   int grid = tiles < g_num_sms ? tiles : g_num_sms;
   if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
-  gemm_kernel<BN><<<grid, kThreads, L::kTotal, stream>>>(ma, mb, p);
+  gemm_kernel<BM, BN><<<grid, kThreads, L::kTotal, stream>>>(ma, mb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : GEMM_ERR_LAUNCH;
+}
+
+int dispatch(int bm, int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t s) {
+  if (bm == 256) {
+    if (bn == 128) return launch<256, 128>(ma, mb, p, s);
+    return launch<256, 256>(ma, mb, p, s);
+  }
+  if (bn == 64) return launch<128, 64>(ma, mb, p, s);
+  if (bn == 128) return launch<128, 128>(ma, mb, p, s);
+  return launch<128, 256>(ma, mb, p, s);
+}
+
+// Tall tiles pay off once there are enough of them to fill the machine about twice over.
+int pick_bm(long long m, int n, int bn, int requested) {
+  if (requested == 128 || requested == 256) return (requested == 256 && bn < 128) ? 128 : requested;
+  if (bn < 128) return 128;
+  const long long tiles256 = ((m + 255) / 256) * ((n + bn - 1) / bn);
+  return tiles256 >= 2 * 148 ? 256 : 128;
 }
 
 int pick_bn(int n, int requested) {
@@ -487,12 +523,13 @@ extern "C" int fbam_gemm_bf16(const void* A, long long lda, int a_mn_major, cons
   p.mode = GEMM_MODE_PLAIN;
   p.M = M; p.N = N; p.K = K;
   p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
-  p.tiles_m = (M + BM - 1) / BM;
   p.k_blocks = (K + BK - 1) / BK;
   if (p.splits < 1) p.splits = 1;
   if (p.splits > p.k_blocks) p.splits = p.k_blocks;
   if (p.splits > 1 && !(p.out_fp32 && p.accumulate == GEMM_ACC_ATOMIC)) return GEMM_ERR_SHAPE;
   const int bn = pick_bn(N, p.bn);
+  const int BM = pick_bm(M, N, bn, p.bm);
+  p.tiles_m = (M + BM - 1) / BM;
   const int elt = p.out_fp32 ? 4 : 2;
   p.vec_ok = (p.ldd % (16 / elt) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&
              (p.preact_out == nullptr || (reinterpret_cast<uintptr_t>(p.preact_out) & 15) == 0) &&
@@ -501,15 +538,12 @@ extern "C" int fbam_gemm_bf16(const void* A, long long lda, int a_mn_major, cons
   CUtensorMap ma, mb;
   int e;
   if (a_mn_major) e = encode_2d(&ma, A, K, M, lda, 64);  // rows = K, cols = M, panels of 64 columns
-  else e = encode_2d(&ma, A, M, K, lda, BM);
+  else e = encode_2d(&ma, A, M, K, lda, BM);  // one box of BM rows
   if (e) return e;
   if (b_mn_major) e = encode_2d(&mb, B, K, N, ldb, 64);
   else e = encode_2d(&mb, B, N, K, ldb, bn);
   if (e) return e;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (bn == 64) return launch<64>(ma, mb, p, s);
-  if (bn == 128) return launch<128>(ma, mb, p, s);
-  return launch<256>(ma, mb, p, s);
+  return dispatch(BM, bn, ma, mb, p, reinterpret_cast<cudaStream_t>(stream));
 }
 
 // Implicit-GEMM convolution pass.  `X` is the gathered NHWC tensor [batch, in_h, in_w, C]; `Wmat` is the
@@ -518,7 +552,8 @@ extern "C" int fbam_conv_bf16(const void* X, int in_h, int in_w, int C, const vo
                               GemmParams* params, void* stream) {
   GemmParams p = *params;
   ConvGeom& g = p.conv;
-  if (C % 64 != 0 || g.tn * g.th * g.tw != BM || g.num_taps < 1 || g.num_taps > 9) return GEMM_ERR_SHAPE;
+  const int BM = g.tn * g.th * g.tw;
+  if (C % 64 != 0 || (BM != 128 && BM != 256) || g.num_taps < 1 || g.num_taps > 9) return GEMM_ERR_SHAPE;
   p.mode = GEMM_MODE_CONV;
   p.a_mn_major = 0; p.b_mn_major = 0;
   g.c_blocks = C / 64;
@@ -531,6 +566,7 @@ extern "C" int fbam_conv_bf16(const void* X, int in_h, int in_w, int C, const vo
   p.k_blocks = g.num_taps * g.c_blocks;
   p.splits = 1;
   const int bn = pick_bn(N, p.bn);
+  if (BM == 256 && bn < 128) return GEMM_ERR_SHAPE;
   const int elt = p.out_fp32 ? 4 : 2;
   p.vec_ok = (p.ldd % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) && (p.ldd % (16 / elt) == 0);
   CUtensorMap ma, mb;
@@ -538,10 +574,7 @@ extern "C" int fbam_conv_bf16(const void* X, int in_h, int in_w, int C, const vo
   if (e) return e;
   e = encode_2d(&mb, Wmat, N, p.K, ldw, bn);
   if (e) return e;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (bn == 64) return launch<64>(ma, mb, p, s);
-  if (bn == 128) return launch<128>(ma, mb, p, s);
-  return launch<256>(ma, mb, p, s);
+  return dispatch(BM, bn, ma, mb, p, reinterpret_cast<cudaStream_t>(stream));
 }
 
 // Convolution weight gradient as a split-K GEMM over output pixels:
@@ -562,17 +595,20 @@ extern "C" int fbam_conv_wgrad_bf16(const void* dY, int O, const void* X, int in
   g.tiles_h = (g.grid_h + g.th - 1) / g.th;
   const int bricks = g.tiles_w * g.tiles_h * ((g.batch + g.tn - 1) / g.tn);
   p.M = O; p.N = g.num_taps * C; p.K = bricks * BK;
+  // N tiles may span two filter taps (each 64-column panel is gathered with its own tap), so 256-wide tiles
+  // work for every C that is a multiple of 64.
+  int bn = p.N >= 256 ? 256 : (p.N >= 128 ? 128 : 64);
+  if (p.bn == 64 || p.bn == 128 || p.bn == 256) bn = p.bn;
+  const int BM = (O >= 256 && bn >= 128 && p.bm != 128) ? 256 : 128;
   p.tiles_m = (O + BM - 1) / BM;
   p.k_blocks = bricks;
-  int bn = (C % 256 == 0) ? 256 : (C % 128 == 0 ? 128 : 64);
-  if (p.bn == 64 || (p.bn == 128 && C % 128 == 0)) bn = p.bn;
   if (p.splits < 1) {
     if (g_num_sms == 0) {
       int dev = 0;
       cudaGetDevice(&dev);
       cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
     }
-    const int tiles = p.tiles_m * (p.N / bn);
+    const int tiles = p.tiles_m * ((p.N + bn - 1) / bn);
     p.splits = (g_num_sms + tiles - 1) / tiles;
   }
   if (p.splits > bricks) p.splits = bricks;
@@ -582,8 +618,5 @@ extern "C" int fbam_conv_wgrad_bf16(const void* dY, int O, const void* X, int in
   if (e) return e;
   e = encode_nhwc(&mb, X, g.batch, in_h, in_w, C, g.tn, g.th, g.tw, g.in_mul);
   if (e) return e;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (bn == 64) return launch<64>(ma, mb, p, s);
-  if (bn == 128) return launch<128>(ma, mb, p, s);
-  return launch<256>(ma, mb, p, s);
+  return dispatch(BM, bn, ma, mb, p, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -39,6 +39,7 @@ struct GemmParams {
   float alpha;
   int out_fp32, bias_fp32, act, accumulate;
   int bn;                           // 0 = choose from N; else 64 / 128 / 256
+  int bm;                           // 0 = choose from the tile count; else 128 / 256 (plain GEMM and wgrad)
   int max_ctas;                     // 0 = one per SM
   int splits;                       // split-K factor (needs fp32 output with atomic accumulation); 0/1 = none
   // filled by the launcher

@@ -15,7 +15,8 @@ import torch
 from . import native as nv
 
 
-def conv2d_wgrad(x, dy, w_shape, stride, padding, dilation, out_dtype=torch.bfloat16, splits: int = 0, bn: int = 0):
+def conv2d_wgrad(x, dy, w_shape, stride, padding, dilation, out_dtype=torch.bfloat16, splits: int = 0, bn: int = 0,
+                 bm: int = 0):
     from .native_ops import _brick
     o, _, _, c = w_shape
     b, ih, iw, _ = x.shape
@@ -37,7 +38,7 @@ def conv2d_wgrad(x, dy, w_shape, stride, padding, dilation, out_dtype=torch.bflo
     p.status = nv.status_word(x.device).data_ptr()
     p.alpha = 1.0
     p.out_fp32 = 1
-    p.splits, p.bn = splits, bn
+    p.splits, p.bn, p.bm = splits, bn, bm
     code = nv.lib().fbam_conv_wgrad_bf16(nv.ptr(dy), o, nv.ptr(x), ih, iw, c, C.byref(p), nv.stream_ptr())
     nv.check(code, "fbam_conv_wgrad_bf16")
     return dw.view(o, 3, 3, c).to(out_dtype)

@@ -35,7 +35,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = BF16, bias: Optional[torch.Tensor] = None,
          act: str = "none", residual: Optional[torch.Tensor] = None, preact_out: Optional[torch.Tensor] = None,
          gelu_grad_in: Optional[torch.Tensor] = None, accumulate: int = 0, alpha: float = 1.0,
-         bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
+         bn: int = 0, bm: int = 0, max_ctas: int = 0) -> torch.Tensor:
     """``D[M, N] = epilogue(A · Bᵀ)``.
 
     ``a``: ``(M, K)`` (or ``(K, M)`` when ``a_mn``); ``b``: ``(N, K)`` (or ``(K, N)`` when ``b_mn``).
@@ -72,7 +72,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     p.out_fp32 = int(out.dtype == torch.float32)
     p.act = nv.GEMM_ACT[act]
     p.accumulate = accumulate
-    p.bn, p.max_ctas = bn, max_ctas
+    p.bn, p.bm, p.max_ctas = bn, bm, max_ctas
     code = nv.lib().fbam_gemm_bf16(nv.ptr(a), C.c_longlong(a.stride(0)), int(a_mn), nv.ptr(b),
                                    C.c_longlong(b.stride(0)), int(b_mn), m, n, k, C.byref(p), nv.stream_ptr())
     nv.check(code, "fbam_gemm_bf16")
@@ -177,14 +177,22 @@ def _brick(n: int, h: int, w: int, total: int = 128) -> Tuple[int, int, int]:
 
 def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor, *, grid_hw, in_mul, taps,
               out_mul=1, out_off=(0, 0), accumulate=0, bn: int = 0, act: str = "none",
-              preact_out: Optional[torch.Tensor] = None, gelu_grad_in: Optional[torch.Tensor] = None) -> None:
+              preact_out: Optional[torch.Tensor] = None, gelu_grad_in: Optional[torch.Tensor] = None,
+              tile_rows: int = 0) -> None:
     """One implicit-GEMM pass (see ``ConvGeom`` in csrc/gemm_tcgen05.h).  ``x`` NHWC bf16, ``wmat``
     ``(n_out, taps·C)`` bf16, ``out`` NHWC with ``n_out`` channels."""
     b, ih, iw, c = x.shape
     p = nv.GemmParams()
     g = p.conv
     g.batch, g.grid_h, g.grid_w = b, grid_hw[0], grid_hw[1]
-    g.tn, g.th, g.tw = _brick(b, grid_hw[0], grid_hw[1])
+    # 256-pixel bricks (two stacked M halves sharing each filter fetch) once there are enough tiles to fill
+    # the machine twice; 128-pixel bricks otherwise
+    tn, th, tw = _brick(b, grid_hw[0], grid_hw[1], 256)
+    tiles256 = math.ceil(b / tn) * math.ceil(grid_hw[0] / th) * math.ceil(grid_hw[1] / tw)
+    if tile_rows == 128 or n_out < 128 or (tile_rows == 0 and tiles256 < 2 * 148) or (tw - 1) * in_mul + 1 > 256 \
+            or (th - 1) * in_mul + 1 > 256 or tn > 256:
+        tn, th, tw = _brick(b, grid_hw[0], grid_hw[1], 128)
+    g.tn, g.th, g.tw = tn, th, tw
     g.in_mul, g.out_mul = in_mul, out_mul
     g.out_off_h, g.out_off_w = out_off
     g.out_h, g.out_w = out.shape[1], out.shape[2]

@@ -51,6 +51,22 @@ def test_gemm_mn_major_operands(a_mn, b_mn, m, n, k):
     assert _rel_err(d, expect) < 5e-3
 
 
+@pytest.mark.parametrize("bm", [128, 256])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, True)])
+def test_gemm_tall_tiles(bm, a_mn, b_mn):
+    nv, no = _nops()
+    torch.manual_seed(13)
+    m, n, k = 1000, 520, 328
+    a = torch.randn(m, k, device=DEV).to(BF)
+    b = torch.randn(n, k, device=DEV).to(BF)
+    d = no.gemm(a.t().contiguous() if a_mn else a, b.t().contiguous() if b_mn else b, a_mn=a_mn, b_mn=b_mn, bm=bm)
+    nv.check_status(a.device)
+    assert _rel_err(d, a.float() @ b.float().t()) < 5e-3
+    bias = torch.randn(n, device=DEV).to(BF)
+    d = no.gemm(a, b, bias=bias, act="gelu", bm=bm, bn=128)
+    assert_similar(torch.nn.functional.gelu(a.float() @ b.float().t() + bias.float()).to(BF), d, 0.25)
+
+
 def test_gemm_epilogues():
     nv, no = _nops()
     torch.manual_seed(2)
@@ -93,6 +109,13 @@ def test_conv_fprop_and_dgrad(stride, pad, dil, shape):
     expect = ref.conv2d_nhwc(x.float(), wt.float(), stride, pad, dil)
     assert y.shape == expect.shape
     assert _rel_err(y, expect) < 5e-3
+    if o >= 128:   # the same convolution with the other tile height
+        oh, ow = no.conv_out_hw(h, w, stride, pad, dil)
+        taps = [(r * dil - pad, s * dil - pad) for r in range(3) for s in range(3)]
+        for rows in (128, 256):
+            y2 = torch.empty_like(y)
+            no.conv_pass(x, wt.reshape(o, 9 * c), o, y2, grid_hw=(oh, ow), in_mul=stride, taps=taps, tile_rows=rows)
+            assert _rel_err(y2, expect) < 5e-3, rows
     dy = torch.randn_like(expect).to(BF)
     dx = no.conv2d_dgrad(dy, wt, (h, w), stride, pad, dil)
     xf = x.float().requires_grad_(True)
