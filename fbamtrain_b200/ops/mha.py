@@ -1,10 +1,74 @@
-"""Scaled-dot-product attention over ``(B, T, H, D)`` views."""
+"""Scaled-dot-product attention over ``(B, T, H, D)`` views on the tcgen05 flash kernels
+(``csrc/attention_tcgen05.cu``): causal or not, head dimension 64 or 128, bf16.
+
+q, k and v are normally strided views into one fused-QKV projection output and are consumed in place
+(reference layout: ``tensorlib/include/attention.h:95-114``; the reference's kernels cover head
+dimension 128 only, ``src/passes/mha_attention_pass.cpp:1017-1124``).  The forward returns the
+output and keeps the per-row log-sum-exp for the backward pass.  Other head dimensions run the
+library attention.
+"""
 from __future__ import annotations
 
+import ctypes as C
+import math
+
+import torch
 import torch.nn.functional as F
+
+from . import native as nv
+
+BF16 = torch.bfloat16
+_warned = set()
+
+
+def _same_layout(q, k, v) -> bool:
+    return q.stride() == k.stride() == v.stride() and q.stride(3) == 1
+
+
+class _FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal):
+        b, t, h, d = q.shape
+        if not _same_layout(q, k, v):
+            q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        out = torch.empty(b, t, h, d, dtype=BF16, device=q.device)
+        lse = torch.empty(b, h, t, dtype=torch.float32, device=q.device)
+        scale = 1.0 / math.sqrt(d)
+        sb, st, sh = q.stride(0), q.stride(1), q.stride(2)
+        nv.check(nv.lib().fbam_attn_fwd(nv.ptr(q), nv.ptr(k), nv.ptr(v), C.c_longlong(sb), C.c_longlong(st),
+                                        C.c_longlong(sh), nv.ptr(out), nv.ptr(lse), b, t, h, d, int(causal),
+                                        C.c_float(scale), nv.ptr(nv.status_word(q.device)), nv.stream_ptr()),
+                 "fbam_attn_fwd")
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        q, k, v, out, lse = ctx.saved_tensors
+        b, t, h, d = q.shape
+        if d_out.stride(3) != 1:
+            d_out = d_out.contiguous()
+        dq32 = torch.zeros(b, t, h, d, dtype=torch.float32, device=q.device)
+        dk = torch.empty(b, t, h, d, dtype=BF16, device=q.device)
+        dv = torch.empty(b, t, h, d, dtype=BF16, device=q.device)
+        delta = torch.empty(b, h, t, dtype=torch.float32, device=q.device)
+        nv.check(nv.lib().fbam_attn_bwd(
+            nv.ptr(q), nv.ptr(k), nv.ptr(v), C.c_longlong(q.stride(0)), C.c_longlong(q.stride(1)),
+            C.c_longlong(q.stride(2)), nv.ptr(out), nv.ptr(d_out), C.c_longlong(d_out.stride(0)),
+            C.c_longlong(d_out.stride(1)), C.c_longlong(d_out.stride(2)), nv.ptr(lse), nv.ptr(delta), nv.ptr(dq32),
+            nv.ptr(dk), nv.ptr(dv), b, t, h, d, int(ctx.causal), C.c_float(ctx.scale),
+            nv.ptr(nv.status_word(q.device)), nv.stream_ptr()), "fbam_attn_bwd")
+        return dq32.to(BF16), dk, dv, None
 
 
 def flash_attention(q, k, v, causal):
-    # Interim: library kernel.  The hand-written flash kernel replaces this.
+    d = q.shape[-1]
+    if q.dtype == BF16 and d in (64, 128) and (q.stride(0) * 2) % 16 == 0 and (q.stride(1) * 2) % 16 == 0:
+        return _FlashAttention.apply(q, k, v, bool(causal))
+    if d not in _warned:
+        _warned.add(d)
+        from ..utils.logging import LOG
+        LOG("WARN", f"attention with head dimension {d} runs the library kernel (native kernels cover 64 and 128)")
     o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal)
     return o.transpose(1, 2).contiguous()

@@ -343,3 +343,25 @@ def test_conv_gelu_stack_pool_matches_unfused_reference():
     for name, a, e in zip(("dx", "dw1", "dw2"), got, exp):
         assert _rel_err(a, e) < 2e-2, (name, _rel_err(a, e))
     nv.check_status(x.device)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("b,t,h,d", [(2, 128, 2, 64), (1, 300, 3, 64), (2, 256, 2, 128), (1, 1024, 4, 64),
+                                     (1, 480, 2, 128)])
+def test_flash_attention_fwd_bwd(causal, b, t, h, d):
+    nv, no = _nops()
+    from fbamtrain_b200.ops.mha import flash_attention
+    torch.manual_seed(14)
+    qkv = torch.randn(b, t, 3, h, d, device=DEV).to(BF).requires_grad_(True)     # fused projection layout
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    o = flash_attention(q, k, v, causal)
+    nv.check_status(qkv.device)
+    g = torch.randn_like(o)
+    (gqkv,) = torch.autograd.grad(o, qkv, g)
+    nv.check_status(qkv.device)
+    f = qkv.detach().float().requires_grad_(True)
+    of = ref.attention(f[:, :, 0], f[:, :, 1], f[:, :, 2], causal)
+    (eqkv,) = torch.autograd.grad(of, f, g.float())
+    assert_similar(of.to(BF), o, 3e-2)
+    for i, name in enumerate(("dq", "dk", "dv")):
+        assert _rel_err(gqkv[:, :, i], eqkv[:, :, i]) < 3e-2, (name, _rel_err(gqkv[:, :, i], eqkv[:, :, i]))
