@@ -99,6 +99,7 @@ __device__ __forceinline__ Work decode_work(const GemmParams& p, int item, int t
   const int t = item % tiles;
   w.tile_m = t / tiles_n;
   w.tile_n = t % tiles_n;
+  if (p.tile_m_rotate > 0) w.tile_m = (w.tile_m + p.tile_m_rotate) % p.tiles_m;
   const int per = (p.k_blocks + p.splits - 1) / p.splits;
   w.k_begin = split * per;
   w.k_end = min(p.k_blocks, w.k_begin + per);
@@ -163,6 +164,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           ch = ((tile_m / g.tiles_w) % g.tiles_h) * g.th * g.in_mul;
           cn = (tile_m / (g.tiles_w * g.tiles_h)) * g.tn;
         }
+        if (p.ready_flags != nullptr) {
+          // all-gather -> GEMM: wait (bounded) until the peers' shards that this tile reads have landed
+          const int r0 = p.flag_on_b ? tile_n * BN : tile_m * BM;
+          const int r1 = min(p.flag_on_b ? p.N : p.M, r0 + (p.flag_on_b ? BN : BM)) - 1;
+          for (int f = r0 / p.flag_rows; f <= r1 / p.flag_rows && ok; ++f) {
+            unsigned spins = 0, v;
+            do {
+              asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.ready_flags + f) : "memory");
+              if ((int)(v - p.flag_epoch) >= 0) break;
+              __nanosleep(64);
+            } while (++spins < p.flag_spin_limit);
+            if ((int)(v - p.flag_epoch) < 0) ok = false;
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy acquire -> async-proxy (TMA) reads
+        }
         for (int kb = wk.k_begin; kb < wk.k_end; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::kStageBytes;
@@ -213,6 +230,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
       }
       if (!ok) atomicExch(p.status, GEMM_ERR_PRODUCER_TIMEOUT);
+      // (a timed-out flag wait also lands here: the consumers then time out on their barriers and the CTA unwinds)
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -351,6 +369,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             for (int j = 0; j < 32; ++j)
               if (n0 + j < p.N) v[j] += __bfloat162float(ri[j]);
           }
+        }
+        if (p.rs_rows_per_rank > 0) {
+          // GEMM -> reduce-scatter: add this rank's partial sums into the owner's fp32 buffer over NVLink
+          const int m = (int)(roff / p.ldd);
+          const int owner = m / p.rs_rows_per_rank;
+          float* out = reinterpret_cast<float*>(p.rs_out[owner]) + (long long)(m - owner * p.rs_rows_per_rank) * p.ldd + n0;
+          if (full_vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + j), "f"(v[j]),
+                           "f"(v[j + 1]), "f"(v[j + 2]), "f"(v[j + 3])
+                           : "memory");
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N)
+                asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(out + j), "f"(v[j]) : "memory");
+          }
+          continue;
         }
         if (p.out_fp32) {
           float* out = reinterpret_cast<float*>(p.D) + roff + n0;
@@ -535,6 +571,14 @@ extern "C" int fbam_gemm_bf16(const void* A, long long lda, int a_mn_major, cons
              (p.preact_out == nullptr || (reinterpret_cast<uintptr_t>(p.preact_out) & 15) == 0) &&
              (p.gelu_grad_in == nullptr || (reinterpret_cast<uintptr_t>(p.gelu_grad_in) & 15) == 0) &&
              (p.residual == nullptr || (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) && (p.ldd % 8 == 0);
+  if (p.rs_rows_per_rank > 0) {
+    if (p.mode != GEMM_MODE_PLAIN) return GEMM_ERR_SHAPE;
+    p.vec_ok = (p.ldd % 4 == 0);
+    for (int r = 0; r * p.rs_rows_per_rank < M; ++r)
+      if (r >= 8 || p.rs_out[r] == nullptr || (reinterpret_cast<uintptr_t>(p.rs_out[r]) & 15)) return GEMM_ERR_ALIGNMENT;
+  }
+  if (p.ready_flags != nullptr && (p.flag_rows <= 0)) return GEMM_ERR_SHAPE;
+  if (p.flag_spin_limit == 0) p.flag_spin_limit = 1u << 22;
   CUtensorMap ma, mb;
   int e;
   if (a_mn_major) e = encode_2d(&ma, A, K, M, lda, 64);  // rows = K, cols = M, panels of 64 columns

@@ -42,6 +42,16 @@ struct GemmParams {
   int bm;                           // 0 = choose from the tile count; else 128 / 256 (plain GEMM and wgrad)
   int max_ctas;                     // 0 = one per SM
   int splits;                       // split-K factor (needs fp32 output with atomic accumulation); 0/1 = none
+  // all-gather -> GEMM: rows of the gated operand arrive from peers; rows [i*flag_rows, (i+1)*flag_rows) are
+  // complete once ready_flags[i] >= flag_epoch (ready_flags is in local memory; peers store to it)
+  const unsigned* ready_flags;
+  int tile_m_rotate;                // tile rows are visited starting at this tile index (own shard first)
+  int flag_rows, flag_on_b;
+  unsigned flag_epoch, flag_spin_limit;
+  // GEMM -> reduce-scatter: fp32 partial sums are added (system-scope reductions over peer memory) into the
+  // buffer of the rank that owns the output row: owner = m / rs_rows_per_rank, local row = m % rs_rows_per_rank
+  void* rs_out[8];
+  int rs_rows_per_rank;
   // filled by the launcher
   int mode, M, N, K, tiles_m, k_blocks, a_mn_major, b_mn_major, vec_ok;
   ConvGeom conv;

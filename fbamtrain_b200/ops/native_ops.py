@@ -35,12 +35,20 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = BF16, bias: Optional[torch.Tensor] = None,
          act: str = "none", residual: Optional[torch.Tensor] = None, preact_out: Optional[torch.Tensor] = None,
          gelu_grad_in: Optional[torch.Tensor] = None, accumulate: int = 0, alpha: float = 1.0,
-         bn: int = 0, bm: int = 0, max_ctas: int = 0) -> torch.Tensor:
+         bn: int = 0, bm: int = 0, max_ctas: int = 0, ready_flags: Optional[torch.Tensor] = None,
+         flag_rows: int = 0, flag_on_b: bool = False, flag_epoch: int = 0, flag_spin_limit: int = 0,
+         rs_out=None, rs_rows_per_rank: int = 0, tile_m_rotate: int = 0) -> torch.Tensor:
     """``D[M, N] = epilogue(A · Bᵀ)``.
 
     ``a``: ``(M, K)`` (or ``(K, M)`` when ``a_mn``); ``b``: ``(N, K)`` (or ``(K, N)`` when ``b_mn``).
     Operands must be bf16 with unit inner stride, 16-byte aligned rows.  ``accumulate``: 0 overwrite,
-    1 read-modify-write ``D +=``, 2 atomic adds (fp32 output only)."""
+    1 read-modify-write ``D +=``, 2 atomic adds (fp32 output only).
+
+    ``ready_flags`` (int32 tensor in local memory, written by peers) gates the loads of A (or B with
+    ``flag_on_b``): rows ``[i·flag_rows, (i+1)·flag_rows)`` are read only once ``ready_flags[i] >= flag_epoch``
+    (all-gather → GEMM).  ``rs_out`` (list of peer fp32 buffer addresses) with ``rs_rows_per_rank`` makes the
+    epilogue add the tile into the buffer of the rank owning each output row (GEMM → reduce-scatter); ``out``
+    is then only used for its shape and pitch."""
     _need_bf16(a, b)
     if a.stride(-1) != 1 or b.stride(-1) != 1:
         raise ValueError("GEMM operands need unit inner stride")
@@ -73,6 +81,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     p.act = nv.GEMM_ACT[act]
     p.accumulate = accumulate
     p.bn, p.bm, p.max_ctas = bn, bm, max_ctas
+    p.tile_m_rotate = tile_m_rotate
+    if ready_flags is not None:
+        p.ready_flags = ready_flags.data_ptr()
+        p.flag_rows, p.flag_on_b, p.flag_epoch, p.flag_spin_limit = flag_rows, int(flag_on_b), flag_epoch, flag_spin_limit
+    if rs_out is not None:
+        for i, ptr_ in enumerate(rs_out):
+            p.rs_out[i] = ptr_
+        p.rs_rows_per_rank = rs_rows_per_rank
     code = nv.lib().fbam_gemm_bf16(nv.ptr(a), C.c_longlong(a.stride(0)), int(a_mn), nv.ptr(b),
                                    C.c_longlong(b.stride(0)), int(b_mn), m, n, k, C.byref(p), nv.stream_ptr())
     nv.check(code, "fbam_gemm_bf16")

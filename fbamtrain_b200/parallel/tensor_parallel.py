@@ -1,0 +1,301 @@
+"""Tensor parallelism for the attention / MLP blocks of the action model (Megatron-style with
+sequence-sharded activations between the parallel regions).
+
+Activations between blocks are sharded by token rows; a *column-parallel* linear (fused QKV, MLP fc1) needs all
+rows — all-gather → GEMM — and a *row-parallel* linear (attention out-projection, MLP fc2) produces partial sums
+over the hidden shards — GEMM → reduce-scatter.  Two transports implement the two patterns:
+
+``nccl``   ``all_gather_into_tensor`` / ``reduce_scatter_tensor`` around plain GEMMs (the baseline; also what
+           runs on CPU ranks with gloo).
+``fused``  the tcgen05 GEMM itself talks to peer memory (``csrc/gemm_tcgen05.cu``):
+           *all-gather → GEMM*: every rank pushes its row shard into all peers' staging windows and raises a
+           per-source flag; the consuming GEMM starts with its own rows and its TMA producer waits, tile by tile,
+           for the flag of the shard a tile reads, so remote shards stream in underneath the math (the remote
+           tile lands in local memory first — no TMA load ever targets a peer).
+           *GEMM → reduce-scatter*: the epilogue adds each fp32 tile directly into the buffer of the rank that
+           owns those rows (system-scope vector reductions over NVLink), so there is no separate collective.
+
+The reference has no tensor parallelism (it shards positions of the sequence across frame-head workers
+instead); the benchmark configurations ask for 4-way TP inside the action-model pipeline stage.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from .. import ops
+from ..models.blocks import AttentionBlock
+
+
+class TpContext:
+    def __init__(self, group: Optional[dist.ProcessGroup], device: torch.device, transport: str = "nccl",
+                 spin_limit: int = 1 << 22):
+        if transport not in ("nccl", "fused"):
+            raise ValueError("transport must be nccl or fused")
+        self.group, self.device, self.transport = group, device, transport
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.spin_limit = spin_limit
+        self.peers = None
+        self._win: Dict[Tuple, object] = {}
+        if transport == "fused":
+            from .peer_window import PeerGroup
+            self.peers = PeerGroup(group, device)
+            self._side = torch.cuda.Stream(device=device)
+
+    # ---------------------------------------------------------------- library collectives
+    def all_gather_rows(self, shard: torch.Tensor) -> torch.Tensor:
+        full = torch.empty((shard.shape[0] * self.world,) + tuple(shard.shape[1:]), dtype=shard.dtype,
+                           device=shard.device)
+        dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
+        return full
+
+    def reduce_scatter_rows(self, partial: torch.Tensor) -> torch.Tensor:
+        out = torch.empty((partial.shape[0] // self.world,) + tuple(partial.shape[1:]), dtype=partial.dtype,
+                          device=partial.device)
+        dist.reduce_scatter_tensor(out, partial.contiguous(), group=self.group)
+        return out
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        dist.all_reduce(t, group=self.group)
+        return t
+
+    # ---------------------------------------------------------------- fused kernels
+    def _window(self, kind: str, numel: int, dtype: torch.dtype):
+        key = (kind, numel, dtype)
+        if key not in self._win:
+            self._win[key] = self.peers.allocate(f"tp/{kind}/{numel}/{dtype}", numel, dtype)
+        return self._win[key]
+
+    def _barrier(self, slot: int) -> None:
+        from ..ops import native as nv
+        epoch = self.peers.next_epoch()
+        nv.check(nv.lib().fbam_peer_barrier(self.peers.flags.c_ptrs, self.rank, self.world, slot, C.c_uint(epoch),
+                                            C.c_uint(self.spin_limit), nv.ptr(nv.status_word(self.device)),
+                                            nv.stream_ptr()), "fbam_peer_barrier")
+
+    def ag_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, bias, act: str, preact_out=None):
+        """``act(all_gather(x_shard) · wᵀ + bias)``; returns the result and the gathered input."""
+        from ..ops import native as nv
+        from ..ops import native_ops as no
+        rows, k = x_shard.shape
+        win = self._window("ag", rows * self.world * k, x_shard.dtype)
+        x_full = win.local.view(rows * self.world, k)
+        self._barrier(2)                                   # everyone is done reading the previous contents
+        x_full[self.rank * rows:(self.rank + 1) * rows].copy_(x_shard)
+        epoch = self.peers.next_epoch()
+        cur = torch.cuda.current_stream()
+        self._side.wait_stream(cur)
+        with torch.cuda.stream(self._side):                # push to the peers beside the GEMM
+            lo = self.rank * rows * k * x_shard.element_size()
+            nv.check(nv.lib().fbam_push_shard(win.c_ptrs, self.peers.flags.c_ptrs, C.c_longlong(lo),
+                                              C.c_longlong(lo + rows * k * x_shard.element_size()), self.rank,
+                                              self.world, 3, C.c_uint(epoch), nv.ptr(self.peers.arrive[1:]),
+                                              nv.stream_ptr()), "fbam_push_shard")
+        from .peer_window import MAX_RANKS
+        flags = self.peers.flags.local[3 * MAX_RANKS:4 * MAX_RANKS]
+        m_full, n_out = rows * self.world, w.shape[0]
+        tile_rows = 256 if ((m_full + 255) // 256) * ((n_out + 255) // 256) >= 296 and n_out >= 128 else 128
+        y = no.gemm(x_full, w, bias=bias, act=act, preact_out=preact_out, ready_flags=flags, flag_rows=rows,
+                    flag_epoch=epoch, flag_spin_limit=self.spin_limit, bm=tile_rows,
+                    tile_m_rotate=(self.rank * rows) // tile_rows)
+        cur.wait_stream(self._side)
+        return y, x_full.clone() if x_shard.requires_grad or w.requires_grad else x_full
+
+    def gemm_rs(self, h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """``reduce_scatter_rows(h · wᵀ)`` with the reduction done by the GEMM epilogue; returns bf16 rows."""
+        from ..ops import native_ops as no
+        m, n = h.shape[0], w.shape[0]
+        rows = m // self.world
+        win = self._window("rs", rows * n, torch.float32)
+        acc = win.local.view(rows, n)
+        acc.zero_()
+        self._barrier(4)                                   # every accumulator is cleared before anyone adds
+        # the epilogue never writes through `out` in this mode; it only supplies the (M, N) shape and row pitch
+        shape_only = torch.as_strided(acc, (m, n), (0, 1))
+        no.gemm(h, w, out=_RsShape(shape_only, n), rs_out=list(win.ptrs), rs_rows_per_rank=rows)
+        self._barrier(5)                                   # all partial sums have arrived
+        return acc.to(torch.bfloat16)
+
+
+class _RsShape:
+    """Stand-in output for the reduce-scatter GEMM: exposes shape, dtype, pitch and an address for the
+    launcher's checks (the kernel writes to the owners' buffers instead)."""
+
+    def __init__(self, t: torch.Tensor, pitch: int):
+        self._t, self._pitch = t, pitch
+        self.shape, self.dtype = t.shape, t.dtype
+
+    def stride(self, i: int) -> int:
+        return (self._pitch, 1)[i]
+
+    def data_ptr(self) -> int:
+        return self._t.data_ptr()
+
+
+# =================================================================================================
+# autograd functions
+# =================================================================================================
+def _mm_nt(a, b, bias=None, act="none"):
+    return ops.linear(a, b, bias, act)
+
+
+class _ColumnParallel(torch.autograd.Function):
+    """``y = act(AG_rows(x) · wᵀ + b)``; backward reduce-scatters the input gradient."""
+
+    @staticmethod
+    def forward(ctx, x_shard, w, b, tp: TpContext, act: str):
+        fused = tp.transport == "fused" and x_shard.is_cuda
+        preact = None
+        if fused:
+            if act == "gelu":
+                preact = torch.empty((x_shard.shape[0] * tp.world, w.shape[0]), dtype=x_shard.dtype,
+                                     device=x_shard.device)
+            y, x_full = tp.ag_gemm(x_shard, w, b, act, preact)
+        else:
+            x_full = tp.all_gather_rows(x_shard)
+            z = x_full.float() @ w.float().t() if not x_full.is_cuda else None
+            if x_full.is_cuda:
+                from ..ops import native_ops as no
+                if act == "gelu":
+                    preact = torch.empty((x_full.shape[0], w.shape[0]), dtype=x_full.dtype, device=x_full.device)
+                y = no.gemm(x_full, w, bias=b, act=act, preact_out=preact)
+            else:
+                if b is not None:
+                    z = z + b.float()
+                preact = z.to(x_full.dtype) if act == "gelu" else None
+                y = (torch.nn.functional.gelu(z) if act == "gelu" else z).to(x_full.dtype)
+        ctx.save_for_backward(x_full, w, preact)
+        ctx.tp, ctx.act, ctx.has_bias = tp, act, b is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_full, w, preact = ctx.saved_tensors
+        tp: TpContext = ctx.tp
+        dy = dy.contiguous()
+        if ctx.act == "gelu":
+            from ..ops import reference as ref
+            dy = (dy.float() * ref.gelu_grad(preact)).to(dy.dtype)
+        if dy.is_cuda:
+            from ..ops import native_ops as no
+            if tp.transport == "fused":
+                dx = tp.gemm_rs(dy, w.t().contiguous())
+            else:
+                dx = tp.reduce_scatter_rows(no.gemm_nn(dy, w))
+            dw = no.gemm_tn(dy, x_full)
+            db = no._colsum(dy).to(dy.dtype) if ctx.has_bias else None
+        else:
+            dx = tp.reduce_scatter_rows((dy.float() @ w.float()).to(dy.dtype))
+            dw = (dy.float().t() @ x_full.float()).to(w.dtype)
+            db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias else None
+        return dx, dw, db, None, None
+
+
+class _RowParallel(torch.autograd.Function):
+    """``y_shard = RS_rows(h · wᵀ)``; backward all-gathers the output gradient."""
+
+    @staticmethod
+    def forward(ctx, h, w, tp: TpContext):
+        if h.is_cuda:
+            from ..ops import native_ops as no
+            if tp.transport == "fused":
+                y = tp.gemm_rs(h.contiguous(), w)
+            else:
+                y = tp.reduce_scatter_rows(no.gemm(h.contiguous(), w))
+        else:
+            y = tp.reduce_scatter_rows((h.float() @ w.float().t()).to(h.dtype))
+        ctx.save_for_backward(h, w)
+        ctx.tp = tp
+        return y
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        h, w = ctx.saved_tensors
+        tp: TpContext = ctx.tp
+        if dy_shard.is_cuda:
+            from ..ops import native_ops as no
+            if tp.transport == "fused":
+                dh, dy_full = tp.ag_gemm(dy_shard.contiguous(), w.t().contiguous(), None, "none")
+            else:
+                dy_full = tp.all_gather_rows(dy_shard)
+                dh = no.gemm_nn(dy_full, w)
+            dw = no.gemm_tn(dy_full, h)
+        else:
+            dy_full = tp.all_gather_rows(dy_shard)
+            dh = (dy_full.float() @ w.float()).to(h.dtype)
+            dw = (dy_full.float().t() @ h.float()).to(w.dtype)
+        return dh, dw, None
+
+
+# =================================================================================================
+# tensor-parallel attention / MLP block
+# =================================================================================================
+class TensorParallelBlock(nn.Module):
+    """One pre-norm attention + MLP block with heads and MLP columns split over the TP group.  Built from an
+    unsharded :class:`AttentionBlock` so that both share initialisation (and tests can compare them).
+    Input and output are row shards ``(B·T / tp, E)`` of the token matrix."""
+
+    def __init__(self, block: AttentionBlock, tp: TpContext, batch: int, seq: int):
+        super().__init__()
+        self.tp, self.batch, self.seq = tp, batch, seq
+        r, w = tp.rank, tp.world
+        attn = block.attn
+        e = attn.proj.weight.shape[0]
+        self.heads_local = attn.n_head // w
+        self.head_dim = e // attn.n_head
+        if attn.n_head % w or (batch * seq) % w:
+            raise ValueError("heads and tokens must divide by the tensor-parallel degree")
+        self.causal = attn.causal
+        hl, d = self.heads_local, self.head_dim
+        qkv = attn.qkv.weight.detach().view(3, attn.n_head, d, e)[:, r * hl:(r + 1) * hl].reshape(3 * hl * d, e)
+        self.w_qkv = nn.Parameter(qkv.clone())
+        self.b_qkv = None
+        if attn.qkv.bias is not None:
+            self.b_qkv = nn.Parameter(attn.qkv.bias.detach().view(3, attn.n_head, d)[:, r * hl:(r + 1) * hl]
+                                      .reshape(-1).clone())
+        self.w_proj = nn.Parameter(attn.proj.weight.detach()[:, r * hl * d:(r + 1) * hl * d].clone())
+        self.b_proj = nn.Parameter(attn.proj.bias.detach().clone()) if attn.proj.bias is not None else None
+        f = block.mlp.fc1.weight.shape[0]
+        fl = f // w
+        self.w_fc1 = nn.Parameter(block.mlp.fc1.weight.detach()[r * fl:(r + 1) * fl].clone())
+        self.b_fc1 = nn.Parameter(block.mlp.fc1.bias.detach()[r * fl:(r + 1) * fl].clone()) \
+            if block.mlp.fc1.bias is not None else None
+        self.w_fc2 = nn.Parameter(block.mlp.fc2.weight.detach()[:, r * fl:(r + 1) * fl].clone())
+        self.b_fc2 = nn.Parameter(block.mlp.fc2.bias.detach().clone()) if block.mlp.fc2.bias is not None else None
+        self.ln1_weight = nn.Parameter(block.ln1.weight.detach().clone())
+        self.ln2_weight = nn.Parameter(block.ln2.weight.detach().clone())
+        self.eps = block.ln1.eps
+
+    def replicated_parameters(self):
+        """Parameters every TP rank holds in full; their gradients are partial sums over row shards and must be
+        all-reduced over the TP group after backward (:func:`sync_replicated_grads`)."""
+        return [p for p in (self.ln1_weight, self.ln2_weight, self.b_proj, self.b_fc2) if p is not None]
+
+    def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
+        tp = self.tp
+        h = ops.rms_norm(x_shard, self.ln1_weight, self.eps)
+        qkv = _ColumnParallel.apply(h, self.w_qkv, self.b_qkv, tp, "none")
+        qkv = qkv.view(self.batch, self.seq, 3, self.heads_local, self.head_dim)
+        o = ops.attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], self.causal)
+        a = _RowParallel.apply(o.reshape(self.batch * self.seq, -1), self.w_proj, tp)
+        if self.b_proj is not None:
+            a = a + self.b_proj
+        x_shard = x_shard + a
+        h = ops.rms_norm(x_shard, self.ln2_weight, self.eps)
+        u = _ColumnParallel.apply(h, self.w_fc1, self.b_fc1, tp, "gelu")
+        m = _RowParallel.apply(u, self.w_fc2, tp)
+        if self.b_fc2 is not None:
+            m = m + self.b_fc2
+        return x_shard + m
+
+
+def sync_replicated_grads(blocks, tp: TpContext) -> None:
+    for blk in blocks:
+        for p in blk.replicated_parameters():
+            if p.grad is not None:
+                tp.all_reduce(p.grad)

@@ -143,3 +143,49 @@ def test_fused_dp_matches_nccl_zero1_on_two_gpus(tmp_path, variant):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert out.read_text() == "ok"
+
+
+def test_fused_tensor_parallel_block_matches_nccl_on_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = tmp_path / "result.txt"
+    worker = os.path.join(os.path.dirname(__file__), "workers", "tp_fused_worker.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), worker, str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert out.read_text() == "ok"
+
+
+def test_flag_gated_gemm_and_reduce_scatter_epilogue_single_gpu():
+    """The gated producer with flags already raised, and the reduce-scatter epilogue with every 'peer' buffer
+    on this device (one rank's launch at a time, no cross-rank waits)."""
+    from fbamtrain_b200.ops import native_ops as no
+    nv = _nv()
+    torch.manual_seed(3)
+    m, n, k, world = 512, 384, 256, 4
+    a = torch.randn(m, k, device=DEV).to(BF)
+    b = torch.randn(n, k, device=DEV).to(BF)
+    expect = a.float() @ b.float().t()
+    flags = torch.full((8,), 9, dtype=torch.int32, device=DEV)
+    y = no.gemm(a, b, ready_flags=flags, flag_rows=m // world, flag_epoch=9, flag_spin_limit=100, tile_m_rotate=2)
+    assert float((y.float() - expect).norm() / expect.norm()) < 5e-3
+    # a flag that is never raised: the producer gives up, the kernel unwinds, the status word says so
+    status = nv.status_word(torch.device(DEV))
+    status.zero_()
+    flags.fill_(1)
+    no.gemm(a, b, ready_flags=flags, flag_rows=m // world, flag_epoch=5, flag_spin_limit=50)
+    torch.cuda.synchronize()
+    assert int(status.item()) in (101, 102, 103)
+    status.zero_()
+    # reduce-scatter epilogue: two "ranks" contribute partial products into four owners' buffers
+    rows = m // world
+    owners = [torch.zeros(rows, n, device=DEV) for _ in range(world)]
+    from fbamtrain_b200.parallel.tensor_parallel import _RsShape
+    for part in range(2):
+        ap, bp = a[:, part * 128:(part + 1) * 128].contiguous(), b[:, part * 128:(part + 1) * 128].contiguous()
+        shape = _RsShape(torch.as_strided(owners[0], (m, n), (0, 1)), n)
+        no.gemm(ap, bp, out=shape, rs_out=[o.data_ptr() for o in owners], rs_rows_per_rank=rows)
+    nv.check_status(torch.device(DEV))
+    got = torch.cat(owners, 0)
+    assert float((got - expect).norm() / expect.norm()) < 5e-3
