@@ -63,28 +63,38 @@ __device__ __forceinline__ bool wait_all(const unsigned* my_flags, int slot, int
   return true;
 }
 
-// Grid-wide, cross-GPU barrier.  CTA 0 publishes this rank's arrival to every peer (after all CTAs of this
-// grid have arrived locally when `local_arrive` is given), and every CTA waits on the local flag array.
+// Entry barrier: CTA 0 tells every peer that this rank has arrived; every CTA then waits on the LOCAL flag array
+// until all peers have arrived.  CTAs do not depend on one another, so the grid need not be co-resident.
 __device__ bool signal_and_wait(const PeerPtrs& flags, int rank, int world, int slot, unsigned epoch,
-                                unsigned spin_limit, int* status, unsigned* local_arrive, unsigned arrive_target) {
-  __syncthreads();
+                                unsigned spin_limit, int* status) {
   int ok = 1;
   if (threadIdx.x == 0) {
-    __threadfence_system();
-    bool publish = (blockIdx.x == 0);
-    if (local_arrive != nullptr) {
-      // last CTA to arrive publishes, so that peers see the signal only after the whole grid's writes
-      const unsigned prev = atomicAdd(local_arrive, 1u);
-      publish = (prev + 1 == arrive_target);
-      if (publish) __threadfence_system();
-    }
-    if (publish) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
       for (int r = 0; r < world; ++r)
         st_release_sys(reinterpret_cast<unsigned*>(flags.p[r]) + slot * FBAM_MAX_RANKS + rank, epoch);
     }
     ok = wait_all(reinterpret_cast<const unsigned*>(flags.p[rank]), slot, world, epoch, spin_limit, status) ? 1 : 0;
   }
   return __syncthreads_and(ok) != 0;
+}
+
+// Exit barrier: every CTA makes its writes visible and counts itself in; only the LAST CTA of the grid
+// publishes this rank's completion to the peers and waits for theirs.  All other CTAs leave at once, so no CTA
+// ever waits for a CTA of its own grid that may not have been scheduled yet.
+__device__ void finish_and_wait(const PeerPtrs& flags, int rank, int world, int slot, unsigned epoch,
+                                unsigned spin_limit, int* status, unsigned* local_arrive) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned prev = atomicAdd(local_arrive, 1u);
+    if (prev + 1 == gridDim.x) {
+      __threadfence_system();
+      for (int r = 0; r < world; ++r)
+        st_release_sys(reinterpret_cast<unsigned*>(flags.p[r]) + slot * FBAM_MAX_RANKS + rank, epoch);
+      wait_all(reinterpret_cast<const unsigned*>(flags.p[rank]), slot, world, epoch, spin_limit, status);
+    }
+  }
 }
 
 __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* f) {
@@ -120,7 +130,7 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_gra
                    float* master, long long lo, long long hi, AdamArgs a, int rank, int world, unsigned epoch,
                    int sync, unsigned spin_limit, int* status, unsigned* arrive) {
   // phase 0: every rank's gradients are complete (this kernel is stream-ordered after the local backward)
-  if (sync && !signal_and_wait(flags, rank, world, 0, epoch, spin_limit, status, nullptr, 0)) return;
+  if (sync && !signal_and_wait(flags, rank, world, 0, epoch, spin_limit, status)) return;
 
   constexpr int VEC = BF16 ? 8 : 4;  // elements per 16-byte packet
   const long long packets = (hi - lo) / VEC;
@@ -201,7 +211,7 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_gra
     }
   }
   // phase 1: every rank has written its shard everywhere (and has finished reading everyone's gradients)
-  if (sync) signal_and_wait(flags, rank, world, 1, epoch, spin_limit, status, arrive, gridDim.x);
+  if (sync) finish_and_wait(flags, rank, world, 1, epoch, spin_limit, status, arrive);
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -274,7 +284,7 @@ push_shard_kernel(PeerPtrs bufs, PeerPtrs flags, long long lo_bytes, long long h
 
 __global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int slot, unsigned epoch, unsigned spin_limit,
                                     int* status) {
-  signal_and_wait(flags, rank, world, slot, epoch, spin_limit, status, nullptr, 0);
+  signal_and_wait(flags, rank, world, slot, epoch, spin_limit, status);
 }
 
 // Wait (bounded) until the local flags of `slot` reach `epoch`; sets status on timeout.
@@ -322,7 +332,6 @@ int fbam_rs_adamw_ag(void* const* grads, void* const* params, void* const* flags
   if (sync && flags == nullptr) return 1;
   AdamArgs a{lr, b1, b2, eps, wd, 1.0f / bc1, 1.0f / bc2, grad_scale};
   const long long packets = (hi - lo) / vec;
-  // Persistent-style grid: all CTAs must be co-resident because they spin on the end-of-kernel barrier.
   int grid = (int)((packets + 255) / 256);
   int cap = max_ctas > 0 ? max_ctas : num_sms() * 2;
   if (grid > cap) grid = cap;

@@ -598,6 +598,33 @@ def adamw_flat(param, grad, m, v, master, lo, hi, lr, b1, b2, eps, wd, bc1, bc2,
 
 
 # =================================================================================================
+# Newton–Schulz orthogonalisation on the tensor-core GEMM (Muon)
+# =================================================================================================
+NS_A, NS_B, NS_C = 3.4445, -4.7750, 2.0315
+
+
+def newton_schulz(g: torch.Tensor, steps: int = 5, dtype: torch.dtype = BF16, norm: Optional[torch.Tensor] = None
+                  ) -> torch.Tensor:
+    """Five (by default) iterations of ``A = X Xᵀ; B = b·A + c·A A; X = a·X + B X`` in bf16, every product on the
+    tcgen05 GEMM with the affine terms folded into its epilogue (``alpha`` and the residual input).  ``norm`` may
+    carry a precomputed Frobenius norm (the fused gradient pull produces Σx² on the way)."""
+    x = g.to(BF16)
+    transposed = x.shape[0] > x.shape[1]
+    if transposed:
+        x = x.t().contiguous()
+    if x.shape[1] % 8 != 0 or x.shape[0] % 8 != 0:
+        from ..optim.muon import newton_schulz as ns_ref
+        return ns_ref(g, steps, dtype)
+    nrm = x.float().norm() if norm is None else norm
+    x = (x.float() / (nrm + 1e-7)).to(BF16).contiguous()
+    for _ in range(steps):
+        a = gemm(x, x)                                            # X Xᵀ           (r x r)
+        b = gemm(a, a, alpha=NS_C, residual=(a * NS_B))           # c·A A + b·A   (A is symmetric: A Aᵀ = A A)
+        x = gemm(b, x, b_mn=True, residual=(x * NS_A))            # B X + a·X
+    return (x.t() if transposed else x).to(dtype)
+
+
+# =================================================================================================
 # attention and LSTM sequence
 # =================================================================================================
 def attention(q, k, v, causal):

@@ -64,6 +64,24 @@ class MuonOptimizer(Optimizer):
                 raise ValueError(f"Muon needs tensors with ndim >= 2, got '{name}' with shape {tuple(p.shape)}")
             self.state[name]["momentum"] = torch.zeros_like(p, dtype=torch.float32)
 
+    def _ns(self, device) -> Callable:
+        if self.ns_fn is not newton_schulz:
+            return self.ns_fn
+        if device.type == "cuda":
+            from ..ops import dispatch
+            if dispatch.get_backend() == "auto":
+                from ..ops.native_ops import newton_schulz as native_ns
+                return native_ns
+        return newton_schulz
+
+    def apply_update(self, name: str, p: torch.nn.Parameter, u2d: torch.Tensor) -> None:
+        """``p ← p·(1 − lr·wd) − lr·scale·U`` on the master copy; ``u2d`` is the orthogonalised ``(out, rest)`` update."""
+        w = self._master(name, p)
+        rows, cols = u2d.shape
+        scale = max(1.0, rows / cols) ** 0.5
+        w.mul_(1.0 - self.lr * self.weight_decay).add_(u2d.float().view_as(w), alpha=-self.lr * scale)
+        self._publish(name, p)
+
     @torch.no_grad()
     def step(self) -> None:
         self.step_count += 1
@@ -73,7 +91,7 @@ class MuonOptimizer(Optimizer):
             w = self._master(name, p)
             g2 = p.grad.float().reshape(p.shape[0], -1)
             u = muon_update(g2, self.state[name]["momentum"].view_as(g2), self.momentum, self.nesterov,
-                            self.ns_steps, self.ns_fn)
+                            self.ns_steps, self._ns(p.device))
             w.mul_(1.0 - self.lr * self.weight_decay).add_(u.view_as(w), alpha=-self.lr)
             self._publish(name, p)
 

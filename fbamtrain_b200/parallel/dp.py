@@ -58,6 +58,14 @@ class DataParallel:
             for fs, g in zip(opt.flat_state, opt.groups):
                 if "master" in fs:
                     fs["master"].copy_(g.data.float())
+        for opt in trainer.optimizers.values():       # per-parameter master copies (Muon, SGD)
+            for sub in (opt, getattr(opt, "muon", None)):
+                if sub is None or isinstance(sub, AdamwOptimizer) or not hasattr(sub, "named_params"):
+                    continue
+                for n, p in sub.named_params:
+                    st = sub.state.get(n, {}) if isinstance(sub.state, dict) else {}
+                    if "master" in st:
+                        st["master"].copy_(p.data.float())
         if self.mode == "fused":
             if trainer.device.type != "cuda":
                 raise ValueError("the fused mode needs CUDA peer memory")
@@ -163,14 +171,92 @@ class DataParallel:
                                             group=self.group)
         self._step_non_adamw(trainer)
 
+    # -- Muon over peer memory --------------------------------------------------------------------
+    def _muon_owner_map(self, muon):
+        """Greedy balance of the matrices over the ranks (largest first); identical on every rank."""
+        if getattr(self, "_owners", None) is None:
+            self._owners = {}
+        key = id(muon)
+        if key not in self._owners:
+            load = [0] * self.world_size
+            owners = {}
+            for name, p in sorted(muon.named_params, key=lambda np_: -np_[1].numel()):
+                r = min(range(self.world_size), key=lambda i: (load[i], i))
+                owners[name] = r
+                load[r] += p.numel()
+            self._owners[key] = owners
+        return self._owners[key]
+
+    def _fused_muon(self, trainer, muon, groups) -> None:
+        """Muon under data parallelism without NCCL: the owner of each matrix pulls and sums all peers' gradients
+        for it (fused with the momentum update, the bf16 cast and Σx²), orthogonalises it with Newton–Schulz on
+        the tensor-core GEMM, updates its master copy and pushes the new parameter into every peer's window."""
+        from ..ops import native as nv
+        from ..ops.native_ops import newton_schulz as native_ns
+        dev = trainer.device
+        owners = self._muon_owner_map(muon)
+        by_param = {}
+        for g in groups:
+            for n, p in g.named_params:
+                by_param[n] = (g, g.offsets[n])
+        muon.step_count += 1
+        flags = self.peers.flags.c_ptrs
+        status = nv.ptr(nv.status_word(dev))
+
+        def barrier(slot):
+            nv.check(nv.lib().fbam_peer_barrier(flags, self.rank, self.world_size, slot,
+                                                C.c_uint(self.peers.next_epoch()), C.c_uint(self.spin_limit), status,
+                                                nv.stream_ptr()), "fbam_peer_barrier")
+
+        barrier(6)                                   # every rank's gradients are complete
+        for name, p in muon.named_params:
+            if owners[name] != self.rank:
+                continue
+            g, off = by_param[name]
+            wg, wp = self._windows[g.name]
+            n = p.numel()
+            is_bf16 = g.dtype == torch.bfloat16
+            esize = 2 if is_bf16 else 4
+            if (not is_bf16 and g.dtype != torch.float32) or n % (16 // esize) != 0:
+                raise ValueError(f"fused Muon needs bf16/fp32 matrices whose size is a multiple of 16 bytes ('{name}')")
+            buf = muon.state[name]["momentum"].view(-1)
+            u = torch.empty(n, dtype=torch.bfloat16, device=dev)
+            sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+            nv.check(nv.lib().fbam_reduce_pull(wg.c_ptrs, nv.ptr(buf), nv.ptr(u), nv.ptr(sumsq), C.c_longlong(off),
+                                               C.c_longlong(off + n), int(is_bf16), C.c_float(muon.momentum),
+                                               int(muon.nesterov), C.c_float(1.0), self.world_size, nv.stream_ptr()),
+                     "fbam_reduce_pull")
+            u2 = native_ns(u.view(p.shape[0], -1), muon.ns_steps, norm=sumsq.sqrt())
+            muon.apply_update(name, p, u2)          # writes the local window (p.data is a view of it)
+            lo_b = off * esize
+            nv.check(nv.lib().fbam_push_shard(wp.c_ptrs, flags, C.c_longlong(lo_b), C.c_longlong(lo_b + n * esize),
+                                              self.rank, self.world_size, 7, C.c_uint(self.peers.next_epoch()),
+                                              nv.ptr(self.peers.arrive[2:]), nv.stream_ptr()), "fbam_push_shard")
+            self.stats["bytes_reduced"] += n * esize
+        barrier(8)                                   # all pushes have landed everywhere
+
     def _step_non_adamw(self, trainer) -> None:
-        """Optimizers without a sharded form (SGD, Muon matrices): all-reduce their buckets, step replicated."""
+        """Optimizers without a sharded form (SGD, Muon matrices): all-reduce their buckets, step replicated —
+        except Muon in the fused mode, which runs matrix-parallel over peer memory."""
         handled = {id(g) for opt in self._adamw_optimizers(trainer) for g in opt.groups}
+        if self.mode == "fused":
+            for scope, opt in trainer.optimizers.items():
+                if hasattr(opt, "muon") and opt.muon.named_params:
+                    groups = [g for g in trainer.groups[scope] if id(g) not in handled]
+                    opt.step_count += 1
+                    self._fused_muon(trainer, opt.muon, groups)
+                    handled.update(id(g) for g in groups)
+                    if not (isinstance(opt.adam, AdamwOptimizer) and opt.adam.groups is not None):
+                        opt.adam.step()
+            if all(id(g) in handled for g in trainer.all_groups()):
+                return
         for g in trainer.all_groups():
             if id(g) not in handled:
                 dist.all_reduce(g.grad, group=self.group)
         for opt in trainer.optimizers.values():
             if isinstance(opt, AdamwOptimizer):
+                continue
+            if hasattr(opt, "muon") and self.mode == "fused":
                 continue
             if hasattr(opt, "muon"):
                 opt.step_count += 1
@@ -251,3 +337,10 @@ class DataParallel:
                 per = g.numel // self.world_size
                 for t in fs.values():
                     dist.all_gather_into_tensor(t, t[self.rank * per:(self.rank + 1) * per].clone(), group=self.group)
+        if self.mode == "fused":
+            for opt in trainer.optimizers.values():
+                if hasattr(opt, "muon"):
+                    owners = self._muon_owner_map(opt.muon)
+                    for name, _ in opt.muon.named_params:
+                        for t in opt.muon.state[name].values():
+                            dist.broadcast(t, src=self._global(owners[name]), group=self.group)

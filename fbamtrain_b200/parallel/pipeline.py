@@ -1,0 +1,189 @@
+"""Two-stage pipeline: frame head on the first group of ranks, action model on the second.
+
+The reference's closest mode is *frame-head parallel*: workers own positions of the sequence, run the frame head
+for them and ``ncclSend`` the embeddings to a recurrence master, which sends the upstream gradients back
+(rotating buffers + events on a communication stream; reference: ``src/main.cpp:3119-3123, 3204-3273,
+3368-3414``).  Here the same idea is a micro-batched 1F1B pipeline:
+
+* stage 0 ranks split every micro-batch's frames among themselves (contiguous slices), run the frame head and
+  send their slice of the ``(frames, n_embed)`` embeddings to their partner rank of stage 1;
+* stage 1 ranks all-gather the slices inside their tensor-parallel group, run the action model — LSTM
+  replicated, attention/MLP blocks tensor-parallel over token rows, LM head + loss on the local rows —
+  back-propagate, and return the matching slice of the embedding gradient;
+* stage 0 back-propagates a micro-batch as soon as its gradient arrives, always keeping the next forward in
+  flight first (1F1B), with sends and receives on their own stream so they overlap the convolutions.
+
+Point-to-point traffic is NCCL (``isend`` / ``irecv``; gloo on CPU ranks).  Gradients of parameters that are
+replicated inside a stage are all-reduced over that stage's group at the end of the step.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from .. import ops
+from ..models import FbamModel
+from .tensor_parallel import TensorParallelBlock, TpContext, sync_replicated_grads
+
+
+@dataclass
+class PipelineLayout:
+    frame_ranks: List[int]
+    action_ranks: List[int]
+
+    @staticmethod
+    def even_split(world: int) -> "PipelineLayout":
+        if world % 2:
+            raise ValueError("the two-stage pipeline needs an even number of ranks")
+        half = world // 2
+        return PipelineLayout(list(range(half)), list(range(half, world)))
+
+
+class TensorParallelActionModel(nn.Module):
+    """The action model of one pipeline stage: replicated LSTM, tensor-parallel blocks, row-sharded head/loss."""
+
+    def __init__(self, model: FbamModel, tp: TpContext, batch: int, seq: int):
+        super().__init__()
+        am = model.action_model
+        self.tp, self.batch, self.seq = tp, batch, seq
+        self.lstm = am.lstm
+        self.blocks = nn.ModuleList([TensorParallelBlock(b, tp, batch, seq) for b in am.block])
+        self.ln_f = am.ln_f
+        self.head_weight = am.head_weight
+        self.vocab = am.vocab
+
+    def replicated_before_shard(self):
+        return list(self.lstm.parameters())
+
+    def replicated_in_shard(self):
+        ps = [p for b in self.blocks for p in b.replicated_parameters()]
+        if self.ln_f is not None:
+            ps += list(self.ln_f.parameters())
+        ps.append(self.head_weight)
+        return ps
+
+    def forward(self, emb: torch.Tensor, targets: torch.Tensor, loss_scale: float) -> torch.Tensor:
+        """``emb`` ``(B, T, E)`` full micro-batch; returns this rank's share of the scaled loss."""
+        tp = self.tp
+        y, _ = self.lstm(emb.transpose(0, 1).contiguous())
+        x = y.transpose(0, 1).reshape(self.batch * self.seq, -1)
+        rows = x.shape[0] // tp.world
+        xs = x[tp.rank * rows:(tp.rank + 1) * rows]
+        for blk in self.blocks:
+            xs = blk(xs)
+        if self.ln_f is not None:
+            xs = self.ln_f(xs)
+        tg = targets.reshape(-1)[tp.rank * rows:(tp.rank + 1) * rows]
+        return ops.lm_head_ce(xs.contiguous(), self.head_weight, tg, self.vocab, loss_scale)
+
+
+class TwoStagePipeline:
+    def __init__(self, model: FbamModel, layout: PipelineLayout, device: torch.device, micro_batches: int,
+                 micro_batch_size: int, seq: int, tp_transport: str = "nccl"):
+        self.model, self.layout, self.device = model, layout, device
+        self.rank = dist.get_rank()
+        self.micro_batches, self.mb_size, self.seq = micro_batches, micro_batch_size, seq
+        if len(layout.frame_ranks) != len(layout.action_ranks):
+            raise ValueError("both stages need the same number of ranks (one partner each)")
+        self.is_frame = self.rank in layout.frame_ranks
+        self.stage_ranks = layout.frame_ranks if self.is_frame else layout.action_ranks
+        self.index = self.stage_ranks.index(self.rank)
+        self.partner = (layout.action_ranks if self.is_frame else layout.frame_ranks)[self.index]
+        # every rank creates both groups (collective), keeps its own
+        g_frame = dist.new_group(layout.frame_ranks)
+        g_action = dist.new_group(layout.action_ranks)
+        self.stage_group = g_frame if self.is_frame else g_action
+        self.n_stage = len(self.stage_ranks)
+        frames = micro_batch_size * seq
+        if frames % self.n_stage:
+            raise ValueError("frames per micro-batch must divide by the ranks of a stage")
+        self.slice_rows = frames // self.n_stage
+        self.comm_stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
+        if not self.is_frame:
+            self.tp = TpContext(self.stage_group, device, tp_transport)
+            self.action = TensorParallelActionModel(model, self.tp, micro_batch_size, seq).to(device)
+        self.stats = {"p2p_bytes": 0}
+
+    # ------------------------------------------------------------------------------------------
+    def parameters_of_stage(self):
+        if self.is_frame:
+            return list(self.model.frame_head.parameters())
+        return list(self.action.parameters())
+
+    def _isend(self, t: torch.Tensor):
+        self.stats["p2p_bytes"] += t.numel() * t.element_size()
+        return dist.isend(t, self.partner)
+
+    def _irecv(self, t: torch.Tensor):
+        return dist.irecv(t, self.partner)
+
+    def run_step(self, cells: Optional[torch.Tensor], targets: Optional[torch.Tensor], loss_scale: float) -> float:
+        """One step over ``micro_batches`` micro-batches.  Stage-0 ranks pass ``cells``
+        ``(micro_batches, mb_size, T, P, 3)``; stage-1 ranks pass ``targets`` ``(micro_batches, mb_size, T)``.
+        Returns this rank's share of the loss (0 on stage 0)."""
+        return self._run_frame(cells) if self.is_frame else self._run_action(targets, loss_scale)
+
+    def _run_frame(self, cells: torch.Tensor) -> float:
+        fh = self.model.frame_head
+        e = self.model.cfg.n_embed
+        dtype = next(p for p in fh.parameters() if p.dim() == 2 and p.dtype != torch.float32).dtype \
+            if any(p.dtype != torch.float32 for p in fh.parameters()) else torch.float32
+        outs, grads, recvs, sends = {}, {}, {}, []
+        lo = self.index * self.slice_rows
+
+        def forward(k):
+            flat = cells[k].reshape(self.mb_size * self.seq, cells.shape[-2], 3)[lo:lo + self.slice_rows]
+            emb = fh(flat.to(self.device))
+            outs[k] = emb
+            payload = emb.detach().contiguous()
+            sends.append((self._isend(payload), payload))
+            grads[k] = torch.empty(self.slice_rows, e, dtype=emb.dtype, device=self.device)
+            recvs[k] = self._irecv(grads[k])
+
+        def backward(k):
+            recvs[k].wait()
+            outs.pop(k).backward(grads.pop(k))
+
+        forward(0)
+        for k in range(1, self.micro_batches):   # 1F1B: next forward first, then the oldest backward
+            forward(k)
+            backward(k - 1)
+        backward(self.micro_batches - 1)
+        for work, _ in sends:
+            work.wait()
+        for p in fh.parameters():                # frame ranks are data parallel over frame slices
+            if p.grad is not None:
+                dist.all_reduce(p.grad, group=self.stage_group)
+        return 0.0
+
+    def _run_action(self, targets: torch.Tensor, loss_scale: float) -> float:
+        e = self.model.cfg.n_embed
+        am = self.action
+        dtype = am.head_weight.dtype
+        total = 0.0
+        sends = []
+        bufs = [torch.empty(self.slice_rows, e, dtype=dtype, device=self.device) for _ in range(2)]
+        recv = self._irecv(bufs[0])
+        for k in range(self.micro_batches):
+            recv.wait()
+            mine = bufs[k % 2]
+            if k + 1 < self.micro_batches:        # rotating buffers: post the next receive before computing
+                recv = self._irecv(bufs[(k + 1) % 2])
+            full = self.tp.all_gather_rows(mine).view(self.mb_size, self.seq, e).requires_grad_(True)
+            loss = am(full, targets[k].to(self.device), loss_scale)
+            loss.backward()
+            total += float(loss.detach())
+            d_emb = full.grad.reshape(self.mb_size * self.seq, e)
+            self.tp.all_reduce(d_emb)             # every TP rank saw only its rows' contribution
+            payload = d_emb[self.index * self.slice_rows:(self.index + 1) * self.slice_rows].contiguous()
+            sends.append((self._isend(payload), payload))
+        for work, _ in sends:
+            work.wait()
+        for p in am.replicated_before_shard() + am.replicated_in_shard():
+            if p.grad is not None:
+                self.tp.all_reduce(p.grad)
+        return total

@@ -45,7 +45,6 @@ class TpContext:
         if transport == "fused":
             from .peer_window import PeerGroup
             self.peers = PeerGroup(group, device)
-            self._side = torch.cuda.Stream(device=device)
 
     # ---------------------------------------------------------------- library collectives
     def all_gather_rows(self, shard: torch.Tensor) -> torch.Tensor:
@@ -88,14 +87,14 @@ class TpContext:
         self._barrier(2)                                   # everyone is done reading the previous contents
         x_full[self.rank * rows:(self.rank + 1) * rows].copy_(x_shard)
         epoch = self.peers.next_epoch()
-        cur = torch.cuda.current_stream()
-        self._side.wait_stream(cur)
-        with torch.cuda.stream(self._side):                # push to the peers beside the GEMM
-            lo = self.rank * rows * k * x_shard.element_size()
-            nv.check(nv.lib().fbam_push_shard(win.c_ptrs, self.peers.flags.c_ptrs, C.c_longlong(lo),
-                                              C.c_longlong(lo + rows * k * x_shard.element_size()), self.rank,
-                                              self.world, 3, C.c_uint(epoch), nv.ptr(self.peers.arrive[1:]),
-                                              nv.stream_ptr()), "fbam_push_shard")
+        # The push runs BEFORE the GEMM on the same stream: a kernel that waits on flags must never share a GPU
+        # with the (not yet scheduled) kernel that raises them.  What overlaps with the math is the arrival of
+        # the OTHER ranks' shards: the GEMM starts with its own rows and waits per tile for remote ones.
+        lo = self.rank * rows * k * x_shard.element_size()
+        nv.check(nv.lib().fbam_push_shard(win.c_ptrs, self.peers.flags.c_ptrs, C.c_longlong(lo),
+                                          C.c_longlong(lo + rows * k * x_shard.element_size()), self.rank,
+                                          self.world, 3, C.c_uint(epoch), nv.ptr(self.peers.arrive[1:]),
+                                          nv.stream_ptr()), "fbam_push_shard")
         from .peer_window import MAX_RANKS
         flags = self.peers.flags.local[3 * MAX_RANKS:4 * MAX_RANKS]
         m_full, n_out = rows * self.world, w.shape[0]
@@ -103,7 +102,6 @@ class TpContext:
         y = no.gemm(x_full, w, bias=bias, act=act, preact_out=preact_out, ready_flags=flags, flag_rows=rows,
                     flag_epoch=epoch, flag_spin_limit=self.spin_limit, bm=tile_rows,
                     tile_m_rotate=(self.rank * rows) // tile_rows)
-        cur.wait_stream(self._side)
         return y, x_full.clone() if x_shard.requires_grad or w.requires_grad else x_full
 
     def gemm_rs(self, h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:

@@ -130,7 +130,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("variant", ["p2p", "multicast"])
+@pytest.mark.parametrize("variant", ["p2p", "multicast", "muon"])
 def test_fused_dp_matches_nccl_zero1_on_two_gpus(tmp_path, variant):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -138,11 +138,18 @@ def test_fused_dp_matches_nccl_zero1_on_two_gpus(tmp_path, variant):
     worker = os.path.join(os.path.dirname(__file__), "workers", "dp_fused_worker.py")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", str(_free_port()), worker, str(out)]
-    if variant == "multicast":
-        cmd.append("multicast")
+    if variant != "p2p":
+        cmd.append(variant)
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, _tail(r)
     assert out.read_text() == "ok"
+
+
+def _tail(r):
+    """The part of a child's output that holds the Python traceback (torchrun appends a long banner after it)."""
+    text = r.stdout + r.stderr
+    i = text.find("Traceback")
+    return text[i:i + 4000] if i >= 0 else text[-4000:]
 
 
 def test_fused_tensor_parallel_block_matches_nccl_on_two_gpus(tmp_path):

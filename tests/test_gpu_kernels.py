@@ -365,3 +365,33 @@ def test_flash_attention_fwd_bwd(causal, b, t, h, d):
     assert_similar(of.to(BF), o, 3e-2)
     for i, name in enumerate(("dq", "dk", "dv")):
         assert _rel_err(gqkv[:, :, i], eqkv[:, :, i]) < 3e-2, (name, _rel_err(gqkv[:, :, i], eqkv[:, :, i]))
+
+
+@pytest.mark.parametrize("shape", [(256, 512), (1024, 256), (64, 64)])
+def test_newton_schulz_on_tensor_cores_matches_reference(shape):
+    nv, no = _nops()
+    from fbamtrain_b200.optim.muon import newton_schulz as ns_ref
+    torch.manual_seed(15)
+    g = torch.randn(*shape, device=DEV)
+    got = no.newton_schulz(g, 5).float()
+    exp = ns_ref(g, 5, torch.float32)
+    nv.check_status(g.device)
+    assert _rel_err(got, exp) < 5e-2
+    s = torch.linalg.svdvals(got)
+    assert float(s.min()) > 0.4 and float(s.max()) < 1.4
+
+
+def test_muon_training_step_native():
+    from fbamtrain_b200 import RunConfiguration, Trainer, presets
+    from fbamtrain_b200.data import SyntheticBatchSource
+    d = presets.tiny("bf16")
+    d["model_config"].update({"cell_embed_dim": 64, "downsample_channels": [64], "n_embed": 64})
+    d["optimizer"]["type"] = "muon"
+    d["optimizer"]["learning_rate"] = 2e-3
+    cfg = RunConfiguration.from_json(d)
+    tr = Trainer(cfg, device=torch.device(DEV))
+    src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=1, pin=False)
+    cells, tg = src.next_batch(2, 16)
+    losses = [float(tr.train_step(cells, tg)) for _ in range(8)]
+    tr.close()
+    assert losses[-1] < losses[0], losses

@@ -1,0 +1,83 @@
+"""Two-stage pipeline (2 frame-head ranks → 2 action-model ranks with 2-way tensor parallelism) on CPU ranks,
+against the same model trained in one process."""
+import os
+import socket
+
+import torch
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _setup():
+    from fbamtrain_b200 import RunConfiguration, presets
+    from fbamtrain_b200.data import SyntheticBatchSource
+    from fbamtrain_b200.models import FbamModel
+    d = presets.tiny()
+    d["model_config"].update({"action_heads": 2, "lstm_layers": 1})
+    cfg = RunConfiguration.from_json(d)
+    model = FbamModel(cfg.model_config, 32)
+    src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=9, pin=False)
+    micro_batches, mb, seq = 3, 2, 16
+    cells, targets = src.next_batch(micro_batches * mb, seq)
+    return cfg, model, cells.view(micro_batches, mb, seq, -1, 3), targets.view(micro_batches, mb, seq), (micro_batches, mb, seq)
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from fbamtrain_b200.parallel.pipeline import PipelineLayout, TwoStagePipeline
+    cfg, model, cells, targets, (nmb, mb, seq) = _setup()
+    pipe = TwoStagePipeline(model, PipelineLayout.even_split(world), torch.device("cpu"), nmb, mb, seq)
+    scale = 1.0 / (seq * nmb * mb)
+    loss = pipe.run_step(cells, targets, scale)
+    out = {"loss": loss, "frame": pipe.is_frame, "index": pipe.index}
+    if pipe.is_frame:
+        out["grads"] = {n: p.grad.clone() for n, p in model.frame_head.named_parameters()}
+    else:
+        out["grads"] = {"lstm." + n: p.grad.clone() for n, p in pipe.action.lstm.named_parameters()}
+        out["grads"]["head"] = pipe.action.head_weight.grad.clone()
+        out["grads"]["blk0.w_fc1"] = pipe.action.blocks[0].w_fc1.grad.clone()
+        out["grads"]["blk0.ln1"] = pipe.action.blocks[0].ln1_weight.grad.clone()
+    q.put((rank, out))
+    dist.destroy_process_group()
+
+
+def test_pipeline_matches_single_process():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 4, port, q)) for r in range(4)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=180) for _ in range(4))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    cfg, model, cells, targets, (nmb, mb, seq) = _setup()
+    scale = 1.0 / (seq * nmb * mb)
+    total = 0.0
+    for k in range(nmb):
+        loss = model(cells[k], targets[k], scale)
+        loss.backward()
+        total += float(loss)
+    assert abs(results[2]["loss"] + results[3]["loss"] - total) < 1e-5
+    ref_fh = {n: p.grad for n, p in model.frame_head.named_parameters()}
+    for r in (0, 1):
+        for n, g in results[r]["grads"].items():
+            assert torch.allclose(g, ref_fh[n], atol=2e-6), (r, n)
+    am = model.action_model
+    for r in (2, 3):
+        g = results[r]["grads"]
+        for n, p in am.lstm.named_parameters():
+            assert torch.allclose(g["lstm." + n], p.grad, atol=2e-6), (r, n)
+        assert torch.allclose(g["head"], am.head_weight.grad, atol=2e-6)
+        assert torch.allclose(g["blk0.ln1"], am.block[0].ln1.weight.grad, atol=2e-6)
+        fl = am.block[0].mlp.fc1.weight.shape[0] // 2
+        i = results[r]["index"]
+        assert torch.allclose(g["blk0.w_fc1"], am.block[0].mlp.fc1.weight.grad[i * fl:(i + 1) * fl], atol=2e-6)

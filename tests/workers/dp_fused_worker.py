@@ -13,7 +13,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 
 
-def main(out_path: str, multicast: bool) -> None:
+def main(out_path: str, multicast: bool, optimizer: str = "adamw") -> None:
     from fbamtrain_b200 import RunConfiguration, Trainer, presets
     from fbamtrain_b200.data import SyntheticBatchSource
     from fbamtrain_b200.ops import native
@@ -26,6 +26,7 @@ def main(out_path: str, multicast: bool) -> None:
     d = presets.tiny("bf16")
     d["model_config"].update({"cell_embed_dim": 64, "downsample_channels": [64], "n_embed": 64})
     d["micro_batch_size"], d["total_batch_size"] = 2, 2 * world
+    d["optimizer"]["type"] = optimizer
     cfg = RunConfiguration.from_json(d)
     src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=100 + rank, pin=False)
     batches = [src.next_batch(2, cfg.train_sequence_length) for _ in range(3)]
@@ -64,4 +65,4 @@ def main(out_path: str, multicast: bool) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1], len(sys.argv) > 2 and sys.argv[2] == "multicast")
+    main(sys.argv[1], "multicast" in sys.argv[2:], "muon" if "muon" in sys.argv[2:] else "adamw")
