@@ -1,0 +1,112 @@
+"""The C++ host runtime against the Python implementations of the same components."""
+import json
+import os
+import socket
+import threading
+
+import numpy as np
+import pytest
+import torch
+
+from fbamtrain_b200 import runtime as rt
+from fbamtrain_b200.rng import SplitMix64
+from fbamtrain_b200.tokenizer import Tokenizer
+from fbamtrain_b200.utils import safetensors_io as st
+
+
+def test_native_rng_matches_python_and_draws_batches():
+    a, b = rt.NativeSplitMix64(42), SplitMix64(42)
+    assert [a.randu64() for _ in range(5)] == [b.randu64() for _ in range(5)]
+    assert [a.randint(3, 1000) for _ in range(5)] == [b.randint(3, 1000) for _ in range(5)]
+    assert a.state == b.state
+    totals = [40, 47, 54]
+    idx, start = a.draw_batch(totals, 16, 6)
+    exp_i, exp_s = [], []
+    for _ in range(6):
+        i = b.randint(0, 3)
+        exp_i.append(i)
+        exp_s.append(b.randint(0, max(0, totals[i] - 16) + 1))
+    assert (idx, start) == (exp_i, exp_s) and a.state == b.state
+
+
+def test_native_tokenizer_matches_python(tmp_path):
+    toks = ["a", "ab", "abc", "\x1b[A", "é", "日本", "b", "\U0001F600x", "\"q\\", "\n"]
+    path = str(tmp_path / "tok.txt")
+    with open(path, "w", encoding="utf-8") as f:
+        f.write("# FBAM_TOK v1.0\n")
+        for t in toks:
+            f.write(json.dumps(t) + "\n")        # ensure_ascii: exercises \\uXXXX and surrogate pairs
+        f.write("\n")
+    py, nat = Tokenizer.from_file(path), rt.NativeTokenizer(path)
+    assert len(nat) == len(py)
+    assert [nat.token(i) for i in range(len(nat))] == py.tokens
+    text = "abcabé日本zz\x1b[Ab\U0001F600x\"q\\\n"
+    assert nat.encode_longest_match(text) == py.encode_longest_match(text)
+    with open(path, "w") as f:
+        f.write("# nope\n")
+    with pytest.raises(ValueError, match="header"):
+        rt.NativeTokenizer(path)
+
+
+def test_reference_tokenizer_file_natively_if_present():
+    path = "/root/reference/working_dir/tokenizer.txt"
+    if not os.path.exists(path):
+        pytest.skip("reference tree not mounted")
+    nat, py = rt.NativeTokenizer(path), Tokenizer.from_file(path)
+    assert len(nat) == len(py) == 20351
+    for i in (0, 1, 100, 5000, 20350):
+        assert nat.token(i) == py.tokens[i]
+
+
+def test_native_safetensors_interop_and_tenscmp(tmp_path):
+    tensors = {"w": torch.randn(5, 7), "h": torch.randn(3, 2).bfloat16(), "s": torch.tensor([9], dtype=torch.uint64),
+               "e": torch.zeros(0, dtype=torch.uint32)}
+    p1 = str(tmp_path / "py.safetensors")
+    st.save_file(tensors, p1)
+    got = rt.st_read(p1)                                    # native reader on a Python-written file
+    assert set(got) == set(tensors)
+    assert got["w"][0] == "F32" and np.array_equal(got["w"][1], tensors["w"].numpy())
+    assert got["h"][0] == "BF16" and np.array_equal(got["h"][1], tensors["h"].view(torch.int16).numpy().view(np.uint16))
+    p2 = str(tmp_path / "native.safetensors")
+    rt.st_write(p2, got)                                    # native writer, Python reader
+    back = st.load_file(p2)
+    for k, v in tensors.items():
+        assert back[k].dtype == v.dtype and torch.equal(back[k].view(torch.uint8), v.view(torch.uint8))
+    bad, report = rt.tenscmp(p1, p2, 0.0)
+    assert bad == 0 and report == ""
+    tensors["w"] = tensors["w"] + 0.5
+    del tensors["e"]
+    st.save_file(tensors, p1)
+    bad, report = rt.tenscmp(p1, p2, 0.3)
+    assert bad == 2 and "w: max |a-b|" in report and "missing in first file" in report
+    assert rt.tenscmp(p1, p2, 0.6)[0] == 1
+
+
+def test_native_cursor_writer(tmp_path):
+    path = str(tmp_path / "c" / "cursor.json")
+    c = rt.NativeCursorCommitter(path)
+    for s in range(50):
+        c.commit(s, 2 ** 63 + s, 8, 1024)
+    assert c.flush()
+    c.close()
+    d = json.load(open(path))
+    assert d == {"version": 1, "step_count": 49, "rng_state": 2 ** 63 + 49, "batch_size": 8, "sequence_length": 1024}
+    from fbamtrain_b200.data import DatasetCursorCommitter
+    assert DatasetCursorCommitter.load(path).step_count == 49          # the Python loader reads the native file
+
+
+def test_native_rendezvous_and_interop_with_python():
+    from fbamtrain_b200.parallel import rendezvous as rdv
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    blob = bytes(range(128))
+    out = {}
+    th = threading.Thread(target=lambda: rt.rdv_serve("127.0.0.1", port, 3, blob, 20))
+    th.start()
+    t2 = threading.Thread(target=lambda: out.__setitem__("py", rdv.fetch_blob("127.0.0.1", port, 2)))
+    t2.start()
+    out["native"] = rt.rdv_fetch("127.0.0.1", port, 1)
+    t2.join(20)
+    th.join(20)
+    assert out["native"] == blob and out["py"] == blob
