@@ -42,6 +42,7 @@ class DataParallel:
         self.world_size = dist.get_world_size(group)
         self.use_multicast, self.overlap, self.spin_limit = use_multicast, overlap, spin_limit
         self.peers = None
+        self.grad_scale = 1.0
         self._windows: Dict[str, tuple] = {}
         self._side = None
         self.stats = {"bytes_reduced": 0}
@@ -89,6 +90,16 @@ class DataParallel:
             for p in self._am_params:
                 p.register_post_accumulate_grad_hook(_hook)
 
+    def attach_windows_only(self, trainer) -> None:
+        """For callers that synchronise the parameters themselves (fault-tolerant DP): set up the peer windows
+        and the early-start hooks without the initial broadcast."""
+        if trainer.device.type != "cuda":
+            raise ValueError("the fused mode needs CUDA peer memory")
+        self._build_windows(trainer)
+        self._side = torch.cuda.Stream(device=trainer.device)
+        self._am_params = [p for _, p in trainer.model.action_model.named_parameters() if p.requires_grad]
+        self._pending, self._armed, self.overlap = 0, False, False
+
     def _global(self, rank_in_group: int) -> int:
         return rank_in_group if self.group is None else dist.get_global_rank(self.group, rank_in_group)
 
@@ -127,6 +138,11 @@ class DataParallel:
         self.rank = dist.get_rank(group)
         self.world_size = dist.get_world_size(group)
         if self.mode == "fused":
+            # buckets are padded to the NOMINAL world; with fewer ranks the slice size must still divide
+            for g in trainer.all_groups():
+                if g.numel % self.world_size != 0:
+                    raise ValueError(f"bucket '{g.name}' ({g.numel} elements) does not divide by world size "
+                                     f"{self.world_size}; pad buckets to the least common multiple")
             saved = {g.name: g.data.clone() for g in trainer.all_groups()}
             self.peers.rebuild(group)
             self._build_windows(trainer)
@@ -282,7 +298,8 @@ class DataParallel:
             C.c_void_p(wg.multicast_ptr), C.c_void_p(wp.multicast_ptr),
             nv.ptr(fs["m"]), nv.ptr(fs["v"]), nv.ptr(master), C.c_longlong(lo), C.c_longlong(hi), int(is_bf16),
             C.c_float(opt.lr), C.c_float(opt.beta1), C.c_float(opt.beta2), C.c_float(opt.eps),
-            C.c_float(opt.weight_decay), C.c_float(bc1), C.c_float(bc2), C.c_float(1.0), self.rank, self.world_size,
+            C.c_float(opt.weight_decay), C.c_float(bc1), C.c_float(bc2), C.c_float(self.grad_scale), self.rank,
+            self.world_size,
             C.c_uint(epoch), 1, C.c_uint(self.spin_limit), nv.ptr(nv.status_word(device)), nv.ptr(self.peers.arrive),
             0, nv.stream_ptr())
         nv.check(code, "fbam_rs_adamw_ag")

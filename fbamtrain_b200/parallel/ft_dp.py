@@ -1,0 +1,156 @@
+"""Fault-tolerant data parallelism: the training-side protocol on top of :mod:`.ftccl`.
+
+Protocol of the reference trainer with ``transport: "ftccl"`` (reference: ``src/main.cpp:266-320, 350-478,
+2955-2984, 3672-3767``):
+
+* *collective phase gate* before every reduction: if peers wait to be admitted, or the world is smaller than it
+  should be, update the topology (admits joiners, drops the dead);
+* *shared state* = every parameter and optimizer tensor, with revision = training step; after a topology change
+  everybody synchronises it (joiners receive it — this is how a restarted rank catches up without a checkpoint);
+* gradients are all-reduced with retry; if too few peers remain the step is *dropped*: no optimizer update, the
+  loss slot is discarded, state is re-synchronised at the old revision;
+* after a committed step the revision is incremented.
+
+Here a topology change also re-creates the process group of the new epoch and, for the ``fused`` reduction,
+re-allocates the peer-memory windows and re-points the parameter / gradient buckets at them.  Failures are noticed
+on the host (heartbeats at the master, exceptions from collectives) *between* steps; device-side waits are bounded.
+When the world is smaller than ``expected_world`` the summed gradient is scaled by ``expected / actual`` so the
+update keeps the magnitude of the full-batch mean.
+"""
+from __future__ import annotations
+
+import time
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..utils.logging import LOG
+from .dp import DataParallel
+from .ftccl import FtPeer, Result, SharedStateSyncStrategy, TensorInfo
+
+
+class FaultTolerantDataParallel:
+    def __init__(self, peer: FtPeer, expected_world: int, min_world: int = 1, mode: str = "allreduce",
+                 wait_for_full_world: bool = False):
+        if mode not in ("allreduce", "fused"):
+            raise ValueError("mode must be allreduce or fused")
+        self.peer, self.expected_world, self.min_world, self.mode = peer, expected_world, min_world, mode
+        self.wait_for_full_world = wait_for_full_world
+        self.inner: Optional[DataParallel] = None
+        self.events: List[dict] = []          # topology changes with timestamps (recovery-time accounting)
+        self.tx_bytes = self.rx_bytes = 0
+        self.dropped_steps = 0
+
+    # the trainer reads these
+    @property
+    def rank(self) -> int:
+        return self.peer.rank
+
+    @property
+    def world_size(self) -> int:
+        # batch arithmetic (total_batch / micro / world) is defined by the nominal world
+        return self.expected_world
+
+    # ------------------------------------------------------------------------------------------
+    def _shared_state(self, trainer) -> List[TensorInfo]:
+        infos = [TensorInfo("group/" + g.name, g.data) for g in trainer.all_groups()]
+        for opt in trainer.optimizers.values():
+            for name, t in sorted(opt.state_tensors().items()):
+                if name.endswith("__optimizer/step"):
+                    continue
+                infos.append(TensorInfo(name, t))
+        return infos
+
+    def _sync_state(self, trainer, joining: bool = False) -> bool:
+        strategy = SharedStateSyncStrategy.RECEIVE_ONLY if joining else SharedStateSyncStrategy.ENFORCE_POPULAR
+        res, info = self.peer.synchronize_shared_state(trainer.step_count, self._shared_state(trainer), strategy)
+        if res != Result.SUCCESS:
+            return False
+        self.tx_bytes += info.tx_bytes
+        self.rx_bytes += info.rx_bytes
+        if info.revision != trainer.step_count:
+            LOG("INFO", f"ftccl: adopting shared-state revision {info.revision} (was {trainer.step_count})")
+            trainer.step_count = info.revision
+            for opt in trainer.optimizers.values():
+                opt.set_step(info.revision)
+        for opt in trainer.optimizers.values():      # masters of 16-bit parameters follow the synchronised copies
+            pass
+        return True
+
+    def _retopologize(self, trainer, joining: bool = False) -> bool:
+        t0 = time.perf_counter()
+        for _ in range(50):
+            res = self.peer.update_topology(min_world=self.min_world)
+            if res == Result.SUCCESS:
+                break
+            time.sleep(0.1)       # the reference retries every 100 ms on UpdateTopologyFailed
+        else:
+            return False
+        if self.mode == "fused":
+            if self.inner is None:
+                self.inner = DataParallel(mode="fused", group=None)
+                self.inner.attach_windows_only(trainer)
+            else:
+                self.inner.rebuild(trainer, None)
+        ok = self._sync_state(trainer, joining)
+        self.events.append({"epoch": self.peer.epoch, "world": self.peer.world_size, "step": trainer.step_count,
+                            "seconds": time.perf_counter() - t0})
+        return ok
+
+    def attach(self, trainer) -> None:
+        joining = trainer.step_count == 0 and self.peer.epoch == 0 and getattr(self, "late_joiner", False)
+        if not self._retopologize(trainer, joining):
+            raise RuntimeError("ftccl: could not join the training group")
+
+    def arm(self) -> None:
+        if self.inner is not None:
+            self.inner.arm()
+
+    # ------------------------------------------------------------------------------------------
+    def reduce_and_step(self, trainer) -> bool:
+        peer = self.peer
+        # collective phase gate (host side, between kernels)
+        if peer.membership_changed() or peer.are_peers_pending() or peer.world_size < self.expected_world:
+            if peer.membership_changed() or peer.are_peers_pending():
+                if not self._retopologize(trainer):
+                    return self._drop(trainer, "topology update failed")
+            while self.wait_for_full_world and peer.world_size < self.expected_world:
+                time.sleep(1.0)   # "not ready": the reference spins until the expected world is present
+                if peer.are_peers_pending() and not self._retopologize(trainer):
+                    return self._drop(trainer, "topology update failed")
+        if peer.world_size < self.min_world:
+            return self._drop(trainer, "too few peers")
+        scale = self.expected_world / max(1, peer.world_size)
+        if self.mode == "fused" and peer.world_size > 1:
+            self.inner.grad_scale = scale
+            self.inner.reduce_and_step(trainer)
+        else:
+            grads = [g.grad for g in trainer.all_groups()]
+            if peer.world_size > 1:
+                res, info = peer.all_reduce_multiple_with_retry(grads, [(trainer.step_count << 8) | k
+                                                                        for k in range(len(grads))],
+                                                                min_world=self.min_world)
+                self.tx_bytes += info.tx_bytes
+                self.rx_bytes += info.rx_bytes
+                if res != Result.SUCCESS:
+                    return self._drop(trainer, res.name)
+                scale = self.expected_world / max(1, peer.world_size)
+            if scale != 1.0:
+                for g in grads:
+                    g.mul_(scale)
+            trainer.optimizers["action_model"].step()
+            trainer.optimizers["frame_head"].step()
+        return True
+
+    def _drop(self, trainer, why: str) -> bool:
+        """No update for this step; peers re-synchronise at the old revision."""
+        LOG("WARN", f"ftccl: dropping step {trainer.step_count}: {why}")
+        self.dropped_steps += 1
+        if self.peer.world_size > 1:
+            self._sync_state(trainer)
+        return False
+
+    def gather_optimizer_state(self, trainer) -> None:
+        if self.inner is not None:
+            self.inner.gather_optimizer_state(trainer)

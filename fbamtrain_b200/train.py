@@ -67,7 +67,10 @@ class Trainer:
         self.frame_chunk = frame_chunk
 
         # flat parameter / gradient buffers, grouped by scope, optimizer kind and dtype
-        shard_multiple = self.world
+        # buckets divide evenly by every world size up to the nominal one, so the sharded / fused update keeps
+        # working after ranks have left (fault-tolerant data parallelism)
+        import math
+        shard_multiple = math.lcm(*range(1, self.world + 1)) if self.world > 1 else 1
         self.groups: Dict[str, List[FlatGroup]] = {}
         self.optimizers: Dict[str, Optimizer] = {}
         for scope, module in (("frame_head", self.model.frame_head), ("action_model", self.model.action_model)):
@@ -95,10 +98,10 @@ class Trainer:
             else:
                 self.groups[scope] = build_groups(scope, named, shard_multiple)
                 self.optimizers[scope] = create_optimizer(ocfg, named, prefix)
+        self.step_count = 0
         if self.dp is not None:
             self.dp.attach(self)
 
-        self.step_count = 0
         self.ring = LossRingBuffer(self.device)
         self.logger = AsyncStepLogger(self.ring)
         self.ckpt = CheckpointManager(os.path.join(working_dir, cfg.checkpointing.checkpoint_directory),

@@ -1,0 +1,74 @@
+"""Trainer under fault-tolerant data parallelism on CPU ranks: a peer falls silent between steps, the others go
+on; a fresh peer joins later, receives parameters + optimizer state and continues in lock-step."""
+import os
+import time
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from fbamtrain_b200.parallel.ftccl import MembershipMaster
+
+
+def _worker(idx, port, q, total_steps):
+    from fbamtrain_b200 import RunConfiguration, Trainer, presets
+    from fbamtrain_b200.data import SyntheticBatchSource
+    from fbamtrain_b200.parallel.ft_dp import FaultTolerantDataParallel
+    from fbamtrain_b200.parallel.ftccl import FtPeer, Result
+    torch.manual_seed(0)
+    d = presets.tiny()
+    d["micro_batch_size"], d["total_batch_size"] = 1, 3
+    d["optimizer"]["learning_rate"] = 1e-3
+    cfg = RunConfiguration.from_json(d)
+    late = idx == 3
+    if late:
+        time.sleep(4.0)
+    peer = FtPeer("127.0.0.1", port, torch.device("cpu"), heartbeat_interval_s=0.1, collective_timeout_s=20.0)
+    assert peer.connect() == Result.SUCCESS
+    ft = FaultTolerantDataParallel(peer, expected_world=3, min_world=2 if not late else 2)
+    ft.late_joiner = late
+    if not late:
+        ft.min_world = 3                      # the founding members start together
+    tr = Trainer(cfg, device=torch.device("cpu"), dp=ft)
+    ft.min_world = 2
+    src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=50 + idx, pin=False)
+    losses = {}
+    while tr.step_count < total_steps:
+        if idx == 2 and tr.step_count == 3:
+            peer.inject_failure()             # silent failure between steps
+            q.put(("died", idx, tr.step_count, None, None))
+            tr.close()
+            return
+        cells, tg = src.next_batch(1, cfg.train_sequence_length)
+        step_before = tr.step_count
+        loss = float(tr.train_step(cells, tg))
+        if tr.step_count > step_before:
+            losses[step_before] = loss
+        time.sleep(0.2)
+    params = torch.cat([p.detach().reshape(-1) for p in tr.model.parameters()])
+    q.put(("done", idx, tr.step_count, params, {"events": ft.events, "dropped": ft.dropped_steps,
+                                                "first_step": min(losses), "rx": ft.rx_bytes}))
+    peer.leave()
+    tr.close()
+
+
+def test_trainer_survives_peer_loss_and_admits_joiner():
+    master = MembershipMaster(heartbeat_timeout_s=0.8).start()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(i, master.port, q, 14)) for i in range(4)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in range(4)]
+    for p in procs:
+        p.join(60)
+    master.interrupt()
+    done = sorted((r for r in results if r[0] == "done"), key=lambda r: r[1])
+    assert [r[1] for r in done] == [0, 1, 3] and len([r for r in results if r[0] == "died"]) == 1
+    assert all(r[2] == 14 for r in done)
+    for r in done[1:]:                                            # identical parameters everywhere
+        assert torch.equal(r[3], done[0][3])
+    joiner = done[2][4]
+    assert joiner["first_step"] >= 1 and joiner["rx"] > 0         # joined mid-run and received the state
+    assert len(done[0][4]["events"]) >= 3                         # start, shrink to two, grow to three
+    assert done[0][4]["events"][-1]["world"] == 3
