@@ -1,0 +1,154 @@
+"""Command-line trainer: ``python -m fbamtrain_b200.cli -c run.json [--parallel-config p.json ...]``.
+
+Flags follow the reference binary (reference: ``src/main.cpp:970-1003``): ``-c/--config``,
+``--parallel-config``, ``--master``, ``--worker_id``, ``--world-size``, ``--ddp-world-size``,
+``--validation-dump``, ``--validation-dump-file``, ``--validation-dump-steps``, ``-v``.  Additions:
+``--synthetic`` (seeded synthetic frames instead of recordings), ``--steps`` (stop early),
+``--ftccl-master`` (run the membership master of the fault-tolerant transport and nothing else),
+``--device``.
+
+Role resolution: with a parallel configuration whose ``ddp_parallel.use_ddp_parallel`` is true, ``--worker_id``
+is the data-parallel rank and ``--ddp-world-size`` the world size; transport ``ccl`` rendezvouses at
+``ccl_rendezvous`` and reduces gradients as ``grad_reduce`` says (all-reduce, ZeRO-1 or the fused peer-memory
+kernels); transport ``ftccl`` joins the membership master at ``ftccl_master``.  ``frame_head_parallel`` maps to
+the two-stage pipeline over ``--world-size`` ranks.  Under ``torch.distributed.run`` the RANK / WORLD_SIZE
+environment takes the place of the flags.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import time
+
+import torch
+
+from .config import ParallelConfiguration, RunConfiguration
+from .utils.logging import LOG
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="fbamtrain", description="Train a frame-based action model.")
+    ap.add_argument("-c", "--config", required=False, help="run configuration JSON")
+    ap.add_argument("--parallel-config", default=None)
+    ap.add_argument("--master", action="store_true", help="this process is the recurrence master (pipeline stage 1)")
+    ap.add_argument("--worker_id", "--worker-id", type=int, default=None)
+    ap.add_argument("--world-size", type=int, default=1)
+    ap.add_argument("--ddp-world-size", type=int, default=1)
+    ap.add_argument("--validation-dump", action="store_true")
+    ap.add_argument("--validation-dump-file", default="validation_dump.safetensors")
+    ap.add_argument("--validation-dump-steps", type=int, default=1)
+    ap.add_argument("-v", "--verbose", action="store_true")
+    ap.add_argument("--synthetic", action="store_true")
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--device", default=None)
+    ap.add_argument("--frame-chunk", type=int, default=1024)
+    ap.add_argument("--ftccl-master", action="store_true")
+    return ap
+
+
+def _run_ftccl_master(par: ParallelConfiguration) -> int:
+    from .parallel.ftccl import MembershipMaster
+    ep = par.ddp_parallel.ftccl_master
+    if ep is None:
+        LOG("FATAL", "--ftccl-master needs ddp_parallel.transport = \"ftccl\" with an ftccl_master endpoint")
+    master = MembershipMaster(ep.ip, ep.port)
+    LOG("INFO", f"ftccl master listening on {ep.ip}:{master.port}")
+    try:
+        master.run()
+    except KeyboardInterrupt:
+        master.interrupt()
+    return 0
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    if args.verbose:
+        os.environ["FBAMTRAIN_LOG_LEVEL"] = "INFO"
+    par = None
+    if args.parallel_config:
+        par = ParallelConfiguration.from_json_file(args.parallel_config)
+        if par is None:
+            LOG("FATAL", f"parallel configuration {args.parallel_config} not found")
+    if args.ftccl_master:
+        if par is None:
+            LOG("FATAL", "--ftccl-master needs --parallel-config")
+        return _run_ftccl_master(par)
+    if not args.config:
+        LOG("FATAL", "a run configuration is required (-c)")
+    cfg = RunConfiguration.from_json_file(args.config)
+    if cfg is None:
+        LOG("FATAL", f"run configuration {args.config} not found")
+    working_dir = os.path.dirname(os.path.abspath(args.config))
+
+    from .train import Trainer, run_training
+    env_rank, env_world = os.environ.get("RANK"), os.environ.get("WORLD_SIZE")
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.device:
+        device = torch.device(args.device)
+    elif torch.cuda.is_available():
+        device = torch.device("cuda", local_rank if env_rank is not None else (args.worker_id or 0) % max(
+            1, torch.cuda.device_count()))
+        torch.cuda.set_device(device)
+    else:
+        device = torch.device("cpu")
+
+    dp = None
+    ddp = par.ddp_parallel if par is not None else None
+    if env_rank is not None and int(env_world) > 1:
+        import torch.distributed as dist
+        from .parallel.dp import DataParallel
+        kwargs = {"device_id": device} if device.type == "cuda" else {}
+        dist.init_process_group("nccl" if device.type == "cuda" else "gloo", **kwargs)
+        dp = DataParallel(mode=(ddp.grad_reduce if ddp is not None and ddp.use_ddp_parallel else "allreduce"))
+    elif ddp is not None and ddp.use_ddp_parallel:
+        rank = args.worker_id if args.worker_id is not None else 0
+        if ddp.transport == "ccl":
+            from .parallel import rendezvous
+            from .parallel.dp import DataParallel
+            rendezvous.perform_ccl_rendezvous(ddp.ccl_rendezvous.ip, ddp.ccl_rendezvous.port, rank,
+                                              args.ddp_world_size, device)
+            dp = DataParallel(mode=ddp.grad_reduce)
+        else:
+            from .parallel.ft_dp import FaultTolerantDataParallel
+            from .parallel.ftccl import FtPeer, Result
+            peer = FtPeer(ddp.ftccl_master.ip, ddp.ftccl_master.port, device)
+            if peer.connect() != Result.SUCCESS:
+                LOG("FATAL", "cannot reach the ftccl master")
+            dp = FaultTolerantDataParallel(peer, expected_world=args.ddp_world_size, min_world=1,
+                                           mode="fused" if ddp.grad_reduce == "fused" else "allreduce")
+
+    if cfg.model_config.dtype == "fp16" and device.type == "cuda":
+        LOG("WARN", "the native kernels compute in bf16; running the fp16 configuration as bf16")
+        cfg.model_config.dtype = "bf16"
+        cfg.model_config.use_fp16_accumulation = False
+    trainer = Trainer(cfg, parallel=par, device=device, dp=dp, frame_chunk=args.frame_chunk, working_dir=working_dir)
+    if args.synthetic:
+        cfg.train_data_config.recordings_directory_path = ""
+
+    if args.validation_dump:
+        from .data import SyntheticBatchSource
+        from .utils import safetensors_io as st
+        src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point, trainer.vocab,
+                                   seed=cfg.validation_data_config.iteration_seed, pin=False)
+        for step in range(args.validation_dump_steps):
+            cells, targets = src.next_batch(cfg.micro_batch_size, cfg.validation_sequence_length)
+            dump = trainer.validation_dump(cells, targets)
+            path = args.validation_dump_file if args.validation_dump_steps == 1 else \
+                args.validation_dump_file.replace(".safetensors", f"_{step}.safetensors")
+            st.save_file(dump, path)
+            LOG("INFO", f"wrote {path}")
+            trainer.train_step(cells, targets)
+        trainer.close()
+        return 0
+
+    t0 = time.time()
+    history = run_training(trainer, max_steps=args.steps)
+    trainer.close()
+    if history:
+        LOG("INFO", f"finished {len(history)} steps in {time.time() - t0:.1f} s; last loss {history[-1]['loss/train']:.4f}")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

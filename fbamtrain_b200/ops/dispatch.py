@@ -114,6 +114,13 @@ def lstm_sequence(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype):
     if _native(x):
         from .native_ops import lstm_sequence as f
         return f(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype)
+    if x.is_cuda and h0.dim() == 1:
+        # PyTorch baseline on GPU: the library (cuDNN) LSTM instead of a Python loop over time steps
+        b = x.shape[1]
+        params = [w_ih.to(compute_dtype), w_hh.to(compute_dtype), b_ih.to(compute_dtype), b_hh.to(compute_dtype)]
+        hx = (h0.to(compute_dtype).expand(1, b, -1).contiguous(), c0.to(compute_dtype).expand(1, b, -1).contiguous())
+        y, h_n, c_n = torch._VF.lstm(x.to(compute_dtype), hx, params, True, 1, 0.0, True, False, False)
+        return y, h_n[0], c_n[0].float()
     return ref.lstm_sequence(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype)
 
 

@@ -1,0 +1,54 @@
+import json
+import os
+import subprocess
+import sys
+
+import torch
+
+from fbamtrain_b200 import presets
+from fbamtrain_b200.utils import safetensors_io as st
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(args, **kw):
+    env = dict(os.environ, PYTHONPATH=ROOT, FBAMTRAIN_LOG_LEVEL="INFO")
+    return subprocess.run([sys.executable, "-m"] + args, capture_output=True, text=True, env=env, timeout=300, **kw)
+
+
+def test_cli_trains_synthetic_and_dumps(tmp_path):
+    cfg = presets.tiny()
+    cfg["checkpointing"]["checkpoint_directory"] = "ckpt"
+    cfg["checkpointing"]["checkpoint_interval"] = 2
+    cfg["checkpointing"]["resume_behavior"] = "load_latest"
+    p = tmp_path / "run.json"
+    p.write_text(json.dumps(cfg))
+    r = _run(["fbamtrain_b200.cli", "-c", str(p), "--synthetic", "--steps", "3", "--device", "cpu", "-v"])
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "Step 2 took" in r.stdout and os.path.exists(tmp_path / "ckpt" / "checkpoint_step_02.safetensors")
+    dump = tmp_path / "d.safetensors"
+    r = _run(["fbamtrain_b200.cli", "-c", str(p), "--device", "cpu", "--validation-dump", "--validation-dump-file",
+              str(dump)])
+    assert r.returncode == 0, r.stdout + r.stderr
+    keys = set(st.load_file(str(dump)))
+    assert {"output", "h_n", "c_n", "loss", "frame_embeddings", "logits"} <= keys
+
+
+def test_tenscmp_cli(tmp_path):
+    a, b = str(tmp_path / "a.safetensors"), str(tmp_path / "b.safetensors")
+    t = torch.randn(4, 4)
+    st.save_file({"x": t}, a)
+    st.save_file({"x": t + 0.01}, b)
+    assert _run(["fbamtrain_b200.tenscmp", a, b, "-t", "0.1"]).returncode == 0
+    r = _run(["fbamtrain_b200.tenscmp", a, b, "-t", "0.001"])
+    assert r.returncode == 1 and "x: max |a-b|" in r.stdout
+
+
+def test_wandb_wrapper_collects_metric_lines():
+    from fbamtrain_b200.wandb_log_wrapper import parse_metric_line
+    assert parse_metric_line('{"step": 3, "loss/train": 1.5}') == {"step": 3, "loss/train": 1.5}
+    assert parse_metric_line("Step 3 took 1 s") is None and parse_metric_line('{"no_step": 1}') is None
+    code = "import json;print('hello');print(json.dumps({'step': 1, 'loss/train': 2.0}))"
+    r = _run(["fbamtrain_b200.wandb_log_wrapper", "--dry-run", "--", sys.executable, "-c", code])
+    assert r.returncode == 0 and "hello" in r.stdout
+    assert json.loads(r.stdout.strip().splitlines()[-1])["metrics_logged"] == 1
