@@ -70,7 +70,7 @@ template <int MAXKS>  // k-steps (of 16) per warp: H <= MAXKS * 8 * 16
 __global__ void __launch_bounds__(kThreads, 1)
 lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const float* __restrict__ h0,
                 const float* __restrict__ c0, bf16* __restrict__ y, float* __restrict__ c_all, bf16* hbuf,
-                unsigned* counter, int* status, int T, int B, int H) {
+                unsigned* counter, int* status, int T, int B, int H, int per_sample) {
   __shared__ float part[kWarps][2][16][8];
   __shared__ float pre[32][8];
   extern __shared__ uint4 dyn_smem[];
@@ -102,8 +102,11 @@ lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const f
   const int u = threadIdx.x >> 3, b = threadIdx.x & 7;
   float c = 0.0f;
   if (threadIdx.x < 64) {
-    c = c0[unit0 + u];
-    hbuf[(long long)b * H + unit0 + u] = __float2bfloat16(h0[unit0 + u]);
+    // initial state: one learned vector broadcast over the batch, or (per_sample) a (B, H) state carried over
+    // from the previous chunk of the same sequences
+    const long long si = per_sample ? (long long)min(b, B - 1) * H + unit0 + u : unit0 + u;
+    c = c0[si];
+    hbuf[(long long)b * H + unit0 + u] = __float2bfloat16(h0[si]);
   }
   // Each of the 256 threads owns one (gate row, batch) entry of the pre-activations; the value for the next
   // step is fetched from HBM before the grid barrier so that its latency is hidden behind the wait.
@@ -187,7 +190,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all, const float* __restrict__ c0,
                 const bf16* __restrict__ dy, const bf16* __restrict__ whh_t, bf16* dgates, float* __restrict__ dh0,
                 float* __restrict__ dc0, const float* __restrict__ dh_last, const float* __restrict__ dc_last,
-                unsigned* counter, int* status, int T, int B, int H) {
+                unsigned* counter, int* status, int T, int B, int H, int per_sample) {
   __shared__ float part[kWarps][16][8];
   extern __shared__ uint4 dyn_smem[];
   bf16* ds = reinterpret_cast<bf16*>(dyn_smem);  // [8][4H + 8]: dGates[t], padded rows
@@ -228,7 +231,7 @@ lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all
     const float* gt = gates + ((long long)t * B + b) * K + unit;
     n_ig = gt[0]; n_fg = gt[H]; n_gg = gt[2 * (long long)H]; n_og = gt[3 * (long long)H];
     n_ct = c_all[((long long)t * B + b) * H + unit];
-    n_cp = t > 0 ? c_all[((long long)(t - 1) * B + b) * H + unit] : c0[unit];
+    n_cp = t > 0 ? c_all[((long long)(t - 1) * B + b) * H + unit] : c0[per_sample ? (long long)b * H + unit : unit];
     n_dy = __bfloat162float(dy[((long long)t * B + b) * H + unit]);
   }
 
@@ -253,7 +256,8 @@ lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all
         const float* gt = gates + ((long long)tn * B + b) * K + unit;
         n_ig = gt[0]; n_fg = gt[H]; n_gg = gt[2 * (long long)H]; n_og = gt[3 * (long long)H];
         n_ct = cp;
-        n_cp = tn > 0 ? c_all[((long long)(tn - 1) * B + b) * H + unit] : c0[unit];
+        n_cp = tn > 0 ? c_all[((long long)(tn - 1) * B + b) * H + unit]
+                      : c0[per_sample ? (long long)b * H + unit : unit];
         n_dy = __bfloat162float(dy[((long long)tn * B + b) * H + unit]);
       }
     }
@@ -318,12 +322,12 @@ int fbam_lstm_persistent_max_hidden() { return 1024; }
 
 // gates: (T, B, 4H) fp32, pre-activations incl. bias on entry, activated gates on exit.
 // hbuf: 2*8*H bf16 scratch; counter: one zeroed unsigned.
-int fbam_lstm_fwd(float* gates, const void* whh, const float* h0, const float* c0, void* y, float* c_all,
-                  void* hbuf, unsigned* counter, int* status, int T, int B, int H, void* stream) {
+int fbam_lstm_fwd_ex(float* gates, const void* whh, const float* h0, const float* c0, void* y, float* c_all,
+                     void* hbuf, unsigned* counter, int* status, int T, int B, int H, int per_sample, void* stream) {
   if (B < 1 || B > 8 || H % 16 != 0 || H > 1024 || T < 1) return 1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(counter, 0, sizeof(unsigned), s) != cudaSuccess) return 5;
-  void* args[] = {&gates, &whh, &h0, &c0, &y, &c_all, &hbuf, &counter, &status, &T, &B, &H};
+  void* args[] = {&gates, &whh, &h0, &c0, &y, &c_all, &hbuf, &counter, &status, &T, &B, &H, &per_sample};
   const int grid = H / 8;
   const size_t smem = (size_t)8 * (H + 8) * sizeof(bf16);
   if (H <= 256) return coop_launch(lstm_fwd_kernel<2>, grid, args, smem, s);
@@ -331,20 +335,33 @@ int fbam_lstm_fwd(float* gates, const void* whh, const float* h0, const float* c
   return coop_launch(lstm_fwd_kernel<8>, grid, args, smem, s);
 }
 
+// h0 / c0 are (H) vectors broadcast over the batch.
+int fbam_lstm_fwd(float* gates, const void* whh, const float* h0, const float* c0, void* y, float* c_all,
+                  void* hbuf, unsigned* counter, int* status, int T, int B, int H, void* stream) {
+  return fbam_lstm_fwd_ex(gates, whh, h0, c0, y, c_all, hbuf, counter, status, T, B, H, 0, stream);
+}
+
 // whh_t: (H, 4H) bf16 = W_hh transposed.  dgates: (T, B, 4H) bf16 out.  dh0/dc0: (B, H) fp32 out.
-int fbam_lstm_bwd(const float* gates, const float* c_all, const float* c0, const void* dy, const void* whh_t,
-                  void* dgates, float* dh0, float* dc0, const float* dh_last, const float* dc_last, unsigned* counter,
-                  int* status, int T, int B, int H, void* stream) {
+int fbam_lstm_bwd_ex(const float* gates, const float* c_all, const float* c0, const void* dy, const void* whh_t,
+                     void* dgates, float* dh0, float* dc0, const float* dh_last, const float* dc_last,
+                     unsigned* counter, int* status, int T, int B, int H, int per_sample, void* stream) {
   if (B < 1 || B > 8 || H % 16 != 0 || H > 1024 || T < 1) return 1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(counter, 0, sizeof(unsigned), s) != cudaSuccess) return 5;
   void* args[] = {&gates, &c_all, &c0, &dy, &whh_t, &dgates, &dh0, &dc0, &dh_last, &dc_last, &counter, &status,
-                  &T, &B, &H};
+                  &T, &B, &H, &per_sample};
   const int grid = H / 16;
   const size_t smem = (size_t)8 * (4 * H + 8) * sizeof(bf16);
   if (H <= 256) return coop_launch(lstm_bwd_kernel<8>, grid, args, smem, s);
   if (H <= 512) return coop_launch(lstm_bwd_kernel<16>, grid, args, smem, s);
   return coop_launch(lstm_bwd_kernel<32>, grid, args, smem, s);
+}
+
+int fbam_lstm_bwd(const float* gates, const float* c_all, const float* c0, const void* dy, const void* whh_t,
+                  void* dgates, float* dh0, float* dc0, const float* dh_last, const float* dc_last, unsigned* counter,
+                  int* status, int T, int B, int H, void* stream) {
+  return fbam_lstm_bwd_ex(gates, c_all, c0, dy, whh_t, dgates, dh0, dc0, dh_last, dc_last, counter, status, T, B, H, 0,
+                          stream);
 }
 
 }  // extern "C"
@@ -407,7 +424,8 @@ int fbam_lstm_fwd_noalloc(float* gates, const void* whh, const float* h0, const 
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // the counter must start at zero; the h buffer is written (initial state) before any CTA reads it
   if (cudaMemsetAsync(counter, 0, sizeof(unsigned), s) != cudaSuccess) return 5;
-  void* args[] = {&gates, &whh, &h0, &c0, &y, &c_all, &hbuf, &counter, &status, &T, &B, &H};
+  int per_sample = 0;
+  void* args[] = {&gates, &whh, &h0, &c0, &y, &c_all, &hbuf, &counter, &status, &T, &B, &H, &per_sample};
   const int grid = H / 8;
   const size_t smem = (size_t)8 * (H + 8) * sizeof(bf16);
   if (H <= 256) return coop_launch(lstm_fwd_kernel<2>, grid, args, smem, s);

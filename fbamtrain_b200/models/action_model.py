@@ -37,6 +37,10 @@ class ActionModel(nn.Module):
         self.ln_f = RmsNorm(h, cfg.rms_norm_eps, dtype) if cfg.action_blocks > 0 else None
         self.head_weight = nn.Parameter(torch.empty(padded_vocab(vocab), h, dtype=dtype))
         fill_uniform_fan_(self.head_weight.data, h, seeds)
+        # The reference's model (one LSTM layer straight into the head) can be streamed chunk by chunk with the
+        # head / loss computed per chunk; ``host_offload`` additionally keeps the stored dY chunks in pinned memory.
+        self.streaming = cfg.action_blocks == 0 and cfg.lstm_layers == 1
+        self.host_offload = False
 
     def features(self, frame_embeddings: torch.Tensor, state=None):
         """``(B, T, E)`` → hidden states ``(B, T, H)`` and the LSTM's final state."""
@@ -53,5 +57,15 @@ class ActionModel(nn.Module):
 
     def forward(self, frame_embeddings: torch.Tensor, targets: torch.Tensor, loss_scale: float, state=None):
         """Returns ``loss_scale · Σ CE`` over all ``B·T`` positions."""
+        if self.streaming and state is None and frame_embeddings.is_cuda and ops.get_backend() == "auto":
+            from ..ops.lstm import persistent_ok
+            layer = self.lstm.layers[0]
+            b, t, e = frame_embeddings.shape
+            if persistent_ok(b, layer.hidden) and e % 8 == 0 and frame_embeddings.dtype == torch.bfloat16:
+                from ..ops.streaming import streaming_lstm_head_ce
+                return streaming_lstm_head_ce(frame_embeddings.transpose(0, 1).contiguous(), layer.weights_ih,
+                                              layer.weights_hh, layer.bias_ih, layer.bias_hh, layer.h0, layer.c0,
+                                              self.head_weight, targets.t().contiguous(), self.vocab, loss_scale,
+                                              max(1, self.lstm.chunk_size), self.host_offload)
         x, _ = self.features(frame_embeddings, state)
         return ops.lm_head_ce(x.reshape(-1, x.shape[-1]), self.head_weight, targets.reshape(-1), self.vocab, loss_scale)

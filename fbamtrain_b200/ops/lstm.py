@@ -51,11 +51,14 @@ class _LstmSequence(torch.autograd.Function):
         c_all = torch.empty(t_len, b, h, dtype=torch.float32, device=dev)
         hbuf = torch.empty(2 * 8 * h, dtype=BF16, device=dev)
         h0f, c0f = h0.float().contiguous(), c0.float().contiguous()
-        nv.check(nv.lib().fbam_lstm_fwd(nv.ptr(gates), nv.ptr(wh), nv.ptr(h0f), nv.ptr(c0f), nv.ptr(y), nv.ptr(c_all),
-                                        nv.ptr(hbuf), nv.ptr(_counter(dev)), nv.ptr(nv.status_word(dev)), t_len, b, h,
-                                        nv.stream_ptr()), "fbam_lstm_fwd")
+        per_sample = int(h0.dim() == 2)
+        nv.check(nv.lib().fbam_lstm_fwd_ex(nv.ptr(gates), nv.ptr(wh), nv.ptr(h0f), nv.ptr(c0f), nv.ptr(y),
+                                           nv.ptr(c_all), nv.ptr(hbuf), nv.ptr(_counter(dev)),
+                                           nv.ptr(nv.status_word(dev)), t_len, b, h, per_sample, nv.stream_ptr()),
+                 "fbam_lstm_fwd")
         ctx.save_for_backward(x2, wi, wh, gates, y, c_all, h0f, c0f)
         ctx.dims = (t_len, b, i_dim, h)
+        ctx.per_sample = per_sample
         return y, y[-1].clone(), c_all[-1].clone()
 
     @staticmethod
@@ -70,17 +73,20 @@ class _LstmSequence(torch.autograd.Function):
         dc0 = torch.empty(b, h, dtype=torch.float32, device=dev)
         dhl = None if dh_last is None else dh_last.float().contiguous()
         dcl = None if dc_last is None else dc_last.float().contiguous()
-        nv.check(nv.lib().fbam_lstm_bwd(nv.ptr(gates), nv.ptr(c_all), nv.ptr(c0f), nv.ptr(dy), nv.ptr(wh_t),
-                                        nv.ptr(dgates), nv.ptr(dh0), nv.ptr(dc0), nv.ptr(dhl), nv.ptr(dcl),
-                                        nv.ptr(_counter(dev)), nv.ptr(nv.status_word(dev)), t_len, b, h,
-                                        nv.stream_ptr()), "fbam_lstm_bwd")
+        nv.check(nv.lib().fbam_lstm_bwd_ex(nv.ptr(gates), nv.ptr(c_all), nv.ptr(c0f), nv.ptr(dy), nv.ptr(wh_t),
+                                           nv.ptr(dgates), nv.ptr(dh0), nv.ptr(dc0), nv.ptr(dhl), nv.ptr(dcl),
+                                           nv.ptr(_counter(dev)), nv.ptr(nv.status_word(dev)), t_len, b, h,
+                                           ctx.per_sample, nv.stream_ptr()), "fbam_lstm_bwd")
         dg2 = dgates.view(t_len * b, 4 * h)
         dx = gemm_nn(dg2, wi).view(t_len, b, i_dim) if ctx.needs_input_grad[0] else None
         dw_ih = gemm_tn(dg2, x2, out_dtype=torch.float32)
-        h_prev = torch.cat([h0f.to(BF16).expand(1, b, h), y[:-1]], 0).reshape(t_len * b, h)
+        h_first = h0f.to(BF16).view(1, b, h) if ctx.per_sample else h0f.to(BF16).expand(1, b, h)
+        h_prev = torch.cat([h_first, y[:-1]], 0).reshape(t_len * b, h)
         dw_hh = gemm_tn(dg2, h_prev, out_dtype=torch.float32)
         from .native_ops import _colsum
         db = _colsum(dg2)
+        if ctx.per_sample:
+            return dx, dw_ih, dw_hh, db, db.clone(), dh0, dc0
         return dx, dw_ih, dw_hh, db, db.clone(), dh0.sum(0), dc0.sum(0)
 
 
@@ -105,9 +111,6 @@ def _stepwise(x, w_ih, w_hh, b_ih, b_hh, h0, c0):
 def lstm_sequence(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype):
     if compute_dtype != BF16:
         raise TypeError("native LSTM computes in bf16")
-    if h0.dim() != 1:
-        # per-sample initial state (sequence fed in pieces): handled by the step-wise path
-        raise NotImplementedError("per-sample initial state is not wired on the native path")
     if not persistent_ok(x.shape[1], w_hh.shape[1]) or x.shape[2] % 8 != 0:
         return _stepwise(x, w_ih, w_hh, b_ih, b_hh, h0, c0)
     return _LstmSequence.apply(x.to(BF16), w_ih, w_hh, b_ih, b_hh, h0, c0)
