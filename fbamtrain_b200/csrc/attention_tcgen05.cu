@@ -45,6 +45,11 @@ __device__ __forceinline__ void tma_load_attn(void* dst, const CUtensorMap* map,
 }
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 // Address of element (row, col8 = 8-element group index) in a [rows x 64]-bf16 panel with 128-byte swizzle.
 __device__ __forceinline__ uint32_t swz(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
@@ -52,8 +57,10 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) { return row * 128 +
 // -------------------------------------------------------------------------------------------------
 // forward
 // -------------------------------------------------------------------------------------------------
-template <int D>
-__global__ void __launch_bounds__(160, 1)
+// KV_STAGES = 2 prefetches the next K/V block inside the CTA; KV_STAGES = 1 halves the K/V footprint so that two
+// CTAs share an SM and overlap each other's softmax and tensor-core phases instead (used for D = 64).
+template <int D, int KV_STAGES>
+__global__ void __launch_bounds__(160, KV_STAGES == 1 ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
   constexpr int DP = D / 64;                 // 64-wide panels per row
@@ -64,9 +71,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + kQBytes;                // 2 stages
-  uint8_t* sV = sK + 2 * kKVBytes;           // 2 stages
-  uint8_t* sP = sV + 2 * kKVBytes;
+  uint8_t* sK = sQ + kQBytes;                // KV_STAGES stages
+  uint8_t* sV = sK + KV_STAGES * kKVBytes;   // KV_STAGES stages
+  uint8_t* sP = sV + KV_STAGES * kKVBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);
   uint64_t* q_full = bars;                   // 1
   uint64_t* kv_full = bars + 1;              // 2
@@ -107,7 +114,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
       for (int j = 0; j < DP; ++j) tma_load_attn(sQ + j * BQ * 128, &map_q, q_full, j * 64, h, q0, b);
       auto load_kv = [&](int kb) {
-        const int s = kb & 1;
+        const int s = kb % KV_STAGES;
         mbar_expect_tx(&kv_full[s], 2 * kKVBytes);
 #pragma unroll
         for (int j = 0; j < DP; ++j) {
@@ -120,12 +127,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);   // B = V is MN-major
       ok = mbar_wait(q_full, 0);
       for (int kb = 0; kb < nkb && ok; ++kb) {
-        const int s = kb & 1;
-        if (kb + 1 < nkb) {   // prefetch the next block into the other stage once its previous user is done
+        const int s = kb % KV_STAGES;
+        if (KV_STAGES == 2 && kb + 1 < nkb) {   // prefetch the next block into the other stage once it is free
           if (kb >= 1 && !mbar_wait(&kv_empty[s ^ 1], ((kb - 1) >> 1) & 1)) { ok = false; break; }
           load_kv(kb + 1);
         }
-        if (!mbar_wait(&kv_full[s], (kb >> 1) & 1)) { ok = false; break; }
+        if (KV_STAGES == 1 && kb >= 1) {        // single stage: reload once the previous block's P·V has read it
+          if (!mbar_wait(&kv_empty[0], (kb - 1) & 1)) { ok = false; break; }
+          load_kv(kb);
+        }
+        if (!mbar_wait(&kv_full[s], (kb / KV_STAGES) & 1)) { ok = false; break; }
         fence_after_sync();
         const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK + s * kKVBytes), v_addr = smem_u32(sV + s * kKVBytes);
 #pragma unroll
@@ -186,7 +197,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       const float m_new = mx;
       const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;   // fully masked row: keep exponents finite
-      const float alpha = exp2f((m - m_use) * p.scale_log2);     // m = -inf on the first block -> 0
+      const float alpha = fast_exp2((m - m_use) * p.scale_log2);     // m = -inf on the first block -> 0
       float rs = 0.0f;
       // pass 2: P = exp2(scale*(S - m)) -> bf16 -> swizzled shared memory
 #pragma unroll 1
@@ -202,7 +213,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             const int tk = k0 + c0 + j;
             if (tk >= p.T || (p.causal && tk > t_q)) sv = -INFINITY;
           }
-          pv[j] = exp2f((sv - m_use) * p.scale_log2);
+          pv[j] = fast_exp2((sv - m_use) * p.scale_log2);
         }
 #pragma unroll
         for (int j8 = 0; j8 < 4; ++j8) {
@@ -434,7 +445,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             for (int e = 0; e < 2; ++e) {
               const int j = j8 * 8 + 2 * q + e;
               const int tk = k0 + c0 + j;
-              float pr = exp2f(__uint_as_float(rs[j]) * p.scale_log2 - lse * 1.4426950408889634f);
+              float pr = fast_exp2(__uint_as_float(rs[j]) * p.scale_log2 - lse * 1.4426950408889634f);
               if (need_mask && (!row_ok || tk >= p.T || (p.causal && tk > t_q))) pr = 0.0f;
               pe[e] = pr;
               de[e] = pr * (__uint_as_float(rd[j]) - dl) * p.scale;
@@ -558,14 +569,15 @@ int fbam_attn_fwd(const void* q, const void* k, const void* v, long long sb, lon
   if ((e = encode_bthd(&mv, v, B, T, H, D, sb, st, sh))) return e;
   AttnParams p{B, T, H, D, causal, scale * 1.4426950408889634f, scale, (bf16*)out, lse, status};
   dim3 grid((T + BQ - 1) / BQ, H, B);
-  const int smem = BQ * D * 2 + 4 * BKV * D * 2 + BQ * BKV * 2 + 256 + 1024;
+  const int stages = D == 64 ? 1 : 2;
+  const int smem = BQ * D * 2 + 2 * stages * BKV * D * 2 + BQ * BKV * 2 + 256 + 1024;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (D == 64) {
-    if (set_smem(attn_fwd_kernel<64>, smem)) return 5;
-    attn_fwd_kernel<64><<<grid, 160, smem, s>>>(mq, mk, mv, p);
+    if (set_smem(attn_fwd_kernel<64, 1>, smem)) return 5;
+    attn_fwd_kernel<64, 1><<<grid, 160, smem, s>>>(mq, mk, mv, p);
   } else {
-    if (set_smem(attn_fwd_kernel<128>, smem)) return 5;
-    attn_fwd_kernel<128><<<grid, 160, smem, s>>>(mq, mk, mv, p);
+    if (set_smem(attn_fwd_kernel<128, 2>, smem)) return 5;
+    attn_fwd_kernel<128, 2><<<grid, 160, smem, s>>>(mq, mk, mv, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }

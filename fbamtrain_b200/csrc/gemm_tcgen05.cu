@@ -25,6 +25,7 @@
 //
 // Every mbarrier wait is bounded; on timeout the CTA writes an error code to `status` and unwinds.
 #include "gemm_tcgen05.h"
+#include "gemm_epilogue.cuh"
 #include "tc05.cuh"
 
 namespace {
@@ -49,25 +50,6 @@ struct SmemLayout {
   static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024: manual alignment slack
 };
-
-// erf via Abramowitz-Stegun 7.1.26 (|error| < 1.5e-7, far below bf16 resolution): the epilogue must not cost
-// more issue slots than the tile's main loop, and erff() would.  e = exp(-x²/2) is shared with gelu'.
-__device__ __forceinline__ float erf_core(float x, float& e) {
-  const float u = fabsf(x) * 0.70710678118654752f;
-  const float t = __fdividef(1.0f, 1.0f + 0.3275911f * u);
-  e = __expf(-u * u);
-  const float poly = t * (0.254829592f + t * (-0.284496736f + t * (1.421413741f + t * (-1.453152027f + t * 1.061405429f))));
-  return copysignf(1.0f - poly * e, x);
-}
-__device__ __forceinline__ float gelu_f(float x) {
-  float e;
-  return 0.5f * x * (1.0f + erf_core(x, e));
-}
-__device__ __forceinline__ float gelu_grad_f(float x) {
-  float e;
-  const float er = erf_core(x, e);
-  return 0.5f * (1.0f + er) + x * 0.3989422804014327f * e;
-}
 
 // Row of the output tile -> element offset of that row in D (or -1 when the row is out of range).
 __device__ __forceinline__ long long row_offset(const GemmParams& p, int tile_m, int row, int BM) {
@@ -299,140 +281,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         tmem_ld_wait();
         const int n0 = tile_n * BN + c0;
         if (roff < 0 || n0 >= p.N || wk.k_end <= wk.k_begin) continue;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-        const bool full_vec = (n0 + 32 <= p.N) && p.vec_ok;
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (n0 + j < p.N)
-              v[j] += p.bias_fp32 ? reinterpret_cast<const float*>(p.bias)[n0 + j]
-                                  : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n0 + j]);
-        }
-        if (p.preact_out != nullptr) {
-          __nv_bfloat16* po = p.preact_out + roff + n0;
-          if (full_vec) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              __align__(16) __nv_bfloat162 h[4];
-#pragma unroll
-              for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
-              *reinterpret_cast<uint4*>(po + j) = *reinterpret_cast<uint4*>(h);
-            }
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N) po[j] = __float2bfloat16(v[j]);
-          }
-        }
-        if (p.act == GEMM_ACT_GELU) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
-        } else if (p.act == GEMM_ACT_RELU) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
-        }
-        if (p.gelu_grad_in != nullptr) {
-          const __nv_bfloat16* gi = p.gelu_grad_in + roff + n0;
-          if (full_vec) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 raw = *reinterpret_cast<const uint4*>(gi + j);
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                float2 f = __bfloat1622float2(h[q]);
-                v[j + 2 * q] *= gelu_grad_f(f.x);
-                v[j + 2 * q + 1] *= gelu_grad_f(f.y);
-              }
-            }
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N) v[j] *= gelu_grad_f(__bfloat162float(gi[j]));
-          }
-        }
-        if (p.residual != nullptr) {
-          const __nv_bfloat16* ri = p.residual + roff / p.ldd * p.ldr + n0;
-          if (full_vec && (p.ldr % 8 == 0)) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 raw = *reinterpret_cast<const uint4*>(ri + j);
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                float2 f = __bfloat1622float2(h[q]);
-                v[j + 2 * q] += f.x;
-                v[j + 2 * q + 1] += f.y;
-              }
-            }
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N) v[j] += __bfloat162float(ri[j]);
-          }
-        }
-        if (p.rs_rows_per_rank > 0) {
-          // GEMM -> reduce-scatter: add this rank's partial sums into the owner's fp32 buffer over NVLink
-          const int m = (int)(roff / p.ldd);
-          const int owner = m / p.rs_rows_per_rank;
-          float* out = reinterpret_cast<float*>(p.rs_out[owner]) + (long long)(m - owner * p.rs_rows_per_rank) * p.ldd + n0;
-          if (full_vec) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + j), "f"(v[j]),
-                           "f"(v[j + 1]), "f"(v[j + 2]), "f"(v[j + 3])
-                           : "memory");
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N)
-                asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(out + j), "f"(v[j]) : "memory");
-          }
-          continue;
-        }
-        if (p.out_fp32) {
-          float* out = reinterpret_cast<float*>(p.D) + roff + n0;
-          if (p.accumulate == GEMM_ACC_ATOMIC) {
-            for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N) atomicAdd(out + j, v[j]);
-          } else if (full_vec) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-              if (p.accumulate) {
-                float4 c = *reinterpret_cast<const float4*>(out + j);
-                o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
-              }
-              *reinterpret_cast<float4*>(out + j) = o;
-            }
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N) out[j] = p.accumulate ? out[j] + v[j] : v[j];
-          }
-        } else {
-          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + roff + n0;
-          if (full_vec) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (p.accumulate) {
-                uint4 raw = *reinterpret_cast<const uint4*>(out + j);
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  float2 f = __bfloat1622float2(h[q]);
-                  v[j + 2 * q] += f.x;
-                  v[j + 2 * q + 1] += f.y;
-                }
-              }
-              __align__(16) __nv_bfloat162 h[4];
-#pragma unroll
-              for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
-              *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
-            }
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N)
-                out[j] = __float2bfloat16(p.accumulate ? __bfloat162float(out[j]) + v[j] : v[j]);
-          }
-        }
+        gemm_epi::store_chunk(p, roff, n0, r);
       }
       fence_before_sync();
       __syncwarp();

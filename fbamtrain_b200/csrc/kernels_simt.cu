@@ -373,14 +373,30 @@ __global__ void colsum_kernel(const bf16* __restrict__ x, float* __restrict__ ou
 // ------------------------------------------------------------------------------------------------
 // out[f, p, :] = cp_embed[cp] (0 if out of range) + pos_embed[p] + sum_c chan_c/255 * colour[c]
 // A thread owns (position p, 8 channels) and walks a slice of the frames: its position row and the six
-// colour vectors stay in registers, so per cell it loads only the three cell words and one 32-byte slice
-// of the code-point table (L1/L2 resident) and stores 16 bytes.  The threads of a block cover 16
-// neighbouring positions x all channels, i.e. one contiguous 4 KB span of the output per frame.
-__global__ void cell_embed_fwd_kernel(const int* __restrict__ cells, const float* __restrict__ cp_embed,
+// colour vectors stay in registers, so per cell it loads only the three cell words and one slice of the
+// code-point table and stores 16 bytes.  The threads of a block cover 16 neighbouring positions x all channels,
+// i.e. one contiguous 4 KB span of the output per frame.  When the code-point table fits (SMEM_TABLE), a bf16
+// copy of it is staged in shared memory once per block (rows padded by 16 bytes against bank conflicts), which
+// removes the table's L2 traffic — otherwise 2 bytes read per byte written.
+template <bool SMEM_TABLE>
+__global__ void __launch_bounds__(512) cell_embed_fwd_kernel(const int* __restrict__ cells, const float* __restrict__ cp_embed,
                                       const float* __restrict__ pos_embed, const float* __restrict__ colour,
                                       bf16* __restrict__ out, long long frames, int positions, int e, int vocab,
                                       int frames_per_block) {
+  extern __shared__ uint4 embed_smem[];
   const int e8 = e / 8;
+  const int row_u4 = e8 + 1;   // padded row length in 16-byte units
+  if (SMEM_TABLE) {
+    for (int i = threadIdx.x; i < vocab * e8; i += blockDim.x) {
+      const int r = i / e8, c = i % e8;
+      const float4* src = reinterpret_cast<const float4*>(cp_embed + (long long)r * e + c * 8);
+      const float4 a = src[0], b = src[1];
+      const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      const Pack8 pk = pack8(f);
+      embed_smem[r * row_u4 + c] = *reinterpret_cast<const uint4*>(&pk);
+    }
+    __syncthreads();
+  }
   const int g = threadIdx.x % e8, pl = threadIdx.x / e8;
   const int p = blockIdx.x * (blockDim.x / e8) + pl;
   if (p >= positions) return;
@@ -400,27 +416,52 @@ __global__ void cell_embed_fwd_kernel(const int* __restrict__ cells, const float
   }
   const long long f0 = (long long)blockIdx.y * frames_per_block;
   const long long f1 = min(frames, f0 + frames_per_block);
-#pragma unroll 4
-  for (long long f = f0; f < f1; ++f) {
-    const long long cell = f * positions + p;
-    const int cp = cells[cell * 3 + 0];
-    const uint32_t fg = (uint32_t)cells[cell * 3 + 1], bg = (uint32_t)cells[cell * 3 + 2];
-    const float ch[6] = {((fg >> 16) & 255) * (1.0f / 255.0f), ((fg >> 8) & 255) * (1.0f / 255.0f),
-                         (fg & 255) * (1.0f / 255.0f),         ((bg >> 16) & 255) * (1.0f / 255.0f),
-                         ((bg >> 8) & 255) * (1.0f / 255.0f),  (bg & 255) * (1.0f / 255.0f)};
-    float o[8];
+  constexpr int G = 8;   // frames whose cell words are fetched together (loads in flight per thread)
+  for (long long fb = f0; fb < f1; fb += G) {
+    int cpq[G];
+    uint32_t fgq[G], bgq[G];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = pos[j];
-    if (cp >= 0 && cp < vocab) {
-      const float4* ce = reinterpret_cast<const float4*>(cp_embed + (long long)cp * e + col);
-      const float4 a = ce[0], b = ce[1];
-      o[0] += a.x; o[1] += a.y; o[2] += a.z; o[3] += a.w; o[4] += b.x; o[5] += b.y; o[6] += b.z; o[7] += b.w;
+    for (int u = 0; u < G; ++u) {
+      const long long f = fb + u;
+      if (f < f1) {
+        const int* cw = cells + (f * positions + p) * 3;
+        cpq[u] = cw[0];
+        fgq[u] = (uint32_t)cw[1];
+        bgq[u] = (uint32_t)cw[2];
+      }
     }
 #pragma unroll
-    for (int k = 0; k < 6; ++k)
+    for (int u = 0; u < G; ++u) {
+      const long long f = fb + u;
+      if (f >= f1) break;
+      const long long cell = f * positions + p;
+      const int cp = cpq[u];
+      const uint32_t fg = fgq[u], bg = bgq[u];
+      const float ch[6] = {((fg >> 16) & 255) * (1.0f / 255.0f), ((fg >> 8) & 255) * (1.0f / 255.0f),
+                           (fg & 255) * (1.0f / 255.0f),         ((bg >> 16) & 255) * (1.0f / 255.0f),
+                           ((bg >> 8) & 255) * (1.0f / 255.0f),  (bg & 255) * (1.0f / 255.0f)};
+      float o[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] += ch[k] * cv[k][j];
-    *reinterpret_cast<Pack8*>(out + cell * e + col) = pack8(o);
+      for (int j = 0; j < 8; ++j) o[j] = pos[j];
+      if (cp >= 0 && cp < vocab) {
+        if (SMEM_TABLE) {
+          float t[8];
+          const uint4 raw = embed_smem[cp * row_u4 + g];
+          unpack8(*reinterpret_cast<const Pack8*>(&raw), t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += t[j];
+        } else {
+          const float4* ce = reinterpret_cast<const float4*>(cp_embed + (long long)cp * e + col);
+          const float4 a = ce[0], b = ce[1];
+          o[0] += a.x; o[1] += a.y; o[2] += a.z; o[3] += a.w; o[4] += b.x; o[5] += b.y; o[6] += b.z; o[7] += b.w;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 6; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += ch[k] * cv[k][j];
+      *reinterpret_cast<Pack8*>(out + cell * e + col) = pack8(o);
+    }
   }
 }
 
@@ -454,12 +495,29 @@ __global__ void cell_embed_bwd_kernel(const int* __restrict__ cells, const bf16*
     for (int k = 0; k < 6; ++k)
 #pragma unroll
       for (int j = 0; j < 8; ++j) col_acc[k][j] = 0.0f;
-    for (long long f = f0; f < f1; ++f) {
-      const long long cell = f * positions + p;
+    for (long long fb = f0; fb < f1; fb += 4) {
+     // issue the loads of four frames before touching any of them (memory-level parallelism)
+     Pack8 dq[4];
+     int cpq[4];
+     uint32_t fgq[4], bgq[4];
+#pragma unroll
+     for (int u = 0; u < 4; ++u) {
+       const long long f = fb + u;
+       if (f < f1) {
+         const long long cell = f * positions + p;
+         dq[u] = *reinterpret_cast<const Pack8*>(dout + cell * e + col);
+         cpq[u] = cells[cell * 3 + 0];
+         fgq[u] = (uint32_t)cells[cell * 3 + 1];
+         bgq[u] = (uint32_t)cells[cell * 3 + 2];
+       }
+     }
+#pragma unroll
+     for (int u = 0; u < 4; ++u) {
+      if (fb + u >= f1) break;
       float d[8];
-      unpack8(*reinterpret_cast<const Pack8*>(dout + cell * e + col), d);
-      const int cp = cells[cell * 3 + 0];
-      const uint32_t fg = (uint32_t)cells[cell * 3 + 1], bg = (uint32_t)cells[cell * 3 + 2];
+      unpack8(dq[u], d);
+      const int cp = cpq[u];
+      const uint32_t fg = fgq[u], bg = bgq[u];
       const float ch[6] = {((fg >> 16) & 255) * (1.0f / 255.0f), ((fg >> 8) & 255) * (1.0f / 255.0f),
                            (fg & 255) * (1.0f / 255.0f),         ((bg >> 16) & 255) * (1.0f / 255.0f),
                            ((bg >> 8) & 255) * (1.0f / 255.0f),  (bg & 255) * (1.0f / 255.0f)};
@@ -482,6 +540,7 @@ __global__ void cell_embed_bwd_kernel(const int* __restrict__ cells, const bf16*
       for (int k = 0; k < 6; ++k)
 #pragma unroll
         for (int j = 0; j < 8; ++j) col_acc[k][j] += ch[k] * d[j];
+     }
     }
     if (run_cp >= 0 && run_cp < vocab) {
       float* dst = d_cp + (long long)run_cp * e + col;
@@ -527,6 +586,35 @@ __global__ void ce_fwd_bwd_kernel(bf16* __restrict__ logits, const long long* __
     float g = 0.0f;
     if (c < vocab) g = scale * (__expf(__bfloat162float(lr[c]) - mx) * inv - (c == t ? 1.0f : 0.0f));
     lr[c] = __float2bfloat16(g);
+  }
+}
+
+// Same with fp32 logits in (the LM-head GEMM keeps its fp32 accumulators) and bf16 gradient out: the loss and the
+// softmax are then free of the bf16 rounding of the logits.
+__global__ void ce_fwd_bwd_f32_kernel(const float* __restrict__ logits, bf16* __restrict__ dlogits,
+                                      const long long* __restrict__ targets, float* __restrict__ loss_sum, int vocab,
+                                      int ld, float scale) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const float* lr = logits + row * ld;
+  float mx = -INFINITY;
+  for (int c = threadIdx.x; c < vocab; c += blockDim.x) mx = fmaxf(mx, lr[c]);
+  mx = block_max(mx, scratch);
+  float s = 0.0f;
+  for (int c = threadIdx.x; c < vocab; c += blockDim.x) s += __expf(lr[c] - mx);
+  s = block_sum(s, scratch);
+  const int t = (int)targets[row];
+  if (threadIdx.x == 0) {
+    const float lt = (t >= 0 && t < vocab) ? lr[t] : 0.0f;
+    atomicAdd(loss_sum, scale * (logf(s) + mx - lt));
+  }
+  if (dlogits == nullptr) return;
+  const float inv = 1.0f / s;
+  bf16* dr = dlogits + row * ld;
+  for (int c = threadIdx.x; c < ld; c += blockDim.x) {
+    float g = 0.0f;
+    if (c < vocab) g = scale * (__expf(lr[c] - mx) * inv - (c == t ? 1.0f : 0.0f));
+    dr[c] = __float2bfloat16(g);
   }
 }
 
@@ -665,10 +753,28 @@ int fbam_cell_embed_fwd(const int* cells, const float* cp_embed, const float* po
                         void* out, long long frames, int positions, int e, int vocab, void* stream) {
   if (e % 8 != 0 || e / 8 > 256) return 1;
   const int e8 = e / 8, threads = embed_threads(e8), ppb = threads / e8;
+  const size_t table = (size_t)vocab * (e8 + 1) * 16;
+  if (table <= 160 * 1024 && frames >= 256) {
+    // code-point table staged in shared memory: larger frame slices amortise the staging
+    static bool configured = false;
+    if (!configured) {
+      if (cudaFuncSetAttribute(cell_embed_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) !=
+          cudaSuccess)
+        return 5;
+      configured = true;
+    }
+    const int fpb = 256;
+    const int big = (512 / e8 > 0 ? 512 / e8 : 1) * e8;   // one 512-thread block per SM next to the 136 KB table
+    const int ppb2 = big / e8;
+    dim3 grid((positions + ppb2 - 1) / ppb2, (unsigned)((frames + fpb - 1) / fpb));
+    cell_embed_fwd_kernel<true><<<grid, big, table, STREAM(stream)>>>(cells, cp_embed, pos_embed, colour, (bf16*)out,
+                                                                      frames, positions, e, vocab, fpb);
+    return CHECK_LAUNCH();
+  }
   const int fpb = 64;
   dim3 grid((positions + ppb - 1) / ppb, (unsigned)((frames + fpb - 1) / fpb));
-  cell_embed_fwd_kernel<<<grid, threads, 0, STREAM(stream)>>>(cells, cp_embed, pos_embed, colour, (bf16*)out, frames,
-                                                              positions, e, vocab, fpb);
+  cell_embed_fwd_kernel<false><<<grid, threads, 0, STREAM(stream)>>>(cells, cp_embed, pos_embed, colour, (bf16*)out,
+                                                                     frames, positions, e, vocab, fpb);
   return CHECK_LAUNCH();
 }
 
@@ -687,6 +793,13 @@ int fbam_ce_fwd_bwd(void* logits, const long long* targets, float* loss_sum, lon
                     float scale, int write_grad, void* stream) {
   ce_fwd_bwd_kernel<<<(unsigned)rows, 256, 0, STREAM(stream)>>>((bf16*)logits, targets, loss_sum, vocab, ld, scale,
                                                                 write_grad);
+  return CHECK_LAUNCH();
+}
+
+int fbam_ce_fwd_bwd_f32(const float* logits, void* dlogits, const long long* targets, float* loss_sum, long long rows,
+                        int vocab, int ld, float scale, void* stream) {
+  ce_fwd_bwd_f32_kernel<<<(unsigned)rows, 256, 0, STREAM(stream)>>>(logits, (bf16*)dlogits, targets, loss_sum, vocab, ld,
+                                                                    scale);
   return CHECK_LAUNCH();
 }
 

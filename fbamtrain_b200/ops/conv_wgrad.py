@@ -39,6 +39,8 @@ def conv2d_wgrad(x, dy, w_shape, stride, padding, dilation, out_dtype=torch.bflo
     p.alpha = 1.0
     p.out_fp32 = 1
     p.splits, p.bn, p.bm = splits, bn, bm
-    code = nv.lib().fbam_conv_wgrad_bf16(nv.ptr(dy), o, nv.ptr(x), ih, iw, c, C.byref(p), nv.stream_ptr())
+    from ..utils import debug
+    with debug.label(f"wgrad c{c} o{o}"):
+        code = nv.lib().fbam_conv_wgrad_bf16(nv.ptr(dy), o, nv.ptr(x), ih, iw, c, C.byref(p), nv.stream_ptr())
     nv.check(code, "fbam_conv_wgrad_bf16")
     return dw.view(o, 3, 3, c).to(out_dtype)

@@ -66,6 +66,8 @@ def lib() -> C.CDLL:
         _lib.fbam_gemm_bf16.restype = C.c_int
         _lib.fbam_conv_bf16.restype = C.c_int
         _lib.fbam_conv_wgrad_bf16.restype = C.c_int
+        _lib.fbam_gemm2_bf16.restype = C.c_int
+        _lib.fbam_conv2_bf16.restype = C.c_int
         _lib.fbam_lstm_persistent_max_hidden.restype = C.c_int
         _lib.fbam_lstm_fwd_ex.restype = C.c_int
         _lib.fbam_lstm_bwd_ex.restype = C.c_int

@@ -17,6 +17,9 @@ from . import native as nv
 from . import reference as ref
 
 BF16 = torch.bfloat16
+# Large problems run on CTA pairs (tcgen05 cta_group::2: two SMs share every B fetch and keep double-buffered
+# accumulators).  "auto" picks the pair kernel when there are enough 256-row tiles; False forces single CTAs.
+TWO_CTA = "auto"
 # Weight-gradient and data-gradient GEMMs read their operands in place through the transposed
 # (MN-major) operand form of the tensor-core descriptors.  False = materialise transposes instead.
 USE_MN_MAJOR = True
@@ -37,7 +40,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          gelu_grad_in: Optional[torch.Tensor] = None, accumulate: int = 0, alpha: float = 1.0,
          bn: int = 0, bm: int = 0, max_ctas: int = 0, ready_flags: Optional[torch.Tensor] = None,
          flag_rows: int = 0, flag_on_b: bool = False, flag_epoch: int = 0, flag_spin_limit: int = 0,
-         rs_out=None, rs_rows_per_rank: int = 0, tile_m_rotate: int = 0) -> torch.Tensor:
+         rs_out=None, rs_rows_per_rank: int = 0, tile_m_rotate: int = 0, two_cta=None) -> torch.Tensor:
     """``D[M, N] = epilogue(A · Bᵀ)``.
 
     ``a``: ``(M, K)`` (or ``(K, M)`` when ``a_mn``); ``b``: ``(N, K)`` (or ``(K, N)`` when ``b_mn``).
@@ -89,8 +92,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         for i, ptr_ in enumerate(rs_out):
             p.rs_out[i] = ptr_
         p.rs_rows_per_rank = rs_rows_per_rank
-    code = nv.lib().fbam_gemm_bf16(nv.ptr(a), C.c_longlong(a.stride(0)), int(a_mn), nv.ptr(b),
-                                   C.c_longlong(b.stride(0)), int(b_mn), m, n, k, C.byref(p), nv.stream_ptr())
+    pair = TWO_CTA if two_cta is None else two_cta
+    if pair == "auto":
+        pair = (ready_flags is None and n >= 128 and n % 16 == 0 and bm != 128 and
+                ((m + 255) // 256) * ((n + 255) // 256) >= 148)
+    fn = nv.lib().fbam_gemm2_bf16 if pair and ready_flags is None else nv.lib().fbam_gemm_bf16
+    with debug.label(f"gemm{'2' if pair else ''} m{m} n{n} k{k} {'T' if a_mn else 'N'}{'T' if b_mn else 'N'}"):
+        code = fn(nv.ptr(a), C.c_longlong(a.stride(0)), int(a_mn), nv.ptr(b), C.c_longlong(b.stride(0)), int(b_mn),
+                  m, n, k, C.byref(p), nv.stream_ptr())
     nv.check(code, "fbam_gemm_bf16")
     debug.after_launch("gemm", a, b, out)
     return out
@@ -194,7 +203,7 @@ def _brick(n: int, h: int, w: int, total: int = 128) -> Tuple[int, int, int]:
 def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor, *, grid_hw, in_mul, taps,
               out_mul=1, out_off=(0, 0), accumulate=0, bn: int = 0, act: str = "none",
               preact_out: Optional[torch.Tensor] = None, gelu_grad_in: Optional[torch.Tensor] = None,
-              tile_rows: int = 0) -> None:
+              tile_rows: int = 0, two_cta=None) -> None:
     """One implicit-GEMM pass (see ``ConvGeom`` in csrc/gemm_tcgen05.h).  ``x`` NHWC bf16, ``wmat``
     ``(n_out, taps·C)`` bf16, ``out`` NHWC with ``n_out`` channels."""
     b, ih, iw, c = x.shape
@@ -205,6 +214,11 @@ def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor
     # the machine twice; 128-pixel bricks otherwise
     tn, th, tw = _brick(b, grid_hw[0], grid_hw[1], 256)
     tiles256 = math.ceil(b / tn) * math.ceil(grid_hw[0] / th) * math.ceil(grid_hw[1] / tw)
+    pair = TWO_CTA if two_cta is None else two_cta
+    if pair == "auto":
+        pair = tile_rows == 0 and n_out >= 128 and tiles256 >= 148
+    if pair:
+        tile_rows = 128          # each CTA of the pair owns one 128-pixel brick
     if tile_rows == 128 or n_out < 128 or (tile_rows == 0 and tiles256 < 2 * 148) or (tw - 1) * in_mul + 1 > 256 \
             or (th - 1) * in_mul + 1 > 256 or tn > 256:
         tn, th, tw = _brick(b, grid_hw[0], grid_hw[1], 128)
@@ -226,8 +240,10 @@ def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor
         p.preact_out = preact_out.data_ptr()
     if gelu_grad_in is not None:
         p.gelu_grad_in = gelu_grad_in.data_ptr()
-    code = nv.lib().fbam_conv_bf16(nv.ptr(x), ih, iw, c, nv.ptr(wmat), C.c_longlong(wmat.stride(0)), n_out,
-                                   C.byref(p), nv.stream_ptr())
+    fn = nv.lib().fbam_conv2_bf16 if pair else nv.lib().fbam_conv_bf16
+    with debug.label(f"conv{'2' if pair else ''} c{c} n{n_out} taps{len(taps)} in_mul{in_mul} out_mul{out_mul} {act}"):
+        code = fn(nv.ptr(x), ih, iw, c, nv.ptr(wmat), C.c_longlong(wmat.stride(0)), n_out, C.byref(p),
+                  nv.stream_ptr())
     nv.check(code, "fbam_conv_bf16")
     debug.after_launch("conv_pass", x, wmat, out)
 
@@ -560,13 +576,14 @@ class _LmHeadCe(torch.autograd.Function):
         for lo in range(0, rows, LM_HEAD_CHUNK_ROWS):
             hi = min(rows, lo + LM_HEAD_CHUNK_ROWS)
             xc = x[lo:hi]
-            logits = gemm(xc, w_head)                                    # (chunk, vpad) bf16
-            nv.check(nv.lib().fbam_ce_fwd_bwd(nv.ptr(logits), nv.ptr(targets[lo:hi]), nv.ptr(loss),
-                                              C.c_longlong(hi - lo), vocab, vpad, C.c_float(scale), int(need_grad),
-                                              nv.stream_ptr()), "fbam_ce_fwd_bwd")
-            if need_grad:                                                # logits now hold scale·(softmax − onehot)
-                gemm_nn(logits, w_head, out=dx[lo:hi])
-                gemm_tn(logits, xc, out=dw, accumulate=nv.GEMM_ACC_RMW)
+            logits = gemm(xc, w_head, out_dtype=torch.float32)           # (chunk, vpad) fp32 accumulators
+            dlogits = torch.empty(hi - lo, vpad, dtype=BF16, device=x.device) if need_grad else None
+            nv.check(nv.lib().fbam_ce_fwd_bwd_f32(nv.ptr(logits), nv.ptr(dlogits), nv.ptr(targets[lo:hi]),
+                                                  nv.ptr(loss), C.c_longlong(hi - lo), vocab, vpad, C.c_float(scale),
+                                                  nv.stream_ptr()), "fbam_ce_fwd_bwd_f32")
+            if need_grad:                                                # dlogits = scale·(softmax − onehot)
+                gemm_nn(dlogits, w_head, out=dx[lo:hi])
+                gemm_tn(dlogits, xc, out=dw, accumulate=nv.GEMM_ACC_RMW)
         ctx.save_for_backward(dx, dw)
         return loss.reshape(())
 

@@ -109,7 +109,9 @@ class Trainer:
         self.cursor: Optional[DatasetCursorCommitter] = None
         self._cuda = self.device.type == "cuda"
         if self._cuda:
-            self.h2d_stream = torch.cuda.Stream(device=self.device)
+            from .utils.streams import stream_bundle
+            self.streams = stream_bundle(self.device)
+            self.h2d_stream = self.streams.h2d
         self._staging: Dict[Tuple, torch.Tensor] = {}
 
     # ------------------------------------------------------------------------------------------
@@ -211,6 +213,11 @@ class Trainer:
                                       dropped=not committed, wall_start=wall0, wall_end=time.perf_counter()))
         if committed:
             self.step_count += 1
+        if self._cuda and self.step_count % 50 == 0:
+            from .utils.streams import allocator_metrics
+            m = allocator_metrics(self.device)
+            LOG("INFO", "allocator: peak {:.2f} GiB, current {:.2f} GiB, cached {:.2f} GiB, reserved {:.2f} GiB".format(
+                *(m[k] / 2 ** 30 for k in ("peak_bytes", "current_bytes", "cached_bytes", "reserved_bytes"))))
         return total
 
     # ------------------------------------------------------------------------------------------

@@ -21,6 +21,7 @@ def _flag(name: str) -> bool:
     return os.environ.get(name, "0") not in ("", "0", "false", "False")
 
 
+PROFILE_LABELS = _flag("FBAMTRAIN_PROFILE_LABELS")   # wrap every native launch in a record_function range
 SYNC_EVERY_OP = _flag("FBAMTRAIN_SYNC_EVERY_OP")
 POISON_ALLOC = _flag("FBAMTRAIN_POISON_ALLOC")
 DEBUG_KERNEL_LAUNCH = _flag("FBAMTRAIN_DEBUG_KERNEL_LAUNCH")
@@ -35,6 +36,14 @@ def fresh(shape, dtype, device) -> torch.Tensor:
         else:
             t.view(torch.uint8).fill_(0xFF)
     return t
+
+
+def label(name: str):
+    """Profiler range around a native launch (only when FBAMTRAIN_PROFILE_LABELS is set)."""
+    if PROFILE_LABELS:
+        return torch.profiler.record_function(name)
+    import contextlib
+    return contextlib.nullcontext()
 
 
 def after_launch(name: str, *args) -> None:

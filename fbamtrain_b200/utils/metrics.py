@@ -34,8 +34,9 @@ class LossRingBuffer:
         self.host = torch.zeros(RING_SLOTS, dtype=torch.float32)
         self.cuda = device.type == "cuda"
         if self.cuda:
+            from .streams import stream_bundle
             self.host = self.host.pin_memory()
-            self.d2h = torch.cuda.Stream(device=device)
+            self.d2h = stream_bundle(device).d2h
 
     def begin(self, step: int) -> None:
         self.ring[step % RING_SLOTS].zero_()

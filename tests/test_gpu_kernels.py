@@ -451,3 +451,38 @@ def test_reference_structure_model_streams_on_gpu():
         finally:
             ops.set_backend("auto")
     assert losses["auto"] == pytest.approx(losses["torch"], abs=5e-2)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(512, 256, 128), (1000, 520, 328), (4096, 4096, 1024), (304, 128, 64)])
+def test_gemm_cta_pairs(a_mn, b_mn, m, n, k):
+    """cta_group::2 kernel: two SMs per 256-row tile."""
+    nv, no = _nops()
+    torch.manual_seed(17)
+    a = torch.randn(m, k, device=DEV).to(BF)
+    b = torch.randn(n, k, device=DEV).to(BF)
+    d = no.gemm(a.t().contiguous() if a_mn else a, b.t().contiguous() if b_mn else b, a_mn=a_mn, b_mn=b_mn,
+                two_cta=True)
+    nv.check_status(a.device)
+    assert _rel_err(d, a.float() @ b.float().t()) < 5e-3
+    if not a_mn and not b_mn:
+        bias = torch.randn(n, device=DEV).to(BF)
+        d = no.gemm(a, b, bias=bias, act="gelu", two_cta=True)
+        assert_similar(torch.nn.functional.gelu(a.float() @ b.float().t() + bias.float()).to(BF), d, 0.25)
+        nv.check_status(a.device)
+
+
+@pytest.mark.parametrize("stride,pad,dil", [(2, 1, 1), (1, 2, 2)])
+def test_conv_cta_pairs(stride, pad, dil):
+    nv, no = _nops()
+    torch.manual_seed(18)
+    n, h, w, c, o = 9, 24, 80, 128, 256
+    x = torch.randn(n, h, w, c, device=DEV).to(BF)
+    wt = (torch.randn(o, 3, 3, c, device=DEV) / math.sqrt(9 * c)).to(BF)
+    expect = ref.conv2d_nhwc(x.float(), wt.float(), stride, pad, dil)
+    oh, ow = no.conv_out_hw(h, w, stride, pad, dil)
+    taps = [(r * dil - pad, s * dil - pad) for r in range(3) for s in range(3)]
+    y = torch.empty(n, oh, ow, o, device=DEV, dtype=BF)
+    no.conv_pass(x, wt.reshape(o, 9 * c), o, y, grid_hw=(oh, ow), in_mul=stride, taps=taps, two_cta=True)
+    nv.check_status(x.device)
+    assert _rel_err(y, expect) < 5e-3
