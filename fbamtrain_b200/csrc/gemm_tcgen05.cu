@@ -71,20 +71,24 @@ __device__ __forceinline__ long long row_offset(const GemmParams& p, int tile_m,
 }
 
 // Work item = (split, tile_m, tile_n): output tile plus the range of K blocks this CTA accumulates.
+// With split-K, split s takes K blocks s, s + splits, s + 2*splits, ...: concurrently running CTAs then stream
+// through neighbouring addresses together instead of starting many far-apart streams whose strides can all fall
+// onto the same memory channels.
 struct Work {
-  int tile_m, tile_n, k_begin, k_end;
+  int tile_m, tile_n, k_begin, k_end, k_step, split;
 };
 __device__ __forceinline__ Work decode_work(const GemmParams& p, int item, int tiles_n) {
   Work w;
   const int tiles = p.tiles_m * tiles_n;
   const int split = item / tiles;
   const int t = item % tiles;
+  w.split = split;
   w.tile_m = t / tiles_n;
   w.tile_n = t % tiles_n;
   if (p.tile_m_rotate > 0) w.tile_m = (w.tile_m + p.tile_m_rotate) % p.tiles_m;
-  const int per = (p.k_blocks + p.splits - 1) / p.splits;
-  w.k_begin = split * per;
-  w.k_end = min(p.k_blocks, w.k_begin + per);
+  w.k_begin = split;
+  w.k_end = p.k_blocks;
+  w.k_step = p.splits;
   return w;
 }
 
@@ -162,7 +166,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           if (!ok) break;
           asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy acquire -> async-proxy (TMA) reads
         }
-        for (int kb = wk.k_begin; kb < wk.k_end; ++kb) {
+        for (int kb = wk.k_begin; kb < wk.k_end; kb += wk.k_step) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
@@ -234,7 +238,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { ok = false; break; }
         fence_after_sync();
         const uint32_t d_tmem = tmem_base + (MH == 1 ? acc * BN : 0);
-        for (int kb = wk.k_begin; kb < wk.k_end; ++kb) {
+        for (int kb = wk.k_begin; kb < wk.k_end; kb += wk.k_step) {
           if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
           fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
@@ -245,7 +249,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
             for (int h = 0; h < MH; ++h) {   // M half h: rows [128h, 128h+128) = 16 KB further in either layout
               const uint64_t da = make_smem_desc_sw128(sa + h * 128 * 128 + k * a_kstep, a_lbo, 1024);
-              mma_f16_ss(d_tmem + h * BN, da, db, idesc, ((kb - wk.k_begin) | k) != 0);
+              mma_f16_ss(d_tmem + h * BN, da, db, idesc, ((kb - wk.k_begin) | k) != 0);   // first block overwrites
             }
           }
           mma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
@@ -280,7 +284,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         tmem_ld_32x32(taddr + c0, r);
         tmem_ld_wait();
         const int n0 = tile_n * BN + c0;
-        if (roff < 0 || n0 >= p.N || wk.k_end <= wk.k_begin) continue;
+        if (roff < 0 || n0 >= p.N) continue;
+        if (p.split_workspace != nullptr) {
+          // partial sums of this K split: plain vector stores into the split's slab (zeros for an empty range)
+          float* out = p.split_workspace + (long long)wk.split * p.split_stride + roff + n0;
+          const bool empty = wk.k_end <= wk.k_begin;
+          if (n0 + 32 <= p.N && (p.ldd % 4 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>(out + j) =
+                  empty ? make_float4(0, 0, 0, 0)
+                        : make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                      __uint_as_float(r[j + 3]));
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) out[j] = empty ? 0.0f : __uint_as_float(r[j]);
+          }
+          continue;
+        }
+        if (wk.k_end <= wk.k_begin) continue;
         gemm_epi::store_chunk(p, roff, n0, r);
       }
       fence_before_sync();
@@ -411,7 +433,8 @@ extern "C" int fbam_gemm_bf16(const void* A, long long lda, int a_mn_major, cons
   p.k_blocks = (K + BK - 1) / BK;
   if (p.splits < 1) p.splits = 1;
   if (p.splits > p.k_blocks) p.splits = p.k_blocks;
-  if (p.splits > 1 && !(p.out_fp32 && p.accumulate == GEMM_ACC_ATOMIC)) return GEMM_ERR_SHAPE;
+  if (p.splits > 1 && p.split_workspace == nullptr && !(p.out_fp32 && p.accumulate == GEMM_ACC_ATOMIC))
+    return GEMM_ERR_SHAPE;
   const int bn = pick_bn(N, p.bn);
   const int BM = pick_bm(M, N, bn, p.bm);
   p.tiles_m = (M + BM - 1) / BM;

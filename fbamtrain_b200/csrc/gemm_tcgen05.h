@@ -42,6 +42,10 @@ struct GemmParams {
   int bm;                           // 0 = choose from the tile count; else 128 / 256 (plain GEMM and wgrad)
   int max_ctas;                     // 0 = one per SM
   int splits;                       // split-K factor (needs fp32 output with atomic accumulation); 0/1 = none
+  // split-K without atomics: split s writes its partial tile to split_workspace + s * split_stride (fp32,
+  // same pitch as D) with plain stores; the caller sums the partials afterwards
+  float* split_workspace;
+  long long split_stride;
   // all-gather -> GEMM: rows of the gated operand arrive from peers; rows [i*flag_rows, (i+1)*flag_rows) are
   // complete once ready_flags[i] >= flag_epoch (ready_flags is in local memory; peers store to it)
   const unsigned* ready_flags;

@@ -45,6 +45,7 @@ class GemmParams(C.Structure):
                 ("alpha", C.c_float),
                 ("out_fp32", C.c_int), ("bias_fp32", C.c_int), ("act", C.c_int), ("accumulate", C.c_int),
                 ("bn", C.c_int), ("bm", C.c_int), ("max_ctas", C.c_int), ("splits", C.c_int),
+                ("split_workspace", C.c_void_p), ("split_stride", C.c_longlong),
                 ("ready_flags", C.c_void_p), ("tile_m_rotate", C.c_int), ("flag_rows", C.c_int), ("flag_on_b", C.c_int),
                 ("flag_epoch", C.c_uint), ("flag_spin_limit", C.c_uint),
                 ("rs_out", C.c_void_p * 8), ("rs_rows_per_rank", C.c_int),

@@ -94,7 +94,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         p.rs_rows_per_rank = rs_rows_per_rank
     pair = TWO_CTA if two_cta is None else two_cta
     if pair == "auto":
-        pair = (ready_flags is None and n >= 128 and n % 16 == 0 and bm != 128 and
+        pair = (ready_flags is None and n >= 256 and n % 16 == 0 and bm != 128 and
                 ((m + 255) // 256) * ((n + 255) // 256) >= 148)
     fn = nv.lib().fbam_gemm2_bf16 if pair and ready_flags is None else nv.lib().fbam_gemm_bf16
     with debug.label(f"gemm{'2' if pair else ''} m{m} n{n} k{k} {'T' if a_mn else 'N'}{'T' if b_mn else 'N'}"):
@@ -215,8 +215,8 @@ def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor
     tn, th, tw = _brick(b, grid_hw[0], grid_hw[1], 256)
     tiles256 = math.ceil(b / tn) * math.ceil(grid_hw[0] / th) * math.ceil(grid_hw[1] / tw)
     pair = TWO_CTA if two_cta is None else two_cta
-    if pair == "auto":
-        pair = tile_rows == 0 and n_out >= 128 and tiles256 >= 148
+    if pair == "auto":      # pairs pay off only with 256-wide tiles (a 128-wide pair tile fetches as much as one CTA)
+        pair = tile_rows == 0 and n_out >= 256 and tiles256 >= 148
     if pair:
         tile_rows = 128          # each CTA of the pair owns one 128-pixel brick
     if tile_rows == 128 or n_out < 128 or (tile_rows == 0 and tiles256 < 2 * 148) or (tw - 1) * in_mul + 1 > 256 \
