@@ -299,17 +299,290 @@ lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all
   }
 }
 
+// -------------------------------------------------------------------------------------------------
+// hidden sizes above 1024 (up to 2048): the W_hh slice of a CTA (256 KB at H = 2048) no longer fits in
+// registers alone, so the kernels below run 16 warps and keep the first RKS k-steps of every warp in
+// registers and the remaining SKS in shared memory, stored fragment by fragment (one conflict-free 16-byte
+// read per thread and MMA).  Everything else follows the kernels above.
+// -------------------------------------------------------------------------------------------------
+constexpr int kBigWarps = 16;
+constexpr int kBigThreads = kBigWarps * 32;
+
+template <int RKS, int SKS>  // H <= (RKS + SKS) * 16 warps * 16
+__global__ void __launch_bounds__(kBigThreads, 1)
+lstm_fwd_big_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const float* __restrict__ h0,
+                    const float* __restrict__ c0, bf16* __restrict__ y, float* __restrict__ c_all, bf16* hbuf,
+                    unsigned* counter, int* status, int T, int B, int H, int per_sample) {
+  extern __shared__ uint4 dyn_smem[];
+  uint4* wsm = dyn_smem;                                                  // [SKS * 4][512] A fragments
+  bf16* hs = reinterpret_cast<bf16*>(dyn_smem + SKS * 4 * kBigThreads);   // [8][H + 8]
+  const int hs_ld = H + 8;
+  float* part = reinterpret_cast<float*>(hs + 8 * hs_ld);                 // [16 warps][4 tiles][16][8]
+  float* pre = part + kBigWarps * 4 * 128;                                // [64][8]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int unit0 = blockIdx.x * 16;  // 16 hidden units = 64 gate rows: tile = (unit group of 8) * 2 + {i|f, g|o}
+  const int nks = H / 16;
+
+  auto load_frag = [&](int tile, int ks, uint32_t (&a)[4]) {
+    const bool on = ks < nks;
+    const int k = ks * 16 + q * 2;
+    const int unit = unit0 + (tile >> 1) * 8 + g;
+    const bf16* r_lo = whh + ((long long)((tile & 1) * 2) * H + unit) * H;
+    const bf16* r_hi = whh + ((long long)((tile & 1) * 2 + 1) * H + unit) * H;
+    a[0] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k) : 0u;
+    a[1] = on ? *reinterpret_cast<const uint32_t*>(r_hi + k) : 0u;
+    a[2] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k + 8) : 0u;
+    a[3] = on ? *reinterpret_cast<const uint32_t*>(r_hi + k + 8) : 0u;
+  };
+  uint32_t afrag[RKS][4][4];
+#pragma unroll
+  for (int j = 0; j < RKS; ++j)
+#pragma unroll
+    for (int tile = 0; tile < 4; ++tile) load_frag(tile, warp + kBigWarps * j, afrag[j][tile]);
+#pragma unroll
+  for (int j = 0; j < SKS; ++j)
+#pragma unroll
+    for (int tile = 0; tile < 4; ++tile) {
+      uint32_t a[4];
+      load_frag(tile, warp + kBigWarps * (RKS + j), a);
+      wsm[(j * 4 + tile) * kBigThreads + threadIdx.x] = make_uint4(a[0], a[1], a[2], a[3]);
+    }
+
+  const int u = threadIdx.x >> 3, b = threadIdx.x & 7;  // threads 0..127 own (unit u of 16, batch b)
+  float c = 0.0f;
+  if (threadIdx.x < 128) {
+    const long long si = per_sample ? (long long)min(b, B - 1) * H + unit0 + u : unit0 + u;
+    c = c0[si];
+    hbuf[(long long)b * H + unit0 + u] = __float2bfloat16(h0[si]);
+  }
+  // every thread owns one (gate row of 64, batch) pre-activation, fetched one step ahead of its use
+  const int prow = threadIdx.x >> 3, pbb = threadIdx.x & 7;
+  const int ptile = prow >> 4, pr = prow & 15;
+  const long long pre_off = (long long)((ptile & 1) * 2 + (pr >> 3)) * H + unit0 + (ptile >> 1) * 8 + (pr & 7);
+  float xg_next = 0.0f;
+  if (pbb < B) xg_next = gates[(long long)pbb * 4 * H + pre_off];
+  unsigned bar = 0;
+  if (!grid_barrier(counter, ++bar * gridDim.x, status)) return;
+
+  for (int t = 0; t < T; ++t) {
+    const float xg = xg_next;
+    const bf16* hprev = hbuf + (long long)(t & 1) * 8 * H;
+    bf16* hnext = hbuf + (long long)((t + 1) & 1) * 8 * H;
+    for (int cc = threadIdx.x; cc < H; cc += kBigThreads) {
+      const int row = cc / (H / 8), col = (cc % (H / 8)) * 8;
+      *reinterpret_cast<uint4*>(hs + row * hs_ld + col) =
+          __ldcg(reinterpret_cast<const uint4*>(hprev + (long long)row * H + col));
+    }
+    __syncthreads();
+    float acc[4][4];
+#pragma unroll
+    for (int tile = 0; tile < 4; ++tile)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[tile][i] = 0.0f;
+#pragma unroll
+    for (int j = 0; j < RKS + SKS; ++j) {
+      const int ks = warp + kBigWarps * j;
+      if (ks < nks) {
+        const bf16* hp = hs + g * hs_ld + ks * 16 + q * 2;
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(hp);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(hp + 8);
+#pragma unroll
+        for (int tile = 0; tile < 4; ++tile) {
+          if (j < RKS) {
+            mma_16816(acc[tile], afrag[j < RKS ? j : 0][tile], b0, b1);
+          } else {
+            const uint4 w = wsm[((j - RKS) * 4 + tile) * kBigThreads + threadIdx.x];
+            const uint32_t a[4] = {w.x, w.y, w.z, w.w};
+            mma_16816(acc[tile], a, b0, b1);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int tile = 0; tile < 4; ++tile) {
+      float* pt = part + (warp * 4 + tile) * 128;
+      pt[g * 8 + q * 2] = acc[tile][0];
+      pt[g * 8 + q * 2 + 1] = acc[tile][1];
+      pt[(g + 8) * 8 + q * 2] = acc[tile][2];
+      pt[(g + 8) * 8 + q * 2 + 1] = acc[tile][3];
+    }
+    __syncthreads();
+    {
+      float s = 0.0f;  // thread = (row of 64, batch): row = tile * 16 + r
+#pragma unroll
+      for (int w = 0; w < kBigWarps; ++w) s += part[(w * 4 + ptile) * 128 + pr * 8 + pbb];
+      pre[prow * 8 + pbb] = s + xg;
+    }
+    __syncthreads();
+    if (threadIdx.x < 128) {
+      const int base = (u >> 3) * 32 + (u & 7);  // tile pair of the unit group; rows +0 i, +8 f, +16 g, +24 o
+      const float ig = sigmoid_f(pre[base * 8 + b]), fg = sigmoid_f(pre[(base + 8) * 8 + b]);
+      const float gg = tanhf(pre[(base + 16) * 8 + b]), og = sigmoid_f(pre[(base + 24) * 8 + b]);
+      c = fg * c + ig * gg;
+      const float h = og * tanhf(c);
+      const bf16 hb = __float2bfloat16(h);
+      if (b < B) {
+        float* gt = gates + ((long long)t * B + b) * 4 * H + unit0 + u;
+        gt[0] = ig; gt[H] = fg; gt[2 * (long long)H] = gg; gt[3 * (long long)H] = og;
+        y[((long long)t * B + b) * H + unit0 + u] = hb;
+        c_all[((long long)t * B + b) * H + unit0 + u] = c;
+        hnext[(long long)b * H + unit0 + u] = hb;
+      } else {
+        hnext[(long long)b * H + unit0 + u] = __float2bfloat16(0.0f);
+      }
+    }
+    if (pbb < B && t + 1 < T) xg_next = gates[((long long)(t + 1) * B + pbb) * 4 * H + pre_off];
+    if (!grid_barrier(counter, ++bar * gridDim.x, status)) return;
+  }
+}
+
+// Backward: the CTA's 16 rows of W_hh^T span K = 4H (8192 at H = 2048).  dGates[t] is staged in two halves of K
+// so that the staging buffer and the shared-memory part of the weights fit together; the first half's k-steps
+// use the register fragments, the second half's the shared-memory ones.
+template <int HKS>  // k-steps per warp and half: 4H <= 2 * HKS * 16 warps * 16
+__global__ void __launch_bounds__(kBigThreads, 1)
+lstm_bwd_big_kernel(const float* __restrict__ gates, const float* __restrict__ c_all, const float* __restrict__ c0,
+                    const bf16* __restrict__ dy, const bf16* __restrict__ whh_t, bf16* dgates,
+                    float* __restrict__ dh0, float* __restrict__ dc0, const float* __restrict__ dh_last,
+                    const float* __restrict__ dc_last, unsigned* counter, int* status, int T, int B, int H,
+                    int per_sample) {
+  extern __shared__ uint4 dyn_smem[];
+  uint4* wsm = dyn_smem;                                              // [HKS][512] A fragments (second half of K)
+  bf16* ds = reinterpret_cast<bf16*>(dyn_smem + HKS * kBigThreads);   // [8][K/2 + 8]: half of dGates[t]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int unit0 = blockIdx.x * 16;
+  const int K = 4 * H, kh = K / 32;  // k-steps per half
+  const int ds_ld = K / 2 + 8;
+  float* part = reinterpret_cast<float*>(ds + 8 * ds_ld);             // [16 warps][16][8]
+  for (int cc = threadIdx.x; cc < 8 * ds_ld / 8; cc += kBigThreads)   // rows >= B stay zero
+    reinterpret_cast<uint4*>(ds)[cc] = make_uint4(0, 0, 0, 0);
+
+  auto load_frag = [&](int ks, bool on, uint32_t (&a)[4]) {
+    const int k = ks * 16 + q * 2;
+    const bf16* r_lo = whh_t + (long long)(unit0 + g) * K;
+    const bf16* r_hi = whh_t + (long long)(unit0 + g + 8) * K;
+    a[0] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k) : 0u;
+    a[1] = on ? *reinterpret_cast<const uint32_t*>(r_hi + k) : 0u;
+    a[2] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k + 8) : 0u;
+    a[3] = on ? *reinterpret_cast<const uint32_t*>(r_hi + k + 8) : 0u;
+  };
+  uint32_t afrag[HKS][4];
+#pragma unroll
+  for (int j = 0; j < HKS; ++j) {
+    const int ks = warp + kBigWarps * j;
+    load_frag(ks, ks < kh, afrag[j]);
+    uint32_t a[4];
+    load_frag(kh + ks, ks < kh, a);
+    wsm[j * kBigThreads + threadIdx.x] = make_uint4(a[0], a[1], a[2], a[3]);
+  }
+
+  const int u = threadIdx.x >> 3, b = threadIdx.x & 7;
+  const bool owner = threadIdx.x < 128 && b < B;
+  const int unit = unit0 + (u & 15);
+  float dh_next = 0.0f, dc_next = 0.0f;
+  if (owner) {
+    if (dh_last != nullptr) dh_next = dh_last[(long long)b * H + unit];
+    if (dc_last != nullptr) dc_next = dc_last[(long long)b * H + unit];
+  }
+  unsigned bar = 0;
+  float n_ig = 0, n_fg = 0, n_gg = 0, n_og = 0, n_ct = 0, n_cp = 0, n_dy = 0;
+  if (owner) {
+    const int t = T - 1;
+    const float* gt = gates + ((long long)t * B + b) * K + unit;
+    n_ig = gt[0]; n_fg = gt[H]; n_gg = gt[2 * (long long)H]; n_og = gt[3 * (long long)H];
+    n_ct = c_all[((long long)t * B + b) * H + unit];
+    n_cp = t > 0 ? c_all[((long long)(t - 1) * B + b) * H + unit] : c0[per_sample ? (long long)b * H + unit : unit];
+    n_dy = __bfloat162float(dy[((long long)t * B + b) * H + unit]);
+  }
+
+  for (int t = T - 1; t >= 0; --t) {
+    if (owner) {
+      const float ig = n_ig, fg = n_fg, gg = n_gg, og = n_og, ct = n_ct, cp = n_cp;
+      const float dh = n_dy + dh_next;
+      const float tc = tanhf(ct);
+      const float d_o = dh * tc * og * (1.0f - og);
+      const float dc = dh * og * (1.0f - tc * tc) + dc_next;
+      const float d_i = dc * gg * ig * (1.0f - ig);
+      const float d_f = dc * cp * fg * (1.0f - fg);
+      const float d_g = dc * ig * (1.0f - gg * gg);
+      dc_next = dc * fg;
+      bf16* dg = dgates + ((long long)t * B + b) * K + unit;
+      dg[0] = __float2bfloat16(d_i);
+      dg[H] = __float2bfloat16(d_f);
+      dg[2 * (long long)H] = __float2bfloat16(d_g);
+      dg[3 * (long long)H] = __float2bfloat16(d_o);
+      if (t > 0) {
+        const int tn = t - 1;
+        const float* gt = gates + ((long long)tn * B + b) * K + unit;
+        n_ig = gt[0]; n_fg = gt[H]; n_gg = gt[2 * (long long)H]; n_og = gt[3 * (long long)H];
+        n_ct = cp;
+        n_cp = tn > 0 ? c_all[((long long)(tn - 1) * B + b) * H + unit]
+                      : c0[per_sample ? (long long)b * H + unit : unit];
+        n_dy = __bfloat162float(dy[((long long)tn * B + b) * H + unit]);
+      }
+    }
+    if (!grid_barrier(counter, ++bar * gridDim.x, status)) return;
+    const bf16* dgt = dgates + (long long)t * B * K;
+    float acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int hcols = K / 2;
+      for (int cc = threadIdx.x; cc < B * (hcols / 8); cc += kBigThreads) {
+        const int row = cc / (hcols / 8), col = (cc % (hcols / 8)) * 8;
+        *reinterpret_cast<uint4*>(ds + row * ds_ld + col) =
+            __ldcg(reinterpret_cast<const uint4*>(dgt + (long long)row * K + half * hcols + col));
+      }
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < HKS; ++j) {
+        const int ks = warp + kBigWarps * j;
+        if (ks < kh) {
+          const bf16* p = ds + g * ds_ld + ks * 16 + q * 2;
+          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(p), b1 = *reinterpret_cast<const uint32_t*>(p + 8);
+          if (half == 0) {
+            mma_16816(acc[j & 1], afrag[j], b0, b1);
+          } else {
+            const uint4 w = wsm[j * kBigThreads + threadIdx.x];
+            const uint32_t a[4] = {w.x, w.y, w.z, w.w};
+            mma_16816(acc[j & 1], a, b0, b1);
+          }
+        }
+      }
+      __syncthreads();
+    }
+    float* pt = part + warp * 128;
+    pt[g * 8 + q * 2] = acc[0][0] + acc[1][0];
+    pt[g * 8 + q * 2 + 1] = acc[0][1] + acc[1][1];
+    pt[(g + 8) * 8 + q * 2] = acc[0][2] + acc[1][2];
+    pt[(g + 8) * 8 + q * 2 + 1] = acc[0][3] + acc[1][3];
+    __syncthreads();
+    if (threadIdx.x < 128) {
+      float s = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kBigWarps; ++w) s += part[w * 128 + u * 8 + b];
+      dh_next = s;
+    }
+    __syncthreads();
+  }
+  if (owner) {
+    dh0[(long long)b * H + unit] = dh_next;
+    dc0[(long long)b * H + unit] = dc_next;
+  }
+}
+
 template <typename K>
-int coop_launch(K kernel, int grid, void** args, size_t smem, cudaStream_t stream) {
+int coop_launch(K kernel, int grid, void** args, size_t smem, cudaStream_t stream, int threads = kThreads) {
   int dev = 0, sms = 0, per_sm = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return 5;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem) != cudaSuccess) return 5;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess) return 5;
   if (grid > sms * per_sm) return 1;  // all CTAs must be co-resident
-  return cudaLaunchCooperativeKernel((void*)kernel, dim3(grid), dim3(kThreads), args, smem, stream) == cudaSuccess
+  return cudaLaunchCooperativeKernel((void*)kernel, dim3(grid), dim3(threads), args, smem, stream) == cudaSuccess
              ? 0 : 5;
 }
 
@@ -318,16 +591,21 @@ int coop_launch(K kernel, int grid, void** args, size_t smem, cudaStream_t strea
 extern "C" {
 
 // Largest hidden size the register-resident kernels accept (and the batch limit is 8).
-int fbam_lstm_persistent_max_hidden() { return 1024; }
+int fbam_lstm_persistent_max_hidden() { return 2048; }
 
 // gates: (T, B, 4H) fp32, pre-activations incl. bias on entry, activated gates on exit.
 // hbuf: 2*8*H bf16 scratch; counter: one zeroed unsigned.
 int fbam_lstm_fwd_ex(float* gates, const void* whh, const float* h0, const float* c0, void* y, float* c_all,
                      void* hbuf, unsigned* counter, int* status, int T, int B, int H, int per_sample, void* stream) {
-  if (B < 1 || B > 8 || H % 16 != 0 || H > 1024 || T < 1) return 1;
+  if (B < 1 || B > 8 || H % 16 != 0 || H > 2048 || T < 1) return 1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(counter, 0, sizeof(unsigned), s) != cudaSuccess) return 5;
   void* args[] = {&gates, &whh, &h0, &c0, &y, &c_all, &hbuf, &counter, &status, &T, &B, &H, &per_sample};
+  if (H > 1024) {  // 16 units per CTA; half of each warp's 8 k-steps in registers, half in shared memory
+    const size_t big = (size_t)4 * 4 * kBigThreads * 16 + (size_t)8 * (H + 8) * sizeof(bf16) +
+                       (size_t)(kBigWarps * 4 * 128 + 64 * 8) * sizeof(float);
+    return coop_launch(lstm_fwd_big_kernel<4, 4>, H / 16, args, big, s, kBigThreads);
+  }
   const int grid = H / 8;
   const size_t smem = (size_t)8 * (H + 8) * sizeof(bf16);
   if (H <= 256) return coop_launch(lstm_fwd_kernel<2>, grid, args, smem, s);
@@ -345,11 +623,16 @@ int fbam_lstm_fwd(float* gates, const void* whh, const float* h0, const float* c
 int fbam_lstm_bwd_ex(const float* gates, const float* c_all, const float* c0, const void* dy, const void* whh_t,
                      void* dgates, float* dh0, float* dc0, const float* dh_last, const float* dc_last,
                      unsigned* counter, int* status, int T, int B, int H, int per_sample, void* stream) {
-  if (B < 1 || B > 8 || H % 16 != 0 || H > 1024 || T < 1) return 1;
+  if (B < 1 || B > 8 || H % 16 != 0 || H > 2048 || T < 1) return 1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(counter, 0, sizeof(unsigned), s) != cudaSuccess) return 5;
   void* args[] = {&gates, &c_all, &c0, &dy, &whh_t, &dgates, &dh0, &dc0, &dh_last, &dc_last, &counter, &status,
                   &T, &B, &H, &per_sample};
+  if (H > 1024) {
+    const size_t big = (size_t)16 * kBigThreads * 16 + (size_t)8 * (2 * H + 8) * sizeof(bf16) +
+                       (size_t)kBigWarps * 128 * sizeof(float);
+    return coop_launch(lstm_bwd_big_kernel<16>, H / 16, args, big, s, kBigThreads);
+  }
   const int grid = H / 16;
   const size_t smem = (size_t)8 * (4 * H + 8) * sizeof(bf16);
   if (H <= 256) return coop_launch(lstm_bwd_kernel<8>, grid, args, smem, s);

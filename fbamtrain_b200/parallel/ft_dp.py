@@ -128,11 +128,15 @@ class FaultTolerantDataParallel:
         else:
             grads = [g.grad for g in trainer.all_groups()]
             if peer.world_size > 1:
+                epoch_before, t0 = peer.epoch, time.perf_counter()
                 res, info = peer.all_reduce_multiple_with_retry(grads, [(trainer.step_count << 8) | k
                                                                         for k in range(len(grads))],
                                                                 min_world=self.min_world)
                 self.tx_bytes += info.tx_bytes
                 self.rx_bytes += info.rx_bytes
+                if peer.epoch != epoch_before:    # a peer fell out during the collective; the retry re-formed the group
+                    self.events.append({"epoch": peer.epoch, "world": peer.world_size, "step": trainer.step_count,
+                                        "seconds": time.perf_counter() - t0})
                 if res != Result.SUCCESS:
                     return self._drop(trainer, res.name)
                 scale = self.expected_world / max(1, peer.world_size)
