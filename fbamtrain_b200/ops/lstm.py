@@ -10,7 +10,7 @@ the gates in the backward pass (reference: ``tensorlib/src/streaming_lstm_fwd.cp
 ``streaming_lstm_bwd.cpp:1218-1307``); here the activated gates are kept (in the buffer that held the
 pre-activations), so nothing is recomputed.
 
-Shapes beyond the persistent kernels' limits (hidden > 1024 or batch > 8) run step by step: a GEMM
+Shapes beyond the persistent kernels' limits (hidden > 2048 or batch > 8) run step by step: a GEMM
 per step against ``W_hh`` followed by the same gate arithmetic.
 """
 from __future__ import annotations

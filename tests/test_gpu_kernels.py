@@ -277,7 +277,8 @@ def test_model_step_native_vs_reference_path():
     assert losses["auto"] == pytest.approx(losses["torch"], abs=5e-2)
 
 
-@pytest.mark.parametrize("t_len,b,i_dim,h", [(5, 2, 64, 64), (33, 8, 128, 256), (16, 3, 256, 1024)])
+@pytest.mark.parametrize("t_len,b,i_dim,h", [(5, 2, 64, 64), (33, 8, 128, 256), (16, 3, 256, 1024),
+                                             (9, 4, 128, 2048), (7, 8, 64, 1536)])
 def test_persistent_lstm_fwd_bwd(t_len, b, i_dim, h):
     nv, no = _nops()
     from fbamtrain_b200.ops import lstm as L
