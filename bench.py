@@ -206,7 +206,7 @@ def run_ours(args) -> dict:
         "model_tflop_per_step_per_gpu": flops / 1e12,
         "final_loss": last_loss,
         "config": {"model": args.model, "global_batch": micro * world, "micro_batch_per_gpu": micro, "seq_len": seq,
-                   "parallelism": f"dp{world}" + (f"-{args.dp_mode}" if world > 1 else ""), "optimizer": "adamw",
+                   "parallelism": f"dp{world}" + (f"-{args.dp_mode}" if world > 1 else ""), "optimizer": cfg.optimizer_config.type,
                    "l2_policy": "inputs larger than L2 (≈0.75 GB of frames and >10 GB of activations per step)",
                    "frame_chunk": args.frame_chunk},
         "clocks": clocks,

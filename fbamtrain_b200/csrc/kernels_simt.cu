@@ -663,6 +663,48 @@ int launch_rms_bwd(const bf16* dy, const bf16* x, const bf16* w, const float* rs
   return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 
+
+// -------------------------------------------------------------------------------------------------
+// 128-bit content fingerprint of a buffer (shared-state comparison between peers): the sum, over all 8-byte
+// words, of two independent 64-bit mixes of (word, index).  Sums commute, so the result does not depend on how
+// the words are spread over threads.  A fingerprint for equality checks between cooperating peers, not a
+// cryptographic hash.
+// -------------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+__global__ void fingerprint_kernel(const unsigned long long* __restrict__ words, long long n_words,
+                                   const unsigned char* __restrict__ tail, int tail_bytes,
+                                   unsigned long long* __restrict__ out) {
+  unsigned long long h0 = 0, h1 = 0;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += stride) {
+    const unsigned long long w = words[i];
+    const unsigned long long a = mix64(w + (unsigned long long)(i + 1) * 0x9E3779B97F4A7C15ull);
+    h0 += a;
+    h1 += mix64((a ^ 0xD6E8FEB86659FD93ull) + w);
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0 && tail_bytes > 0) {
+    unsigned long long w = 0;
+    for (int b = 0; b < tail_bytes; ++b) w |= (unsigned long long)tail[b] << (8 * b);
+    const unsigned long long a = mix64(w + (unsigned long long)(n_words + 1) * 0x9E3779B97F4A7C15ull);
+    h0 += a;
+    h1 += mix64((a ^ 0xD6E8FEB86659FD93ull) + w + (unsigned long long)tail_bytes);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    h0 += __shfl_xor_sync(0xffffffffu, h0, o);
+    h1 += __shfl_xor_sync(0xffffffffu, h1, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    atomicAdd(out, h0);
+    atomicAdd(out + 1, h1);
+  }
+}
+
 }  // namespace
 
 #define STREAM(s) reinterpret_cast<cudaStream_t>(s)
@@ -814,6 +856,20 @@ int fbam_adamw(void* param, const void* grad, float* m, float* v, float* master,
   else
     adamw_kernel<float><<<blocks, 256, 0, STREAM(stream)>>>((float*)param, (const float*)grad, m, v, master, n, lr, b1,
                                                             b2, eps, wd, 1.0f / bc1, 1.0f / bc2, grad_scale);
+  return CHECK_LAUNCH();
+}
+
+// out: two zero-initialised 64-bit words in device memory; data must be 8-byte aligned.
+int fbam_fingerprint(const void* data, long long n_bytes, unsigned long long* out, void* stream) {
+  if (n_bytes < 0 || (reinterpret_cast<uintptr_t>(data) & 7) != 0) return 1;
+  if (n_bytes == 0) return 0;
+  const long long n_words = n_bytes / 8;
+  const int tail = (int)(n_bytes % 8);
+  long long blocks = (n_words + 256 * 8 - 1) / (256 * 8);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  fingerprint_kernel<<<(unsigned)blocks, 256, 0, STREAM(stream)>>>(
+      (const unsigned long long*)data, n_words, (const unsigned char*)data + n_words * 8, tail, out);
   return CHECK_LAUNCH();
 }
 

@@ -41,6 +41,7 @@ class FaultTolerantDataParallel:
         self.events: List[dict] = []          # topology changes with timestamps (recovery-time accounting)
         self.tx_bytes = self.rx_bytes = 0
         self.dropped_steps = 0
+        self.ready_gate = None                # optional callable run right before a late joiner connects
 
     # the trainer reads these
     @property
@@ -99,6 +100,13 @@ class FaultTolerantDataParallel:
         return ok
 
     def attach(self, trainer) -> None:
+        if self.peer.uid is None:
+            # a peer that joins a running group builds its model first and only then announces itself, so that
+            # the members are not held at their phase gate while it initialises
+            if self.ready_gate is not None:
+                self.ready_gate()
+            if self.peer.connect() != Result.SUCCESS:
+                raise RuntimeError("ftccl: cannot reach the membership master")
         joining = trainer.step_count == 0 and self.peer.epoch == 0 and getattr(self, "late_joiner", False)
         if not self._retopologize(trainer, joining):
             raise RuntimeError("ftccl: could not join the training group")

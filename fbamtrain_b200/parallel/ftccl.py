@@ -301,9 +301,34 @@ def _free_port(ip: str) -> int:
 
 
 def tensor_hash(t: torch.Tensor) -> str:
-    data = t.detach().contiguous().cpu()
-    raw = data.view(torch.uint8).numpy().tobytes() if data.numel() else b""
-    return hashlib.blake2b(raw, digest_size=16).hexdigest()
+    return tensor_hashes([t])[0]
+
+
+def tensor_hashes(tensors: Sequence[torch.Tensor]) -> List[str]:
+    """Content fingerprints.  CUDA tensors are fingerprinted on the device (one kernel per tensor, one read-back
+    for all of them); host tensors with BLAKE2b.  Peers only compare fingerprints of the same kind."""
+    out: List[Optional[str]] = [None] * len(tensors)
+    on_gpu = [i for i, t in enumerate(tensors) if t.is_cuda and t.numel()]
+    if on_gpu:
+        import ctypes as C
+        from ..ops import native as nv
+        dev = tensors[on_gpu[0]].device
+        words = torch.zeros(len(on_gpu), 2, dtype=torch.int64, device=dev)
+        keep = []
+        for slot, i in enumerate(on_gpu):
+            data = tensors[i].detach().contiguous()
+            keep.append(data)
+            nv.check(nv.lib().fbam_fingerprint(nv.ptr(data), C.c_longlong(data.numel() * data.element_size()),
+                                               nv.ptr(words[slot]), nv.stream_ptr()), "fbam_fingerprint")
+        host = words.cpu()
+        for slot, i in enumerate(on_gpu):
+            out[i] = f"{int(host[slot, 0]) & (2 ** 64 - 1):016x}{int(host[slot, 1]) & (2 ** 64 - 1):016x}"
+    for i, t in enumerate(tensors):
+        if out[i] is None:
+            data = t.detach().contiguous().cpu()
+            raw = data.view(torch.uint8).numpy().tobytes() if data.numel() else b""
+            out[i] = hashlib.blake2b(raw, digest_size=16).hexdigest()
+    return out
 
 
 class FtPeer:
@@ -395,6 +420,10 @@ class FtPeer:
         store = res["store"]
         backend = "nccl" if self.device.type == "cuda" else "gloo"
         kwargs = {"device_id": self.device} if self.device.type == "cuda" else {}
+        # Process-group names restart from "0" after destroy_process_group(); caches keyed by group name (the
+        # symmetric-memory rendezvous among them) must not see an old epoch's group under a new epoch's name.
+        import torch.distributed.distributed_c10d as c10d
+        c10d._world.group_count = max(c10d._world.group_count, 64 * self.epoch)
         try:
             dist.init_process_group(backend, init_method=f"tcp://{store['ip']}:{store['port']}", rank=self.rank,
                                     world_size=self.world_size,
@@ -489,10 +518,10 @@ class FtPeer:
         if self.world_size <= 1:
             return Result.SUCCESS, out
         h = hashlib.blake2b(digest_size=16)
-        for ti in infos:
-            if not ti.allow_content_inequality:
-                h.update(ti.name.encode())
-                h.update(tensor_hash(ti.tensor).encode())
+        compared = [ti for ti in infos if not ti.allow_content_inequality]
+        for ti, digest in zip(compared, tensor_hashes([ti.tensor for ti in compared])):
+            h.update(ti.name.encode())
+            h.update(digest.encode())
         mine = (int(revision), h.hexdigest(), strategy.value)
         try:
             everyone: List[Optional[tuple]] = [None] * self.world_size

@@ -164,7 +164,7 @@ class TwoStagePipeline:
         e = self.model.cfg.n_embed
         am = self.action
         dtype = am.head_weight.dtype
-        total = 0.0
+        total = torch.zeros((), dtype=torch.float32, device=self.device)   # summed on the device: no host sync
         sends = []
         bufs = [torch.empty(self.slice_rows, e, dtype=dtype, device=self.device) for _ in range(2)]
         recv = self._irecv(bufs[0])
@@ -176,7 +176,7 @@ class TwoStagePipeline:
             full = self.tp.all_gather_rows(mine).view(self.mb_size, self.seq, e).requires_grad_(True)
             loss = am(full, targets[k].to(self.device), loss_scale)
             loss.backward()
-            total += float(loss.detach())
+            total += loss.detach().float()
             d_emb = full.grad.reshape(self.mb_size * self.seq, e)
             self.tp.all_reduce(d_emb)             # every TP rank saw only its rows' contribution
             payload = d_emb[self.index * self.slice_rows:(self.index + 1) * self.slice_rows].contiguous()
@@ -186,4 +186,4 @@ class TwoStagePipeline:
         for p in am.replicated_before_shard() + am.replicated_in_shard():
             if p.grad is not None:
                 self.tp.all_reduce(p.grad)
-        return total
+        return float(total)

@@ -487,3 +487,21 @@ def test_conv_cta_pairs(stride, pad, dil):
     no.conv_pass(x, wt.reshape(o, 9 * c), o, y, grid_hw=(oh, ow), in_mul=stride, taps=taps, two_cta=True)
     nv.check_status(x.device)
     assert _rel_err(y, expect) < 5e-3
+
+
+def test_device_fingerprint_detects_single_bit_changes():
+    _nops()
+    from fbamtrain_b200.parallel.ftccl import tensor_hashes
+    torch.manual_seed(21)
+    a = torch.randn(1_000_003, device=DEV)
+    b = a.clone()
+    c = a.clone()
+    c.view(torch.int32)[777_777] ^= 1
+    odd = torch.arange(13, device=DEV, dtype=torch.uint8)
+    odd2 = odd.clone()
+    odd2[12] = 99
+    ha, hb, hc, ho, ho2 = tensor_hashes([a, b, c, odd, odd2])
+    assert ha == hb and ha != hc and ho != ho2 and len(ha) == 32
+    swapped = a.clone()
+    swapped[[0, 1]] = swapped[[1, 0]]
+    assert tensor_hashes([swapped])[0] != ha          # position matters
