@@ -20,6 +20,8 @@ import torch
 import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+# few CTAs per send/receive kernel: they share the GPU with persistent compute kernels (see parallel/pipeline.py)
+os.environ.setdefault("NCCL_MAX_P2P_NCHANNELS", "4")
 
 
 def main():

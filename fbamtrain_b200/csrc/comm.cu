@@ -155,17 +155,27 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_gra
                      : "memory");
       }
     } else {
-      // fixed summation order (rank 0, 1, ...) on every rank: results do not depend on who owns the shard
-      for (int r = 0; r < world; ++r) {
-        if constexpr (BF16) {
-          float t[8];
-          unpack_bf16x8(ld_cg_v4(reinterpret_cast<const bf16*>(grads.p[r]) + i), t);
+      // All peers' packets are requested before any is used: one NVLink round trip in flight per peer instead of
+      // one after the other.  Fixed summation order (rank 0, 1, ...) on every rank: results do not depend on
+      // who owns the shard.
+      uint4 raw[FBAM_MAX_RANKS];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) g[j] += t[j];
-        } else {
-          const uint4 raw = ld_cg_v4(reinterpret_cast<const float*>(grads.p[r]) + i);
-          g[0] += __uint_as_float(raw.x); g[1] += __uint_as_float(raw.y);
-          g[2] += __uint_as_float(raw.z); g[3] += __uint_as_float(raw.w);
+      for (int r = 0; r < FBAM_MAX_RANKS; ++r)
+        if (r < world)
+          raw[r] = BF16 ? ld_cg_v4(reinterpret_cast<const bf16*>(grads.p[r]) + i)
+                        : ld_cg_v4(reinterpret_cast<const float*>(grads.p[r]) + i);
+#pragma unroll
+      for (int r = 0; r < FBAM_MAX_RANKS; ++r) {
+        if (r < world) {
+          if constexpr (BF16) {
+            float t[8];
+            unpack_bf16x8(raw[r], t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[j] += t[j];
+          } else {
+            g[0] += __uint_as_float(raw[r].x); g[1] += __uint_as_float(raw[r].y);
+            g[2] += __uint_as_float(raw[r].z); g[3] += __uint_as_float(raw[r].w);
+          }
         }
       }
     }
@@ -203,10 +213,13 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_gra
                    "f"(__uint_as_float(out.w))
                    : "memory");
     } else {
-      for (int r = 0; r < world; ++r) {
-        void* dst = BF16 ? static_cast<void*>(reinterpret_cast<bf16*>(params.p[r]) + i)
-                         : static_cast<void*>(reinterpret_cast<float*>(params.p[r]) + i);
-        *reinterpret_cast<uint4*>(dst) = out;
+#pragma unroll
+      for (int r = 0; r < FBAM_MAX_RANKS; ++r) {
+        if (r < world) {
+          void* dst = BF16 ? static_cast<void*>(reinterpret_cast<bf16*>(params.p[r]) + i)
+                           : static_cast<void*>(reinterpret_cast<float*>(params.p[r]) + i);
+          *reinterpret_cast<uint4*>(dst) = out;
+        }
       }
     }
   }
@@ -231,26 +244,48 @@ reduce_pull_kernel(PeerPtrs grads, float* momentum_buf, bf16* out, float* sumsq,
     float g[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) g[j] = 0.0f;
-    for (int r = 0; r < world; ++r) {
-      if constexpr (BF16) {
-        float t[8];
-        unpack_bf16x8(ld_cg_v4(reinterpret_cast<const bf16*>(grads.p[r]) + i), t);
+    uint4 raw[FBAM_MAX_RANKS];  // every peer's packet is in flight before the first is used
 #pragma unroll
-        for (int j = 0; j < 8; ++j) g[j] += t[j];
-      } else {
-        const uint4 raw = ld_cg_v4(reinterpret_cast<const float*>(grads.p[r]) + i);
-        g[0] += __uint_as_float(raw.x); g[1] += __uint_as_float(raw.y);
-        g[2] += __uint_as_float(raw.z); g[3] += __uint_as_float(raw.w);
+    for (int r = 0; r < FBAM_MAX_RANKS; ++r)
+      if (r < world)
+        raw[r] = BF16 ? ld_cg_v4(reinterpret_cast<const bf16*>(grads.p[r]) + i)
+                      : ld_cg_v4(reinterpret_cast<const float*>(grads.p[r]) + i);
+#pragma unroll
+    for (int r = 0; r < FBAM_MAX_RANKS; ++r) {
+      if (r < world) {
+        if constexpr (BF16) {
+          float t[8];
+          unpack_bf16x8(raw[r], t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] += t[j];
+        } else {
+          g[0] += __uint_as_float(raw[r].x); g[1] += __uint_as_float(raw[r].y);
+          g[2] += __uint_as_float(raw[r].z); g[3] += __uint_as_float(raw[r].w);
+        }
       }
+    }
+    // momentum buffer and output are indexed from lo; lo is a multiple of VEC and both are 16-byte aligned
+    float bufv[VEC], u[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; j += 4) {
+      const float4 t = *reinterpret_cast<const float4*>(momentum_buf + (i - lo) + j);
+      bufv[j] = t.x; bufv[j + 1] = t.y; bufv[j + 2] = t.z; bufv[j + 3] = t.w;
     }
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
       const float gj = g[j] * grad_scale;
-      const float bj = mu * momentum_buf[i - lo + j] + gj;
-      momentum_buf[i - lo + j] = bj;
-      const float u = nesterov ? gj + mu * bj : bj;
-      out[i - lo + j] = __float2bfloat16(u);
-      local += u * u;
+      bufv[j] = mu * bufv[j] + gj;
+      u[j] = nesterov ? gj + mu * bufv[j] : bufv[j];
+      local += u[j] * u[j];
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; j += 4)
+      *reinterpret_cast<float4*>(momentum_buf + (i - lo) + j) = make_float4(bufv[j], bufv[j + 1], bufv[j + 2], bufv[j + 3]);
+    if constexpr (BF16) {
+      *reinterpret_cast<uint4*>(out + (i - lo)) = pack_bf16x8(u);
+    } else {
+      __align__(8) __nv_bfloat162 h[2] = {__floats2bfloat162_rn(u[0], u[1]), __floats2bfloat162_rn(u[2], u[3])};
+      *reinterpret_cast<uint2*>(out + (i - lo)) = *reinterpret_cast<uint2*>(h);
     }
   }
 #pragma unroll
@@ -264,11 +299,21 @@ push_shard_kernel(PeerPtrs bufs, PeerPtrs flags, long long lo_bytes, long long h
                   unsigned epoch, unsigned* arrive) {
   const long long packets = (hi_bytes - lo_bytes) / 16;
   const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(bufs.p[rank]) + lo_bytes);
-  for (long long pk = (long long)blockIdx.x * blockDim.x + threadIdx.x; pk < packets;
-       pk += (long long)gridDim.x * blockDim.x) {
-    const uint4 val = src[pk];
-    for (int r = 0; r < world; ++r)
-      if (r != rank) reinterpret_cast<uint4*>(reinterpret_cast<char*>(bufs.p[r]) + lo_bytes)[pk] = val;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long pk = (long long)blockIdx.x * blockDim.x + threadIdx.x; pk < packets; pk += 4 * stride) {
+    uint4 val[4];  // four independent loads in flight per thread
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (pk + u * stride < packets) val[u] = src[pk + u * stride];
+#pragma unroll
+    for (int r = 0; r < FBAM_MAX_RANKS; ++r) {
+      if (r < world && r != rank) {
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(bufs.p[r]) + lo_bytes);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (pk + u * stride < packets) dst[pk + u * stride] = val[u];
+      }
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -291,6 +336,33 @@ __global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int slo
 __global__ void wait_flags_kernel(const unsigned* my_flags, int slot, int world, unsigned epoch, unsigned spin_limit,
                                   int* status) {
   if (threadIdx.x == 0) wait_all(my_flags, slot, world, epoch, spin_limit, status);
+}
+
+
+// Owner-side half of the slot-form GEMM -> reduce-scatter: after every peer has announced that its partial tiles
+// are stored (entry barrier on the flag words), sum the `world` bf16 slots of the local buffer in fp32.
+__global__ void __launch_bounds__(256)
+reduce_slots_kernel(const uint4* __restrict__ slots, uint4* __restrict__ out, long long packets_per_slot, int world,
+                    PeerPtrs flags, int rank, int slot, unsigned epoch, unsigned spin_limit, int sync, int* status) {
+  if (sync && !signal_and_wait(flags, rank, world, slot, epoch, spin_limit, status)) return;
+  for (long long pk = (long long)blockIdx.x * blockDim.x + threadIdx.x; pk < packets_per_slot;
+       pk += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = 0; r < world; ++r) {
+      const uint4 raw = __ldcg(slots + (long long)r * packets_per_slot + pk);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(h[q]);
+        acc[2 * q] += f.x;
+        acc[2 * q + 1] += f.y;
+      }
+    }
+    __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) o[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+    out[pk] = *reinterpret_cast<uint4*>(o);
+  }
 }
 
 int num_sms() {
@@ -333,7 +405,7 @@ int fbam_rs_adamw_ag(void* const* grads, void* const* params, void* const* flags
   AdamArgs a{lr, b1, b2, eps, wd, 1.0f / bc1, 1.0f / bc2, grad_scale};
   const long long packets = (hi - lo) / vec;
   int grid = (int)((packets + 255) / 256);
-  int cap = max_ctas > 0 ? max_ctas : num_sms() * 2;
+  int cap = max_ctas > 0 ? max_ctas : num_sms() * 4;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
   cudaStream_t s = STREAM(stream);
@@ -353,6 +425,7 @@ int fbam_reduce_pull(void* const* grads, float* momentum_buf, void* out_bf16, fl
   if (world < 1 || world > FBAM_MAX_RANKS) return 1;
   const int vec = is_bf16 ? 8 : 4;
   if (lo % vec != 0 || hi % vec != 0 || hi < lo) return 1;
+  if ((reinterpret_cast<uintptr_t>(momentum_buf) & 15) || (reinterpret_cast<uintptr_t>(out_bf16) & 15)) return 1;
   PeerPtrs G{};
   for (int r = 0; r < world; ++r) G.p[r] = grads[r];
   const long long packets = (hi - lo) / vec;
@@ -377,8 +450,8 @@ int fbam_push_shard(void* const* bufs, void* const* flags, long long lo_bytes, l
     F.p[r] = flags[r];
   }
   const long long packets = (hi_bytes - lo_bytes) / 16;
-  int grid = (int)((packets + 255) / 256);
-  if (grid > num_sms()) grid = num_sms();
+  int grid = (int)((packets + 1023) / 1024);
+  if (grid > num_sms() * 2) grid = num_sms() * 2;
   if (grid < 1) grid = 1;
   cudaStream_t s = STREAM(stream);
   if (cudaMemsetAsync(arrive, 0, sizeof(unsigned), s) != cudaSuccess) return 5;
@@ -398,6 +471,24 @@ int fbam_peer_barrier(void* const* flags, int rank, int world, int slot, unsigne
 int fbam_wait_flags(const void* my_flags, int slot, int world, unsigned epoch, unsigned spin_limit, int* status,
                     void* stream) {
   wait_flags_kernel<<<1, 32, 0, STREAM(stream)>>>((const unsigned*)my_flags, slot, world, epoch, spin_limit, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+
+// slots: local buffer [world][n_per_slot] bf16; out: n_per_slot bf16.  flags == null skips the entry barrier
+// (single-process emulation).
+int fbam_reduce_slots(const void* slots, void* out, long long n_per_slot, int world, void* const* flags, int rank,
+                      int slot, unsigned epoch, unsigned spin_limit, int* status, void* stream) {
+  if (world < 1 || world > FBAM_MAX_RANKS || n_per_slot % 8 != 0 || n_per_slot < 0) return 1;
+  if ((reinterpret_cast<uintptr_t>(slots) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return 1;
+  PeerPtrs F{};
+  if (flags != nullptr)
+    for (int r = 0; r < world; ++r) F.p[r] = flags[r];
+  const long long packets = n_per_slot / 8;
+  int grid = (int)((packets + 255) / 256);
+  if (grid > num_sms() * 4) grid = num_sms() * 4;
+  if (grid < 1) grid = 1;
+  reduce_slots_kernel<<<grid, 256, 0, STREAM(stream)>>>((const uint4*)slots, (uint4*)out, packets, world, F, rank, slot,
+                                                        epoch, spin_limit, flags != nullptr, status);
   return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 

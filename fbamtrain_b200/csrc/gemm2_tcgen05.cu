@@ -16,6 +16,8 @@
 #include "gemm_tcgen05.h"
 #include "tc05.cuh"
 
+extern int g_fbam_reserved_sms;  // defined in gemm_tcgen05.cu
+
 namespace {
 
 using namespace tc05;
@@ -166,7 +168,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const int tile_m = tile / tiles_n, tile_n = tile % tiles_n;
+        const int tile_m = (tile / tiles_n + p.tile_m_rotate) % p.tiles_m, tile_n = tile % tiles_n;
         const int half = tile_m * 2 + (int)rank;              // this CTA's 128-row tile / brick
         const int b_row0 = tile_n * BN + (int)rank * (BN / 2);   // this CTA's half of the B tile
         int cn = 0, ch = 0, cw = 0;
@@ -175,6 +177,22 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
           cw = (half % g.tiles_w) * g.tw * g.in_mul;
           ch = ((half / g.tiles_w) % g.tiles_h) * g.th * g.in_mul;
           cn = (half / (g.tiles_w * g.tiles_h)) * g.tn;
+        }
+        if (p.ready_flags != nullptr) {
+          // all-gather -> GEMM: wait (bounded) until the peers' shards that this CTA's loads read have landed
+          const int r0 = p.flag_on_b ? b_row0 : half * BM;
+          const int r1 = min(p.flag_on_b ? p.N : p.M, r0 + (p.flag_on_b ? BN / 2 : BM)) - 1;
+          for (int f = r0 / p.flag_rows; f <= r1 / p.flag_rows && ok; ++f) {
+            unsigned spins = 0, v;
+            do {
+              asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.ready_flags + f) : "memory");
+              if ((int)(v - p.flag_epoch) >= 0) break;
+              __nanosleep(64);
+            } while (++spins < p.flag_spin_limit);
+            if ((int)(v - p.flag_epoch) < 0) ok = false;
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy acquire -> async-proxy (TMA) reads
         }
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
@@ -247,7 +265,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-      const int tile_m = tile / tiles_n, tile_n = tile % tiles_n;
+      const int tile_m = (tile / tiles_n + p.tile_m_rotate) % p.tiles_m, tile_n = tile % tiles_n;
       const int half = tile_m * 2 + (int)rank;
       if (!mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
       fence_after_sync();
@@ -338,7 +356,8 @@ int launch2(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStr
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
   const int tiles = p.tiles_m * ((p.N + BN - 1) / BN);
-  int clusters = tiles < sms / 2 ? tiles : sms / 2;
+  const int usable = sms - g_fbam_reserved_sms > 2 ? sms - g_fbam_reserved_sms : 2;
+  int clusters = tiles < usable / 2 ? tiles : usable / 2;
   if (p.max_ctas > 1 && clusters > p.max_ctas / 2) clusters = p.max_ctas / 2;
   gemm2_kernel<BN><<<2 * clusters, kThreads, L::kTotal, stream>>>(ma, mb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : GEMM_ERR_LAUNCH;
@@ -347,12 +366,13 @@ int launch2(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStr
 }  // namespace
 
 // Same contracts as fbam_gemm_bf16 / fbam_conv_bf16 (gemm_tcgen05.cu), computed by CTA pairs.  N must be a
-// multiple of 16 with BN in {128, 256}; split-K, flag gating and the reduce-scatter epilogue stay on the
-// single-CTA kernel.
+// multiple of 16 with BN in {128, 256}; split-K stays on the single-CTA kernel.
 extern "C" int fbam_gemm2_bf16(const void* A, long long lda, int a_mn_major, const void* B, long long ldb,
                                int b_mn_major, int M, int N, int K, GemmParams* params, void* stream) {
   GemmParams p = *params;
-  if (M <= 0 || N <= 0 || K <= 0 || p.splits > 1 || p.ready_flags != nullptr) return GEMM_ERR_SHAPE;
+  if (M <= 0 || N <= 0 || K <= 0 || p.splits > 1) return GEMM_ERR_SHAPE;
+  if (p.ready_flags != nullptr && p.flag_rows <= 0) return GEMM_ERR_SHAPE;
+  if (p.flag_spin_limit == 0) p.flag_spin_limit = 1u << 22;
   p.mode = GEMM_MODE_PLAIN;
   p.M = M; p.N = N; p.K = K;
   p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
@@ -365,7 +385,7 @@ extern "C" int fbam_gemm2_bf16(const void* A, long long lda, int a_mn_major, con
              (p.preact_out == nullptr || (reinterpret_cast<uintptr_t>(p.preact_out) & 15) == 0) &&
              (p.gelu_grad_in == nullptr || (reinterpret_cast<uintptr_t>(p.gelu_grad_in) & 15) == 0) &&
              (p.residual == nullptr || (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) && (p.ldd % 8 == 0);
-  if (p.rs_rows_per_rank > 0) p.vec_ok = (p.ldd % 4 == 0);
+  if (p.rs_rows_per_rank > 0) p.vec_ok = (p.ldd % (p.rs_slot_plus1 > 0 ? 8 : 4) == 0);
   CUtensorMap ma, mb;
   int e = a_mn_major ? enc2d(&ma, A, K, M, lda, 64) : enc2d(&ma, A, M, K, lda, BM);
   if (e) return e;

@@ -97,6 +97,28 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
                 if (n0 + j < p.N) v[j] += __bfloat162float(ri[j]);
             }
           }
+          if (p.rs_rows_per_rank > 0 && p.rs_slot_plus1 > 0) {
+            // GEMM -> reduce-scatter, slot form: this rank's partial tile goes, as bf16, into its slot of the
+            // owner's buffer (plain 16-byte stores over NVLink)
+            const int m = (int)(roff / p.ldd);
+            const int owner = m / p.rs_rows_per_rank;
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.rs_out[owner]) +
+                                 ((long long)(p.rs_slot_plus1 - 1) * p.rs_rows_per_rank + (m - owner * p.rs_rows_per_rank)) *
+                                     p.ldd + n0;
+            if (full_vec) {
+  #pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                __align__(16) __nv_bfloat162 h[4];
+  #pragma unroll
+                for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+                *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (n0 + j < p.N) out[j] = __float2bfloat16(v[j]);
+            }
+            return;
+          }
           if (p.rs_rows_per_rank > 0) {
             // GEMM -> reduce-scatter: add this rank's partial sums into the owner's fp32 buffer over NVLink
             const int m = (int)(roff / p.ldd);

@@ -28,6 +28,9 @@
 #include "gemm_epilogue.cuh"
 #include "tc05.cuh"
 
+// SMs the persistent kernels leave free (see fbam_set_reserved_sms).
+int g_fbam_reserved_sms = 0;
+
 namespace {
 
 using namespace tc05;
@@ -390,7 +393,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStre
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
   const int tiles = p.tiles_m * ((p.N + BN - 1) / BN) * p.splits;
-  int grid = tiles < g_num_sms ? tiles : g_num_sms;
+  const int usable = g_num_sms - g_fbam_reserved_sms > 0 ? g_num_sms - g_fbam_reserved_sms : 1;
+  int grid = tiles < usable ? tiles : usable;
   if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
   gemm_kernel<BM, BN><<<grid, kThreads, L::kTotal, stream>>>(ma, mb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : GEMM_ERR_LAUNCH;
@@ -423,6 +427,16 @@ int pick_bn(int n, int requested) {
 
 }  // namespace
 
+// A persistent kernel sized to the whole machine cannot finish while another long-running kernel (a library
+// send/receive that waits for its peer, say) occupies some SMs: its last CTAs are never scheduled.  Callers that
+// keep such kernels in flight reserve SMs for them; every persistent GEMM / convolution launch then uses at most
+// (SM count - n) CTAs.  Returns the previous value.
+extern "C" int fbam_set_reserved_sms(int n) {
+  const int old = g_fbam_reserved_sms;
+  g_fbam_reserved_sms = n < 0 ? 0 : n;
+  return old;
+}
+
 extern "C" int fbam_gemm_bf16(const void* A, long long lda, int a_mn_major, const void* B, long long ldb,
                               int b_mn_major, int M, int N, int K, GemmParams* params, void* stream) {
   GemmParams p = *params;
@@ -445,7 +459,7 @@ extern "C" int fbam_gemm_bf16(const void* A, long long lda, int a_mn_major, cons
              (p.residual == nullptr || (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) && (p.ldd % 8 == 0);
   if (p.rs_rows_per_rank > 0) {
     if (p.mode != GEMM_MODE_PLAIN) return GEMM_ERR_SHAPE;
-    p.vec_ok = (p.ldd % 4 == 0);
+    p.vec_ok = (p.ldd % (p.rs_slot_plus1 > 0 ? 8 : 4) == 0);
     for (int r = 0; r * p.rs_rows_per_rank < M; ++r)
       if (r >= 8 || p.rs_out[r] == nullptr || (reinterpret_cast<uintptr_t>(p.rs_out[r]) & 15)) return GEMM_ERR_ALIGNMENT;
   }

@@ -56,6 +56,11 @@ struct GemmParams {
   // buffer of the rank that owns the output row: owner = m / rs_rows_per_rank, local row = m % rs_rows_per_rank
   void* rs_out[8];
   int rs_rows_per_rank;
+  // rs_slot_plus1 = 0: the mode above.  rs_slot_plus1 = s + 1: instead of adding, the tile is rounded to bf16 and
+  // written with plain vector stores into slot s of the owner's buffer, laid out [slot][rs_rows_per_rank][ldd]
+  // (one slot per source rank); the owner sums the slots afterwards.  Plain stores run at link bandwidth, remote
+  // reductions do not.
+  int rs_slot_plus1;
   // filled by the launcher
   int mode, M, N, K, tiles_m, k_blocks, a_mn_major, b_mn_major, vec_ok;
   ConvGeom conv;

@@ -40,7 +40,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          gelu_grad_in: Optional[torch.Tensor] = None, accumulate: int = 0, alpha: float = 1.0,
          bn: int = 0, bm: int = 0, max_ctas: int = 0, ready_flags: Optional[torch.Tensor] = None,
          flag_rows: int = 0, flag_on_b: bool = False, flag_epoch: int = 0, flag_spin_limit: int = 0,
-         rs_out=None, rs_rows_per_rank: int = 0, tile_m_rotate: int = 0, two_cta=None) -> torch.Tensor:
+         rs_out=None, rs_rows_per_rank: int = 0, tile_m_rotate: int = 0, two_cta=None,
+         rs_slot: int = -1) -> torch.Tensor:
     """``D[M, N] = epilogue(A · Bᵀ)``.
 
     ``a``: ``(M, K)`` (or ``(K, M)`` when ``a_mn``); ``b``: ``(N, K)`` (or ``(K, N)`` when ``b_mn``).
@@ -92,11 +93,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         for i, ptr_ in enumerate(rs_out):
             p.rs_out[i] = ptr_
         p.rs_rows_per_rank = rs_rows_per_rank
+        p.rs_slot_plus1 = rs_slot + 1
     pair = TWO_CTA if two_cta is None else two_cta
     if pair == "auto":
-        pair = (ready_flags is None and n >= 256 and n % 16 == 0 and bm != 128 and
+        pair = (n >= 256 and n % 16 == 0 and bm != 128 and
                 ((m + 255) // 256) * ((n + 255) // 256) >= 148)
-    fn = nv.lib().fbam_gemm2_bf16 if pair and ready_flags is None else nv.lib().fbam_gemm_bf16
+    fn = nv.lib().fbam_gemm2_bf16 if pair else nv.lib().fbam_gemm_bf16
     with debug.label(f"gemm{'2' if pair else ''} m{m} n{n} k{k} {'T' if a_mn else 'N'}{'T' if b_mn else 'N'}"):
         code = fn(nv.ptr(a), C.c_longlong(a.stride(0)), int(a_mn), nv.ptr(b), C.c_longlong(b.stride(0)), int(b_mn),
                   m, n, k, C.byref(p), nv.stream_ptr())

@@ -30,6 +30,9 @@ from ..models import FbamModel
 from .tensor_parallel import TensorParallelBlock, TpContext, sync_replicated_grads
 
 
+RESERVED_SMS = 16   # SMs left to the library's send/receive kernels while a pipeline is active
+
+
 @dataclass
 class PipelineLayout:
     frame_ranks: List[int]
@@ -97,12 +100,30 @@ class TwoStagePipeline:
         g_frame = dist.new_group(layout.frame_ranks)
         g_action = dist.new_group(layout.action_ranks)
         self.stage_group = g_frame if self.is_frame else g_action
+        # One group per partner pair and direction.  NCCL runs the point-to-point operations of a group in issue
+        # order on one stream; with both directions in one group, stage 0's "receive gradient k" (issued before
+        # "send embeddings k+1") and stage 1's "receive embeddings k+1" (issued before "send gradient k") would
+        # wait for each other forever.
+        self.fwd_group = self.bwd_group = None
+        for f_rank, a_rank in zip(layout.frame_ranks, layout.action_ranks):
+            g_fwd, g_bwd = dist.new_group([f_rank, a_rank]), dist.new_group([f_rank, a_rank])
+            if self.rank in (f_rank, a_rank):
+                self.fwd_group, self.bwd_group = g_fwd, g_bwd
         self.n_stage = len(self.stage_ranks)
         frames = micro_batch_size * seq
         if frames % self.n_stage:
             raise ValueError("frames per micro-batch must divide by the ranks of a stage")
         self.slice_rows = frames // self.n_stage
         self.comm_stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
+        if device.type == "cuda":
+            # A posted receive is a resident kernel that spins until its partner sends.  The persistent GEMM /
+            # convolution kernels are sized to the machine and could not finish next to it (their last CTAs would
+            # wait for the SMs the receive holds, while the partner waits for this rank's results): keep a few
+            # SMs out of their grids.  Launch with NCCL_MAX_P2P_NCHANNELS <= 4 so that the two point-to-point
+            # kernels that can be resident at once (one per direction) stay within the reserve.
+            from ..ops import native as nv
+            if nv.available():
+                nv.lib().fbam_set_reserved_sms(RESERVED_SMS)
         if not self.is_frame:
             self.tp = TpContext(self.stage_group, device, tp_transport)
             self.action = TensorParallelActionModel(model, self.tp, micro_batch_size, seq).to(device)
@@ -115,11 +136,12 @@ class TwoStagePipeline:
         return list(self.action.parameters())
 
     def _isend(self, t: torch.Tensor):
+        """Stage 0 sends embeddings forward, stage 1 sends gradients backward."""
         self.stats["p2p_bytes"] += t.numel() * t.element_size()
-        return dist.isend(t, self.partner)
+        return dist.isend(t, self.partner, group=self.fwd_group if self.is_frame else self.bwd_group)
 
     def _irecv(self, t: torch.Tensor):
-        return dist.irecv(t, self.partner)
+        return dist.irecv(t, self.partner, group=self.bwd_group if self.is_frame else self.fwd_group)
 
     def run_step(self, cells: Optional[torch.Tensor], targets: Optional[torch.Tensor], loss_scale: float) -> float:
         """One step over ``micro_batches`` micro-batches.  Stage-0 ranks pass ``cells``

@@ -98,41 +98,53 @@ class TpContext:
         from .peer_window import MAX_RANKS
         flags = self.peers.flags.local[3 * MAX_RANKS:4 * MAX_RANKS]
         m_full, n_out = rows * self.world, w.shape[0]
-        tile_rows = 256 if ((m_full + 255) // 256) * ((n_out + 255) // 256) >= 296 and n_out >= 128 else 128
+        tiles256 = ((m_full + 255) // 256) * ((n_out + 255) // 256)
+        pair = n_out >= 256 and n_out % 16 == 0 and tiles256 >= 148       # CTA pairs: 256-row tiles
+        tile_rows = 256 if pair or (tiles256 >= 296 and n_out >= 128) else 128
         y = no.gemm(x_full, w, bias=bias, act=act, preact_out=preact_out, ready_flags=flags, flag_rows=rows,
-                    flag_epoch=epoch, flag_spin_limit=self.spin_limit, bm=tile_rows,
+                    flag_epoch=epoch, flag_spin_limit=self.spin_limit, bm=tile_rows, two_cta=pair,
                     tile_m_rotate=(self.rank * rows) // tile_rows)
         return y, x_full.clone() if x_shard.requires_grad or w.requires_grad else x_full
 
     def gemm_rs(self, h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        """``reduce_scatter_rows(h · wᵀ)`` with the reduction done by the GEMM epilogue; returns bf16 rows."""
+        """``reduce_scatter_rows(h · wᵀ)``: the GEMM epilogue stores every bf16 partial tile straight into this
+        rank's slot of the buffer of the rank that owns the rows (plain vector stores over NVLink, remote owners
+        first and in a different order on every rank so that no owner is written by two peers at once); one more
+        kernel waits for all peers' tiles and sums the slots.  Returns this rank's bf16 rows."""
+        from ..ops import native as nv
         from ..ops import native_ops as no
         m, n = h.shape[0], w.shape[0]
         rows = m // self.world
-        win = self._window("rs", rows * n, torch.float32)
-        acc = win.local.view(rows, n)
-        acc.zero_()
-        self._barrier(4)                                   # every accumulator is cleared before anyone adds
-        # the epilogue never writes through `out` in this mode; it only supplies the (M, N) shape and row pitch
-        shape_only = torch.as_strided(acc, (m, n), (0, 1))
-        no.gemm(h, w, out=_RsShape(shape_only, n), rs_out=list(win.ptrs), rs_rows_per_rank=rows)
-        self._barrier(5)                                   # all partial sums have arrived
-        return acc.to(torch.bfloat16)
+        self._rs_round = getattr(self, "_rs_round", 0) + 1
+        # two buffers in turn: a peer may still be summing the previous call's slots while this call's tiles arrive
+        win = self._window(f"rs{self._rs_round & 1}", self.world * rows * n, torch.bfloat16)
+        pair = n >= 256 and n % 16 == 0 and ((m + 255) // 256) * ((n + 255) // 256) >= 148
+        tile_rows = 256 if pair else 128
+        first = ((self.rank + 1) % self.world) * rows
+        rotate = first // tile_rows if rows % tile_rows == 0 else 0
+        no.gemm(h, w, out=_RsShape((m, n), torch.bfloat16, n, win.local.data_ptr()), rs_out=list(win.ptrs),
+                rs_rows_per_rank=rows, rs_slot=self.rank, tile_m_rotate=rotate, two_cta=pair, bm=tile_rows)
+        out = torch.empty(rows, n, dtype=torch.bfloat16, device=h.device)
+        epoch = self.peers.next_epoch()
+        nv.check(nv.lib().fbam_reduce_slots(nv.ptr(win.local), nv.ptr(out), C.c_longlong(rows * n), self.world,
+                                            self.peers.flags.c_ptrs, self.rank, 5, C.c_uint(epoch),
+                                            C.c_uint(self.spin_limit), nv.ptr(nv.status_word(self.device)),
+                                            nv.stream_ptr()), "fbam_reduce_slots")
+        return out
 
 
 class _RsShape:
     """Stand-in output for the reduce-scatter GEMM: exposes shape, dtype, pitch and an address for the
     launcher's checks (the kernel writes to the owners' buffers instead)."""
 
-    def __init__(self, t: torch.Tensor, pitch: int):
-        self._t, self._pitch = t, pitch
-        self.shape, self.dtype = t.shape, t.dtype
+    def __init__(self, shape, dtype, pitch: int, address: int):
+        self.shape, self.dtype, self._pitch, self._address = torch.Size(shape), dtype, pitch, address
 
     def stride(self, i: int) -> int:
         return (self._pitch, 1)[i]
 
     def data_ptr(self) -> int:
-        return self._t.data_ptr()
+        return self._address
 
 
 # =================================================================================================

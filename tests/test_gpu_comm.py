@@ -185,14 +185,43 @@ def test_flag_gated_gemm_and_reduce_scatter_epilogue_single_gpu():
     torch.cuda.synchronize()
     assert int(status.item()) in (101, 102, 103)
     status.zero_()
+    # the same two cases on the CTA-pair kernel (each CTA of a pair waits for the rows its own loads read)
+    flags.fill_(9)
+    y = no.gemm(a, b, ready_flags=flags, flag_rows=m // world, flag_epoch=9, flag_spin_limit=100, tile_m_rotate=1,
+                two_cta=True)
+    assert float((y.float() - expect).norm() / expect.norm()) < 5e-3
+    flags.fill_(1)
+    no.gemm(a, b, ready_flags=flags, flag_rows=m // world, flag_epoch=5, flag_spin_limit=50, two_cta=True)
+    torch.cuda.synchronize()
+    assert int(status.item()) in (101, 102, 103)
+    status.zero_()
     # reduce-scatter epilogue: two "ranks" contribute partial products into four owners' buffers
     rows = m // world
     owners = [torch.zeros(rows, n, device=DEV) for _ in range(world)]
     from fbamtrain_b200.parallel.tensor_parallel import _RsShape
     for part in range(2):
         ap, bp = a[:, part * 128:(part + 1) * 128].contiguous(), b[:, part * 128:(part + 1) * 128].contiguous()
-        shape = _RsShape(torch.as_strided(owners[0], (m, n), (0, 1)), n)
+        shape = _RsShape((m, n), torch.float32, n, owners[0].data_ptr())
         no.gemm(ap, bp, out=shape, rs_out=[o.data_ptr() for o in owners], rs_rows_per_rank=rows)
     nv.check_status(torch.device(DEV))
     got = torch.cat(owners, 0)
     assert float((got - expect).norm() / expect.norm()) < 5e-3
+    # slot form: each "rank" stores its bf16 partial tiles into its slot of the owners' buffers, the owners sum
+    import ctypes as C
+    for pair in (False, True):
+        slots = [torch.zeros(2, rows, n, device=DEV, dtype=BF) for _ in range(world)]
+        for part in range(2):
+            ap, bp = a[:, part * 128:(part + 1) * 128].contiguous(), b[:, part * 128:(part + 1) * 128].contiguous()
+            shape = _RsShape((m, n), BF, n, slots[0].data_ptr())
+            no.gemm(ap, bp, out=shape, rs_out=[o.data_ptr() for o in slots], rs_rows_per_rank=rows, rs_slot=part,
+                    tile_m_rotate=1, two_cta=pair, bm=256 if pair else 128)
+        outs = []
+        for o in slots:
+            red = torch.empty(rows, n, device=DEV, dtype=BF)
+            nv.check(nv.lib().fbam_reduce_slots(nv.ptr(o), nv.ptr(red), C.c_longlong(rows * n), 2, None, 0, 0,
+                                                C.c_uint(0), C.c_uint(0), nv.ptr(status), nv.stream_ptr()),
+                     "fbam_reduce_slots")
+            outs.append(red)
+        nv.check_status(torch.device(DEV))
+        got = torch.cat(outs, 0).float()
+        assert float((got - expect).norm() / expect.norm()) < 1e-2
