@@ -538,6 +538,14 @@ int encode_bthd(CUtensorMap* map, const void* base, int B, int T, int H, int D, 
                 long long sh) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return 4;
+  {  // the driver entry point needs a context current on this thread (see gemm_tcgen05.h)
+    static thread_local int bound = -1;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev != bound) {
+      cudaSetDevice(dev);
+      bound = dev;
+    }
+  }
   if ((reinterpret_cast<uintptr_t>(base) & 15) || (sb * 2) % 16 || (st * 2) % 16 || (sh * 2) % 16) return 2;
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
   cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)st * 2, (cuuint64_t)sb * 2};

@@ -187,19 +187,29 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_gra
       const float4 w0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(params.p[rank]) + i);
       w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w;
     }
+    float mv[VEC], vv[VEC];  // optimizer state moves in 16-byte accesses
+#pragma unroll
+    for (int j = 0; j < VEC; j += 4) {
+      const float4 tm = *reinterpret_cast<const float4*>(m + i + j), tv = *reinterpret_cast<const float4*>(v + i + j);
+      mv[j] = tm.x; mv[j + 1] = tm.y; mv[j + 2] = tm.z; mv[j + 3] = tm.w;
+      vv[j] = tv.x; vv[j + 1] = tv.y; vv[j + 2] = tv.z; vv[j + 3] = tv.w;
+    }
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
       const float gj = g[j] * a.grad_scale;
-      const float mj = a.b1 * m[i + j] + (1.0f - a.b1) * gj;
-      const float vj = a.b2 * v[i + j] + (1.0f - a.b2) * gj * gj;
-      m[i + j] = mj;
-      v[i + j] = vj;
-      w[j] = w[j] * (1.0f - a.lr * a.wd) - a.lr * (mj * a.inv_bc1) / (sqrtf(vj * a.inv_bc2) + a.eps);
+      mv[j] = a.b1 * mv[j] + (1.0f - a.b1) * gj;
+      vv[j] = a.b2 * vv[j] + (1.0f - a.b2) * gj * gj;
+      w[j] = w[j] * (1.0f - a.lr * a.wd) - a.lr * (mv[j] * a.inv_bc1) / (sqrtf(vv[j] * a.inv_bc2) + a.eps);
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; j += 4) {
+      *reinterpret_cast<float4*>(m + i + j) = make_float4(mv[j], mv[j + 1], mv[j + 2], mv[j + 3]);
+      *reinterpret_cast<float4*>(v + i + j) = make_float4(vv[j], vv[j + 1], vv[j + 2], vv[j + 3]);
     }
     uint4 out;
     if constexpr (BF16) {
-#pragma unroll
-      for (int j = 0; j < VEC; ++j) master[i + j] = w[j];
+      *reinterpret_cast<float4*>(master + i) = make_float4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<float4*>(master + i + 4) = make_float4(w[4], w[5], w[6], w[7]);
       out = pack_bf16x8(w);
     } else {
       out = make_uint4(__float_as_uint(w[0]), __float_as_uint(w[1]), __float_as_uint(w[2]), __float_as_uint(w[3]));
@@ -395,6 +405,9 @@ int fbam_rs_adamw_ag(void* const* grads, void* const* params, void* const* flags
   const int vec = is_bf16 ? 8 : 4;
   if (lo % vec != 0 || hi % vec != 0 || hi < lo) return 1;
   if (is_bf16 && master == nullptr) return 1;
+  if ((reinterpret_cast<uintptr_t>(m) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
+      (reinterpret_cast<uintptr_t>(master) & 15))
+    return 1;
   PeerPtrs G{}, P{}, F{};
   for (int r = 0; r < world; ++r) {
     G.p[r] = grads[r];

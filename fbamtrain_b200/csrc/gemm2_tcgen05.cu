@@ -16,7 +16,8 @@
 #include "gemm_tcgen05.h"
 #include "tc05.cuh"
 
-extern int g_fbam_reserved_sms;  // defined in gemm_tcgen05.cu
+extern int g_fbam_reserved_sms;        // defined in gemm_tcgen05.cu
+extern int g_fbam_last_driver_error;   // defined in gemm_tcgen05.cu
 
 namespace {
 
@@ -318,18 +319,22 @@ EncodeTiledFn encode_fn2() {
 int enc2d(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
   EncodeTiledFn enc = encode_fn2();
   if (!enc) return GEMM_ERR_DRIVER;
+  fbam_bind_context_to_thread();
   if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld * 2) % 16) return GEMM_ERR_ALIGNMENT;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : GEMM_ERR_TENSORMAP;
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) g_fbam_last_driver_error = (int)r;
+  return r == CUDA_SUCCESS ? 0 : GEMM_ERR_TENSORMAP;
 }
 int enc_nhwc(CUtensorMap* map, const void* base, int n, int h, int w, int c, int tn, int th, int tw, int stride) {
   EncodeTiledFn enc = encode_fn2();
   if (!enc) return GEMM_ERR_DRIVER;
+  fbam_bind_context_to_thread();
   if ((reinterpret_cast<uintptr_t>(base) & 15) || (c * 2) % 16) return GEMM_ERR_ALIGNMENT;
   cuuint64_t dims[4] = {(cuuint64_t)c, (cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)n};
   cuuint64_t strides[3] = {(cuuint64_t)c * 2, (cuuint64_t)w * c * 2, (cuuint64_t)h * w * c * 2};

@@ -30,6 +30,8 @@
 
 // SMs the persistent kernels leave free (see fbam_set_reserved_sms).
 int g_fbam_reserved_sms = 0;
+// Result code of the last failed tensor-map encode (diagnostics: fbam_last_driver_error).
+int g_fbam_last_driver_error = 0;
 
 namespace {
 
@@ -349,6 +351,7 @@ EncodeTiledFn get_encode_fn() {
 int encode_2d(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return GEMM_ERR_DRIVER;
+  fbam_bind_context_to_thread();
   if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld * 2) % 16) return GEMM_ERR_ALIGNMENT;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
@@ -357,6 +360,7 @@ int encode_2d(CUtensorMap* map, const void* base, long long rows, long long cols
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) g_fbam_last_driver_error = (int)r;
   return r == CUDA_SUCCESS ? 0 : GEMM_ERR_TENSORMAP;
 }
 
@@ -364,6 +368,7 @@ int encode_2d(CUtensorMap* map, const void* base, long long rows, long long cols
 int encode_nhwc(CUtensorMap* map, const void* base, int n, int h, int w, int c, int tn, int th, int tw, int stride) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return GEMM_ERR_DRIVER;
+  fbam_bind_context_to_thread();
   if ((reinterpret_cast<uintptr_t>(base) & 15) || (c * 2) % 16) return GEMM_ERR_ALIGNMENT;
   cuuint64_t dims[4] = {(cuuint64_t)c, (cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)n};
   cuuint64_t strides[3] = {(cuuint64_t)c * 2, (cuuint64_t)w * c * 2, (cuuint64_t)h * w * c * 2};
@@ -431,6 +436,10 @@ int pick_bn(int n, int requested) {
 // send/receive that waits for its peer, say) occupies some SMs: its last CTAs are never scheduled.  Callers that
 // keep such kernels in flight reserve SMs for them; every persistent GEMM / convolution launch then uses at most
 // (SM count - n) CTAs.  Returns the previous value.
+// Driver result code of the most recent failed tensor-map encode, and the runtime's pending error (not cleared).
+extern "C" int fbam_last_driver_error() { return g_fbam_last_driver_error; }
+extern "C" int fbam_pending_runtime_error() { return (int)cudaPeekAtLastError(); }
+
 extern "C" int fbam_set_reserved_sms(int n) {
   const int old = g_fbam_reserved_sms;
   g_fbam_reserved_sms = n < 0 ? 0 : n;

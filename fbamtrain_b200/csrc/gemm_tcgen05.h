@@ -65,3 +65,16 @@ struct GemmParams {
   int mode, M, N, K, tiles_m, k_blocks, a_mn_major, b_mn_major, vec_ok;
   ConvGeom conv;
 };
+
+// Driver entry points (tensor-map encoding) need a context that is current on the CALLING thread.  A thread that
+// has only inherited "device 0" by default (an autograd worker whose first CUDA work is one of these launchers)
+// has none yet; a runtime call that names the device binds the primary context to it.
+static inline void fbam_bind_context_to_thread() {
+  static thread_local int bound = -1;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev != bound) {
+    cudaSetDevice(dev);
+    bound = dev;
+  }
+}
+

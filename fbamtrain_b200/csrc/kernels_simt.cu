@@ -625,25 +625,70 @@ __global__ void ce_fwd_bwd_f32_kernel(const float* __restrict__ logits, bf16* __
 template <typename PT>
 __global__ void adamw_kernel(PT* __restrict__ param, const PT* __restrict__ grad, float* __restrict__ m,
                              float* __restrict__ v, float* __restrict__ master, long long n, float lr, float b1,
-                             float b2, float eps, float wd, float inv_bc1, float inv_bc2, float grad_scale) {
+                             float b2, float eps, float wd, float inv_bc1, float inv_bc2, float grad_scale, int vec_ok) {
   const long long i0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i0 >= n) return;
+  const bool vec = vec_ok && i0 + 4 <= n;   // 16-byte accesses when the launcher found every pointer aligned
+  float g[4], w[4], mm[4], vv[4];
+  if (vec) {
+    const float4 tm = *reinterpret_cast<const float4*>(m + i0), tv = *reinterpret_cast<const float4*>(v + i0);
+    mm[0] = tm.x; mm[1] = tm.y; mm[2] = tm.z; mm[3] = tm.w;
+    vv[0] = tv.x; vv[1] = tv.y; vv[2] = tv.z; vv[3] = tv.w;
+    if constexpr (sizeof(PT) == 2) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(grad + i0);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+      g[0] = a.x; g[1] = a.y; g[2] = b.x; g[3] = b.y;
+    } else {
+      const float4 tg = *reinterpret_cast<const float4*>(grad + i0);
+      g[0] = tg.x; g[1] = tg.y; g[2] = tg.z; g[3] = tg.w;
+    }
+    if (master != nullptr) {
+      const float4 tw = *reinterpret_cast<const float4*>(master + i0);
+      w[0] = tw.x; w[1] = tw.y; w[2] = tw.z; w[3] = tw.w;
+    } else if constexpr (sizeof(PT) == 2) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(param + i0);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+      w[0] = a.x; w[1] = a.y; w[2] = b.x; w[3] = b.y;
+    } else {
+      const float4 tw = *reinterpret_cast<const float4*>(param + i0);
+      w[0] = tw.x; w[1] = tw.y; w[2] = tw.z; w[3] = tw.w;
+    }
+  }
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const long long i = i0 + k;
-    if (i >= n) return;
-    float g, w;
-    if constexpr (sizeof(PT) == 2) g = __bfloat162float(grad[i]); else g = grad[i];
-    g *= grad_scale;
-    if (master != nullptr) w = master[i];
-    else if constexpr (sizeof(PT) == 2) w = __bfloat162float(param[i]); else w = param[i];
-    w *= 1.0f - lr * wd;
-    const float mi = b1 * m[i] + (1.0f - b1) * g;
-    const float vi = b2 * v[i] + (1.0f - b2) * g * g;
-    m[i] = mi;
-    v[i] = vi;
-    w -= lr * (mi * inv_bc1) / (sqrtf(vi * inv_bc2) + eps);
-    if (master != nullptr) master[i] = w;
-    if constexpr (sizeof(PT) == 2) param[i] = __float2bfloat16(w); else param[i] = w;
+    if (!vec) {
+      if (i >= n) return;
+      if constexpr (sizeof(PT) == 2) g[k] = __bfloat162float(grad[i]); else g[k] = grad[i];
+      if (master != nullptr) w[k] = master[i];
+      else if constexpr (sizeof(PT) == 2) w[k] = __bfloat162float(param[i]); else w[k] = param[i];
+      mm[k] = m[i];
+      vv[k] = v[i];
+    }
+    const float gk = g[k] * grad_scale;
+    w[k] *= 1.0f - lr * wd;
+    mm[k] = b1 * mm[k] + (1.0f - b1) * gk;
+    vv[k] = b2 * vv[k] + (1.0f - b2) * gk * gk;
+    w[k] -= lr * (mm[k] * inv_bc1) / (sqrtf(vv[k] * inv_bc2) + eps);
+    if (!vec) {
+      m[i] = mm[k];
+      v[i] = vv[k];
+      if (master != nullptr) master[i] = w[k];
+      if constexpr (sizeof(PT) == 2) param[i] = __float2bfloat16(w[k]); else param[i] = w[k];
+    }
+  }
+  if (vec) {
+    *reinterpret_cast<float4*>(m + i0) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    *reinterpret_cast<float4*>(v + i0) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    if (master != nullptr) *reinterpret_cast<float4*>(master + i0) = make_float4(w[0], w[1], w[2], w[3]);
+    if constexpr (sizeof(PT) == 2) {
+      __align__(8) __nv_bfloat162 h[2] = {__floats2bfloat162_rn(w[0], w[1]), __floats2bfloat162_rn(w[2], w[3])};
+      *reinterpret_cast<uint2*>(param + i0) = *reinterpret_cast<uint2*>(h);
+    } else {
+      *reinterpret_cast<float4*>(param + i0) = make_float4(w[0], w[1], w[2], w[3]);
+    }
   }
 }
 
@@ -850,12 +895,16 @@ int fbam_adamw(void* param, const void* grad, float* m, float* v, float* master,
                void* stream) {
   if (n <= 0) return 0;
   const unsigned blocks = (unsigned)((n + 1023) / 1024);
+  const uintptr_t pa = param_bf16 ? 7 : 15;
+  const int vec_ok = !((reinterpret_cast<uintptr_t>(param) & pa) || (reinterpret_cast<uintptr_t>(grad) & pa) ||
+                       (reinterpret_cast<uintptr_t>(m) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
+                       (reinterpret_cast<uintptr_t>(master) & 15));
   if (param_bf16)
     adamw_kernel<bf16><<<blocks, 256, 0, STREAM(stream)>>>((bf16*)param, (const bf16*)grad, m, v, master, n, lr, b1, b2,
-                                                           eps, wd, 1.0f / bc1, 1.0f / bc2, grad_scale);
+                                                           eps, wd, 1.0f / bc1, 1.0f / bc2, grad_scale, vec_ok);
   else
     adamw_kernel<float><<<blocks, 256, 0, STREAM(stream)>>>((float*)param, (const float*)grad, m, v, master, n, lr, b1,
-                                                            b2, eps, wd, 1.0f / bc1, 1.0f / bc2, grad_scale);
+                                                            b2, eps, wd, 1.0f / bc1, 1.0f / bc2, grad_scale, vec_ok);
   return CHECK_LAUNCH();
 }
 

@@ -86,7 +86,11 @@ def launches() -> int:
 def check(code: int, what: str) -> None:
     global _launches
     if code != 0:
-        raise RuntimeError(f"{what}: {_ERRORS.get(code, 'error')} (code {code})")
+        detail = ""
+        if code in (3, 5) and _lib is not None and hasattr(_lib, "fbam_last_driver_error"):
+            detail = (f"; driver result {_lib.fbam_last_driver_error()}, pending runtime error "
+                      f"{_lib.fbam_pending_runtime_error()}")
+        raise RuntimeError(f"{what}: {_ERRORS.get(code, 'error')} (code {code}){detail}")
     _launches += 1
 
 

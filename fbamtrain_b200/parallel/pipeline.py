@@ -26,6 +26,7 @@ import torch.distributed as dist
 from torch import nn
 
 from .. import ops
+from ..utils.logging import LOG
 from ..models import FbamModel
 from .tensor_parallel import TensorParallelBlock, TpContext, sync_replicated_grads
 
@@ -193,8 +194,7 @@ class TwoStagePipeline:
         for k in range(self.micro_batches):
             recv.wait()
             mine = bufs[k % 2]
-            if k + 1 < self.micro_batches:        # rotating buffers: post the next receive before computing
-                recv = self._irecv(bufs[(k + 1) % 2])
+            LOG("DEBUG", f"pipeline: action rank {self.rank} micro-batch {k}: embeddings received")
             full = self.tp.all_gather_rows(mine).view(self.mb_size, self.seq, e).requires_grad_(True)
             loss = am(full, targets[k].to(self.device), loss_scale)
             loss.backward()
@@ -203,6 +203,12 @@ class TwoStagePipeline:
             self.tp.all_reduce(d_emb)             # every TP rank saw only its rows' contribution
             payload = d_emb[self.index * self.slice_rows:(self.index + 1) * self.slice_rows].contiguous()
             sends.append((self._isend(payload), payload))
+            # The next receive is posted only now: a posted receive is a resident kernel that spins until the data
+            # arrives, and the recurrent kernels of this stage are cooperative launches that need most of the
+            # machine at once.  The partner sent these embeddings long ago, so the transfer starts immediately.
+            if k + 1 < self.micro_batches:
+                recv = self._irecv(bufs[(k + 1) % 2])
+            LOG("DEBUG", f"pipeline: action rank {self.rank} micro-batch {k}: gradient sent")
         for work, _ in sends:
             work.wait()
         for p in am.replicated_before_shard() + am.replicated_in_shard():
