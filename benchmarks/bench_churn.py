@@ -39,8 +39,11 @@ os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 def _worker(idx, port, a, q, go):
     """``go`` is None for a founding member; a late joiner builds its model and then waits for it."""
     import torch
-    torch.cuda.set_device(idx)
-    dev = torch.device("cuda", idx)
+    cpu = a.device == "cpu"                           # host-logic rehearsal on gloo ranks
+    if not cpu:
+        torch.cuda.set_device(idx)
+    dev = torch.device("cpu") if cpu else torch.device("cuda", idx)
+    sync = (lambda: None) if cpu else (lambda: torch.cuda.synchronize(dev))
     from fbamtrain_b200 import RunConfiguration, Trainer, presets
     from fbamtrain_b200.data import SyntheticBatchSource
     from fbamtrain_b200.parallel.ft_dp import FaultTolerantDataParallel
@@ -48,7 +51,11 @@ def _worker(idx, port, a, q, go):
 
     late = go is not None
     torch.manual_seed(0)
-    d = presets.PRESETS[a.model](a.micro_batch, a.gpus)
+    if a.model == "tiny":
+        d = presets.tiny()
+        d["micro_batch_size"], d["total_batch_size"] = a.micro_batch, a.micro_batch * a.gpus
+    else:
+        d = presets.PRESETS[a.model](a.micro_batch, a.gpus)
     d["train_sequence_length"] = d["validation_sequence_length"] = a.seq
     d["max_training_steps"] = a.steps
     cfg = RunConfiguration.from_json(d)
@@ -68,21 +75,21 @@ def _worker(idx, port, a, q, go):
     join_seconds = time.perf_counter() - joined_at[0]
     ft.min_world = floor
     src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point, tr.vocab,
-                               seed=1000 + idx)
+                               seed=1000 + idx, pin=not cpu)
     is_leaver = idx >= a.gpus - a.leavers and not a.no_churn
     first_step = tr.step_count
     losses, times, worlds = {}, {}, {}
     while tr.step_count < a.steps:
         step = tr.step_count
         if is_leaver and step >= first_step + a.interval and step + a.interval < a.steps:
-            torch.cuda.synchronize(dev)
+            sync()
             peer.leave()                              # orderly, between steps
             q.put(("left", idx, step, None))
             tr.close()
             return
         src._calls = step                             # the data of step s is the same whoever computes it
         cells, tg = src.next_batch(a.micro_batch, a.seq)
-        torch.cuda.synchronize(dev)
+        sync()
         t0 = time.perf_counter()
         loss = tr.train_step(cells, tg)
         val = float(loss)                             # synchronises
@@ -91,7 +98,7 @@ def _worker(idx, port, a, q, go):
             losses[step], times[step], worlds[step] = val, t1 - t0, peer.world_size
             if idx == 0:
                 q.put(("progress", 0, tr.step_count, None))
-    torch.cuda.synchronize(dev)
+    sync()
     q.put(("done", idx, tr.step_count, {"losses": losses, "times": times, "worlds": worlds, "events": ft.events,
                                         "dropped": ft.dropped_steps, "rx": ft.rx_bytes, "tx": ft.tx_bytes,
                                         "join_seconds": join_seconds if late else None, "first_step": first_step}))
@@ -110,6 +117,7 @@ def main():
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--mode", default="fused", choices=["fused", "allreduce"])
     ap.add_argument("--no-churn", action="store_true")
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"])
     ap.add_argument("--save", default="")
     ap.add_argument("--compare", default="")
     a = ap.parse_args()

@@ -19,6 +19,7 @@
 // COMM_ERR_PEER_TIMEOUT plus the rank it was waiting for in `status` and returns, leaving the context usable.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <string.h>
 #include <stdint.h>
 
 #define FBAM_MAX_RANKS 8
@@ -504,5 +505,36 @@ int fbam_reduce_slots(const void* slots, void* out, long long n_per_slot, int wo
                                                         epoch, spin_limit, flags != nullptr, status);
   return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
+
+// ---- peer windows over CUDA IPC -------------------------------------------------------------------------------
+// One dedicated device allocation per window, exported as a 64-byte handle that the other processes of the
+// machine open to obtain a pointer they can load from and store to.  Used where the set of processes changes
+// while the job runs (a fresh process can open the handles of processes that have been running for hours; the
+// exchange itself travels through whatever the caller uses for small messages).
+int fbam_ipc_alloc(void** out, long long bytes) {
+  if (out == nullptr || bytes <= 0) return 1;
+  void* p = nullptr;
+  if (cudaMalloc(&p, (size_t)bytes) != cudaSuccess) return 5;
+  if (cudaMemset(p, 0, (size_t)bytes) != cudaSuccess) { cudaFree(p); return 5; }
+  *out = p;
+  return 0;
+}
+int fbam_ipc_free(void* p) { return cudaFree(p) == cudaSuccess ? 0 : 5; }
+int fbam_ipc_export(void* p, unsigned char* handle64) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) return 5;
+  memcpy(handle64, &h, 64);
+  return 0;
+}
+int fbam_ipc_open(const unsigned char* handle64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return 5;
+  *out = p;
+  return 0;
+}
+int fbam_ipc_close(void* p) { return cudaIpcCloseMemHandle(p) == cudaSuccess ? 0 : 5; }
 
 }  // extern "C"

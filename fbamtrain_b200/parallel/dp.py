@@ -34,13 +34,19 @@ from ..utils.nvtx import gputx_range
 
 class DataParallel:
     def __init__(self, mode: str = "allreduce", group: Optional[dist.ProcessGroup] = None,
-                 use_multicast: bool = False, overlap: bool = True, spin_limit: int = 1 << 22):
+                 use_multicast: bool = False, overlap: bool = True, spin_limit: int = 1 << 22,
+                 window_transport: str = "symm"):
         if mode not in ("allreduce", "zero1", "fused"):
             raise ValueError("mode must be allreduce, zero1 or fused")
         self.mode, self.group = mode, group
         self.rank = dist.get_rank(group)
         self.world_size = dist.get_world_size(group)
         self.use_multicast, self.overlap, self.spin_limit = use_multicast, overlap, spin_limit
+        # "symm": torch's symmetric-memory allocator (multicast address available); "ipc": CUDA IPC handles exchanged
+        # over the group, usable when the members of the group change while the job runs
+        if window_transport not in ("symm", "ipc"):
+            raise ValueError("window_transport must be symm or ipc")
+        self.window_transport = window_transport
         self.peers = None
         self.grad_scale = 1.0
         self._windows: Dict[str, tuple] = {}
@@ -114,9 +120,10 @@ class DataParallel:
         return out
 
     def _build_windows(self, trainer) -> None:
-        from .peer_window import PeerGroup
+        from .peer_window import IpcPeerGroup, PeerGroup
         if self.peers is None:
-            self.peers = PeerGroup(self.group, trainer.device, self.use_multicast)
+            cls = IpcPeerGroup if self.window_transport == "ipc" else PeerGroup
+            self.peers = cls(self.group, trainer.device, self.use_multicast)
         self._windows.clear()
         for g in trainer.all_groups():
             wg = self.peers.allocate(g.name + "/grad", g.numel, g.dtype)

@@ -90,7 +90,7 @@ class FaultTolerantDataParallel:
             return False
         if self.mode == "fused":
             if self.inner is None:
-                self.inner = DataParallel(mode="fused", group=None)
+                self.inner = DataParallel(mode="fused", group=None, window_transport="ipc")
                 self.inner.attach_windows_only(trainer)
             else:
                 self.inner.rebuild(trainer, None)
@@ -118,7 +118,9 @@ class FaultTolerantDataParallel:
     # ------------------------------------------------------------------------------------------
     def reduce_and_step(self, trainer) -> bool:
         peer = self.peer
-        # collective phase gate (host side, between kernels)
+        # collective phase gate (host side, between kernels): a peer that left in an orderly way after the previous
+        # step is already known to the master, so ask it rather than rely on the last heartbeat
+        peer.refresh_view()
         if peer.membership_changed() or peer.are_peers_pending() or peer.world_size < self.expected_world:
             if peer.membership_changed() or peer.are_peers_pending():
                 if not self._retopologize(trainer):
@@ -133,6 +135,10 @@ class FaultTolerantDataParallel:
         if self.mode == "fused" and peer.world_size > 1:
             self.inner.grad_scale = scale
             self.inner.reduce_and_step(trainer)
+            if not self._fused_step_completed(trainer):
+                # a peer stopped answering inside the step: its bounded waits ran out and the kernels returned
+                self._retopologize(trainer)
+                return self._drop(trainer, "a device-side wait for a peer timed out")
         else:
             grads = [g.grad for g in trainer.all_groups()]
             if peer.world_size > 1:
@@ -153,6 +159,18 @@ class FaultTolerantDataParallel:
                     g.mul_(scale)
             trainer.optimizers["action_model"].step()
             trainer.optimizers["frame_head"].step()
+        return True
+
+    def _fused_step_completed(self, trainer) -> bool:
+        """Host-synchronises and reads the word the fused kernels set when a bounded wait expires."""
+        from ..ops import native as nv
+        torch.cuda.synchronize(trainer.device)
+        word = nv.status_word(trainer.device)
+        code = int(word.item())
+        if code != 0:
+            word.zero_()
+            LOG("WARN", f"ftccl: fused step reported status {code}")
+            return False
         return True
 
     def _drop(self, trainer, why: str) -> bool:

@@ -388,6 +388,14 @@ class FtPeer:
                 self._master_view = dict(self._master_view, ok=False)
                 return
 
+    def refresh_view(self) -> None:
+        """Asks the master for its current view NOW (the heartbeat thread's copy can be one interval old, which is
+        longer than a training step on a fast device)."""
+        try:
+            self._master_view = self._rpc({"op": "heartbeat"}, timeout=5.0)
+        except (OSError, ConnectionError, json.JSONDecodeError):
+            self._master_view = dict(self._master_view, ok=False)
+
     def are_peers_pending(self) -> bool:
         try:
             return int(self._rpc({"op": "pending"})["pending"]) > 0

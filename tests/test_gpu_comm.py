@@ -130,7 +130,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("variant", ["p2p", "multicast", "muon"])
+@pytest.mark.parametrize("variant", ["p2p", "multicast", "muon", "ipc"])
 def test_fused_dp_matches_nccl_zero1_on_two_gpus(tmp_path, variant):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

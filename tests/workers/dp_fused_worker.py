@@ -13,7 +13,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 
 
-def main(out_path: str, multicast: bool, optimizer: str = "adamw") -> None:
+def main(out_path: str, multicast: bool, optimizer: str = "adamw", transport: str = "symm") -> None:
     from fbamtrain_b200 import RunConfiguration, Trainer, presets
     from fbamtrain_b200.data import SyntheticBatchSource
     from fbamtrain_b200.ops import native
@@ -32,7 +32,8 @@ def main(out_path: str, multicast: bool, optimizer: str = "adamw") -> None:
     batches = [src.next_batch(2, cfg.train_sequence_length) for _ in range(3)]
     results = {}
     for mode in ("zero1", "fused"):
-        tr = Trainer(cfg, device=dev, dp=DataParallel(mode=mode, use_multicast=multicast and mode == "fused"))
+        tr = Trainer(cfg, device=dev, dp=DataParallel(mode=mode, use_multicast=multicast and mode == "fused",
+                                                      window_transport=transport))
         losses = [float(tr.train_step(c, t)) for c, t in batches]
         native.check_status(dev)
         torch.cuda.synchronize()
@@ -65,4 +66,5 @@ def main(out_path: str, multicast: bool, optimizer: str = "adamw") -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1], "multicast" in sys.argv[2:], "muon" if "muon" in sys.argv[2:] else "adamw")
+    main(sys.argv[1], "multicast" in sys.argv[2:], "muon" if "muon" in sys.argv[2:] else "adamw",
+         "ipc" if "ipc" in sys.argv[2:] else "symm")
