@@ -57,5 +57,7 @@ def conv2d_wgrad(x, dy, w_shape, stride, padding, dilation, out_dtype=torch.bflo
     with debug.label(f"wgrad c{c} o{o}"):
         code = nv.lib().fbam_conv_wgrad_bf16(nv.ptr(dy), o, nv.ptr(x), ih, iw, c, C.byref(p), nv.stream_ptr())
     nv.check(code, "fbam_conv_wgrad_bf16")
+    from ..utils import flops
+    flops.add(2.0 * b * oh * ow * o * 9 * c)
     dw = work[0] if splits == 1 else work.sum(0)
     return dw.view(o, 3, 3, c).to(out_dtype)

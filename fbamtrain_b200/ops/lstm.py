@@ -19,6 +19,8 @@ import ctypes as C
 
 import torch
 
+from ..utils import flops
+
 from . import native as nv
 from . import reference as ref
 from .native_ops import BF16, gemm, gemm_nn, gemm_tn
@@ -56,6 +58,7 @@ class _LstmSequence(torch.autograd.Function):
                                            nv.ptr(c_all), nv.ptr(hbuf), nv.ptr(_counter(dev)),
                                            nv.ptr(nv.status_word(dev)), t_len, b, h, per_sample, nv.stream_ptr()),
                  "fbam_lstm_fwd")
+        flops.add(2.0 * t_len * b * h * 4 * h)          # the recurrent product; the input projection is a counted GEMM
         ctx.save_for_backward(x2, wi, wh, gates, y, c_all, h0f, c0f)
         ctx.dims = (t_len, b, i_dim, h)
         ctx.per_sample = per_sample
@@ -77,6 +80,7 @@ class _LstmSequence(torch.autograd.Function):
                                            nv.ptr(dgates), nv.ptr(dh0), nv.ptr(dc0), nv.ptr(dhl), nv.ptr(dcl),
                                            nv.ptr(_counter(dev)), nv.ptr(nv.status_word(dev)), t_len, b, h,
                                            ctx.per_sample, nv.stream_ptr()), "fbam_lstm_bwd")
+        flops.add(2.0 * t_len * b * h * 4 * h)
         dg2 = dgates.view(t_len * b, 4 * h)
         dx = gemm_nn(dg2, wi).view(t_len, b, i_dim) if ctx.needs_input_grad[0] else None
         dw_ih = gemm_tn(dg2, x2, out_dtype=torch.float32)

@@ -13,6 +13,8 @@ import ctypes as C
 import math
 
 import torch
+
+from ..utils import flops
 import torch.nn.functional as F
 
 from . import native as nv
@@ -39,6 +41,7 @@ class _FlashAttention(torch.autograd.Function):
                                         C.c_longlong(sh), nv.ptr(out), nv.ptr(lse), b, t, h, d, int(causal),
                                         C.c_float(scale), nv.ptr(nv.status_word(q.device)), nv.stream_ptr()),
                  "fbam_attn_fwd")
+        flops.add(4.0 * b * h * t * t * d * (0.5 if causal else 1.0))
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.causal, ctx.scale = causal, scale
         return out
@@ -59,6 +62,7 @@ class _FlashAttention(torch.autograd.Function):
             C.c_longlong(d_out.stride(1)), C.c_longlong(d_out.stride(2)), nv.ptr(lse), nv.ptr(delta), nv.ptr(dq32),
             nv.ptr(dk), nv.ptr(dv), b, t, h, d, int(ctx.causal), C.c_float(ctx.scale),
             nv.ptr(nv.status_word(q.device)), nv.stream_ptr()), "fbam_attn_bwd")
+        flops.add(10.0 * b * h * t * t * d * (0.5 if ctx.causal else 1.0))   # 2.5 x forward
         return dq32.to(BF16), dk, dv, None
 
 

@@ -12,7 +12,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from ..utils import debug
+from ..utils import debug, flops
 from . import native as nv
 from . import reference as ref
 
@@ -103,6 +103,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         code = fn(nv.ptr(a), C.c_longlong(a.stride(0)), int(a_mn), nv.ptr(b), C.c_longlong(b.stride(0)), int(b_mn),
                   m, n, k, C.byref(p), nv.stream_ptr())
     nv.check(code, "fbam_gemm_bf16")
+    flops.add(2.0 * m * n * k)
     debug.after_launch("gemm", a, b, out)
     return out
 
@@ -247,6 +248,7 @@ def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor
         code = fn(nv.ptr(x), ih, iw, c, nv.ptr(wmat), C.c_longlong(wmat.stride(0)), n_out, C.byref(p),
                   nv.stream_ptr())
     nv.check(code, "fbam_conv_bf16")
+    flops.add(2.0 * b * grid_hw[0] * grid_hw[1] * n_out * len(taps) * c)
     debug.after_launch("conv_pass", x, wmat, out)
 
 

@@ -28,6 +28,7 @@ from .data import (DatasetCursorCommitter, DatasetCursorSnapshot, RecordingDatas
 from .models import FbamModel
 from .optim import AdamwOptimizer, MuonWithAuxAdam, Optimizer, create_optimizer
 from .tokenizer import Tokenizer
+from .utils import flops
 from .utils.flat import FlatGroup, build_groups
 from .utils.logging import LOG
 from .utils.metrics import AsyncStepLogger, LossRingBuffer, StepRecord
@@ -185,6 +186,7 @@ class Trainer:
         step = self.step_count
         start_ev = end_ev = None
         wall0 = time.perf_counter()
+        flops_total0, flops_useful0 = flops.snapshot()
         if self._cuda:
             start_ev = torch.cuda.Event(enable_timing=True)
             start_ev.record()
@@ -209,8 +211,11 @@ class Trainer:
         if self._cuda:
             end_ev = torch.cuda.Event(enable_timing=True)
             end_ev.record()
+        flops_total1, flops_useful1 = flops.snapshot()
         self.logger.submit(StepRecord(step, start_ev, end_ev, loss_ev, cells.shape[1], cfg.total_batch_size,
-                                      dropped=not committed, wall_start=wall0, wall_end=time.perf_counter()))
+                                      dropped=not committed, wall_start=wall0, wall_end=time.perf_counter(),
+                                      useful_flops=flops_useful1 - flops_useful0,
+                                      total_flops=flops_total1 - flops_total0))
         if committed:
             self.step_count += 1
         if self._cuda and self.step_count % 50 == 0:

@@ -74,6 +74,8 @@ class StepRecord:
     dropped: bool = False
     wall_start: float = 0.0
     wall_end: float = 0.0
+    useful_flops: float = 0.0      # tensor-core FLOPs launched by this rank during the step, recomputation excluded
+    total_flops: float = 0.0
 
 
 class AsyncStepLogger:
@@ -114,11 +116,19 @@ class AsyncStepLogger:
                 loss = self.ring.read(rec.step)
                 rate = rec.seq_len * rec.batch / seconds if seconds > 0 else float("inf")
                 entry = {"step": rec.step, "step_time_sec": seconds, "loss/train": loss, "frames_per_sec": rate}
+                if rec.useful_flops > 0 and seconds > 0:
+                    from .mfu import mfu as _mfu
+                    entry["tflops_useful"] = rec.useful_flops / seconds / 1e12
+                    entry["tflops_total"] = rec.total_flops / seconds / 1e12
+                    entry["mfu"] = _mfu(rec.useful_flops, seconds)
                 self.history.append(entry)
                 LOG("INFO", f"Step {rec.step} took {seconds:.4f} seconds; seqlen/time = "
                             f"{rec.seq_len / seconds if seconds > 0 else float('inf'):.2f}; loss/train = {loss:.6f}")
                 if self.json_lines:
-                    sys.stdout.write(json.dumps({"step": rec.step, "step_time_sec": seconds, "loss/train": loss}) + "\n")
+                    line = {"step": rec.step, "step_time_sec": seconds, "loss/train": loss}
+                    if "mfu" in entry:
+                        line["mfu"] = entry["mfu"]
+                    sys.stdout.write(json.dumps(line) + "\n")
                     sys.stdout.flush()
                 if self.sink is not None:
                     self.sink(entry)

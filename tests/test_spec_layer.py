@@ -186,3 +186,17 @@ def test_assert_similar_rules():
         assert_similar(torch.tensor([float("nan")]), torch.tensor([0.0]), 1.0)
     with pytest.raises(AssertionError, match="shape"):
         assert_similar(torch.zeros(2), torch.zeros(3), 1.0)
+
+
+def test_flop_accounting_separates_recomputation():
+    from fbamtrain_b200.utils import flops
+    flops.reset()
+    flops.add(10.0)
+    with flops.not_useful():
+        flops.add(5.0)
+        with flops.not_useful():
+            flops.add(1.0)
+    flops.add(2.0)
+    assert flops.snapshot() == (18.0, 12.0)
+    flops.reset()
+    assert flops.snapshot() == (0.0, 0.0)
