@@ -61,7 +61,8 @@ def _worker(idx, port, a, q, go):
     cfg = RunConfiguration.from_json(d)
     peer = FtPeer("127.0.0.1", port, dev, heartbeat_interval_s=0.1, collective_timeout_s=60.0)
     floor = a.gpus if a.no_churn else a.gpus - a.leavers
-    ft = FaultTolerantDataParallel(peer, expected_world=a.gpus, min_world=floor if late else a.gpus, mode=a.mode)
+    ft = FaultTolerantDataParallel(peer, expected_world=a.gpus, min_world=floor if late else a.gpus, mode=a.mode,
+                                   full_world_poll_s=0.05)
     ft.late_joiner = late
     joined_at = [0.0]
 
@@ -79,8 +80,16 @@ def _worker(idx, port, a, q, go):
     is_leaver = idx >= a.gpus - a.leavers and not a.no_churn
     first_step = tr.step_count
     losses, times, worlds = {}, {}, {}
+    reduced_since = None
     while tr.step_count < a.steps:
         step = tr.step_count
+        if not a.no_churn:
+            # `interval` steps at the reduced world, then hold at the phase gate until the replacement is admitted
+            if peer.world_size < a.gpus:
+                reduced_since = step if reduced_since is None else reduced_since
+                ft.wait_for_full_world = step >= reduced_since + a.interval
+            else:
+                reduced_since, ft.wait_for_full_world = None, False
         if is_leaver and step >= first_step + a.interval and step + a.interval < a.steps:
             sync()
             peer.leave()                              # orderly, between steps
@@ -134,11 +143,15 @@ def main():
     progress, report0, joiners = 0, None, []
     waiting = {}                                      # idx -> (go event, step at which to release it, ready?)
     deadline = time.time() + 3000
+    t_start = time.time()
     while running and time.time() < deadline:
         try:
             kind, idx, step, payload = q.get(timeout=0.2)
         except queue.Empty:
             kind = None
+        if kind is not None and kind != "progress":
+            sys.stderr.write(f"[churn] t={time.time() - t_start:6.1f}s {kind} slot={idx} step={step} "
+                             f"progress={progress}\n")
         if kind == "progress":
             progress = max(progress, step)
         elif kind == "left":
@@ -161,6 +174,7 @@ def main():
             procs[idx].join(120)
         for idx, (go, at_step, ready) in list(waiting.items()):
             if ready and progress >= at_step:
+                sys.stderr.write(f"[churn] t={time.time() - t_start:6.1f}s go slot={idx} progress={progress}\n")
                 go.set()
                 del waiting[idx]
     for go, _, _ in waiting.values():

@@ -57,7 +57,8 @@ class ActionModel(nn.Module):
 
     def forward(self, frame_embeddings: torch.Tensor, targets: torch.Tensor, loss_scale: float, state=None):
         """Returns ``loss_scale · Σ CE`` over all ``B·T`` positions."""
-        if self.streaming and state is None and frame_embeddings.is_cuda and ops.get_backend() == "auto":
+        if (self.streaming and state is None and frame_embeddings.is_cuda and ops.get_backend() == "auto"
+                and frame_embeddings.dtype == torch.bfloat16):
             from ..ops.lstm import persistent_ok
             layer = self.lstm.layers[0]
             b, t, e = frame_embeddings.shape

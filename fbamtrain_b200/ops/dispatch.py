@@ -21,12 +21,27 @@ def get_backend() -> str:
     return _BACKEND
 
 
-def _native(t: torch.Tensor) -> bool:
-    return t.is_cuda and _BACKEND == "auto"
+_warned_dtypes = set()
+
+
+def _native(t: torch.Tensor, dtype: Optional[torch.dtype] = None) -> bool:
+    """The hand-written kernels compute in bf16 (fp32 accumulate).  CUDA tensors of another activation dtype
+    (the reference's fp16 mode, fp32 debugging runs) take the PyTorch definitions, i.e. the vendor libraries."""
+    if not (t.is_cuda and _BACKEND == "auto"):
+        return False
+    dtype = dtype or t.dtype
+    if dtype == torch.bfloat16:
+        return True
+    if dtype not in _warned_dtypes:
+        _warned_dtypes.add(dtype)
+        from ..utils.logging import LOG
+        LOG("WARN", f"ops: {dtype} activations on a GPU run on the PyTorch / vendor-library path; the sm_100a kernels "
+                    "of this package compute in bf16")
+    return False
 
 
 def cell_embed(cells, cp_embed, pos_embed, colour_embed, out_dtype):
-    if _native(cells):
+    if _native(cells, out_dtype):
         from .native_ops import cell_embed as f
         return f(cells, cp_embed, pos_embed, colour_embed, out_dtype)
     return ref.cell_embed(cells, cp_embed, pos_embed, colour_embed, out_dtype)
@@ -111,7 +126,7 @@ def attention(q, k, v, causal: bool):
 
 
 def lstm_sequence(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype):
-    if _native(x):
+    if _native(x, compute_dtype) and x.dtype == torch.bfloat16:
         from .native_ops import lstm_sequence as f
         return f(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype)
     if x.is_cuda and h0.dim() == 1:

@@ -32,11 +32,12 @@ from .ftccl import FtPeer, Result, SharedStateSyncStrategy, TensorInfo
 
 class FaultTolerantDataParallel:
     def __init__(self, peer: FtPeer, expected_world: int, min_world: int = 1, mode: str = "allreduce",
-                 wait_for_full_world: bool = False):
+                 wait_for_full_world: bool = False, full_world_poll_s: float = 1.0):
         if mode not in ("allreduce", "fused"):
             raise ValueError("mode must be allreduce or fused")
         self.peer, self.expected_world, self.min_world, self.mode = peer, expected_world, min_world, mode
         self.wait_for_full_world = wait_for_full_world
+        self.full_world_poll_s = full_world_poll_s
         self.inner: Optional[DataParallel] = None
         self.events: List[dict] = []          # topology changes with timestamps (recovery-time accounting)
         self.tx_bytes = self.rx_bytes = 0
@@ -126,7 +127,7 @@ class FaultTolerantDataParallel:
                 if not self._retopologize(trainer):
                     return self._drop(trainer, "topology update failed")
             while self.wait_for_full_world and peer.world_size < self.expected_world:
-                time.sleep(1.0)   # "not ready": the reference spins until the expected world is present
+                time.sleep(self.full_world_poll_s)   # "not ready": the reference sleeps 1 s per round
                 if peer.are_peers_pending() and not self._retopologize(trainer):
                     return self._drop(trainer, "topology update failed")
         if peer.world_size < self.min_world:

@@ -505,3 +505,18 @@ def test_device_fingerprint_detects_single_bit_changes():
     swapped = a.clone()
     swapped[[0, 1]] = swapped[[1, 0]]
     assert tensor_hashes([swapped])[0] != ha          # position matters
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "fp32"])
+def test_non_bf16_models_train_on_the_library_path(dtype):
+    """fp16 (the reference's default dtype) and fp32 configurations run on a GPU through the PyTorch definitions."""
+    from fbamtrain_b200 import RunConfiguration, Trainer, presets
+    from fbamtrain_b200.data import SyntheticBatchSource
+    d = presets.tiny(dtype)
+    cfg = RunConfiguration.from_json(d)
+    src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=3, pin=False)
+    cells, tg = src.next_batch(2, cfg.train_sequence_length)
+    tr = Trainer(cfg, device=torch.device(DEV))
+    losses = [float(tr.train_step(cells, tg)) for _ in range(4)]
+    tr.close()
+    assert all(math.isfinite(x) for x in losses) and losses[-1] < losses[0]
