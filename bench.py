@@ -184,7 +184,9 @@ def run_ours(args) -> dict:
         return float(t.item()), clocks, float(last), native.launches() - launches0
 
     ms_dev, clocks, last_loss, launches = timed(dev_batches, read_loss=False)
+    native.check_status(device)      # a bounded device-side wait that ran out would invalidate the measurement
     ms_e2e, clocks_e2e, _, _ = timed(host_batches, read_loss=True)
+    native.check_status(device)
     trainer.logger.drain()
 
     frames_per_step = micro * seq * world

@@ -225,14 +225,19 @@ class DataParallel:
         muon.step_count += 1
         flags = self.peers.flags.c_ptrs
         status = nv.ptr(nv.status_word(dev))
+        # Every rank must tag the same event with the same epoch although each pushes only the matrices it owns:
+        # the step reserves one epoch per matrix (in the optimizer's order) plus two for its barriers.
+        ordered = [name for name, _ in muon.named_params]
+        base = self.peers.epoch
+        self.peers.epoch = base + len(ordered) + 2
 
-        def barrier(slot):
-            nv.check(nv.lib().fbam_peer_barrier(flags, self.rank, self.world_size, slot,
-                                                C.c_uint(self.peers.next_epoch()), C.c_uint(self.spin_limit), status,
-                                                nv.stream_ptr()), "fbam_peer_barrier")
+        def barrier(slot, epoch):
+            nv.check(nv.lib().fbam_peer_barrier(flags, self.rank, self.world_size, slot, C.c_uint(epoch),
+                                                C.c_uint(self.spin_limit), status, nv.stream_ptr()),
+                     "fbam_peer_barrier")
 
-        barrier(6)                                   # every rank's gradients are complete
-        for name, p in muon.named_params:
+        barrier(6, base + 1)                         # every rank's gradients are complete
+        for index, (name, p) in enumerate(muon.named_params):
             if owners[name] != self.rank:
                 continue
             g, off = by_param[name]
@@ -253,10 +258,10 @@ class DataParallel:
             muon.apply_update(name, p, u2)          # writes the local window (p.data is a view of it)
             lo_b = off * esize
             nv.check(nv.lib().fbam_push_shard(wp.c_ptrs, flags, C.c_longlong(lo_b), C.c_longlong(lo_b + n * esize),
-                                              self.rank, self.world_size, 7, C.c_uint(self.peers.next_epoch()),
+                                              self.rank, self.world_size, 7, C.c_uint(base + 2 + index),
                                               nv.ptr(self.peers.arrive[2:]), nv.stream_ptr()), "fbam_push_shard")
             self.stats["bytes_reduced"] += n * esize
-        barrier(8)                                   # all pushes have landed everywhere
+        barrier(8, base + len(ordered) + 2)          # all pushes have landed everywhere
 
     def _step_non_adamw(self, trainer) -> None:
         """Optimizers without a sharded form (SGD, Muon matrices): all-reduce their buckets, step replicated —
