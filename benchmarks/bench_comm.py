@@ -52,15 +52,16 @@ def _time(fn, iters, warmup=3):
     return float(t.item())
 
 
-def _report(rank, name, world, fused_ms, nccl_ms, flops, link_bytes, extra=None):
+def _report(rank, name, world, fused_ms, nccl_ms, flops, link_bytes, extra=None, hbm_bytes=0.0):
     pk = _peaks()
     t_compute = flops / (pk["bf16_tflops"] * 1e12) * 1e3
     t_link = link_bytes / (NVLINK_GBS * 1e9) * 1e3
-    roof = max(t_compute, t_link)
+    t_hbm = hbm_bytes / (pk["hbm_gbs"] * 1e9) * 1e3
+    roof = max(t_compute, t_link, t_hbm)
     if rank == 0:
         out = {"bench": name, "n_gpus": world, "fused_ms": round(fused_ms, 4), "nccl_ms": round(nccl_ms, 4),
                "speedup_vs_nccl": round(nccl_ms / fused_ms, 3), "roofline_ms": round(roof, 4),
-               "roofline_bound": "compute" if t_compute >= t_link else "nvlink",
+               "roofline_bound": {t_compute: "compute", t_link: "nvlink", t_hbm: "hbm"}[roof],
                "fused_frac_of_roofline": round(roof / fused_ms, 3), "nccl_frac_of_roofline": round(roof / nccl_ms, 3),
                "peaks": pk["source"], "nvlink_gbs_per_dir": NVLINK_GBS}
         out.update(extra or {})
@@ -107,8 +108,9 @@ def bench_rs_adamw_ag(a, rank, world, dev):
     tf, tl = _time(fused, a.iters), _time(library, a.iters)
     nv.check_status(dev)
     link = (world - 1) / world * n * 2          # incoming gradient slices; the outgoing parameter slices are equal
+    hbm = per * (2 + 24 + 2) + (world - 1) / world * n * 2   # local grads, m/v/master read+write, params; peers' writes
     _report(rank, "rs_adamw_ag" + ("_multimem" if a.multicast and wg.multicast_ptr else "_p2p"), world, tf, tl, 0.0,
-            link, {"bucket_bytes": n * 2})
+            link, {"bucket_bytes": n * 2}, hbm_bytes=hbm)
 
 
 def bench_ag_gemm(a, rank, world, dev):
@@ -156,9 +158,8 @@ def bench_gemm_rs(a, rank, world, dev):
         tf, tl = _time(fused, a.iters), _time(library, a.iters)
         nv.check_status(dev)
         flops = 2.0 * m_full * kk * k
-        link = (world - 1) / world * m_full * k * 4     # fp32 partial sums sent to the rows' owners
-        _report(rank, f"gemm_rs M{m_full} K{n_out}/{world} N{k}", world, tf, tl, flops, link,
-                {"note": "fused path reduces fp32 partial sums; the library path reduce-scatters bf16"})
+        link = (world - 1) / world * m_full * k * 2     # bf16 partial tiles stored into the owners' slots
+        _report(rank, f"gemm_rs M{m_full} K{n_out}/{world} N{k}", world, tf, tl, flops, link)
 
 
 def bench_muon(a, rank, world, dev):
