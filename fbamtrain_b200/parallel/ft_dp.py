@@ -38,6 +38,7 @@ class FaultTolerantDataParallel:
         self.peer, self.expected_world, self.min_world, self.mode = peer, expected_world, min_world, mode
         self.wait_for_full_world = wait_for_full_world
         self.full_world_poll_s = full_world_poll_s
+        self.gate_timeout_s = 30.0            # how long members wait for each other at the host-side step barrier
         self.inner: Optional[DataParallel] = None
         self.events: List[dict] = []          # topology changes with timestamps (recovery-time accounting)
         self.tx_bytes = self.rx_bytes = 0
@@ -119,11 +120,15 @@ class FaultTolerantDataParallel:
     # ------------------------------------------------------------------------------------------
     def reduce_and_step(self, trainer) -> bool:
         peer = self.peer
-        # collective phase gate (host side, between kernels): a peer that left in an orderly way after the previous
-        # step is already known to the master, so ask it rather than rely on the last heartbeat
-        peer.refresh_view()
-        if peer.membership_changed() or peer.are_peers_pending() or peer.world_size < self.expected_world:
-            if peer.membership_changed() or peer.are_peers_pending():
+        # Collective phase gate (host side, between kernels).  The members meet at the master before every
+        # collective: a peer that left after the previous step, fell silent or waits for admission is noticed here,
+        # before anything is launched that would wait for it on the device, and the members enter the fused
+        # kernels within a network round trip of each other, so the bounded device-side waits stay short.
+        aligned = peer.gate(trainer.step_count, timeout_s=self.gate_timeout_s) if peer.world_size > 1 \
+            else (peer.refresh_view() or not peer.membership_changed())
+        if not aligned or peer.membership_changed() or peer.are_peers_pending() or \
+                peer.world_size < self.expected_world:
+            if not aligned or peer.membership_changed() or peer.are_peers_pending():
                 if not self._retopologize(trainer):
                     return self._drop(trainer, "topology update failed")
             while self.wait_for_full_world and peer.world_size < self.expected_world:

@@ -116,6 +116,7 @@ class _PeerRecord:
     accepted: bool = False
     vote: Optional[dict] = None
     conn: Optional[socket.socket] = None
+    gate_step: Optional[int] = None
 
 
 class MembershipMaster:
@@ -274,6 +275,47 @@ class MembershipMaster:
                                 self._peers[uid].vote = None
                             res = {"ok": False, "error": "timeout"}
                     _send_json(conn, res)
+                elif op == "gate":
+                    # Step barrier on the host: answers once every live accepted peer has reached the same step's
+                    # phase gate, or as soon as the membership differs from the caller's epoch (someone left, was
+                    # evicted or waits for admission) — then the caller must update the topology first.
+                    step = int(msg.get("step", -1))
+                    deadline = time.monotonic() + float(msg.get("timeout", 30.0))
+                    with self._lock:
+                        if uid not in self._peers:
+                            _send_json(conn, {"ok": False, "error": "evicted"})
+                            continue
+                        self._peers[uid].gate_step = step
+                        self._lock.notify_all()
+                        res = None
+                        while not self._stop:
+                            live = [r for r in self._peers.values() if self._alive(r) or r.uid == uid]
+                            accepted = [r for r in live if r.accepted]
+                            pending = [r for r in live if not r.accepted]
+                            changed = pending or int(msg.get("epoch", self.epoch)) != self.epoch or \
+                                len(accepted) != int(msg.get("world", len(accepted)))
+                            if changed:
+                                res = {"ok": True, "aligned": False, "world": len(accepted), "pending": len(pending),
+                                       "epoch": self.epoch}
+                                break
+                            if all(getattr(r, "gate_step", None) is not None and r.gate_step >= step for r in accepted):
+                                res = {"ok": True, "aligned": True, "world": len(accepted), "pending": 0,
+                                       "epoch": self.epoch}
+                                break
+                            remaining = deadline - time.monotonic()
+                            if remaining <= 0:
+                                res = {"ok": True, "aligned": False, "world": len(accepted), "pending": 0,
+                                       "epoch": self.epoch, "timeout": True}
+                                break
+                            self._lock.wait(min(0.05, remaining))
+                            if uid not in self._peers:
+                                res = {"ok": False, "error": "evicted"}
+                                break
+                            self._peers[uid].last_seen = time.monotonic()
+                            for u in [u for u, r in self._peers.items() if not self._alive(r) and u != uid]:
+                                del self._peers[u]
+                        res = res or {"ok": False, "error": "stopped"}
+                    _send_json(conn, res)
                 elif op == "leave":
                     with self._lock:
                         self._peers.pop(uid, None)
@@ -395,6 +437,23 @@ class FtPeer:
             self._master_view = self._rpc({"op": "heartbeat"}, timeout=5.0)
         except (OSError, ConnectionError, json.JSONDecodeError):
             self._master_view = dict(self._master_view, ok=False)
+
+    def gate(self, step: int, timeout_s: float = 30.0) -> bool:
+        """Host-side step barrier through the master.  True: every member of the current topology has reached the
+        phase gate of ``step`` — launch the collective.  False: the membership differs from this peer's topology
+        (or someone did not arrive in time) — update the topology before launching anything."""
+        try:
+            res = self._rpc({"op": "gate", "step": int(step), "epoch": self.epoch, "world": self.world_size,
+                             "timeout": timeout_s}, timeout=timeout_s + 10.0)
+        except (OSError, ConnectionError, json.JSONDecodeError):
+            self._master_view = dict(self._master_view, ok=False)
+            return False
+        if not res.get("ok"):
+            self._master_view = dict(self._master_view, ok=False)
+            return False
+        self._master_view = {"epoch": res.get("epoch", self.epoch), "pending": res.get("pending", 0),
+                             "world": res.get("world", self.world_size), "ok": True}
+        return bool(res.get("aligned"))
 
     def are_peers_pending(self) -> bool:
         try:
