@@ -77,8 +77,16 @@ class PeerGroup:
     def _build_flags(self) -> None:
         self.flags = self.allocate("__flags__", FLAG_SLOTS * MAX_RANKS, torch.int32)
         self.arrive = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._agree_on_epoch()
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
+
+    def _agree_on_epoch(self) -> None:
+        """Every member continues from the highest epoch any member has used: the flag words of a new window start
+        at zero, a long-running member's counter does not, and a wait compares the two."""
+        t = torch.tensor([self.epoch], dtype=torch.int64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        self.epoch = int(t.item())
 
     def next_epoch(self) -> int:
         self.epoch += 1
@@ -155,9 +163,17 @@ class IpcPeerGroup:
     def _build_flags(self) -> None:
         self.flags = self.allocate("__flags__", FLAG_SLOTS * MAX_RANKS, torch.int32)
         self.arrive = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._agree_on_epoch()
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
         self._free_retired()
+
+    def _agree_on_epoch(self) -> None:
+        """Every member continues from the highest epoch any member has used: the flag words of a new window start
+        at zero, a long-running member's counter does not, and a wait compares the two."""
+        t = torch.tensor([self.epoch], dtype=torch.int64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        self.epoch = int(t.item())
 
     def next_epoch(self) -> int:
         self.epoch += 1
