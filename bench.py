@@ -33,7 +33,7 @@ BASELINE_FRAMES_PER_SEC = None  # the reference publishes no end-to-end throughp
 
 
 def reference_unavailable_reason() -> str:
-    return ("reference is a CMake/C++ binary, not a Python package: `pip install --no-index ... /root/reference` fails "
+    return ("reference is a CMake/C++ binary, not a Python package: `pip install --no-index ... <reference checkout>` fails "
             "with \"Neither 'setup.py' nor 'pyproject.toml' found\"; its six git submodules (json, argparse, "
             "termstreamxz, threadpark, nccl, pccl) are empty and its kernels are fetched/AOT-built from the network")
 
@@ -183,10 +183,19 @@ def run_ours(args) -> dict:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()), clocks, float(last), native.launches() - launches0
 
+    def status_code() -> int:
+        """0 unless a bounded device-side wait ran out on some rank (which would invalidate the measurement)."""
+        word = native.status_word(device)
+        code = torch.tensor([int(word.item())], device=device)
+        word.zero_()
+        if world > 1:
+            dist.all_reduce(code, op=dist.ReduceOp.MAX)
+        return int(code.item())
+
     ms_dev, clocks, last_loss, launches = timed(dev_batches, read_loss=False)
-    native.check_status(device)      # a bounded device-side wait that ran out would invalidate the measurement
+    status_dev = status_code()
     ms_e2e, clocks_e2e, _, _ = timed(host_batches, read_loss=True)
-    native.check_status(device)
+    status_e2e = status_code()
     trainer.logger.drain()
 
     frames_per_step = micro * seq * world
@@ -215,6 +224,8 @@ def run_ours(args) -> dict:
         "e2e": {"value": e2e_value, "unit": "frames/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "clocks": clocks_e2e},
         "gpu_launches": launches,
+        "device_status": {"timed": status_dev, "e2e": status_e2e,
+                          "meaning": "0 = no bounded device-side wait expired on any rank"},
     }
     trainer.close()
     if world > 1:

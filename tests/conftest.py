@@ -22,3 +22,12 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def reference_path(*parts: str) -> str:
+    """Path inside a checkout of the reference project, for the tests that read its sample files when it is
+    available: ``FBAM_REFERENCE_DIR``, else a directory named ``reference`` beside this repository."""
+    import os
+    base = os.environ.get("FBAM_REFERENCE_DIR") or os.path.join(
+        os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
+    return os.path.join(base, *parts)

@@ -3,6 +3,7 @@ import json
 import os
 
 import pytest
+from conftest import reference_path
 
 from fbamtrain_b200 import presets
 from fbamtrain_b200.config import ConfigError, ParallelConfiguration, RunConfiguration
@@ -45,7 +46,7 @@ def test_reference_debug_config_parses():
 
 
 def test_reference_file_on_disk_if_present():
-    path = "/root/reference/working_dir/run-configs/debug.json"
+    path = reference_path("working_dir", "run-configs", "debug.json")
     if not os.path.exists(path):
         pytest.skip("reference tree not mounted")
     assert RunConfiguration.from_json_file(path) is not None

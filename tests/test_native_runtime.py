@@ -6,6 +6,7 @@ import threading
 
 import numpy as np
 import pytest
+from conftest import reference_path
 import torch
 
 from fbamtrain_b200 import runtime as rt
@@ -49,7 +50,7 @@ def test_native_tokenizer_matches_python(tmp_path):
 
 
 def test_reference_tokenizer_file_natively_if_present():
-    path = "/root/reference/working_dir/tokenizer.txt"
+    path = reference_path("working_dir", "tokenizer.txt")
     if not os.path.exists(path):
         pytest.skip("reference tree not mounted")
     nat, py = rt.NativeTokenizer(path), Tokenizer.from_file(path)

@@ -3,6 +3,7 @@ import os
 
 import numpy as np
 import pytest
+from conftest import reference_path
 import torch
 
 from fbamtrain_b200.data import (ArrayRecording, DatasetCursorCommitter, DatasetCursorSnapshot,
@@ -52,7 +53,7 @@ def test_tokenizer_sort_trie_and_longest_match(tmp_path):
 
 
 def test_reference_tokenizer_file_if_present():
-    path = "/root/reference/working_dir/tokenizer.txt"
+    path = reference_path("working_dir", "tokenizer.txt")
     if not os.path.exists(path):
         pytest.skip("reference tree not mounted")
     tok = Tokenizer.from_file(path)
