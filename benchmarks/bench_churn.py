@@ -132,8 +132,8 @@ def main():
     a = ap.parse_args()
 
     import torch.multiprocessing as mp
-    from fbamtrain_b200.parallel.ftccl import MembershipMaster
-    master = MembershipMaster(heartbeat_timeout_s=15.0).start()
+    from fbamtrain_b200.parallel.ftccl import create_master
+    master = create_master(heartbeat_timeout_s=15.0).start()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = {i: ctx.Process(target=_worker, args=(i, master.port, a, q, None)) for i in range(a.gpus)}

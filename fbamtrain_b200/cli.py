@@ -48,11 +48,13 @@ def build_parser() -> argparse.ArgumentParser:
 
 
 def _run_ftccl_master(par: ParallelConfiguration) -> int:
-    from .parallel.ftccl import MembershipMaster
+    from .parallel.ftccl import create_master
     ep = par.ddp_parallel.ftccl_master
     if ep is None:
         LOG("FATAL", "--ftccl-master needs ddp_parallel.transport = \"ftccl\" with an ftccl_master endpoint")
-    master = MembershipMaster(ep.ip, ep.port)
+    master = create_master(ep.ip, ep.port)
+    if master.port == 0:          # the native service binds when started
+        master.start()
     LOG("INFO", f"ftccl master listening on {ep.ip}:{master.port}")
     try:
         master.run()

@@ -333,6 +333,61 @@ class MembershipMaster:
                 pass
 
 
+class NativeMembershipMaster:
+    """The same service implemented in the native runtime (``csrc/runtime/membership.cpp``): one accept thread and
+    one thread per peer connection inside the library, no Python in the request path.  Drop-in for
+    :class:`MembershipMaster` (``start`` / ``port`` / ``snapshot`` / ``interrupt`` / ``await_termination``)."""
+
+    def __init__(self, ip: str = "127.0.0.1", port: int = 0, heartbeat_timeout_s: float = 2.0):
+        self.ip, self._want_port, self.heartbeat_timeout_s = ip, port, heartbeat_timeout_s
+        self.port = 0
+        self._handle = None
+
+    def start(self) -> "NativeMembershipMaster":
+        import ctypes as C
+        from .. import runtime
+        out = C.c_int(0)
+        handle = runtime.lib().fbam_master_start(self.ip.encode(), self._want_port, self.heartbeat_timeout_s,
+                                                 C.byref(out))
+        if not handle:
+            raise OSError(f"cannot start the membership master on {self.ip}:{self._want_port}")
+        self._handle, self.port = handle, out.value
+        return self
+
+    def run(self) -> None:
+        """Blocks until interrupted (for a stand-alone master process)."""
+        if self._handle is None:
+            self.start()
+        while self._handle is not None:
+            time.sleep(0.2)
+
+    def snapshot(self) -> dict:
+        import ctypes as C
+        from .. import runtime
+        buf = C.create_string_buffer(1 << 16)
+        runtime.lib().fbam_master_snapshot(self._handle, buf, len(buf))
+        return json.loads(buf.value.decode())
+
+    def interrupt(self) -> None:
+        if self._handle is not None:
+            from .. import runtime
+            handle, self._handle = self._handle, None
+            runtime.lib().fbam_master_stop(handle)
+
+    def await_termination(self, timeout: float = 5.0) -> None:
+        return None
+
+
+def create_master(ip: str = "127.0.0.1", port: int = 0, heartbeat_timeout_s: float = 2.0, native: Optional[bool] = None):
+    """The membership master for a job: the native service when the runtime library is built (or ``native=True``),
+    the Python one otherwise."""
+    if native is None:
+        from .. import runtime
+        native = runtime.available()
+    cls = NativeMembershipMaster if native else MembershipMaster
+    return cls(ip, port, heartbeat_timeout_s)
+
+
 # =================================================================================================
 # peer
 # =================================================================================================

@@ -2,7 +2,8 @@
 
 The native library holds the pieces the reference implements in C++ outside its tensor library: SplitMix64
 dataset RNG and batch drawing, the ``FBAM_TOK v1.0`` trie tokenizer, a safetensors reader / durable writer /
-file comparer, the durable dataset-cursor writer thread, and the TCP rendezvous.  The pure-Python modules
+file comparer, the durable dataset-cursor writer thread, the TCP rendezvous, and the membership master of the
+fault-tolerant collective layer.  The pure-Python modules
 (``rng``, ``tokenizer``, ``utils.safetensors_io``, ``data.cursor``, ``parallel.rendezvous``) implement the same
 behaviour and are used as oracles in the tests; callers may use either.
 """
@@ -35,6 +36,11 @@ def lib() -> C.CDLL:
             build.build_runtime()
         L = C.CDLL(LIB_PATH)
         L.fbam_rt_last_error.restype = C.c_char_p
+        L.fbam_master_start.restype = C.c_void_p
+        L.fbam_master_start.argtypes = [C.c_char_p, C.c_int, C.c_double, C.POINTER(C.c_int)]
+        L.fbam_master_stop.argtypes = [C.c_void_p]
+        L.fbam_master_snapshot.restype = C.c_int
+        L.fbam_master_snapshot.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
         L.fbam_splitmix_next.restype = C.c_uint64
         L.fbam_splitmix_next.argtypes = [C.POINTER(C.c_uint64)]
         L.fbam_splitmix_randint.restype = C.c_int64

@@ -8,7 +8,7 @@ import pytest
 import torch
 import torch.multiprocessing as mp
 
-from fbamtrain_b200.parallel.ftccl import MembershipMaster
+from fbamtrain_b200.parallel.ftccl import create_master
 
 
 def _worker(idx, port, q, total_steps, shrunk):
@@ -70,7 +70,7 @@ def _worker(idx, port, q, total_steps, shrunk):
 
 
 def test_trainer_survives_peer_loss_and_admits_joiner():
-    master = MembershipMaster(heartbeat_timeout_s=0.8).start()
+    master = create_master(heartbeat_timeout_s=0.8).start()      # the native service when the runtime is built
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     shrunk = ctx.Event()

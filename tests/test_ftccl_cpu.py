@@ -7,8 +7,10 @@ import pytest
 import torch
 import torch.multiprocessing as mp
 
-from fbamtrain_b200.parallel.ftccl import (Attribute, FtPeer, MembershipMaster, Result, SharedStateSyncStrategy,
-                                            TensorInfo, tensor_hash)
+from fbamtrain_b200.parallel.ftccl import (Attribute, FtPeer, MembershipMaster, NativeMembershipMaster, Result,
+                                            SharedStateSyncStrategy, TensorInfo, tensor_hash)
+
+MASTERS = {"python": MembershipMaster, "native": NativeMembershipMaster}
 
 
 def _peer_main(idx, port, q, script):
@@ -37,8 +39,9 @@ def _script_basic(idx, peer, q):
     q.put(("basic", idx, peer.rank, state.tolist()[0], t.tolist()[0], info.rx_bytes, info.tx_bytes))
 
 
-def test_admission_shared_state_and_allreduce():
-    master = MembershipMaster(heartbeat_timeout_s=2.0).start()
+@pytest.mark.parametrize("kind", ["python", "native"])
+def test_admission_shared_state_and_allreduce(kind):
+    master = MASTERS[kind](heartbeat_timeout_s=2.0).start()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_peer_main, args=(i, master.port, q, _script_basic)) for i in range(3)]
@@ -93,8 +96,9 @@ def _script_churn(idx, peer, q):
     q.put(("done", idx, step, w.tolist(), dropped, peer.world_size))
 
 
-def test_silent_failure_eviction_and_late_joiner_catch_up():
-    master = MembershipMaster(heartbeat_timeout_s=0.6).start()
+@pytest.mark.parametrize("kind", ["python", "native"])
+def test_silent_failure_eviction_and_late_joiner_catch_up(kind):
+    master = MASTERS[kind](heartbeat_timeout_s=0.6).start()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_peer_main, args=(i, master.port, q, _script_churn)) for i in range(4)]

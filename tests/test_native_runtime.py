@@ -111,3 +111,54 @@ def test_native_rendezvous_and_interop_with_python():
     t2.join(20)
     th.join(20)
     assert out["native"] == blob and out["py"] == blob
+
+
+def test_native_membership_master_protocol():
+    """Wire-level check of the native membership service: connect, heartbeat, a two-peer vote, a step gate that
+    reports a newcomer, leave."""
+    import json
+    import socket
+    import threading
+    from fbamtrain_b200.parallel.ftccl import NativeMembershipMaster
+    master = NativeMembershipMaster(heartbeat_timeout_s=5.0).start()
+    try:
+        def rpc(sock, obj):
+            sock.sendall((json.dumps(obj) + "\n").encode())
+            buf = b""
+            while not buf.endswith(b"\n"):
+                buf += sock.recv(4096)
+            return json.loads(buf)
+
+        a = socket.create_connection(("127.0.0.1", master.port))
+        b = socket.create_connection(("127.0.0.1", master.port))
+        ua = rpc(a, {"op": "connect", "peer_group": 0, "ip": "127.0.0.1"})["uid"]
+        ub = rpc(b, {"op": "connect", "peer_group": 1, "ip": "127.0.0.1"})["uid"]
+        assert rpc(a, {"op": "heartbeat"}) == {"epoch": 0, "pending": 2, "world": 0, "ok": True}
+        out = {}
+        t = threading.Thread(target=lambda: out.update(b=rpc(b, {"op": "vote", "free_port": 7002, "min_world": 2,
+                                                                 "timeout": 20})))
+        t.start()
+        ra = rpc(a, {"op": "vote", "free_port": 7001, "min_world": 2, "timeout": 20})
+        t.join(30)
+        assert ra["ok"] and out["b"]["ok"] and ra["epoch"] == out["b"]["epoch"] == 1 and ra["world"] == 2
+        assert ra["ranks"] == {str(ua): 0, str(ub): 1} and ra["store"] == {"ip": "127.0.0.1", "port": 7001}
+        assert ra["groups"] == {str(ua): 0, str(ub): 1}
+        assert master.snapshot() == {"epoch": 1, "accepted": [ua, ub], "pending": []}
+        # both members reach the gate of step 3: aligned
+        t = threading.Thread(target=lambda: out.update(g=rpc(b, {"op": "gate", "step": 3, "epoch": 1, "world": 2,
+                                                                 "timeout": 10})))
+        t.start()
+        ga = rpc(a, {"op": "gate", "step": 3, "epoch": 1, "world": 2, "timeout": 10})
+        t.join(20)
+        assert ga["aligned"] and out["g"]["aligned"]
+        # a newcomer waits for admission: the gate sends the members to a new vote instead
+        c = socket.create_connection(("127.0.0.1", master.port))
+        rpc(c, {"op": "connect", "peer_group": 0, "ip": "127.0.0.1"})
+        ga = rpc(a, {"op": "gate", "step": 4, "epoch": 1, "world": 2, "timeout": 10})
+        assert ga["ok"] and not ga["aligned"] and ga["pending"] == 1
+        assert rpc(b, {"op": "leave"}) == {"ok": True}
+        assert rpc(a, {"op": "heartbeat"})["world"] == 1
+        for s in (a, b, c):
+            s.close()
+    finally:
+        master.interrupt()
