@@ -57,6 +57,35 @@ class Linear(nn.Module):
         return ops.linear(x, self.weight, self.bias, self.act)
 
 
+class Embedding(nn.Module):
+    """Row lookup ``weight[ids]`` with N(0, 1) initialisation; ids outside ``[0, rows)`` give a zero row, as in the
+    cell-embedding kernel (reference: ``tensorlib/include/embedding.h:16-85`` — forward only there; here the
+    gradient is a scatter-add into the table)."""
+
+    def __init__(self, rows: int, dim: int, dtype: torch.dtype, seeds: SeedSequence):
+        super().__init__()
+        from .init_utils import fill_normal_
+        self.weight = nn.Parameter(torch.empty(rows, dim, dtype=dtype))
+        fill_normal_(self.weight.data, seeds)
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        rows = self.weight.shape[0]
+        valid = (ids >= 0) & (ids < rows)
+        out = torch.nn.functional.embedding(ids.clamp(0, rows - 1).long(), self.weight)
+        return out * valid.unsqueeze(-1).to(out.dtype)
+
+
+class Mean(nn.Module):
+    """Mean over one dimension with fp32 accumulation (reference: ``tensorlib/include/mean.h:13-138``)."""
+
+    def __init__(self, dim: int, keepdim: bool = False):
+        super().__init__()
+        self.dim, self.keepdim = dim, keepdim
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return x.float().mean(dim=self.dim, keepdim=self.keepdim).to(x.dtype)
+
+
 class MlpBlock(nn.Module):
     def __init__(self, dim: int, hidden: int, bias: bool, dtype: torch.dtype, seeds: SeedSequence):
         super().__init__()

@@ -296,3 +296,22 @@ def test_lstm_matches_torch_nn_lstm():
     y2, h2, c2 = ref.lstm_sequence(x, lstm.weight_ih_l0, lstm.weight_hh_l0, lstm.bias_ih_l0, lstm.bias_hh_l0,
                                    h0, c0, torch.float32)
     assert torch.allclose(y, y2, atol=1e-5) and torch.allclose(c[0], c2, atol=1e-5)
+
+
+def test_embedding_and_mean_modules():
+    import torch
+    from fbamtrain_b200.models import Embedding, Mean
+    from fbamtrain_b200.models.init_utils import SeedSequence
+    emb = Embedding(10, 4, torch.float32, SeedSequence(7))
+    ids = torch.tensor([[0, 3, 9], [10, -1, 3]])
+    out = emb(ids)
+    assert out.shape == (2, 3, 4)
+    assert torch.equal(out[0, 1], emb.weight[3]) and torch.equal(out[1, 2], emb.weight[3])
+    assert float(out[1, 0].abs().sum()) == 0.0 and float(out[1, 1].abs().sum()) == 0.0   # out of range -> zero row
+    out.sum().backward()
+    assert float(emb.weight.grad[3].sum()) == 8.0 and float(emb.weight.grad[5].abs().sum()) == 0.0
+    x = torch.arange(24, dtype=torch.float32).view(2, 3, 4).requires_grad_(True)
+    m = Mean(1)(x)
+    assert torch.allclose(m, x.detach().mean(1))
+    m.sum().backward()
+    assert torch.allclose(x.grad, torch.full_like(x, 1.0 / 3))
