@@ -63,6 +63,50 @@ def _run_ftccl_master(par: ParallelConfiguration) -> int:
     return 0
 
 
+def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, device: torch.device) -> int:
+    """``frame_head_parallel``: the first half of ``--world-size`` ranks runs the frame head, the second half the
+    action model (tensor-parallel blocks); ``--master`` marks the first action-model rank, as the reference marks
+    its recurrence master."""
+    import torch.distributed as dist
+    from .data import SyntheticBatchSource
+    from .parallel import rendezvous
+    from .parallel.pipeline import PipelineLayout, PipelineTrainer
+    env_rank = os.environ.get("RANK")
+    if env_rank is not None:
+        rank, world = int(env_rank), int(os.environ["WORLD_SIZE"])
+        kwargs = {"device_id": device} if device.type == "cuda" else {}
+        dist.init_process_group("nccl" if device.type == "cuda" else "gloo", **kwargs)
+    else:
+        rank, world = (args.worker_id or 0), args.world_size
+        ep = par.frame_head_parallel.ccl_rendezvous
+        rendezvous.perform_ccl_rendezvous(ep.ip, ep.port, rank, world, device)
+    layout = PipelineLayout.even_split(world)
+    if args.master and rank != layout.action_ranks[0]:
+        LOG("FATAL", f"--master belongs to rank {layout.action_ranks[0]} (the first action-model rank) of {world}")
+    vocab = cfg.model_config.action_vocab
+    if vocab <= 0:
+        from .tokenizer import Tokenizer
+        vocab = len(Tokenizer.from_file(os.path.join(os.path.dirname(os.path.abspath(args.config)),
+                                                     cfg.tokenizer_file_path)))
+    trainer = PipelineTrainer(cfg, device, vocab, layout, tp_transport="fused" if device.type == "cuda" else "nccl")
+    src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point, vocab,
+                               seed=cfg.train_data_config.iteration_seed, pin=device.type == "cuda")
+    steps = args.steps if args.steps is not None else cfg.max_training_steps
+    for step in range(steps):
+        cells, targets = src.next_batch(cfg.total_batch_size, cfg.train_sequence_length)
+        t0 = time.perf_counter()
+        loss = trainer.train_step(cells.to(device), targets.to(device))
+        if rank == layout.action_ranks[0]:
+            LOG("INFO", f"Step {step} took {time.perf_counter() - t0:.4f} seconds; loss/train = {loss:.6f}")
+            if os.environ.get("FBAMTRAIN_METRICS_JSON"):
+                import json
+                sys.stdout.write(json.dumps({"step": step, "step_time_sec": time.perf_counter() - t0,
+                                             "loss/train": loss}) + "\n")
+                sys.stdout.flush()
+    dist.destroy_process_group()
+    return 0
+
+
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
     if args.verbose:
@@ -94,6 +138,13 @@ def main(argv=None) -> int:
         torch.cuda.set_device(device)
     else:
         device = torch.device("cpu")
+
+    fhp = par.frame_head_parallel if par is not None else None
+    if fhp is not None and fhp.use_frame_head_parallel:
+        if not args.synthetic and cfg.train_data_config.recordings_directory_path:
+            LOG("WARN", "the pipeline mode trains on seeded synthetic frames (recordings are read in the "
+                        "data-parallel mode)")
+        return _run_pipeline(cfg, par, args, device)
 
     dp = None
     ddp = par.ddp_parallel if par is not None else None

@@ -215,3 +215,49 @@ class TwoStagePipeline:
             if p.grad is not None:
                 self.tp.all_reduce(p.grad)
         return float(total)
+
+
+class PipelineTrainer:
+    """Training loop body for the two-stage pipeline: one model replica per rank (each rank only touches its
+    stage's parameters), one optimizer per rank over its stage's parameters, ``total_batch_size / micro_batch_size``
+    micro-batches per step.  Every rank draws the same seeded batch; frame ranks use its cells, action ranks its
+    targets.  This is the mode the reference's ``frame_head_parallel`` configuration maps to (reference:
+    ``src/main.cpp:3119-3123, 3204-3273, 3368-3414, 3588-3598``)."""
+
+    def __init__(self, cfg, device: torch.device, vocab: int, layout: Optional[PipelineLayout] = None,
+                 tp_transport: str = "nccl"):
+        from ..optim import create_optimizer
+        self.cfg, self.device = cfg, device
+        if cfg.total_batch_size % cfg.micro_batch_size:
+            raise ValueError("total_batch_size must be a multiple of micro_batch_size")
+        self.micro_batches = cfg.total_batch_size // cfg.micro_batch_size
+        self.seq = cfg.train_sequence_length
+        torch.manual_seed(cfg.model_config.model_init_seed)
+        self.model = FbamModel(cfg.model_config, vocab).to(device)
+        self.pipe = TwoStagePipeline(self.model, layout or PipelineLayout.even_split(dist.get_world_size()), device,
+                                     self.micro_batches, cfg.micro_batch_size, self.seq, tp_transport)
+        if self.pipe.is_frame:
+            named = [("frame_head." + n, p) for n, p in self.model.frame_head.named_parameters()]
+            prefix = "optim/frame_head"
+        else:
+            named = [("action_model." + n, p) for n, p in self.pipe.action.named_parameters()]
+            prefix = "optim/action_model"
+        self.named = named
+        self.optimizer = create_optimizer(cfg.optimizer_config, named, prefix)
+        self.loss_scale = 1.0 / (self.seq * cfg.total_batch_size)
+        self.step_count = 0
+
+    def train_step(self, cells: torch.Tensor, targets: torch.Tensor) -> float:
+        """``cells`` ``(total_batch, T, P, 3)`` and ``targets`` ``(total_batch, T)`` (the same on every rank).
+        Returns the step loss (identical on every rank)."""
+        for _, p in self.named:
+            p.grad = None
+        mb = self.cfg.micro_batch_size
+        c5 = cells.view(self.micro_batches, mb, *cells.shape[1:]) if self.pipe.is_frame else None
+        t3 = targets.view(self.micro_batches, mb, targets.shape[1]) if not self.pipe.is_frame else None
+        share = self.pipe.run_step(c5, t3, self.loss_scale)
+        self.optimizer.step()
+        self.step_count += 1
+        total = torch.tensor([share], dtype=torch.float64, device=self.device)
+        dist.all_reduce(total)
+        return float(total.item())

@@ -52,3 +52,32 @@ def test_wandb_wrapper_collects_metric_lines():
     r = _run(["fbamtrain_b200.wandb_log_wrapper", "--dry-run", "--", sys.executable, "-c", code])
     assert r.returncode == 0 and "hello" in r.stdout
     assert json.loads(r.stdout.strip().splitlines()[-1])["metrics_logged"] == 1
+
+
+def test_cli_frame_head_parallel_runs_the_two_stage_pipeline(tmp_path):
+    """Two processes launched the way the reference's launcher script does it (``--worker_id`` / ``--world-size``
+    / ``--master`` plus a parallel configuration): rank 0 runs the frame head, rank 1 the action model."""
+    import socket
+    cfg = presets.tiny()
+    cfg["model_config"].update({"action_heads": 2, "lstm_layers": 1})
+    cfg["micro_batch_size"], cfg["total_batch_size"] = 2, 4
+    run = tmp_path / "run.json"
+    run.write_text(json.dumps(cfg))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    par = {"frame_head_parallel": {"use_frame_head_parallel": True, "transport": "ccl",
+                                   "ccl_rendezvous": {"ip": "127.0.0.1", "port": port}},
+           "ddp_parallel": {"use_ddp_parallel": False}}
+    parallel = tmp_path / "parallel.json"
+    parallel.write_text(json.dumps(par))
+    env = dict(os.environ, PYTHONPATH=ROOT, FBAMTRAIN_LOG_LEVEL="INFO")
+    base = [sys.executable, "-m", "fbamtrain_b200.cli", "-c", str(run), "--parallel-config", str(parallel),
+            "--synthetic", "--steps", "2", "--device", "cpu", "--world-size", "2"]
+    procs = [subprocess.Popen(base + ["--worker_id", "0"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                              env=env),
+             subprocess.Popen(base + ["--worker_id", "1", "--master"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                              text=True, env=env)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    assert "Step 1 took" in outs[1] and "loss/train" in outs[1]

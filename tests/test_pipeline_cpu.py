@@ -81,3 +81,39 @@ def test_pipeline_matches_single_process():
         fl = am.block[0].mlp.fc1.weight.shape[0] // 2
         i = results[r]["index"]
         assert torch.allclose(g["blk0.w_fc1"], am.block[0].mlp.fc1.weight.grad[i * fl:(i + 1) * fl], atol=2e-6)
+
+
+def _trainer_worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from fbamtrain_b200 import RunConfiguration, presets
+    from fbamtrain_b200.data import SyntheticBatchSource
+    from fbamtrain_b200.parallel.pipeline import PipelineTrainer
+    d = presets.tiny()
+    d["model_config"].update({"action_heads": 2, "lstm_layers": 1})
+    d["micro_batch_size"], d["total_batch_size"] = 2, 4
+    d["optimizer"]["learning_rate"] = 3e-3
+    cfg = RunConfiguration.from_json(d)
+    tr = PipelineTrainer(cfg, torch.device("cpu"), vocab=32)
+    src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=5, pin=False)
+    cells, targets = src.next_batch(4, cfg.train_sequence_length)
+    losses = [tr.train_step(cells, targets) for _ in range(6)]
+    q.put((rank, losses))
+    dist.destroy_process_group()
+
+
+def test_pipeline_trainer_reduces_the_loss():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_trainer_worker, args=(r, 4, port, q)) for r in range(4)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=240) for _ in range(4))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    for r in range(1, 4):
+        assert results[r] == results[0]                 # every rank reports the same global loss
+    assert results[0][-1] < results[0][0] - 0.05        # and training on one batch brings it down
