@@ -77,18 +77,24 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
         kwargs = {"device_id": device} if device.type == "cuda" else {}
         dist.init_process_group("nccl" if device.type == "cuda" else "gloo", **kwargs)
     else:
-        rank, world = (args.worker_id or 0), args.world_size
+        # --world-size ranks per pipeline, --ddp-world-size pipelines side by side; --worker_id counts over all
+        rank, world = (args.worker_id or 0), args.world_size * max(1, args.ddp_world_size)
         ep = par.frame_head_parallel.ccl_rendezvous
         rendezvous.perform_ccl_rendezvous(ep.ip, ep.port, rank, world, device)
-    layout = PipelineLayout.even_split(world)
-    if args.master and rank != layout.action_ranks[0]:
-        LOG("FATAL", f"--master belongs to rank {layout.action_ranks[0]} (the first action-model rank) of {world}")
+    replicas = max(1, args.ddp_world_size) if env_rank is None else max(1, args.ddp_world_size)
+    if world % replicas or (world // replicas) % 2:
+        LOG("FATAL", f"{world} ranks do not split into {replicas} pipelines of an even number of ranks")
+    per = world // replicas
+    layout = PipelineLayout(list(range(per // 2)), list(range(per // 2, per)))   # positions inside one pipeline
+    if args.master and rank % per != layout.action_ranks[0]:
+        LOG("FATAL", f"--master belongs to position {layout.action_ranks[0]} (the first action-model rank) of a pipeline")
     vocab = cfg.model_config.action_vocab
     if vocab <= 0:
         from .tokenizer import Tokenizer
         vocab = len(Tokenizer.from_file(os.path.join(os.path.dirname(os.path.abspath(args.config)),
                                                      cfg.tokenizer_file_path)))
-    trainer = PipelineTrainer(cfg, device, vocab, layout, tp_transport="fused" if device.type == "cuda" else "nccl")
+    trainer = PipelineTrainer(cfg, device, vocab, tp_transport="fused" if device.type == "cuda" else "nccl",
+                              replicas=replicas)
     src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point, vocab,
                                seed=cfg.train_data_config.iteration_seed, pin=device.type == "cuda")
     steps = args.steps if args.steps is not None else cfg.max_training_steps
@@ -96,7 +102,7 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
         cells, targets = src.next_batch(cfg.total_batch_size, cfg.train_sequence_length)
         t0 = time.perf_counter()
         loss = trainer.train_step(cells.to(device), targets.to(device))
-        if rank == layout.action_ranks[0]:
+        if rank == layout.action_ranks[0]:                 # the first pipeline's recurrence master reports
             LOG("INFO", f"Step {step} took {time.perf_counter() - t0:.4f} seconds; loss/train = {loss:.6f}")
             if os.environ.get("FBAMTRAIN_METRICS_JSON"):
                 import json

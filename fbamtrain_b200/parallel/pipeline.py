@@ -87,8 +87,12 @@ class TensorParallelActionModel(nn.Module):
 
 class TwoStagePipeline:
     def __init__(self, model: FbamModel, layout: PipelineLayout, device: torch.device, micro_batches: int,
-                 micro_batch_size: int, seq: int, tp_transport: str = "nccl"):
+                 micro_batch_size: int, seq: int, tp_transport: str = "nccl",
+                 all_layouts: Optional[Sequence[PipelineLayout]] = None):
+        """``all_layouts``: the layouts of every pipeline replica of the job (data parallelism over whole
+        pipelines); process groups are created collectively, so every rank walks through all of them."""
         self.model, self.layout, self.device = model, layout, device
+        all_layouts = list(all_layouts) if all_layouts is not None else [layout]
         self.rank = dist.get_rank()
         self.micro_batches, self.mb_size, self.seq = micro_batches, micro_batch_size, seq
         if len(layout.frame_ranks) != len(layout.action_ranks):
@@ -97,19 +101,25 @@ class TwoStagePipeline:
         self.stage_ranks = layout.frame_ranks if self.is_frame else layout.action_ranks
         self.index = self.stage_ranks.index(self.rank)
         self.partner = (layout.action_ranks if self.is_frame else layout.frame_ranks)[self.index]
-        # every rank creates both groups (collective), keeps its own
-        g_frame = dist.new_group(layout.frame_ranks)
-        g_action = dist.new_group(layout.action_ranks)
-        self.stage_group = g_frame if self.is_frame else g_action
+        # every rank creates every group (collective), keeps its own
+        self.stage_group = None
+        for lay in all_layouts:
+            g_frame = dist.new_group(lay.frame_ranks)
+            g_action = dist.new_group(lay.action_ranks)
+            if self.rank in lay.frame_ranks:
+                self.stage_group = g_frame
+            elif self.rank in lay.action_ranks:
+                self.stage_group = g_action
         # One group per partner pair and direction.  NCCL runs the point-to-point operations of a group in issue
         # order on one stream; with both directions in one group, stage 0's "receive gradient k" (issued before
         # "send embeddings k+1") and stage 1's "receive embeddings k+1" (issued before "send gradient k") would
         # wait for each other forever.
         self.fwd_group = self.bwd_group = None
-        for f_rank, a_rank in zip(layout.frame_ranks, layout.action_ranks):
-            g_fwd, g_bwd = dist.new_group([f_rank, a_rank]), dist.new_group([f_rank, a_rank])
-            if self.rank in (f_rank, a_rank):
-                self.fwd_group, self.bwd_group = g_fwd, g_bwd
+        for lay in all_layouts:
+            for f_rank, a_rank in zip(lay.frame_ranks, lay.action_ranks):
+                g_fwd, g_bwd = dist.new_group([f_rank, a_rank]), dist.new_group([f_rank, a_rank])
+                if self.rank in (f_rank, a_rank):
+                    self.fwd_group, self.bwd_group = g_fwd, g_bwd
         self.n_stage = len(self.stage_ranks)
         frames = micro_batch_size * seq
         if frames % self.n_stage:
@@ -225,17 +235,39 @@ class PipelineTrainer:
     ``src/main.cpp:3119-3123, 3204-3273, 3368-3414, 3588-3598``)."""
 
     def __init__(self, cfg, device: torch.device, vocab: int, layout: Optional[PipelineLayout] = None,
-                 tp_transport: str = "nccl"):
+                 tp_transport: str = "nccl", replicas: int = 1):
+        """``replicas`` > 1 runs that many pipelines side by side (data parallelism over pipelines: the reference's
+        combination of ``ddp_parallel`` with ``frame_head_parallel``, ``src/main.cpp:2563-2588``): consecutive
+        blocks of ``world / replicas`` ranks form one pipeline each, every replica takes its share of the batch
+        and the gradients of ranks in the same position are summed across replicas."""
         from ..optim import create_optimizer
         self.cfg, self.device = cfg, device
-        if cfg.total_batch_size % cfg.micro_batch_size:
-            raise ValueError("total_batch_size must be a multiple of micro_batch_size")
-        self.micro_batches = cfg.total_batch_size // cfg.micro_batch_size
+        world, rank = dist.get_world_size(), dist.get_rank()
+        if replicas < 1 or world % replicas or (world // replicas) % 2:
+            raise ValueError("the world must split into `replicas` pipelines with an even number of ranks each")
+        if cfg.total_batch_size % (cfg.micro_batch_size * replicas):
+            raise ValueError("total_batch_size must be a multiple of micro_batch_size x replicas")
+        self.replicas, self.per_replica = replicas, world // replicas
+        self.replica = rank // self.per_replica
+        self.micro_batches = cfg.total_batch_size // (cfg.micro_batch_size * replicas)
         self.seq = cfg.train_sequence_length
         torch.manual_seed(cfg.model_config.model_init_seed)
         self.model = FbamModel(cfg.model_config, vocab).to(device)
-        self.pipe = TwoStagePipeline(self.model, layout or PipelineLayout.even_split(dist.get_world_size()), device,
-                                     self.micro_batches, cfg.micro_batch_size, self.seq, tp_transport)
+        if replicas == 1:
+            layouts = [layout or PipelineLayout.even_split(world)]
+        else:
+            half = self.per_replica // 2
+            layouts = [PipelineLayout(list(range(r * self.per_replica, r * self.per_replica + half)),
+                                      list(range(r * self.per_replica + half, (r + 1) * self.per_replica)))
+                       for r in range(replicas)]
+        self.pipe = TwoStagePipeline(self.model, layouts[self.replica], device, self.micro_batches,
+                                     cfg.micro_batch_size, self.seq, tp_transport, all_layouts=layouts)
+        self.cross_group = None            # ranks in this rank's position of every replica
+        if replicas > 1:
+            for pos in range(self.per_replica):
+                g = dist.new_group([r * self.per_replica + pos for r in range(replicas)])
+                if rank % self.per_replica == pos:
+                    self.cross_group = g
         if self.pipe.is_frame:
             named = [("frame_head." + n, p) for n, p in self.model.frame_head.named_parameters()]
             prefix = "optim/frame_head"
@@ -253,9 +285,16 @@ class PipelineTrainer:
         for _, p in self.named:
             p.grad = None
         mb = self.cfg.micro_batch_size
+        per = self.micro_batches * mb                      # sequences of this replica
+        cells, targets = cells[self.replica * per:(self.replica + 1) * per], \
+            targets[self.replica * per:(self.replica + 1) * per]
         c5 = cells.view(self.micro_batches, mb, *cells.shape[1:]) if self.pipe.is_frame else None
         t3 = targets.view(self.micro_batches, mb, targets.shape[1]) if not self.pipe.is_frame else None
         share = self.pipe.run_step(c5, t3, self.loss_scale)
+        if self.cross_group is not None:                   # data parallelism over pipelines: sum (loss is pre-scaled)
+            for _, p in self.named:
+                if p.grad is not None:
+                    dist.all_reduce(p.grad, group=self.cross_group)
         self.optimizer.step()
         self.step_count += 1
         total = torch.tensor([share], dtype=torch.float64, device=self.device)

@@ -1,6 +1,8 @@
 """Two-stage pipeline (2 frame-head ranks → 2 action-model ranks with 2-way tensor parallelism) on CPU ranks,
 against the same model trained in one process."""
 import os
+
+import pytest
 import socket
 
 import torch
@@ -83,7 +85,7 @@ def test_pipeline_matches_single_process():
         assert torch.allclose(g["blk0.w_fc1"], am.block[0].mlp.fc1.weight.grad[i * fl:(i + 1) * fl], atol=2e-6)
 
 
-def _trainer_worker(rank, world, port, q):
+def _trainer_worker(rank, world, port, q, replicas=1):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -95,7 +97,7 @@ def _trainer_worker(rank, world, port, q):
     d["micro_batch_size"], d["total_batch_size"] = 2, 4
     d["optimizer"]["learning_rate"] = 3e-3
     cfg = RunConfiguration.from_json(d)
-    tr = PipelineTrainer(cfg, torch.device("cpu"), vocab=32)
+    tr = PipelineTrainer(cfg, torch.device("cpu"), vocab=32, replicas=replicas)
     src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=5, pin=False)
     cells, targets = src.next_batch(4, cfg.train_sequence_length)
     losses = [tr.train_step(cells, targets) for _ in range(6)]
@@ -117,3 +119,22 @@ def test_pipeline_trainer_reduces_the_loss():
     for r in range(1, 4):
         assert results[r] == results[0]                 # every rank reports the same global loss
     assert results[0][-1] < results[0][0] - 0.05        # and training on one batch brings it down
+
+
+def test_data_parallel_over_pipelines_matches_one_pipeline():
+    """Two one-plus-one pipelines side by side (4 ranks) against a single one-plus-one pipeline (2 ranks) on the
+    same total batch: identical loss curves."""
+    ctx = mp.get_context("spawn")
+    curves = {}
+    for world, replicas in ((2, 1), (4, 2)):
+        q = ctx.Queue()
+        port = _free_port()
+        procs = [ctx.Process(target=_trainer_worker, args=(r, world, port, q, replicas)) for r in range(world)]
+        for p in procs:
+            p.start()
+        results = dict(q.get(timeout=240) for _ in range(world))
+        for p in procs:
+            p.join(60)
+            assert p.exitcode == 0
+        curves[replicas] = results[0]
+    assert curves[1] == pytest.approx(curves[2], abs=2e-5)
