@@ -7,7 +7,34 @@ import torch
 
 from . import reference as ref
 
+import os
+
 _BACKEND = "auto"  # "auto": native kernels for CUDA tensors, PyTorch on CPU; "torch": PyTorch everywhere
+
+# Per-family preference from the environment, as the reference's FBAMTRAIN_PREFER_{GEMM,CONV2D,MHA}_BACKEND
+# (reference: ``src/passes/matmul_pass.cpp:35-62``, ``conv2d_pass.cpp:140-172``, ``mha_attention_pass.cpp:290-313``).
+# Values: "native" (the sm_100a kernels of this package; the default) or "torch" (the vendor-library path).
+_FAMILIES = ("gemm", "conv2d", "mha")
+_prefer = {}
+_last = {}
+
+
+def _read_preferences() -> None:
+    _prefer.clear()
+    for fam in _FAMILIES:
+        raw = os.environ.get(f"FBAMTRAIN_PREFER_{fam.upper()}_BACKEND", "native").strip().lower()
+        if raw not in ("native", "torch"):
+            raise ValueError(f"FBAMTRAIN_PREFER_{fam.upper()}_BACKEND must be 'native' or 'torch', got '{raw}'")
+        _prefer[fam] = raw
+
+
+_read_preferences()
+
+
+def last_backend(family: str) -> str:
+    """Which implementation the most recent call of an op family used: "native", "torch" or "" (not called yet).
+    Tests assert on it the way the reference's tests assert that the expected backend was chosen."""
+    return _last.get(family, "")
 
 
 def set_backend(name: str) -> None:
@@ -24,10 +51,19 @@ def get_backend() -> str:
 _warned_dtypes = set()
 
 
-def _native(t: torch.Tensor, dtype: Optional[torch.dtype] = None) -> bool:
+def _native(t: torch.Tensor, dtype: Optional[torch.dtype] = None, family: Optional[str] = None) -> bool:
     """The hand-written kernels compute in bf16 (fp32 accumulate).  CUDA tensors of another activation dtype
     (the reference's fp16 mode, fp32 debugging runs) take the PyTorch definitions, i.e. the vendor libraries."""
+    use = _native_inner(t, dtype, family)
+    if family is not None:
+        _last[family] = "native" if use else "torch"
+    return use
+
+
+def _native_inner(t: torch.Tensor, dtype: Optional[torch.dtype], family: Optional[str]) -> bool:
     if not (t.is_cuda and _BACKEND == "auto"):
+        return False
+    if family is not None and _prefer.get(family, "native") == "torch":
         return False
     dtype = dtype or t.dtype
     if dtype == torch.bfloat16:
@@ -48,7 +84,7 @@ def cell_embed(cells, cp_embed, pos_embed, colour_embed, out_dtype):
 
 
 def conv2d_nhwc(x, w_ohwi, stride: int, padding: int, dilation: int):
-    if _native(x):
+    if _native(x, family="conv2d"):
         from .native_ops import conv2d_nhwc as f
         return f(x, w_ohwi, stride, padding, dilation)
     return ref.conv2d_nhwc(x, w_ohwi, stride, padding, dilation)
@@ -99,7 +135,7 @@ def global_avg_pool_nhwc(x):
 
 def conv_gelu_stack_pool(x, weights, stride: int, paddings, dilations):
     """``[conv3x3 (no bias) → GELU] x n → mean over positions``: ``(N, H, W, C)`` → ``(N, C_last)``."""
-    if _native(x) and all(w.shape[3] % 64 == 0 for w in weights):
+    if _native(x, family="conv2d") and all(w.shape[3] % 64 == 0 for w in weights):
         from .native_ops import conv_gelu_stack_pool as f
         return f(x, weights, stride, paddings, dilations)
     for w, pad, dil in zip(weights, paddings, dilations):
@@ -108,14 +144,14 @@ def conv_gelu_stack_pool(x, weights, stride: int, paddings, dilations):
 
 
 def linear(x, weight, bias: Optional[torch.Tensor] = None, act: str = "none"):
-    if _native(x):
+    if _native(x, family="gemm"):
         from .native_ops import linear as f
         return f(x, weight, bias, act)
     return ref.linear(x, weight, bias, act)
 
 
 def attention(q, k, v, causal: bool):
-    if _native(q):
+    if _native(q, family="mha"):
         from .native_ops import attention as f
         return f(q, k, v, causal)
     if q.is_cuda:  # PyTorch baseline on GPU: library flash attention

@@ -520,3 +520,23 @@ def test_non_bf16_models_train_on_the_library_path(dtype):
     losses = [float(tr.train_step(cells, tg)) for _ in range(4)]
     tr.close()
     assert all(math.isfinite(x) for x in losses) and losses[-1] < losses[0]
+
+
+def test_expected_backends_are_chosen_on_gpu():
+    """bf16 CUDA tensors must reach the sm_100a kernels (no silent library fallback), other dtypes the library."""
+    _nops()
+    from fbamtrain_b200 import ops
+    from fbamtrain_b200.ops import dispatch
+    x = torch.randn(64, 128, device=DEV).to(BF)
+    w = torch.randn(256, 128, device=DEV).to(BF)
+    ops.linear(x, w)
+    assert dispatch.last_backend("gemm") == "native"
+    q = torch.randn(1, 128, 2, 64, device=DEV).to(BF)
+    ops.attention(q, q, q, True)
+    assert dispatch.last_backend("mha") == "native"
+    img = torch.randn(2, 8, 16, 64, device=DEV).to(BF)
+    wt = torch.randn(64, 3, 3, 64, device=DEV).to(BF)
+    ops.conv2d_nhwc(img, wt, 1, 1, 1)
+    assert dispatch.last_backend("conv2d") == "native"
+    ops.linear(x.float(), w.float())
+    assert dispatch.last_backend("gemm") == "torch"

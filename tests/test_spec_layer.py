@@ -201,3 +201,20 @@ def test_flop_accounting_separates_recomputation():
     assert flops.snapshot() == (18.0, 12.0)
     flops.reset()
     assert flops.snapshot() == (0.0, 0.0)
+
+
+def test_backend_preference_environment(monkeypatch):
+    import torch
+    from fbamtrain_b200.ops import dispatch
+    monkeypatch.setenv("FBAMTRAIN_PREFER_MHA_BACKEND", "torch")
+    dispatch._read_preferences()
+    assert dispatch._prefer == {"gemm": "native", "conv2d": "native", "mha": "torch"}
+    q = torch.randn(1, 4, 2, 8)
+    dispatch.attention(q, q, q, True)
+    assert dispatch.last_backend("mha") == "torch"           # CPU tensors never take the native path
+    monkeypatch.setenv("FBAMTRAIN_PREFER_GEMM_BACKEND", "cutlass")
+    with pytest.raises(ValueError, match="GEMM_BACKEND"):
+        dispatch._read_preferences()
+    monkeypatch.delenv("FBAMTRAIN_PREFER_GEMM_BACKEND")
+    monkeypatch.delenv("FBAMTRAIN_PREFER_MHA_BACKEND")
+    dispatch._read_preferences()
