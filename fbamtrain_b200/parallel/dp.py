@@ -346,14 +346,17 @@ class DataParallel:
 
     def _fused_step(self, trainer) -> None:
         cur = torch.cuda.current_stream()
-        if not getattr(self, "_early", False):
+        if getattr(self, "_early", False):
+            # The action-model buckets went out on the side stream under the frame head's backward.  All fused
+            # kernels share the entry/exit flag slots, so the frame head's buckets queue behind them rather than
+            # beside them (by now the side stream has long finished; this only fixes the order).
+            cur.wait_stream(self._side)
+            self._early = False
+        else:
             with gputx_range("fbamtrain::action_model_grad_allreduce"):
                 self._fused_scope(trainer, "action_model")
         with gputx_range("fbamtrain::frame_head_grad_allreduce"):
             self._fused_scope(trainer, "frame_head")
-        if getattr(self, "_early", False):
-            cur.wait_stream(self._side)
-            self._early = False
         self._step_non_adamw(trainer)
 
     # ------------------------------------------------------------------------------------------
