@@ -144,6 +144,7 @@ class DataParallel:
         self.group = group
         self.rank = dist.get_rank(group)
         self.world_size = dist.get_world_size(group)
+        self._owners = None               # the matrix-to-owner map of the fused Muon path depends on the world size
         if self.mode == "fused":
             # buckets are padded to the NOMINAL world; with fewer ranks the slice size must still divide
             for g in trainer.all_groups():
@@ -376,3 +377,39 @@ class DataParallel:
                     for name, _ in opt.muon.named_params:
                         for t in opt.muon.state[name].values():
                             dist.broadcast(t, src=self._global(owners[name]), group=self.group)
+
+
+def recover_sharded_state(tensors_with_fallback, old: Optional[tuple], group: Optional[dist.ProcessGroup]) -> int:
+    """After a membership change of a group whose members each maintained only a slice of some flat state tensors
+    (the sharded AdamW moments and fp32 masters of the fused / ZeRO-1 modes): make every member hold all of it again.
+
+    ``tensors_with_fallback``: list of ``(tensor, fallback)``; ``tensor`` is a flat state tensor of which this
+    member's OLD slice ``[old_rank · n/old_world, (old_rank + 1) · n/old_world)`` is current; ``fallback`` is
+    ``None`` (slices whose owner is gone restart from zero — Adam moments) or a tensor of the same length to take
+    them from (masters: the current low-precision parameters, which every member holds).  ``old = (old_rank,
+    old_world)``, or ``None`` for a member that just joined and owns nothing.  Collective over ``group``.
+    Returns the number of old slices that had no surviving owner."""
+    world = dist.get_world_size(group)
+    everyone: List[Optional[tuple]] = [None] * world
+    dist.all_gather_object(everyone, old, group=group)
+    known = [o for o in everyone if o is not None]
+    if not known:
+        return 0
+    old_world = known[0][1]
+    if any(o[1] != old_world for o in known):
+        raise ValueError("members disagree about the previous world size")
+    covered = {o[0] for o in known}
+    lost = [r for r in range(old_world) if r not in covered]
+    for t, fallback in tensors_with_fallback:
+        n = t.numel()
+        per = n // old_world
+        mine = torch.zeros_like(t)
+        if old is not None:
+            lo, hi = old[0] * per, (old[0] + 1) * per
+            mine[lo:hi] = t[lo:hi]
+        dist.all_reduce(mine, group=group)
+        if fallback is not None:
+            for r in lost:
+                mine[r * per:(r + 1) * per] = fallback[r * per:(r + 1) * per].to(mine.dtype)
+        t.copy_(mine)
+    return len(lost)

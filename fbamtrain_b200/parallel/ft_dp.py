@@ -77,9 +77,7 @@ class FaultTolerantDataParallel:
             trainer.step_count = info.revision
             for opt in trainer.optimizers.values():
                 opt.set_step(info.revision)
-        for opt in trainer.optimizers.values():      # masters of 16-bit parameters follow the synchronised copies
-            pass
-        return True
+        return True     # fp32 master copies are optimizer tensors and were synchronised with the rest
 
     def _retopologize(self, trainer, joining: bool = False) -> bool:
         t0 = time.perf_counter()
@@ -91,15 +89,73 @@ class FaultTolerantDataParallel:
         else:
             return False
         if self.mode == "fused":
+            old = None
             if self.inner is None:
                 self.inner = DataParallel(mode="fused", group=None, window_transport="ipc")
                 self.inner.attach_windows_only(trainer)
             else:
+                old = (self.inner.rank, self.inner.world_size)
+                old_owners = {id(opt.muon): dict(self.inner._muon_owner_map(opt.muon))
+                              for opt in trainer.optimizers.values() if hasattr(opt, "muon") and old[1] > 1}
                 self.inner.rebuild(trainer, None)
+                self._old_muon_owners = old_owners
+            self._recover_sharded_state(trainer, old)
         ok = self._sync_state(trainer, joining)
         self.events.append({"epoch": self.peer.epoch, "world": self.peer.world_size, "step": trainer.step_count,
                             "seconds": time.perf_counter() - t0})
         return ok
+
+    def _recover_sharded_state(self, trainer, old) -> None:
+        """The fused step keeps AdamW moments and fp32 masters current only in each member's slice of a bucket, and
+        the slices move when the world changes: collect them from the members that are still here before the state
+        is compared and handed to joiners.  Slices of members that are gone restart their moments from zero and
+        take their masters from the (replicated) parameters; Muon momentum of matrices whose owner is gone restarts
+        from zero as well."""
+        from .dp import recover_sharded_state
+        pairs = []
+        for opt in self.inner._adamw_optimizers(trainer):
+            for g, fs in zip(opt.groups, opt.flat_state):
+                pairs.append((fs["m"], None))
+                pairs.append((fs["v"], None))
+                if "master" in fs:
+                    pairs.append((fs["master"], g.data))
+        if pairs and self.peer.world_size > 1:
+            lost = recover_sharded_state(pairs, old, None)
+            if lost:
+                LOG("WARN", f"ftccl: {lost} optimizer-state slice(s) had no surviving owner; their moments restart")
+        # Muon: the momentum of a matrix is current only on the rank that owned it in the old world (a world of
+        # one owned everything); one summed exchange moves every matrix to where it is needed next
+        old_owners = getattr(self, "_old_muon_owners", {}) or {}
+        self._old_muon_owners = {}
+        if self.peer.world_size > 1:
+            bufs = []
+            for opt in trainer.optimizers.values():
+                if not hasattr(opt, "muon") or not opt.muon.named_params:
+                    continue
+                owners = old_owners.get(id(opt.muon))
+                for name, _ in opt.muon.named_params:
+                    buf = opt.muon.state[name]["momentum"]
+                    if not (old is not None and (owners is None or owners[name] == old[0])):
+                        buf.zero_()
+                    bufs.append(buf)
+            if bufs:
+                flat = torch.cat([b.reshape(-1) for b in bufs])
+                dist.all_reduce(flat)
+                offset = 0
+                for b in bufs:
+                    b.copy_(flat[offset:offset + b.numel()].view_as(b))
+                    offset += b.numel()
+        if pairs and self.peer.world_size <= 1 and old is not None and old[1] > 1:
+            # alone now: everything outside the old slice is stale
+            for t, fallback in pairs:
+                per = t.numel() // old[1]
+                lo, hi = old[0] * per, (old[0] + 1) * per
+                keep = t[lo:hi].clone()
+                if fallback is None:
+                    t.zero_()
+                else:
+                    t.copy_(fallback.to(t.dtype))
+                t[lo:hi] = keep
 
     def attach(self, trainer) -> None:
         if self.peer.uid is None:

@@ -150,3 +150,41 @@ def test_rendezvous_rejects_bad_ranks():
     assert "out of range" in err["e"]
     with pytest.raises(rdv.RendezvousError):
         rdv.perform_ccl_rendezvous("127.0.0.1", port, 5, 2, torch.device("cpu"))
+
+
+def _recover_worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from fbamtrain_b200.parallel.dp import recover_sharded_state
+    n, old_world = 12, 3
+    # old world of three; old rank 1 is gone; new rank 0 was old rank 0, new rank 1 was old rank 2, new rank 2 is new
+    old = {0: (0, old_world), 1: (2, old_world), 2: None}[rank]
+    moment = torch.full((n,), -1.0)
+    master = torch.full((n,), -1.0)
+    if old is not None:
+        per = n // old_world
+        moment[old[0] * per:(old[0] + 1) * per] = 10.0 + old[0]
+        master[old[0] * per:(old[0] + 1) * per] = 20.0 + old[0]
+    params = torch.arange(n, dtype=torch.float32)
+    lost = recover_sharded_state([(moment, None), (master, params)], old, None)
+    q.put((rank, lost, moment.tolist(), master.tolist()))
+    dist.destroy_process_group()
+
+
+def test_recover_sharded_state_after_membership_change():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_recover_worker, args=(r, 3, port, q)) for r in range(3)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=120) for _ in range(3)]
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    want_moment = [10.0] * 4 + [0.0] * 4 + [12.0] * 4          # the lost slice restarts from zero
+    want_master = [20.0] * 4 + [4.0, 5.0, 6.0, 7.0] + [22.0] * 4   # ... and takes its masters from the parameters
+    for rank, lost, moment, master in got:
+        assert lost == 1 and moment == want_moment and master == want_master, (rank, moment, master)
