@@ -4,6 +4,7 @@
     python benchmarks/bench_kernels.py gemm  [--m 4096 --n 4096 --k 4096] [--library]
     python benchmarks/bench_kernels.py conv  [--batch 512 --h 48 --w 160 --cin 128 --cout 256 --stride 2]
     python benchmarks/bench_kernels.py lstm  [--t 1024 --b 8 --hidden 1024]
+    python benchmarks/bench_kernels.py lstm-stream [--t 1024 --b 8 --hidden 1024 --vocab 4096 --chunk 64] [--offload]
     python benchmarks/bench_kernels.py mha   [--b 8 --heads 8 --t 1024 --d 128] [--causal]
 
 Shapes default to the ones the reference's own benchmark programs use (GEMM 4096³ / 8192³, conv
@@ -118,6 +119,39 @@ def bench_lstm(a):
     report(f"lstm_fwd_bwd T{a.t} B{a.b} H{h}", timeit(fwd_bwd, iters=10), 3 * useful)
 
 
+def bench_lstm_stream(a):
+    """Streaming LSTM with the per-chunk LM-head + cross-entropy hook and the recomputing backward whose dY comes
+    from the head (the reference's "backward with supplier" benchmark: ``benchmarks/bench_streaming_lstm*``)."""
+    from fbamtrain_b200.ops.streaming import streaming_lstm_head_ce
+    h, vocab = a.hidden, a.vocab
+    k = 1.0 / math.sqrt(h)
+    x = torch.randn(a.t, a.b, h).bfloat16()
+    x = x.pin_memory() if a.offload else x.cuda().requires_grad_(True)
+    ps = [((torch.rand(4 * h, h, device="cuda") * 2 - 1) * k).requires_grad_(True) for _ in range(2)]
+    bs = [((torch.rand(4 * h, device="cuda") * 2 - 1) * k).requires_grad_(True) for _ in range(2)]
+    h0 = torch.zeros(h, device="cuda", requires_grad=True)
+    c0 = torch.zeros(h, device="cuda", requires_grad=True)
+    w_head = (torch.randn((vocab + 7) // 8 * 8, h, device="cuda") * k).bfloat16().requires_grad_(True)
+    tg = torch.randint(0, vocab, (a.t, a.b), device="cuda")
+    scale = 1.0 / (a.t * a.b)
+    useful = 2.0 * a.t * a.b * (2 * h * 4 * h + h * vocab)
+
+    def fwd():
+        with torch.no_grad():
+            return streaming_lstm_head_ce(x, ps[0], ps[1], bs[0], bs[1], h0, c0, w_head, tg, vocab, scale, a.chunk,
+                                          a.offload)
+
+    def fwd_bwd():
+        loss = streaming_lstm_head_ce(x, ps[0], ps[1], bs[0], bs[1], h0, c0, w_head, tg, vocab, scale, a.chunk,
+                                      a.offload)
+        torch.autograd.grad(loss, ps + bs + [w_head])
+
+    tag = f"T{a.t} B{a.b} H{h} V{vocab} chunk{a.chunk} offload={a.offload}"
+    report(f"lstm_stream_fwd {tag}", timeit(fwd, iters=5), useful)
+    report(f"lstm_stream_fwd_bwd_supplier {tag}", timeit(fwd_bwd, iters=5), 3 * useful,
+           extra={"note": "time includes the recomputation of every chunk's gates (not counted as useful FLOPs)"})
+
+
 def bench_mha(a):
     from fbamtrain_b200 import ops
     q, k, v = (torch.randn(a.b, a.t, a.heads, a.d, device="cuda").bfloat16().requires_grad_(True) for _ in range(3))
@@ -150,12 +184,20 @@ def main():
     l.add_argument("--t", type=int, default=1024)
     l.add_argument("--b", type=int, default=8)
     l.add_argument("--hidden", type=int, default=1024)
+    ls = sub.add_parser("lstm-stream")
+    ls.add_argument("--t", type=int, default=1024)
+    ls.add_argument("--b", type=int, default=8)
+    ls.add_argument("--hidden", type=int, default=1024)
+    ls.add_argument("--vocab", type=int, default=4096)
+    ls.add_argument("--chunk", type=int, default=64)
+    ls.add_argument("--offload", action="store_true")
     m = sub.add_parser("mha")
     for name, default in (("b", 8), ("heads", 8), ("t", 1024), ("d", 128)):
         m.add_argument("--" + name, type=int, default=default)
     m.add_argument("--causal", action="store_true")
     a = ap.parse_args()
-    {"gemm": bench_gemm, "conv": bench_conv, "lstm": bench_lstm, "mha": bench_mha}[a.cmd](a)
+    {"gemm": bench_gemm, "conv": bench_conv, "lstm": bench_lstm, "lstm-stream": bench_lstm_stream,
+     "mha": bench_mha}[a.cmd](a)
 
 
 if __name__ == "__main__":
