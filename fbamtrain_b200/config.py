@@ -129,6 +129,7 @@ class FbamModelConfiguration:
     action_heads: int = 0              # 0 -> n_head
     action_mlp_dim: int = 0            # 0 -> 4 * n_embed
     action_vocab: int = 0              # 0 -> tokenizer size (reference)
+    frame_head_recompute: bool = False  # recompute the frame head's activations in the backward, chunk by chunk
 
     @staticmethod
     def from_json(o: Dict[str, Any]) -> "FbamModelConfiguration":
@@ -164,7 +165,7 @@ class FbamModelConfiguration:
                     "action_blocks", "action_heads", "action_mlp_dim", "action_vocab"):
             if key in o:
                 kw[key] = _uint(o, key, ctx)
-        for key in ("downsample_norm", "frame_proj"):
+        for key in ("downsample_norm", "frame_proj", "frame_head_recompute"):
             if key in o:
                 kw[key] = _bool(o, key, ctx)
         if "downsample_channels" in o:

@@ -38,15 +38,29 @@ class FbamModel(nn.Module):
         self.action_model = ActionModel(cfg, self.vocab, dtype, seeds)
         self.frame_chunk = 0  # frames per frame-head call; 0 = all at once
 
+    def frame_head_chunk(self, flat_cells: torch.Tensor) -> torch.Tensor:
+        """The frame head on ``(frames, P, 3)`` cells.  With ``frame_head_recompute`` nothing but the cells and
+        the embeddings is kept for the backward, which runs the frame head on the chunk again — the memory of the
+        frame head is then one chunk's activations whatever the sequence length (the reference replays and
+        recomputes frame by frame: ``src/main.cpp:3354-3483``).  The second forward does not count as useful FLOPs."""
+        if self.cfg.frame_head_recompute and torch.is_grad_enabled():
+            import contextlib
+            from torch.utils.checkpoint import checkpoint
+            from ..utils import flops
+            return checkpoint(self.frame_head, flat_cells, use_reentrant=False,
+                              context_fn=lambda: (contextlib.nullcontext(), flops.not_useful()))
+        return self.frame_head(flat_cells)
+
     def frame_embeddings(self, cells: torch.Tensor) -> torch.Tensor:
         """``cells`` int32 ``(B, T, P, 3)`` → ``(B, T, n_embed)``."""
         b, t, p, _ = cells.shape
         flat = cells.reshape(b * t, p, 3)
         if self.frame_chunk and flat.shape[0] > self.frame_chunk:
-            parts = [self.frame_head(flat[i:i + self.frame_chunk]) for i in range(0, flat.shape[0], self.frame_chunk)]
+            parts = [self.frame_head_chunk(flat[i:i + self.frame_chunk])
+                     for i in range(0, flat.shape[0], self.frame_chunk)]
             emb = torch.cat(parts, 0)
         else:
-            emb = self.frame_head(flat)
+            emb = self.frame_head_chunk(flat)
         return emb.view(b, t, -1)
 
     def forward(self, cells: torch.Tensor, targets: torch.Tensor, loss_scale: float) -> torch.Tensor:

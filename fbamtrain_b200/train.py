@@ -167,7 +167,7 @@ class Trainer:
                 with gputx_range("fbamtrain::frame_head_fwd"):
                     for i, lo in enumerate(range(0, b * t, chunk)):
                         torch.cuda.current_stream().wait_event(events[i])
-                        parts.append(self.model.frame_head(flat[lo:lo + chunk]))
+                        parts.append(self.model.frame_head_chunk(flat[lo:lo + chunk]))
                 emb = (parts[0] if len(parts) == 1 else torch.cat(parts, 0)).view(b, t, -1)
             with gputx_range("fbamtrain::action_model_fwd_bwd"):
                 loss = self.model.action_model(emb, dev_targets, loss_scale)

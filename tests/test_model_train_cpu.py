@@ -315,3 +315,28 @@ def test_embedding_and_mean_modules():
     assert torch.allclose(m, x.detach().mean(1))
     m.sum().backward()
     assert torch.allclose(x.grad, torch.full_like(x, 1.0 / 3))
+
+
+def test_frame_head_recompute_gives_identical_gradients():
+    import copy
+    import torch
+    from fbamtrain_b200 import RunConfiguration, presets
+    from fbamtrain_b200.data import SyntheticBatchSource
+    from fbamtrain_b200.models import FbamModel
+    from fbamtrain_b200.utils import flops
+    d = presets.tiny()
+    cfg = RunConfiguration.from_json(d)
+    src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=4, pin=False)
+    cells, targets = src.next_batch(2, cfg.train_sequence_length)
+    grads = {}
+    for recompute in (False, True):
+        mc = copy.deepcopy(cfg.model_config)
+        mc.frame_head_recompute = recompute
+        torch.manual_seed(0)
+        model = FbamModel(mc, 32)
+        model.frame_chunk = 8                      # 32 frames -> four chunks
+        flops.reset()
+        model(cells, targets, 1.0 / 32).backward()
+        grads[recompute] = {n: p.grad.clone() for n, p in model.named_parameters()}
+    for n, g in grads[False].items():
+        assert torch.allclose(g, grads[True][n], atol=1e-7), n
