@@ -8,7 +8,6 @@ sit between the LSTM and the head.
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 from torch import nn

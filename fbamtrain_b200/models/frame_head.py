@@ -9,7 +9,6 @@ of the convolutions, per-block channel counts, and a linear projection of the po
 """
 from __future__ import annotations
 
-from typing import List
 
 import torch
 from torch import nn

@@ -15,7 +15,6 @@ per step against ``W_hh`` followed by the same gate arithmetic.
 """
 from __future__ import annotations
 
-import ctypes as C
 
 import torch
 

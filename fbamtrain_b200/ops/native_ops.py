@@ -14,7 +14,6 @@ import torch
 
 from ..utils import debug, flops
 from . import native as nv
-from . import reference as ref
 
 BF16 = torch.bfloat16
 # Large problems run on CTA pairs (tcgen05 cta_group::2: two SMs share every B fetch and keep double-buffered

@@ -28,7 +28,7 @@ from torch import nn
 from .. import ops
 from ..utils.logging import LOG
 from ..models import FbamModel
-from .tensor_parallel import TensorParallelBlock, TpContext, sync_replicated_grads
+from .tensor_parallel import TensorParallelBlock, TpContext
 
 
 RESERVED_SMS = 16   # SMs left to the library's send/receive kernels while a pipeline is active

@@ -21,7 +21,6 @@ instead); the benchmark configurations ask for 4-way TP inside the action-model 
 from __future__ import annotations
 
 import ctypes as C
-import math
 from typing import Dict, Optional, Tuple
 
 import torch

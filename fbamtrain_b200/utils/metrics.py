@@ -16,7 +16,6 @@ import os
 import queue
 import sys
 import threading
-import time
 from dataclasses import dataclass
 from typing import Callable, List, Optional
 

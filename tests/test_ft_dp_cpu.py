@@ -1,10 +1,8 @@
 """Trainer under fault-tolerant data parallelism on CPU ranks: a peer falls silent between steps, the others go
 on; a fresh peer joins later, receives parameters + optimizer state and continues in lock-step."""
-import os
 import threading
 import time
 
-import pytest
 import torch
 import torch.multiprocessing as mp
 

@@ -1,6 +1,5 @@
 """Fault-tolerant membership on CPU ranks: admission, eviction after a silent failure, catch-up of a late joiner
 through shared-state synchronisation, retrying all-reduce.  All failures are injected on the host."""
-import os
 import time
 
 import pytest
