@@ -268,6 +268,269 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 }
 
 // -------------------------------------------------------------------------------------------------
+// forward, two query tiles per CTA
+// -------------------------------------------------------------------------------------------------
+// Same arithmetic as attn_fwd_kernel, organised for more softmax throughput per SM: a CTA owns 256 consecutive
+// queries of one head as two 128-row tiles, each with its own group of four softmax warps, its own S and P·V
+// accumulators in TMEM (S_A, S_B, O_A, O_B = 256 + 2·D columns) and its own P buffer in shared memory; K and V
+// blocks (one stage each, loaded as soon as the MMAs that read the previous block have completed) are shared by
+// both tiles.  One elected thread issues all TMA loads and all MMAs in an order in which no tile ever waits for
+// the other: while one group is busy with its softmax, the tensor core works for the other one.
+template <int D>
+__global__ void __launch_bounds__(288, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+  constexpr int DP = D / 64;
+  constexpr int kQBytes = BQ * D * 2;      // one query tile
+  constexpr int kKVBytes = BKV * D * 2;
+  constexpr int kPBytes = BQ * BKV * 2;
+  constexpr uint32_t kTmemCols = 512;      // S_A [0,128) S_B [128,256) O_A [256,256+D) O_B [256+D,256+2D)
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                      // two tiles
+  uint8_t* sK = sQ + 2 * kQBytes;
+  uint8_t* sV = sK + kKVBytes;
+  uint8_t* sP = sV + kKVBytes;             // two tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kPBytes);
+  uint64_t* q_full = bars;                 // 1
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = bars + 2;
+  uint64_t* v_full = bars + 3;
+  uint64_t* v_empty = bars + 4;
+  uint64_t* s_full = bars + 5;             // [2]
+  uint64_t* p_ready = bars + 7;            // [2]
+  uint64_t* pv_full = bars + 9;            // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb2 = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qb2 * 2 * BQ;
+  const int nkb_all = (p.T + BKV - 1) / BKV;
+  // key blocks each tile attends to (a tile that starts beyond the sequence has none)
+  int nkb_tile[2];
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    const int qb = qb2 * 2 + g;
+    nkb_tile[g] = (q0 + g * BQ >= p.T) ? 0 : (p.causal ? min(nkb_all, qb + 1) : nkb_all);
+  }
+  const int nkb = max(nkb_tile[0], nkb_tile[1]);
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+    mbar_init(q_full, 1);
+    mbar_init(k_full, 1);
+    mbar_init(k_empty, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(&s_full[g], 1);
+      mbar_init(&p_ready[g], 128);
+      mbar_init(&pv_full[g], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 0) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      bool ok = true;
+      mbar_expect_tx(q_full, 2 * kQBytes);
+#pragma unroll
+      for (int g = 0; g < 2; ++g)
+#pragma unroll
+        for (int j = 0; j < DP; ++j)   // rows beyond the sequence are filled with zeros by TMA
+          tma_load_attn(sQ + g * kQBytes + j * BQ * 128, &map_q, q_full, j * 64, h, q0 + g * BQ, b);
+      auto load_k = [&](int kb) {
+        mbar_expect_tx(k_full, kKVBytes);
+#pragma unroll
+        for (int j = 0; j < DP; ++j) tma_load_attn(sK + j * BKV * 128, &map_k, k_full, j * 64, h, kb * BKV, b);
+      };
+      auto load_v = [&](int kb) {
+        mbar_expect_tx(v_full, kKVBytes);
+#pragma unroll
+        for (int j = 0; j < DP; ++j) tma_load_attn(sV + j * BKV * 128, &map_v, v_full, j * 64, h, kb * BKV, b);
+      };
+      const uint32_t idesc_s = make_idesc_bf16(128, BKV, false, false);
+      const uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);   // B = V is MN-major
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      auto issue_s = [&](int g) {      // S_g = Q_g · Kᵀ
+        const uint32_t q_addr = smem_u32(sQ + g * kQBytes);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t da = make_smem_desc_sw128(q_addr + (k / 4) * BQ * 128 + (k % 4) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(k_addr + (k / 4) * BKV * 128 + (k % 4) * 32, 16, 1024);
+          mma_f16_ss(tmem + g * 128, da, db, idesc_s, k != 0);
+        }
+        mma_commit(&s_full[g]);
+      };
+      auto issue_pv = [&](int g) {     // O_g block = P_g · V
+        const uint32_t p_addr = smem_u32(sP + g * kPBytes);
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k) {
+          const uint64_t da = make_smem_desc_sw128(p_addr + (k / 4) * BQ * 128 + (k % 4) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(v_addr + k * 16 * 128, BKV * 128, 1024);
+          mma_f16_ss(tmem + 256 + g * D, da, db, idesc_pv, k != 0);
+        }
+        mma_commit(&pv_full[g]);
+      };
+      if (nkb > 0) {
+        load_k(0);
+        load_v(0);
+        ok = mbar_wait(q_full, 0) && mbar_wait(k_full, 0);
+        if (ok) {
+          fence_after_sync();
+          if (0 < nkb_tile[0]) issue_s(0);
+          if (0 < nkb_tile[1]) issue_s(1);
+          mma_commit(k_empty);
+        }
+      }
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const uint32_t ph = kb & 1;
+        const bool more = kb + 1 < nkb;
+        if (more) {                          // K block kb has been read by both S MMAs: fetch the next one
+          if (!mbar_wait(k_empty, ph)) { ok = false; break; }
+          load_k(kb + 1);
+        }
+        if (!mbar_wait(v_full, ph)) { ok = false; break; }
+        if (kb < nkb_tile[0]) {
+          if (!mbar_wait(&p_ready[0], ph)) { ok = false; break; }
+          fence_after_sync();
+          issue_pv(0);
+        }
+        if (more) {
+          if (!mbar_wait(k_full, ph ^ 1)) { ok = false; break; }
+          fence_after_sync();
+          if (kb + 1 < nkb_tile[0]) issue_s(0);   // S_A was consumed before p_ready[0] arrived
+        }
+        if (kb < nkb_tile[1]) {
+          if (!mbar_wait(&p_ready[1], ph)) { ok = false; break; }
+          fence_after_sync();
+          issue_pv(1);
+        }
+        mma_commit(v_empty);
+        if (more) {
+          if (kb + 1 < nkb_tile[1]) issue_s(1);
+          mma_commit(k_empty);
+          if (!mbar_wait(v_empty, ph)) { ok = false; break; }   // both P·V MMAs of this block have read V
+          load_v(kb + 1);
+        }
+      }
+      if (!ok) atomicExch(p.status, ATT_ERR_TIMEOUT);
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax / output threads of one tile
+    const int g = (warp - 1) >> 2;                   // tile of this warp group
+    const int lane_group = warp & 3;                 // TMEM lane quarter this warp may access
+    const int row = lane_group * 32 + lane;
+    const int qb = qb2 * 2 + g;
+    const int t_q = q0 + g * BQ + row;
+    const uint32_t lane_addr = uint32_t(lane_group * 32) << 16;
+    const uint32_t tmem_s = tmem + g * 128, tmem_pv = tmem + 256 + g * D;
+    uint8_t* sPg = sP + g * kPBytes;
+    const int my_nkb = nkb_tile[g];
+    float m = -INFINITY, l = 0.0f;
+    float o[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) o[d] = 0.0f;
+    bool ok = true;
+    for (int kb = 0; kb < my_nkb; ++kb) {
+      if (!mbar_wait(&s_full[g], kb & 1)) { ok = false; break; }
+      fence_after_sync();
+      const int k0 = kb * BKV;
+      const bool need_mask = (p.causal && kb == qb) || (k0 + BKV > p.T);
+      float mx = m;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BKV; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_s + lane_addr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float sv = __uint_as_float(r[j]);
+          if (need_mask) {
+            const int tk = k0 + c0 + j;
+            if (tk >= p.T || (p.causal && tk > t_q)) sv = -INFINITY;
+          }
+          mx = fmaxf(mx, sv);
+        }
+      }
+      const float m_new = mx;
+      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+      const float alpha = fast_exp2((m - m_use) * p.scale_log2);
+      float rs = 0.0f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BKV; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_s + lane_addr + c0, r);
+        tmem_ld_wait();
+        float pv[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float sv = __uint_as_float(r[j]);
+          if (need_mask) {
+            const int tk = k0 + c0 + j;
+            if (tk >= p.T || (p.causal && tk > t_q)) sv = -INFINITY;
+          }
+          pv[j] = fast_exp2((sv - m_use) * p.scale_log2);
+        }
+#pragma unroll
+        for (int j8 = 0; j8 < 4; ++j8) {
+          __align__(16) __nv_bfloat162 hh[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            hh[q] = __floats2bfloat162_rn(pv[j8 * 8 + 2 * q], pv[j8 * 8 + 2 * q + 1]);
+            const float2 back = __bfloat1622float2(hh[q]);
+            rs += back.x + back.y;
+          }
+          const int chunk = (c0 >> 3) + j8;
+          uint8_t* dst = sPg + (chunk >> 3) * BQ * 128 + swz(row, chunk & 7);
+          *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(hh);
+        }
+      }
+      l = l * alpha + rs;
+      m = m_new;
+      fence_proxy_async();
+      fence_before_sync();
+      mbar_arrive(&p_ready[g]);
+      if (!mbar_wait(&pv_full[g], kb & 1)) { ok = false; break; }
+      fence_after_sync();
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_pv + lane_addr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[c0 + j] = o[c0 + j] * alpha + __uint_as_float(r[j]);
+      }
+      fence_before_sync();
+    }
+    if (ok && my_nkb > 0 && t_q < p.T) {
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      bf16* dst = p.out + (((long long)b * p.T + t_q) * p.H + h) * D;
+#pragma unroll
+      for (int d = 0; d < D; d += 8) {
+        __align__(16) __nv_bfloat162 hh[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) hh[q] = __floats2bfloat162_rn(o[d + 2 * q] * inv, o[d + 2 * q + 1] * inv);
+        *reinterpret_cast<uint4*>(dst + d) = *reinterpret_cast<uint4*>(hh);
+      }
+      if (p.lse != nullptr)
+        p.lse[((long long)b * p.H + h) * p.T + t_q] = (l > 0.0f) ? m * p.scale + logf(l) : -INFINITY;
+    }
+    if (!ok && lane == 0) atomicExch(p.status, ATT_ERR_TIMEOUT);
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) { fence_after_sync(); tmem_dealloc(tmem, kTmemCols); }
+}
+
+// -------------------------------------------------------------------------------------------------
 // backward pre-pass: delta[b,h,t] = sum_d dO*O
 // -------------------------------------------------------------------------------------------------
 __global__ void attn_delta_kernel(const bf16* __restrict__ o, const bf16* __restrict__ d_o, float* __restrict__ delta,
@@ -586,6 +849,29 @@ int fbam_attn_fwd(const void* q, const void* k, const void* v, long long sb, lon
   } else {
     if (set_smem(attn_fwd_kernel<128, 2>, smem)) return 5;
     attn_fwd_kernel<128, 2><<<grid, 160, smem, s>>>(mq, mk, mv, p);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+
+// Variant of fbam_attn_fwd with two query tiles per CTA (attn_fwd2_kernel); same arguments and results.
+int fbam_attn_fwd2(const void* q, const void* k, const void* v, long long sb, long long st, long long sh, void* out,
+                   float* lse, int B, int T, int H, int D, int causal, float scale, int* status, void* stream) {
+  if ((D != 64 && D != 128) || B < 1 || T < 1 || H < 1) return 1;
+  CUtensorMap mq, mk, mv;
+  int e;
+  if ((e = encode_bthd(&mq, q, B, T, H, D, sb, st, sh))) return e;
+  if ((e = encode_bthd(&mk, k, B, T, H, D, sb, st, sh))) return e;
+  if ((e = encode_bthd(&mv, v, B, T, H, D, sb, st, sh))) return e;
+  AttnParams p{B, T, H, D, causal, scale * 1.4426950408889634f, scale, (bf16*)out, lse, status};
+  dim3 grid((T + 2 * BQ - 1) / (2 * BQ), H, B);
+  const int smem = 2 * BQ * D * 2 + 2 * BKV * D * 2 + 2 * BQ * BKV * 2 + 256 + 1024;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 64) {
+    if (set_smem(attn_fwd2_kernel<64>, smem)) return 5;
+    attn_fwd2_kernel<64><<<grid, 288, smem, s>>>(mq, mk, mv, p);
+  } else {
+    if (set_smem(attn_fwd2_kernel<128>, smem)) return 5;
+    attn_fwd2_kernel<128><<<grid, 288, smem, s>>>(mq, mk, mv, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }

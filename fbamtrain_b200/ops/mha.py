@@ -11,12 +11,13 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 
 import torch
 
-from ..utils import flops
 import torch.nn.functional as F
 
+from ..utils import flops
 from . import native as nv
 
 BF16 = torch.bfloat16
@@ -37,10 +38,12 @@ class _FlashAttention(torch.autograd.Function):
         lse = torch.empty(b, h, t, dtype=torch.float32, device=q.device)
         scale = 1.0 / math.sqrt(d)
         sb, st, sh = q.stride(0), q.stride(1), q.stride(2)
-        nv.check(nv.lib().fbam_attn_fwd(nv.ptr(q), nv.ptr(k), nv.ptr(v), C.c_longlong(sb), C.c_longlong(st),
-                                        C.c_longlong(sh), nv.ptr(out), nv.ptr(lse), b, t, h, d, int(causal),
-                                        C.c_float(scale), nv.ptr(nv.status_word(q.device)), nv.stream_ptr()),
-                 "fbam_attn_fwd")
+        # FBAMTRAIN_ATTENTION_FWD2=1 selects the variant with two query tiles per CTA (same results; opt-in until its
+        # measurements are in)
+        fwd = nv.lib().fbam_attn_fwd2 if os.environ.get("FBAMTRAIN_ATTENTION_FWD2") == "1" else nv.lib().fbam_attn_fwd
+        nv.check(fwd(nv.ptr(q), nv.ptr(k), nv.ptr(v), C.c_longlong(sb), C.c_longlong(st), C.c_longlong(sh),
+                     nv.ptr(out), nv.ptr(lse), b, t, h, d, int(causal), C.c_float(scale),
+                     nv.ptr(nv.status_word(q.device)), nv.stream_ptr()), "fbam_attn_fwd")
         flops.add(4.0 * b * h * t * t * d * (0.5 if causal else 1.0))
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.causal, ctx.scale = causal, scale
