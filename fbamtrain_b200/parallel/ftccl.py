@@ -587,11 +587,11 @@ class FtPeer:
                    quantization: QuantizationAlgorithm = QuantizationAlgorithm.NONE) -> Tuple[Result, ReduceInfo]:
         """Sum all-reduce.  A failed collective (lost peer) returns RANK_CONNECTION_LOST and leaves
         ``tensor`` unspecified: callers retry after a topology update or drop the step."""
-        if quantization != QuantizationAlgorithm.NONE:
-            LOG("WARN", "ftccl: quantised all-reduce is not implemented on NVLink transports; using full precision")
         info = ReduceInfo(world_size=self.world_size)
         if self.world_size <= 1:
             return (Result.TOO_FEW_PEERS if self.world_size < 1 else Result.SUCCESS), info
+        if quantization != QuantizationAlgorithm.NONE:
+            return self._all_reduce_quantized(tensor, tag, quantization, info)
         try:
             dist.all_reduce(tensor)
             if tensor.is_cuda:
@@ -601,6 +601,38 @@ class FtPeer:
             return Result.RANK_CONNECTION_LOST, info
         nbytes = tensor.numel() * tensor.element_size()
         info.tx_bytes = info.rx_bytes = 2 * nbytes * (self.world_size - 1) // self.world_size
+        return Result.SUCCESS, info
+
+    def _all_reduce_quantized(self, tensor: torch.Tensor, tag: int, quantization: QuantizationAlgorithm,
+                              info: ReduceInfo) -> Tuple[Result, ReduceInfo]:
+        """Lossy sum for slow links (the reference exposes PCCL's MinMax / ZeroPointScale options,
+        ``ftccl/include/ftccl.h``): every peer sends its contribution as 8-bit codes with a per-tensor affine
+        map, all peers decode and sum in fp32 in rank order — a quarter of the bytes of an fp32 exchange.
+        MinMax maps [min, max] onto 0..255; ZeroPointScale uses a symmetric scale around zero (code 128 = 0)."""
+        x = tensor.detach().float().reshape(-1)
+        if quantization == QuantizationAlgorithm.MIN_MAX:
+            lo, hi = x.min(), x.max()
+        else:
+            hi = x.abs().max()
+            lo = -hi
+        span = torch.clamp(hi - lo, min=1e-30)
+        codes = torch.clamp(torch.round((x - lo) / span * 255.0), 0, 255).to(torch.uint8)
+        meta = torch.stack([lo, span]).float()
+        try:
+            all_codes = [torch.empty_like(codes) for _ in range(self.world_size)]
+            all_meta = [torch.empty_like(meta) for _ in range(self.world_size)]
+            dist.all_gather(all_codes, codes)
+            dist.all_gather(all_meta, meta)
+            if tensor.is_cuda:
+                torch.cuda.synchronize(tensor.device)
+        except Exception as ex:  # noqa: BLE001
+            LOG("WARN", f"ftccl: quantised all-reduce (tag {tag}) failed: {ex}")
+            return Result.RANK_CONNECTION_LOST, info
+        total = torch.zeros_like(x)
+        for c, mt in zip(all_codes, all_meta):
+            total += c.float() * (mt[1] / 255.0) + mt[0]
+        tensor.copy_(total.view_as(tensor).to(tensor.dtype))
+        info.tx_bytes = info.rx_bytes = (codes.numel() + 8) * (self.world_size - 1)
         return Result.SUCCESS, info
 
     def all_reduce_multiple_with_retry(self, tensors: Sequence[torch.Tensor], tags: Sequence[int],

@@ -35,6 +35,17 @@ def _script_basic(idx, peer, q):
     t = torch.full((8,), float(peer.rank + 1))
     res, rinfo = peer.all_reduce(t)
     assert res == Result.SUCCESS
+    # the lossy 8-bit variants agree with the exact sum to within the code resolution and move a quarter of the bytes
+    from fbamtrain_b200.parallel.ftccl import QuantizationAlgorithm
+    gen = torch.Generator().manual_seed(100 + peer.rank)
+    mine = torch.randn(1024, generator=gen)
+    exact = sum(torch.randn(1024, generator=torch.Generator().manual_seed(100 + r)) for r in range(3))
+    for algo in (QuantizationAlgorithm.MIN_MAX, QuantizationAlgorithm.ZERO_POINT_SCALE):
+        q_t = mine.clone()
+        res, qinfo = peer.all_reduce(q_t, quantization=algo)
+        assert res == Result.SUCCESS
+        assert float((q_t - exact).abs().max()) < 3 * 8.0 / 255.0      # three peers, range below 8, half a code each
+        assert qinfo.tx_bytes < 1024 * 4 * 2 * 2 // 3 // 2
     q.put(("basic", idx, peer.rank, state.tolist()[0], t.tolist()[0], info.rx_bytes, info.tx_bytes))
 
 
