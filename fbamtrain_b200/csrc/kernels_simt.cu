@@ -710,6 +710,30 @@ int launch_rms_bwd(const bf16* dy, const bf16* x, const bf16* w, const float* rs
 
 
 // -------------------------------------------------------------------------------------------------
+// SGD step: g' = g + wd·w;  v = mu·v + g';  step = nesterov ? g' + mu·v : v  (no momentum: step = g');
+// w -= lr·step.  w is the fp32 master copy when there is one, else the parameter itself.
+// -------------------------------------------------------------------------------------------------
+template <typename PT>
+__global__ void sgd_kernel(PT* __restrict__ param, const PT* __restrict__ grad, float* __restrict__ velocity,
+                           float* __restrict__ master, long long n, float lr, float mu, int nesterov, float wd) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float g, w;
+  if constexpr (sizeof(PT) == 2) g = __bfloat162float(grad[i]); else g = grad[i];
+  if (master != nullptr) w = master[i];
+  else if constexpr (sizeof(PT) == 2) w = __bfloat162float(param[i]); else w = param[i];
+  g += wd * w;
+  if (velocity != nullptr) {
+    const float v = mu * velocity[i] + g;
+    velocity[i] = v;
+    g = nesterov ? g + mu * v : v;
+  }
+  w -= lr * g;
+  if (master != nullptr) master[i] = w;
+  if constexpr (sizeof(PT) == 2) param[i] = __float2bfloat16(w); else param[i] = w;
+}
+
+// -------------------------------------------------------------------------------------------------
 // 128-bit content fingerprint of a buffer (shared-state comparison between peers): the sum, over all 8-byte
 // words, of two independent 64-bit mixes of (word, index).  Sums commute, so the result does not depend on how
 // the words are spread over threads.  A fingerprint for equality checks between cooperating peers, not a
@@ -905,6 +929,20 @@ int fbam_adamw(void* param, const void* grad, float* m, float* v, float* master,
   else
     adamw_kernel<float><<<blocks, 256, 0, STREAM(stream)>>>((float*)param, (const float*)grad, m, v, master, n, lr, b1,
                                                             b2, eps, wd, 1.0f / bc1, 1.0f / bc2, grad_scale, vec_ok);
+  return CHECK_LAUNCH();
+}
+
+// velocity may be null (no momentum); master may be null (fp32 parameters).
+int fbam_sgd(void* param, const void* grad, float* velocity, float* master, long long n, int param_bf16, float lr,
+             float momentum, int nesterov, float wd, void* stream) {
+  if (n <= 0) return 0;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (param_bf16)
+    sgd_kernel<bf16><<<blocks, 256, 0, STREAM(stream)>>>((bf16*)param, (const bf16*)grad, velocity, master, n, lr,
+                                                        momentum, nesterov, wd);
+  else
+    sgd_kernel<float><<<blocks, 256, 0, STREAM(stream)>>>((float*)param, (const float*)grad, velocity, master, n, lr,
+                                                         momentum, nesterov, wd);
   return CHECK_LAUNCH();
 }
 

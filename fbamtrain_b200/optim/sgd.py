@@ -22,6 +22,8 @@ class SgdOptimizer(Optimizer):
         for name, p in self.named_params:
             if p.grad is None:
                 continue
+            if self._native_step(name, p):
+                continue
             w = self._master(name, p)
             g = p.grad.float()
             if self.weight_decay != 0.0:
@@ -32,3 +34,22 @@ class SgdOptimizer(Optimizer):
                 g = g + self.momentum * v if self.nesterov else v
             w.add_(g, alpha=-self.lr)
             self._publish(name, p)
+
+    def _native_step(self, name: str, p: torch.Tensor) -> bool:
+        """One fused kernel per tensor on a GPU (bf16 parameters with an fp32 master, or fp32 parameters)."""
+        if not p.is_cuda or p.dtype not in (torch.bfloat16, torch.float32) or p.grad.dtype != p.dtype:
+            return False
+        from ..ops import dispatch
+        if dispatch.get_backend() != "auto" or not p.is_contiguous() or not p.grad.is_contiguous():
+            return False
+        import ctypes as C
+        from ..ops import native as nv
+        st = self.state[name]
+        master = st.get("master")
+        if p.dtype == torch.bfloat16 and master is None:
+            return False
+        nv.check(nv.lib().fbam_sgd(nv.ptr(p.data), nv.ptr(p.grad), nv.ptr(st.get("velocity")), nv.ptr(master),
+                                   C.c_longlong(p.numel()), int(p.dtype == torch.bfloat16), C.c_float(self.lr),
+                                   C.c_float(self.momentum), int(self.nesterov), C.c_float(self.weight_decay),
+                                   nv.stream_ptr()), "fbam_sgd")
+        return True

@@ -540,3 +540,27 @@ def test_expected_backends_are_chosen_on_gpu():
     assert dispatch.last_backend("conv2d") == "native"
     ops.linear(x.float(), w.float())
     assert dispatch.last_backend("gemm") == "torch"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("momentum,nesterov", [(0.0, False), (0.9, False), (0.9, True)])
+def test_fused_sgd_step_matches_torch_path(dtype, momentum, nesterov):
+    _nops()
+    from fbamtrain_b200 import ops
+    from fbamtrain_b200.optim import SgdOptimizer
+    torch.manual_seed(22)
+    results = {}
+    for backend in ("auto", "torch"):
+        p = torch.nn.Parameter(torch.linspace(-1, 1, 1000, device=DEV).to(dtype))
+        opt = SgdOptimizer([("w", p)], "optim/t", lr=0.1, momentum=momentum, nesterov=nesterov, weight_decay=0.01)
+        ops.set_backend(backend)
+        try:
+            for k in range(3):
+                p.grad = torch.sin(torch.arange(1000, device=DEV) * 0.01 * (k + 1)).to(dtype)
+                opt.step()
+        finally:
+            ops.set_backend("auto")
+        results[backend] = (p.detach().float().clone(), {n: t.clone() for n, t in opt.state["w"].items()})
+    assert torch.allclose(results["auto"][0], results["torch"][0], atol=1e-6 if dtype == torch.float32 else 1e-2)
+    for n, t in results["torch"][1].items():
+        assert torch.allclose(results["auto"][1][n], t, atol=1e-5), n
