@@ -26,6 +26,7 @@ import torch
 import torch.distributed as dist
 
 from ..utils.logging import LOG
+from ..utils.nvtx import gputx_range
 from .dp import DataParallel
 from .ftccl import FtPeer, Result, SharedStateSyncStrategy, TensorInfo
 
@@ -67,7 +68,8 @@ class FaultTolerantDataParallel:
 
     def _sync_state(self, trainer, joining: bool = False) -> bool:
         strategy = SharedStateSyncStrategy.RECEIVE_ONLY if joining else SharedStateSyncStrategy.ENFORCE_POPULAR
-        res, info = self.peer.synchronize_shared_state(trainer.step_count, self._shared_state(trainer), strategy)
+        with gputx_range("fbamtrain::ccl_state_broadcast"):
+            res, info = self.peer.synchronize_shared_state(trainer.step_count, self._shared_state(trainer), strategy)
         if res != Result.SUCCESS:
             return False
         self.tx_bytes += info.tx_bytes
@@ -205,9 +207,10 @@ class FaultTolerantDataParallel:
             grads = [g.grad for g in trainer.all_groups()]
             if peer.world_size > 1:
                 epoch_before, t0 = peer.epoch, time.perf_counter()
-                res, info = peer.all_reduce_multiple_with_retry(grads, [(trainer.step_count << 8) | k
-                                                                        for k in range(len(grads))],
-                                                                min_world=self.min_world)
+                with gputx_range("fbamtrain::ftccl_action_model_grad_allreduce"):
+                    res, info = peer.all_reduce_multiple_with_retry(grads, [(trainer.step_count << 8) | k
+                                                                            for k in range(len(grads))],
+                                                                    min_world=self.min_world)
                 self.tx_bytes += info.tx_bytes
                 self.rx_bytes += info.rx_bytes
                 if peer.epoch != epoch_before:    # a peer fell out during the collective; the retry re-formed the group

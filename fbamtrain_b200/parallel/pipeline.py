@@ -27,6 +27,7 @@ from torch import nn
 
 from .. import ops
 from ..utils.logging import LOG
+from ..utils.nvtx import gputx_range
 from ..models import FbamModel
 from .tensor_parallel import TensorParallelBlock, TpContext
 
@@ -170,16 +171,20 @@ class TwoStagePipeline:
 
         def forward(k):
             flat = cells[k].reshape(self.mb_size * self.seq, cells.shape[-2], 3)[lo:lo + self.slice_rows]
-            emb = fh(flat.to(self.device))
+            with gputx_range("fbamtrain::frame_head_fwd"):
+                emb = fh(flat.to(self.device))
             outs[k] = emb
             payload = emb.detach().contiguous()
-            sends.append((self._isend(payload), payload))
+            with gputx_range("fbamtrain::ccl_send"):
+                sends.append((self._isend(payload), payload))
             grads[k] = torch.empty(self.slice_rows, e, dtype=emb.dtype, device=self.device)
-            recvs[k] = self._irecv(grads[k])
+            with gputx_range("fbamtrain::ccl_recv_upstream"):
+                recvs[k] = self._irecv(grads[k])
 
         def backward(k):
             recvs[k].wait()
-            outs.pop(k).backward(grads.pop(k))
+            with gputx_range("fbamtrain::frame_head_bwd"):
+                outs.pop(k).backward(grads.pop(k))
 
         forward(0)
         for k in range(1, self.micro_batches):   # 1F1B: next forward first, then the oldest backward
@@ -188,9 +193,10 @@ class TwoStagePipeline:
         backward(self.micro_batches - 1)
         for work, _ in sends:
             work.wait()
-        for p in fh.parameters():                # frame ranks are data parallel over frame slices
-            if p.grad is not None:
-                dist.all_reduce(p.grad, group=self.stage_group)
+        with gputx_range("fbamtrain::frame_head_grad_allreduce"):
+            for p in fh.parameters():            # frame ranks are data parallel over frame slices
+                if p.grad is not None:
+                    dist.all_reduce(p.grad, group=self.stage_group)
         return 0.0
 
     def _run_action(self, targets: torch.Tensor, loss_scale: float) -> float:
@@ -206,13 +212,15 @@ class TwoStagePipeline:
             mine = bufs[k % 2]
             LOG("DEBUG", f"pipeline: action rank {self.rank} micro-batch {k}: embeddings received")
             full = self.tp.all_gather_rows(mine).view(self.mb_size, self.seq, e).requires_grad_(True)
-            loss = am(full, targets[k].to(self.device), loss_scale)
-            loss.backward()
+            with gputx_range("fbamtrain::action_model_fwd_bwd"):
+                loss = am(full, targets[k].to(self.device), loss_scale)
+                loss.backward()
             total += loss.detach().float()
             d_emb = full.grad.reshape(self.mb_size * self.seq, e)
             self.tp.all_reduce(d_emb)             # every TP rank saw only its rows' contribution
             payload = d_emb[self.index * self.slice_rows:(self.index + 1) * self.slice_rows].contiguous()
-            sends.append((self._isend(payload), payload))
+            with gputx_range("fbamtrain::ccl_send_upstream"):
+                sends.append((self._isend(payload), payload))
             # The next receive is posted only now: a posted receive is a resident kernel that spins until the data
             # arrives, and the recurrent kernels of this stage are cooperative launches that need most of the
             # machine at once.  The partner sent these embeddings long ago, so the transfer starts immediately.
@@ -221,9 +229,10 @@ class TwoStagePipeline:
             LOG("DEBUG", f"pipeline: action rank {self.rank} micro-batch {k}: gradient sent")
         for work, _ in sends:
             work.wait()
-        for p in am.replicated_before_shard() + am.replicated_in_shard():
-            if p.grad is not None:
-                self.tp.all_reduce(p.grad)
+        with gputx_range("fbamtrain::action_model_grad_allreduce"):
+            for p in am.replicated_before_shard() + am.replicated_in_shard():
+                if p.grad is not None:
+                    self.tp.all_reduce(p.grad)
         return float(total)
 
 
