@@ -16,6 +16,8 @@ from typing import List, Optional, Tuple
 
 import torch
 
+from ..utils.nvtx import gputx_range
+
 from ..utils.flat import FlatGroup
 from .base import Optimizer
 
@@ -50,8 +52,12 @@ class AdamwOptimizer(Optimizer):
         denom = (v / bc2).sqrt_().add_(self.eps)
         w.addcdiv_(m / bc1, denom, value=-self.lr)
 
-    @torch.no_grad()
     def step(self, shard: Optional[Tuple[int, int]] = None, grad_scale: float = 1.0) -> None:
+        with gputx_range("fbamtrain::optimizer::adamw_step"):
+            return self._step_impl(shard, grad_scale)
+
+    @torch.no_grad()
+    def _step_impl(self, shard: Optional[Tuple[int, int]] = None, grad_scale: float = 1.0) -> None:
         self.step_count += 1
         bc1 = 1.0 - self.beta1 ** self.step_count
         bc2 = 1.0 - self.beta2 ** self.step_count

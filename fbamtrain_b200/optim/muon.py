@@ -22,6 +22,8 @@ from typing import Callable, Iterable, Optional, Tuple
 
 import torch
 
+from ..utils.nvtx import gputx_range
+
 from .adamw import AdamwOptimizer
 from .base import Optimizer
 
@@ -82,8 +84,12 @@ class MuonOptimizer(Optimizer):
         w.mul_(1.0 - self.lr * self.weight_decay).add_(u2d.float().view_as(w), alpha=-self.lr * scale)
         self._publish(name, p)
 
-    @torch.no_grad()
     def step(self) -> None:
+        with gputx_range("fbamtrain::optimizer::muon_step"):
+            return self._step_impl()
+
+    @torch.no_grad()
+    def _step_impl(self) -> None:
         self.step_count += 1
         for name, p in self.named_params:
             if p.grad is None:

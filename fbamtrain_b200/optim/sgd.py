@@ -4,6 +4,8 @@ from __future__ import annotations
 
 import torch
 
+from ..utils.nvtx import gputx_range
+
 from .base import Optimizer
 
 
@@ -16,8 +18,12 @@ class SgdOptimizer(Optimizer):
             for name, p in self.named_params:
                 self.state[name]["velocity"] = torch.zeros_like(p, dtype=torch.float32)
 
-    @torch.no_grad()
     def step(self) -> None:
+        with gputx_range("fbamtrain::optimizer::sgd_step"):
+            return self._step_impl()
+
+    @torch.no_grad()
+    def _step_impl(self) -> None:
         self.step_count += 1
         for name, p in self.named_params:
             if p.grad is None:
