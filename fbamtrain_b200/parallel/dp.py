@@ -253,7 +253,8 @@ class DataParallel:
             sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
             nv.check(nv.lib().fbam_reduce_pull(wg.c_ptrs, nv.ptr(buf), nv.ptr(u), nv.ptr(sumsq), C.c_longlong(off),
                                                C.c_longlong(off + n), int(is_bf16), C.c_float(muon.momentum),
-                                               int(muon.nesterov), C.c_float(1.0), self.world_size, nv.stream_ptr()),
+                                               int(muon.nesterov), C.c_float(self.grad_scale), self.world_size,
+                                               nv.stream_ptr()),
                      "fbam_reduce_pull")
             u2 = native_ns(u.view(p.shape[0], -1), muon.ns_steps, norm=sumsq.sqrt())
             muon.apply_update(name, p, u2)          # writes the local window (p.data is a view of it)
