@@ -139,27 +139,33 @@ def bench_ag_gemm(a, rank, world, dev):
 
 
 def bench_gemm_rs(a, rank, world, dev):
-    """GEMM with a row shard of W (K split) -> reduce-scatter over rows (tensor-parallel fc2 / out-proj)."""
+    """GEMM with a row shard of W (K split) -> reduce-scatter over rows (tensor-parallel fc2 / out-proj), in both
+    forms of the fused transport: partial tiles stored to the owners from the GEMM epilogue, and one GEMM per
+    owner's block with copy-engine transfers under the next GEMM."""
     from fbamtrain_b200.ops import native as nv
     from fbamtrain_b200.ops import native_ops as no
     from fbamtrain_b200.parallel.tensor_parallel import TpContext
-    tp = TpContext(None, dev, "fused")
+    contexts = {}
+    for mode in ("epilogue", "chunked"):
+        os.environ["FBAMTRAIN_TP_RS_MODE"] = mode
+        contexts[mode] = TpContext(None, dev, "fused")
+    os.environ.pop("FBAMTRAIN_TP_RS_MODE", None)
     for m_full, k, n_out in a.shapes:
         kk = n_out // world                     # the K of this GEMM is the sharded hidden dimension
         h = torch.randn(m_full, kk, device=dev).to(BF)
         w = (torch.randn(k, kk, device=dev) / n_out ** 0.5).to(BF)
-
-        def fused():
-            tp.gemm_rs(h, w)
+        tp = contexts["epilogue"]
 
         def library():
             tp.reduce_scatter_rows(no.gemm(h, w))
 
-        tf, tl = _time(fused, a.iters), _time(library, a.iters)
-        nv.check_status(dev)
+        tl = _time(library, a.iters)
         flops = 2.0 * m_full * kk * k
         link = (world - 1) / world * m_full * k * 2     # bf16 partial tiles stored into the owners' slots
-        _report(rank, f"gemm_rs M{m_full} K{n_out}/{world} N{k}", world, tf, tl, flops, link)
+        for mode, ctx in contexts.items():
+            tf = _time(lambda: ctx.gemm_rs(h, w), a.iters)
+            nv.check_status(dev)
+            _report(rank, f"gemm_rs[{mode}] M{m_full} K{n_out}/{world} N{k}", world, tf, tl, flops, link)
 
 
 def bench_muon(a, rank, world, dev):

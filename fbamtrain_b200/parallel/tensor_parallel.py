@@ -21,6 +21,7 @@ instead); the benchmark configurations ask for 4-way TP inside the action-model 
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -39,6 +40,14 @@ class TpContext:
         self.group, self.device, self.transport = group, device, transport
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.spin_limit = spin_limit
+        # GEMM -> reduce-scatter form of the fused transport: "epilogue" (partial tiles stored to the owners from
+        # inside the GEMM) or "chunked" (one GEMM per owner's row block, each block copied to its owner by the copy
+        # engines while the next GEMM runs)
+        self.rs_mode = os.environ.get("FBAMTRAIN_TP_RS_MODE", "epilogue")
+        if self.rs_mode not in ("epilogue", "chunked"):
+            raise ValueError("FBAMTRAIN_TP_RS_MODE must be epilogue or chunked")
+        self._copy_stream = None
+        self._peer_views: Dict[Tuple, torch.Tensor] = {}
         self.peers = None
         self._win: Dict[Tuple, object] = {}
         if transport == "fused":
@@ -117,6 +126,8 @@ class TpContext:
         self._rs_round = getattr(self, "_rs_round", 0) + 1
         # two buffers in turn: a peer may still be summing the previous call's slots while this call's tiles arrive
         win = self._window(f"rs{self._rs_round & 1}", self.world * rows * n, torch.bfloat16)
+        if self.rs_mode == "chunked":
+            return self._gemm_rs_chunked(h, w, win, rows, n)
         pair = n >= 256 and n % 16 == 0 and ((m + 255) // 256) * ((n + 255) // 256) >= 148
         tile_rows = 256 if pair else 128
         first = ((self.rank + 1) % self.world) * rows
@@ -130,6 +141,52 @@ class TpContext:
                                             C.c_uint(self.spin_limit), nv.ptr(nv.status_word(self.device)),
                                             nv.stream_ptr()), "fbam_reduce_slots")
         return out
+
+    def _gemm_rs_chunked(self, h: torch.Tensor, w: torch.Tensor, win, rows: int, n: int) -> torch.Tensor:
+        """One GEMM per owner's block of rows (remote owners first, own block last, a different order on every
+        rank); each finished block goes into this rank's slot of its owner's buffer as one peer-to-peer copy on a
+        second stream — the copy engines move it while the tensor cores work on the next block — and the slot
+        reduction waits for all peers as in the epilogue form."""
+        from ..ops import native as nv
+        from ..ops import native_ops as no
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+        main = torch.cuda.current_stream()
+        slot_elems = rows * n
+        for i in range(self.world):
+            owner = (self.rank + 1 + i) % self.world
+            block = h[owner * rows:(owner + 1) * rows]
+            if owner == self.rank:
+                own = win.local[self.rank * slot_elems:(self.rank + 1) * slot_elems].view(rows, n)
+                no.gemm(block, w, out=own)
+                continue
+            part = no.gemm(block, w)
+            done = torch.cuda.Event()
+            done.record(main)
+            dst = _peer_view(self, win, owner, self.world * slot_elems)[self.rank * slot_elems:
+                                                                        (self.rank + 1) * slot_elems]
+            with torch.cuda.stream(self._copy_stream):
+                self._copy_stream.wait_event(done)
+                dst.copy_(part.view(-1), non_blocking=True)
+            part.record_stream(self._copy_stream)
+        main.wait_stream(self._copy_stream)
+        out = torch.empty(rows, n, dtype=torch.bfloat16, device=h.device)
+        epoch = self.peers.next_epoch()
+        nv.check(nv.lib().fbam_reduce_slots(nv.ptr(win.local), nv.ptr(out), C.c_longlong(slot_elems), self.world,
+                                            self.peers.flags.c_ptrs, self.rank, 5, C.c_uint(epoch),
+                                            C.c_uint(self.spin_limit), nv.ptr(nv.status_word(self.device)),
+                                            nv.stream_ptr()), "fbam_reduce_slots")
+        return out
+
+
+def _peer_view(ctx: "TpContext", win, owner: int, numel: int) -> torch.Tensor:
+    """A bf16 tensor over rank ``owner``'s buffer of ``win`` as mapped into this process."""
+    from .peer_window import _RawDeviceBytes
+    key = (id(win), owner)
+    if key not in ctx._peer_views:
+        raw = torch.as_tensor(_RawDeviceBytes(win.ptrs[owner], numel * 2), device=ctx.device)
+        ctx._peer_views[key] = raw.view(torch.bfloat16)
+    return ctx._peer_views[key]
 
 
 class _RsShape:
