@@ -152,14 +152,16 @@ def _tail(r):
     return text[i:i + 4000] if i >= 0 else text[-4000:]
 
 
-def test_fused_tensor_parallel_block_matches_nccl_on_two_gpus(tmp_path):
+@pytest.mark.parametrize("rs_mode", ["epilogue", "chunked"])
+def test_fused_tensor_parallel_block_matches_nccl_on_two_gpus(tmp_path, rs_mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     out = tmp_path / "result.txt"
     worker = os.path.join(os.path.dirname(__file__), "workers", "tp_fused_worker.py")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", str(_free_port()), worker, str(out)]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, FBAMTRAIN_TP_RS_MODE=rs_mode))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert out.read_text() == "ok"
 
