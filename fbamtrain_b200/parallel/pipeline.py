@@ -89,13 +89,16 @@ class TensorParallelActionModel(nn.Module):
 class TwoStagePipeline:
     def __init__(self, model: FbamModel, layout: PipelineLayout, device: torch.device, micro_batches: int,
                  micro_batch_size: int, seq: int, tp_transport: str = "nccl",
-                 all_layouts: Optional[Sequence[PipelineLayout]] = None):
+                 all_layouts: Optional[Sequence[PipelineLayout]] = None, action_group: int = 1):
         """``all_layouts``: the layouts of every pipeline replica of the job (data parallelism over whole
         pipelines); process groups are created collectively, so every rank walks through all of them."""
         self.model, self.layout, self.device = model, layout, device
         all_layouts = list(all_layouts) if all_layouts is not None else [layout]
         self.rank = dist.get_rank()
         self.micro_batches, self.mb_size, self.seq = micro_batches, micro_batch_size, seq
+        if action_group < 1 or micro_batches % action_group:
+            raise ValueError("action_group must divide the number of micro-batches")
+        self.action_group = action_group
         if len(layout.frame_ranks) != len(layout.action_ranks):
             raise ValueError("both stages need the same number of ranks (one partner each)")
         self.is_frame = self.rank in layout.frame_ranks
@@ -138,7 +141,7 @@ class TwoStagePipeline:
                 nv.lib().fbam_set_reserved_sms(RESERVED_SMS)
         if not self.is_frame:
             self.tp = TpContext(self.stage_group, device, tp_transport)
-            self.action = TensorParallelActionModel(model, self.tp, micro_batch_size, seq).to(device)
+            self.action = TensorParallelActionModel(model, self.tp, micro_batch_size * action_group, seq).to(device)
         self.stats = {"p2p_bytes": 0}
 
     # ------------------------------------------------------------------------------------------
@@ -186,11 +189,16 @@ class TwoStagePipeline:
             with gputx_range("fbamtrain::frame_head_bwd"):
                 outs.pop(k).backward(grads.pop(k))
 
-        forward(0)
-        for k in range(1, self.micro_batches):   # 1F1B: next forward first, then the oldest backward
+        # 1F1B with a lead of `action_group` micro-batches: the action stage returns gradients only once it has a
+        # whole group, so that many forwards go out before the first backward is awaited
+        ahead = min(self.action_group, self.micro_batches)
+        for k in range(ahead):
             forward(k)
-            backward(k - 1)
-        backward(self.micro_batches - 1)
+        for k in range(ahead, self.micro_batches):   # next forward first, then the oldest backward
+            forward(k)
+            backward(k - ahead)
+        for k in range(self.micro_batches - ahead, self.micro_batches):
+            backward(k)
         for work, _ in sends:
             work.wait()
         with gputx_range("fbamtrain::frame_head_grad_allreduce"):
@@ -200,33 +208,38 @@ class TwoStagePipeline:
         return 0.0
 
     def _run_action(self, targets: torch.Tensor, loss_scale: float) -> float:
+        """Receives the micro-batches' embeddings, runs the action model on ``action_group`` micro-batches at a time
+        (the recurrent kernels take the same time for 2 sequences as for 8, so grouping divides their share of the
+        step) and returns each micro-batch's slice of the embedding gradient to the partner rank."""
         e = self.model.cfg.n_embed
         am = self.action
         dtype = am.head_weight.dtype
+        group = self.action_group
         total = torch.zeros((), dtype=torch.float32, device=self.device)   # summed on the device: no host sync
         sends = []
-        bufs = [torch.empty(self.slice_rows, e, dtype=dtype, device=self.device) for _ in range(2)]
-        recv = self._irecv(bufs[0])
-        for k in range(self.micro_batches):
-            recv.wait()
-            mine = bufs[k % 2]
-            LOG("DEBUG", f"pipeline: action rank {self.rank} micro-batch {k}: embeddings received")
-            full = self.tp.all_gather_rows(mine).view(self.mb_size, self.seq, e).requires_grad_(True)
+        bufs = [torch.empty(self.slice_rows, e, dtype=dtype, device=self.device) for _ in range(group)]
+        for k0 in range(0, self.micro_batches, group):
+            # Receives are posted only when their data is needed: a posted receive is a resident kernel that spins
+            # until the data arrives, and the recurrent kernels of this stage are cooperative launches that need
+            # most of the machine at once.  The partner sent these embeddings long ago (or is about to).
+            fulls = []
+            for j in range(group):
+                self._irecv(bufs[j]).wait()
+                fulls.append(self.tp.all_gather_rows(bufs[j]).view(self.mb_size, self.seq, e))
+            LOG("DEBUG", f"pipeline: action rank {self.rank} micro-batches {k0}..{k0 + group - 1}: embeddings received")
+            full = (fulls[0] if group == 1 else torch.cat(fulls, 0)).detach().requires_grad_(True)
+            tg = targets[k0:k0 + group].reshape(group * self.mb_size, self.seq).to(self.device)
             with gputx_range("fbamtrain::action_model_fwd_bwd"):
-                loss = am(full, targets[k].to(self.device), loss_scale)
+                loss = am(full, tg, loss_scale)
                 loss.backward()
             total += loss.detach().float()
-            d_emb = full.grad.reshape(self.mb_size * self.seq, e)
-            self.tp.all_reduce(d_emb)             # every TP rank saw only its rows' contribution
-            payload = d_emb[self.index * self.slice_rows:(self.index + 1) * self.slice_rows].contiguous()
-            with gputx_range("fbamtrain::ccl_send_upstream"):
-                sends.append((self._isend(payload), payload))
-            # The next receive is posted only now: a posted receive is a resident kernel that spins until the data
-            # arrives, and the recurrent kernels of this stage are cooperative launches that need most of the
-            # machine at once.  The partner sent these embeddings long ago, so the transfer starts immediately.
-            if k + 1 < self.micro_batches:
-                recv = self._irecv(bufs[(k + 1) % 2])
-            LOG("DEBUG", f"pipeline: action rank {self.rank} micro-batch {k}: gradient sent")
+            d_all = full.grad.reshape(group, self.mb_size * self.seq, e)
+            self.tp.all_reduce(d_all)             # every TP rank saw only its rows' contribution
+            for j in range(group):
+                payload = d_all[j, self.index * self.slice_rows:(self.index + 1) * self.slice_rows].contiguous()
+                with gputx_range("fbamtrain::ccl_send_upstream"):
+                    sends.append((self._isend(payload), payload))
+            LOG("DEBUG", f"pipeline: action rank {self.rank} micro-batches {k0}..{k0 + group - 1}: gradients sent")
         for work, _ in sends:
             work.wait()
         with gputx_range("fbamtrain::action_model_grad_allreduce"):
@@ -244,7 +257,7 @@ class PipelineTrainer:
     ``src/main.cpp:3119-3123, 3204-3273, 3368-3414, 3588-3598``)."""
 
     def __init__(self, cfg, device: torch.device, vocab: int, layout: Optional[PipelineLayout] = None,
-                 tp_transport: str = "nccl", replicas: int = 1):
+                 tp_transport: str = "nccl", replicas: int = 1, action_group: int = 1):
         """``replicas`` > 1 runs that many pipelines side by side (data parallelism over pipelines: the reference's
         combination of ``ddp_parallel`` with ``frame_head_parallel``, ``src/main.cpp:2563-2588``): consecutive
         blocks of ``world / replicas`` ranks form one pipeline each, every replica takes its share of the batch
@@ -270,7 +283,8 @@ class PipelineTrainer:
                                       list(range(r * self.per_replica + half, (r + 1) * self.per_replica)))
                        for r in range(replicas)]
         self.pipe = TwoStagePipeline(self.model, layouts[self.replica], device, self.micro_batches,
-                                     cfg.micro_batch_size, self.seq, tp_transport, all_layouts=layouts)
+                                     cfg.micro_batch_size, self.seq, tp_transport, all_layouts=layouts,
+                                     action_group=action_group)
         self.cross_group = None            # ranks in this rank's position of every replica
         if replicas > 1:
             for pos in range(self.per_replica):
