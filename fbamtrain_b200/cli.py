@@ -81,7 +81,7 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
         rank, world = (args.worker_id or 0), args.world_size * max(1, args.ddp_world_size)
         ep = par.frame_head_parallel.ccl_rendezvous
         rendezvous.perform_ccl_rendezvous(ep.ip, ep.port, rank, world, device)
-    replicas = max(1, args.ddp_world_size) if env_rank is None else max(1, args.ddp_world_size)
+    replicas = max(1, args.ddp_world_size)
     if world % replicas or (world // replicas) % 2:
         LOG("FATAL", f"{world} ranks do not split into {replicas} pipelines of an even number of ranks")
     per = world // replicas
@@ -93,8 +93,8 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
         from .tokenizer import Tokenizer
         vocab = len(Tokenizer.from_file(os.path.join(os.path.dirname(os.path.abspath(args.config)),
                                                      cfg.tokenizer_file_path)))
-    trainer = PipelineTrainer(cfg, device, vocab, tp_transport="fused" if device.type == "cuda" else "nccl",
-                              replicas=replicas)
+    fused_tp = device.type == "cuda" and per // 2 > 1        # peer-memory kernels need at least two TP ranks
+    trainer = PipelineTrainer(cfg, device, vocab, tp_transport="fused" if fused_tp else "nccl", replicas=replicas)
     src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point, vocab,
                                seed=cfg.train_data_config.iteration_seed, pin=device.type == "cuda")
     steps = args.steps if args.steps is not None else cfg.max_training_steps
