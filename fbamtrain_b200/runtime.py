@@ -181,7 +181,8 @@ def st_read(path: str) -> Dict[str, Tuple[str, np.ndarray]]:
 def st_write(path: str, tensors: Dict[str, Tuple[str, np.ndarray]]) -> None:
     names = list(tensors)
     n = len(names)
-    arrs = [np.ascontiguousarray(tensors[k][1]) for k in names]
+    # (np.ascontiguousarray would turn a 0-d array into shape (1,))
+    arrs = [np.require(tensors[k][1], requirements="C") for k in names]
     c_names = (C.c_char_p * n)(*[k.encode() for k in names])
     c_dtypes = (C.c_char_p * n)(*[tensors[k][0].encode() for k in names])
     ndims = (C.c_int64 * n)(*[a.ndim for a in arrs])
