@@ -69,3 +69,32 @@ def test_safetensors_files_cross_read(tmp_path_factory, shapes, dtype_ix, seed):
         if v.numel():
             assert torch.equal(back[k].reshape(-1).view(torch.uint8), v.reshape(-1).view(torch.uint8))
     assert rt.tenscmp(p_py, p_nat, 0.0)[0] == 0
+
+
+@settings(max_examples=30, deadline=None)
+@given(shapes=st.lists(st.lists(st.integers(1, 7), min_size=1, max_size=3), min_size=1, max_size=8),
+       kinds=st.lists(st.integers(0, 1), min_size=8, max_size=8), multiple=st.sampled_from([1, 2, 6, 12, 840]))
+def test_flat_groups_pack_aligned_and_keep_values(shapes, kinds, multiple):
+    """Packing parameters into flat buckets keeps their values, aliases them into the bucket, aligns every slot to
+    256 bytes, pads the bucket to the shard multiple and leaves no two slots overlapping."""
+    from fbamtrain_b200.utils.flat import ALIGN_BYTES, build_groups
+    dts = [torch.float32, torch.bfloat16]
+    named = [(f"p{i}", torch.nn.Parameter(torch.randn(tuple(s)).to(dts[kinds[i]]))) for i, s in enumerate(shapes)]
+    before = {n: p.detach().clone() for n, p in named}
+    groups = build_groups("scope", named, multiple)
+    assert sum(len(g.named_params) for g in groups) == len(named)
+    for g in groups:
+        esize = torch.empty((), dtype=g.dtype).element_size()
+        assert (g.numel * esize) % (ALIGN_BYTES * multiple) == 0
+        spans = []
+        for n, p in g.named_params:
+            o = g.offsets[n]
+            assert (o * esize) % ALIGN_BYTES == 0
+            assert torch.equal(p.detach(), before[n])
+            assert p.data_ptr() == g.data.data_ptr() + o * esize          # the parameter lives in the bucket
+            assert p.grad.data_ptr() == g.grad.data_ptr() + o * esize
+            spans.append((o, o + p.numel()))
+        spans.sort()
+        assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:])) and spans[-1][1] <= g.numel
+        g.data.zero_()
+        assert all(float(p.detach().float().abs().sum()) == 0.0 for _, p in g.named_params)
