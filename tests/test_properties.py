@@ -98,3 +98,34 @@ def test_flat_groups_pack_aligned_and_keep_values(shapes, kinds, multiple):
         assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:])) and spans[-1][1] <= g.numel
         g.data.zero_()
         assert all(float(p.detach().float().abs().sum()) == 0.0 for _, p in g.named_params)
+
+
+@settings(max_examples=60, deadline=None)
+@given(tokens=st.lists(st.text(alphabet="abc", min_size=1, max_size=4), min_size=1, max_size=8, unique=True),
+       keys=st.lists(st.text(alphabet="abcd", max_size=4), min_size=1, max_size=12))
+def test_token_stream_consumption_equals_greedy_longest_match_over_frames(tokens, keys):
+    """Keystrokes typed over several frames are consumed as the greedy longest-match tokenization of their
+    concatenation; every token is paired with the frame on which its first keystroke was typed; keystrokes that
+    start no token are skipped."""
+    from fbamtrain_b200.data.frames import StreamTokenizationContext, consume_next_token
+    from fbamtrain_b200.data.recording import ArrayRecording
+    tok = Tokenizer(tokens)
+    rec = ArrayRecording(np.zeros((len(keys), 1, 1, 3), dtype=np.uint32), keys)
+    ctx = StreamTokenizationContext(rec, tok, 0)
+    got = []
+    while True:
+        r = consume_next_token(ctx)
+        if r is None:
+            break
+        got.append(r)
+    text = "".join(keys)
+    frame_of = [f for f, k in enumerate(keys) for _ in k]
+    want, i = [], 0
+    while i < len(text):
+        best = max((t for t in tok.tokens if text.startswith(t, i)), key=len, default=None)
+        if best is None:
+            i += 1
+            continue
+        want.append((tok.tokens.index(best), frame_of[i]))
+        i += len(best)
+    assert got == want
