@@ -340,3 +340,36 @@ def test_frame_head_recompute_gives_identical_gradients():
         grads[recompute] = {n: p.grad.clone() for n, p in model.named_parameters()}
     for n, g in grads[False].items():
         assert torch.allclose(g, grads[True][n], atol=1e-7), n
+
+
+def test_oracle_ops_agree_with_torch_builtins():
+    """The PyTorch definitions every kernel is compared against, checked against independent torch formulations."""
+    import torch
+    import torch.nn.functional as F
+    torch.manual_seed(3)
+    q, k, v = (torch.randn(2, 9, 3, 8) for _ in range(3))
+    for causal in (False, True):
+        want = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                              is_causal=causal).transpose(1, 2)
+        assert torch.allclose(ref.attention(q, k, v, causal), want, atol=1e-5)
+    x = torch.randn(5, 7, requires_grad=True)
+    (g,) = torch.autograd.grad(ref.gelu(x).sum(), x)
+    assert torch.allclose(g, ref.gelu_grad(x.detach()), atol=1e-6)
+    img = torch.randn(2, 6, 8, 4)
+    want = F.avg_pool2d(img.permute(0, 3, 1, 2), 2).permute(0, 2, 3, 1)
+    assert torch.allclose(ref.avg_pool2x2_nhwc(img), want, atol=1e-6)
+    w = torch.randn(5, 3, 3, 4)
+    for stride, pad, dil in ((1, 1, 1), (2, 1, 1), (1, 2, 2)):
+        want = F.conv2d(img.permute(0, 3, 1, 2), w.permute(0, 3, 1, 2), None, stride, pad, dil).permute(0, 2, 3, 1)
+        assert torch.allclose(ref.conv2d_nhwc(img, w, stride, pad, dil), want, atol=1e-5)
+    xr = torch.randn(4, 16)
+    gamma = torch.rand(16) + 0.5
+    want = xr / torch.sqrt((xr * xr).mean(-1, keepdim=True) + 1e-5) * gamma
+    assert torch.allclose(ref.rms_norm(xr, gamma, 1e-5), want, atol=1e-6)
+    hdn, head = torch.randn(6, 16), torch.randn(24, 16)
+    tg = torch.randint(0, 20, (6,))
+    want = F.cross_entropy(hdn @ head[:20].t(), tg, reduction="sum") * 0.25
+    assert torch.allclose(ref.lm_head_ce(hdn, head, tg, 20, 0.25), want, atol=1e-5)
+    gate_in = torch.randn(3, 10)
+    vv, gg = gate_in.chunk(2, -1)
+    assert torch.allclose(ref.geglu(gate_in), vv * F.gelu(gg), atol=1e-6)
