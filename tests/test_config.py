@@ -117,3 +117,15 @@ def test_parallel_configs():
 def test_presets_parse(name):
     cfg = RunConfiguration.from_json(json.loads(json.dumps(presets.PRESETS[name]())))
     assert cfg.model_config.frame_proj and cfg.model_config.downsample_conv_stride == 2
+
+
+def test_shipped_sample_configurations_parse():
+    import glob
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs")
+    runs = sorted(glob.glob(os.path.join(root, "*.json")))
+    pars = sorted(glob.glob(os.path.join(root, "parallel", "*.json")))
+    assert len(runs) >= 4 and len(pars) >= 3
+    for p in runs:
+        assert RunConfiguration.from_json_file(p) is not None
+    for p in pars:
+        assert ParallelConfiguration.from_json_file(p) is not None
