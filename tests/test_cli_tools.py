@@ -81,3 +81,24 @@ def test_cli_frame_head_parallel_runs_the_two_stage_pipeline(tmp_path):
     outs = [p.communicate(timeout=300)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), outs
     assert "Step 1 took" in outs[1] and "loss/train" in outs[1]
+
+
+def test_launcher_starts_data_parallel_ranks(tmp_path):
+    """``fbamtrain_b200.launch`` with a ccl data-parallel configuration: two CPU ranks rendezvous and train."""
+    import socket
+    cfg = presets.tiny()
+    cfg["micro_batch_size"], cfg["total_batch_size"] = 1, 2
+    run = tmp_path / "run.json"
+    run.write_text(json.dumps(cfg))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ep = {"ip": "127.0.0.1", "port": port}
+    par = {"frame_head_parallel": {"use_frame_head_parallel": False, "transport": "ccl", "ccl_rendezvous": ep},
+           "ddp_parallel": {"use_ddp_parallel": True, "transport": "ccl", "ccl_rendezvous": ep}}
+    parallel = tmp_path / "parallel.json"
+    parallel.write_text(json.dumps(par))
+    r = _run(["fbamtrain_b200.launch", "--nproc", "2", "--", "-c", str(run), "--parallel-config", str(parallel),
+              "--synthetic", "--steps", "2", "--device", "cpu", "-v"])
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "[rank 0]" in r.stdout and "[rank 1]" in r.stdout and "Step 1 took" in r.stdout
