@@ -11,7 +11,10 @@
 //                           gradient), fused with the momentum update and the Frobenius-norm partial sum.
 //  * fbam_push_shard      — copy a range of a local buffer into every peer's buffer and raise a per-source
 //                           ready flag (all-gather whose consumers wait per shard, e.g. the flag-gated GEMM).
+//  * fbam_reduce_slots    — owner-side half of GEMM -> reduce-scatter: waits for all peers' partial tiles (stored
+//                           into per-source slots by the GEMM epilogue or by peer copies) and sums the slots.
 //  * fbam_peer_barrier    — stand-alone cross-GPU barrier on the flag words.
+//  * fbam_ipc_*           — peer windows over CUDA IPC handles, for groups whose member processes change.
 //
 // Synchronisation is by epoch-tagged flag words in peer memory: a rank publishes epoch e by storing e into
 // its slot of every peer's flag array (st.release.sys after a system-scope fence) and waits until all slots

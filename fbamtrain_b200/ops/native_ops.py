@@ -49,9 +49,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
 
     ``ready_flags`` (int32 tensor in local memory, written by peers) gates the loads of A (or B with
     ``flag_on_b``): rows ``[i·flag_rows, (i+1)·flag_rows)`` are read only once ``ready_flags[i] >= flag_epoch``
-    (all-gather → GEMM).  ``rs_out`` (list of peer fp32 buffer addresses) with ``rs_rows_per_rank`` makes the
-    epilogue add the tile into the buffer of the rank owning each output row (GEMM → reduce-scatter); ``out``
-    is then only used for its shape and pitch."""
+    (all-gather → GEMM).  ``rs_out`` (list of peer buffer addresses) with ``rs_rows_per_rank`` sends each tile to
+    the rank owning its output rows (GEMM → reduce-scatter): with ``rs_slot = s`` as bf16 stores into slot ``s`` of
+    the owner's ``[slot][rows][n]`` buffer (the owner sums the slots afterwards), with ``rs_slot = -1`` as fp32
+    remote additions into the owner's ``[rows][n]`` buffer; ``out`` is then only used for its shape and pitch.
+    ``two_cta`` selects the CTA-pair kernel (default: automatically for large problems)."""
     _need_bf16(a, b)
     if a.stride(-1) != 1 or b.stride(-1) != 1:
         raise ValueError("GEMM operands need unit inner stride")
