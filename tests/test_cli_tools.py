@@ -102,3 +102,13 @@ def test_launcher_starts_data_parallel_ranks(tmp_path):
               "--synthetic", "--steps", "2", "--device", "cpu", "-v"])
     assert r.returncode == 0, r.stdout + r.stderr
     assert "[rank 0]" in r.stdout and "[rank 1]" in r.stdout and "Step 1 took" in r.stdout
+
+
+def test_validate_numerics_flow_on_cpu(tmp_path):
+    """Both arms are the PyTorch definitions on a CPU, so the dumps must be identical: checks the plumbing of the
+    end-to-end comparison (step, dump, native tenscmp)."""
+    from fbamtrain_b200 import validate_numerics
+    bad = validate_numerics.run(steps=2, threshold=0.3, preset="tiny", device=torch.device("cpu"),
+                                out_dir=str(tmp_path))
+    assert bad == 0
+    assert any(name.endswith(".safetensors") for name in os.listdir(tmp_path))
