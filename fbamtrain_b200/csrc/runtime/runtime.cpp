@@ -346,8 +346,33 @@ void* fbam_tok_load(const char* path) {
     return nullptr;
   }
 }
+// A tokenizer over the given UTF-8 tokens, ids = positions in the list (no sorting: the caller's order stands).
+void* fbam_tok_from_list(const char* const* tokens_utf8, int64_t n) {
+  try {
+    auto tok = std::make_unique<Tokenizer>();
+    for (int64_t i = 0; i < n; ++i) {
+      std::string s(tokens_utf8[i]);
+      tok->tokens.push_back(fbam::utf8_to_u32(s));
+      tok->tokens_utf8.push_back(std::move(s));
+    }
+    tok->build();
+    return tok.release();
+  } catch (const std::exception& ex) {
+    set_error(ex.what());
+    return nullptr;
+  }
+}
 void fbam_tok_free(void* h) { delete static_cast<Tokenizer*>(h); }
 int64_t fbam_tok_size(void* h) { return static_cast<int64_t>(static_cast<Tokenizer*>(h)->tokens.size()); }
+// Length in code points of the longest token.
+int64_t fbam_tok_max_len(void* h) {
+  const Tokenizer* tok = static_cast<Tokenizer*>(h);
+  size_t longest = 0;
+  for (const auto& t : tok->tokens) longest = std::max(longest, t.size());
+  return static_cast<int64_t>(longest);
+}
+// Error text for other translation units of the runtime library.
+void fbam_rt_set_error(const char* text) { set_error(text); }
 int64_t fbam_tok_token(void* h, int64_t idx, char* buf, int64_t cap) {
   const auto& s = static_cast<Tokenizer*>(h)->tokens_utf8.at(static_cast<size_t>(idx));
   if (static_cast<int64_t>(s.size()) <= cap) memcpy(buf, s.data(), s.size());

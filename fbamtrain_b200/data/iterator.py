@@ -16,7 +16,7 @@ from __future__ import annotations
 import os
 import threading
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from typing import Callable, List, Optional, Sequence
 
 from ..rng import SplitMix64
 from .recording import Recording, open_recording, recording_extensions
@@ -33,15 +33,24 @@ class DatasetIteratorState:
 
 @dataclass
 class Batch:
-    """One batch: per item, the recording and the frame index where its sequence starts."""
+    """One batch: per item, the recording and the frame index where its sequence starts; ``tensors`` holds what
+    the iterator's assembler produced for it on the prefetch thread (None without an assembler)."""
     recordings: List[Recording]
     indices: List[int]
     start_positions: List[int]
+    tensors: Optional[object] = None
 
 
 class RecordingDatasetIterator:
     def __init__(self, recordings_folder_path: Optional[str], batch_size: int, sequence_length: int, seed: int,
-                 recordings: Optional[Sequence[Recording]] = None):
+                 recordings: Optional[Sequence[Recording]] = None,
+                 assembler: Optional[Callable[[List[int], List[int], int], object]] = None):
+        """``assembler(indices, start_positions, buffer_index)`` — optional; called on the prefetch thread for every
+        prepared batch (outside the iterator's lock), its result travels with the batch.  ``buffer_index``
+        alternates between 0 and 1 so the assembler can fill two (pinned) buffers in turn: the one handed out with
+        batch k stays untouched until batch k + 2 is prepared."""
+        self._assembler = assembler
+        self._prepared_tensors = None
         self.batch_size, self.sequence_length, self.seed = int(batch_size), int(sequence_length), int(seed)
         if recordings is not None:
             self._recordings: List[Optional[Recording]] = list(recordings)
@@ -90,15 +99,22 @@ class RecordingDatasetIterator:
         return indices, starts
 
     def _worker_loop(self) -> None:
-        with self._mutex:
-            while True:
+        while True:
+            with self._mutex:
                 self._cv_request.wait_for(lambda: self._stop or self._requested)
                 if self._stop:
                     return
                 self._requested = False
                 buf = self._buffer_index
-                self._prepared_indices, self._prepared_starts = self._draw()
-                self._prepared_rng_state = self._rng.state
+                indices, starts = self._draw()          # only this thread touches the RNG while it runs
+                rng_state = self._rng.state
+            tensors = self._assembler(indices, starts, buf) if self._assembler is not None else None
+            with self._mutex:
+                if self._stop:
+                    return
+                self._prepared_indices, self._prepared_starts = indices, starts
+                self._prepared_rng_state = rng_state
+                self._prepared_tensors = tensors
                 self._ready = True
                 self._buffer_index = 1 - buf
                 self._cv_ready.notify_all()
@@ -129,11 +145,15 @@ class RecordingDatasetIterator:
             if not self._ready:
                 raise RuntimeError("Dataset iterator was stopped.")
             indices, starts = list(self._prepared_indices), list(self._prepared_starts)
+            tensors, self._prepared_tensors = self._prepared_tensors, None
+            buf = 1 - self._buffer_index               # the buffer the prepared batch was (or would be) written to
             self._cursor_rng_state = self._prepared_rng_state
             self._ready = False
             self._requested = True
             self._cv_request.notify_all()
-        return Batch([self._recordings[i] for i in indices], indices, starts)
+        if tensors is None and self._assembler is not None:   # a batch restored from a checkpoint: assemble it now
+            tensors = self._assembler(indices, starts, buf)
+        return Batch([self._recordings[i] for i in indices], indices, starts, tensors)
 
     def cursor_checkpoint(self) -> DatasetIteratorState:
         return DatasetIteratorState(rng_state=self._cursor_rng_state, batch_size=self.batch_size,
@@ -170,6 +190,7 @@ class RecordingDatasetIterator:
             self._prepared_indices = list(state.prepared_indices)
             self._prepared_starts = list(state.prepared_start_positions)
             self._prepared_rng_state = state.rng_state
+            self._prepared_tensors = None
             self._cursor_rng_state = state.rng_state
             self._rng.state = state.rng_state
         self._start_worker()

@@ -6,6 +6,8 @@ interface; decoders are registered per file extension, and two implementations s
 
 * :class:`ArrayRecording` — frames held in a NumPy array, loadable from ``.npz`` (extension
   ``.fbrec.npz``), used by tests and small experiments;
+* :class:`RawRecording` — the uncompressed, memory-mapped ``.fbrec`` form that the native batch loader
+  (``csrc/runtime/loader.cpp``) gathers from with worker threads;
 * :class:`SyntheticRecording` — the seeded generator that the benchmark configurations specify:
   the first frame is uniform random, every later frame copies its predecessor and resamples a
   fixed fraction of the cells.
@@ -95,7 +97,62 @@ class SyntheticRecording(Recording):
         return self._cells[index], self._user[index]
 
 
-_DECODERS: Dict[str, Callable[[str], Recording]] = {".fbrec.npz": ArrayRecording.load}
+RAW_MAGIC = b"FBAMREC1"
+RAW_HEADER_BYTES = 64
+
+
+def write_raw_recording(path: str, cells: np.ndarray, user_data: List[str]) -> None:
+    """Writes the uncompressed, memory-mappable ``.fbrec`` form that the native batch loader gathers from:
+    64-byte header (magic, rows, cols, frames, offset of the keystroke section), the ``uint32`` cell states, then
+    ``frames + 1`` byte offsets into the UTF-8 keystroke blob that follows them."""
+    cells = np.ascontiguousarray(cells, dtype=np.uint32)
+    if cells.ndim != 4 or cells.shape[-1] != 3 or len(user_data) != cells.shape[0]:
+        raise ValueError("cells must be (frames, rows, cols, 3) with one keystroke string per frame")
+    frames, rows, cols = int(cells.shape[0]), int(cells.shape[1]), int(cells.shape[2])
+    blobs = [u.encode("utf-8") for u in user_data]
+    offsets = np.zeros(frames + 1, dtype=np.uint64)
+    offsets[1:] = np.cumsum([len(b) for b in blobs], dtype=np.uint64)
+    keys_offset = RAW_HEADER_BYTES + cells.nbytes
+    header = RAW_MAGIC + np.array([rows, cols], dtype="<u4").tobytes() + \
+        np.array([frames, keys_offset], dtype="<u8").tobytes()
+    header += b"\0" * (RAW_HEADER_BYTES - len(header))
+    tmp = path + ".tmp"
+    with open(tmp, "wb") as f:
+        f.write(header)
+        f.write(cells.tobytes())
+        f.write(offsets.astype("<u8").tobytes())
+        f.write(b"".join(blobs))
+    os.replace(tmp, path)
+
+
+class RawRecording(Recording):
+    """A ``.fbrec`` file, memory-mapped (see :func:`write_raw_recording`)."""
+
+    def __init__(self, path: str):
+        self.path = path
+        with open(path, "rb") as f:
+            head = f.read(RAW_HEADER_BYTES)
+        if len(head) < RAW_HEADER_BYTES or head[:8] != RAW_MAGIC:
+            raise ValueError(f"{path} is not a raw recording")
+        self.rows, self.cols = (int(v) for v in np.frombuffer(head, dtype="<u4", count=2, offset=8))
+        frames, keys_offset = (int(v) for v in np.frombuffer(head, dtype="<u8", count=2, offset=16))
+        self._frames = frames
+        self._cells = np.memmap(path, dtype="<u4", mode="r", offset=RAW_HEADER_BYTES,
+                                shape=(frames, self.rows, self.cols, 3))
+        self._offsets = np.memmap(path, dtype="<u8", mode="r", offset=keys_offset, shape=(frames + 1,))
+        self._blob_base = keys_offset + (frames + 1) * 8
+        self._blob = np.memmap(path, dtype=np.uint8, mode="r", offset=self._blob_base) \
+            if int(self._offsets[-1]) > 0 else np.zeros(0, dtype=np.uint8)
+
+    def total_frames(self) -> int:
+        return self._frames
+
+    def frame(self, index: int) -> Tuple[np.ndarray, str]:
+        lo, hi = int(self._offsets[index]), int(self._offsets[index + 1])
+        return self._cells[index], bytes(self._blob[lo:hi]).decode("utf-8")
+
+
+_DECODERS: Dict[str, Callable[[str], Recording]] = {".fbrec.npz": ArrayRecording.load, ".fbrec": RawRecording}
 
 
 def register_decoder(extension: str, factory: Callable[[str], Recording]) -> None:

@@ -36,6 +36,19 @@ def lib() -> C.CDLL:
             build.build_runtime()
         L = C.CDLL(LIB_PATH)
         L.fbam_rt_last_error.restype = C.c_char_p
+        L.fbam_tok_from_list.restype = C.c_void_p
+        L.fbam_tok_from_list.argtypes = [C.c_void_p, C.c_int64]
+        L.fbam_tok_free.argtypes = [C.c_void_p]
+        L.fbam_tok_max_len.restype = C.c_int64
+        L.fbam_tok_max_len.argtypes = [C.c_void_p]
+        L.fbam_loader_open.restype = C.c_void_p
+        L.fbam_loader_open.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_uint32, C.c_int64, C.c_int]
+        L.fbam_loader_close.argtypes = [C.c_void_p]
+        L.fbam_loader_frames.restype = C.c_int64
+        L.fbam_loader_frames.argtypes = [C.c_void_p, C.c_int64]
+        L.fbam_loader_rows.argtypes = [C.c_void_p]
+        L.fbam_loader_cols.argtypes = [C.c_void_p]
+        L.fbam_loader_fill.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
         L.fbam_master_start.restype = C.c_void_p
         L.fbam_master_start.argtypes = [C.c_char_p, C.c_int, C.c_double, C.POINTER(C.c_int)]
         L.fbam_master_stop.argtypes = [C.c_void_p]
@@ -237,3 +250,52 @@ def rdv_fetch(ip: str, port: int, rank: int, timeout_s: float = 60.0) -> bytes:
     if rc != 0:
         raise RuntimeError_(_err())
     return buf.raw
+
+
+# -- batch loader --------------------------------------------------------------------------------
+class NativeBatchLoader:
+    """Gathers batches from raw ``.fbrec`` recordings with worker threads (``csrc/runtime/loader.cpp``).
+    ``tokens`` is the tokenizer's vocabulary with ids = list positions; ``fill`` writes into caller-provided (pinned) tensors and
+    releases the interpreter lock while it runs, so a prefetch thread really overlaps with the training step."""
+
+    def __init__(self, paths: List[str], tokens: List[str], max_code_point: int, vocab: int, threads: int = 0):
+        if any("\0" in t for t in tokens):
+            raise ValueError("tokens containing NUL cannot be passed to the native loader")
+        tok_arr = (C.c_char_p * len(tokens))(*[t.encode("utf-8") for t in tokens])
+        self._tok_handle = lib().fbam_tok_from_list(tok_arr, len(tokens))
+        if not self._tok_handle:
+            raise ValueError(_err())
+        arr = (C.c_char_p * len(paths))(*[p.encode() for p in paths])
+        threads = threads or min(16, max(1, (os.cpu_count() or 2) // 2))
+        self._h = lib().fbam_loader_open(arr, len(paths), self._tok_handle, max_code_point, vocab, threads)
+        if not self._h:
+            raise ValueError(_err())
+        self.rows, self.cols = int(lib().fbam_loader_rows(self._h)), int(lib().fbam_loader_cols(self._h))
+        self.frames = [int(lib().fbam_loader_frames(self._h, i)) for i in range(len(paths))]
+
+    def fill(self, indices, starts, seq: int, out_cells, out_targets) -> None:
+        """``out_cells`` int32 ``(B, seq, rows*cols, 3)`` and ``out_targets`` int64 ``(B, seq)`` host tensors."""
+        b = len(indices)
+        idx = np.asarray(indices, dtype=np.uint32)
+        st = np.asarray(starts, dtype=np.uint64)
+        if tuple(out_cells.shape) != (b, seq, self.rows * self.cols, 3) or tuple(out_targets.shape) != (b, seq):
+            raise ValueError("output tensors have the wrong shape")
+        if not out_cells.is_contiguous() or not out_targets.is_contiguous():
+            raise ValueError("output tensors must be contiguous")
+        if lib().fbam_loader_fill(self._h, idx.ctypes.data, st.ctypes.data, b, seq, out_cells.data_ptr(),
+                                  out_targets.data_ptr()) != 0:
+            raise ValueError(_err())
+
+    def close(self) -> None:
+        if self._h:
+            lib().fbam_loader_close(self._h)
+            self._h = None
+        if getattr(self, "_tok_handle", None):
+            lib().fbam_tok_free(self._tok_handle)
+            self._tok_handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass

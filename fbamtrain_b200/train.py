@@ -100,6 +100,7 @@ class Trainer:
                 self.groups[scope] = build_groups(scope, named, shard_multiple)
                 self.optimizers[scope] = create_optimizer(ocfg, named, prefix)
         self.step_count = 0
+        self.last_upload_event = None
         if self.dp is not None:
             self.dp.attach(self)
 
@@ -151,6 +152,7 @@ class Trainer:
                 ev = torch.cuda.Event()
                 ev.record()
                 events.append(ev)
+        self.last_upload_event = events[-1] if events else None   # all of this step's host→device copies are done
         return dev_cells.view(b, t, p, 3), dev_targets, events, chunk
 
     def _forward_backward(self, cells: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
@@ -309,6 +311,58 @@ def build_batch_from_recordings(batch, tokenizer: Tokenizer, seq_len: int, rows:
     return torch.from_numpy(cells.view(np.int32)), torch.from_numpy(targets)
 
 
+class _PinnedBatchBuffer:
+    """One of the two host buffers the native loader fills in turn.  ``release(event)`` is called after the step
+    that read it has queued its host→device copies; the next fill waits for that event, because the copies are
+    asynchronous and the host can be several steps ahead of the device."""
+
+    def __init__(self, batch: int, seq: int, cells_per_frame: int, pin: bool):
+        self.cells = torch.empty((batch, seq, cells_per_frame, 3), dtype=torch.int32, pin_memory=pin)
+        self.targets = torch.empty((batch, seq), dtype=torch.int64, pin_memory=pin)
+        self._event = None
+
+    def wait_until_free(self) -> None:
+        event, self._event = self._event, None
+        if event is not None:
+            event.synchronize()
+
+    def release(self, event) -> None:
+        self._event = event
+
+
+def _make_assembler(trainer: Trainer, local_batch: int):
+    """The batch assembler for the dataset iterator's prefetch thread, or None when the per-frame Python path has
+    to be used: the native loader needs raw ``.fbrec`` recordings, a tokenizer and the runtime library."""
+    from . import runtime
+    from .data.recording import recording_extensions
+    cfg = trainer.cfg
+    folder = os.path.join(trainer.working_dir, cfg.train_data_config.recordings_directory_path)
+    if trainer.tokenizer is None or not runtime.available() or not os.path.isdir(folder):
+        return None
+    exts = tuple(recording_extensions())
+    paths = sorted(os.path.join(folder, f) for f in os.listdir(folder)
+                   if f.endswith(exts) and not os.path.isdir(os.path.join(folder, f)))
+    if not paths or not all(p.endswith(".fbrec") for p in paths):
+        return None
+    loader = runtime.NativeBatchLoader(paths, trainer.tokenizer.tokens, cfg.model_config.max_code_point, trainer.vocab)
+    if (loader.rows, loader.cols) != (cfg.frame_rows, cfg.frame_cols):
+        raise RuntimeError(f"Obtained input frame from dataset with size different from configuration: Expected "
+                           f"{cfg.frame_rows}x{cfg.frame_cols} according to configuration, got "
+                           f"{loader.rows}x{loader.cols}")
+    seq = cfg.train_sequence_length
+    buffers = [_PinnedBatchBuffer(local_batch, seq, cfg.frame_rows * cfg.frame_cols, trainer.device.type == "cuda")
+               for _ in range(2)]
+
+    def assemble(indices, starts, buffer_index):
+        buf = buffers[buffer_index]
+        buf.wait_until_free()
+        loader.fill(indices, starts, seq, buf.cells, buf.targets)
+        return buf, buf.cells, buf.targets
+
+    assemble.loader = loader          # keeps the mapping alive as long as the assembler
+    return assemble
+
+
 def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None) -> List[dict]:
     """The outer loop: data → ``train_step`` → cursor commit → validation → checkpoint."""
     cfg = trainer.cfg
@@ -318,7 +372,8 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
         if cfg.train_data_config.recordings_directory_path:
             iterator = RecordingDatasetIterator(
                 os.path.join(trainer.working_dir, cfg.train_data_config.recordings_directory_path), local_batch,
-                cfg.train_sequence_length, cfg.train_data_config.iteration_seed + trainer.rank)
+                cfg.train_sequence_length, cfg.train_data_config.iteration_seed + trainer.rank,
+                assembler=_make_assembler(trainer, local_batch))
         else:
             source = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point,
                                           trainer.vocab, seed=cfg.train_data_config.iteration_seed + trainer.rank)
@@ -339,14 +394,20 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
     mc = cfg.model_config
     while trainer.step_count < limit:
         with gputx_range("fbamtrain::next_batch_wait"):
+            assembled = None
             if iterator is not None:
                 batch = iterator.next_batch()
-                cells, targets = build_batch_from_recordings(batch, trainer.tokenizer, cfg.train_sequence_length,
-                                                             cfg.frame_rows, cfg.frame_cols, trainer.vocab,
-                                                             mc.max_code_point)
+                if batch.tensors is not None:          # gathered by the native loader on the prefetch thread
+                    assembled, cells, targets = batch.tensors
+                else:
+                    cells, targets = build_batch_from_recordings(batch, trainer.tokenizer, cfg.train_sequence_length,
+                                                                 cfg.frame_rows, cfg.frame_cols, trainer.vocab,
+                                                                 mc.max_code_point)
             else:
                 cells, targets = source.next_batch(local_batch, cfg.train_sequence_length)
         trainer.train_step(cells, targets)
+        if assembled is not None:
+            assembled.release(trainer.last_upload_event)
         if trainer.cursor is not None and iterator is not None:
             st = iterator.cursor_checkpoint()
             trainer.cursor.commit(DatasetCursorSnapshot(trainer.step_count, st.rng_state, local_batch,

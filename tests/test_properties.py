@@ -129,3 +129,41 @@ def test_token_stream_consumption_equals_greedy_longest_match_over_frames(tokens
         want.append((tok.tokens.index(best), frame_of[i]))
         i += len(best)
     assert got == want
+
+
+@settings(max_examples=25, deadline=None)
+@given(tokens=st.lists(st.text(alphabet="abcé", min_size=1, max_size=3), min_size=1, max_size=6, unique=True),
+       keys=st.lists(st.text(alphabet="abcdé", max_size=3), min_size=3, max_size=20),
+       seq=st.integers(1, 9), start_frac=st.floats(0, 1), seed=st.integers(0, 1000))
+def test_native_batch_loader_equals_python_assembly(tmp_path_factory, tokens, keys, seq, start_frac, seed):
+    """Raw recordings gathered by the native loader give the same cells and targets as the per-frame Python path
+    (tokens paired with the frame of their first keystroke, code points clamped, exhausted streams zero-padded)."""
+    from fbamtrain_b200.data.iterator import Batch
+    from fbamtrain_b200.data.recording import ArrayRecording, RawRecording, write_raw_recording
+    from fbamtrain_b200.train import build_batch_from_recordings
+    rng = np.random.default_rng(seed)
+    d = tmp_path_factory.mktemp("rec")
+    rows, cols, max_cp, vocab = 2, 3, 50, 5
+    recs, paths = [], []
+    for r in range(2):
+        ks = keys if r == 0 else keys[::-1]
+        cells = rng.integers(0, 80, size=(len(ks), rows, cols, 3), dtype=np.uint32)
+        path = str(d / f"r{r}.fbrec")
+        write_raw_recording(path, cells, ks)
+        raw = RawRecording(path)
+        assert raw.total_frames() == len(ks) and raw.frame(1)[1] == ks[1]
+        assert np.array_equal(raw.frame(len(ks) - 1)[0], cells[-1])
+        recs.append(ArrayRecording(cells, ks))
+        paths.append(path)
+    tok = Tokenizer(tokens)
+    start = int(start_frac * (len(keys) - 1))
+    indices, starts = [0, 1, 0], [start, 0, len(keys) - 1]
+    want_cells, want_targets = build_batch_from_recordings(Batch([recs[i] for i in indices], indices, starts), tok,
+                                                           seq, rows, cols, vocab, max_cp)
+    loader = rt.NativeBatchLoader(paths, tok.tokens, max_cp, vocab, threads=3)
+    got_cells = torch.full((3, seq, rows * cols, 3), -7, dtype=torch.int32)
+    got_targets = torch.full((3, seq), -7, dtype=torch.int64)
+    loader.fill(indices, starts, seq, got_cells, got_targets)
+    loader.close()
+    assert torch.equal(got_targets, want_targets)
+    assert torch.equal(got_cells, want_cells)
