@@ -223,3 +223,67 @@ int fbam_loader_fill(void* h, const uint32_t* indices, const uint64_t* starts, i
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Seeded synthetic batches (the benchmark configurations' data): per sequence, frame 0 draws every cell's code point
+// uniformly from [0, cell_vocab) and an attribute id from [0, attr_ids); every later frame copies its predecessor
+// and redraws `k` distinct cells; colours come from a 16-entry palette (fg = palette[attr % 16], bg =
+// palette[(15 - attr) % 16]); targets are uniform in [0, action_vocab).  Sequences are independent SplitMix64
+// streams keyed by (seed, call, item), so the result does not depend on the number of worker threads.
+// ------------------------------------------------------------------------------------------------
+namespace {
+struct Mix64 {
+  uint64_t s;
+  uint64_t next() {
+    s += 0x9E3779B97F4A7C15ull;
+    uint64_t z = s;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+  }
+  uint32_t below(uint32_t n) { return static_cast<uint32_t>(next() % n); }
+};
+}  // namespace
+
+extern "C" int fbam_synth_fill(uint64_t seed, uint64_t call, int64_t cells_per_frame, int64_t batch, int64_t seq,
+                               uint32_t cell_vocab, uint32_t attr_ids, int64_t k, uint32_t action_vocab,
+                               const uint32_t* palette16, int32_t* out_cells, int64_t* out_targets, int threads) {
+  if (cells_per_frame < 1 || batch < 1 || seq < 1 || cell_vocab < 1 || attr_ids < 1 || action_vocab < 1 || k < 0 ||
+      k > cells_per_frame)
+    return 1;
+  const int workers = static_cast<int>(std::min<int64_t>(std::max(1, threads), batch));
+  auto work = [&](int w) {
+    std::vector<uint32_t> attr(static_cast<size_t>(cells_per_frame)), order(static_cast<size_t>(cells_per_frame));
+    for (int64_t b = w; b < batch; b += workers) {
+      Mix64 rng{seed * 0xD6E8FEB86659FD93ull + call * 0xA0761D6478BD642Full + static_cast<uint64_t>(b) + 1};
+      rng.next();
+      uint32_t* item = reinterpret_cast<uint32_t*>(out_cells) + static_cast<size_t>(b) * seq * cells_per_frame * 3;
+      for (int64_t c = 0; c < cells_per_frame; ++c) {
+        attr[c] = rng.below(attr_ids);
+        order[c] = static_cast<uint32_t>(c);
+        item[c * 3] = rng.below(cell_vocab);
+        item[c * 3 + 1] = palette16[attr[c] % 16];
+        item[c * 3 + 2] = palette16[(15 - attr[c] % 16) % 16];
+      }
+      for (int64_t t = 1; t < seq; ++t) {
+        uint32_t* cur = item + static_cast<size_t>(t) * cells_per_frame * 3;
+        memcpy(cur, cur - cells_per_frame * 3, static_cast<size_t>(cells_per_frame) * 12);
+        for (int64_t j = 0; j < k; ++j) {   // partial Fisher-Yates: k distinct cells
+          const uint32_t pick = static_cast<uint32_t>(j) + rng.below(static_cast<uint32_t>(cells_per_frame - j));
+          std::swap(order[j], order[pick]);
+          const uint32_t c = order[j];
+          attr[c] = rng.below(attr_ids);
+          cur[c * 3] = rng.below(cell_vocab);
+          cur[c * 3 + 1] = palette16[attr[c] % 16];
+          cur[c * 3 + 2] = palette16[(15 - attr[c] % 16) % 16];
+        }
+      }
+      for (int64_t t = 0; t < seq; ++t) out_targets[b * seq + t] = static_cast<int64_t>(rng.below(action_vocab));
+    }
+  };
+  std::vector<std::thread> pool;
+  for (int w = 1; w < workers; ++w) pool.emplace_back(work, w);
+  work(0);
+  for (auto& t : pool) t.join();
+  return 0;
+}

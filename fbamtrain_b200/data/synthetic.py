@@ -10,7 +10,7 @@ upload it with one asynchronous copy.
 """
 from __future__ import annotations
 
-from typing import Tuple
+from typing import Optional, Tuple
 
 import numpy as np
 import torch
@@ -20,7 +20,15 @@ from .palette import ANSI_PALETTE
 
 class SyntheticBatchSource:
     def __init__(self, rows: int, cols: int, cell_vocab: int, action_vocab: int, seed: int = 0,
-                 resample: float = 0.05, attr_ids: int = 16, pin: bool = True):
+                 resample: float = 0.05, attr_ids: int = 16, pin: bool = True, native: Optional[bool] = None):
+        """``native``: generate with the multi-threaded generator of the runtime library (default when it is built;
+        ~50x faster than the NumPy loop, which otherwise takes longer than a training step).  The two generators
+        follow the same recipe with different random streams, so their batches differ; each is reproducible from
+        ``(seed, call number)``."""
+        if native is None:
+            from .. import runtime
+            native = runtime.available()
+        self.native = native
         self.rows, self.cols = rows, cols
         self.cell_vocab, self.action_vocab = cell_vocab, action_vocab
         self.resample, self.attr_ids = resample, attr_ids
@@ -30,6 +38,15 @@ class SyntheticBatchSource:
 
     def next_batch(self, batch: int, seq: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """Returns ``(cells uint32-as-int32 (B, T, P, 3), targets int64 (B, T))`` on the host."""
+        if self.native:
+            from .. import runtime
+            n = self.rows * self.cols
+            cells = torch.empty((batch, seq, n, 3), dtype=torch.int32, pin_memory=self.pin)
+            tg = torch.empty((batch, seq), dtype=torch.int64, pin_memory=self.pin)
+            runtime.synth_fill(self.seed, self._calls, n, self.cell_vocab, self.attr_ids,
+                               max(1, int(round(self.resample * n))), self.action_vocab, ANSI_PALETTE, cells, tg)
+            self._calls += 1
+            return cells, tg
         rng = np.random.default_rng([self.seed, self._calls])
         self._calls += 1
         n = self.rows * self.cols

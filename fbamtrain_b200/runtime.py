@@ -39,6 +39,8 @@ def lib() -> C.CDLL:
         L.fbam_tok_from_list.restype = C.c_void_p
         L.fbam_tok_from_list.argtypes = [C.c_void_p, C.c_int64]
         L.fbam_tok_free.argtypes = [C.c_void_p]
+        L.fbam_synth_fill.argtypes = [C.c_uint64, C.c_uint64, C.c_int64, C.c_int64, C.c_int64, C.c_uint32, C.c_uint32,
+                                      C.c_int64, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
         L.fbam_tok_max_len.restype = C.c_int64
         L.fbam_tok_max_len.argtypes = [C.c_void_p]
         L.fbam_loader_open.restype = C.c_void_p
@@ -299,3 +301,17 @@ class NativeBatchLoader:
             self.close()
         except Exception:  # noqa: BLE001
             pass
+
+
+def synth_fill(seed: int, call: int, cells_per_frame: int, cell_vocab: int, attr_ids: int, k: int, action_vocab: int,
+               palette16, out_cells, out_targets, threads: int = 0) -> None:
+    """Fills ``out_cells`` int32 ``(B, T, P, 3)`` and ``out_targets`` int64 ``(B, T)`` with a seeded synthetic batch
+    (``csrc/runtime/loader.cpp``: ``fbam_synth_fill``)."""
+    b, t = int(out_cells.shape[0]), int(out_cells.shape[1])
+    pal = np.ascontiguousarray(palette16, dtype=np.uint32)
+    if pal.size != 16 or not out_cells.is_contiguous() or not out_targets.is_contiguous():
+        raise ValueError("need a 16-entry palette and contiguous outputs")
+    threads = threads or min(16, max(1, (os.cpu_count() or 2) // 2))
+    if lib().fbam_synth_fill(seed & ((1 << 64) - 1), call, cells_per_frame, b, t, cell_vocab, attr_ids, k, action_vocab,
+                             pal.ctypes.data, out_cells.data_ptr(), out_targets.data_ptr(), threads) != 0:
+        raise ValueError("invalid arguments for the synthetic batch generator")

@@ -162,3 +162,29 @@ def test_native_membership_master_protocol():
             s.close()
     finally:
         master.interrupt()
+
+
+def test_native_synthetic_generator_is_reproducible_and_follows_the_recipe():
+    """The threaded generator: the same ``(seed, call)`` gives the same batch whatever the thread count, about
+    ``resample`` of the cells change between consecutive frames, and every field stays inside its range."""
+    from fbamtrain_b200.data import SyntheticBatchSource
+    from fbamtrain_b200.data.synthetic import ANSI_PALETTE
+    n, k = 8 * 16, 6
+    outs = []
+    for threads in (1, 3):
+        cells = torch.empty((3, 12, n, 3), dtype=torch.int32)
+        tg = torch.empty((3, 12), dtype=torch.int64)
+        rt.synth_fill(5, 2, n, 300, 16, k, 40, ANSI_PALETTE, cells, tg, threads=threads)
+        outs.append((cells, tg))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    cells, tg = outs[0]
+    u = cells.numpy().view(np.uint32)
+    assert u[..., 0].max() < 300 and 0 <= tg.min() and tg.max() < 40
+    assert set(np.unique(u[..., 1])) <= set(np.asarray(ANSI_PALETTE, dtype=np.uint32))
+    changed = (u[:, 1:] != u[:, :-1]).any(-1).sum(-1)           # cells that differ between consecutive frames
+    assert changed.max() <= k and changed.mean() > k / 2
+    src = SyntheticBatchSource(8, 16, 300, 40, seed=5, pin=False, native=True)
+    a0, a1 = src.next_batch(3, 12), src.next_batch(3, 12)
+    assert not torch.equal(a0[0], a1[0])                        # the call number advances the stream
+    again = SyntheticBatchSource(8, 16, 300, 40, seed=5, pin=False, native=True)
+    assert torch.equal(again.next_batch(3, 12)[0], a0[0])
