@@ -527,15 +527,15 @@ def test_expected_backends_are_chosen_on_gpu():
     _nops()
     from fbamtrain_b200 import ops
     from fbamtrain_b200.ops import dispatch
-    x = torch.randn(64, 128, device=DEV).to(BF)
-    w = torch.randn(256, 128, device=DEV).to(BF)
+    x = torch.randn(256, 512, device=DEV).to(BF)
+    w = torch.randn(256, 512, device=DEV).to(BF)
     ops.linear(x, w)
     assert dispatch.last_backend("gemm") == "native"
-    q = torch.randn(1, 128, 2, 64, device=DEV).to(BF)
-    ops.attention(q, q, q, True)
+    q, k, v = (torch.randn(2, 128, 2, 64, device=DEV).to(BF) for _ in range(3))
+    ops.attention(q, k, v, True)
     assert dispatch.last_backend("mha") == "native"
-    img = torch.randn(2, 8, 16, 64, device=DEV).to(BF)
-    wt = torch.randn(64, 3, 3, 64, device=DEV).to(BF)
+    img = torch.randn(3, 12, 40, 128, device=DEV).to(BF)
+    wt = torch.randn(64, 3, 3, 128, device=DEV).to(BF)
     ops.conv2d_nhwc(img, wt, 1, 1, 1)
     assert dispatch.last_backend("conv2d") == "native"
     ops.linear(x.float(), w.float())
