@@ -509,6 +509,13 @@ int fbam_reduce_slots(const void* slots, void* out, long long n_per_slot, int wo
   return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 
+// Device-to-device copy on `stream` by the copy engines (cudaMemcpyAsync); either side may be a peer mapping.
+int fbam_copy_async(void* dst, const void* src, long long bytes, void* stream) {
+  if (bytes < 0 || (bytes > 0 && (dst == nullptr || src == nullptr))) return 1;
+  if (bytes == 0) return 0;
+  return cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice, STREAM(stream)) == cudaSuccess ? 0 : 5;
+}
+
 // ---- peer windows over CUDA IPC -------------------------------------------------------------------------------
 // One dedicated device allocation per window, exported as a 64-byte handle that the other processes of the
 // machine open to obtain a pointer they can load from and store to.  Used where the set of processes changes

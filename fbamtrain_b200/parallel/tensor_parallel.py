@@ -47,7 +47,6 @@ class TpContext:
         if self.rs_mode not in ("epilogue", "chunked"):
             raise ValueError("FBAMTRAIN_TP_RS_MODE must be epilogue or chunked")
         self._copy_stream = None
-        self._peer_views: Dict[Tuple, torch.Tensor] = {}
         self.peers = None
         self._win: Dict[Tuple, object] = {}
         if transport == "fused":
@@ -163,11 +162,10 @@ class TpContext:
             part = no.gemm(block, w)
             done = torch.cuda.Event()
             done.record(main)
-            dst = _peer_view(self, win, owner, self.world * slot_elems)[self.rank * slot_elems:
-                                                                        (self.rank + 1) * slot_elems]
-            with torch.cuda.stream(self._copy_stream):
-                self._copy_stream.wait_event(done)
-                dst.copy_(part.view(-1), non_blocking=True)
+            self._copy_stream.wait_event(done)
+            dst = win.ptrs[owner] + self.rank * slot_elems * 2       # this rank's slot in the owner's buffer
+            nv.check(nv.lib().fbam_copy_async(C.c_void_p(dst), nv.ptr(part), C.c_longlong(slot_elems * 2),
+                                              C.c_void_p(self._copy_stream.cuda_stream)), "fbam_copy_async")
             part.record_stream(self._copy_stream)
         main.wait_stream(self._copy_stream)
         out = torch.empty(rows, n, dtype=torch.bfloat16, device=h.device)
@@ -177,16 +175,6 @@ class TpContext:
                                             C.c_uint(self.spin_limit), nv.ptr(nv.status_word(self.device)),
                                             nv.stream_ptr()), "fbam_reduce_slots")
         return out
-
-
-def _peer_view(ctx: "TpContext", win, owner: int, numel: int) -> torch.Tensor:
-    """A bf16 tensor over rank ``owner``'s buffer of ``win`` as mapped into this process."""
-    from .peer_window import _RawDeviceBytes
-    key = (id(win), owner)
-    if key not in ctx._peer_views:
-        raw = torch.as_tensor(_RawDeviceBytes(win.ptrs[owner], numel * 2), device=ctx.device)
-        ctx._peer_views[key] = raw.view(torch.bfloat16)
-    return ctx._peer_views[key]
 
 
 class _RsShape:
