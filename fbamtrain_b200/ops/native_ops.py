@@ -156,6 +156,8 @@ class _Linear(torch.autograd.Function):
         if act == "gelu" and (x.requires_grad or weight.requires_grad):
             preact = torch.empty((x2.shape[0], weight.shape[0]), dtype=BF16, device=x.device)
         y = gemm(x2, weight, bias=bias, act=act, preact_out=preact)
+        if act == "relu":
+            preact = y        # the output's sign is all the backward needs
         ctx.save_for_backward(x2, weight, preact)
         ctx.act, ctx.has_bias, ctx.in_shape = act, bias is not None, x.shape
         return y.view(*x.shape[:-1], weight.shape[0])
@@ -169,7 +171,7 @@ class _Linear(torch.autograd.Function):
         if ctx.act == "gelu":
             dy2 = _gelu_bwd(preact, dy2)
         elif ctx.act == "relu":
-            raise NotImplementedError("relu backward is not wired on the native path")
+            dy2 = dy2 * (preact > 0)
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
             dx = gemm_nn(dy2, weight).view(ctx.in_shape)
