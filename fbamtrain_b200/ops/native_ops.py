@@ -14,6 +14,7 @@ import torch
 
 from ..utils import debug, flops
 from . import native as nv
+from . import tuning
 
 BF16 = torch.bfloat16
 # Large problems run on CTA pairs (tcgen05 cta_group::2: two SMs share every B fetch and keep double-buffered
@@ -61,6 +62,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     n, kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
     if k != kb:
         raise ValueError(f"inner dimensions differ: {k} vs {kb}")
+    if bm == 0 and bn == 0 and max_ctas == 0 and two_cta is None and ready_flags is None and rs_out is None:
+        tuned = tuning.lookup(tuning.gemm_key(m, n, k, a_mn, b_mn), {"m": m, "n": n, "k": k, "a_mn": a_mn, "b_mn": b_mn})
+        if tuned is not None:
+            bm, bn, max_ctas = tuned.get("bm", 0), tuned.get("bn", 0), tuned.get("max_ctas", 0)
+            two_cta = tuned.get("two_cta")
     if out is None:
         out = debug.fresh((m, n), out_dtype, a.device)
     if out.shape != (m, n) or out.stride(1) != 1:
@@ -213,6 +219,13 @@ def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor
     """One implicit-GEMM pass (see ``ConvGeom`` in csrc/gemm_tcgen05.h).  ``x`` NHWC bf16, ``wmat``
     ``(n_out, taps·C)`` bf16, ``out`` NHWC with ``n_out`` channels."""
     b, ih, iw, c = x.shape
+    if bn == 0 and tile_rows == 0 and two_cta is None:
+        tuned = tuning.lookup(tuning.conv_key(b, grid_hw[0], grid_hw[1], c, n_out, len(taps), in_mul, out_mul),
+                              {"batch": b, "in_h": ih, "in_w": iw, "c": c, "n_out": n_out, "grid_hw": list(grid_hw),
+                               "in_mul": in_mul, "out_mul": out_mul, "taps": [list(t) for t in taps],
+                               "out_off": list(out_off), "out_hw": [out.shape[1], out.shape[2]]})
+        if tuned is not None:
+            bn, tile_rows, two_cta = tuned.get("bn", 0), tuned.get("tile_rows", 0), tuned.get("two_cta")
     p = nv.GemmParams()
     g = p.conv
     g.batch, g.grid_h, g.grid_w = b, grid_hw[0], grid_hw[1]

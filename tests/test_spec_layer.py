@@ -218,3 +218,43 @@ def test_backend_preference_environment(monkeypatch):
     monkeypatch.delenv("FBAMTRAIN_PREFER_GEMM_BACKEND")
     monkeypatch.delenv("FBAMTRAIN_PREFER_MHA_BACKEND")
     dispatch._read_preferences()
+
+
+def test_tuning_table_parse_lookup_and_recording(tmp_path, monkeypatch):
+    import json
+    from fbamtrain_b200.ops import tuning
+    key = tuning.gemm_key(8192, 4096, 1024, False, True)
+    assert key == "gemm m8192 n4096 k1024 NT"
+    ckey = tuning.conv_key(1024, 24, 80, 128, 256, 9, 2, 1)
+    doc = {"device": "x", "entries": {key: {"best": {"bm": 256, "bn": 128, "two_cta": False}, "ms": 0.1},
+                                      ckey: {"best": {"tile_rows": 128, "two_cta": False}, "ms": 0.2}}}
+    path = tmp_path / "tuning.json"
+    path.write_text(json.dumps(doc))
+    assert tuning.lookup(key) is None                                  # no table configured
+    monkeypatch.setenv("FBAMTRAIN_TUNING_FILE", str(path))
+    assert tuning.lookup(key) == {"bm": 256, "bn": 128, "two_cta": False}
+    assert tuning.lookup(ckey) == {"tile_rows": 128, "two_cta": False}
+    assert tuning.lookup("gemm m1 n1 k1 NN") is None
+    with tuning.recording() as seen:
+        tuning.lookup(key, {"m": 8192})
+        tuning.lookup(key, {"m": 1})                                   # first sighting wins
+        tuning.lookup("gemm m2 n2 k2 NN", {"m": 2})
+    assert seen == {key: {"m": 8192}, "gemm m2 n2 k2 NN": {"m": 2}}
+    monkeypatch.delenv("FBAMTRAIN_TUNING_FILE")
+    assert tuning.lookup(key) is None
+    tuning.set_table({key: {"bm": 128}})
+    try:
+        assert tuning.lookup(key) == {"bm": 128}
+    finally:
+        tuning.set_table(None)
+    for bad in ({"entries": {key: {"best": {"bm": 100}}}}, {"entries": {key: {"best": {"tile_rows": 128}}}},
+                {"entries": {key: {"best": {"two_cta": 1}}}}, {"entries": {"lstm x": {"best": {}}}}, {"entries": {key: {}}},
+                {}):
+        with pytest.raises(ValueError):
+            tuning.parse(bad)
+    cands = tuning.gemm_candidates(8192, 4096)
+    assert {"bm": 256, "bn": 256, "two_cta": True} in cands and {"bm": 128, "bn": 128, "two_cta": False} in cands
+    assert all(not c["two_cta"] for c in tuning.gemm_candidates(8192, 64))
+    assert all(c.get("bn", 0) <= 128 for c in tuning.conv_candidates(64))
+    for c in cands + tuning.conv_candidates(512):
+        tuning._validate(key if "bm" in c else ckey, c)                 # every candidate is a legal table entry
