@@ -13,6 +13,8 @@ from typing import Optional
 
 import torch
 
+from ..utils import plan as _plan
+
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libfbam_kernels.so")
 _lib: Optional[C.CDLL] = None
@@ -92,6 +94,9 @@ def check(code: int, what: str) -> None:
                       f"{_lib.fbam_pending_runtime_error()}")
         raise RuntimeError(f"{what}: {_ERRORS.get(code, 'error')} (code {code}){detail}")
     _launches += 1
+    recording = _plan.active()
+    if recording is not None:
+        recording.on_launch(what)
 
 
 def stream_ptr() -> C.c_void_p:

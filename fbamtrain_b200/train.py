@@ -28,7 +28,7 @@ from .data import (DatasetCursorCommitter, DatasetCursorSnapshot, RecordingDatas
 from .models import FbamModel
 from .optim import AdamwOptimizer, MuonWithAuxAdam, Optimizer, create_optimizer
 from .tokenizer import Tokenizer
-from .utils import flops
+from .utils import flops, plan
 from .utils.flat import FlatGroup, build_groups
 from .utils.logging import LOG
 from .utils.metrics import AsyncStepLogger, LossRingBuffer, StepRecord
@@ -178,6 +178,18 @@ class Trainer:
         return loss.detach()
 
     def train_step(self, cells: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """One optimizer step (see :meth:`_train_step`).  With ``FBAMTRAIN_DUMP_PLAN=<file>`` the first step is
+        recorded as a launch plan (``utils/plan.py``) and its listing written to the file."""
+        path = os.environ.get("FBAMTRAIN_DUMP_PLAN", "")
+        if not path or self.step_count != 0 or self.rank != 0 or plan.active() is not None:
+            return self._train_step(cells, targets)
+        with plan.record() as recorded:
+            loss = self._train_step(cells, targets)
+        with open(path, "w") as f:
+            f.write(recorded.listing())
+        return loss
+
+    def _train_step(self, cells: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """One optimizer step.  ``cells`` int32 ``(B_local, T, P, 3)`` and ``targets`` int64 ``(B_local, T)``
         hold this rank's share of the batch (``grad_accum_steps`` micro-batches).  Returns the step
         loss as a device scalar (this rank's share of the global mean)."""

@@ -13,6 +13,8 @@ import threading
 from contextlib import contextmanager
 from typing import Tuple
 
+from . import plan
+
 _lock = threading.Lock()       # backward runs on autograd worker threads
 _total = 0.0
 _useful = 0.0
@@ -21,10 +23,14 @@ _local = threading.local()
 
 def add(flops: float) -> None:
     global _total, _useful
+    useful = not getattr(_local, "depth", 0)
     with _lock:
         _total += flops
-        if not getattr(_local, "depth", 0):
+        if useful:
             _useful += flops
+    recording = plan.active()
+    if recording is not None:
+        recording.on_flops(flops, useful)
 
 
 @contextmanager

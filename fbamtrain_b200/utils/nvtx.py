@@ -13,6 +13,8 @@ import os
 
 import torch
 
+from . import plan
+
 _ENABLED = os.environ.get("FBAMTRAIN_NVTX", "1") != "0"
 
 
@@ -21,8 +23,13 @@ def gputx_range(name: str):
     active = _ENABLED and torch.cuda.is_available()
     if active:
         torch.cuda.nvtx.range_push(name)
+    recording = plan.active() is not None
+    if recording:
+        plan.push_phase(name)
     try:
         yield
     finally:
+        if recording:
+            plan.pop_phase()
         if active:
             torch.cuda.nvtx.range_pop()

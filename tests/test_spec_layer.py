@@ -258,3 +258,39 @@ def test_tuning_table_parse_lookup_and_recording(tmp_path, monkeypatch):
     assert all(c.get("bn", 0) <= 128 for c in tuning.conv_candidates(64))
     for c in cands + tuning.conv_candidates(512):
         tuning._validate(key if "bm" in c else ckey, c)                 # every candidate is a legal table entry
+
+
+def test_step_plan_records_launches_phases_and_flops():
+    import threading
+    from fbamtrain_b200.ops import native as nv
+    from fbamtrain_b200.utils import flops, plan
+    from fbamtrain_b200.utils.nvtx import gputx_range
+    nv.check(0, "fbam_before")                                         # outside a recording: no effect
+    with plan.record() as p:
+        with gputx_range("fbamtrain::frame_head_fwd"):
+            nv.check(0, "fbam_gemm_bf16")
+            flops.add(2e9)
+            with flops.not_useful():
+                nv.check(0, "fbam_conv_bf16")
+                flops.add(1e9)
+
+        def backward_thread():
+            nv.check(0, "fbam_gemm_bf16")
+            flops.add(4e9)
+        t = threading.Thread(target=backward_thread)
+        t.start()
+        t.join()
+        nv.check(0, "fbam_adamw")
+        with pytest.raises(RuntimeError):
+            with plan.record():
+                pass
+    assert plan.active() is None
+    assert [(e.name, e.phase, e.backward, e.flops, e.useful_flops) for e in p.entries] == [
+        ("fbam_gemm_bf16", "fbamtrain::frame_head_fwd", False, 2e9, 2e9),
+        ("fbam_conv_bf16", "fbamtrain::frame_head_fwd", False, 1e9, 0.0),
+        ("fbam_gemm_bf16", "", True, 4e9, 4e9),
+        ("fbam_adamw", "", False, 0.0, 0.0)]
+    assert p.total_flops() == 7e9 and p.total_useful_flops() == 6e9
+    assert p.by("name")["fbam_gemm_bf16"] == (2, 6e9)
+    text = p.listing()
+    assert text.startswith("# 4 launches") and "(recompute)" in text and "fbamtrain::frame_head_fwd" in text
