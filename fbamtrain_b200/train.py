@@ -115,6 +115,9 @@ class Trainer:
             self.streams = stream_bundle(self.device)
             self.h2d_stream = self.streams.h2d
         self._staging: Dict[Tuple, torch.Tensor] = {}
+        self._loss_events: List[Tuple[int, object]] = [(-1, None)] * 64
+        self._upload_slot, self._slot_in_use, self._fresh_buffer = 0, 0, False
+        self._slot_free: List[Optional[torch.cuda.Event]] = [None, None]
 
     # ------------------------------------------------------------------------------------------
     def all_groups(self) -> List[FlatGroup]:
@@ -130,6 +133,7 @@ class Trainer:
         if buf is None or tuple(buf.shape) != tuple(shape) or buf.dtype != dtype:
             buf = torch.empty(shape, dtype=dtype, device=self.device)
             self._staging[key] = buf
+            self._fresh_buffer = True
         return buf
 
     def _upload(self, cells: torch.Tensor, targets: torch.Tensor):
@@ -139,11 +143,22 @@ class Trainer:
         b, t, p, _ = cells.shape
         frames = b * t
         chunk = self.frame_chunk or frames
-        dev_cells = self._device_buffer(("cells",), (frames, p, 3), cells.dtype)
-        dev_targets = self._device_buffer(("targets",), tuple(targets.shape), targets.dtype)
+        # Two device buffers in turn: the copies for this micro-batch only wait until the micro-batch before the
+        # previous one has finished its backward (the last reader of the buffer), so a caller that queues step
+        # k + 1 while step k computes gets its upload overlapped with that compute.
+        slot = self._upload_slot
+        self._upload_slot = 1 - slot
+        self._fresh_buffer = False
+        dev_cells = self._device_buffer(("cells", slot), (frames, p, 3), cells.dtype)
+        dev_targets = self._device_buffer(("targets", slot), tuple(targets.shape), targets.dtype)
         flat = cells.reshape(frames, p, 3)
         events = []
-        self.h2d_stream.wait_stream(torch.cuda.current_stream())
+        if self._fresh_buffer or self._slot_free[slot] is None:
+            # new memory from the caching allocator: order the copies behind everything queued on the compute stream
+            self.h2d_stream.wait_stream(torch.cuda.current_stream())
+        else:
+            self.h2d_stream.wait_event(self._slot_free[slot])
+        self._slot_in_use = slot
         with torch.cuda.stream(self.h2d_stream):
             dev_targets.copy_(targets, non_blocking=True)
             for lo in range(0, frames, chunk):
@@ -175,6 +190,10 @@ class Trainer:
                 loss = self.model.action_model(emb, dev_targets, loss_scale)
         with gputx_range("fbamtrain::backward"):
             loss.backward()
+        if events is not None:          # the backward was the last reader of this micro-batch's device buffers
+            done = torch.cuda.Event()
+            done.record()
+            self._slot_free[self._slot_in_use] = done
         return loss.detach()
 
     def train_step(self, cells: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
@@ -222,6 +241,7 @@ class Trainer:
             with gputx_range("fbamtrain::frame_head_optim_step"):
                 self.optimizers["frame_head"].step()
         loss_ev = self.ring.finalize(step)
+        self._loss_events[step % len(self._loss_events)] = (step, loss_ev)
         if self._cuda:
             end_ev = torch.cuda.Event(enable_timing=True)
             end_ev.record()
@@ -238,6 +258,17 @@ class Trainer:
             LOG("INFO", "allocator: peak {:.2f} GiB, current {:.2f} GiB, cached {:.2f} GiB, reserved {:.2f} GiB".format(
                 *(m[k] / 2 ** 30 for k in ("peak_bytes", "current_bytes", "cached_bytes", "reserved_bytes"))))
         return total
+
+    def host_loss(self, step: int) -> float:
+        """The loss of step ``step`` (this rank's share) as a host float.  Waits only for that step's own
+        device→host copy — 4 bytes on the side stream, queued when the step was — and not for steps launched after
+        it, so a loop can launch step k + 1 and then read the loss of step k without draining the device."""
+        kept_step, event = self._loss_events[step % len(self._loss_events)]
+        if kept_step != step:
+            raise ValueError(f"the loss of step {step} is no longer kept (latest {self.step_count - 1})")
+        if event is not None:
+            event.synchronize()
+        return self.ring.read(step)
 
     # ------------------------------------------------------------------------------------------
     @torch.no_grad()

@@ -414,3 +414,27 @@ def test_training_on_raw_recordings_uses_native_loader_and_matches_python_path(t
     assert len(curves["raw"]) == 5
     assert curves["raw"] == pytest.approx(curves["npz"], abs=1e-6)
     assert curves["raw"][2] == pytest.approx(curves["raw"][3], abs=1e-6)   # step 2 replayed identically after resume
+
+
+def test_host_loss_returns_each_steps_loss_without_the_returned_tensor():
+    """``Trainer.host_loss(step)`` reads the step's slot of the loss ring: same value as the returned scalar, also
+    when it is read one step late, and an error once the slot has been reused."""
+    from fbamtrain_b200 import RunConfiguration, Trainer, presets
+    from fbamtrain_b200.data import SyntheticBatchSource
+    cfg = RunConfiguration.from_json(presets.tiny())
+    tr = Trainer(cfg, device=torch.device("cpu"))
+    src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point, tr.vocab, seed=3,
+                               pin=False)
+    returned, read_late = [], []
+    previous = None
+    for _ in range(3):
+        step = tr.step_count
+        returned.append(float(tr.train_step(*src.next_batch(2, cfg.train_sequence_length))))
+        if previous is not None:
+            read_late.append(tr.host_loss(previous))
+        previous = step
+    read_late.append(tr.host_loss(previous))
+    assert read_late == pytest.approx(returned, rel=1e-6)
+    with pytest.raises(ValueError):
+        tr.host_loss(99)
+    tr.close()
