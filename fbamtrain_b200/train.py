@@ -30,8 +30,8 @@ from .optim import AdamwOptimizer, MuonWithAuxAdam, Optimizer, create_optimizer
 from .tokenizer import Tokenizer
 from .utils import flops, plan
 from .utils.flat import FlatGroup, build_groups
-from .utils.logging import LOG
-from .utils.metrics import AsyncStepLogger, LossRingBuffer, StepRecord
+from .utils.logging import LOG, enabled as log_enabled
+from .utils.metrics import AsyncStepLogger, LossRingBuffer, ProgressRecord, StepRecord
 from .utils.nvtx import gputx_range
 
 
@@ -170,14 +170,26 @@ class Trainer:
         self.last_upload_event = events[-1] if events else None   # all of this step's host→device copies are done
         return dev_cells.view(b, t, p, 3), dev_targets, events, chunk
 
+    def _mark(self):
+        """A point in time on the compute stream: a timing event on a GPU, wall-clock seconds on the CPU."""
+        if not self._cuda:
+            return time.perf_counter()
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        return ev
+
     def _forward_backward(self, cells: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         loss_scale = 1.0 / (cells.shape[1] * cfg.total_batch_size)
         dev_cells, dev_targets, events, chunk = self._upload(cells, targets)
         b, t, p, _ = dev_cells.shape
+        progress = log_enabled("INFO")          # per-chunk progress lines cost two events per chunk: only when shown
+        phase0 = self._mark() if progress else None
         with gputx_range("fbamtrain::forward"):
             if events is None:
                 emb = self.model.frame_embeddings(dev_cells)
+                if progress:
+                    self.logger.progress(ProgressRecord("Frame head: frames", b * t, b * t, phase0, self._mark()))
             else:
                 flat = dev_cells.view(b * t, p, 3)
                 parts = []
@@ -185,11 +197,17 @@ class Trainer:
                     for i, lo in enumerate(range(0, b * t, chunk)):
                         torch.cuda.current_stream().wait_event(events[i])
                         parts.append(self.model.frame_head_chunk(flat[lo:lo + chunk]))
+                        if progress:
+                            self.logger.progress(ProgressRecord("Frame head: frames", min(b * t, lo + chunk), b * t,
+                                                                phase0, self._mark()))
                 emb = (parts[0] if len(parts) == 1 else torch.cat(parts, 0)).view(b, t, -1)
             with gputx_range("fbamtrain::action_model_fwd_bwd"):
                 loss = self.model.action_model(emb, dev_targets, loss_scale)
+        phase1 = self._mark() if progress else None
         with gputx_range("fbamtrain::backward"):
             loss.backward()
+        if progress:
+            self.logger.progress(ProgressRecord("Backward: frames", b * t, b * t, phase1, self._mark()))
         if events is not None:          # the backward was the last reader of this micro-batch's device buffers
             done = torch.cuda.Event()
             done.record()

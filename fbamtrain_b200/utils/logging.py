@@ -21,6 +21,11 @@ def _threshold() -> int:
     return _LEVELS.get(raw, _LEVELS["ERR"])
 
 
+def enabled(level: str) -> bool:
+    """Whether a message of this level would be printed."""
+    return _LEVELS.get(level.upper(), _LEVELS["ERR"]) >= _threshold()
+
+
 def LOG(level: str, message: str) -> None:
     level = level.upper()
     rank = _LEVELS.get(level, _LEVELS["ERR"])

@@ -77,6 +77,17 @@ class StepRecord:
     total_flops: float = 0.0
 
 
+@dataclass
+class ProgressRecord:
+    """``done`` of ``total`` frames of a phase have been processed once ``event`` completes; the rate is measured
+    from ``phase_start`` (GPU events, or wall-clock seconds on CPU)."""
+    label: str                 # "Sequence position" (forward) or "Backward sequence position"
+    done: int
+    total: int
+    phase_start: object
+    event: object
+
+
 class AsyncStepLogger:
     def __init__(self, ring: LossRingBuffer, sink: Optional[Callable[[dict], None]] = None):
         self.ring = ring
@@ -90,6 +101,20 @@ class AsyncStepLogger:
     def submit(self, rec: StepRecord) -> None:
         self._q.put(rec)
 
+    def progress(self, rec: ProgressRecord) -> None:
+        """Queues a line ``<label> done/total processed | FPS: x`` (reference: ``src/async_step_logger.cpp:115-170``;
+        FPS = frames processed / time since the phase began)."""
+        self._q.put(rec)
+
+    def _progress_line(self, rec: ProgressRecord) -> None:
+        if isinstance(rec.event, float):
+            seconds = rec.event - rec.phase_start
+        else:
+            rec.event.synchronize()
+            seconds = rec.phase_start.elapsed_time(rec.event) / 1e3
+        fps = rec.done / seconds if seconds > 0 else float("inf")
+        LOG("INFO", f"{rec.label} {rec.done}/{rec.total} processed | FPS: {fps:.1f}")
+
     def log_validation(self, step: int, loss: float) -> None:
         LOG("INFO", f"Step {step} validation loss = {loss:.6f}")
         if self.json_lines:
@@ -101,6 +126,12 @@ class AsyncStepLogger:
             rec = self._q.get()
             if rec is None:
                 return
+            if isinstance(rec, ProgressRecord):
+                try:
+                    self._progress_line(rec)
+                finally:
+                    self._q.task_done()
+                continue
             try:
                 if rec.end_event is not None:
                     rec.end_event.synchronize()

@@ -438,3 +438,21 @@ def test_host_loss_returns_each_steps_loss_without_the_returned_tensor():
     with pytest.raises(ValueError):
         tr.host_loss(99)
     tr.close()
+
+
+def test_progress_lines_at_info_level(monkeypatch, capsys):
+    from fbamtrain_b200 import RunConfiguration, Trainer, presets
+    from fbamtrain_b200.data import SyntheticBatchSource
+    monkeypatch.setenv("FBAMTRAIN_LOG_LEVEL", "INFO")
+    cfg = RunConfiguration.from_json(presets.tiny())
+    tr = Trainer(cfg, device=torch.device("cpu"))
+    src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point, tr.vocab, seed=3,
+                               pin=False)
+    tr.train_step(*src.next_batch(2, cfg.train_sequence_length))
+    tr.logger.drain()
+    tr.close()
+    out = capsys.readouterr().out
+    frames = 2 * cfg.train_sequence_length
+    assert f"Frame head: frames {frames}/{frames} processed | FPS:" in out
+    assert f"Backward: frames {frames}/{frames} processed | FPS:" in out
+    assert "Step 0 took" in out
