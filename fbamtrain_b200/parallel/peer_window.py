@@ -45,7 +45,23 @@ class PeerWindow:
         return _ptr_array([p + byte_offset for p in self.ptrs])
 
 
-class PeerGroup:
+class _EpochCounter:
+    """The flag-epoch bookkeeping shared by the window groups (``group``, ``device`` and ``epoch`` are the
+    subclass's attributes)."""
+
+    def _agree_on_epoch(self) -> None:
+        """Every member continues from the highest epoch any member has used: the flag words of a new window start
+        at zero, a long-running member's counter does not, and a wait compares the two."""
+        t = torch.tensor([self.epoch], dtype=torch.int64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        self.epoch = int(t.item())
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+
+class PeerGroup(_EpochCounter):
     def __init__(self, group: Optional[dist.ProcessGroup], device: torch.device, use_multicast: bool = False):
         self.group = group
         self.device = device
@@ -81,17 +97,6 @@ class PeerGroup:
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
 
-    def _agree_on_epoch(self) -> None:
-        """Every member continues from the highest epoch any member has used: the flag words of a new window start
-        at zero, a long-running member's counter does not, and a wait compares the two."""
-        t = torch.tensor([self.epoch], dtype=torch.int64, device=self.device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
-        self.epoch = int(t.item())
-
-    def next_epoch(self) -> int:
-        self.epoch += 1
-        return self.epoch
-
     def rebuild(self, group: Optional[dist.ProcessGroup]) -> None:
         """Drops every window and re-creates the flag words for a new group; callers re-allocate their
         buffers (and re-point parameter / gradient views) afterwards.  The epoch counter is kept."""
@@ -109,7 +114,7 @@ class _RawDeviceBytes:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (address, False), "version": 2}
 
 
-class IpcPeerGroup:
+class IpcPeerGroup(_EpochCounter):
     """Same interface as :class:`PeerGroup`, with windows shared through CUDA IPC handles that the ranks exchange
     over the process group.  Nothing here depends on how long a process has been running, so a freshly started
     process can build windows together with long-running ones — which the fault-tolerant data-parallel mode needs
@@ -167,17 +172,6 @@ class IpcPeerGroup:
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
         self._free_retired()
-
-    def _agree_on_epoch(self) -> None:
-        """Every member continues from the highest epoch any member has used: the flag words of a new window start
-        at zero, a long-running member's counter does not, and a wait compares the two."""
-        t = torch.tensor([self.epoch], dtype=torch.int64, device=self.device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
-        self.epoch = int(t.item())
-
-    def next_epoch(self) -> int:
-        self.epoch += 1
-        return self.epoch
 
     def _free_retired(self) -> None:
         """Frees the windows of the group before the previous one: every process that had them open has closed them
