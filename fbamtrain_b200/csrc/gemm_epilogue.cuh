@@ -24,6 +24,15 @@ __device__ __forceinline__ float gelu_grad_f(float x) {
   return 0.5f * (1.0f + er) + x * 0.3989422804014327f * e;
 }
 
+__device__ __forceinline__ uint4 shfl_xor_u4(const uint4& x, int lane_mask) {
+  uint4 y;
+  y.x = __shfl_xor_sync(0xffffffffu, x.x, lane_mask);
+  y.y = __shfl_xor_sync(0xffffffffu, x.y, lane_mask);
+  y.z = __shfl_xor_sync(0xffffffffu, x.z, lane_mask);
+  y.w = __shfl_xor_sync(0xffffffffu, x.w, lane_mask);
+  return y;
+}
+
 // r: 32 fp32 accumulator values of output row `roff / ldd`, columns [n0, n0 + 32).
 __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff, int n0, const uint32_t (&r)[32]) {
           float v[32];
@@ -105,7 +114,35 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.rs_out[owner]) +
                                  ((long long)(p.rs_slot_plus1 - 1) * p.rs_rows_per_rank + (m - owner * p.rs_rows_per_rank)) *
                                      p.ldd + n0;
-            if (full_vec) {
+            if (full_vec && p.rs_row_stores != 0 && (p.M & 31) == 0 && (p.rs_rows_per_rank & 31) == 0) {
+              // Every lane of the warp is here (rows of a warp are 32 consecutive ones and M is a multiple of 32),
+              // and the four rows of a lane quad belong to the same owner.  4 x 4 transpose of the 16-byte pieces
+              // inside each quad: afterwards lane j of the quad holds piece j of the quad's rows 0..3.
+              uint4 piece[4];
+  #pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                __align__(16) __nv_bfloat162 h[4];
+  #pragma unroll
+                for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]);
+                piece[q] = *reinterpret_cast<uint4*>(h);
+              }
+              const int j = (int)(threadIdx.x & 3);
+  #pragma unroll
+              for (int k = 0; k < 4; k += 2) {        // exchange with the neighbouring lane
+                const uint4 send = (j & 1) ? piece[k] : piece[k + 1];
+                const uint4 got = shfl_xor_u4(send, 1);
+                if (j & 1) piece[k] = got; else piece[k + 1] = got;
+              }
+  #pragma unroll
+              for (int b = 0; b < 2; ++b) {           // exchange with the lane two further
+                const uint4 send = (j & 2) ? piece[b] : piece[2 + b];
+                const uint4 got = shfl_xor_u4(send, 2);
+                if (j & 2) piece[b] = got; else piece[2 + b] = got;
+              }
+  #pragma unroll
+              for (int q = 0; q < 4; ++q)             // row (own row - j + q), columns [n0 + 8j, n0 + 8j + 8)
+                *reinterpret_cast<uint4*>(out + (long long)(q - j) * p.ldd + 8 * j) = piece[q];
+            } else if (full_vec) {
   #pragma unroll
               for (int j = 0; j < 32; j += 8) {
                 __align__(16) __nv_bfloat162 h[4];

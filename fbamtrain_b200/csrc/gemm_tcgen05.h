@@ -61,6 +61,10 @@ struct GemmParams {
   // (one slot per source rank); the owner sums the slots afterwards.  Plain stores run at link bandwidth, remote
   // reductions do not.
   int rs_slot_plus1;
+  // rs_row_stores != 0 (slot form only): the four lanes that hold four neighbouring rows exchange their 16-byte
+  // pieces first, so that one store instruction writes 64 contiguous bytes of a row (two full sectors per
+  // NVLink write) instead of 16 bytes of each of 32 rows.  Needs M and rs_rows_per_rank to be multiples of 32.
+  int rs_row_stores;
   // filled by the launcher
   int mode, M, N, K, tiles_m, k_blocks, a_mn_major, b_mn_major, vec_ok;
   ConvGeom conv;

@@ -41,7 +41,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          bn: int = 0, bm: int = 0, max_ctas: int = 0, ready_flags: Optional[torch.Tensor] = None,
          flag_rows: int = 0, flag_on_b: bool = False, flag_epoch: int = 0, flag_spin_limit: int = 0,
          rs_out=None, rs_rows_per_rank: int = 0, tile_m_rotate: int = 0, two_cta=None,
-         rs_slot: int = -1) -> torch.Tensor:
+         rs_slot: int = -1, rs_row_stores: bool = False) -> torch.Tensor:
     """``D[M, N] = epilogue(A · Bᵀ)``.
 
     ``a``: ``(M, K)`` (or ``(K, M)`` when ``a_mn``); ``b``: ``(N, K)`` (or ``(K, N)`` when ``b_mn``).
@@ -54,6 +54,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     the rank owning its output rows (GEMM → reduce-scatter): with ``rs_slot = s`` as bf16 stores into slot ``s`` of
     the owner's ``[slot][rows][n]`` buffer (the owner sums the slots afterwards), with ``rs_slot = -1`` as fp32
     remote additions into the owner's ``[rows][n]`` buffer; ``out`` is then only used for its shape and pitch.
+    ``rs_row_stores`` (slot form): lanes exchange pieces so that each store instruction writes 64 contiguous bytes
+    of a row instead of 16 bytes of 32 rows (needs ``M`` and ``rs_rows_per_rank`` in multiples of 32).
     ``two_cta`` selects the CTA-pair kernel (default: automatically for large problems)."""
     _need_bf16(a, b)
     if a.stride(-1) != 1 or b.stride(-1) != 1:
@@ -101,6 +103,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
             p.rs_out[i] = ptr_
         p.rs_rows_per_rank = rs_rows_per_rank
         p.rs_slot_plus1 = rs_slot + 1
+        p.rs_row_stores = int(rs_row_stores)
     pair = TWO_CTA if two_cta is None else two_cta
     if pair == "auto":
         pair = (n >= 256 and n % 16 == 0 and bm != 128 and

@@ -46,6 +46,8 @@ class TpContext:
         self.rs_mode = os.environ.get("FBAMTRAIN_TP_RS_MODE", "epilogue")
         if self.rs_mode not in ("epilogue", "chunked"):
             raise ValueError("FBAMTRAIN_TP_RS_MODE must be epilogue or chunked")
+        # opt-in: 64-byte row pieces per store instruction in the reduce-scatter epilogue (see native_ops.gemm)
+        self.rs_row_stores = os.environ.get("FBAMTRAIN_TP_RS_ROW_STORES", "0") == "1"
         self._copy_stream = None
         self.peers = None
         self._win: Dict[Tuple, object] = {}
@@ -132,7 +134,8 @@ class TpContext:
         first = ((self.rank + 1) % self.world) * rows
         rotate = first // tile_rows if rows % tile_rows == 0 else 0
         no.gemm(h, w, out=_RsShape((m, n), torch.bfloat16, n, win.local.data_ptr()), rs_out=list(win.ptrs),
-                rs_rows_per_rank=rows, rs_slot=self.rank, tile_m_rotate=rotate, two_cta=pair, bm=tile_rows)
+                rs_rows_per_rank=rows, rs_slot=self.rank, tile_m_rotate=rotate, two_cta=pair, bm=tile_rows,
+                rs_row_stores=self.rs_row_stores)
         out = torch.empty(rows, n, dtype=torch.bfloat16, device=h.device)
         epoch = self.peers.next_epoch()
         nv.check(nv.lib().fbam_reduce_slots(nv.ptr(win.local), nv.ptr(out), C.c_longlong(rows * n), self.world,

@@ -229,3 +229,32 @@ def test_flag_gated_gemm_and_reduce_scatter_epilogue_single_gpu():
         nv.check_status(torch.device(DEV))
         got = torch.cat(outs, 0).float()
         assert float((got - expect).norm() / expect.norm()) < 1e-2
+
+
+@pytest.mark.parametrize("pair", [False, True])
+def test_reduce_scatter_row_stores_single_gpu(pair):
+    """The opt-in store pattern of the slot epilogue (lane quads exchange pieces, 64 contiguous bytes per row and
+    instruction) must write exactly what the default pattern writes; every 'peer' buffer is on this device."""
+    if os.environ.get("FBAMTRAIN_TEST_OPT_IN_PATHS") != "1":
+        pytest.skip("opt-in path; set FBAMTRAIN_TEST_OPT_IN_PATHS=1 to test it")
+    from fbamtrain_b200.ops import native_ops as no
+    from fbamtrain_b200.parallel.tensor_parallel import _RsShape
+    nv = _nv()
+    torch.manual_seed(5)
+    m, n, k, world = 1024, 512, 192, 4
+    rows = m // world
+    a = torch.randn(m, k, device=DEV).to(BF)
+    b = torch.randn(n, k, device=DEV).to(BF)
+    results = []
+    for row_stores in (False, True):
+        slots = [torch.zeros(3, rows, n, device=DEV, dtype=BF) for _ in range(world)]
+        shape = _RsShape((m, n), BF, n, slots[0].data_ptr())
+        no.gemm(a, b, out=shape, rs_out=[o.data_ptr() for o in slots], rs_rows_per_rank=rows, rs_slot=1,
+                tile_m_rotate=1, two_cta=pair, bm=256 if pair else 128, rs_row_stores=row_stores)
+        nv.check_status(torch.device(DEV))
+        results.append(torch.stack(slots, 0))
+    assert torch.equal(results[0], results[1])
+    expect = (a.float() @ b.float().t()).view(world, rows, n)
+    got = results[1][:, 1].float()
+    assert float((got - expect).norm() / expect.norm()) < 1e-2
+    assert float(results[1][:, 0].abs().max()) == 0.0 and float(results[1][:, 2].abs().max()) == 0.0
