@@ -95,11 +95,31 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
                                                      cfg.tokenizer_file_path)))
     fused_tp = device.type == "cuda" and per // 2 > 1        # peer-memory kernels need at least two TP ranks
     trainer = PipelineTrainer(cfg, device, vocab, tp_transport="fused" if fused_tp else "nccl", replicas=replicas)
-    src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point, vocab,
-                               seed=cfg.train_data_config.iteration_seed, pin=device.type == "cuda")
+    working_dir = os.path.dirname(os.path.abspath(args.config))
+    rec_dir = cfg.train_data_config.recordings_directory_path
+    if rec_dir and not args.synthetic:
+        # Every rank draws the same batches (same seed): frame-head ranks use the frames, action-model ranks the
+        # targets of the sequences of their pipeline.
+        from .data import RecordingDatasetIterator
+        from .tokenizer import Tokenizer
+        from .train import build_batch_from_recordings
+        tokenizer = Tokenizer.from_file(os.path.join(working_dir, cfg.tokenizer_file_path))
+        iterator = RecordingDatasetIterator(os.path.join(working_dir, rec_dir), cfg.total_batch_size,
+                                            cfg.train_sequence_length, cfg.train_data_config.iteration_seed)
+
+        def next_batch():
+            return build_batch_from_recordings(iterator.next_batch(), tokenizer, cfg.train_sequence_length,
+                                               cfg.frame_rows, cfg.frame_cols, vocab, cfg.model_config.max_code_point)
+    else:
+        iterator = None
+        src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point, vocab,
+                                   seed=cfg.train_data_config.iteration_seed, pin=device.type == "cuda")
+
+        def next_batch():
+            return src.next_batch(cfg.total_batch_size, cfg.train_sequence_length)
     steps = args.steps if args.steps is not None else cfg.max_training_steps
     for step in range(steps):
-        cells, targets = src.next_batch(cfg.total_batch_size, cfg.train_sequence_length)
+        cells, targets = next_batch()
         t0 = time.perf_counter()
         loss = trainer.train_step(cells.to(device), targets.to(device))
         if rank == layout.action_ranks[0]:                 # the first pipeline's recurrence master reports
@@ -109,6 +129,8 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
                 sys.stdout.write(json.dumps({"step": step, "step_time_sec": time.perf_counter() - t0,
                                              "loss/train": loss}) + "\n")
                 sys.stdout.flush()
+    if iterator is not None:
+        iterator.close()
     dist.destroy_process_group()
     return 0
 
@@ -147,9 +169,6 @@ def main(argv=None) -> int:
 
     fhp = par.frame_head_parallel if par is not None else None
     if fhp is not None and fhp.use_frame_head_parallel:
-        if not args.synthetic and cfg.train_data_config.recordings_directory_path:
-            LOG("WARN", "the pipeline mode trains on seeded synthetic frames (recordings are read in the "
-                        "data-parallel mode)")
         return _run_pipeline(cfg, par, args, device)
 
     dp = None

@@ -112,3 +112,44 @@ def test_validate_numerics_flow_on_cpu(tmp_path):
                                 out_dir=str(tmp_path))
     assert bad == 0
     assert any(name.endswith(".safetensors") for name in os.listdir(tmp_path))
+
+
+def test_cli_pipeline_reads_recordings(tmp_path):
+    """The two-stage pipeline launched on a recordings folder: every rank draws the same seeded batches; the
+    frame-head rank uses the frames, the action-model rank the tokenised keystrokes."""
+    import socket
+    import numpy as np
+    from fbamtrain_b200.data import ArrayRecording, SyntheticRecording
+    from fbamtrain_b200.tokenizer import Tokenizer
+    rec_dir = tmp_path / "rec"
+    rec_dir.mkdir()
+    for i in range(2):
+        r = SyntheticRecording(8, 16, 50, seed=i)
+        cells = np.stack([r.frame(t)[0] for t in range(50)])
+        ArrayRecording(cells, [r.frame(t)[1] for t in range(50)]).save(str(rec_dir / f"r{i}.fbrec.npz"))
+    Tokenizer(list("abcdefghijklmnopqrstuvwxyz") + ["ab", "th"]).save(str(tmp_path / "tok.txt"))
+    cfg = presets.tiny()
+    cfg["model_config"].update({"action_heads": 2, "lstm_layers": 1, "action_vocab": 0})
+    cfg["micro_batch_size"], cfg["total_batch_size"] = 2, 4
+    cfg["tokenizer_file_path"] = "tok.txt"
+    cfg["train_data_config"]["recordings_directory_path"] = "rec"
+    run = tmp_path / "run.json"
+    run.write_text(json.dumps(cfg))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    par = {"frame_head_parallel": {"use_frame_head_parallel": True, "transport": "ccl",
+                                   "ccl_rendezvous": {"ip": "127.0.0.1", "port": port}},
+           "ddp_parallel": {"use_ddp_parallel": False}}
+    parallel = tmp_path / "parallel.json"
+    parallel.write_text(json.dumps(par))
+    env = dict(os.environ, PYTHONPATH=ROOT, FBAMTRAIN_LOG_LEVEL="INFO")
+    base = [sys.executable, "-m", "fbamtrain_b200.cli", "-c", str(run), "--parallel-config", str(parallel),
+            "--steps", "2", "--device", "cpu", "--world-size", "2"]
+    procs = [subprocess.Popen(base + ["--worker_id", "0"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                              env=env),
+             subprocess.Popen(base + ["--worker_id", "1", "--master"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                              text=True, env=env)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    assert "Step 1 took" in outs[1] and "loss/train" in outs[1]
