@@ -117,8 +117,24 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
 
         def next_batch():
             return src.next_batch(cfg.total_batch_size, cfg.train_sequence_length)
-    steps = args.steps if args.steps is not None else cfg.max_training_steps
-    for step in range(steps):
+    from .checkpoint import CheckpointManager
+    manager = CheckpointManager(os.path.join(working_dir, cfg.checkpointing.checkpoint_directory),
+                                cfg.max_training_steps)
+    if cfg.checkpointing.resume_behavior == "load_latest":
+        latest = manager.find_latest()
+        if latest is not None:
+            restored = trainer.load_checkpoint(manager, latest[1])
+            LOG("INFO", f"Resumed from {latest[1]} at step {trainer.step_count}")
+            if iterator is not None and restored is not None and restored.prepared_indices:
+                restored.batch_size = cfg.total_batch_size
+                iterator.restore(restored)
+            elif iterator is None:
+                src.seek(trainer.step_count)
+    limit = cfg.max_training_steps if args.steps is None else min(cfg.max_training_steps,
+                                                                  trainer.step_count + args.steps)
+    interval = cfg.checkpointing.checkpoint_interval
+    while trainer.step_count < limit:
+        step = trainer.step_count
         cells, targets = next_batch()
         t0 = time.perf_counter()
         loss = trainer.train_step(cells.to(device), targets.to(device))
@@ -129,6 +145,8 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
                 sys.stdout.write(json.dumps({"step": step, "step_time_sec": time.perf_counter() - t0,
                                              "loss/train": loss}) + "\n")
                 sys.stdout.flush()
+        if interval > 0 and trainer.step_count % interval == 0:
+            trainer.save_checkpoint(manager, iterator.checkpoint() if iterator is not None else None)
     if iterator is not None:
         iterator.close()
     dist.destroy_process_group()

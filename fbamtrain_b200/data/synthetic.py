@@ -36,6 +36,11 @@ class SyntheticBatchSource:
         self.pin = pin and torch.cuda.is_available()
         self._calls = 0
 
+    def seek(self, call: int) -> None:
+        """The next batch will be the one of call number ``call`` (batches are a function of seed and call number),
+        e.g. the step count after resuming from a checkpoint."""
+        self._calls = int(call)
+
     def next_batch(self, batch: int, seq: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """Returns ``(cells uint32-as-int32 (B, T, P, 3), targets int64 (B, T))`` on the host."""
         if self.native:

@@ -302,6 +302,66 @@ class PipelineTrainer:
         self.loss_scale = 1.0 / (self.seq * cfg.total_batch_size)
         self.step_count = 0
 
+    # -- checkpoints ---------------------------------------------------------------------------------------
+    # One model file in the single-process layout (every mode can load it) written by global rank 0, plus one
+    # optimizer-state file per position of a pipeline (the optimizers hold stage-local, TP-sharded tensors).
+    def _optimizer_path(self, model_path: str) -> str:
+        pos = dist.get_rank() % self.per_replica
+        return model_path.replace(".safetensors", f".optim.pos{pos}.safetensors")
+
+    @torch.no_grad()
+    def gather_model(self) -> None:
+        """Makes ``self.model`` hold the complete, current model on every rank.  Collective over all ranks."""
+        layout = self.pipe.layout
+        if not self.pipe.is_frame:
+            for blk, full in zip(self.pipe.action.blocks, self.model.action_model.block):
+                blk.gather_into(full)
+        first_frame, first_action = layout.frame_ranks[0], layout.action_ranks[0]
+        if self.replicas > 1:            # replicas hold identical parameters: everyone takes replica 0's
+            first_frame, first_action = first_frame % self.per_replica, first_action % self.per_replica
+        for p in self.model.frame_head.parameters():
+            dist.broadcast(p.data, src=first_frame)
+        for p in self.model.action_model.parameters():
+            dist.broadcast(p.data, src=first_action)
+
+    def save_checkpoint(self, manager, dataset_state=None) -> str:
+        """Collective.  Returns the model file's path."""
+        from ..utils import safetensors_io as st
+        self.gather_model()
+        path = manager.path_for(self.step_count)
+        if dist.get_rank() == 0:
+            manager.save(self.step_count, self.model, {}, dataset_state)
+        if self.replica == 0:
+            import os
+            os.makedirs(manager.directory, exist_ok=True)
+            st.save_file({k: v.detach().cpu() for k, v in self.optimizer.state_tensors().items()},
+                         self._optimizer_path(path))
+        dist.barrier()
+        return path
+
+    def load_checkpoint(self, manager, path: str):
+        """Every rank reads the model file and takes its stage's (shards of the) parameters; optimizer state comes
+        from this position's file when there is one (otherwise moments start from zero and the fp32 masters from
+        the loaded parameters).  Returns the dataset state stored with the model."""
+        import os
+        from ..utils import safetensors_io as st
+        step, dataset_state = manager.load(path, self.model, {})
+        if not self.pipe.is_frame:
+            for blk, full in zip(self.pipe.action.blocks, self.model.action_model.block):
+                blk.load_from(full)
+        opt_path = self._optimizer_path(path)
+        if os.path.exists(opt_path):
+            tensors = {k: v.to(self.device) for k, v in st.load_file(opt_path).items()}
+            self.optimizer.load_state_tensors(tensors)
+        else:
+            for name, p in self.named:
+                master = self.optimizer.state.get(name, {}).get("master")
+                if master is not None:
+                    master.copy_(p.data.float())
+        self.optimizer.set_step(step)
+        self.step_count = step
+        return dataset_state
+
     def train_step(self, cells: torch.Tensor, targets: torch.Tensor) -> float:
         """``cells`` ``(total_batch, T, P, 3)`` and ``targets`` ``(total_batch, T)`` (the same on every rank).
         Returns the step loss (identical on every rank)."""

@@ -328,6 +328,57 @@ class TensorParallelBlock(nn.Module):
         self.ln2_weight = nn.Parameter(block.ln2.weight.detach().clone())
         self.eps = block.ln1.eps
 
+    # name -> (tensor of the unsharded block, how it is cut): "qkv" = per-head rows of the fused projection,
+    # "rows" / "cols" = a contiguous range of rows / columns, None = replicated
+    def _layout(self, block: AttentionBlock):
+        attn, mlp = block.attn, block.mlp
+        return [("w_qkv", attn.qkv.weight, "qkv"), ("b_qkv", attn.qkv.bias, "qkv"),
+                ("w_proj", attn.proj.weight, "cols"), ("b_proj", attn.proj.bias, None),
+                ("w_fc1", mlp.fc1.weight, "rows"), ("b_fc1", mlp.fc1.bias, "rows"),
+                ("w_fc2", mlp.fc2.weight, "cols"), ("b_fc2", mlp.fc2.bias, None),
+                ("ln1_weight", block.ln1.weight, None), ("ln2_weight", block.ln2.weight, None)]
+
+    @torch.no_grad()
+    def gather_into(self, block: AttentionBlock) -> None:
+        """Writes the full parameters into the unsharded ``block`` (inverse of the constructor's slicing).
+        Collective over the TP group."""
+        w, hl, d = self.tp.world, self.heads_local, self.head_dim
+        for name, full, cut in self._layout(block):
+            mine = getattr(self, name)
+            if mine is None or full is None:
+                continue
+            if cut is None:
+                full.data.copy_(mine.data)
+                continue
+            parts = [torch.empty_like(mine.data) for _ in range(w)]
+            dist.all_gather(parts, mine.data.contiguous(), group=self.tp.group)
+            if cut == "qkv":      # rank r holds (3, hl, d, ...) of the (3, heads, d, ...) tensor
+                tail = mine.shape[1:]
+                merged = torch.cat([q.view(3, hl, d, *tail) for q in parts], dim=1)
+                full.data.copy_(merged.reshape(full.shape))
+            else:
+                full.data.copy_(torch.cat(parts, dim=0 if cut == "rows" else 1))
+
+    @torch.no_grad()
+    def load_from(self, block: AttentionBlock) -> None:
+        """Takes this rank's shards from the unsharded ``block`` again (after a checkpoint was loaded into it)."""
+        r, w, hl, d = self.tp.rank, self.tp.world, self.heads_local, self.head_dim
+        for name, full, cut in self._layout(block):
+            mine = getattr(self, name)
+            if mine is None or full is None:
+                continue
+            src = full.data
+            if cut == "qkv":
+                tail = src.shape[1:]
+                src = src.view(3, w * hl, d, *tail)[:, r * hl:(r + 1) * hl].reshape(mine.shape)
+            elif cut == "rows":
+                n = mine.shape[0]
+                src = src[r * n:(r + 1) * n]
+            elif cut == "cols":
+                n = mine.shape[1]
+                src = src[:, r * n:(r + 1) * n]
+            mine.data.copy_(src)
+
     def replicated_parameters(self):
         """Parameters every TP rank holds in full; their gradients are partial sums over row shards and must be
         all-reduced over the TP group after backward (:func:`sync_replicated_grads`)."""

@@ -157,3 +157,57 @@ def test_grouped_action_stage_matches_ungrouped():
             assert p.exitcode == 0
         curves[group] = results[0]
     assert curves[2] == pytest.approx(curves[1], abs=2e-5)
+
+
+def _checkpoint_worker(rank, world, port, q, directory):
+    """Trains 3 steps, saves, trains 2 more; then a fresh trainer loads the checkpoint and repeats those 2 steps.
+    Also loads the model file into a plain single-process model (the file is in the single-process layout)."""
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from fbamtrain_b200 import RunConfiguration, presets
+    from fbamtrain_b200.checkpoint import CheckpointManager, load_model_params
+    from fbamtrain_b200.data import SyntheticBatchSource
+    from fbamtrain_b200.models import FbamModel
+    from fbamtrain_b200.parallel.pipeline import PipelineTrainer
+    from fbamtrain_b200.utils import safetensors_io as st
+    d = presets.tiny()
+    d["model_config"].update({"action_heads": 2, "lstm_layers": 1})
+    d["micro_batch_size"], d["total_batch_size"] = 2, 4
+    d["optimizer"]["learning_rate"] = 3e-3
+    cfg = RunConfiguration.from_json(d)
+    manager = CheckpointManager(directory, cfg.max_training_steps)
+    src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=5, pin=False)
+    batches = [src.next_batch(4, cfg.train_sequence_length) for _ in range(5)]
+    tr = PipelineTrainer(cfg, torch.device("cpu"), vocab=32)
+    for k in range(3):
+        tr.train_step(*batches[k])
+    path = tr.save_checkpoint(manager)
+    first = [tr.train_step(*batches[k]) for k in (3, 4)]
+    tr2 = PipelineTrainer(cfg, torch.device("cpu"), vocab=32)
+    tr2.load_checkpoint(manager, path)
+    assert tr2.step_count == 3
+    again = [tr2.train_step(*batches[k]) for k in (3, 4)]
+    plain = FbamModel(cfg.model_config, 32)
+    load_model_params(plain, st.load_file(path))            # strict names, dtypes and shapes
+    q.put((rank, first, again, sorted(os.listdir(directory))))
+    dist.destroy_process_group()
+
+
+def test_pipeline_checkpoint_resume_repeats_the_same_steps(tmp_path):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    directory = str(tmp_path / "ck")
+    procs = [ctx.Process(target=_checkpoint_worker, args=(r, 4, port, q, directory)) for r in range(4)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in range(4)]
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    for _, first, again, files in results:
+        assert again == pytest.approx(first, rel=1e-6, abs=1e-7)
+    files = results[0][3]
+    assert any(f.endswith(".safetensors") and ".optim." not in f for f in files)
+    assert sum(".optim.pos" in f for f in files) == 4           # one optimizer file per position of the pipeline
