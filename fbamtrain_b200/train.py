@@ -424,6 +424,33 @@ def _make_assembler(trainer: Trainer, local_batch: int):
     return assemble
 
 
+def _validation_source(trainer: Trainer):
+    """A callable returning one validation batch per call: sequences drawn from the validation recordings with
+    their own seeded iterator when the configuration names a folder (the reference runs a second dataset iterator
+    for validation, ``src/main.cpp:2169-2175``), else seeded synthetic frames — the same batch every time, so the
+    curve is comparable across steps."""
+    cfg = trainer.cfg
+    mc = cfg.model_config
+    vcfg = cfg.validation_data_config
+    folder = os.path.join(trainer.working_dir, vcfg.recordings_directory_path) if vcfg.recordings_directory_path else ""
+    if folder and os.path.isdir(folder) and trainer.tokenizer is not None:
+        iterator = RecordingDatasetIterator(folder, cfg.micro_batch_size, cfg.validation_sequence_length,
+                                            vcfg.iteration_seed)
+
+        def from_recordings():
+            return build_batch_from_recordings(iterator.next_batch(), trainer.tokenizer,
+                                               cfg.validation_sequence_length, cfg.frame_rows, cfg.frame_cols,
+                                               trainer.vocab, mc.max_code_point)
+        from_recordings.iterator = iterator
+        return from_recordings
+
+    def synthetic():
+        src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, mc.max_code_point, trainer.vocab,
+                                   seed=vcfg.iteration_seed, pin=False)
+        return src.next_batch(cfg.micro_batch_size, cfg.validation_sequence_length)
+    return synthetic
+
+
 def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None) -> List[dict]:
     """The outer loop: data → ``train_step`` → cursor commit → validation → checkpoint."""
     cfg = trainer.cfg
@@ -438,6 +465,7 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
         else:
             source = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point,
                                           trainer.vocab, seed=cfg.train_data_config.iteration_seed + trainer.rank)
+    validation = None
     restored = trainer.load_latest_checkpoint()
     if iterator is not None and restored is not None and restored.batch_size:
         iterator.restore(restored)
@@ -475,13 +503,15 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
                                                         cfg.train_sequence_length))
         if cfg.enable_validation and cfg.validation_interval and trainer.step_count % cfg.validation_interval == 0:
             with gputx_range("fbamtrain::validation"):
-                vsrc = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, mc.max_code_point, trainer.vocab,
-                                            seed=cfg.validation_data_config.iteration_seed, pin=False)
-                vc, vt = vsrc.next_batch(cfg.micro_batch_size, cfg.validation_sequence_length)
+                if validation is None:
+                    validation = _validation_source(trainer)
+                vc, vt = validation()
                 trainer.logger.log_validation(trainer.step_count, trainer.validation_loss(vc, vt))
         if trainer.step_count % cfg.checkpointing.checkpoint_interval == 0 and trainer.rank == 0:
             trainer.save_checkpoint(iterator.checkpoint() if iterator is not None else None)
     trainer.logger.drain()
     if iterator is not None:
         iterator.close()
+    if validation is not None and getattr(validation, "iterator", None) is not None:
+        validation.iterator.close()
     return list(trainer.logger.history)

@@ -456,3 +456,41 @@ def test_progress_lines_at_info_level(monkeypatch, capsys):
     assert f"Frame head: frames {frames}/{frames} processed | FPS:" in out
     assert f"Backward: frames {frames}/{frames} processed | FPS:" in out
     assert "Step 0 took" in out
+
+
+def test_validation_reads_the_validation_recordings(tmp_path):
+    """With a validation folder configured, the periodic validation draws its sequences from those recordings
+    through a second seeded iterator; without one it falls back to seeded synthetic frames."""
+    import numpy as np
+    from fbamtrain_b200.data import ArrayRecording, SyntheticRecording
+    from fbamtrain_b200.tokenizer import Tokenizer
+    from fbamtrain_b200.train import _validation_source
+    for name, seeds in (("rec", (0, 1)), ("val", (7,))):
+        (tmp_path / name).mkdir()
+        for i in seeds:
+            r = SyntheticRecording(8, 16, 50, seed=i)
+            cells = np.stack([r.frame(t)[0] for t in range(50)])
+            ArrayRecording(cells, [r.frame(t)[1] for t in range(50)]).save(str(tmp_path / name / f"r{i}.fbrec.npz"))
+    Tokenizer(list("abcdefghijklmnopqrstuvwxyz") + ["ab", "th"]).save(str(tmp_path / "tok.txt"))
+    d = presets.tiny()
+    d["tokenizer_file_path"] = "tok.txt"
+    d["model_config"]["action_vocab"] = 0
+    d["train_data_config"]["recordings_directory_path"] = "rec"
+    d["validation_data_config"]["recordings_directory_path"] = "val"
+    d["enable_validation"], d["validation_interval"] = True, 1
+    cfg = RunConfiguration.from_json(d)
+    tr = Trainer(cfg, device=CPU, working_dir=str(tmp_path))
+    source = _validation_source(tr)
+    assert source.__name__ == "from_recordings"
+    vc, vt = source()
+    assert tuple(vc.shape[:2]) == (cfg.micro_batch_size, cfg.validation_sequence_length)
+    source.iterator.close()
+    lines = []
+    tr.logger.log_validation = lambda step, loss: lines.append((step, loss))
+    run_training(tr, max_steps=2)
+    tr.close()
+    assert [s for s, _ in lines] == [1, 2] and all(np.isfinite(l) for _, l in lines)
+    d["validation_data_config"]["recordings_directory_path"] = ""
+    tr = Trainer(RunConfiguration.from_json(d), device=CPU, working_dir=str(tmp_path))
+    assert _validation_source(tr).__name__ == "synthetic"
+    tr.close()
