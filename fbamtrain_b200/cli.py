@@ -145,6 +145,16 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
                 sys.stdout.write(json.dumps({"step": step, "step_time_sec": time.perf_counter() - t0,
                                              "loss/train": loss}) + "\n")
                 sys.stdout.flush()
+        if cfg.enable_validation and cfg.validation_interval and trainer.step_count % cfg.validation_interval == 0:
+            vsrc = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point, vocab,
+                                        seed=cfg.validation_data_config.iteration_seed, pin=False)
+            vloss = trainer.validation_loss(*vsrc.next_batch(cfg.micro_batch_size, cfg.validation_sequence_length))
+            if rank == layout.action_ranks[0]:
+                LOG("INFO", f"Step {trainer.step_count} validation loss = {vloss:.6f}")
+                if os.environ.get("FBAMTRAIN_METRICS_JSON"):
+                    import json
+                    sys.stdout.write(json.dumps({"step": trainer.step_count, "loss/validation": vloss}) + "\n")
+                    sys.stdout.flush()
         if interval > 0 and trainer.step_count % interval == 0:
             trainer.save_checkpoint(manager, iterator.checkpoint() if iterator is not None else None)
     if iterator is not None:

@@ -324,6 +324,20 @@ class PipelineTrainer:
         for p in self.model.action_model.parameters():
             dist.broadcast(p.data, src=first_action)
 
+    @torch.no_grad()
+    def validation_loss(self, cells: torch.Tensor, targets: torch.Tensor) -> float:
+        """Mean cross-entropy of the current model on ``cells`` / ``targets`` (one micro-batch).  Collective: the
+        model is gathered, the first action-model rank evaluates it in one piece and shares the result."""
+        self.gather_model()
+        first_action = self.pipe.layout.action_ranks[0] % self.per_replica if self.replicas > 1 \
+            else self.pipe.layout.action_ranks[0]
+        out = torch.zeros(1, dtype=torch.float64, device=self.device)
+        if dist.get_rank() == first_action:
+            scale = 1.0 / (cells.shape[0] * cells.shape[1])
+            out[0] = float(self.model(cells.to(self.device), targets.to(self.device), scale))
+        dist.broadcast(out, src=first_action)
+        return float(out.item())
+
     def save_checkpoint(self, manager, dataset_state=None) -> str:
         """Collective.  Returns the model file's path."""
         from ..utils import safetensors_io as st

@@ -61,6 +61,7 @@ def test_cli_frame_head_parallel_runs_the_two_stage_pipeline(tmp_path):
     cfg = presets.tiny()
     cfg["model_config"].update({"action_heads": 2, "lstm_layers": 1})
     cfg["micro_batch_size"], cfg["total_batch_size"] = 2, 4
+    cfg["enable_validation"], cfg["validation_interval"] = True, 2
     run = tmp_path / "run.json"
     run.write_text(json.dumps(cfg))
     with socket.socket() as s:
@@ -81,6 +82,7 @@ def test_cli_frame_head_parallel_runs_the_two_stage_pipeline(tmp_path):
     outs = [p.communicate(timeout=300)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), outs
     assert "Step 1 took" in outs[1] and "loss/train" in outs[1]
+    assert "Step 2 validation loss" in outs[1]
 
 
 def test_launcher_starts_data_parallel_ranks(tmp_path):
