@@ -18,6 +18,12 @@
 //
 // Q/K/V/O/dO are addressed as (B, T, H, D) views with arbitrary batch / row / head strides (the fused QKV
 // projection output is used in place).  All mbarrier waits are bounded.
+//
+// Takes the place of the reference's attention kernels: flash-attention forward with log-sum-exp output, the
+// dO·O pre-pass and the backward producing dQ, dK, dV (reference:
+// kernel_gen/kernel_gen/kernels/flash_attention_codegen/compile.py:280-330, kernels/flash_attention_fwd.py:36-266,
+// kernels/flash_attention_bwd.py:6-313; selected in src/passes/mha_attention_pass.cpp).  The reference supports
+// head dimension 128 only; 64 is added here.
 #include "tc05.cuh"
 
 namespace {

@@ -20,6 +20,9 @@
 // its slot of every peer's flag array (st.release.sys after a system-scope fence) and waits until all slots
 // of its own array hold >= e (ld.acquire.sys).  Every wait is bounded; when it runs out the kernel records
 // COMM_ERR_PEER_TIMEOUT plus the rank it was waiting for in `status` and returns, leaving the context usable.
+//
+// The reference reduces gradients with NCCL all-reduce calls on packed buffers and steps the optimizer afterwards
+// (reference: src/main.cpp:3572-3713, ccl/src/ccl_nccl.cpp:197-232); these kernels replace that sequence.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <string.h>

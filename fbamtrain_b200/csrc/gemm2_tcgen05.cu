@@ -12,6 +12,9 @@
 // .cta_group::2 and the barrier address of the leader; no multicast anywhere); tcgen05.commit arrives on both CTAs'
 // "empty" / "tmem_full" barriers at once; the epilogue warps of the second CTA release the accumulator by a remote
 // arrive on the leader's "tmem_empty" barrier.  All waits are bounded; the cluster is re-joined before exit.
+//
+// Same operation set as gemm_tcgen05.cu (reference kernel families: cutlass_codegen/gemm_cutlass_kernel.cu:198-330,
+// cutlass_codegen/conv2d_cutlass_kernel.cu).
 #include "gemm_epilogue.cuh"
 #include "gemm_tcgen05.h"
 #include "tc05.cuh"

@@ -24,6 +24,13 @@
 // accumulate-into-output), bf16 or fp32 output.
 //
 // Every mbarrier wait is bounded; on timeout the CTA writes an error code to `status` and unwinds.
+//
+// Takes the place of the reference's GEMM and convolution kernel families: matmul / addmm / addmm_gelu[_preact] /
+// matmul_gelu_bwd with transposed-operand, fp32-output and accumulate variants (reference:
+// kernel_gen/kernel_gen/kernels/cutlass_codegen/gemm_cutlass_kernel.cu:198-330, kernels/matmul.py), the fusions
+// its matmul pass selects (src/passes/matmul_pass.cpp:2783-3468), and conv2d fprop / dgrad / wgrad with
+// accumulation (cutlass_codegen/conv2d_cutlass_kernel.cu, kernels/conv2d.py:72-190, kernels/conv2d_bwd.py:6-232;
+// dispatch in src/passes/conv2d_pass.cpp).
 #include "gemm_tcgen05.h"
 #include "gemm_epilogue.cuh"
 #include "tc05.cuh"

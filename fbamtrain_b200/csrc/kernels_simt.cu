@@ -2,6 +2,14 @@
 // cross-entropy, bias-gradient reductions and the fused optimizer update.  All are written for
 // 16-byte vector accesses on bf16 data with fp32 arithmetic, one pass over memory per tensor, grids
 // sized from the problem (rows or 16-byte packets), and predicated tails.
+//
+// Reference kernel families covered: build_cell_embeds and its three backward kernels
+// (kernel_gen/kernel_gen/kernels/build_cell_embeds.py:23-248, build_cell_embeds_bwd.py:6-322), rms_norm fwd / bwd
+// (kernels/rms_norm.py:14-104), layer_norm fwd (kernels/layer_norm.py:13-90), cross_entropy_on_targets fwd / bwd
+// (kernels/cross_entropy.py:23-58, cross_entropy_bwd.py:22-66), avg_pool2d NHWC 2x2 fwd / bwd and the mean over
+// positions (kernels/avg_pool2d.py:35-144, avg_pool2d_bwd.py:6-214, mean_reduce.py:30-108), column sums for bias
+// gradients (kernels/sum_reduce.py:33-140), GELU / GeGLU and their gradients (kernels/act.py:43-86), and the AdamW
+// and SGD steps (kernels/optimizer.py:6-79).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>

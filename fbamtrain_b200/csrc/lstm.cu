@@ -18,6 +18,11 @@
 //
 // (The batch dimension is the 8-wide N of mma.sync.m16n8k16; the legacy tensor path is the right tool
 // here: tcgen05 tiles start at M = 64 rows per CTA and would be ≥ 87 % padding for this shape.)
+//
+// The reference runs the recurrence as one GEMM launch plus a point-wise cell kernel per time step (reference:
+// kernel_gen/kernel_gen/kernels/lstm_cell.py:6-144, kernels/lstm_cell_bwd.py:6-273 for the cell arithmetic and the
+// recompute / backward point-wise kernels; tensorlib/src/streaming_lstm.cpp and streaming_lstm_bwd.cpp for the loop
+// around them); gate order i, f, g, o, fp32 gates and cell state, tanh(x) = 2·sigmoid(2x) - 1 as there.
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>

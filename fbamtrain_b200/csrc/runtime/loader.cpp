@@ -1,5 +1,9 @@
 // Batch assembly for recordings stored as raw ".fbrec" files.
 //
+// The rules follow the reference's batch preparation (reference: src/main.cpp:1812-1984 — token stream consumption
+// and frame pairing; src/frame_utils.cpp:5-32 — cell states; src/dataset_iterator.cpp:169-237 — sampling), whose
+// decoder pool and prefetch thread this loader replaces.
+//
 // A training step of the small benchmark model consumes 8 x 1024 frames of 48 x 160 cells = 755 MB of cell states
 // per GPU; at the step rates this framework reaches that is several GB/s of host-side gathering per GPU, which a
 // per-frame Python loop cannot deliver.  This loader memory-maps the recordings once and fills a (pinned) batch

@@ -1,5 +1,9 @@
 // Membership master of the fault-tolerant collective layer, as a native service.
 //
+// The reference delegates this role to the master process of the PCCL library behind its ftccl wrapper (reference:
+// ftccl/include/ftccl.h:198-229 — CreateMaster / RunMaster / InterruptMaster; src/main.cpp:266-320, 401-425 — how the
+// trainer votes on topology updates and waits for the world size).
+//
 // Peers hold one TCP connection to the master and exchange newline-terminated JSON objects with it:
 //
 //   {"op":"connect","peer_group":g,"ip":"a.b.c.d"}          -> {"ok":true,"uid":u}

@@ -4,7 +4,8 @@ Run as a split-K tensor-core GEMM whose K dimension is the output pixels: both o
 place through 4-D TMA gathers (``dY`` bricks of 64 pixels as the transposed A operand, the input
 shifted by the filter tap as the transposed B operand), each CTA accumulates one ``128 x BN`` tile of
 ``dW`` for one tap over its share of the pixels in tensor memory, and partial tiles are added into an
-fp32 ``dW`` with atomics.
+fp32 ``dW`` with atomics.  (reference: wgrad with accumulate-into-existing and split-K in
+``kernel_gen/kernel_gen/kernels/conv2d_bwd.py:120-232`` and the CUTLASS wgrad path of ``src/passes/conv2d_pass.cpp``.)
 """
 from __future__ import annotations
 

@@ -3,6 +3,11 @@
 Tensor-core work (linear layers, convolutions, LM head) goes through the tcgen05 GEMM /
 implicit-GEMM entry points; everything else through the bandwidth-bound kernels.  Model dtype on
 this path is bf16 (fp32 parameters — embeddings, LSTM — are handled where noted).
+
+What the reference does in lowering passes over its op graph — fusing bias / GELU / pre-activation output into
+the GEMM, choosing transposed-operand variants, splitting convolutions into fprop / dgrad / wgrad kernels
+(reference: ``src/passes/matmul_pass.cpp:2783-3689``, ``src/passes/conv2d_pass.cpp``) — happens here at call
+time: the autograd Functions pick the epilogue and operand form of each launch.
 """
 from __future__ import annotations
 

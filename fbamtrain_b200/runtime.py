@@ -5,7 +5,9 @@ dataset RNG and batch drawing, the ``FBAM_TOK v1.0`` trie tokenizer, a safetenso
 file comparer, the durable dataset-cursor writer thread, the TCP rendezvous, and the membership master of the
 fault-tolerant collective layer.  The pure-Python modules
 (``rng``, ``tokenizer``, ``utils.safetensors_io``, ``data.cursor``, ``parallel.rendezvous``) implement the same
-behaviour and are used as oracles in the tests; callers may use either.
+behaviour and are used as oracles in the tests; callers may use either.  (reference: ``src/random.cpp``,
+``src/tokenizer.cpp``, ``tensorlib/src/safe_tensors.cpp``, ``src/dataset_cursor.cpp``, ``src/rdvz.cpp``,
+``src/dataset_iterator.cpp``, ``src/tenscmp.cpp:12-79``.)
 """
 from __future__ import annotations
 
