@@ -860,9 +860,15 @@ int fbam_global_avgpool(const void* in, void* out, long long n, int pix, int c, 
 
 int fbam_colsum(const void* x, float* out, long long rows, int cols, void* stream) {
   if (cols % 8 != 0) return 1;
-  const int threads = 128, rpb = 256;
-  dim3 grid((cols / 8 + threads - 1) / threads, (unsigned)((rows + rpb - 1) / rpb));
-  colsum_kernel<<<grid, threads, 0, STREAM(stream)>>>((const bf16*)x, out, rows, cols, rpb);
+  const int threads = 128;
+  const int gx = (cols / 8 + threads - 1) / threads;
+  // rows per block: enough blocks to occupy every SM several times over (the loads of a thread are its only
+  // memory parallelism), but at least 32 rows per block so that the atomics stay a small part of the work
+  const long long want_gy = (148 * 8 + gx - 1) / gx;
+  long long rpb = (rows + want_gy - 1) / want_gy;
+  rpb = rpb < 32 ? 32 : (rpb > 256 ? 256 : rpb);
+  dim3 grid(gx, (unsigned)((rows + rpb - 1) / rpb));
+  colsum_kernel<<<grid, threads, 0, STREAM(stream)>>>((const bf16*)x, out, rows, cols, (int)rpb);
   return CHECK_LAUNCH();
 }
 
