@@ -32,6 +32,7 @@
 // accumulation (cutlass_codegen/conv2d_cutlass_kernel.cu, kernels/conv2d.py:72-190, kernels/conv2d_bwd.py:6-232;
 // dispatch in src/passes/conv2d_pass.cpp).
 #include "gemm_tcgen05.h"
+#include <cstddef>
 #include "gemm_epilogue.cuh"
 #include "tc05.cuh"
 
@@ -446,6 +447,19 @@ int pick_bn(int n, int requested) {
 // Driver result code of the most recent failed tensor-map encode, and the runtime's pending error (not cleared).
 extern "C" int fbam_last_driver_error() { return g_fbam_last_driver_error; }
 extern "C" int fbam_pending_runtime_error() { return (int)cudaPeekAtLastError(); }
+
+// Layout of GemmParams as this library was compiled: total size, then the offsets of a few fields spread over
+// the struct.  Callers that mirror the struct (the ctypes binding) compare these with their own layout at load.
+extern "C" void fbam_gemm_params_layout(long long* out) {
+  out[0] = (long long)sizeof(GemmParams);
+  out[1] = (long long)offsetof(GemmParams, status);
+  out[2] = (long long)offsetof(GemmParams, split_workspace);
+  out[3] = (long long)offsetof(GemmParams, rs_out);
+  out[4] = (long long)offsetof(GemmParams, rs_row_stores);
+  out[5] = (long long)offsetof(GemmParams, mode);
+  out[6] = (long long)offsetof(GemmParams, conv);
+  out[7] = (long long)sizeof(ConvGeom);
+}
 
 extern "C" int fbam_set_reserved_sms(int n) {
   const int old = g_fbam_reserved_sms;

@@ -61,12 +61,26 @@ def available() -> bool:
     return os.path.exists(LIB_PATH)
 
 
+def _check_struct_layout(library: C.CDLL) -> None:
+    """The parameter struct is mirrored by hand above: refuse a library whose layout differs (a stale build)."""
+    got = (C.c_longlong * 8)()
+    library.fbam_gemm_params_layout.restype = None
+    library.fbam_gemm_params_layout(got)
+    mine = [C.sizeof(GemmParams), GemmParams.status.offset, GemmParams.split_workspace.offset,
+            GemmParams.rs_out.offset, GemmParams.rs_row_stores.offset, GemmParams.mode.offset,
+            GemmParams.conv.offset, C.sizeof(ConvGeom)]
+    if list(got) != mine:
+        raise RuntimeError(f"{LIB_PATH} was built from different sources than this binding (GemmParams layout "
+                           f"{list(got)} vs {mine}); run `python -m fbamtrain_b200.build`")
+
+
 def lib() -> C.CDLL:
     global _lib
     if _lib is None:
         if not os.path.exists(LIB_PATH):
             raise RuntimeError(f"native kernel library missing: {LIB_PATH} (run `python -m fbamtrain_b200.build`)")
         _lib = C.CDLL(LIB_PATH)
+        _check_struct_layout(_lib)
         _lib.fbam_gemm_bf16.restype = C.c_int
         _lib.fbam_conv_bf16.restype = C.c_int
         _lib.fbam_conv_wgrad_bf16.restype = C.c_int

@@ -294,3 +294,14 @@ def test_step_plan_records_launches_phases_and_flops():
     assert p.by("name")["fbam_gemm_bf16"] == (2, 6e9)
     text = p.listing()
     assert text.startswith("# 4 launches") and "(recompute)" in text and "fbamtrain::frame_head_fwd" in text
+
+
+def test_kernel_library_layout_matches_the_binding():
+    """Loading the kernel library compares the compiled layout of its parameter struct with the ctypes mirror."""
+    from fbamtrain_b200.ops import native as nv
+    if not nv.available():
+        pytest.skip("kernel library not built")
+    nv.lib()                                            # raises on a mismatch
+    got = (nv.C.c_longlong * 8)()
+    nv.lib().fbam_gemm_params_layout(got)
+    assert got[0] == nv.C.sizeof(nv.GemmParams) and got[7] == nv.C.sizeof(nv.ConvGeom)
