@@ -12,6 +12,7 @@ step in the file name must equal the stored ``step_count`` (reference:
 from __future__ import annotations
 
 import os
+import threading
 import re
 from typing import Dict, Optional, Tuple
 
@@ -64,15 +65,39 @@ def load_model_params(model: FbamModel, tensors: Dict[str, torch.Tensor]) -> Non
 
 
 class CheckpointManager:
-    def __init__(self, directory: str, max_training_steps: int):
+    def __init__(self, directory: str, max_training_steps: int, background: bool = False):
+        """``background``: ``save`` snapshots the tensors into host memory on the calling thread (device→host copies
+        only) and leaves the file write — the slow part for multi-gigabyte states — to a worker thread; training
+        continues meanwhile.  A later ``save``, ``find_latest``, ``load`` or ``wait`` first waits for the pending
+        write, and a write error is raised there.  The file appears under its final name only when complete
+        (temporary file, fsync, rename), in either mode."""
         self.directory = directory
         self.max_training_steps = int(max_training_steps)
         self.pad = len(str(self.max_training_steps))
+        self.background = background
+        self._writer: Optional[threading.Thread] = None
+        self._write_error: Optional[BaseException] = None
+
+    def wait(self) -> None:
+        """Blocks until the pending background write (if any) is on disk; raises what it raised."""
+        writer, self._writer = self._writer, None
+        if writer is not None:
+            writer.join()
+        error, self._write_error = self._write_error, None
+        if error is not None:
+            raise RuntimeError(f"background checkpoint write failed: {error}") from error
+
+    def _write(self, tensors: Dict[str, torch.Tensor], path: str) -> None:
+        try:
+            st.save_file(tensors, path)
+        except BaseException as e:  # noqa: BLE001 - reported by wait()
+            self._write_error = e
 
     def path_for(self, step: int) -> str:
         return os.path.join(self.directory, f"checkpoint_step_{int(step):0{self.pad}d}.safetensors")
 
     def find_latest(self) -> Optional[Tuple[int, str]]:
+        self.wait()
         if not os.path.isdir(self.directory):
             return None
         best: Optional[Tuple[int, str]] = None
@@ -101,11 +126,19 @@ class CheckpointManager:
                     t = _u64([int(t.reshape(-1)[0])])
                 tensors[name] = t
         path = self.path_for(step)
-        st.save_file({k: v.detach().cpu() for k, v in tensors.items()}, path)
+        self.wait()
+        if not self.background:
+            st.save_file({k: v.detach().cpu() for k, v in tensors.items()}, path)
+            return path
+        # the snapshot must not alias live training state: .cpu() copies device tensors, host tensors are cloned
+        snapshot = {k: (v.detach().cpu() if v.device.type != "cpu" else v.detach().clone()) for k, v in tensors.items()}
+        self._writer = threading.Thread(target=self._write, args=(snapshot, path), name="fbam-checkpoint-writer")
+        self._writer.start()
         return path
 
     def load(self, path: str, model: FbamModel, optimizers: Dict[str, Optimizer],
              batch_size: Optional[int] = None) -> Tuple[int, DatasetIteratorState]:
+        self.wait()
         m = _NAME_RE.match(os.path.basename(path))
         tensors = st.load_file(path)
         if "step_count" not in tensors:

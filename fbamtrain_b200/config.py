@@ -242,6 +242,7 @@ class CheckpointingConfiguration:
     checkpoint_directory: str
     resume_behavior: str = "load_latest"
     dataset_cursor_path: str = ""
+    background_write: bool = False       # addition: write checkpoint files on a worker thread (see checkpoint.py)
 
     @staticmethod
     def from_json(o: Dict[str, Any]) -> "CheckpointingConfiguration":
@@ -256,7 +257,8 @@ class CheckpointingConfiguration:
         cursor = ""
         if "dataset_cursor_path" in o:
             cursor = _str(o, "dataset_cursor_path", ctx)
-        return CheckpointingConfiguration(interval, directory, _RESUME[raw], cursor)
+        background = _bool(o, "background_write", ctx) if "background_write" in o else False
+        return CheckpointingConfiguration(interval, directory, _RESUME[raw], cursor, background)
 
 
 @dataclass

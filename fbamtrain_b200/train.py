@@ -107,7 +107,7 @@ class Trainer:
         self.ring = LossRingBuffer(self.device)
         self.logger = AsyncStepLogger(self.ring)
         self.ckpt = CheckpointManager(os.path.join(working_dir, cfg.checkpointing.checkpoint_directory),
-                                      cfg.max_training_steps)
+                                      cfg.max_training_steps, background=cfg.checkpointing.background_write)
         self.cursor: Optional[DatasetCursorCommitter] = None
         self._cuda = self.device.type == "cuda"
         if self._cuda:
@@ -338,6 +338,7 @@ class Trainer:
         return ds
 
     def close(self) -> None:
+        self.ckpt.wait()
         self.logger.drain()
         self.logger.close()
         if self.cursor is not None:

@@ -494,3 +494,58 @@ def test_validation_reads_the_validation_recordings(tmp_path):
     tr = Trainer(RunConfiguration.from_json(d), device=CPU, working_dir=str(tmp_path))
     assert _validation_source(tr).__name__ == "synthetic"
     tr.close()
+
+
+def test_background_checkpoint_write_snapshots_before_training_continues(tmp_path, monkeypatch):
+    """With ``background_write`` the file is written by a worker thread from a snapshot taken inside ``save``:
+    steps taken while the (artificially slow) write is in flight do not leak into the file, the file name appears
+    only when complete, and resuming from it repeats the continued run."""
+    import threading
+    from fbamtrain_b200.utils import safetensors_io
+    d = presets.tiny()
+    d["checkpointing"] = {"checkpoint_interval": 3, "checkpoint_directory": "ckpt", "resume_behavior": "load_latest",
+                          "background_write": True}
+    d["max_training_steps"] = 100
+    cfg = RunConfiguration.from_json(d)
+    assert cfg.checkpointing.background_write
+    batches = [_batch(cfg, seed=s) for s in range(6)]
+    gate = threading.Event()
+    real_save = safetensors_io.save_file
+
+    def slow_save(tensors, path, metadata=None):
+        gate.wait(30)
+        real_save(tensors, path, metadata)
+    monkeypatch.setattr(safetensors_io, "save_file", slow_save)
+    tr = Trainer(cfg, device=CPU, working_dir=str(tmp_path))
+    for i in range(3):
+        tr.train_step(*batches[i])
+    path = tr.save_checkpoint()
+    assert not os.path.exists(path)                                    # still being written
+    cont = [float(tr.train_step(*batches[i])) for i in range(3, 6)]   # training goes on meanwhile
+    gate.set()
+    tr.close()                                                         # waits for the writer
+    assert os.path.exists(path) and not os.path.exists(path + ".tmp")
+    monkeypatch.setattr(safetensors_io, "save_file", real_save)
+    tr2 = Trainer(cfg, device=CPU, working_dir=str(tmp_path))
+    tr2.load_latest_checkpoint()
+    assert tr2.step_count == 3
+    resumed = [float(tr2.train_step(*batches[i])) for i in range(3, 6)]
+    tr2.close()
+    assert resumed == pytest.approx(cont, abs=1e-6)
+
+
+def test_background_checkpoint_write_errors_surface(tmp_path, monkeypatch):
+    from fbamtrain_b200.checkpoint import CheckpointManager
+    from fbamtrain_b200.models import FbamModel
+    from fbamtrain_b200.utils import safetensors_io
+    cfg = RunConfiguration.from_json(presets.tiny())
+    model = FbamModel(cfg.model_config, 32)
+
+    def failing_save(tensors, path, metadata=None):
+        raise OSError("disk full")
+    monkeypatch.setattr(safetensors_io, "save_file", failing_save)
+    manager = CheckpointManager(str(tmp_path / "ck"), 100, background=True)
+    manager.save(1, model, {}, None)
+    with pytest.raises(RuntimeError, match="disk full"):
+        manager.wait()
+    manager.wait()                                                     # reported once
