@@ -23,7 +23,7 @@ import torch
 
 from .checkpoint import CheckpointManager
 from .config import ParallelConfiguration, RunConfiguration
-from .data import (DatasetCursorCommitter, DatasetCursorSnapshot, RecordingDatasetIterator,
+from .data import (Batch, DatasetCursorCommitter, DatasetCursorSnapshot, RecordingDatasetIterator,
                    StreamTokenizationContext, SyntheticBatchSource, consume_next_token, prepare_cell_states)
 from .models import FbamModel
 from .optim import AdamwOptimizer, MuonWithAuxAdam, Optimizer, create_optimizer
@@ -318,10 +318,14 @@ class Trainer:
 
     # ------------------------------------------------------------------------------------------
     def save_checkpoint(self, dataset_state=None) -> str:
+        """Collective under data parallelism (every rank calls it: the sharded optimizer state is gathered first);
+        rank 0 writes the file.  Returns the file's path on every rank."""
         if self._cuda:
             torch.cuda.synchronize()
         if self.dp is not None:
             self.dp.gather_optimizer_state(self)
+        if self.rank != 0:
+            return self.ckpt.path_for(self.step_count)
         return self.ckpt.save(self.step_count, self.model, self.optimizers, dataset_state)
 
     def load_latest_checkpoint(self):
@@ -332,7 +336,7 @@ class Trainer:
         if latest is None:
             return None
         step, ds = self.ckpt.load(latest[1], self.model, self.optimizers,
-                                  self.cfg.micro_batch_size * self.grad_accum_steps)
+                                  self.cfg.micro_batch_size * self.grad_accum_steps * self.world)
         self.step_count = step
         LOG("INFO", f"Resumed from {latest[1]} at step {step}")
         return ds
@@ -392,6 +396,13 @@ class _PinnedBatchBuffer:
         self._event = event
 
 
+def _data_rank(trainer: Trainer) -> int:
+    """Which share of a global batch draw this process takes: its current data-parallel rank (ranks renumber when
+    the membership of a fault-tolerant group changes), within the nominal world the batch is drawn for."""
+    rank = trainer.dp.rank if trainer.dp is not None else 0
+    return rank % max(1, trainer.world)
+
+
 def _make_assembler(trainer: Trainer, local_batch: int):
     """The batch assembler for the dataset iterator's prefetch thread, or None when the per-frame Python path has
     to be used: the native loader needs raw ``.fbrec`` recordings, a tokenizer and the runtime library."""
@@ -416,9 +427,10 @@ def _make_assembler(trainer: Trainer, local_batch: int):
                for _ in range(2)]
 
     def assemble(indices, starts, buffer_index):
+        lo = _data_rank(trainer) * local_batch   # the iterator draws the global batch; this rank assembles its share
         buf = buffers[buffer_index]
         buf.wait_until_free()
-        loader.fill(indices, starts, seq, buf.cells, buf.targets)
+        loader.fill(indices[lo:lo + local_batch], starts[lo:lo + local_batch], seq, buf.cells, buf.targets)
         return buf, buf.cells, buf.targets
 
     assemble.loader = loader          # keeps the mapping alive as long as the assembler
@@ -456,12 +468,16 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
     """The outer loop: data → ``train_step`` → cursor commit → validation → checkpoint."""
     cfg = trainer.cfg
     local_batch = cfg.micro_batch_size * trainer.grad_accum_steps
+    global_batch = local_batch * trainer.world
     iterator = None
     if source is None:
         if cfg.train_data_config.recordings_directory_path:
+            # Every rank runs the same seeded iterator over the GLOBAL batch and takes its own share of each draw:
+            # the data order does not depend on the number of ranks, and one iterator state (stored in the
+            # checkpoint and the cursor file) resumes all of them.
             iterator = RecordingDatasetIterator(
-                os.path.join(trainer.working_dir, cfg.train_data_config.recordings_directory_path), local_batch,
-                cfg.train_sequence_length, cfg.train_data_config.iteration_seed + trainer.rank,
+                os.path.join(trainer.working_dir, cfg.train_data_config.recordings_directory_path), global_batch,
+                cfg.train_sequence_length, cfg.train_data_config.iteration_seed,
                 assembler=_make_assembler(trainer, local_batch))
         else:
             source = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point,
@@ -470,6 +486,8 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
     restored = trainer.load_latest_checkpoint()
     if iterator is not None and restored is not None and restored.batch_size:
         iterator.restore(restored)
+    if source is not None and trainer.step_count and hasattr(source, "seek"):
+        source.seek(trainer.step_count)        # synthetic batches are a function of (seed, call number)
     cursor_path = cfg.checkpointing.dataset_cursor_path
     if cursor_path:
         cursor_path = os.path.join(trainer.working_dir, cursor_path)
@@ -478,7 +496,7 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
             if snap.step_count != trainer.step_count:
                 LOG("WARN", f"dataset cursor is at step {snap.step_count}, checkpoint at {trainer.step_count}")
             from .data.iterator import DatasetIteratorState
-            iterator.restore(DatasetIteratorState(rng_state=snap.rng_state, batch_size=local_batch))
+            iterator.restore(DatasetIteratorState(rng_state=snap.rng_state, batch_size=global_batch))
         trainer.cursor = DatasetCursorCommitter(cursor_path)
     limit = cfg.max_training_steps if max_steps is None else min(cfg.max_training_steps, trainer.step_count + max_steps)
     mc = cfg.model_config
@@ -490,6 +508,10 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
                 if batch.tensors is not None:          # gathered by the native loader on the prefetch thread
                     assembled, cells, targets = batch.tensors
                 else:
+                    if trainer.world > 1:              # this rank's share of the global draw
+                        lo = _data_rank(trainer) * local_batch
+                        batch = Batch(batch.recordings[lo:lo + local_batch], batch.indices[lo:lo + local_batch],
+                                      batch.start_positions[lo:lo + local_batch])
                     cells, targets = build_batch_from_recordings(batch, trainer.tokenizer, cfg.train_sequence_length,
                                                                  cfg.frame_rows, cfg.frame_cols, trainer.vocab,
                                                                  mc.max_code_point)
@@ -500,7 +522,7 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
             assembled.release(trainer.last_upload_event)
         if trainer.cursor is not None and iterator is not None:
             st = iterator.cursor_checkpoint()
-            trainer.cursor.commit(DatasetCursorSnapshot(trainer.step_count, st.rng_state, local_batch,
+            trainer.cursor.commit(DatasetCursorSnapshot(trainer.step_count, st.rng_state, global_batch,
                                                         cfg.train_sequence_length))
         if cfg.enable_validation and cfg.validation_interval and trainer.step_count % cfg.validation_interval == 0:
             with gputx_range("fbamtrain::validation"):
@@ -508,7 +530,7 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
                     validation = _validation_source(trainer)
                 vc, vt = validation()
                 trainer.logger.log_validation(trainer.step_count, trainer.validation_loss(vc, vt))
-        if trainer.step_count % cfg.checkpointing.checkpoint_interval == 0 and trainer.rank == 0:
+        if trainer.step_count % cfg.checkpointing.checkpoint_interval == 0:
             trainer.save_checkpoint(iterator.checkpoint() if iterator is not None else None)
     trainer.logger.drain()
     if iterator is not None:
