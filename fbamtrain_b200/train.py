@@ -497,7 +497,8 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
                 LOG("WARN", f"dataset cursor is at step {snap.step_count}, checkpoint at {trainer.step_count}")
             from .data.iterator import DatasetIteratorState
             iterator.restore(DatasetIteratorState(rng_state=snap.rng_state, batch_size=global_batch))
-        trainer.cursor = DatasetCursorCommitter(cursor_path)
+        if trainer.rank == 0:                  # the iterator state is the same on every rank: one writer
+            trainer.cursor = DatasetCursorCommitter(cursor_path)
     limit = cfg.max_training_steps if max_steps is None else min(cfg.max_training_steps, trainer.step_count + max_steps)
     mc = cfg.model_config
     while trainer.step_count < limit:
