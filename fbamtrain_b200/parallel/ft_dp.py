@@ -182,17 +182,25 @@ class FaultTolerantDataParallel:
         # collective: a peer that left after the previous step, fell silent or waits for admission is noticed here,
         # before anything is launched that would wait for it on the device, and the members enter the fused
         # kernels within a network round trip of each other, so the bounded device-side waits stay short.
-        aligned = peer.gate(trainer.step_count, timeout_s=self.gate_timeout_s) if peer.world_size > 1 \
-            else (peer.refresh_view() or not peer.membership_changed())
-        if not aligned or peer.membership_changed() or peer.are_peers_pending() or \
-                peer.world_size < self.expected_world:
-            if not aligned or peer.membership_changed() or peer.are_peers_pending():
-                if not self._retopologize(trainer):
-                    return self._drop(trainer, "topology update failed")
+        # After a topology change the members pass the gate again, now together with whoever was admitted: a member
+        # that re-formed the group on its own schedule (it was alone, or noticed the newcomer first) must not enter
+        # the collective while the others still expect it at the gate.
+        for _ in range(8):
+            aligned = peer.gate(trainer.step_count, timeout_s=self.gate_timeout_s) if peer.world_size > 1 \
+                else (peer.refresh_view() or not peer.membership_changed())
+            changed = not aligned or peer.membership_changed() or peer.are_peers_pending()
+            if changed and not self._retopologize(trainer):
+                return self._drop(trainer, "topology update failed")
             while self.wait_for_full_world and peer.world_size < self.expected_world:
                 time.sleep(self.full_world_poll_s)   # "not ready": the reference sleeps 1 s per round
-                if peer.are_peers_pending() and not self._retopologize(trainer):
-                    return self._drop(trainer, "topology update failed")
+                if peer.are_peers_pending():
+                    changed = True
+                    if not self._retopologize(trainer):
+                        return self._drop(trainer, "topology update failed")
+            if not changed:
+                break
+        else:
+            return self._drop(trainer, "membership did not settle")
         if peer.world_size < self.min_world:
             return self._drop(trainer, "too few peers")
         scale = self.expected_world / max(1, peer.world_size)

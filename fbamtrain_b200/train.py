@@ -50,7 +50,6 @@ class Trainer:
         self.device = device or torch.device("cuda" if torch.cuda.is_available() else "cpu")
         self.dp = dp
         self.world = dp.world_size if dp is not None else 1
-        self.rank = dp.rank if dp is not None else 0
         if cfg.total_batch_size % (cfg.micro_batch_size * self.world) != 0:
             raise ValueError("total_batch_size must be a multiple of micro_batch_size x data-parallel world size")
         self.grad_accum_steps = cfg.total_batch_size // (cfg.micro_batch_size * self.world)
@@ -118,6 +117,12 @@ class Trainer:
         self._loss_events: List[Tuple[int, object]] = [(-1, None)] * 64
         self._upload_slot, self._slot_in_use, self._fresh_buffer = 0, 0, False
         self._slot_free: List[Optional[torch.cuda.Event]] = [None, None]
+
+    @property
+    def rank(self) -> int:
+        """This process's current data-parallel rank (ranks are assigned, and can change, when the membership of a
+        fault-tolerant group changes)."""
+        return self.dp.rank if self.dp is not None else 0
 
     # ------------------------------------------------------------------------------------------
     def all_groups(self) -> List[FlatGroup]:

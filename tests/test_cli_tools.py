@@ -155,3 +155,32 @@ def test_cli_pipeline_reads_recordings(tmp_path):
     outs = [p.communicate(timeout=300)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), outs
     assert "Step 1 took" in outs[1] and "loss/train" in outs[1]
+
+
+def test_launcher_with_fault_tolerant_transport(tmp_path):
+    """``transport: "ftccl"`` through the launcher: it starts the membership master and two CPU ranks; the rank that
+    forms the group first must take the other in at the step gate, after which both train in lockstep (same
+    committed losses, no dropped step)."""
+    import socket
+    cfg = presets.tiny()
+    cfg["micro_batch_size"], cfg["total_batch_size"] = 1, 2
+    run = tmp_path / "run.json"
+    run.write_text(json.dumps(cfg))
+    ports = []
+    for _ in range(2):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            ports.append(s.getsockname()[1])
+    par = {"frame_head_parallel": {"use_frame_head_parallel": False, "transport": "ccl",
+                                   "ccl_rendezvous": {"ip": "127.0.0.1", "port": ports[0]}},
+           "ddp_parallel": {"use_ddp_parallel": True, "transport": "ftccl",
+                            "ftccl_master": {"ip": "127.0.0.1", "port": ports[1]}}}
+    parallel = tmp_path / "parallel.json"
+    parallel.write_text(json.dumps(par))
+    r = _run(["fbamtrain_b200.launch", "--nproc", "2", "--", "-c", str(run), "--parallel-config", str(parallel),
+              "--synthetic", "--steps", "3", "--device", "cpu", "-v"])
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "dropping step" not in r.stdout and "failed" not in r.stdout, r.stdout
+    for rank in (0, 1):
+        assert f"[rank {rank}]" in r.stdout
+    assert r.stdout.count("Step 2 took") == 2
