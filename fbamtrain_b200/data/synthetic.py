@@ -75,3 +75,50 @@ class SyntheticBatchSource:
         if self.pin:
             tg = tg.pin_memory()
         return cells, tg
+
+
+class PrefetchingSource:
+    """Generates the next batch of a source on a background thread while the current one trains (one batch ahead,
+    same order as calling the source directly).  Generating an 8 x 1024-frame batch takes longer on a few host
+    cores than a training step takes on the GPU; without this the loop would wait for its data."""
+
+    def __init__(self, source, batch: int, seq: int):
+        import queue
+        import threading
+        self.source, self.batch, self.seq = source, batch, seq
+        self._queue: "queue.Queue" = queue.Queue(maxsize=1)
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._produce, name="fbam-synthetic-prefetch", daemon=True)
+        self._thread.start()
+
+    def _produce(self) -> None:
+        import queue
+        while not self._stop.is_set():
+            try:
+                item = self.source.next_batch(self.batch, self.seq)
+            except BaseException as e:  # noqa: BLE001 - handed to the consumer
+                item = e
+            while not self._stop.is_set():
+                try:
+                    self._queue.put(item, timeout=0.1)
+                    break
+                except queue.Full:
+                    continue
+            if isinstance(item, BaseException):
+                return
+
+    def next_batch(self, batch: int, seq: int):
+        if (batch, seq) != (self.batch, self.seq):
+            raise ValueError("the prefetching source was set up for another batch shape")
+        item = self._queue.get()
+        if isinstance(item, BaseException):
+            raise item
+        return item
+
+    def close(self) -> None:
+        self._stop.set()
+        try:
+            self._queue.get_nowait()
+        except Exception:  # noqa: BLE001 - empty queue
+            pass
+        self._thread.join(5)

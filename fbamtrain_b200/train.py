@@ -24,7 +24,7 @@ import torch
 from .checkpoint import CheckpointManager
 from .config import ParallelConfiguration, RunConfiguration
 from .data import (Batch, DatasetCursorCommitter, DatasetCursorSnapshot, RecordingDatasetIterator,
-                   StreamTokenizationContext, SyntheticBatchSource, consume_next_token, prepare_cell_states)
+                   PrefetchingSource, StreamTokenizationContext, SyntheticBatchSource, consume_next_token, prepare_cell_states)
 from .models import FbamModel
 from .optim import AdamwOptimizer, MuonWithAuxAdam, Optimizer, create_optimizer
 from .tokenizer import Tokenizer
@@ -475,6 +475,7 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
     local_batch = cfg.micro_batch_size * trainer.grad_accum_steps
     global_batch = local_batch * trainer.world
     iterator = None
+    own_source = False
     if source is None:
         if cfg.train_data_config.recordings_directory_path:
             # Every rank runs the same seeded iterator over the GLOBAL batch and takes its own share of each draw:
@@ -487,12 +488,16 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
         else:
             source = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point,
                                           trainer.vocab, seed=cfg.train_data_config.iteration_seed + trainer.rank)
+            own_source = True
     validation = None
     restored = trainer.load_latest_checkpoint()
     if iterator is not None and restored is not None and restored.batch_size:
         iterator.restore(restored)
     if source is not None and trainer.step_count and hasattr(source, "seek"):
         source.seek(trainer.step_count)        # synthetic batches are a function of (seed, call number)
+    prefetcher = None
+    if own_source:                             # generate batch k + 1 on a host thread while batch k trains
+        source = prefetcher = PrefetchingSource(source, local_batch, cfg.train_sequence_length)
     cursor_path = cfg.checkpointing.dataset_cursor_path
     if cursor_path:
         cursor_path = os.path.join(trainer.working_dir, cursor_path)
@@ -541,6 +546,8 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
     trainer.logger.drain()
     if iterator is not None:
         iterator.close()
+    if prefetcher is not None:
+        prefetcher.close()
     if validation is not None and getattr(validation, "iterator", None) is not None:
         validation.iterator.close()
     return list(trainer.logger.history)

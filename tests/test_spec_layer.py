@@ -305,3 +305,24 @@ def test_kernel_library_layout_matches_the_binding():
     got = (nv.C.c_longlong * 8)()
     nv.lib().fbam_gemm_params_layout(got)
     assert got[0] == nv.C.sizeof(nv.GemmParams) and got[7] == nv.C.sizeof(nv.ConvGeom)
+
+
+def test_prefetching_source_keeps_order_and_reports_errors():
+    from fbamtrain_b200.data import PrefetchingSource, SyntheticBatchSource
+    direct = SyntheticBatchSource(8, 16, 256, 32, seed=4, pin=False)
+    want = [direct.next_batch(2, 8) for _ in range(4)]
+    pre = PrefetchingSource(SyntheticBatchSource(8, 16, 256, 32, seed=4, pin=False), 2, 8)
+    got = [pre.next_batch(2, 8) for _ in range(4)]
+    pre.close()
+    for (c0, t0), (c1, t1) in zip(want, got):
+        assert torch.equal(c0, c1) and torch.equal(t0, t1)
+    with pytest.raises(ValueError):
+        pre.next_batch(3, 8)
+
+    class Broken:
+        def next_batch(self, batch, seq):
+            raise OSError("no data")
+    bad = PrefetchingSource(Broken(), 1, 1)
+    with pytest.raises(OSError, match="no data"):
+        bad.next_batch(1, 1)
+    bad.close()
