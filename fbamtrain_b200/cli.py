@@ -115,8 +115,15 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
         src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point, vocab,
                                    seed=cfg.train_data_config.iteration_seed, pin=device.type == "cuda")
 
+        prefetch = None
+
         def next_batch():
-            return src.next_batch(cfg.total_batch_size, cfg.train_sequence_length)
+            nonlocal prefetch
+            if prefetch is None:               # started after a resume has positioned the source
+                from .data import PrefetchingSource
+                prefetch = PrefetchingSource(src, cfg.total_batch_size, cfg.train_sequence_length)
+            return prefetch.next_batch(cfg.total_batch_size, cfg.train_sequence_length)
+        next_batch.close = lambda: prefetch.close() if prefetch is not None else None
     from .checkpoint import CheckpointManager
     manager = CheckpointManager(os.path.join(working_dir, cfg.checkpointing.checkpoint_directory),
                                 cfg.max_training_steps)
@@ -159,6 +166,8 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
             trainer.save_checkpoint(manager, iterator.checkpoint() if iterator is not None else None)
     if iterator is not None:
         iterator.close()
+    if hasattr(next_batch, "close"):
+        next_batch.close()
     dist.destroy_process_group()
     return 0
 
