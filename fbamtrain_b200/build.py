@@ -70,7 +70,30 @@ def build_kernels(force: bool = False, verbose: bool = False) -> str:
     return KERNELS_SO
 
 
-def build_runtime(force: bool = False) -> str:
+SANITIZE_FLAGS = ["-O1", "-g", "-fsanitize=address,undefined", "-fno-omit-frame-pointer"]
+
+
+def sanitizer_preload() -> str:
+    """``LD_PRELOAD`` value for running Python with the sanitised runtime library (the sanitizer runtime must come
+    first, and libstdc++ has to be loaded with it for its C++ exception interceptor)."""
+    cxx = shutil.which("g++") or "g++"
+    libs = [subprocess.run([cxx, f"-print-file-name={n}"], capture_output=True, text=True).stdout.strip()
+            for n in ("libasan.so", "libstdc++.so")]
+    return " ".join(libs)
+
+
+def build_runtime(force: bool = False, sanitize: bool = False) -> str:
+    """``sanitize``: AddressSanitizer + UndefinedBehaviorSanitizer build of the host runtime (``--sanitize`` on the
+    command line; forces a rebuild — rebuild without it afterwards).  Run the CPU tests of the native runtime with
+    ``LD_PRELOAD="$(python -c 'from fbamtrain_b200.build import sanitizer_preload as p; print(p())')"
+    ASAN_OPTIONS=detect_leaks=0 python -m pytest tests/test_native_runtime.py tests/test_properties.py``."""
+    if sanitize:
+        os.makedirs(OBJ, exist_ok=True)
+        sources = sorted(glob.glob(os.path.join(CSRC, "runtime", "*.cpp")))
+        cxx = shutil.which("g++") or "g++"
+        flags = [f for f in CXX_FLAGS if f != "-O2"] + SANITIZE_FLAGS
+        _compile([cxx] + flags + ["-shared", "-o", RUNTIME_SO] + sources, os.path.join(OBJ, "link_runtime.log"))
+        return RUNTIME_SO
     os.makedirs(OBJ, exist_ok=True)
     sources = sorted(glob.glob(os.path.join(CSRC, "runtime", "*.cpp")))
     if not sources:
@@ -88,5 +111,9 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
 
 
 if __name__ == "__main__":
+    if "--sanitize" in sys.argv:
+        print("built (sanitised host runtime):", build_runtime(sanitize=True))
+        print("LD_PRELOAD=" + sanitizer_preload())
+        sys.exit(0)
     build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print("built:", KERNELS_SO, RUNTIME_SO if os.path.exists(RUNTIME_SO) else "")
