@@ -150,6 +150,9 @@ def bench_gemm_rs(a, rank, world, dev):
         os.environ["FBAMTRAIN_TP_RS_MODE"] = mode
         contexts[mode] = TpContext(None, dev, "fused")
     os.environ.pop("FBAMTRAIN_TP_RS_MODE", None)
+    # the epilogue form with 64 contiguous bytes per row and store instruction (lane-quad exchange)
+    contexts["epilogue+row_stores"] = TpContext(None, dev, "fused")
+    contexts["epilogue+row_stores"].rs_row_stores = True
     for m_full, k, n_out in a.shapes:
         kk = n_out // world                     # the K of this GEMM is the sharded hidden dimension
         h = torch.randn(m_full, kk, device=dev).to(BF)
