@@ -13,6 +13,7 @@ from typing import Optional
 
 import torch
 
+from ..utils import debug as _debug
 from ..utils import plan as _plan
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
@@ -109,6 +110,8 @@ def check(code: int, what: str) -> None:
                       f"{_lib.fbam_pending_runtime_error()}")
         raise RuntimeError(f"{what}: {_ERRORS.get(code, 'error')} (code {code}){detail}")
     _launches += 1
+    if _debug.BREAK_ON_LAUNCH and _debug.break_requested(_launches, what):
+        breakpoint()      # FBAMTRAIN_BREAK_ON_LAUNCH: inspect the caller's frames ("up"), "c" continues
     recording = _plan.active()
     if recording is not None:
         recording.on_launch(what)

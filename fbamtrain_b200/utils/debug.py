@@ -8,6 +8,10 @@
   same class of bug by zero-filling op ranges, ``execution_backend.cpp:77-155``).
 * ``FBAMTRAIN_DEBUG_KERNEL_LAUNCH=1`` — print one line per custom-kernel launch with its
   arguments (reference: ``execution_backend.cpp:796-803``).
+* ``FBAMTRAIN_BREAK_ON_LAUNCH=<n | entry point name>`` — stop in the Python debugger (``breakpoint()``) right
+  after the n-th native launch of the process, or after every launch of the named entry point, with the caller's
+  frames on the stack (the reference breaks on a chosen tensor id, ``tensorlib/src/tensorlib.cpp:116-139``,
+  ``tensorlib/src/cpudbg.cpp:7-21``).
 """
 from __future__ import annotations
 
@@ -25,6 +29,16 @@ PROFILE_LABELS = _flag("FBAMTRAIN_PROFILE_LABELS")   # wrap every native launch 
 SYNC_EVERY_OP = _flag("FBAMTRAIN_SYNC_EVERY_OP")
 POISON_ALLOC = _flag("FBAMTRAIN_POISON_ALLOC")
 DEBUG_KERNEL_LAUNCH = _flag("FBAMTRAIN_DEBUG_KERNEL_LAUNCH")
+BREAK_ON_LAUNCH = os.environ.get("FBAMTRAIN_BREAK_ON_LAUNCH", "")
+
+
+def break_requested(ordinal: int, entry_point: str) -> bool:
+    """Whether the launch just made (the ``ordinal``-th of the process, 1-based) is the one to stop at."""
+    if not BREAK_ON_LAUNCH:
+        return False
+    if BREAK_ON_LAUNCH.isdigit():
+        return ordinal == int(BREAK_ON_LAUNCH)
+    return entry_point == BREAK_ON_LAUNCH
 
 
 def fresh(shape, dtype, device) -> torch.Tensor:
