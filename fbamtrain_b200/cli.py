@@ -206,6 +206,9 @@ def main(argv=None) -> int:
 
     fhp = par.frame_head_parallel if par is not None else None
     if fhp is not None and fhp.use_frame_head_parallel:
+        if par.ddp_parallel.use_ddp_parallel and par.ddp_parallel.transport == "ftccl":
+            LOG("WARN", "data parallelism over pipelines runs on static process groups; the fault-tolerant transport "
+                        "(dynamic membership) applies to plain data parallelism")
         return _run_pipeline(cfg, par, args, device)
 
     dp = None
