@@ -1,4 +1,5 @@
 import copy
+import math
 import os
 
 import pytest
@@ -549,3 +550,28 @@ def test_background_checkpoint_write_errors_surface(tmp_path, monkeypatch):
     with pytest.raises(RuntimeError, match="disk full"):
         manager.wait()
     manager.wait()                                                     # reported once
+
+
+@pytest.mark.parametrize("opt", ["muon", "adamw", "sgd"])
+@pytest.mark.parametrize("mode,reduction", [("dilated", "last_pos"), ("geglu", "mean")])
+def test_scaled_down_reference_sample_configuration_trains(opt, mode, reduction):
+    """The reference's sample run configuration (its own architecture: attention layers inside the frame head,
+    dilated or GeGLU downsampling, last-position or mean reduction, one LSTM layer straight into the head), scaled
+    down to CPU size, trains with every optimizer."""
+    import copy
+    from test_config import DEBUG_JSON
+    d = copy.deepcopy(DEBUG_JSON)
+    d["micro_batch_size"] = d["total_batch_size"] = 2
+    d["train_sequence_length"] = d["validation_sequence_length"] = 8
+    d["frame_rows"], d["frame_cols"] = 8, 16
+    d["tokenizer_file_path"] = ""
+    d["optimizer"]["type"] = opt
+    d["model_config"].update({"n_embed": 64, "n_layer": 1, "n_head": 2, "frame_rows": 8, "frame_cols": 16,
+                              "dtype": "fp32", "use_fp16_accumulation": False, "action_vocab": 48,
+                              "downsample_conv_mode": mode, "frame_head_reduction_strategy": reduction})
+    cfg = RunConfiguration.from_json(d)
+    tr = Trainer(cfg, device=CPU)
+    cells, targets = _batch(cfg, seed=2)
+    losses = [float(tr.train_step(cells, targets)) for _ in range(4)]
+    tr.close()
+    assert all(math.isfinite(x) for x in losses) and losses[-1] < losses[0]
