@@ -10,6 +10,8 @@ the reference's checkpoint files (reference: ``src/framehead_model.cpp:733-778``
 """
 from __future__ import annotations
 
+from typing import Optional
+
 from typing import Callable, Dict, List, Tuple
 
 import torch
@@ -38,12 +40,14 @@ class FbamModel(nn.Module):
         self.action_model = ActionModel(cfg, self.vocab, dtype, seeds)
         self.frame_chunk = 0  # frames per frame-head call; 0 = all at once
 
-    def frame_head_chunk(self, flat_cells: torch.Tensor) -> torch.Tensor:
+    def frame_head_chunk(self, flat_cells: torch.Tensor, recompute: Optional[bool] = None) -> torch.Tensor:
         """The frame head on ``(frames, P, 3)`` cells.  With ``frame_head_recompute`` nothing but the cells and
         the embeddings is kept for the backward, which runs the frame head on the chunk again — the memory of the
         frame head is then one chunk's activations whatever the sequence length (the reference replays and
         recomputes frame by frame: ``src/main.cpp:3354-3483``).  The second forward does not count as useful FLOPs."""
-        if self.cfg.frame_head_recompute and torch.is_grad_enabled():
+        if recompute is None:
+            recompute = self.cfg.frame_head_recompute
+        if recompute and torch.is_grad_enabled():
             import contextlib
             from torch.utils.checkpoint import checkpoint
             from ..utils import flops

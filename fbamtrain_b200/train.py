@@ -115,6 +115,7 @@ class Trainer:
             self.h2d_stream = self.streams.h2d
         self._staging: Dict[Tuple, torch.Tensor] = {}
         self._loss_events: List[Tuple[int, object]] = [(-1, None)] * 64
+        self._warned_recompute = False
         self._upload_slot, self._slot_in_use, self._fresh_buffer = 0, 0, False
         self._slot_free: List[Optional[torch.cuda.Event]] = [None, None]
 
@@ -199,9 +200,26 @@ class Trainer:
                 flat = dev_cells.view(b * t, p, 3)
                 parts = []
                 with gputx_range("fbamtrain::frame_head_fwd"):
+                    n_chunks = (b * t + chunk - 1) // chunk
+                    recompute = None                  # None: as configured
                     for i, lo in enumerate(range(0, b * t, chunk)):
                         torch.cuda.current_stream().wait_event(events[i])
-                        parts.append(self.model.frame_head_chunk(flat[lo:lo + chunk]))
+                        before = torch.cuda.memory_allocated(self.device)
+                        parts.append(self.model.frame_head_chunk(flat[lo:lo + chunk], recompute))
+                        if recompute is None and not self.model.cfg.frame_head_recompute:
+                            # Activations kept for the backward grow by about the same amount per chunk.  When
+                            # the rest would not fit, the remaining chunks keep only their inputs and are run
+                            # again in the backward (the alternative is running out of memory).
+                            grown = torch.cuda.memory_allocated(self.device) - before
+                            free, _total = torch.cuda.mem_get_info(self.device)
+                            cached = torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+                            if grown * (n_chunks - i - 1) > 0.9 * (free + cached):
+                                recompute = True
+                                if not self._warned_recompute:
+                                    self._warned_recompute = True
+                                    LOG("WARN", f"frame head: activations of {n_chunks - i - 1} of {n_chunks} chunks "
+                                                "would not fit in device memory; recomputing them in the backward "
+                                                "(set model key frame_head_recompute to choose this up front)")
                         if progress:
                             self.logger.progress(ProgressRecord("Frame head: frames", min(b * t, lo + chunk), b * t,
                                                                 phase0, self._mark()))
