@@ -37,6 +37,8 @@ def main(argv=None) -> int:
     ap.add_argument("--nproc", type=int, required=True, help="trainer processes (= GPUs) to start")
     ap.add_argument("--pipelines", type=int, default=1,
                     help="with a frame_head_parallel configuration: pipelines running side by side")
+    ap.add_argument("--grace", type=float, default=15.0,
+                    help="seconds the remaining ranks get to finish after one rank has failed")
     a = ap.parse_args(argv[:split])
     cli_args: List[str] = argv[split + 1:]
     par = None
@@ -70,7 +72,26 @@ def main(argv=None) -> int:
     else:
         for r in range(a.nproc):
             start(["--worker_id", str(r), "--ddp-world-size", str(a.nproc)], f"rank {r}")
+    # Wait for all ranks; when one fails, the others (which would wait for it in their next collective) are stopped
+    # after a short grace period instead of being left hanging.
     code = 0
+    while any(p.poll() is None for p in procs):
+        failed = [p.returncode for p in procs if p.poll() is not None and p.returncode != 0]
+        if failed:
+            code = failed[0]
+            deadline = time.time() + a.grace
+            while time.time() < deadline and any(p.poll() is None for p in procs):
+                time.sleep(0.2)
+            for p in procs:
+                if p.poll() is None:
+                    p.terminate()
+            for p in procs:
+                try:
+                    p.wait(10)
+                except subprocess.TimeoutExpired:
+                    p.kill()
+            break
+        time.sleep(0.2)
     for p in procs:
         rc = p.wait()
         code = code or rc

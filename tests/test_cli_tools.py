@@ -184,3 +184,40 @@ def test_launcher_with_fault_tolerant_transport(tmp_path):
     for rank in (0, 1):
         assert f"[rank {rank}]" in r.stdout
     assert r.stdout.count("Step 2 took") == 2
+
+
+def test_launcher_stops_the_other_ranks_when_one_fails(tmp_path):
+    """Rank 1 gets a bad argument and exits at once; rank 0 would wait at the rendezvous for it: the launcher ends
+    it after the grace period and reports the failure."""
+    import socket
+    import time
+    cfg = presets.tiny()
+    cfg["micro_batch_size"], cfg["total_batch_size"] = 1, 2
+    run = tmp_path / "run.json"
+    run.write_text(json.dumps(cfg))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ep = {"ip": "127.0.0.1", "port": port}
+    par = {"frame_head_parallel": {"use_frame_head_parallel": False, "transport": "ccl", "ccl_rendezvous": ep},
+           "ddp_parallel": {"use_ddp_parallel": True, "transport": "ccl", "ccl_rendezvous": ep}}
+    parallel = tmp_path / "parallel.json"
+    parallel.write_text(json.dumps(par))
+    from fbamtrain_b200 import launch
+    real_popen = launch.subprocess.Popen
+    count = {"n": 0}
+
+    def popen(cmd, **kw):                       # second rank: an interpreter that fails immediately
+        count["n"] += 1
+        if count["n"] == 2:
+            cmd = [sys.executable, "-c", "import sys; print('boom'); sys.exit(3)"]
+        return real_popen(cmd, **kw)
+    launch.subprocess.Popen = popen
+    t0 = time.time()
+    try:
+        code = launch.main(["--nproc", "2", "--grace", "1", "--", "-c", str(run), "--parallel-config", str(parallel),
+                            "--synthetic", "--steps", "2", "--device", "cpu"])
+    finally:
+        launch.subprocess.Popen = real_popen
+    assert code == 3
+    assert time.time() - t0 < 60
