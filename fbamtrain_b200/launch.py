@@ -77,7 +77,7 @@ def main(argv=None) -> int:
     code = 0
     while any(p.poll() is None for p in procs):
         failed = [p.returncode for p in procs if p.poll() is not None and p.returncode != 0]
-        if failed:
+        if failed and master is None:        # (fault-tolerant ranks carry on without the one that failed)
             code = failed[0]
             deadline = time.time() + a.grace
             while time.time() < deadline and any(p.poll() is None for p in procs):
