@@ -263,6 +263,8 @@ def main(argv=None) -> int:
     t0 = time.time()
     history = run_training(trainer, max_steps=args.steps)
     trainer.close()
+    if dp is not None and hasattr(dp, "peer"):
+        dp.peer.leave()          # orderly departure: the remaining members re-form the group at their next gate
     if history:
         LOG("INFO", f"finished {len(history)} steps in {time.time() - t0:.1f} s; last loss {history[-1]['loss/train']:.4f}")
     return 0
