@@ -229,10 +229,10 @@ def main(argv=None) -> int:
             dp = DataParallel(mode=ddp.grad_reduce)
         else:
             from .parallel.ft_dp import FaultTolerantDataParallel
-            from .parallel.ftccl import FtPeer, Result
+            from .parallel.ftccl import FtPeer
+            # the peer announces itself to the master when the trainer attaches, i.e. after the model is built, so
+            # that a process joining a running group does not hold the members at their gate while it initialises
             peer = FtPeer(ddp.ftccl_master.ip, ddp.ftccl_master.port, device)
-            if peer.connect() != Result.SUCCESS:
-                LOG("FATAL", "cannot reach the ftccl master")
             dp = FaultTolerantDataParallel(peer, expected_world=args.ddp_world_size, min_world=1,
                                            mode="fused" if ddp.grad_reduce == "fused" else "allreduce")
 

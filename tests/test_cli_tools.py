@@ -260,3 +260,47 @@ def test_fault_tolerant_cli_ranks_outlive_an_early_leaver(tmp_path):
     assert "finished 2 steps" in outs[2]
     for r in (0, 1):
         assert "finished 6 steps" in outs[r] and "dropping step" not in outs[r], outs[r]
+
+
+def test_fault_tolerant_cli_admits_a_late_joiner(tmp_path):
+    """Two fault-tolerant CLI ranks are training when a third process starts: it builds its model, announces
+    itself, receives the shared state (adopting the group's step) and trains the remaining steps with them."""
+    import socket
+    import time
+    cfg = presets.tiny()
+    cfg["micro_batch_size"], cfg["total_batch_size"] = 1, 3
+    cfg["max_training_steps"] = 12
+    run = tmp_path / "run.json"
+    run.write_text(json.dumps(cfg))
+    ports = []
+    for _ in range(2):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            ports.append(s.getsockname()[1])
+    par = {"frame_head_parallel": {"use_frame_head_parallel": False, "transport": "ccl",
+                                   "ccl_rendezvous": {"ip": "127.0.0.1", "port": ports[0]}},
+           "ddp_parallel": {"use_ddp_parallel": True, "transport": "ftccl",
+                            "ftccl_master": {"ip": "127.0.0.1", "port": ports[1]}}}
+    parallel = tmp_path / "parallel.json"
+    parallel.write_text(json.dumps(par))
+    env = dict(os.environ, PYTHONPATH=ROOT, FBAMTRAIN_LOG_LEVEL="INFO")
+    master = subprocess.Popen([sys.executable, "-m", "fbamtrain_b200.cli", "--parallel-config", str(parallel),
+                               "--ftccl-master"], env=env, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    try:
+        time.sleep(1.0)
+        base = [sys.executable, "-m", "fbamtrain_b200.cli", "-c", str(run), "--parallel-config", str(parallel),
+                "--synthetic", "--device", "cpu", "--ddp-world-size", "3"]
+        procs = [subprocess.Popen(base + ["--worker_id", str(r)], env=env, stdout=subprocess.PIPE,
+                                  stderr=subprocess.STDOUT, text=True) for r in range(2)]
+        time.sleep(6.0)
+        procs.append(subprocess.Popen(base + ["--worker_id", "2"], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+        outs = [p.communicate(timeout=280)[0] for p in procs]
+    finally:
+        master.terminate()
+        master.wait(10)
+    assert all(p.returncode == 0 for p in procs), outs
+    assert "adopting shared-state revision" in outs[2] and "Step 11 took" in outs[2], outs[2]
+    assert "Step 0 took" not in outs[2]                       # it did not start from scratch
+    for r in (0, 1):
+        assert "Step 11 took" in outs[r] and "dropping step" not in outs[r], outs[r]
