@@ -269,7 +269,7 @@ def test_fault_tolerant_cli_admits_a_late_joiner(tmp_path):
     import time
     cfg = presets.tiny()
     cfg["micro_batch_size"], cfg["total_batch_size"] = 1, 3
-    cfg["max_training_steps"] = 12
+    cfg["max_training_steps"] = 20
     run = tmp_path / "run.json"
     run.write_text(json.dumps(cfg))
     ports = []
@@ -292,15 +292,21 @@ def test_fault_tolerant_cli_admits_a_late_joiner(tmp_path):
                 "--synthetic", "--device", "cpu", "--ddp-world-size", "3"]
         procs = [subprocess.Popen(base + ["--worker_id", str(r)], env=env, stdout=subprocess.PIPE,
                                   stderr=subprocess.STDOUT, text=True) for r in range(2)]
-        time.sleep(6.0)
+        # the third process starts once the group is demonstrably training (not after a fixed delay)
+        head = []
+        for line in procs[0].stdout:
+            head.append(line)
+            if "Step 1 took" in line:
+                break
         procs.append(subprocess.Popen(base + ["--worker_id", "2"], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.STDOUT, text=True))
         outs = [p.communicate(timeout=280)[0] for p in procs]
+        outs[0] = "".join(head) + outs[0]
     finally:
         master.terminate()
         master.wait(10)
     assert all(p.returncode == 0 for p in procs), outs
-    assert "adopting shared-state revision" in outs[2] and "Step 11 took" in outs[2], outs[2]
+    assert "adopting shared-state revision" in outs[2] and "Step 19 took" in outs[2], outs[2]
     assert "Step 0 took" not in outs[2]                       # it did not start from scratch
     for r in (0, 1):
-        assert "Step 11 took" in outs[r] and "dropping step" not in outs[r], outs[r]
+        assert "Step 19 took" in outs[r] and "dropping step" not in outs[r], outs[r]
