@@ -129,3 +129,17 @@ def test_shipped_sample_configurations_parse():
         assert RunConfiguration.from_json_file(p) is not None
     for p in pars:
         assert ParallelConfiguration.from_json_file(p) is not None
+
+
+def test_shipped_sample_configurations_parse():
+    """Every file under ``configs/`` is a valid run / parallel configuration."""
+    import glob
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs")
+    runs = sorted(glob.glob(os.path.join(root, "*.json")))
+    pars = sorted(glob.glob(os.path.join(root, "parallel", "*.json")))
+    assert runs and pars
+    for f in runs:
+        cfg = RunConfiguration.from_json_file(f)
+        assert cfg is not None and cfg.total_batch_size % cfg.micro_batch_size == 0, f
+    for f in pars:
+        assert ParallelConfiguration.from_json_file(f) is not None, f
