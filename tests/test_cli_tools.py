@@ -310,3 +310,51 @@ def test_fault_tolerant_cli_admits_a_late_joiner(tmp_path):
     assert "Step 0 took" not in outs[2]                       # it did not start from scratch
     for r in (0, 1):
         assert "Step 19 took" in outs[r] and "dropping step" not in outs[r], outs[r]
+
+
+def test_fault_tolerant_cli_survives_a_killed_rank(tmp_path):
+    """Host-side failure: one of three fault-tolerant CLI ranks is killed without a goodbye after its third step;
+    the other two notice at their next gate, re-form the group and finish all steps."""
+    import socket
+    import time
+    cfg = presets.tiny()
+    cfg["micro_batch_size"], cfg["total_batch_size"] = 1, 3
+    cfg["max_training_steps"] = 10
+    run = tmp_path / "run.json"
+    run.write_text(json.dumps(cfg))
+    ports = []
+    for _ in range(2):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            ports.append(s.getsockname()[1])
+    par = {"frame_head_parallel": {"use_frame_head_parallel": False, "transport": "ccl",
+                                   "ccl_rendezvous": {"ip": "127.0.0.1", "port": ports[0]}},
+           "ddp_parallel": {"use_ddp_parallel": True, "transport": "ftccl",
+                            "ftccl_master": {"ip": "127.0.0.1", "port": ports[1]}}}
+    parallel = tmp_path / "parallel.json"
+    parallel.write_text(json.dumps(par))
+    env = dict(os.environ, PYTHONPATH=ROOT, FBAMTRAIN_LOG_LEVEL="INFO")
+    master = subprocess.Popen([sys.executable, "-m", "fbamtrain_b200.cli", "--parallel-config", str(parallel),
+                               "--ftccl-master"], env=env, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    procs = []
+    try:
+        time.sleep(1.0)
+        base = [sys.executable, "-m", "fbamtrain_b200.cli", "-c", str(run), "--parallel-config", str(parallel),
+                "--synthetic", "--device", "cpu", "--ddp-world-size", "3"]
+        procs = [subprocess.Popen(base + ["--worker_id", str(r)], env=env, stdout=subprocess.PIPE,
+                                  stderr=subprocess.STDOUT, text=True) for r in range(3)]
+        for line in procs[2].stdout:
+            if "Step 2 took" in line:
+                break
+        procs[2].kill()                                    # this test's own child, by handle
+        procs[2].wait(30)
+        outs = [p.communicate(timeout=280)[0] for p in procs[:2]]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+        master.terminate()
+        master.wait(10)
+    assert all(p.returncode == 0 for p in procs[:2]), outs
+    for out in outs:
+        assert "finished 10 steps" in out, out
