@@ -64,6 +64,10 @@ class FaultTolerantDataParallel:
                 if name.endswith("__optimizer/step"):
                     continue
                 infos.append(TensorInfo(name, t))
+        if getattr(trainer, "data_state", None) is not None:
+            # where the group's dataset iterator stands: travels with the rest to whoever receives the state, but a
+            # difference in it alone is no reason for a transfer
+            infos.append(TensorInfo("data/iterator_state", trainer.data_state, allow_content_inequality=True))
         return infos
 
     def _sync_state(self, trainer, joining: bool = False) -> bool:

@@ -100,6 +100,9 @@ class Trainer:
                 self.optimizers[scope] = create_optimizer(ocfg, named, prefix)
         self.step_count = 0
         self.last_upload_event = None
+        # [valid, iterator RNG state] of the dataset iterator at the start of the current step: part of the shared
+        # state of a fault-tolerant group, so that a process admitted mid-run continues the group's data order
+        self.data_state = torch.zeros(2, dtype=torch.int64, device=self.device)
         if self.dp is not None:
             self.dp.attach(self)
 
@@ -529,9 +532,20 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
             trainer.cursor = DatasetCursorCommitter(cursor_path)
     limit = cfg.max_training_steps if max_steps is None else min(cfg.max_training_steps, trainer.step_count + max_steps)
     mc = cfg.model_config
+    shares_data_state = iterator is not None and hasattr(trainer.dp, "peer")     # fault-tolerant group on recordings
+    if shares_data_state:
+        valid, rng_state = (int(v) for v in trainer.data_state.tolist())
+        if valid:                              # admitted to a running group: continue ITS data order
+            from .data.iterator import DatasetIteratorState
+            iterator.restore(DatasetIteratorState(rng_state=rng_state & ((1 << 64) - 1), batch_size=global_batch))
+            LOG("INFO", "adopted the group's dataset iterator state")
     while trainer.step_count < limit:
         with gputx_range("fbamtrain::next_batch_wait"):
             assembled = None
+            if shares_data_state:
+                rng_now = iterator.cursor_checkpoint().rng_state
+                trainer.data_state.copy_(torch.tensor([1, rng_now - (1 << 64) if rng_now >= (1 << 63) else rng_now],
+                                                      dtype=torch.int64))
             if iterator is not None:
                 batch = iterator.next_batch()
                 if batch.tensors is not None:          # gathered by the native loader on the prefetch thread
@@ -563,6 +577,7 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
             trainer.save_checkpoint(iterator.checkpoint() if iterator is not None else None)
     trainer.logger.drain()
     if iterator is not None:
+        LOG("INFO", f"dataset iterator state at the end: {iterator.cursor_checkpoint().rng_state}")
         iterator.close()
     if prefetcher is not None:
         prefetcher.close()

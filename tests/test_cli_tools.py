@@ -270,6 +270,19 @@ def test_fault_tolerant_cli_admits_a_late_joiner(tmp_path):
     cfg = presets.tiny()
     cfg["micro_batch_size"], cfg["total_batch_size"] = 1, 3
     cfg["max_training_steps"] = 20
+    # on recordings: the newcomer must also continue the group's data order (one seeded iterator for the group)
+    import numpy as np
+    from fbamtrain_b200.data import ArrayRecording, SyntheticRecording
+    from fbamtrain_b200.tokenizer import Tokenizer
+    (tmp_path / "rec").mkdir()
+    for i in range(3):
+        r = SyntheticRecording(8, 16, 60, seed=i)
+        cells = np.stack([r.frame(t)[0] for t in range(60)])
+        ArrayRecording(cells, [r.frame(t)[1] for t in range(60)]).save(str(tmp_path / "rec" / f"r{i}.fbrec.npz"))
+    Tokenizer(list("abcdefghijklmnopqrstuvwxyz") + ["ab", "th"]).save(str(tmp_path / "tok.txt"))
+    cfg["tokenizer_file_path"] = "tok.txt"
+    cfg["train_data_config"]["recordings_directory_path"] = "rec"
+    cfg["model_config"]["action_vocab"] = 0
     run = tmp_path / "run.json"
     run.write_text(json.dumps(cfg))
     ports = []
@@ -289,7 +302,7 @@ def test_fault_tolerant_cli_admits_a_late_joiner(tmp_path):
     try:
         time.sleep(1.0)
         base = [sys.executable, "-m", "fbamtrain_b200.cli", "-c", str(run), "--parallel-config", str(parallel),
-                "--synthetic", "--device", "cpu", "--ddp-world-size", "3"]
+                "--device", "cpu", "--ddp-world-size", "3"]
         procs = [subprocess.Popen(base + ["--worker_id", str(r)], env=env, stdout=subprocess.PIPE,
                                   stderr=subprocess.STDOUT, text=True) for r in range(2)]
         # the third process starts once the group is demonstrably training (not after a fixed delay)
@@ -310,6 +323,9 @@ def test_fault_tolerant_cli_admits_a_late_joiner(tmp_path):
     assert "Step 0 took" not in outs[2]                       # it did not start from scratch
     for r in (0, 1):
         assert "Step 19 took" in outs[r] and "dropping step" not in outs[r], outs[r]
+    assert "adopted the group's dataset iterator state" in outs[2]
+    ends = [[ln.split(": ")[-1] for ln in o.splitlines() if "dataset iterator state at the end" in ln] for o in outs]
+    assert all(len(e) == 1 for e in ends) and ends[0] == ends[1] == ends[2], ends
 
 
 def test_fault_tolerant_cli_survives_a_killed_rank(tmp_path):
