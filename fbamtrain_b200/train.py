@@ -511,7 +511,12 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
                                           trainer.vocab, seed=cfg.train_data_config.iteration_seed + trainer.rank)
             own_source = True
     validation = None
-    restored = trainer.load_latest_checkpoint()
+    if hasattr(trainer.dp, "peer") and trainer.step_count > 0:
+        # admitted to a running fault-tolerant group: its state (received when the trainer attached) is newer than
+        # any checkpoint on disk
+        restored = None
+    else:
+        restored = trainer.load_latest_checkpoint()
     if iterator is not None and restored is not None and restored.batch_size:
         iterator.restore(restored)
     if source is not None and trainer.step_count and hasattr(source, "seek"):
