@@ -213,6 +213,10 @@ def main(argv=None) -> int:
 
     dp = None
     ddp = par.ddp_parallel if par is not None else None
+    if ddp is not None and ddp.use_ddp_parallel and ddp.grad_reduce == "fused" and device.type != "cuda":
+        # the fused reduction runs in kernels over peer GPU memory; CPU ranks take the sharded library path
+        LOG("WARN", "grad_reduce 'fused' needs GPUs; using 'zero1' on this device")
+        ddp.grad_reduce = "zero1"
     if env_rank is not None and int(env_world) > 1:
         import torch.distributed as dist
         from .parallel.dp import DataParallel
