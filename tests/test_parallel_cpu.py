@@ -259,3 +259,9 @@ def test_dp_outer_loop_on_recordings_matches_single_process_and_resumes(tmp_path
     assert summed == pytest.approx(single, rel=2e-4)
     for r in range(2):
         assert results[r][1][0] == pytest.approx(results[r][0][2], rel=1e-5)   # step 3 repeated after the resume
+    # the checkpoint written by two ZeRO-1 ranks resumes in ONE process (state is stored per parameter, the data
+    # order does not depend on the number of ranks): it repeats step 3 with the whole batch
+    tr = Trainer(_recordings_cfg(micro=2, total=4), device=torch.device("cpu"), working_dir=root)
+    alone = [h["loss/train"] for h in run_training(tr, max_steps=1)]
+    tr.close()
+    assert alone[0] == pytest.approx(results[0][0][2] + results[1][0][2], rel=2e-4)
