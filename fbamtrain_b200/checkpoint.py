@@ -22,6 +22,7 @@ from .data.iterator import DatasetIteratorState
 from .models.fbam import FbamModel, checkpoint_name_map
 from .optim.base import Optimizer
 from .utils import safetensors_io as st
+from .utils.logging import LOG
 
 _NAME_RE = re.compile(r"^checkpoint_step_(\d+)\.safetensors$")
 
@@ -151,7 +152,13 @@ class CheckpointManager:
         for opt in optimizers.values():
             as_i64 = {k: (v.view(torch.int64) if v.dtype == torch.uint64 else v).to(dev) for k, v in tensors.items()
                       if k.startswith(opt.prefix + "/")}
-            opt.load_state_tensors(as_i64)
+            if as_i64:
+                opt.load_state_tensors(as_i64)
+            else:
+                # a model-only file (e.g. written by the pipeline trainer, whose optimizer state lives in files of
+                # its own): moments start from zero, the fp32 masters from the parameters just loaded
+                LOG("WARN", f"{path} holds no state under '{opt.prefix}/': optimizer moments start from zero")
+                opt.reset_masters_from_params()
             opt.set_step(step)
         ds = DatasetIteratorState()
         if "dataset_rng_state" in tensors:

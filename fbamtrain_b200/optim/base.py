@@ -42,6 +42,14 @@ class Optimizer:
     def set_step(self, step: int) -> None:
         self.step_count = int(step)
 
+    @torch.no_grad()
+    def reset_masters_from_params(self) -> None:
+        """After parameters were overwritten from outside (a model-only checkpoint): the fp32 master copies follow."""
+        for name, p in self.named_params:
+            master = self.state.get(name, {}).get("master")
+            if master is not None:
+                master.copy_(p.detach().float())
+
     def step(self) -> None:
         raise NotImplementedError
 

@@ -128,6 +128,10 @@ class MuonWithAuxAdam(Optimizer):
         self.muon.set_step(step)
         self.adam.set_step(step)
 
+    def reset_masters_from_params(self) -> None:
+        self.muon.reset_masters_from_params()
+        self.adam.reset_masters_from_params()
+
     def step(self) -> None:
         self.step_count += 1
         self.muon.step()

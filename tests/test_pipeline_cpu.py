@@ -190,6 +190,22 @@ def _checkpoint_worker(rank, world, port, q, directory):
     again = [tr2.train_step(*batches[k]) for k in (3, 4)]
     plain = FbamModel(cfg.model_config, 32)
     load_model_params(plain, st.load_file(path))            # strict names, dtypes and shapes
+    if rank == 0:
+        # the single-process trainer resumes from the pipeline's model file (optimizer moments restart)
+        import copy
+        from fbamtrain_b200 import Trainer
+        d2 = copy.deepcopy(d)
+        d2["checkpointing"] = {"checkpoint_interval": 100, "checkpoint_directory": directory,
+                               "resume_behavior": "load_latest"}
+        d2["model_config"]["action_vocab"] = 32
+        single = Trainer(RunConfiguration.from_json(d2), device=torch.device("cpu"), working_dir="/")
+        single.load_latest_checkpoint()
+        assert single.step_count == 3
+        got = dict(single.model.named_parameters())
+        for n, p in plain.named_parameters():
+            assert torch.equal(got[n].detach(), p.detach()), n
+        single.train_step(*batches[3])
+        single.close()
     q.put((rank, first, again, sorted(os.listdir(directory))))
     dist.destroy_process_group()
 
