@@ -135,6 +135,7 @@ def test_cli_pipeline_reads_recordings(tmp_path):
     cfg["micro_batch_size"], cfg["total_batch_size"] = 2, 4
     cfg["tokenizer_file_path"] = "tok.txt"
     cfg["train_data_config"]["recordings_directory_path"] = "rec"
+    cfg["checkpointing"] = {"checkpoint_interval": 2, "checkpoint_directory": "ck", "resume_behavior": "load_latest"}
     run = tmp_path / "run.json"
     run.write_text(json.dumps(cfg))
     with socket.socket() as s:
@@ -155,6 +156,16 @@ def test_cli_pipeline_reads_recordings(tmp_path):
     outs = [p.communicate(timeout=300)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), outs
     assert "Step 1 took" in outs[1] and "loss/train" in outs[1]
+    # a second launch resumes from the checkpoint written after step 2 (model gathered from the stages, optimizer
+    # state per position, dataset iterator state) and continues with step 2
+    base[base.index("--steps") + 1] = "1"
+    procs = [subprocess.Popen(base + ["--worker_id", "0"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                              env=env),
+             subprocess.Popen(base + ["--worker_id", "1", "--master"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                              text=True, env=env)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    assert "Resumed from" in outs[1] and "Step 2 took" in outs[1] and "Step 0 took" not in outs[1], outs[1]
 
 
 def test_launcher_with_fault_tolerant_transport(tmp_path):
