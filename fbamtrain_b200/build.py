@@ -28,6 +28,15 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread"]
 
 
+def _feature_flags() -> list:
+    """Optional code paths that are compiled in on request (use with --force, then rebuild without to go back):
+    ``FBAMTRAIN_RS_ROW_STORES=1`` — the row-store variant of the GEMM -> reduce-scatter epilogue."""
+    flags = []
+    if os.environ.get("FBAMTRAIN_RS_ROW_STORES", "0") == "1":
+        flags.append("-DFBAM_RS_ROW_STORES=1")
+    return flags
+
+
 def _nvcc() -> str:
     for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and os.path.exists(cand):
@@ -58,7 +67,7 @@ def build_kernels(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_time):
-            jobs.append(([nvcc] + NVCC_FLAGS + ["-I", CSRC, "-c", src, "-o", obj], obj + ".log"))
+            jobs.append(([nvcc] + NVCC_FLAGS + _feature_flags() + ["-I", CSRC, "-c", src, "-o", obj], obj + ".log"))
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(lambda j: _compile(*j), jobs))

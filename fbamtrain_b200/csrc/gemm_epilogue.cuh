@@ -3,6 +3,14 @@
 #include "gemm_tcgen05.h"
 #include <cuda_bf16.h>
 
+// The row-store variant of the reduce-scatter epilogue (GemmParams::rs_row_stores) is compiled in only on request
+// (-DFBAM_RS_ROW_STORES=1, `FBAMTRAIN_RS_ROW_STORES=1 python -m fbamtrain_b200.build --force`): it raises the
+// register count of every kernel that includes this epilogue, and until it has been measured the default build
+// keeps the kernels exactly as they were profiled.  Without it the flag is ignored (default store pattern).
+#ifndef FBAM_RS_ROW_STORES
+#define FBAM_RS_ROW_STORES 0
+#endif
+
 namespace gemm_epi {
 
 // erf via Abramowitz-Stegun 7.1.26 (|error| < 1.5e-7, far below bf16 resolution): the epilogue must not cost
@@ -114,6 +122,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.rs_out[owner]) +
                                  ((long long)(p.rs_slot_plus1 - 1) * p.rs_rows_per_rank + (m - owner * p.rs_rows_per_rank)) *
                                      p.ldd + n0;
+#if FBAM_RS_ROW_STORES
             if (full_vec && p.rs_row_stores != 0 && (p.M & 31) == 0 && (p.rs_rows_per_rank & 31) == 0) {
               // Every lane of the warp is here (rows of a warp are 32 consecutive ones and M is a multiple of 32),
               // and the four rows of a lane quad belong to the same owner.  4 x 4 transpose of the 16-byte pieces
@@ -142,7 +151,9 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
   #pragma unroll
               for (int q = 0; q < 4; ++q)             // row (own row - j + q), columns [n0 + 8j, n0 + 8j + 8)
                 *reinterpret_cast<uint4*>(out + (long long)(q - j) * p.ldd + 8 * j) = piece[q];
-            } else if (full_vec) {
+            } else
+#endif
+            if (full_vec) {
   #pragma unroll
               for (int j = 0; j < 32; j += 8) {
                 __align__(16) __nv_bfloat162 h[4];

@@ -461,6 +461,9 @@ extern "C" void fbam_gemm_params_layout(long long* out) {
   out[7] = (long long)sizeof(ConvGeom);
 }
 
+// 1 when the row-store variant of the reduce-scatter epilogue was compiled in (see gemm_epilogue.cuh).
+extern "C" int fbam_has_rs_row_stores() { return FBAM_RS_ROW_STORES; }
+
 extern "C" int fbam_set_reserved_sms(int n) {
   const int old = g_fbam_reserved_sms;
   g_fbam_reserved_sms = n < 0 ? 0 : n;
