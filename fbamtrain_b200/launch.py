@@ -6,7 +6,8 @@ non-zero exit code.
     python -m fbamtrain_b200.launch --nproc 8 --pipelines 1 -- -c run.json --parallel-config \
         configs/parallel/frame_head_parallel.json
 
-Everything after ``--`` goes to ``fbamtrain_b200.cli`` unchanged; the launcher adds ``--worker_id``, ``--world-size`` /
+When a rank fails, the others get ``--grace`` seconds to finish and are then stopped (ranks of a fault-tolerant job
+carry on instead).  Everything after ``--`` goes to ``fbamtrain_b200.cli`` unchanged; the launcher adds ``--worker_id``, ``--world-size`` /
 ``--ddp-world-size`` and, for pipelines, ``--master`` on each pipeline's first action-model rank — what the
 reference's launcher script does for its binary (reference: ``scripts/run_frame_head_parallel.sh:1-112``).
 """
