@@ -13,136 +13,197 @@ import random
 import pytest
 
 
-class Bar:
-    def __init__(self, need=1): self.need, self.arrived, self.completions = need, 0, 0
-    def arrive(self):
+class Barrier:
+    """An mbarrier: ``need`` arrivals complete a phase; ``test(parity)`` is ``mbarrier.try_wait.parity``."""
+
+    def __init__(self, need: int = 1):
+        self.need, self.arrived, self.completions = need, 0, 0
+
+    def arrive(self) -> None:
         self.arrived += 1
-        if self.arrived == self.need: self.arrived = 0; self.completions += 1
-    def test(self, parity): return (self.completions & 1) != parity
+        if self.arrived == self.need:
+            self.arrived = 0
+            self.completions += 1
 
-def run(nkb0, nkb1, seed):
-    rnd = random.Random(seed)
-    nkb = max(nkb0, nkb1)
-    nk = [nkb0, nkb1]
-    B = {n: Bar() for n in ("q_full","k_full","k_empty","v_full","v_empty")}
-    for g in range(2):
-        B[f"s_full{g}"]=Bar(); B[f"p_ready{g}"]=Bar(1); B[f"pv_full{g}"]=Bar()   # softmax group modelled as one agent
-    pending=[]   # (time, action)
-    now=[0.0]
-    mma_busy_until=[0.0]
-    state={"k_in_smem":-1,"v_in_smem":-1,"k_loading":None,"v_loading":None,
-           "S":[-1,-1],"S_read":[-1,-1],"O":[-1,-1],"O_read":[-1,-1],"P":[-1,-1],
-           "s_done":[-1,-1],"pv_done":[-1,-1], "s_inflight":[None,None], "pv_inflight":[None,None]}
-    errors=[]
-    def at(t,f): pending.append((t,rnd.random(),f))
-    def load(kind,kb):
-        # hazard: previous block must have been fully consumed by the MMAs that read it
-        if kind=="k":
-            for g in range(2):
-                if kb-1 < nk[g] and kb-1>=0 and state["s_done"][g] < kb-1: errors.append(f"K overwritten before S{g}({kb-1}) done")
-        else:
-            for g in range(2):
-                if kb-1 < nk[g] and kb-1>=0 and state["pv_done"][g] < kb-1: errors.append(f"V overwritten before PV{g}({kb-1}) done")
-        def done():
-            state[f"{kind}_in_smem"]=kb; B[f"{kind}_full"].arrive()
-        at(now[0]+rnd.uniform(0.5,3.0), done)
-    def issue_mma(kind,g,kb):
-        start=max(now[0], mma_busy_until[0]); end=start+rnd.uniform(0.2,1.0); mma_busy_until[0]=end
-        if kind=="s":
-            if state["k_in_smem"]!=kb: errors.append(f"S{g}({kb}) issued with K block {state['k_in_smem']}")
-            if state["S_read"][g] < kb-1: errors.append(f"S{g}({kb}) overwrites unread S({kb-1})")
-            def done(): state["S"][g]=kb; state["s_done"][g]=kb
-        else:
-            if state["v_in_smem"]!=kb: errors.append(f"PV{g}({kb}) issued with V block {state['v_in_smem']}")
-            if state["P"][g]!=kb: errors.append(f"PV{g}({kb}) issued with P block {state['P'][g]}")
-            if state["O_read"][g] < kb-1: errors.append(f"PV{g}({kb}) overwrites unread O({kb-1})")
-            def done(): state["O"][g]=kb; state["pv_done"][g]=kb
-        at(end, done)
-        return end
-    def commit(bar):
-        t=mma_busy_until[0]   # arrives when everything issued so far has completed
-        at(max(t,now[0])+1e-6, lambda: B[bar].arrive())
+    def test(self, parity: int) -> bool:
+        return (self.completions & 1) != parity
 
-    def mma_thread():
-        if nkb>0:
-            load("k",0); load("v",0)
-            yield ("wait","k_full",0)   # q_full folded in
-            if 0<nk[0]: issue_mma("s",0,0); commit("s_full0")
-            if 0<nk[1]: issue_mma("s",1,0); commit("s_full1")
-            commit("k_empty")
+
+class Simulation:
+    """State shared by the three agents plus the event queue of asynchronous completions."""
+
+    def __init__(self, blocks_per_tile, seed: int, skip_k_empty_wait: bool = False):
+        self.rnd = random.Random(seed)
+        self.nk = list(blocks_per_tile)                  # key blocks tile 0 / tile 1 attends to (causal: differ)
+        self.nkb = max(self.nk)
+        self.skip_k_empty_wait = skip_k_empty_wait       # fault injection for the self-test of the model
+        names = ["k_full", "k_empty", "v_full", "v_empty"] + [f"{n}{g}" for n in ("s_full", "p_ready", "pv_full")
+                                                                for g in range(2)]
+        self.bars = {n: Barrier() for n in names}        # a softmax group is modelled as one arriving agent
+        self.now = 0.0
+        self.mma_busy_until = 0.0
+        self.pending = []                                # (time, tie-break, action)
+        self.errors = []
+        self.k_in_smem = self.v_in_smem = -1
+        self.s_block = [-1, -1]                          # block whose S / O / P currently sits in TMEM / smem
+        self.o_block = [-1, -1]
+        self.p_block = [-1, -1]
+        self.s_read = [-1, -1]                           # last block whose S / O the softmax group has read
+        self.o_read = [-1, -1]
+        self.s_done = [-1, -1]                           # last block whose S / P·V MMAs have completed
+        self.pv_done = [-1, -1]
+
+    def at(self, time: float, action) -> None:
+        self.pending.append((time, self.rnd.random(), action))
+
+    # -- what the issuing thread does ------------------------------------------------------------------------
+    def load(self, kind: str, kb: int) -> None:
+        done = self.s_done if kind == "k" else self.pv_done
+        for g in range(2):
+            if 0 <= kb - 1 < self.nk[g] and done[g] < kb - 1:
+                self.errors.append(f"{kind.upper()} block {kb - 1} overwritten before tile {g}'s MMAs read it")
+
+        def landed():
+            if kind == "k":
+                self.k_in_smem = kb
+            else:
+                self.v_in_smem = kb
+            self.bars[f"{kind}_full"].arrive()
+        self.at(self.now + self.rnd.uniform(0.5, 3.0), landed)
+
+    def issue(self, kind: str, g: int, kb: int) -> None:
+        start = max(self.now, self.mma_busy_until)
+        end = start + self.rnd.uniform(0.2, 1.0)
+        self.mma_busy_until = end
+        if kind == "s":
+            if self.k_in_smem != kb:
+                self.errors.append(f"S{g}({kb}) issued while K holds block {self.k_in_smem}")
+            if self.s_read[g] < kb - 1:
+                self.errors.append(f"S{g}({kb}) overwrites S({kb - 1}) before it was read")
+
+            def done():
+                self.s_block[g] = self.s_done[g] = kb
+        else:
+            if self.v_in_smem != kb:
+                self.errors.append(f"PV{g}({kb}) issued while V holds block {self.v_in_smem}")
+            if self.p_block[g] != kb:
+                self.errors.append(f"PV{g}({kb}) issued while P holds block {self.p_block[g]}")
+            if self.o_read[g] < kb - 1:
+                self.errors.append(f"PV{g}({kb}) overwrites O({kb - 1}) before it was read")
+
+            def done():
+                self.o_block[g] = self.pv_done[g] = kb
+        self.at(end, done)
+
+    def commit(self, bar: str) -> None:
+        """tcgen05.commit: the barrier is arrived on once everything issued so far has completed."""
+        self.at(max(self.mma_busy_until, self.now) + 1e-6, self.bars[bar].arrive)
+
+    # -- the agents (generators that yield what they wait for) -------------------------------------------------
+    def mma_thread(self):
+        nk, nkb = self.nk, self.nkb
+        if nkb > 0:
+            self.load("k", 0)
+            self.load("v", 0)
+            yield ("wait", "k_full", 0)                  # (the wait for Q is folded in)
+            for g in range(2):
+                if 0 < nk[g]:
+                    self.issue("s", g, 0)
+                    self.commit(f"s_full{g}")
+            self.commit("k_empty")
         for kb in range(nkb):
-            ph=kb&1; more=kb+1<nkb
+            ph, more = kb & 1, kb + 1 < nkb
             if more:
-                yield ("wait","k_empty",ph); load("k",kb+1)
-            yield ("wait","v_full",ph)
-            if kb<nk[0]:
-                yield ("wait","p_ready0",ph); issue_mma("pv",0,kb); commit("pv_full0")
+                if not self.skip_k_empty_wait:
+                    yield ("wait", "k_empty", ph)
+                self.load("k", kb + 1)
+            yield ("wait", "v_full", ph)
+            if kb < nk[0]:
+                yield ("wait", "p_ready0", ph)
+                self.issue("pv", 0, kb)
+                self.commit("pv_full0")
             if more:
-                yield ("wait","k_full",ph^1)
-                if kb+1<nk[0]: issue_mma("s",0,kb+1); commit("s_full0")
-            if kb<nk[1]:
-                yield ("wait","p_ready1",ph); issue_mma("pv",1,kb); commit("pv_full1")
-            commit("v_empty")
+                yield ("wait", "k_full", ph ^ 1)
+                if kb + 1 < nk[0]:
+                    self.issue("s", 0, kb + 1)
+                    self.commit("s_full0")
+            if kb < nk[1]:
+                yield ("wait", "p_ready1", ph)
+                self.issue("pv", 1, kb)
+                self.commit("pv_full1")
+            self.commit("v_empty")
             if more:
-                if kb+1<nk[1]: issue_mma("s",1,kb+1); commit("s_full1")
-                commit("k_empty")
-                yield ("wait","v_empty",ph); load("v",kb+1)
-    def softmax(g):
-        for kb in range(nk[g]):
-            yield ("wait",f"s_full{g}",kb&1)
-            if state["S"][g]!=kb: errors.append(f"softmax{g} reads S block {state['S'][g]} expecting {kb}")
-            yield ("sleep", rnd.uniform(0.3,2.5))
-            state["S_read"][g]=kb
-            if kb>0 and state["pv_done"][g] < kb-1: errors.append(f"softmax{g} overwrites P({kb-1}) before PV done")
-            state["P"][g]=kb
-            B[f"p_ready{g}"].arrive()
-            yield ("wait",f"pv_full{g}",kb&1)
-            if state["O"][g]!=kb: errors.append(f"softmax{g} reads O block {state['O'][g]} expecting {kb}")
-            yield ("sleep", rnd.uniform(0.1,0.8))
-            state["O_read"][g]=kb
-    agents={"mma":mma_thread(),"sm0":softmax(0),"sm1":softmax(1)}
-    waiting={}; sleeping={}
-    def step(name):
-        try:
-            req=next(agents[name])
-        except StopIteration:
-            del agents[name]; return
-        if req[0]=="wait": waiting[name]=(req[1],req[2])
-        else: sleeping[name]=now[0]+req[1]
-    for n in list(agents): step(n)
-    guard=0
-    while agents:
-        guard+=1
-        if guard>100000: return ["livelock"]
-        progressed=False
-        for n,(bar,par) in list(waiting.items()):
-            if B[bar].test(par):
-                del waiting[n]; step(n); progressed=True
-        for n,t in list(sleeping.items()):
-            if t<=now[0]:
-                del sleeping[n]; step(n); progressed=True
-        if progressed: continue
-        times=[t for t,_,_ in pending]+list(sleeping.values())
-        if not times:
-            return errors+[f"DEADLOCK waiting={waiting} completions={{k:v.completions for k,v in B.items()}}".replace("{k:v.completions for k,v in B.items()}", str({k:v.completions for k,v in B.items()}))]
-        tmin=min(times); now[0]=tmin
-        due=[p for p in pending if p[0]<=tmin]; due.sort()
-        for p in due:
-            pending.remove(p); p[2]()
-    return errors
+                if kb + 1 < nk[1]:
+                    self.issue("s", 1, kb + 1)
+                    self.commit("s_full1")
+                self.commit("k_empty")
+                yield ("wait", "v_empty", ph)
+                self.load("v", kb + 1)
+
+    def softmax_group(self, g: int):
+        for kb in range(self.nk[g]):
+            yield ("wait", f"s_full{g}", kb & 1)
+            if self.s_block[g] != kb:
+                self.errors.append(f"softmax {g} reads S of block {self.s_block[g]}, expected {kb}")
+            yield ("sleep", self.rnd.uniform(0.3, 2.5))
+            self.s_read[g] = kb
+            if kb > 0 and self.pv_done[g] < kb - 1:
+                self.errors.append(f"softmax {g} overwrites P({kb - 1}) before its P·V completed")
+            self.p_block[g] = kb
+            self.bars[f"p_ready{g}"].arrive()
+            yield ("wait", f"pv_full{g}", kb & 1)
+            if self.o_block[g] != kb:
+                self.errors.append(f"softmax {g} reads O of block {self.o_block[g]}, expected {kb}")
+            yield ("sleep", self.rnd.uniform(0.1, 0.8))
+            self.o_read[g] = kb
+
+    # -- scheduler -------------------------------------------------------------------------------------------
+    def run(self):
+        agents = {"mma": self.mma_thread(), "softmax0": self.softmax_group(0), "softmax1": self.softmax_group(1)}
+        waiting, sleeping = {}, {}
+
+        def advance(name):
+            try:
+                request = next(agents[name])
+            except StopIteration:
+                del agents[name]
+                return
+            if request[0] == "wait":
+                waiting[name] = request[1:]
+            else:
+                sleeping[name] = self.now + request[1]
+
+        for name in list(agents):
+            advance(name)
+        for _ in range(100000):
+            if not agents:
+                return self.errors
+            ready = [n for n, (bar, parity) in waiting.items() if self.bars[bar].test(parity)]
+            ready += [n for n, t in sleeping.items() if t <= self.now]
+            if ready:
+                for name in ready:
+                    waiting.pop(name, None)
+                    sleeping.pop(name, None)
+                    advance(name)
+                continue
+            times = [t for t, _, _ in self.pending] + list(sleeping.values())
+            if not times:
+                counts = {k: b.completions for k, b in self.bars.items()}
+                return self.errors + [f"deadlock: waiting {waiting}, completed phases {counts}"]
+            self.now = min(times)
+            due = sorted(p for p in self.pending if p[0] <= self.now)
+            for item in due:
+                self.pending.remove(item)
+                item[2]()
+        return self.errors + ["no progress"]
 
 
-@pytest.mark.parametrize("nkb0,nkb1", [(1, 1), (2, 2), (3, 3), (8, 8), (1, 2), (3, 4), (7, 8), (2, 0), (5, 0), (1, 0),
-                                       (4, 5)])
-def test_two_tile_attention_protocol_has_no_deadlock_or_hazard(nkb0, nkb1):
+@pytest.mark.parametrize("blocks", [(1, 1), (2, 2), (3, 3), (8, 8), (1, 2), (3, 4), (7, 8), (2, 0), (5, 0), (1, 0), (4, 5)])
+def test_two_tile_attention_protocol_has_no_deadlock_or_hazard(blocks):
     for seed in range(60):
-        assert run(nkb0, nkb1, seed) == [], (nkb0, nkb1, seed)
+        assert Simulation(blocks, seed).run() == [], (blocks, seed)
 
 
 def test_the_model_notices_a_missing_wait():
-    """The checks are live: dropping the wait that protects the K buffer is reported."""
-    import types
-    source = open(__file__).read().replace('yield ("wait","k_empty",ph); load("k",kb+1)', 'load("k",kb+1)')
-    broken = types.ModuleType("broken_protocol")
-    exec(compile(source, "broken_protocol", "exec"), broken.__dict__)
-    assert any(broken.run(3, 4, seed) for seed in range(20))
+    """The checks are live: without the wait that protects the K buffer an early overwrite is reported."""
+    assert any(Simulation((3, 4), seed, skip_k_empty_wait=True).run() for seed in range(20))
