@@ -79,15 +79,17 @@ class FrameHead(nn.Module):
         """``cells`` int32 ``(N, rows*cols, 3)`` → ``(N, n_embed)``."""
         cfg = self.cfg
         n = cells.shape[0]
-        x = self.embed(cells).view(n, cfg.frame_rows, cfg.frame_cols, cfg.embed_dim)
         fusable = (len(self.block) == 0 and cfg.frame_head_reduction_strategy == "mean" and
                    len(self.downsample_block) > 0 and
                    all(b.ln is None and b.mode == "dilated" and b.stride == 2 for b in self.downsample_block))
-        if fusable:   # conv → GELU chain straight into the pooled frame vector
-            blocks = self.downsample_block
-            v = ops.conv_gelu_stack_pool(x, [b.conv_weight for b in blocks], 2, [b.padding for b in blocks],
-                                         [b.dilation for b in blocks])
+        if fusable:   # cells → (embedding + first conv as table look-ups) → conv → GELU chain → pooled frame vector
+            blocks, emb = self.downsample_block, self.embed
+            v = ops.cell_conv_gelu_stack_pool(cells, emb.codepoint_embedding, emb.position_embedding, emb.colour,
+                                              cfg.frame_rows, cfg.frame_cols, emb.out_dtype,
+                                              [b.conv_weight for b in blocks], 2, [b.padding for b in blocks],
+                                              [b.dilation for b in blocks])
             return self.proj(v) if self.proj is not None else v
+        x = self.embed(cells).view(n, cfg.frame_rows, cfg.frame_cols, cfg.embed_dim)
         for blk in self.downsample_block:
             x = blk(x)
         if len(self.block) == 0 and cfg.frame_head_reduction_strategy == "mean":

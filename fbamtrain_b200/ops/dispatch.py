@@ -143,6 +143,26 @@ def conv_gelu_stack_pool(x, weights, stride: int, paddings, dilations):
     return global_avg_pool_nhwc(x)
 
 
+def embconv_enabled() -> bool:
+    """``FBAMTRAIN_EMBCONV=0`` keeps the cell embedding and the first convolution as separate kernels."""
+    return os.environ.get("FBAMTRAIN_EMBCONV", "1") != "0"
+
+
+def cell_conv_gelu_stack_pool(cells, cp_embed, pos_embed, colour_embed, rows: int, cols: int, out_dtype, weights,
+                              stride: int, paddings, dilations):
+    """``cells (N, rows·cols, 3)`` → cell embedding → ``[conv3x3 (no bias) → GELU] x n`` → mean over positions
+    ``(N, C_last)``.  On the native path the embedding and the first convolution are fused into table look-ups
+    (``ops/embconv.py``) when the shapes allow; otherwise this is the composition of the separate ops."""
+    if (_native(cells, out_dtype, family="conv2d") and embconv_enabled() and
+            all(w.shape[3] % 64 == 0 for w in weights)):
+        from . import embconv
+        if embconv.supported(cells, cp_embed, weights[0]):
+            from .native_ops import cell_conv_gelu_stack_pool as f
+            return f(cells, cp_embed, pos_embed, colour_embed, rows, cols, weights, stride, paddings, dilations)
+    x = cell_embed(cells, cp_embed, pos_embed, colour_embed, out_dtype).view(cells.shape[0], rows, cols, -1)
+    return conv_gelu_stack_pool(x, weights, stride, paddings, dilations)
+
+
 def linear(x, weight, bias: Optional[torch.Tensor] = None, act: str = "none"):
     if _native(x, family="gemm"):
         from .native_ops import linear as f

@@ -373,6 +373,67 @@ class _ConvGeluStackPool(torch.autograd.Function):
         return (dx, None, None, None, *dws)
 
 
+class _CellConvGeluStackPool(torch.autograd.Function):
+    """``cells → cell embedding → [conv3x3 → GELU] x n → mean over positions`` where the embedding and the first
+    convolution are one table look-up (``ops/embconv.py``): the embedding tensor, the first layer's data gradient and
+    the scatter of that gradient into the tables never exist.  Layers 2..n run as in :class:`_ConvGeluStackPool`; the
+    data-gradient convolution of layer 2 delivers ``dZ₁`` (its epilogue multiplies by gelu'(z₁)), which three
+    reductions turn into the gradients of the tables and of the first filter."""
+
+    @staticmethod
+    def forward(ctx, cells, cp_embed, pos_embed, colour, rows, cols, stride, paddings, dilations, *weights):
+        from . import embconv
+        cells = cells.contiguous()
+        y1, z1, feat = embconv.first_layer_forward_native(cells, cp_embed, pos_embed, colour, weights[0], rows, cols,
+                                                          stride, paddings[0], dilations[0])
+        ys, zs = [y1], [z1]
+        for w, pad, dil in zip(weights[1:], paddings[1:], dilations[1:]):
+            oh, ow = conv_out_hw(ys[-1].shape[1], ys[-1].shape[2], stride, pad, dil)
+            z = debug.fresh((cells.shape[0], oh, ow, w.shape[0]), BF16, cells.device)
+            ys.append(conv2d_fprop(ys[-1], w, stride, pad, dil, act="gelu", preact_out=z))
+            zs.append(z)
+        last = ys[-1]
+        n, h, wd, c = last.shape
+        vec = torch.empty(n, c, dtype=BF16, device=cells.device)
+        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(last), nv.ptr(vec), C.c_longlong(n), h * wd, c, 0, None,
+                                              nv.stream_ptr()), "fbam_global_avgpool")
+        ctx.save_for_backward(cells, feat, cp_embed, pos_embed, colour, *ys[:-1], *zs, *weights)
+        ctx.cfg = (rows, cols, stride, tuple(paddings), tuple(dilations), len(weights))
+        return vec
+
+    @staticmethod
+    def backward(ctx, dvec):
+        from . import embconv
+        from .conv_wgrad import conv2d_wgrad
+        rows, cols, stride, paddings, dilations, nb = ctx.cfg
+        saved = ctx.saved_tensors
+        cells, feat, cp_embed, pos_embed, colour = saved[:5]
+        rest = saved[5:]
+        ys, zs, weights = rest[:nb - 1], rest[nb - 1:2 * nb - 1], rest[2 * nb - 1:]     # ys[i] = input of layer i + 1
+        z_last = zs[-1]
+        n, h, wd, c = z_last.shape
+        dz = torch.empty_like(z_last)
+        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(dvec.contiguous()), nv.ptr(dz), C.c_longlong(n), h * wd, c, 1,
+                                              nv.ptr(z_last), nv.stream_ptr()), "fbam_global_avgpool")
+        dws = [None] * nb
+        for i in range(nb - 1, 0, -1):
+            x_in, w = ys[i - 1], weights[i]
+            if ctx.needs_input_grad[9 + i]:
+                dws[i] = conv2d_wgrad(x_in, dz, w.shape, stride, paddings[i], dilations[i])
+            dz = conv2d_dgrad(dz, w, (x_in.shape[1], x_in.shape[2]), stride, paddings[i], dilations[i],
+                              gelu_grad_in=zs[i - 1])
+        d_cp, d_pos, d_col, dws[0] = embconv.first_layer_backward_native(
+            cells, feat, dz, cp_embed, pos_embed, colour, weights[0], rows, cols, stride, paddings[0], dilations[0])
+        return (None, d_cp.to(cp_embed.dtype), d_pos.to(pos_embed.dtype), d_col.to(colour.dtype), None, None, None, None,
+                None, *dws)
+
+
+def cell_conv_gelu_stack_pool(cells, cp_embed, pos_embed, colour, rows, cols, weights, stride, paddings, dilations):
+    _need_bf16(*weights)
+    return _CellConvGeluStackPool.apply(cells, cp_embed, pos_embed, colour, rows, cols, stride, tuple(paddings),
+                                        tuple(dilations), *weights)
+
+
 def conv_gelu_stack_pool(x, weights, stride, paddings, dilations):
     _need_bf16(x, *weights)
     return _ConvGeluStackPool.apply(x.contiguous(), stride, tuple(paddings), tuple(dilations), *weights)

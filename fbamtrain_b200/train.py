@@ -26,6 +26,7 @@ from .config import ParallelConfiguration, RunConfiguration
 from .data import (Batch, DatasetCursorCommitter, DatasetCursorSnapshot, RecordingDatasetIterator,
                    PrefetchingSource, StreamTokenizationContext, SyntheticBatchSource, consume_next_token, prepare_cell_states)
 from .models import FbamModel
+from .ops import embconv
 from .optim import AdamwOptimizer, MuonWithAuxAdam, Optimizer, create_optimizer
 from .tokenizer import Tokenizer
 from .utils import flops, plan
@@ -269,6 +270,9 @@ class Trainer:
             start_ev.record()
         self.zero_grad()
         self.ring.begin(step)
+        # parameter-derived tables of the fused first frame-head layer are valid until the optimizer runs
+        self._table_epoch = getattr(self, "_table_epoch", 0) + 1
+        embconv.set_cache_token((id(self), self._table_epoch))
         total = None
         for k in range(self.grad_accum_steps):
             if self.dp is not None and k == self.grad_accum_steps - 1:
@@ -284,6 +288,7 @@ class Trainer:
                 self.optimizers["action_model"].step()
             with gputx_range("fbamtrain::frame_head_optim_step"):
                 self.optimizers["frame_head"].step()
+        embconv.set_cache_token(None)
         loss_ev = self.ring.finalize(step)
         self._loss_events[step % len(self._loss_events)] = (step, loss_ev)
         if self._cuda:
@@ -319,6 +324,7 @@ class Trainer:
     def validation_loss(self, cells: torch.Tensor, targets: torch.Tensor) -> float:
         cells, targets = cells.to(self.device), targets.to(self.device)
         scale = 1.0 / (cells.shape[0] * cells.shape[1])
+        embconv.set_cache_token(None)
         return float(self.model(cells, targets, scale))
 
     def validation_dump(self, cells: torch.Tensor, targets: torch.Tensor) -> Dict[str, torch.Tensor]:
@@ -327,6 +333,7 @@ class Trainer:
         ``param_*`` (reference: ``src/main.cpp:3492-3564``)."""
         cells, targets = cells.to(self.device), targets.to(self.device)
         self.zero_grad()
+        embconv.set_cache_token(None)
         scale = 1.0 / (cells.shape[1] * cells.shape[0])
         emb = self.model.frame_embeddings(cells)
         emb.retain_grad()
