@@ -6,6 +6,8 @@
     python benchmarks/bench_kernels.py lstm  [--t 1024 --b 8 --hidden 1024]
     python benchmarks/bench_kernels.py lstm-stream [--t 1024 --b 8 --hidden 1024 --vocab 4096 --chunk 64] [--offload]
     python benchmarks/bench_kernels.py mha   [--b 8 --heads 8 --t 1024 --d 128] [--causal]
+    python benchmarks/bench_kernels.py embconv [--frames 1024 --rows 48 --cols 160 --vocab 512 --cin 128 --cout 256
+                                                --change 0.05]
 
 Shapes default to the ones the reference's own benchmark programs use (GEMM 4096³ / 8192³, conv
 (32, 48, 160, 1024→1024), MHA (8, 8, 1024, 128), streaming LSTM; reference: ``benchmarks/`` and
@@ -167,6 +169,61 @@ def bench_mha(a):
     report(f"mha_fwd_bwd B{a.b} H{a.heads} T{a.t} D{a.d} causal={a.causal}", timeit(fb), 3.5 * flops)
 
 
+def coherent_cells(frames, cells_per_frame, vocab, change, seed=0, device="cuda"):
+    """Frames of (code point, fg, bg) words in which every frame copies its predecessor and redraws a fraction
+    ``change`` of the cells (the benchmark configurations' frame statistics)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+
+    def fresh(n):
+        return torch.stack([torch.randint(0, vocab, (n, cells_per_frame), generator=g, device=device),
+                            torch.randint(0, 1 << 24, (n, cells_per_frame), generator=g, device=device),
+                            torch.randint(0, 1 << 24, (n, cells_per_frame), generator=g, device=device)], -1).int()
+    new = fresh(frames)
+    if change >= 1.0:
+        return new
+    keep = torch.rand(frames, cells_per_frame, generator=g, device=device) >= change
+    keep[0] = False
+    # index of the last redraw at or before each frame, per cell
+    idx = torch.where(keep, torch.zeros_like(keep, dtype=torch.long),
+                      torch.arange(frames, device=device).view(-1, 1).expand(-1, cells_per_frame))
+    idx = torch.cummax(idx, 0).values
+    return torch.gather(new, 0, idx.unsqueeze(-1).expand(-1, -1, 3)).contiguous()
+
+
+def bench_embconv(a):
+    """The kernels of the fused "cell embedding + first convolution" layer on one chunk of frames, each timed alone,
+    with the bytes that have to move as the roofline."""
+    from fbamtrain_b200.ops import embconv
+    from fbamtrain_b200.ops import native_ops as no
+    from fbamtrain_b200.ops.conv_wgrad import wgrad_pass
+    rows, cols, o, c, n = a.rows, a.cols, a.cout, a.cin, a.frames
+    geom = (rows, cols, 2, 1, 1)
+    oh, ow = embconv.out_hw(*geom)
+    cells = coherent_cells(n, rows * cols, a.vocab, a.change)
+    table = torch.randn(a.vocab, 9, o, device="cuda").bfloat16()
+    pos = torch.randn(oh * ow, o, device="cuda")
+    cc_t = torch.randn(o, embconv.FEATURES, device="cuda").bfloat16()
+    z = torch.empty(n, oh * ow, o, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty_like(z)
+    dz = torch.randn(n, oh, ow, o, device="cuda").bfloat16()
+    s = torch.zeros(a.vocab, 9, o, device="cuda")
+    d = torch.zeros(oh * ow, o, device="cuda")
+    tag = f"n{n} {rows}x{cols} v{a.vocab} ->{o} change{a.change}"
+    feat = embconv.features_native(cells, *geom)
+    pix = n * oh * ow
+    report("embconv_features " + tag, timeit(lambda: embconv.features_native(cells, *geom)),
+           bytes_moved=cells.numel() * 4 + pix * 128)
+    report("embconv_colour_gemm " + tag, timeit(lambda: no.gemm(feat.view(pix, 64), cc_t, out=z.view(pix, o))),
+           flops=2.0 * pix * 64 * o, bytes_moved=pix * 128 + pix * o * 2)
+    report("embconv_fwd " + tag, timeit(lambda: embconv.forward_native(cells, table, pos, z, y, *geom)),
+           bytes_moved=3 * pix * o * 2 + cells.numel() * 4 // 3)
+    report("embconv_bwd_reduce " + tag, timeit(lambda: embconv.reduce_native(cells, dz.view(n, oh * ow, o), s, d, *geom)),
+           bytes_moved=pix * o * 2 + cells.numel() * 4 // 3)
+    report("embconv_colour_wgrad " + tag,
+           timeit(lambda: wgrad_pass(feat.view(n, oh, ow, 64), dz, o, 64, [(0, 0)], 1, out_dtype=torch.float32)),
+           flops=2.0 * pix * 64 * o, bytes_moved=pix * 128 + pix * o * 2)
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -195,9 +252,13 @@ def main():
     for name, default in (("b", 8), ("heads", 8), ("t", 1024), ("d", 128)):
         m.add_argument("--" + name, type=int, default=default)
     m.add_argument("--causal", action="store_true")
+    e = sub.add_parser("embconv")
+    for name, default in (("frames", 1024), ("rows", 48), ("cols", 160), ("vocab", 512), ("cin", 128), ("cout", 256)):
+        e.add_argument("--" + name, type=int, default=default)
+    e.add_argument("--change", type=float, default=0.05)
     a = ap.parse_args()
     {"gemm": bench_gemm, "conv": bench_conv, "lstm": bench_lstm, "lstm-stream": bench_lstm_stream,
-     "mha": bench_mha}[a.cmd](a)
+     "mha": bench_mha, "embconv": bench_embconv}[a.cmd](a)
 
 
 if __name__ == "__main__":

@@ -41,30 +41,6 @@ struct EmbConvGeom {
 };
 
 struct alignas(16) Pack8 { __nv_bfloat162 h[4]; };
-__device__ __forceinline__ void unpack8(const Pack8& p, float* f) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(p.h[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-__device__ __forceinline__ Pack8 pack8(const float* f) {
-  Pack8 p;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) p.h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-  return p;
-}
-
-// erf by Abramowitz-Stegun 7.1.26 (|error| < 1.5e-7), the form the GEMM epilogue uses for its fused GELU
-__device__ __forceinline__ float gelu_f(float x) {
-  const float u = fabsf(x) * 0.70710678118654752f;
-  const float t = __fdividef(1.0f, 1.0f + 0.3275911f * u);
-  const float e = __expf(-u * u);
-  const float poly = t * (0.254829592f + t * (-0.284496736f + t * (1.421413741f + t * (-1.453152027f + t * 1.061405429f))));
-  return 0.5f * x * (1.0f + copysignf(1.0f - poly * e, x));
-}
-
 // Cell index (row-major within the frame) that output pixel (oy, ox) reads through filter tap `tap`, or -1 when the
 // tap falls into the padding.
 __device__ __forceinline__ int tap_cell(const EmbConvGeom& g, int oy, int ox, int tap) {
@@ -112,22 +88,54 @@ __global__ void __launch_bounds__(256) embconv_features_kernel(const int* __rest
 // ------------------------------------------------------------------------------------------------
 // forward: Z += POS + sum of table rows, Y = GELU(Z)
 // ------------------------------------------------------------------------------------------------
-constexpr int kPrefetch = 4;      // frames whose cell words / rows are fetched before any of them is used (forward)
-constexpr int kPrefetchBwd = 8;   // same in the backward reduction
+constexpr int kPrefetch = 4;       // frames whose cell words / rows are fetched before any of them is used (forward)
+constexpr int kPrefetchBwd = 16;   // same in the backward reduction (8-byte pieces: 128 bytes in flight per lane)
 
-__device__ __forceinline__ void add_row(float* acc, const bf16* row, float sign) {
-  const Pack8 r = *reinterpret_cast<const Pack8*>(row);
-  float f[8];
-  unpack8(r, f);
-#pragma unroll
-  for (int j = 0; j < 8; ++j) acc[j] += sign * f[j];
+// Arithmetic on pairs of fp32 values (one instruction per pair on sm_100).
+__device__ __forceinline__ float2 f2(float a) { return make_float2(a, a); }
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
-__global__ void __launch_bounds__(256, 2) embconv_fwd_kernel(const int* __restrict__ cells, const bf16* __restrict__ table,
-                                                          const float* __restrict__ pos, bf16* __restrict__ z,
-                                                          bf16* __restrict__ y, long long frames, int vocab, int O,
-                                                          EmbConvGeom g, int seg_len, int nseg, int z_has_input,
-                                                          int apply_gelu) {
+// GELU (exact erf form) of two values.  erf by Abramowitz-Stegun 7.1.26 (|error| < 1.5e-7), the form the GEMM
+// epilogue uses for its fused GELU: erf(|v|) = 1 - t (a1 + t (a2 + t (a3 + t (a4 + t a5)))) exp(-v^2), t = 1 / (1 + p v),
+// v = |x| / sqrt(2).  The coefficients carry the minus sign so that the last step is one fused multiply-add.
+__device__ __forceinline__ float2 gelu2(float2 x) {
+  const float2 u = __fmul2_rn(make_float2(fabsf(x.x), fabsf(x.y)), f2(0.70710678118654752f));
+  const float2 den = __ffma2_rn(u, f2(0.3275911f), f2(1.0f));
+  const float2 t = make_float2(rcp_approx(den.x), rcp_approx(den.y));
+  const float2 w = __fmul2_rn(__fmul2_rn(u, u), f2(-1.4426950408889634f));
+  const float2 e = make_float2(ex2_approx(w.x), ex2_approx(w.y));
+  float2 poly = __ffma2_rn(t, f2(-1.061405429f), f2(1.453152027f));
+  poly = __ffma2_rn(poly, t, f2(-1.421413741f));
+  poly = __ffma2_rn(poly, t, f2(0.284496736f));
+  poly = __ffma2_rn(poly, t, f2(-0.254829592f));
+  poly = __fmul2_rn(poly, t);
+  const float2 er_abs = __ffma2_rn(poly, e, f2(1.0f));
+  const float2 er = make_float2(copysignf(er_abs.x, x.x), copysignf(er_abs.y, x.y));
+  const float2 hx = __fmul2_rn(x, f2(0.5f));
+  return __ffma2_rn(hx, er, hx);
+}
+
+__device__ __forceinline__ void add_row(float2* acc, const bf16* row, float sign) {
+  const Pack8 r = *reinterpret_cast<const Pack8*>(row);
+  const float2 s2 = f2(sign);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) acc[j] = __ffma2_rn(s2, __bfloat1622float2(r.h[j]), acc[j]);
+}
+
+__global__ void __launch_bounds__(256, 3) embconv_fwd_kernel(const int* __restrict__ cells, const bf16* __restrict__ table,
+                                                             const float* __restrict__ pos, bf16* __restrict__ z,
+                                                             bf16* __restrict__ y, long long frames, int vocab, int O,
+                                                             EmbConvGeom g, int seg_len, int nseg, int z_has_input,
+                                                             int apply_gelu) {
   const unsigned full = 0xffffffffu;
   const int lane = threadIdx.x & 31;
   const int p_out = g.oh * g.ow;
@@ -138,31 +146,35 @@ __global__ void __launch_bounds__(256, 2) embconv_fwd_kernel(const int* __restri
   const int co = blockIdx.y * 256 + lane * 8;
   const bool act = co < O;
   const long long cells_per_frame = (long long)g.rows * g.cols;
-  float base[8], sum[8];
+  float2 base[4], sum[4];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) { base[j] = 0.0f; sum[j] = 0.0f; }
+  for (int j = 0; j < 4; ++j) { base[j] = f2(0.0f); sum[j] = f2(0.0f); }
   if (act && pos != nullptr) {
     const float4* pp = reinterpret_cast<const float4*>(pos + (long long)p * O + co);
     const float4 a = pp[0], b = pp[1];
-    base[0] = a.x; base[1] = a.y; base[2] = a.z; base[3] = a.w;
-    base[4] = b.x; base[5] = b.y; base[6] = b.z; base[7] = b.w;
+    base[0] = make_float2(a.x, a.y); base[1] = make_float2(a.z, a.w);
+    base[2] = make_float2(b.x, b.y); base[3] = make_float2(b.z, b.w);
   }
   int cur = -1;                                            // lanes 0..8: code point of this lane's tap (-1: none)
   const long long f0 = (long long)seg * seg_len;
   const long long f1 = min(frames, f0 + seg_len);
   const long long row9 = 9ll * O;
+  const bf16* tab = table + (act ? co : 0);
+  const int* cell_ptr = cells + (f0 * cells_per_frame + max(cell, 0)) * 3;
+  const long long cell_step = cells_per_frame * 3, z_step = (long long)p_out * O;
+  long long off = (f0 * p_out + p) * O + (act ? co : 0);
   for (long long fb = f0; fb < f1; fb += kPrefetch) {
     int ncp[kPrefetch];
     Pack8 zin[kPrefetch];
 #pragma unroll
     for (int u = 0; u < kPrefetch; ++u) {
-      const long long f = fb + u;
       ncp[u] = -1;
-      if (f < f1) {
-        if (cell >= 0) ncp[u] = __ldg(cells + (f * cells_per_frame + cell) * 3);
-        if (act && z_has_input) zin[u] = *reinterpret_cast<const Pack8*>(z + (f * p_out + p) * O + co);
+      if (fb + u < f1) {
+        if (cell >= 0) ncp[u] = __ldg(cell_ptr + u * cell_step);
+        if (act && z_has_input) zin[u] = *reinterpret_cast<const Pack8*>(z + off + u * z_step);
       }
     }
+    cell_ptr += kPrefetch * cell_step;
 #pragma unroll
     for (int u = 0; u < kPrefetch; ++u) {
       const long long f = fb + u;
@@ -172,61 +184,64 @@ __global__ void __launch_bounds__(256, 2) embconv_fwd_kernel(const int* __restri
       const unsigned changed = __ballot_sync(full, nc != cur) & 0x1ffu;
       if (f == f0 || __popc(changed) > 4) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) sum[j] = 0.0f;
+        for (int j = 0; j < 4; ++j) sum[j] = f2(0.0f);
 #pragma unroll
         for (int t = 0; t < 9; ++t) {
           const int c = __shfl_sync(full, nc, t);
-          if (c >= 0 && act) add_row(sum, table + c * row9 + (long long)t * O + co, 1.0f);
+          if (c >= 0 && act) add_row(sum, tab + c * row9 + t * O, 1.0f);
         }
-      } else if (changed) {
-#pragma unroll
-        for (int t = 0; t < 9; ++t) {
-          if ((changed >> t) & 1u) {
-            const int o = __shfl_sync(full, cur, t);
-            const int c = __shfl_sync(full, nc, t);
-            if (act) {
-              if (o >= 0) add_row(sum, table + o * row9 + (long long)t * O + co, -1.0f);
-              if (c >= 0) add_row(sum, table + c * row9 + (long long)t * O + co, 1.0f);
-            }
+      } else {
+        unsigned m = changed;
+        while (m) {
+          const int t = __ffs(m) - 1;
+          m &= m - 1;
+          const int o = __shfl_sync(full, cur, t);
+          const int c = __shfl_sync(full, nc, t);
+          if (act) {
+            if (o >= 0) add_row(sum, tab + o * row9 + t * O, -1.0f);
+            if (c >= 0) add_row(sum, tab + c * row9 + t * O, 1.0f);
           }
         }
       }
       cur = nc;
       if (act) {
-        float v[8];
-        if (z_has_input) unpack8(zin[u], v);
-        else {
+        float2 v[4];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+        for (int j = 0; j < 4; ++j) {
+          v[j] = __fadd2_rn(sum[j], base[j]);
+          if (z_has_input) v[j] = __fadd2_rn(v[j], __bfloat1622float2(zin[u].h[j]));
         }
+        Pack8 out;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] += sum[j] + base[j];
-        const long long off = (f * p_out + p) * O + co;
-        *reinterpret_cast<Pack8*>(z + off) = pack8(v);
+        for (int j = 0; j < 4; ++j) out.h[j] = __float22bfloat162_rn(v[j]);
+        *reinterpret_cast<Pack8*>(z + off + u * z_step) = out;
         if (y != nullptr) {
           if (apply_gelu) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = gelu_f(v[j]);
+            for (int j = 0; j < 4; ++j) out.h[j] = __float22bfloat162_rn(gelu2(v[j]));
           }
-          *reinterpret_cast<Pack8*>(y + off) = pack8(v);
+          *reinterpret_cast<Pack8*>(y + off + u * z_step) = out;
         }
       }
     }
+    off += kPrefetch * z_step;
   }
 }
 
 // ------------------------------------------------------------------------------------------------
 // backward: S[v][tap][:] += dZ rows whose tap shows code point v;  D[p][:] += sum over frames of dZ[:, p, :]
 // ------------------------------------------------------------------------------------------------
-// Here a lane owns 4 channels (a warp covers a 128-channel block): nine taps x 4 accumulators plus eight prefetched
-// 8-byte pieces of dZ stay within 128 registers, so two blocks of 256 threads run per SM with 32 KB of dZ in flight.
+// A lane owns 4 channels (a warp covers a 128-channel block).  All nine taps of a pixel accumulate the same dZ
+// values and differ only in where their runs begin and end, so the lane keeps ONE running prefix sum of its dZ over
+// the frames of the segment and, per tap, the value of that prefix when the tap's current run began: a run's sum is
+// the difference of two prefixes, taken when the run ends.  Per frame that is four additions instead of forty; the
+// prefix at the end of the segment is the pixel's contribution to D.  (The prefix spans at most one segment, so the
+// difference loses at most log2(segment) bits of fp32 — far below the bf16 resolution of dZ.)
 struct alignas(8) Pack4 { __nv_bfloat162 h[2]; };
 
-__device__ __forceinline__ void red_add4(float* dst, const float* v) {
-  atomicAdd(reinterpret_cast<float4*>(dst), make_float4(v[0], v[1], v[2], v[3]));
-}
+__device__ __forceinline__ void red_add4(float* dst, float4 v) { atomicAdd(reinterpret_cast<float4*>(dst), v); }
 
-__global__ void __launch_bounds__(256, 2) embconv_bwd_reduce_kernel(const int* __restrict__ cells, const bf16* __restrict__ dz,
+__global__ void __launch_bounds__(256, 3) embconv_bwd_reduce_kernel(const int* __restrict__ cells, const bf16* __restrict__ dz,
                                                                     float* __restrict__ S, float* __restrict__ D,
                                                                     long long frames, int vocab, int O, EmbConvGeom g,
                                                                     int seg_len, int nseg) {
@@ -241,20 +256,20 @@ __global__ void __launch_bounds__(256, 2) embconv_bwd_reduce_kernel(const int* _
   const bool act = co < O;
   const long long cells_per_frame = (long long)g.rows * g.cols;
   const long long row9 = 9ll * O;
-  float acc[9][4], dsum[4];
+  float2 pre[2] = {f2(0.0f), f2(0.0f)};                     // prefix sum of this lane's dZ over the frames so far
+  // per tap: the prefix when its current run began.  Touched only when a run ends, so it lives in shared memory
+  // (one 16-byte slot per thread and tap, conflict-free) and the loop over the changed taps is a real loop.
+  __shared__ float4 start_sm[9][256];
+  float4* start = &start_sm[0][threadIdx.x];
 #pragma unroll
-  for (int t = 0; t < 9; ++t)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[t][j] = 0.0f;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) dsum[j] = 0.0f;
+  for (int t = 0; t < 9; ++t) start[t * 256] = make_float4(0.f, 0.f, 0.f, 0.f);
   int cur = -1;
   const long long f0 = (long long)seg * seg_len;
   const long long f1 = min(frames, f0 + seg_len);
-  const int* cell_ptr = cells + ((long long)f0 * cells_per_frame + max(cell, 0)) * 3;
-  const bf16* dz_ptr = dz + ((long long)f0 * p_out + p) * O + (act ? co : 0);
+  const int* cell_ptr = cells + (f0 * cells_per_frame + max(cell, 0)) * 3;
+  const bf16* dz_ptr = dz + (f0 * p_out + p) * O + (act ? co : 0);
   const long long cell_step = cells_per_frame * 3, dz_step = (long long)p_out * O;
-  float* s_base = S + co;
+  float* s_base = S + (act ? co : 0);
   for (long long fb = f0; fb < f1; fb += kPrefetchBwd) {
     int ncp[kPrefetchBwd];
     Pack4 din[kPrefetchBwd];
@@ -273,37 +288,31 @@ __global__ void __launch_bounds__(256, 2) embconv_bwd_reduce_kernel(const int* _
       if (fb + u >= f1) break;
       int nc = ncp[u];
       if ((unsigned)nc >= (unsigned)vocab) nc = -1;
-      const unsigned changed = __ballot_sync(full, nc != cur) & 0x1ffu;
-      if (changed) {
-#pragma unroll
-        for (int t = 0; t < 9; ++t) {
-          if ((changed >> t) & 1u) {
-            const int o = __shfl_sync(full, cur, t);
-            if (o >= 0 && act) red_add4(s_base + o * row9 + t * O, acc[t]);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[t][j] = 0.0f;
-          }
-        }
+      unsigned changed = __ballot_sync(full, nc != cur) & 0x1ffu;
+      while (changed) {
+        const int t = __ffs(changed) - 1;
+        changed &= changed - 1;
+        const int o = __shfl_sync(full, cur, t);
+        const float4 st = start[t * 256];
+        if (o >= 0 && act)
+          red_add4(s_base + o * row9 + t * O, make_float4(pre[0].x - st.x, pre[0].y - st.y, pre[1].x - st.z, pre[1].y - st.w));
+        start[t * 256] = make_float4(pre[0].x, pre[0].y, pre[1].x, pre[1].y);
       }
       cur = nc;
       if (act) {
-        const float2 a = __bfloat1622float2(din[u].h[0]), b = __bfloat1622float2(din[u].h[1]);
-        const float d[4] = {a.x, a.y, b.x, b.y};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) dsum[j] += d[j];
-#pragma unroll
-        for (int t = 0; t < 9; ++t)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) acc[t][j] += d[j];
+        pre[0] = __fadd2_rn(pre[0], __bfloat1622float2(din[u].h[0]));
+        pre[1] = __fadd2_rn(pre[1], __bfloat1622float2(din[u].h[1]));
       }
     }
   }
-#pragma unroll
+#pragma unroll 1
   for (int t = 0; t < 9; ++t) {
     const int o = __shfl_sync(full, cur, t);
-    if (o >= 0 && act) red_add4(s_base + o * row9 + t * O, acc[t]);
+    const float4 st = start[t * 256];
+    if (o >= 0 && act)
+      red_add4(s_base + o * row9 + t * O, make_float4(pre[0].x - st.x, pre[0].y - st.y, pre[1].x - st.z, pre[1].y - st.w));
   }
-  if (act && f1 > f0) red_add4(D + (long long)p * O + co, dsum);
+  if (act && f1 > f0) red_add4(D + (long long)p * O + co, make_float4(pre[0].x, pre[0].y, pre[1].x, pre[1].y));
 }
 
 // ------------------------------------------------------------------------------------------------

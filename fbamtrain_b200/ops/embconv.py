@@ -32,7 +32,7 @@ import torch
 import torch.nn.functional as F
 
 FEATURES = 64          # colour features per output pixel: 9 taps x 6 channels, padded to one 128-byte bf16 row
-SEGMENT_FRAMES = 64    # consecutive frames one warp walks (run-length state is rebuilt at every segment start)
+SEGMENT_FRAMES = 128   # consecutive frames one warp walks (run-length state is rebuilt at every segment start)
 MAX_TABLE_BYTES = 256 * 1024 * 1024
 
 _tap_cache: Dict[Tuple, torch.Tensor] = {}
