@@ -246,7 +246,8 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_gra
 
 // -------------------------------------------------------------------------------------------------
 // Sum of all peers' gradients over [lo, hi) -> momentum buffer update -> bf16 update direction + Σ x².
-// buf = mu*buf + g;  u = nesterov ? g + mu*buf : buf;  out_bf16 = u;  sumsq += Σ u²
+// buf = mu*buf + (1 - mu)*g;  u = nesterov ? (1 - mu)*g + mu*buf : buf;  out_bf16 = u;  sumsq += Σ u²
+// (the momentum buffer is an exponential moving average, as in the reference: src/optimizers.cpp:1204-1226)
 // -------------------------------------------------------------------------------------------------
 template <bool BF16>
 __global__ void __launch_bounds__(256)
@@ -290,7 +291,7 @@ reduce_pull_kernel(PeerPtrs grads, float* momentum_buf, bf16* out, float* sumsq,
     }
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
-      const float gj = g[j] * grad_scale;
+      const float gj = g[j] * grad_scale * (1.0f - mu);
       bufv[j] = mu * bufv[j] + gj;
       u[j] = nesterov ? gj + mu * bufv[j] : bufv[j];
       local += u[j] * u[j];

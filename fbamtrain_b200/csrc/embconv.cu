@@ -30,6 +30,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "gelu_math.cuh"
+
 namespace {
 
 typedef __nv_bfloat16 bf16;
@@ -91,38 +93,8 @@ __global__ void __launch_bounds__(256) embconv_features_kernel(const int* __rest
 constexpr int kPrefetch = 4;       // frames whose cell words / rows are fetched before any of them is used (forward)
 constexpr int kPrefetchBwd = 16;   // same in the backward reduction (8-byte pieces: 128 bytes in flight per lane)
 
-// Arithmetic on pairs of fp32 values (one instruction per pair on sm_100).
-__device__ __forceinline__ float2 f2(float a) { return make_float2(a, a); }
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ float rcp_approx(float x) {
-  float y;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-// GELU (exact erf form) of two values.  erf by Abramowitz-Stegun 7.1.26 (|error| < 1.5e-7), the form the GEMM
-// epilogue uses for its fused GELU: erf(|v|) = 1 - t (a1 + t (a2 + t (a3 + t (a4 + t a5)))) exp(-v^2), t = 1 / (1 + p v),
-// v = |x| / sqrt(2).  The coefficients carry the minus sign so that the last step is one fused multiply-add.
-__device__ __forceinline__ float2 gelu2(float2 x) {
-  const float2 u = __fmul2_rn(make_float2(fabsf(x.x), fabsf(x.y)), f2(0.70710678118654752f));
-  const float2 den = __ffma2_rn(u, f2(0.3275911f), f2(1.0f));
-  const float2 t = make_float2(rcp_approx(den.x), rcp_approx(den.y));
-  const float2 w = __fmul2_rn(__fmul2_rn(u, u), f2(-1.4426950408889634f));
-  const float2 e = make_float2(ex2_approx(w.x), ex2_approx(w.y));
-  float2 poly = __ffma2_rn(t, f2(-1.061405429f), f2(1.453152027f));
-  poly = __ffma2_rn(poly, t, f2(-1.421413741f));
-  poly = __ffma2_rn(poly, t, f2(0.284496736f));
-  poly = __ffma2_rn(poly, t, f2(-0.254829592f));
-  poly = __fmul2_rn(poly, t);
-  const float2 er_abs = __ffma2_rn(poly, e, f2(1.0f));
-  const float2 er = make_float2(copysignf(er_abs.x, x.x), copysignf(er_abs.y, x.y));
-  const float2 hx = __fmul2_rn(x, f2(0.5f));
-  return __ffma2_rn(hx, er, hx);
-}
+using gelu_math::f2;
+using gelu_math::gelu2;
 
 __device__ __forceinline__ void add_row(float2* acc, const bf16* row, float sign) {
   const Pack8 r = *reinterpret_cast<const Pack8*>(row);

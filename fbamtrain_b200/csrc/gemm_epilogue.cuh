@@ -1,6 +1,7 @@
 // Fused epilogue shared by the tcgen05 GEMM kernels: one call handles 32 consecutive output columns of one row.
 #pragma once
 #include "gemm_tcgen05.h"
+#include "gelu_math.cuh"
 #include <cuda_bf16.h>
 
 // The row-store variant of the reduce-scatter epilogue (GemmParams::rs_row_stores) is compiled in only on request
@@ -13,24 +14,10 @@
 
 namespace gemm_epi {
 
-// erf via Abramowitz-Stegun 7.1.26 (|error| < 1.5e-7, far below bf16 resolution): the epilogue must not cost
-// more issue slots than the tile's main loop, and erff() would.  e = exp(-x²/2) is shared with gelu'.
-__device__ __forceinline__ float erf_core(float x, float& e) {
-  const float u = fabsf(x) * 0.70710678118654752f;
-  const float t = __fdividef(1.0f, 1.0f + 0.3275911f * u);
-  e = __expf(-u * u);
-  const float poly = t * (0.254829592f + t * (-0.284496736f + t * (1.421413741f + t * (-1.453152027f + t * 1.061405429f))));
-  return copysignf(1.0f - poly * e, x);
-}
-__device__ __forceinline__ float gelu_f(float x) {
-  float e;
-  return 0.5f * x * (1.0f + erf_core(x, e));
-}
-__device__ __forceinline__ float gelu_grad_f(float x) {
-  float e;
-  const float er = erf_core(x, e);
-  return 0.5f * (1.0f + er) + x * 0.3989422804014327f * e;
-}
+// GELU and gelu' come from gelu_math.cuh (packed fp32 pairs): the epilogue must not cost more issue slots than the
+// tile's main loop, which erff() — and, for short K, even a scalar polynomial form — would.
+__device__ __forceinline__ float gelu_f(float x) { return gelu_math::gelu1(x); }
+__device__ __forceinline__ float gelu_grad_f(float x) { return gelu_math::gelu_grad1(x); }
 
 __device__ __forceinline__ uint4 shfl_xor_u4(const uint4& x, int lane_mask) {
   uint4 y;
@@ -65,13 +52,18 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
                 *reinterpret_cast<uint4*>(po + j) = *reinterpret_cast<uint4*>(h);
               }
             } else {
+  #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (n0 + j < p.N) po[j] = __float2bfloat16(v[j]);
             }
           }
           if (p.act == GEMM_ACT_GELU) {
   #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
+            for (int j = 0; j < 32; j += 2) {
+              const float2 g = gelu_math::gelu2(make_float2(v[j], v[j + 1]));
+              v[j] = g.x;
+              v[j + 1] = g.y;
+            }
           } else if (p.act == GEMM_ACT_RELU) {
   #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
@@ -85,12 +77,13 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
                 const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
   #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                  float2 f = __bfloat1622float2(h[q]);
-                  v[j + 2 * q] *= gelu_grad_f(f.x);
-                  v[j + 2 * q + 1] *= gelu_grad_f(f.y);
+                  const float2 g = gelu_math::gelu_grad2(__bfloat1622float2(h[q]));
+                  v[j + 2 * q] *= g.x;
+                  v[j + 2 * q + 1] *= g.y;
                 }
               }
             } else {
+  #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (n0 + j < p.N) v[j] *= gelu_grad_f(__bfloat162float(gi[j]));
             }
@@ -110,6 +103,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
                 }
               }
             } else {
+  #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (n0 + j < p.N) v[j] += __bfloat162float(ri[j]);
             }
@@ -162,6 +156,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
                 *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
               }
             } else {
+  #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (n0 + j < p.N) out[j] = __float2bfloat16(v[j]);
             }
@@ -179,6 +174,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
                              "f"(v[j + 1]), "f"(v[j + 2]), "f"(v[j + 3])
                              : "memory");
             } else {
+  #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (n0 + j < p.N)
                   asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(out + j), "f"(v[j]) : "memory");
@@ -188,6 +184,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
           if (p.out_fp32) {
             float* out = reinterpret_cast<float*>(p.D) + roff + n0;
             if (p.accumulate == GEMM_ACC_ATOMIC) {
+  #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (n0 + j < p.N) atomicAdd(out + j, v[j]);
             } else if (full_vec) {
@@ -201,6 +198,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
                 *reinterpret_cast<float4*>(out + j) = o;
               }
             } else {
+  #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (n0 + j < p.N) out[j] = p.accumulate ? out[j] + v[j] : v[j];
             }
@@ -225,6 +223,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
                 *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
               }
             } else {
+  #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (n0 + j < p.N)
                   out[j] = __float2bfloat16(p.accumulate ? __bfloat162float(out[j]) + v[j] : v[j]);

@@ -14,6 +14,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "gelu_math.cuh"
+
 namespace {
 
 typedef __nv_bfloat16 bf16;
@@ -58,9 +60,22 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return scratch[0];
 }
 
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
-__device__ __forceinline__ float gelu_grad_f(float x) {
-  return 0.5f * (1.0f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+// GELU (exact erf form) and its derivative, eight values at a time on packed fp32 pairs (gelu_math.cuh)
+__device__ __forceinline__ void gelu8(const float* x, float* y) {
+#pragma unroll
+  for (int j = 0; j < 8; j += 2) {
+    const float2 g = gelu_math::gelu2(make_float2(x[j], x[j + 1]));
+    y[j] = g.x;
+    y[j + 1] = g.y;
+  }
+}
+__device__ __forceinline__ void gelu_grad8(const float* x, float* y) {
+#pragma unroll
+  for (int j = 0; j < 8; j += 2) {
+    const float2 g = gelu_math::gelu_grad2(make_float2(x[j], x[j + 1]));
+    y[j] = g.x;
+    y[j + 1] = g.y;
+  }
 }
 
 struct alignas(16) Pack8 { __nv_bfloat162 h[4]; };
@@ -215,13 +230,13 @@ __global__ void gelu_kernel(const bf16* __restrict__ x, const bf16* __restrict__
   float a[8], o[8];
   unpack8(reinterpret_cast<const Pack8*>(x)[i], a);
   if (mode == 0) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = gelu_f(a[j]);
+    gelu8(a, o);
   } else {
     float d[8];
     unpack8(reinterpret_cast<const Pack8*>(dy)[i], d);
+    gelu_grad8(a, o);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = d[j] * gelu_grad_f(a[j]);
+    for (int j = 0; j < 8; ++j) o[j] *= d[j];
   }
   reinterpret_cast<Pack8*>(out)[i] = pack8(o);
 }
@@ -236,8 +251,9 @@ __global__ void geglu_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ 
   float v[8], g[8], o[8];
   unpack8(*reinterpret_cast<const Pack8*>(x + row * 2 * c + col), v);
   unpack8(*reinterpret_cast<const Pack8*>(x + row * 2 * c + c + col), g);
+  gelu8(g, o);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) o[j] = v[j] * gelu_f(g[j]);
+  for (int j = 0; j < 8; ++j) o[j] *= v[j];
   *reinterpret_cast<Pack8*>(y + row * c + col) = pack8(o);
 }
 __global__ void geglu_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, bf16* __restrict__ dx,
@@ -251,10 +267,12 @@ __global__ void geglu_bwd_kernel(const bf16* __restrict__ x, const bf16* __restr
   unpack8(*reinterpret_cast<const Pack8*>(x + row * 2 * c + col), v);
   unpack8(*reinterpret_cast<const Pack8*>(x + row * 2 * c + c + col), g);
   unpack8(*reinterpret_cast<const Pack8*>(dy + row * c + col), d);
+  gelu8(g, dv);
+  gelu_grad8(g, dg);
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    dv[j] = d[j] * gelu_f(g[j]);
-    dg[j] = d[j] * v[j] * gelu_grad_f(g[j]);
+    dv[j] *= d[j];
+    dg[j] *= d[j] * v[j];
   }
   *reinterpret_cast<Pack8*>(dx + row * 2 * c + col) = pack8(dv);
   *reinterpret_cast<Pack8*>(dx + row * 2 * c + c + col) = pack8(dg);
@@ -347,10 +365,11 @@ __global__ void global_avgpool_bwd_kernel(const bf16* __restrict__ dy, const bf1
   unpack8(*reinterpret_cast<const Pack8*>(dy + b * c + col), v);
   const float inv = 1.0f / pix;
   if (z != nullptr) {
-    float zv[8];
+    float zv[8], gz[8];
     unpack8(reinterpret_cast<const Pack8*>(z)[i], zv);
+    gelu_grad8(zv, gz);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] *= inv * gelu_grad_f(zv[j]);
+    for (int j = 0; j < 8; ++j) v[j] *= inv * gz[j];
   } else {
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] *= inv;

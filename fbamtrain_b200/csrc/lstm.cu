@@ -22,7 +22,8 @@
 // The reference runs the recurrence as one GEMM launch plus a point-wise cell kernel per time step (reference:
 // kernel_gen/kernel_gen/kernels/lstm_cell.py:6-144, kernels/lstm_cell_bwd.py:6-273 for the cell arithmetic and the
 // recompute / backward point-wise kernels; tensorlib/src/streaming_lstm.cpp and streaming_lstm_bwd.cpp for the loop
-// around them); gate order i, f, g, o, fp32 gates and cell state, tanh(x) = 2·sigmoid(2x) - 1 as there.
+// around them); gate order i, f, g, o, fp32 gates and cell state as there (tanh is tanhf here; the reference
+// writes it as 2·sigmoid(2x) - 1, the same function).
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -661,24 +662,28 @@ int fbam_lstm_bwd(const float* gates, const float* c_all, const float* c0, const
 // -------------------------------------------------------------------------------------------------
 #include "lstm_noalloc.h"
 
+#include <atomic>
+
 static __device__ __align__(256) unsigned char g_lstm_noalloc_scratch[FBAM_LSTM_NOALLOC_SCRATCH_BYTES];
 
 namespace {
 constexpr int kMaxDevices = 64;
 // Device address of the scratch array per device ordinal.  In host code the array's name is only a handle for
 // the runtime; the address a kernel can use has to be asked for, once per device, with that device current.
-void* g_noalloc_scratch_addr[kMaxDevices] = {nullptr};
+// Atomic slots: two host threads making their first call on a device may both look the address up; they store the
+// same value, and the atomics make that a defined race-free publication.
+std::atomic<void*> g_noalloc_scratch_addr[kMaxDevices];
 
 int noalloc_scratch(void** out) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FBAM_LSTM_NOALLOC_ERR_SETUP;
-  if (g_noalloc_scratch_addr[dev] == nullptr) {
-    void* ptr = nullptr;
+  void* ptr = g_noalloc_scratch_addr[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
     if (cudaGetSymbolAddress(&ptr, g_lstm_noalloc_scratch) != cudaSuccess || ptr == nullptr)
       return FBAM_LSTM_NOALLOC_ERR_SETUP;
-    g_noalloc_scratch_addr[dev] = ptr;
+    g_noalloc_scratch_addr[dev].store(ptr, std::memory_order_release);
   }
-  *out = g_noalloc_scratch_addr[dev];
+  *out = ptr;
   return 0;
 }
 }  // namespace

@@ -19,7 +19,8 @@
 //   * The scratch array (FBAM_LSTM_NOALLOC_SCRATCH_BYTES, about 33 KB) lives in every device that loads the
 //     library, from load until the process exits.
 //   * The first call on a device looks up the array's device address (one-time set-up for that device, done
-//     with that device current).  Make that first call outside any stream capture.
+//     with that device current).  Make that first call outside any stream capture.  The looked-up address is
+//     published through an atomic slot per device, so first calls from several host threads are safe.
 //   * No cudaMalloc / cudaFree / allocating library routine is called, on any call.
 //   * All calls on a device share the one array.  The barrier counter is cleared at the start of every call; the
 //     h buffer is fully rewritten before it is read.  Two calls that overlap on the GPU (different streams, or

@@ -6,7 +6,7 @@ Contents and protocol follow the reference (reference: ``src/dataset_cursor.cpp:
 snapshot to a writer thread, which writes a temporary file, ``fsync``s it, renames it over the
 target and ``fsync``s the directory.  Only the newest snapshot matters; intermediate ones may be
 skipped.  The native runtime library provides the same writer in C++
-(``csrc/runtime/cursor.cpp``); this module is its Python front end and portable fallback.
+(``fbam_cursor_*`` in ``csrc/runtime/runtime.cpp``); this module is its Python front end and portable fallback.
 """
 from __future__ import annotations
 

@@ -3,7 +3,8 @@
 Algorithm of the reference (reference: ``src/optimizers.cpp:825-1434``; NS loop ``1320-1367``;
 orientation rule ``941-968``; scale ``1044-1054``):
 
-1. ``buf = μ·buf + g``; the update is ``g + μ·buf`` with Nesterov, else ``buf``;
+1. the momentum buffer is an exponential moving average, ``buf = μ·buf + (1 − μ)·g`` (``1204-1226``); the update
+   is ``(1 − μ)·g + μ·buf`` (the reference's only form; ``nesterov = false`` here takes ``buf`` itself);
 2. cast to bf16, divide by ``(‖·‖_F + 1e-7)``;
 3. five iterations of ``A = X Xᵀ; B = b·A + c·A A; X = a·X + B X`` with
    ``(a, b, c) = (3.4445, -4.7750, 2.0315)``, run on the orientation with rows ≤ cols;
@@ -47,8 +48,8 @@ def newton_schulz(g: torch.Tensor, steps: int = 5, dtype: torch.dtype = torch.bf
 
 def muon_update(grad2d: torch.Tensor, momentum_buf: torch.Tensor, momentum: float, nesterov: bool,
                 ns_steps: int = 5, ns: Callable = newton_schulz) -> torch.Tensor:
-    momentum_buf.mul_(momentum).add_(grad2d)
-    upd = grad2d + momentum * momentum_buf if nesterov else momentum_buf
+    momentum_buf.mul_(momentum).add_(grad2d, alpha=1.0 - momentum)
+    upd = (1.0 - momentum) * grad2d + momentum * momentum_buf if nesterov else momentum_buf
     u = ns(upd, ns_steps).float()
     rows, cols = grad2d.shape
     return u * max(1.0, rows / cols) ** 0.5

@@ -31,6 +31,64 @@ from .dp import DataParallel
 from .ftccl import FtPeer, Result, SharedStateSyncStrategy, TensorInfo
 
 
+class FusedStepSnapshot:
+    """Everything a fused reduce + optimizer step may change, captured before it runs, so that a step in which a
+    peer stopped answering can be undone as a whole.
+
+    The fused step is one kernel per bucket: buckets whose entry barrier passed before the peer fell silent have
+    advanced their slice of m / v / master and stored new parameters into every member's window, later buckets have
+    not, and the step counters are one ahead.  Dropping such a step must leave no trace (the reference's drop path
+    re-synchronises state "at the old revision": ``src/main.cpp:3672-3713``), otherwise the half-applied slices
+    would spread in the next shared-state synchronisation and the bias correction would run one step ahead.  The
+    snapshot holds this member's slice of the sharded AdamW tensors, the Muon momentum / master tensors, the full
+    parameter buckets (peers write into them) and the step counters; buffers are allocated once and reused."""
+
+    def __init__(self):
+        self._buffers = {}
+        self._counters = []
+
+    def _keep(self, key, t: torch.Tensor) -> None:
+        buf = self._buffers.get(key)
+        if buf is None or buf.shape != t.shape or buf.dtype != t.dtype or buf.device != t.device:
+            buf = torch.empty_like(t)
+            self._buffers[key] = buf
+        buf.copy_(t)
+        self._live.append((t, buf))
+
+    @staticmethod
+    def _optimizers(trainer):
+        for opt in trainer.optimizers.values():
+            yield opt
+            for sub in ("adam", "muon"):
+                if hasattr(opt, sub):
+                    yield getattr(opt, sub)
+
+    def capture(self, trainer, rank: int, world: int) -> None:
+        self._live = []
+        self._counters = [(opt, opt.step_count) for opt in self._optimizers(trainer)]
+        for g in trainer.all_groups():
+            self._keep(("param", g.name), g.data)
+        for opt in self._optimizers(trainer):
+            groups = getattr(opt, "groups", None)
+            if groups is not None and getattr(opt, "flat_state", None) is not None:      # flat (shardable) AdamW
+                for g, fs in zip(groups, opt.flat_state):
+                    per = g.numel // world
+                    for key, t in fs.items():
+                        self._keep(("flat", id(opt), g.name, key), t[rank * per:(rank + 1) * per])
+            elif isinstance(getattr(opt, "state", None), dict) and hasattr(opt, "named_params"):
+                for name, _ in opt.named_params:
+                    for key, t in opt.state.get(name, {}).items():
+                        if torch.is_tensor(t):
+                            self._keep(("state", id(opt), name, key), t)
+
+    def restore(self) -> None:
+        for t, buf in self._live:
+            t.copy_(buf)
+        for opt, count in self._counters:
+            opt.step_count = count
+        self._live = []
+
+
 class FaultTolerantDataParallel:
     def __init__(self, peer: FtPeer, expected_world: int, min_world: int = 1, mode: str = "allreduce",
                  wait_for_full_world: bool = False, full_world_poll_s: float = 1.0):
@@ -45,6 +103,7 @@ class FaultTolerantDataParallel:
         self.tx_bytes = self.rx_bytes = 0
         self.dropped_steps = 0
         self.ready_gate = None                # optional callable run right before a late joiner connects
+        self._snapshot: Optional[FusedStepSnapshot] = None
 
     # the trainer reads these
     @property
@@ -210,9 +269,14 @@ class FaultTolerantDataParallel:
         scale = self.expected_world / max(1, peer.world_size)
         if self.mode == "fused" and peer.world_size > 1:
             self.inner.grad_scale = scale
+            if self._snapshot is None:
+                self._snapshot = FusedStepSnapshot()
+            self._snapshot.capture(trainer, self.inner.rank, self.inner.world_size)
             self.inner.reduce_and_step(trainer)
             if not self._fused_step_completed(trainer):
-                # a peer stopped answering inside the step: its bounded waits ran out and the kernels returned
+                # a peer stopped answering inside the step: its bounded waits ran out and the kernels returned.
+                # Some buckets were updated and some were not: undo all of it before anyone compares state.
+                self._snapshot.restore()
                 self._retopologize(trainer)
                 return self._drop(trainer, "a device-side wait for a peer timed out")
         else:

@@ -7,7 +7,7 @@ after that sort.  ``TokenizerHandle`` walks the trie one code point at a time an
 used for longest-match extraction of action tokens from recorded keystrokes
 (reference: ``include/tokenizer.h:14-62``, ``src/main.cpp:1912-1981``).
 
-A native implementation of the same trie lives in ``csrc/runtime/tokenizer.cpp``; when the runtime
+A native implementation of the same trie lives in ``csrc/runtime/runtime.cpp`` (``fbam_tok_*``); when the runtime
 library is built, :func:`Tokenizer.encode_longest_match` dispatches to it.
 """
 from __future__ import annotations

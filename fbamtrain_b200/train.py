@@ -536,6 +536,15 @@ def run_training(trainer: Trainer, source=None, max_steps: Optional[int] = None)
         cursor_path = os.path.join(trainer.working_dir, cursor_path)
         snap = DatasetCursorCommitter.load(cursor_path)
         if snap is not None and iterator is not None:
+            # A cursor written under another batch or sequence length describes a different data order: refuse it,
+            # as the reference does (src/main.cpp:2926-2933).  batch_size is the number of sequences the iterator
+            # draws per call — the global batch here (one iterator serves all ranks), the micro-batch there.
+            if snap.batch_size != global_batch:
+                raise RuntimeError(f"Dataset cursor batch_size does not match run configuration "
+                                   f"(cursor {snap.batch_size}, iterator draws {global_batch} sequences per step).")
+            if snap.sequence_length != cfg.train_sequence_length:
+                raise RuntimeError(f"Dataset cursor sequence_length does not match run configuration "
+                                   f"(cursor {snap.sequence_length}, configured {cfg.train_sequence_length}).")
             if snap.step_count != trainer.step_count:
                 LOG("WARN", f"dataset cursor is at step {snap.step_count}, checkpoint at {trainer.step_count}")
             from .data.iterator import DatasetIteratorState

@@ -5,7 +5,7 @@ Format: 8-byte little-endian header length, a JSON header mapping tensor name to
 are the ones the reference writes — ``U32, U64, BF16, F16, F32`` (reference:
 ``tensorlib/src/safe_tensors.cpp:34-76, 86-530``) — plus ``I32``/``I64`` for convenience.
 ``load(path, pinned=True)`` reads into page-locked memory; ``load_inplace`` fills existing tensors
-after checking dtype and shape.  The native runtime (``csrc/runtime/safetensors.cpp``) implements
+after checking dtype and shape.  The native runtime (``csrc/runtime/runtime.cpp``, ``fbam_st_*``) implements
 the same format in C++ for callers outside Python.
 """
 from __future__ import annotations

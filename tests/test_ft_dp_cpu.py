@@ -88,3 +88,84 @@ def test_trainer_survives_peer_loss_and_admits_joiner():
     assert joiner["first_step"] >= 1 and joiner["rx"] > 0         # joined mid-run and received the state
     assert len(done[0][4]["events"]) >= 3                         # start, shrink to two, grow to three
     assert done[0][4]["events"][-1]["world"] == 3
+
+
+class _FakePeer:
+    """Host side of a two-member group in which nothing changes: enough for the step logic around the reduction."""
+    world_size, rank, epoch, uid = 2, 0, 1, 1
+
+    def gate(self, step, timeout_s=0.0):
+        return True
+
+    def membership_changed(self):
+        return False
+
+    def are_peers_pending(self):
+        return False
+
+
+class _HalfAppliedStep:
+    """Stands in for the fused reduction when a peer falls silent after the first bucket: the action model's
+    optimizer has run (parameters, moments, masters and its step counter moved on), the frame head's has not."""
+    rank, world_size, grad_scale = 0, 2, 1.0
+
+    def reduce_and_step(self, trainer):
+        opt = trainer.optimizers["action_model"]
+        shard = (self.rank, self.world_size)                  # the fused kernels update this member's slice only
+        if getattr(opt, "groups", None) is not None:
+            opt.step(shard=shard)
+        elif hasattr(opt, "muon"):
+            opt.step_count += 1
+            opt.muon.step()
+            opt.adam.step(shard=shard) if opt.adam.groups is not None else opt.adam.step()
+        else:
+            opt.step()
+        return True
+
+
+def _state_of(trainer):
+    out = {"param/" + n: p.detach().clone() for n, p in trainer.model.named_parameters()}
+    for scope, opt in trainer.optimizers.items():
+        for name, t in opt.state_tensors().items():
+            out[scope + "/" + name] = t.detach().clone()
+        out[scope + "/step_count"] = torch.tensor(opt.step_count)
+    return out
+
+
+def test_dropped_fused_step_leaves_no_trace(monkeypatch):
+    """A fused step that reports an expired device-side wait after part of it was applied is undone as a whole:
+    parameters, every optimizer tensor and the step counters equal their values before the step."""
+    from fbamtrain_b200 import RunConfiguration, Trainer, presets
+    from fbamtrain_b200.data import SyntheticBatchSource
+    from fbamtrain_b200.parallel.ft_dp import FaultTolerantDataParallel
+    torch.manual_seed(0)
+    for kind in ("adamw", "muon"):
+        d = presets.tiny()
+        d["optimizer"]["type"] = kind
+        cfg = RunConfiguration.from_json(d)
+        tr = Trainer(cfg, device=torch.device("cpu"))
+        src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=1, pin=False)
+        cells, tg = src.next_batch(cfg.micro_batch_size, cfg.train_sequence_length)
+        tr.train_step(cells, tg)                       # one committed step: moments and counters are non-trivial
+        tr.zero_grad()
+        tr._forward_backward(cells, tg)                # gradients of the step that will be dropped
+        before = _state_of(tr)
+        ft = FaultTolerantDataParallel(_FakePeer(), expected_world=2, mode="fused")
+        ft.inner = _HalfAppliedStep()
+        monkeypatch.setattr(ft, "_fused_step_completed", lambda trainer: False)
+        monkeypatch.setattr(ft, "_retopologize", lambda trainer, joining=False: True)
+        monkeypatch.setattr(ft, "_sync_state", lambda trainer, joining=False: True)
+        assert ft.reduce_and_step(tr) is False
+        assert ft.dropped_steps == 1
+        after = _state_of(tr)
+        assert before.keys() == after.keys()
+        for k in before:
+            assert torch.equal(before[k], after[k]), (kind, k)
+        # and the half-applied step really had changed something before the rollback
+        ft2 = FaultTolerantDataParallel(_FakePeer(), expected_world=2, mode="fused")
+        ft2.inner = _HalfAppliedStep()
+        monkeypatch.setattr(ft2, "_fused_step_completed", lambda trainer: True)
+        assert ft2.reduce_and_step(tr) is True
+        changed = _state_of(tr)
+        assert any(not torch.equal(before[k], changed[k]) for k in before if k.startswith("action_model/")), kind
+        tr.close()

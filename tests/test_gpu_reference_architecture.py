@@ -1,7 +1,6 @@
 """The reference's own architecture (its sample run configuration scaled down: attention layers inside the frame
 head, dilated / GeGLU downsampling convolutions followed by 2x2 average pooling, last-position / mean reduction, one
-LSTM layer straight into the LM head) on the native kernels against the PyTorch op definitions.  Not yet run on a GPU
-when it was written; it sits in a file of its own, last in the order, so that it cannot mask other results."""
+LSTM layer straight into the LM head) on the native kernels against the PyTorch op definitions."""
 import copy
 
 import pytest

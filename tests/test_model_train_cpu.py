@@ -277,6 +277,29 @@ def test_newton_schulz_orthogonalises_and_muon_step():
     assert [n for n, _ in aux.muon.named_params] == ["w"] and [n for n, _ in aux.adam.named_params] == ["b"]
 
 
+def test_muon_momentum_is_the_reference_moving_average():
+    """The stored momentum tensor follows the reference's rule ``m = β·m + (1 − β)·g`` with the update
+    ``(1 − β)·g + β·m`` (reference: ``src/optimizers.cpp:1204-1226``), so a momentum tensor written by the reference
+    continues correctly here: the step taken from such a tensor equals the step computed by hand from that rule."""
+    torch.manual_seed(5)
+    beta, lr = 0.95, 0.02
+    p = torch.nn.Parameter(torch.randn(24, 40))
+    opt = MuonOptimizer([("w", p)], "o/muon", lr=lr, momentum=beta, nesterov=True, weight_decay=0.0)
+    m_ref = torch.zeros(24, 40)
+    for g in (torch.randn(24, 40), torch.randn(24, 40)):            # two steps of the reference's rule, by hand
+        m_ref = beta * m_ref + (1 - beta) * g
+    opt.state["w"]["momentum"].copy_(m_ref)                          # as if loaded from a reference checkpoint
+    g3 = torch.randn(24, 40)
+    before = p.detach().clone()
+    p.grad = g3.clone()
+    opt.step()
+    m3 = beta * m_ref + (1 - beta) * g3
+    assert torch.allclose(opt.state["w"]["momentum"], m3, atol=1e-6)
+    upd = (1 - beta) * g3 + beta * m3
+    expect = before - lr * newton_schulz(upd, 5).float() * max(1.0, 24 / 40) ** 0.5
+    assert torch.allclose(p, expect, atol=5e-3)
+
+
 # ----------------------------------------------------------------------------- reference ops
 def test_cell_embed_formula():
     torch.manual_seed(4)
