@@ -82,13 +82,13 @@ def test_reduce_pull_and_push_shard_emulated():
         total += g.float()
     lo, hi = 512, 2048
     buf = torch.randn(hi - lo, device=DEV)
-    expect_buf = 0.9 * buf + total[lo:hi]
+    expect_buf = 0.9 * buf + 0.1 * total[lo:hi]              # moving average, as the reference keeps it
     out = torch.empty(hi - lo, device=DEV, dtype=BF)
     sumsq = torch.zeros(1, device=DEV)
     nv.check(nv.lib().fbam_reduce_pull(grads[0].c_ptrs, nv.ptr(buf), nv.ptr(out), nv.ptr(sumsq), C.c_longlong(lo),
                                        C.c_longlong(hi), 1, C.c_float(0.9), 1, C.c_float(1.0), world,
                                        nv.stream_ptr()), "fbam_reduce_pull")
-    u = total[lo:hi] + 0.9 * expect_buf
+    u = 0.1 * total[lo:hi] + 0.9 * expect_buf
     assert torch.allclose(buf, expect_buf, atol=1e-5)
     assert torch.allclose(out.float(), u, atol=3e-2, rtol=1e-2)
     assert abs(float(sumsq) - float((u * u).sum())) / float((u * u).sum()) < 1e-3
