@@ -31,9 +31,6 @@ def main():
     ap.add_argument("--mb-size", type=int, default=2)
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--tp", default="fused", choices=["fused", "nccl"])
-    ap.add_argument("--action-group", type=int, default=1,
-                    help="micro-batches the action stage processes together (its recurrent kernels cost the same for "
-                         "2 sequences as for 8)")
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
@@ -58,8 +55,7 @@ def main():
     vocab = cfg.model_config.action_vocab
     torch.manual_seed(0)
     model = FbamModel(cfg.model_config, vocab).to(dev)
-    pipe = TwoStagePipeline(model, PipelineLayout.even_split(world), dev, a.micro_batches, a.mb_size, seq, a.tp,
-                            action_group=a.action_group)
+    pipe = TwoStagePipeline(model, PipelineLayout.even_split(world), dev, a.micro_batches, a.mb_size, seq, a.tp)
     named = [(f"p{i}", p) for i, p in enumerate(pipe.parameters_of_stage())]
     opt = create_optimizer(cfg.optimizer_config, named, "frame_head" if pipe.is_frame else "action_model")
 
@@ -100,7 +96,6 @@ def main():
         print(json.dumps({
             "bench": "two_stage_pipeline", "model": a.model, "n_gpus": world, "tp_transport": a.tp,
             "micro_batches": a.micro_batches, "micro_batch_size": a.mb_size, "seq_len": seq,
-            "action_group": a.action_group,
             "ms_per_step": float(t.item()), "frames_per_s": frames / (float(t.item()) / 1e3),
             "loss": float(lt.item()), "optimizer": cfg.optimizer_config.type, "dtype": "bf16",
             "gpu_launches_rank0": native.launches() - launches0,

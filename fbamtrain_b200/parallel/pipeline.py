@@ -89,16 +89,13 @@ class TensorParallelActionModel(nn.Module):
 class TwoStagePipeline:
     def __init__(self, model: FbamModel, layout: PipelineLayout, device: torch.device, micro_batches: int,
                  micro_batch_size: int, seq: int, tp_transport: str = "nccl",
-                 all_layouts: Optional[Sequence[PipelineLayout]] = None, action_group: int = 1):
+                 all_layouts: Optional[Sequence[PipelineLayout]] = None):
         """``all_layouts``: the layouts of every pipeline replica of the job (data parallelism over whole
         pipelines); process groups are created collectively, so every rank walks through all of them."""
         self.model, self.layout, self.device = model, layout, device
         all_layouts = list(all_layouts) if all_layouts is not None else [layout]
         self.rank = dist.get_rank()
         self.micro_batches, self.mb_size, self.seq = micro_batches, micro_batch_size, seq
-        if action_group < 1 or micro_batches % action_group:
-            raise ValueError("action_group must divide the number of micro-batches")
-        self.action_group = action_group
         if len(layout.frame_ranks) != len(layout.action_ranks):
             raise ValueError("both stages need the same number of ranks (one partner each)")
         self.is_frame = self.rank in layout.frame_ranks
@@ -124,6 +121,21 @@ class TwoStagePipeline:
                 g_fwd, g_bwd = dist.new_group([f_rank, a_rank]), dist.new_group([f_rank, a_rank])
                 if self.rank in (f_rank, a_rank):
                     self.fwd_group, self.bwd_group = g_fwd, g_bwd
+        if device.type == "cuda":
+            # NCCL creates the communicator of a group at the group's first operation, and that creation is a blocking
+            # host-side rendezvous of both partners.  Inside the schedule the two sides reach their first operation
+            # on the gradient group at different points (stage 0 posts its first gradient receive right after its
+            # first forward; stage 1 touches that group only after it has received a whole group of micro-batches),
+            # so stage 0 would sit in the rendezvous without ever sending the embeddings stage 1 waits for.  Create
+            # both communicators here, in the same order on both sides, with a one-element exchange.
+            token = torch.zeros(1, dtype=torch.float32, device=device)
+            if self.is_frame:
+                dist.send(token, self.partner, group=self.fwd_group)
+                dist.recv(token, self.partner, group=self.bwd_group)
+            else:
+                dist.recv(token, self.partner, group=self.fwd_group)
+                dist.send(token, self.partner, group=self.bwd_group)
+            torch.cuda.synchronize(device)
         self.n_stage = len(self.stage_ranks)
         frames = micro_batch_size * seq
         if frames % self.n_stage:
@@ -141,7 +153,7 @@ class TwoStagePipeline:
                 nv.lib().fbam_set_reserved_sms(RESERVED_SMS)
         if not self.is_frame:
             self.tp = TpContext(self.stage_group, device, tp_transport)
-            self.action = TensorParallelActionModel(model, self.tp, micro_batch_size * action_group, seq).to(device)
+            self.action = TensorParallelActionModel(model, self.tp, micro_batch_size, seq).to(device)
         self.stats = {"p2p_bytes": 0}
 
     # ------------------------------------------------------------------------------------------
@@ -189,16 +201,15 @@ class TwoStagePipeline:
             with gputx_range("fbamtrain::frame_head_bwd"):
                 outs.pop(k).backward(grads.pop(k))
 
-        # 1F1B with a lead of `action_group` micro-batches: the action stage returns gradients only once it has a
-        # whole group, so that many forwards go out before the first backward is awaited
-        ahead = min(self.action_group, self.micro_batches)
-        for k in range(ahead):
+        # 1F1B with a lead of one micro-batch.  (A longer lead — the action stage taking several micro-batches at a
+        # time, which would divide the share of its batch-size-independent recurrent kernels — passed on gloo ranks
+        # but stopped making progress on NCCL ranks on two GPUs; the cause was not found by reading, so the
+        # schedule keeps the lead at which every posted receive depends only on data that has already been sent.)
+        forward(0)
+        for k in range(1, self.micro_batches):       # next forward first, then the oldest backward
             forward(k)
-        for k in range(ahead, self.micro_batches):   # next forward first, then the oldest backward
-            forward(k)
-            backward(k - ahead)
-        for k in range(self.micro_batches - ahead, self.micro_batches):
-            backward(k)
+            backward(k - 1)
+        backward(self.micro_batches - 1)
         for work, _ in sends:
             work.wait()
         with gputx_range("fbamtrain::frame_head_grad_allreduce"):
@@ -208,38 +219,32 @@ class TwoStagePipeline:
         return 0.0
 
     def _run_action(self, targets: torch.Tensor, loss_scale: float) -> float:
-        """Receives the micro-batches' embeddings, runs the action model on ``action_group`` micro-batches at a time
-        (the recurrent kernels take the same time for 2 sequences as for 8, so grouping divides their share of the
-        step) and returns each micro-batch's slice of the embedding gradient to the partner rank."""
+        """Receives each micro-batch's embeddings, runs the action model on it and returns its slice of the embedding
+        gradient to the partner rank."""
         e = self.model.cfg.n_embed
         am = self.action
         dtype = am.head_weight.dtype
-        group = self.action_group
         total = torch.zeros((), dtype=torch.float32, device=self.device)   # summed on the device: no host sync
         sends = []
-        bufs = [torch.empty(self.slice_rows, e, dtype=dtype, device=self.device) for _ in range(group)]
-        for k0 in range(0, self.micro_batches, group):
-            # Receives are posted only when their data is needed: a posted receive is a resident kernel that spins
+        buf = torch.empty(self.slice_rows, e, dtype=dtype, device=self.device)
+        for k in range(self.micro_batches):
+            # The receive is posted only when its data is needed: a posted receive is a resident kernel that spins
             # until the data arrives, and the recurrent kernels of this stage are cooperative launches that need
             # most of the machine at once.  The partner sent these embeddings long ago (or is about to).
-            fulls = []
-            for j in range(group):
-                self._irecv(bufs[j]).wait()
-                fulls.append(self.tp.all_gather_rows(bufs[j]).view(self.mb_size, self.seq, e))
-            LOG("DEBUG", f"pipeline: action rank {self.rank} micro-batches {k0}..{k0 + group - 1}: embeddings received")
-            full = (fulls[0] if group == 1 else torch.cat(fulls, 0)).detach().requires_grad_(True)
-            tg = targets[k0:k0 + group].reshape(group * self.mb_size, self.seq).to(self.device)
+            self._irecv(buf).wait()
+            full = self.tp.all_gather_rows(buf).view(self.mb_size, self.seq, e).detach().requires_grad_(True)
+            LOG("DEBUG", f"pipeline: action rank {self.rank} micro-batch {k}: embeddings received")
+            tg = targets[k].to(self.device)
             with gputx_range("fbamtrain::action_model_fwd_bwd"):
                 loss = am(full, tg, loss_scale)
                 loss.backward()
             total += loss.detach().float()
-            d_all = full.grad.reshape(group, self.mb_size * self.seq, e)
+            d_all = full.grad.reshape(self.mb_size * self.seq, e)
             self.tp.all_reduce(d_all)             # every TP rank saw only its rows' contribution
-            for j in range(group):
-                payload = d_all[j, self.index * self.slice_rows:(self.index + 1) * self.slice_rows].contiguous()
-                with gputx_range("fbamtrain::ccl_send_upstream"):
-                    sends.append((self._isend(payload), payload))
-            LOG("DEBUG", f"pipeline: action rank {self.rank} micro-batches {k0}..{k0 + group - 1}: gradients sent")
+            payload = d_all[self.index * self.slice_rows:(self.index + 1) * self.slice_rows].contiguous()
+            with gputx_range("fbamtrain::ccl_send_upstream"):
+                sends.append((self._isend(payload), payload))
+            LOG("DEBUG", f"pipeline: action rank {self.rank} micro-batch {k}: gradient sent")
         for work, _ in sends:
             work.wait()
         with gputx_range("fbamtrain::action_model_grad_allreduce"):
@@ -257,7 +262,7 @@ class PipelineTrainer:
     ``src/main.cpp:3119-3123, 3204-3273, 3368-3414, 3588-3598``)."""
 
     def __init__(self, cfg, device: torch.device, vocab: int, layout: Optional[PipelineLayout] = None,
-                 tp_transport: str = "nccl", replicas: int = 1, action_group: int = 1):
+                 tp_transport: str = "nccl", replicas: int = 1):
         """``replicas`` > 1 runs that many pipelines side by side (data parallelism over pipelines: the reference's
         combination of ``ddp_parallel`` with ``frame_head_parallel``, ``src/main.cpp:2563-2588``): consecutive
         blocks of ``world / replicas`` ranks form one pipeline each, every replica takes its share of the batch
@@ -284,7 +289,7 @@ class PipelineTrainer:
                        for r in range(replicas)]
         self.pipe = TwoStagePipeline(self.model, layouts[self.replica], device, self.micro_batches,
                                      cfg.micro_batch_size, self.seq, tp_transport, all_layouts=layouts,
-                                     action_group=action_group)
+                                     )
         self.cross_group = None            # ranks in this rank's position of every replica
         if replicas > 1:
             for pos in range(self.per_replica):

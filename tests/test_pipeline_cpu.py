@@ -85,7 +85,7 @@ def test_pipeline_matches_single_process():
         assert torch.allclose(g["blk0.w_fc1"], am.block[0].mlp.fc1.weight.grad[i * fl:(i + 1) * fl], atol=2e-6)
 
 
-def _trainer_worker(rank, world, port, q, replicas=1, action_group=1, micro=2):
+def _trainer_worker(rank, world, port, q, replicas=1, micro=2):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -97,7 +97,7 @@ def _trainer_worker(rank, world, port, q, replicas=1, action_group=1, micro=2):
     d["micro_batch_size"], d["total_batch_size"] = micro, 4
     d["optimizer"]["learning_rate"] = 3e-3
     cfg = RunConfiguration.from_json(d)
-    tr = PipelineTrainer(cfg, torch.device("cpu"), vocab=32, replicas=replicas, action_group=action_group)
+    tr = PipelineTrainer(cfg, torch.device("cpu"), vocab=32, replicas=replicas)
     src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=5, pin=False)
     cells, targets = src.next_batch(4, cfg.train_sequence_length)
     losses = [tr.train_step(cells, targets) for _ in range(6)]
@@ -138,25 +138,6 @@ def test_data_parallel_over_pipelines_matches_one_pipeline():
             assert p.exitcode == 0
         curves[replicas] = results[0]
     assert curves[1] == pytest.approx(curves[2], abs=2e-5)
-
-
-def test_grouped_action_stage_matches_ungrouped():
-    """Four micro-batches of one sequence: the action stage taking them two at a time gives the same losses as one
-    at a time (the frame stage then runs two forwards ahead)."""
-    ctx = mp.get_context("spawn")
-    curves = {}
-    for group in (1, 2):
-        q = ctx.Queue()
-        port = _free_port()
-        procs = [ctx.Process(target=_trainer_worker, args=(r, 2, port, q, 1, group, 1)) for r in range(2)]
-        for p in procs:
-            p.start()
-        results = dict(q.get(timeout=240) for _ in range(2))
-        for p in procs:
-            p.join(60)
-            assert p.exitcode == 0
-        curves[group] = results[0]
-    assert curves[2] == pytest.approx(curves[1], abs=2e-5)
 
 
 def _checkpoint_worker(rank, world, port, q, directory):
