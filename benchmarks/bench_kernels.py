@@ -6,6 +6,7 @@
     python benchmarks/bench_kernels.py lstm  [--t 1024 --b 8 --hidden 1024]
     python benchmarks/bench_kernels.py lstm-stream [--t 1024 --b 8 --hidden 1024 --vocab 4096 --chunk 64] [--offload]
     python benchmarks/bench_kernels.py mha   [--b 8 --heads 8 --t 1024 --d 128] [--causal]
+    python benchmarks/bench_kernels.py simt  [--rows 16384 --dim 1024 --vocab 4096 --numel 67108864]
     python benchmarks/bench_kernels.py embconv [--frames 1024 --rows 48 --cols 160 --vocab 512 --cin 128 --cout 256
                                                 --change 0.05]
 
@@ -224,6 +225,42 @@ def bench_embconv(a):
            flops=2.0 * pix * 64 * o, bytes_moved=pix * 128 + pix * o * 2)
 
 
+def bench_simt(a):
+    """The bandwidth-bound kernels on sizes larger than L2: RMSNorm forward / backward, LayerNorm forward / backward,
+    cross-entropy forward + backward on fp32 logits, the fused AdamW step."""
+    from fbamtrain_b200.ops import native as nv
+    from fbamtrain_b200.ops import native_ops as no
+    import ctypes as C
+    rows, dim = a.rows, a.dim
+    x = torch.randn(rows, dim, device="cuda").bfloat16().requires_grad_(True)
+    w = torch.ones(dim, device="cuda").bfloat16().requires_grad_(True)
+    b = torch.zeros(dim, device="cuda").bfloat16().requires_grad_(True)
+    g = torch.randn(rows, dim, device="cuda").bfloat16()
+    report(f"rmsnorm_fwd {rows}x{dim}", timeit(lambda: no.rms_norm(x.detach(), w.detach(), 1e-5)),
+           bytes_moved=2 * rows * dim * 2)
+    y = no.rms_norm(x, w, 1e-5)
+    report(f"rmsnorm_fwd_bwd {rows}x{dim}",
+           timeit(lambda: torch.autograd.grad(no.rms_norm(x, w, 1e-5), (x, w), g)), bytes_moved=5 * rows * dim * 2)
+    report(f"layernorm_fwd_bwd {rows}x{dim}",
+           timeit(lambda: torch.autograd.grad(no.layer_norm(x, w, b, 1e-5), (x, w, b), g)), bytes_moved=5 * rows * dim * 2)
+    vrows, vocab = 4096, a.vocab
+    logits = torch.randn(vrows, vocab, device="cuda")
+    dlogits = torch.empty(vrows, vocab, device="cuda", dtype=torch.bfloat16)
+    tg = torch.randint(0, vocab, (vrows,), device="cuda")
+    loss = torch.zeros(1, device="cuda")
+    report(f"ce_fwd_bwd_f32 {vrows}x{vocab}",
+           timeit(lambda: nv.check(nv.lib().fbam_ce_fwd_bwd_f32(nv.ptr(logits), nv.ptr(dlogits), nv.ptr(tg), nv.ptr(loss),
+                                                               C.c_longlong(vrows), vocab, vocab, C.c_float(1.0),
+                                                               nv.stream_ptr()), "fbam_ce_fwd_bwd_f32")),
+           bytes_moved=vrows * vocab * 6)
+    n = a.numel
+    p = torch.randn(n, device="cuda").bfloat16()
+    gr = torch.randn(n, device="cuda").bfloat16()
+    m, v, master = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda"), p.float()
+    report(f"adamw bf16 {n}", timeit(lambda: no.adamw_flat(p, gr, m, v, master, 0, n, 1e-3, 0.9, 0.999, 1e-8, 0.1, 0.1, 0.001)),
+           bytes_moved=n * (2 + 2 + 4 * 3 * 2))
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -252,13 +289,16 @@ def main():
     for name, default in (("b", 8), ("heads", 8), ("t", 1024), ("d", 128)):
         m.add_argument("--" + name, type=int, default=default)
     m.add_argument("--causal", action="store_true")
+    sm = sub.add_parser("simt")
+    for name, default in (("rows", 16384), ("dim", 1024), ("vocab", 4096), ("numel", 64 * 1024 * 1024)):
+        sm.add_argument("--" + name, type=int, default=default)
     e = sub.add_parser("embconv")
     for name, default in (("frames", 1024), ("rows", 48), ("cols", 160), ("vocab", 512), ("cin", 128), ("cout", 256)):
         e.add_argument("--" + name, type=int, default=default)
     e.add_argument("--change", type=float, default=0.05)
     a = ap.parse_args()
     {"gemm": bench_gemm, "conv": bench_conv, "lstm": bench_lstm, "lstm-stream": bench_lstm_stream,
-     "mha": bench_mha, "embconv": bench_embconv}[a.cmd](a)
+     "mha": bench_mha, "embconv": bench_embconv, "simt": bench_simt}[a.cmd](a)
 
 
 if __name__ == "__main__":

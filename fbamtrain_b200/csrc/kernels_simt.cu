@@ -5,7 +5,7 @@
 //
 // Reference kernel families covered: build_cell_embeds and its three backward kernels
 // (kernel_gen/kernel_gen/kernels/build_cell_embeds.py:23-248, build_cell_embeds_bwd.py:6-322), rms_norm fwd / bwd
-// (kernels/rms_norm.py:14-104), layer_norm fwd (kernels/layer_norm.py:13-90), cross_entropy_on_targets fwd / bwd
+// (kernels/rms_norm.py:14-104), layer_norm fwd (kernels/layer_norm.py:13-90; the backward here has no counterpart there), cross_entropy_on_targets fwd / bwd
 // (kernels/cross_entropy.py:23-58, cross_entropy_bwd.py:22-66), avg_pool2d NHWC 2x2 fwd / bwd and the mean over
 // positions (kernels/avg_pool2d.py:35-144, avg_pool2d_bwd.py:6-214, mean_reduce.py:30-108), column sums for bias
 // gradients (kernels/sum_reduce.py:33-140), GELU / GeGLU and their gradients (kernels/act.py:43-86), and the AdamW
@@ -216,6 +216,89 @@ __global__ void layernorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __r
     float o = (__bfloat162float(xr[c]) - mean) * r * __bfloat162float(w[c]);
     if (b != nullptr) o += __bfloat162float(b[c]);
     y[row * dim + c] = __float2bfloat16(o);
+  }
+}
+
+// LayerNorm forward that also keeps the row statistics for the backward.
+__global__ void layernorm_fwd_stats_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                           const bf16* __restrict__ b, bf16* __restrict__ y, float* __restrict__ mean_out,
+                                           float* __restrict__ rstd_out, int dim, float eps) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const bf16* xr = x + row * dim;
+  float s = 0.0f;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) s += __bfloat162float(xr[c]);
+  const float mean = block_sum(s, scratch) / dim;
+  float q = 0.0f;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    const float d = __bfloat162float(xr[c]) - mean;
+    q += d * d;
+  }
+  const float r = rsqrtf(block_sum(q, scratch) / dim + eps);
+  if (threadIdx.x == 0) {
+    mean_out[row] = mean;
+    rstd_out[row] = r;
+  }
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    float o = (__bfloat162float(xr[c]) - mean) * r * __bfloat162float(w[c]);
+    if (b != nullptr) o += __bfloat162float(b[c]);
+    y[row * dim + c] = __float2bfloat16(o);
+  }
+}
+
+// LayerNorm backward.  With xh = (x - mean) * rstd and g = dy * w:
+//   dx = rstd * (g - mean_c(g) - xh * mean_c(g * xh)),   dw[c] += sum_rows dy * xh,   db[c] += sum_rows dy.
+// A block walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; a thread owns columns threadIdx.x + k * blockDim.x
+// (k < COLS) and keeps their dw / db sums in registers across its rows: one atomic per column and block at the end.
+template <int COLS>
+__global__ void __launch_bounds__(256) layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                            const bf16* __restrict__ w, const float* __restrict__ mean,
+                                                            const float* __restrict__ rstd, bf16* __restrict__ dx,
+                                                            float* __restrict__ dw, float* __restrict__ db,
+                                                            long long rows, int dim) {
+  __shared__ float scratch[32];
+  float wreg[COLS], dw_acc[COLS], db_acc[COLS];
+#pragma unroll
+  for (int k = 0; k < COLS; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    wreg[k] = c < dim ? __bfloat162float(w[c]) : 0.0f;
+    dw_acc[k] = 0.0f;
+    db_acc[k] = 0.0f;
+  }
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float m = mean[row], r = rstd[row];
+    float xh[COLS], g[COLS];
+    float sg = 0.0f, sgx = 0.0f;
+#pragma unroll
+    for (int k = 0; k < COLS; ++k) {
+      const int c = threadIdx.x + k * blockDim.x;
+      xh[k] = 0.0f;
+      g[k] = 0.0f;
+      if (c < dim) {
+        const float d = __bfloat162float(dy[row * dim + c]);
+        xh[k] = (__bfloat162float(x[row * dim + c]) - m) * r;
+        g[k] = d * wreg[k];
+        dw_acc[k] += d * xh[k];
+        db_acc[k] += d;
+        sg += g[k];
+        sgx += g[k] * xh[k];
+      }
+    }
+    const float mg = block_sum(sg, scratch) / dim;
+    const float mgx = block_sum(sgx, scratch) / dim;
+#pragma unroll
+    for (int k = 0; k < COLS; ++k) {
+      const int c = threadIdx.x + k * blockDim.x;
+      if (c < dim) dx[row * dim + c] = __float2bfloat16(r * (g[k] - mg - xh[k] * mgx));
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < COLS; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < dim) {
+      atomicAdd(dw + c, dw_acc[k]);
+      if (db != nullptr) atomicAdd(db + c, db_acc[k]);
+    }
   }
 }
 
@@ -829,6 +912,33 @@ int fbam_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* 
   if (dim <= 1024) return launch_rms_bwd<4>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
   if (dim <= 2048) return launch_rms_bwd<8>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
   return launch_rms_bwd<16>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
+}
+
+// mean / rstd: fp32 [rows], kept for fbam_layernorm_bwd
+int fbam_layernorm_fwd_stats(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                             long long rows, int dim, float eps, void* stream) {
+  if (rows <= 0 || dim <= 0) return rows == 0 ? 0 : 1;
+  layernorm_fwd_stats_kernel<<<(unsigned)rows, 256, 0, STREAM(stream)>>>((const bf16*)x, (const bf16*)w, (const bf16*)b,
+                                                                        (bf16*)y, mean, rstd, dim, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+
+// dw, db: fp32 [dim], added to (the caller zeroes them); db may be null.  dim <= 8192.
+int fbam_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                       float* dw, float* db, long long rows, int dim, void* stream) {
+  if (rows <= 0 || dim <= 0) return rows == 0 ? 0 : 1;
+  if (dim > 8192) return 1;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const unsigned grid = (unsigned)(rows < 4ll * sms ? rows : 4ll * sms);
+  const bf16 *dyp = (const bf16*)dy, *xp = (const bf16*)x, *wp = (const bf16*)w;
+  cudaStream_t s = STREAM(stream);
+  if (dim <= 1024) layernorm_bwd_kernel<4><<<grid, 256, 0, s>>>(dyp, xp, wp, mean, rstd, (bf16*)dx, dw, db, rows, dim);
+  else if (dim <= 2048) layernorm_bwd_kernel<8><<<grid, 256, 0, s>>>(dyp, xp, wp, mean, rstd, (bf16*)dx, dw, db, rows, dim);
+  else if (dim <= 4096) layernorm_bwd_kernel<16><<<grid, 256, 0, s>>>(dyp, xp, wp, mean, rstd, (bf16*)dx, dw, db, rows, dim);
+  else layernorm_bwd_kernel<32><<<grid, 256, 0, s>>>(dyp, xp, wp, mean, rstd, (bf16*)dx, dw, db, rows, dim);
+  return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 
 int fbam_layernorm_fwd(const void* x, const void* w, const void* b, void* y, long long rows, int dim, float eps,

@@ -53,8 +53,8 @@ class Linear(nn.Module):
         else:
             self.bias = None
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(x, self.weight, self.bias, self.act)
+    def forward(self, x: torch.Tensor, residual: torch.Tensor = None) -> torch.Tensor:
+        return ops.linear(x, self.weight, self.bias, self.act, residual)
 
 
 class Embedding(nn.Module):
@@ -92,8 +92,8 @@ class MlpBlock(nn.Module):
         self.fc1 = Linear(dim, hidden, bias, dtype, seeds, act="gelu")
         self.fc2 = Linear(hidden, dim, bias, dtype, seeds)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.fc2(self.fc1(x))
+    def forward(self, x: torch.Tensor, residual: torch.Tensor = None) -> torch.Tensor:
+        return self.fc2(self.fc1(x), residual)
 
 
 class FullMhaAttention(nn.Module):
@@ -105,12 +105,13 @@ class FullMhaAttention(nn.Module):
         self.qkv = Linear(dim, 3 * dim, bias, dtype, seeds)
         self.proj = Linear(dim, dim, bias, dtype, seeds)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: torch.Tensor = None) -> torch.Tensor:
         b, t, e = x.shape
         d = e // self.n_head
         qkv = self.qkv(x.reshape(b * t, e)).view(b, t, 3, self.n_head, d)
-        o = ops.attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], self.causal)
-        return self.proj(o.reshape(b * t, e)).view(b, t, e)
+        o = ops.attention_qkv(qkv, self.causal)
+        res = None if residual is None else residual.reshape(b * t, e)
+        return self.proj(o.reshape(b * t, e), res).view(b, t, e)
 
 
 class AttentionBlock(nn.Module):
@@ -123,7 +124,8 @@ class AttentionBlock(nn.Module):
         self.mlp = MlpBlock(dim, mlp_dim, bias, dtype, seeds)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        x = x + self.attn(self.ln1(x))
+        # the residual additions ride in the epilogues of the output-projection and second MLP GEMMs
+        x = self.attn(self.ln1(x), residual=x)
         b, t, e = x.shape
-        x = x + self.mlp(self.ln2(x).reshape(b * t, e)).view(b, t, e)
-        return x
+        x2 = x.reshape(b * t, e)
+        return self.mlp(self.ln2(x).reshape(b * t, e), residual=x2).view(b, t, e)

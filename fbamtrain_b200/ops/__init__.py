@@ -9,9 +9,9 @@ forces the PyTorch definitions on GPU as well — that is how the cuBLAS/cuDNN/S
 from __future__ import annotations
 
 from . import reference
-from .dispatch import (attention, avg_pool2x2_nhwc, cell_conv_gelu_stack_pool, cell_embed, conv2d_nhwc, conv_gelu_stack_pool, geglu, gelu, get_backend,
+from .dispatch import (attention, attention_qkv, avg_pool2x2_nhwc, cell_conv_gelu_stack_pool, cell_embed, conv2d_nhwc, conv_gelu_stack_pool, geglu, gelu, get_backend,
                        layer_norm, linear, lm_head_ce, lstm_sequence, rms_norm, set_backend, global_avg_pool_nhwc)
 
-__all__ = ["reference", "attention", "avg_pool2x2_nhwc", "cell_embed", "conv2d_nhwc", "geglu", "gelu",
+__all__ = ["reference", "attention", "attention_qkv", "avg_pool2x2_nhwc", "cell_embed", "conv2d_nhwc", "geglu", "gelu",
            "get_backend", "layer_norm", "linear", "lm_head_ce", "lstm_sequence", "rms_norm", "set_backend",
            "global_avg_pool_nhwc", "conv_gelu_stack_pool", "cell_conv_gelu_stack_pool"]

@@ -163,11 +163,14 @@ def cell_conv_gelu_stack_pool(cells, cp_embed, pos_embed, colour_embed, rows: in
     return conv_gelu_stack_pool(x, weights, stride, paddings, dilations)
 
 
-def linear(x, weight, bias: Optional[torch.Tensor] = None, act: str = "none"):
+def linear(x, weight, bias: Optional[torch.Tensor] = None, act: str = "none",
+           residual: Optional[torch.Tensor] = None):
+    """``act(x·Wᵀ + b) [+ residual]``; on the native path the residual rides in the GEMM epilogue."""
     if _native(x, family="gemm"):
         from .native_ops import linear as f
-        return f(x, weight, bias, act)
-    return ref.linear(x, weight, bias, act)
+        return f(x, weight, bias, act, residual)
+    y = ref.linear(x, weight, bias, act)
+    return y if residual is None else y + residual.reshape(y.shape)
 
 
 def attention(q, k, v, causal: bool):
@@ -179,6 +182,14 @@ def attention(q, k, v, causal: bool):
         o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal)
         return o.transpose(1, 2).contiguous()
     return ref.attention(q, k, v, causal)
+
+
+def attention_qkv(qkv, causal: bool):
+    """Attention on a fused projection output ``(B, T, 3, H, D)`` (q, k, v along dimension 2) → ``(B, T, H, D)``."""
+    if _native(qkv, family="mha"):
+        from .mha import flash_attention_qkv
+        return flash_attention_qkv(qkv, causal)
+    return attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], causal)
 
 
 def lstm_sequence(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype):

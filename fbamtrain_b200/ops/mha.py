@@ -50,7 +50,7 @@ class _FlashAttention(torch.autograd.Function):
         return out
 
     @staticmethod
-    def backward(ctx, d_out):
+    def backward(ctx, d_out, raw_dq=False):
         q, k, v, out, lse = ctx.saved_tensors
         b, t, h, d = q.shape
         if d_out.stride(3) != 1:
@@ -66,7 +66,36 @@ class _FlashAttention(torch.autograd.Function):
             nv.ptr(dk), nv.ptr(dv), b, t, h, d, int(ctx.causal), C.c_float(ctx.scale),
             nv.ptr(nv.status_word(q.device)), nv.stream_ptr()), "fbam_attn_bwd")
         flops.add(10.0 * b * h * t * t * d * (0.5 if ctx.causal else 1.0))   # 2.5 x forward
-        return dq32.to(BF16), dk, dv, None
+        return (dq32 if raw_dq else dq32.to(BF16)), dk, dv, None
+
+
+class _FlashAttentionQkv(torch.autograd.Function):
+    """Attention on the fused projection output ``qkv (B, T, 3, H, D)``: q, k and v are read in place as strided views
+    and the three gradients are written into one ``(B, T, 3, H, D)`` buffer, so autograd sees a single tensor in and
+    a single gradient out (separate q / k / v selections would each materialise a zero-filled full-size gradient)."""
+
+    @staticmethod
+    def forward(ctx, qkv, causal):
+        out = _FlashAttention.forward(ctx, qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], causal)
+        ctx.qkv_shape = qkv.shape
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        dq, dk, dv, _ = _FlashAttention.backward(ctx, d_out, raw_dq=True)
+        dqkv = torch.empty(ctx.qkv_shape, dtype=BF16, device=d_out.device)
+        dqkv[:, :, 0].copy_(dq)            # fp32 accumulator -> bf16, straight into its slice
+        dqkv[:, :, 1].copy_(dk)
+        dqkv[:, :, 2].copy_(dv)
+        return dqkv, None
+
+
+def flash_attention_qkv(qkv, causal):
+    """``qkv`` bf16 ``(B, T, 3, H, D)`` contiguous → ``(B, T, H, D)``."""
+    d = qkv.shape[-1]
+    if qkv.dtype == BF16 and d in (64, 128) and qkv.is_contiguous() and (3 * qkv.shape[3] * d * 2) % 16 == 0:
+        return _FlashAttentionQkv.apply(qkv, bool(causal))
+    return flash_attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], causal)
 
 
 def flash_attention(q, k, v, causal):

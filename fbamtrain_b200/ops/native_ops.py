@@ -65,6 +65,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     _need_bf16(a, b)
     if a.stride(-1) != 1 or b.stride(-1) != 1:
         raise ValueError("GEMM operands need unit inner stride")
+    a, b = _tma_pitch(a), _tma_pitch(b)
     m, k = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
     n, kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
     if k != kb:
@@ -123,6 +124,21 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+def _tma_pitch(t: torch.Tensor) -> torch.Tensor:
+    """TMA needs a 16-byte aligned base and row pitch.  An operand that has neither (an inner dimension that is not a
+    multiple of 8 elements, a slice that starts at an odd offset) is copied once into a buffer whose rows are padded
+    to the next multiple of 8 elements; the returned view has the original shape, so the extent TMA sees is unchanged
+    and reads past it are zero-filled.  (The reference keeps separate "unaligned" kernel variants for this:
+    ``src/passes/matmul_pass.cpp:3542-3563``.)"""
+    if t.data_ptr() % 16 == 0 and (t.stride(0) * t.element_size()) % 16 == 0:
+        return t
+    rows, cols = t.shape
+    per = 16 // t.element_size()
+    buf = torch.zeros(rows, (cols + per - 1) // per * per, dtype=t.dtype, device=t.device)
+    buf[:, :cols] = t
+    return buf[:, :cols]
+
+
 def _t(x: torch.Tensor) -> torch.Tensor:
     return x.t().contiguous()
 
@@ -162,14 +178,19 @@ def _gelu_bwd(preact: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
 
 class _Linear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, act):
+    def forward(ctx, x, weight, bias, act, residual=None):
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         preact = None
         if act == "gelu" and (x.requires_grad or weight.requires_grad):
             preact = torch.empty((x2.shape[0], weight.shape[0]), dtype=BF16, device=x.device)
-        y = gemm(x2, weight, bias=bias, act=act, preact_out=preact)
+        res2 = None
+        if residual is not None:            # added in the GEMM epilogue, after the activation
+            res2 = residual.reshape(-1, weight.shape[0])
+            if res2.stride(-1) != 1:
+                res2 = res2.contiguous()
+        y = gemm(x2, weight, bias=bias, act=act, preact_out=preact, residual=res2)
         if act == "relu":
             preact = y        # the output's sign is all the backward needs
         ctx.save_for_backward(x2, weight, preact)
@@ -193,12 +214,13 @@ class _Linear(torch.autograd.Function):
             dw = gemm_tn(dy2, x2)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = _colsum(dy2).to(BF16)
-        return dx, dw, db, None
+        d_res = dy if len(ctx.needs_input_grad) > 4 and ctx.needs_input_grad[4] else None
+        return dx, dw, db, None, d_res
 
 
-def linear(x, weight, bias=None, act="none"):
-    _need_bf16(x, weight, bias)
-    return _Linear.apply(x, weight, bias, act)
+def linear(x, weight, bias=None, act="none", residual=None):
+    _need_bf16(x, weight, bias, residual)
+    return _Linear.apply(x, weight, bias, act, residual)
 
 
 # =================================================================================================
@@ -502,13 +524,42 @@ def rms_norm(x, weight, eps):
     return _RmsNorm.apply(x, weight, eps)
 
 
+class _LayerNorm(torch.autograd.Function):
+    """LayerNorm with a native backward (the reference ships the forward only: ``tensorlib/include/layer_norm.h:12-78``)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        rows, dim = x2.shape
+        y = torch.empty_like(x2)
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        nv.check(nv.lib().fbam_layernorm_fwd_stats(nv.ptr(x2), nv.ptr(weight), nv.ptr(bias), nv.ptr(y), nv.ptr(mean),
+                                                   nv.ptr(rstd), C.c_longlong(rows), dim, C.c_float(eps),
+                                                   nv.stream_ptr()), "fbam_layernorm_fwd_stats")
+        ctx.save_for_backward(x2, weight, mean, rstd)
+        ctx.has_bias = bias is not None
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, mean, rstd = ctx.saved_tensors
+        rows, dim = x2.shape
+        dy2 = dy.reshape(rows, dim).contiguous()
+        dx = torch.empty_like(x2)
+        dw = torch.zeros(dim, dtype=torch.float32, device=x2.device)
+        db = torch.zeros(dim, dtype=torch.float32, device=x2.device) if ctx.has_bias else None
+        nv.check(nv.lib().fbam_layernorm_bwd(nv.ptr(dy2), nv.ptr(x2), nv.ptr(weight), nv.ptr(mean), nv.ptr(rstd),
+                                             nv.ptr(dx), nv.ptr(dw), nv.ptr(db), C.c_longlong(rows), dim,
+                                             nv.stream_ptr()), "fbam_layernorm_bwd")
+        return dx.view(dy.shape), dw.to(weight.dtype), (db.to(weight.dtype) if db is not None else None), None
+
+
 def layer_norm(x, weight, bias, eps):
     _need_bf16(x, weight, bias)
-    x2 = x.reshape(-1, x.shape[-1]).contiguous()
-    y = torch.empty_like(x2)
-    nv.check(nv.lib().fbam_layernorm_fwd(nv.ptr(x2), nv.ptr(weight), nv.ptr(bias), nv.ptr(y), C.c_longlong(x2.shape[0]),
-                                         x2.shape[1], C.c_float(eps), nv.stream_ptr()), "fbam_layernorm_fwd")
-    return y.view(x.shape)
+    if x.shape[-1] > 8192:
+        raise ValueError("native LayerNorm handles rows of up to 8192 elements")
+    return _LayerNorm.apply(x, weight, bias, eps)
 
 
 class _Gelu(torch.autograd.Function):

@@ -51,6 +51,22 @@ def test_gemm_mn_major_operands(a_mn, b_mn, m, n, k):
     assert _rel_err(d, expect) < 5e-3
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, True), (False, True)])
+@pytest.mark.parametrize("m,n,k", [(200, 100, 100), (128, 36, 52), (77, 130, 1001)])
+def test_gemm_operands_without_16_byte_pitch(m, n, k, a_mn, b_mn):
+    """Row pitches that are not multiples of 16 bytes (e.g. an embedding width of 100) and bases at odd offsets."""
+    nv, no = _nops()
+    torch.manual_seed(2)
+    a = torch.randn((k, m) if a_mn else (m, k), device=DEV).to(BF)
+    flat = torch.randn(n * k + 3, device=DEV).to(BF)
+    b = flat[3:].view((k, n) if b_mn else (n, k))                    # base address 6 bytes past an aligned one
+    out = no.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    af = a.float().t() if a_mn else a.float()
+    bf_ = b.float() if b_mn else b.float().t()
+    assert _rel_err(out, af @ bf_) < 1e-2
+    nv.check_status(a.device)
+
+
 @pytest.mark.parametrize("bm", [128, 256])
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, True)])
 def test_gemm_tall_tiles(bm, a_mn, b_mn):
@@ -186,6 +202,26 @@ def test_layernorm_gelu_geglu_pools():
         (ex,) = torch.autograd.grad(yf, xf, g.float())
         assert_similar(yf.to(BF), y, 2e-2)
         assert_similar(ex.to(BF), gx, 2e-2)
+
+
+@pytest.mark.parametrize("rows,dim,with_bias", [(100, 320, True), (700, 1024, True), (33, 2048, False), (9, 5000, True)])
+def test_layernorm_fwd_bwd(rows, dim, with_bias):
+    nv, no = _nops()
+    torch.manual_seed(8)
+    x = torch.randn(rows, dim, device=DEV).to(BF).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(dim, device=DEV)).to(BF).requires_grad_(True)
+    b = torch.randn(dim, device=DEV).to(BF).requires_grad_(True) if with_bias else None
+    params = (x, w, b) if with_bias else (x, w)
+    y = no.layer_norm(x, w, b, 1e-5)
+    g = torch.randn_like(y)
+    got = torch.autograd.grad(y, params, g)
+    fl = [t.detach().float().requires_grad_(True) for t in params]
+    yf = ref.layer_norm(fl[0], fl[1], fl[2] if with_bias else None, 1e-5)
+    want = torch.autograd.grad(yf, fl, g.float())
+    assert_similar(yf.to(BF), y, 3e-2)
+    for name, a, e in zip(("dx", "dw", "db"), got, want):
+        assert _rel_err(a, e) < 2e-2, (name, _rel_err(a, e))
+    nv.check_status(x.device)
 
 
 def test_cell_embed_fwd_bwd():
@@ -523,6 +559,32 @@ def test_non_bf16_models_train_on_the_library_path(dtype):
     losses = [float(tr.train_step(cells, tg)) for _ in range(4)]
     tr.close()
     assert all(math.isfinite(x) for x in losses) and losses[-1] < losses[0]
+
+
+def test_frame_head_recompute_gives_the_same_gradients():
+    """``frame_head_recompute`` keeps only the cells and runs the frame head again in the backward (the reference
+    replays frames and recomputes: ``src/main.cpp:3354-3483``): same loss, same gradients, less memory kept."""
+    from fbamtrain_b200 import RunConfiguration, Trainer, presets
+    from fbamtrain_b200.data import SyntheticBatchSource
+    results = {}
+    for recompute in (False, True):
+        d = presets.tiny("bf16")
+        d["model_config"].update({"cell_embed_dim": 64, "downsample_channels": [64, 128], "downsample_blocks": 2,
+                                  "n_embed": 64, "frame_rows": 16, "frame_cols": 24, "frame_head_recompute": recompute})
+        d["frame_rows"], d["frame_cols"] = 16, 24
+        cfg = RunConfiguration.from_json(d)
+        tr = Trainer(cfg, device=torch.device(DEV), frame_chunk=8)
+        src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point, tr.vocab, seed=3,
+                                   pin=False)
+        cells, tg = src.next_batch(cfg.micro_batch_size, cfg.train_sequence_length)
+        tr.zero_grad()
+        loss = tr._forward_backward(cells, tg)
+        results[recompute] = (float(loss), {n: p.grad.detach().float().clone()
+                                            for n, p in tr.model.frame_head.named_parameters()})
+        tr.close()
+    assert results[True][0] == pytest.approx(results[False][0], abs=1e-3)
+    for name, g in results[False][1].items():
+        assert _rel_err(results[True][1][name], g) < 2e-2, name
 
 
 def test_expected_backends_are_chosen_on_gpu():
