@@ -281,7 +281,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 // accumulators in TMEM (S_A, S_B, O_A, O_B = 256 + 2·D columns) and its own P buffer in shared memory; K and V
 // blocks (one stage each, loaded as soon as the MMAs that read the previous block have completed) are shared by
 // both tiles.  One elected thread issues all TMA loads and all MMAs in an order in which no tile ever waits for
-// the other: while one group is busy with its softmax, the tensor core works for the other one.
+// the other: while one group is busy with its softmax, the tensor core works for the other one.  The output
+// accumulators stay in tensor memory for the whole key loop (every P·V product adds to them); the softmax threads
+// rescale them there only when a row's reference maximum moves (see below), so a group goes from one block's softmax
+// straight to the next while its P·V product is still running.
 template <int D>
 __global__ void __launch_bounds__(288, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -309,7 +312,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb2 = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // causal: the tiles with the most key blocks are scheduled first
+  const int qb2 = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
   const int q0 = qb2 * 2 * BQ;
   const int nkb_all = (p.T + BKV - 1) / BKV;
   // key blocks each tile attends to (a tile that starts beyond the sequence has none)
@@ -375,13 +380,13 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
         mma_commit(&s_full[g]);
       };
-      auto issue_pv = [&](int g) {     // O_g block = P_g · V
+      auto issue_pv = [&](int g, bool first) {     // O_g (+)= P_g · V: accumulated over the key blocks in tensor memory
         const uint32_t p_addr = smem_u32(sP + g * kPBytes);
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
           const uint64_t da = make_smem_desc_sw128(p_addr + (k / 4) * BQ * 128 + (k % 4) * 32, 16, 1024);
           const uint64_t db = make_smem_desc_sw128(v_addr + k * 16 * 128, BKV * 128, 1024);
-          mma_f16_ss(tmem + 256 + g * D, da, db, idesc_pv, k != 0);
+          mma_f16_ss(tmem + 256 + g * D, da, db, idesc_pv, !first || k != 0);
         }
         mma_commit(&pv_full[g]);
       };
@@ -407,7 +412,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (kb < nkb_tile[0]) {
           if (!mbar_wait(&p_ready[0], ph)) { ok = false; break; }
           fence_after_sync();
-          issue_pv(0);
+          issue_pv(0, kb == 0);
         }
         if (more) {
           if (!mbar_wait(k_full, ph ^ 1)) { ok = false; break; }
@@ -417,7 +422,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (kb < nkb_tile[1]) {
           if (!mbar_wait(&p_ready[1], ph)) { ok = false; break; }
           fence_after_sync();
-          issue_pv(1);
+          issue_pv(1, kb == 0);
         }
         mma_commit(v_empty);
         if (more) {
@@ -440,94 +445,134 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const uint32_t tmem_s = tmem + g * 128, tmem_pv = tmem + 256 + g * D;
     uint8_t* sPg = sP + g * kPBytes;
     const int my_nkb = nkb_tile[g];
+    // m is the reference of the exponentials accumulated so far: p = 2^((s - m) * scale_log2).  It follows the running
+    // row maximum lazily — only when the maximum has moved by more than 2^8 past it — so that the output accumulator,
+    // which lives in tensor memory and is added to by every P·V product, has to be rescaled on a few blocks only
+    // (values of p stay below 2^8, far inside bf16 range; the final division by the row sum uses the same reference).
     float m = -INFINITY, l = 0.0f;
-    float o[D];
-#pragma unroll
-    for (int d = 0; d < D; ++d) o[d] = 0.0f;
     bool ok = true;
     for (int kb = 0; kb < my_nkb; ++kb) {
       if (!mbar_wait(&s_full[g], kb & 1)) { ok = false; break; }
       fence_after_sync();
       const int k0 = kb * BKV;
       const bool need_mask = (p.causal && kb == qb) || (k0 + BKV > p.T);
-      float mx = m;
+      // row maximum of this block: two 32-column chunks per TMEM round trip, four independent comparison chains
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
-      for (int c0 = 0; c0 < BKV; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_s + lane_addr + c0, r);
+      for (int c0 = 0; c0 < BKV; c0 += 64) {
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32(tmem_s + lane_addr + c0, ra);
+        tmem_ld_32x32(tmem_s + lane_addr + c0 + 32, rb);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          float sv = __uint_as_float(r[j]);
+          float sa = __uint_as_float(ra[j]), sb = __uint_as_float(rb[j]);
           if (need_mask) {
             const int tk = k0 + c0 + j;
-            if (tk >= p.T || (p.causal && tk > t_q)) sv = -INFINITY;
+            if (tk >= p.T || (p.causal && tk > t_q)) sa = -INFINITY;
+            if (tk + 32 >= p.T || (p.causal && tk + 32 > t_q)) sb = -INFINITY;
           }
-          mx = fmaxf(mx, sv);
+          mx4[j & 1] = fmaxf(mx4[j & 1], sa);
+          mx4[2 + (j & 1)] = fmaxf(mx4[2 + (j & 1)], sb);
         }
       }
-      const float m_new = mx;
-      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
-      const float alpha = fast_exp2((m - m_use) * p.scale_log2);
-      float rs = 0.0f;
+      const float m_blk = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const bool grow = (m_blk - m) * p.scale_log2 > 8.0f;      // true on the first block (m = -inf) of any visible key
+      float alpha = 1.0f;
+      if (grow) {
+        alpha = (m == -INFINITY) ? 0.0f : fast_exp2((m - m_blk) * p.scale_log2);
+        m = m_blk;
+      }
+      const float m_use = (m == -INFINITY) ? 0.0f : m;
+      if (kb > 0 && __any_sync(0xffffffffu, grow)) {
+        // Some row of this warp moved its reference: scale the accumulated output rows in tensor memory.  The P·V
+        // product of the previous block has completed (S of this block was issued after it); the wait makes that
+        // ordering explicit and returns at once.
+        if (!mbar_wait(&pv_full[g], (kb - 1) & 1)) { ok = false; break; }
+        fence_after_sync();
+        const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_pv + lane_addr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float2 v = __fmul2_rn(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), a2);
+            r[j] = __float_as_uint(v.x);
+            r[j + 1] = __float_as_uint(v.y);
+          }
+          tmem_st_32x32(tmem_pv + lane_addr + c0, r);
+        }
+        tmem_st_wait();
+      }
+      // p = 2^(s * scale_log2 - m * scale_log2): one packed multiply-add per pair, then the exponential; the row sum
+      // is taken over the fp32 values (pairs, packed adds)
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+      const float nm = -m_use * p.scale_log2;
+      const float2 nm2 = make_float2(nm, nm);
+      float2 rs2 = make_float2(0.0f, 0.0f), rs2b = make_float2(0.0f, 0.0f);
 #pragma unroll 1
       for (int c0 = 0; c0 < BKV; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(tmem_s + lane_addr + c0, r);
         tmem_ld_wait();
-        float pv[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float sv = __uint_as_float(r[j]);
-          if (need_mask) {
-            const int tk = k0 + c0 + j;
-            if (tk >= p.T || (p.causal && tk > t_q)) sv = -INFINITY;
-          }
-          pv[j] = fast_exp2((sv - m_use) * p.scale_log2);
-        }
 #pragma unroll
         for (int j8 = 0; j8 < 4; ++j8) {
           __align__(16) __nv_bfloat162 hh[4];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            hh[q] = __floats2bfloat162_rn(pv[j8 * 8 + 2 * q], pv[j8 * 8 + 2 * q + 1]);
-            const float2 back = __bfloat1622float2(hh[q]);
-            rs += back.x + back.y;
+            const int j = j8 * 8 + 2 * q;
+            float2 sv = make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            if (need_mask) {
+              const int tk = k0 + c0 + j;
+              if (tk >= p.T || (p.causal && tk > t_q)) sv.x = -INFINITY;
+              if (tk + 1 >= p.T || (p.causal && tk + 1 > t_q)) sv.y = -INFINITY;
+            }
+            const float2 e = __ffma2_rn(sv, sc2, nm2);
+            const float2 pe = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+            if (q & 1) rs2b = __fadd2_rn(rs2b, pe); else rs2 = __fadd2_rn(rs2, pe);
+            hh[q] = __float22bfloat162_rn(pe);
           }
           const int chunk = (c0 >> 3) + j8;
           uint8_t* dst = sPg + (chunk >> 3) * BQ * 128 + swz(row, chunk & 7);
           *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(hh);
         }
       }
-      l = l * alpha + rs;
-      m = m_new;
+      l = l * alpha + ((rs2.x + rs2.y) + (rs2b.x + rs2b.y));
       fence_proxy_async();
       fence_before_sync();
       mbar_arrive(&p_ready[g]);
-      if (!mbar_wait(&pv_full[g], kb & 1)) { ok = false; break; }
+    }
+    if (ok && my_nkb > 0) {
+      // the last P·V product completes the output rows in tensor memory: divide by the row sum and store
+      if (!mbar_wait(&pv_full[g], (my_nkb - 1) & 1)) ok = false;
       fence_after_sync();
+      if (ok) {
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        const float2 inv2 = make_float2(inv, inv);
+        bf16* dst = p.out + (((long long)b * p.T + t_q) * p.H + h) * D;
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_pv + lane_addr + c0, r);
+          tmem_ld_wait();
+          if (t_q < p.T) {
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_pv + lane_addr + c0, r);
-        tmem_ld_wait();
+            for (int d = 0; d < 32; d += 8) {
+              __align__(16) __nv_bfloat162 hh[4];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) o[c0 + j] = o[c0 + j] * alpha + __uint_as_float(r[j]);
+              for (int q = 0; q < 4; ++q)
+                hh[q] = __float22bfloat162_rn(__fmul2_rn(
+                    make_float2(__uint_as_float(r[d + 2 * q]), __uint_as_float(r[d + 2 * q + 1])), inv2));
+              *reinterpret_cast<uint4*>(dst + c0 + d) = *reinterpret_cast<uint4*>(hh);
+            }
+          }
+        }
+        if (t_q < p.T && p.lse != nullptr)
+          p.lse[((long long)b * p.H + h) * p.T + t_q] = (l > 0.0f) ? m * p.scale + logf(l) : -INFINITY;
       }
       fence_before_sync();
-    }
-    if (ok && my_nkb > 0 && t_q < p.T) {
-      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-      bf16* dst = p.out + (((long long)b * p.T + t_q) * p.H + h) * D;
-#pragma unroll
-      for (int d = 0; d < D; d += 8) {
-        __align__(16) __nv_bfloat162 hh[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) hh[q] = __floats2bfloat162_rn(o[d + 2 * q] * inv, o[d + 2 * q + 1] * inv);
-        *reinterpret_cast<uint4*>(dst + d) = *reinterpret_cast<uint4*>(hh);
-      }
-      if (p.lse != nullptr)
-        p.lse[((long long)b * p.H + h) * p.T + t_q] = (l > 0.0f) ? m * p.scale + logf(l) : -INFINITY;
     }
     if (!ok && lane == 0) atomicExch(p.status, ATT_ERR_TIMEOUT);
   }
@@ -741,7 +786,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (row_ok) {
           float* dst = p.dq + (((long long)b * p.T + t_q) * p.H + h) * D + c0;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) atomicAdd(dst + j, __uint_as_float(r[j]));
+          for (int j = 0; j < 32; j += 4)       // 16-byte vector reductions: a quarter of the instructions of scalar adds
+            atomicAdd(reinterpret_cast<float4*>(dst + j),
+                      make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                  __uint_as_float(r[j + 3])));
         }
       }
       fence_before_sync();
