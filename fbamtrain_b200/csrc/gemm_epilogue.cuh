@@ -29,10 +29,24 @@ __device__ __forceinline__ uint4 shfl_xor_u4(const uint4& x, int lane_mask) {
 }
 
 // r: 32 fp32 accumulator values of output row `roff / ldd`, columns [n0, n0 + 32).
+template <bool CE = false>
 __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff, int n0, const uint32_t (&r)[32]) {
           float v[32];
   #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+          if constexpr (CE) {
+            if (p.ce_mode == 2) {   // logits -> scale * (softmax - onehot), straight from the accumulators
+              const long long m = roff / p.ldd;
+              const float lse = p.ce_lse[m];
+              const int tgt = (int)p.ce_targets[m];
+  #pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int col = n0 + j;
+                const float sm = __expf(v[j] - lse) - (col == tgt ? 1.0f : 0.0f);
+                v[j] = col < p.ce_vocab ? p.ce_scale * sm : 0.0f;
+              }
+            }
+          }
           const bool full_vec = (n0 + 32 <= p.N) && p.vec_ok;
           if (p.bias != nullptr) {
   #pragma unroll

@@ -105,7 +105,9 @@ __device__ __forceinline__ Work decode_work(const GemmParams& p, int item, int t
   return w;
 }
 
-template <int BM, int BN>
+// CE: the instantiation that carries the fused LM-head + cross-entropy epilogues (GemmParams::ce_mode); the plain
+// instantiations are compiled without them, so their register use does not change.
+template <int BM, int BN, bool CE = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const GemmParams p) {
@@ -291,6 +293,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       fence_after_sync();
       const long long roff = row_offset(p, tile_m, row, BM);
       const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + (MH == 2 ? second * BN : acc * BN);
+      // fused cross-entropy statistics: running (maximum, sum of exp relative to it) of this thread's row over the
+      // columns of the tile half it owns, and the target column's logit when it falls into them
+      float ce_max = -INFINITY, ce_sum = 0.0f, ce_tl = 0.0f;
+      bool ce_hit = false;
+      int ce_tgt = -1;
+      if constexpr (CE) {
+        if (p.ce_mode == 1 && roff >= 0) ce_tgt = (int)p.ce_targets[roff / p.ldd];
+      }
 #pragma unroll 1
       for (int c0 = c_begin; c0 < c_end; c0 += 32) {
         uint32_t r[32];
@@ -298,6 +308,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         tmem_ld_wait();
         const int n0 = tile_n * BN + c0;
         if (roff < 0 || n0 >= p.N) continue;
+        if constexpr (CE) {
+          if (p.ce_mode == 1) {
+            float cm = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.ce_vocab) cm = fmaxf(cm, __uint_as_float(r[j]) * p.alpha);
+            if (cm > -INFINITY) {
+              const float nm = fmaxf(ce_max, cm);
+              float add = 0.0f;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float vj = __uint_as_float(r[j]) * p.alpha;
+                if (n0 + j < p.ce_vocab) add += __expf(vj - nm);
+                if (n0 + j == ce_tgt) { ce_tl = vj; ce_hit = true; }
+              }
+              ce_sum = ce_sum * __expf(ce_max - nm) + add;      // exp(-inf) = 0 on the first chunk
+              ce_max = nm;
+            }
+            continue;
+          }
+        }
         if (p.split_workspace != nullptr) {
           // partial sums of this K split: plain vector stores into the split's slab (zeros for an empty range)
           float* out = p.split_workspace + (long long)wk.split * p.split_stride + roff + n0;
@@ -316,7 +347,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           continue;
         }
         if (wk.k_end <= wk.k_begin) continue;
-        gemm_epi::store_chunk(p, roff, n0, r);
+        gemm_epi::store_chunk<CE>(p, roff, n0, r);
+      }
+      if constexpr (CE) {
+        if (p.ce_mode == 1 && roff >= 0) {
+          const long long m = roff / p.ldd;
+          const int slot = tile_n * 2 + (MH == 2 ? 0 : second);
+          float* dst = p.ce_partial + (m * p.ce_slots + slot) * 2;
+          dst[0] = ce_max;
+          dst[1] = ce_sum;
+          if (ce_hit) p.ce_tgt_logit[m] = ce_tl;
+        }
       }
       fence_before_sync();
       __syncwarp();
@@ -390,12 +431,12 @@ int encode_nhwc(CUtensorMap* map, const void* base, int n, int h, int w, int c, 
 
 int g_num_sms = 0;
 
-template <int BM, int BN>
+template <int BM, int BN, bool CE = false>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t stream) {
   using L = SmemLayout<BM, BN>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_kernel<BM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
+    if (cudaFuncSetAttribute(gemm_kernel<BM, BN, CE>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
         cudaSuccess)
       return GEMM_ERR_LAUNCH;
     configured = true;
@@ -409,11 +450,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStre
   const int usable = g_num_sms - g_fbam_reserved_sms > 0 ? g_num_sms - g_fbam_reserved_sms : 1;
   int grid = tiles < usable ? tiles : usable;
   if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
-  gemm_kernel<BM, BN><<<grid, kThreads, L::kTotal, stream>>>(ma, mb, p);
+  gemm_kernel<BM, BN, CE><<<grid, kThreads, L::kTotal, stream>>>(ma, mb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : GEMM_ERR_LAUNCH;
 }
 
 int dispatch(int bm, int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStream_t s) {
+  if (p.ce_mode != 0) return launch<128, 256, true>(ma, mb, p, s);   // the launcher fixed the tile to 128 x 256
   if (bm == 256) {
     if (bn == 128) return launch<256, 128>(ma, mb, p, s);
     return launch<256, 256>(ma, mb, p, s);
@@ -482,8 +524,19 @@ extern "C" int fbam_gemm_bf16(const void* A, long long lda, int a_mn_major, cons
   if (p.splits > p.k_blocks) p.splits = p.k_blocks;
   if (p.splits > 1 && p.split_workspace == nullptr && !(p.out_fp32 && p.accumulate == GEMM_ACC_ATOMIC))
     return GEMM_ERR_SHAPE;
-  const int bn = pick_bn(N, p.bn);
-  const int BM = pick_bm(M, N, bn, p.bm);
+  int bn = pick_bn(N, p.bn);
+  int BM = pick_bm(M, N, bn, p.bm);
+  if (p.ce_mode != 0) {
+    // fused cross-entropy epilogues: one tile shape, no split-K, the buffers of the mode present
+    if (p.ce_mode < 0 || p.ce_mode > 2 || p.splits != 1 || p.ce_targets == nullptr || p.ce_vocab < 1 || p.ce_vocab > N)
+      return GEMM_ERR_SHAPE;
+    bn = 256;
+    BM = 128;
+    if (p.ce_mode == 1 && (p.ce_partial == nullptr || p.ce_tgt_logit == nullptr || p.ce_slots != 2 * ((N + bn - 1) / bn)))
+      return GEMM_ERR_SHAPE;
+    if (p.ce_mode == 2 && (p.ce_lse == nullptr || p.D == nullptr)) return GEMM_ERR_SHAPE;
+    if (p.ce_mode == 1 && p.ldd <= 0) return GEMM_ERR_SHAPE;       // ldd only turns row offsets back into rows
+  }
   p.tiles_m = (M + BM - 1) / BM;
   const int elt = p.out_fp32 ? 4 : 2;
   p.vec_ok = (p.ldd % (16 / elt) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&

@@ -65,6 +65,20 @@ struct GemmParams {
   // pieces first, so that one store instruction writes 64 contiguous bytes of a row (two full sectors per
   // NVLink write) instead of 16 bytes of each of 32 rows.  Needs M and rs_rows_per_rank to be multiples of 32.
   int rs_row_stores;
+  // Fused LM head + cross-entropy (plain GEMM on single CTAs with 128 x 256 tiles): the logits tile stays in tensor
+  // memory / registers and never reaches HBM as fp32.
+  //   ce_mode 1 (statistics): nothing is stored per element.  Every epilogue thread reduces its row's columns of the
+  //     tile half it owns to (maximum, sum of exp relative to that maximum) and writes the pair to
+  //     ce_partial[(row * ce_slots + slot) * 2 + {0, 1}], slot = tile_n * 2 + column half; the thread that meets the
+  //     row's target column writes that logit to ce_tgt_logit[row].  Columns >= ce_vocab are padding and ignored.
+  //   ce_mode 2 (gradient): the value stored to D is ce_scale * (exp(logit - ce_lse[row]) - [column == target]);
+  //     padding columns get 0.
+  int ce_mode, ce_vocab, ce_slots;
+  float ce_scale;
+  float* ce_partial;
+  float* ce_tgt_logit;
+  const float* ce_lse;
+  const long long* ce_targets;
   // filled by the launcher
   int mode, M, N, K, tiles_m, k_blocks, a_mn_major, b_mn_major, vec_ok;
   ConvGeom conv;

@@ -699,6 +699,29 @@ __global__ void ce_fwd_bwd_kernel(bf16* __restrict__ logits, const long long* __
   }
 }
 
+// Fused LM head + cross-entropy, second step: the head GEMM's epilogue left, per row and tile half, the maximum of
+// the logits and the sum of exp relative to it (and the target logit); one thread per row merges them into the
+// row's log-sum-exp and adds scale * (lse - target logit) to the loss.
+__global__ void ce_combine_kernel(const float* __restrict__ partial, const float* __restrict__ tgt_logit,
+                                  float* __restrict__ lse, float* __restrict__ loss_sum, long long rows, int slots,
+                                  float scale) {
+  const long long row = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  float contrib = 0.0f;
+  if (row < rows) {
+    const float* pr = partial + row * slots * 2;
+    float m = -INFINITY;
+    for (int s = 0; s < slots; ++s) m = fmaxf(m, pr[2 * s]);
+    float sum = 0.0f;
+    for (int s = 0; s < slots; ++s)
+      if (pr[2 * s] > -INFINITY) sum += pr[2 * s + 1] * __expf(pr[2 * s] - m);
+    const float l = m + logf(sum);
+    lse[row] = l;
+    contrib = scale * (l - tgt_logit[row]);
+  }
+  contrib = warp_sum(contrib);
+  if ((threadIdx.x & 31) == 0 && contrib != 0.0f) atomicAdd(loss_sum, contrib);
+}
+
 // Same with fp32 logits in (the LM-head GEMM keeps its fp32 accumulators) and bf16 gradient out: the loss and the
 // softmax are then free of the bf16 rounding of the logits.
 __global__ void ce_fwd_bwd_f32_kernel(const float* __restrict__ logits, bf16* __restrict__ dlogits,
@@ -912,6 +935,17 @@ int fbam_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* 
   if (dim <= 1024) return launch_rms_bwd<4>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
   if (dim <= 2048) return launch_rms_bwd<8>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
   return launch_rms_bwd<16>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
+}
+
+// partial: fp32 [rows][slots][2] (maximum, sum of exp) from the head GEMM's statistics epilogue; tgt_logit: fp32 [rows];
+// lse: fp32 [rows] out; loss_sum: fp32 [1], added to.
+int fbam_ce_combine(const float* partial, const float* tgt_logit, float* lse, float* loss_sum, long long rows, int slots,
+                    float scale, void* stream) {
+  if (rows < 0 || slots < 1) return 1;
+  if (rows == 0) return 0;
+  ce_combine_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, STREAM(stream)>>>(partial, tgt_logit, lse, loss_sum, rows,
+                                                                               slots, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 
 // mean / rstd: fp32 [rows], kept for fbam_layernorm_bwd

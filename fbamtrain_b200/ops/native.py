@@ -53,6 +53,9 @@ class GemmParams(C.Structure):
                 ("flag_epoch", C.c_uint), ("flag_spin_limit", C.c_uint),
                 ("rs_out", C.c_void_p * 8), ("rs_rows_per_rank", C.c_int), ("rs_slot_plus1", C.c_int),
                 ("rs_row_stores", C.c_int),
+                ("ce_mode", C.c_int), ("ce_vocab", C.c_int), ("ce_slots", C.c_int), ("ce_scale", C.c_float),
+                ("ce_partial", C.c_void_p), ("ce_tgt_logit", C.c_void_p), ("ce_lse", C.c_void_p),
+                ("ce_targets", C.c_void_p),
                 ("mode", C.c_int), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("tiles_m", C.c_int),
                 ("k_blocks", C.c_int), ("a_mn_major", C.c_int), ("b_mn_major", C.c_int), ("vec_ok", C.c_int),
                 ("conv", ConvGeom)]

@@ -46,7 +46,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          bn: int = 0, bm: int = 0, max_ctas: int = 0, ready_flags: Optional[torch.Tensor] = None,
          flag_rows: int = 0, flag_on_b: bool = False, flag_epoch: int = 0, flag_spin_limit: int = 0,
          rs_out=None, rs_rows_per_rank: int = 0, tile_m_rotate: int = 0, two_cta=None,
-         rs_slot: int = -1, rs_row_stores: bool = False) -> torch.Tensor:
+         rs_slot: int = -1, rs_row_stores: bool = False, ce_stats=None, ce_grad=None) -> torch.Tensor:
     """``D[M, N] = epilogue(A · Bᵀ)``.
 
     ``a``: ``(M, K)`` (or ``(K, M)`` when ``a_mn``); ``b``: ``(N, K)`` (or ``(K, N)`` when ``b_mn``).
@@ -61,7 +61,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     remote additions into the owner's ``[rows][n]`` buffer; ``out`` is then only used for its shape and pitch.
     ``rs_row_stores`` (slot form): lanes exchange pieces so that each store instruction writes 64 contiguous bytes
     of a row instead of 16 bytes of 32 rows (needs ``M`` and ``rs_rows_per_rank`` in multiples of 32).
-    ``two_cta`` selects the CTA-pair kernel (default: automatically for large problems)."""
+    ``two_cta`` selects the CTA-pair kernel (default: automatically for large problems).
+
+    Fused LM head + cross-entropy: ``ce_stats = (partial, tgt_logit, targets, vocab)`` stores nothing per element and
+    leaves per-row (maximum, sum of exp) pairs of every tile half in ``partial`` ``(M, 2·⌈N/256⌉, 2)`` fp32 and the
+    target logits in ``tgt_logit``; ``ce_grad = (lse, targets, vocab, scale)`` writes ``scale·(softmax − onehot)``
+    computed from the accumulators and the rows' log-sum-exp instead of the logits."""
     _need_bf16(a, b)
     if a.stride(-1) != 1 or b.stride(-1) != 1:
         raise ValueError("GEMM operands need unit inner stride")
@@ -70,17 +75,32 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     n, kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
     if k != kb:
         raise ValueError(f"inner dimensions differ: {k} vs {kb}")
-    if bm == 0 and bn == 0 and max_ctas == 0 and two_cta is None and ready_flags is None and rs_out is None:
+    if (bm == 0 and bn == 0 and max_ctas == 0 and two_cta is None and ready_flags is None and rs_out is None and
+            ce_stats is None and ce_grad is None):
         tuned = tuning.lookup(tuning.gemm_key(m, n, k, a_mn, b_mn), {"m": m, "n": n, "k": k, "a_mn": a_mn, "b_mn": b_mn})
         if tuned is not None:
             bm, bn, max_ctas = tuned.get("bm", 0), tuned.get("bn", 0), tuned.get("max_ctas", 0)
             two_cta = tuned.get("two_cta")
-    if out is None:
-        out = debug.fresh((m, n), out_dtype, a.device)
-    if out.shape != (m, n) or out.stride(1) != 1:
-        raise ValueError("output has the wrong shape or layout")
     p = nv.GemmParams()
-    p.D, p.ldd = out.data_ptr(), out.stride(0)
+    if ce_stats is not None:
+        partial, tgt_logit, targets, vocab = ce_stats
+        slots = 2 * ((n + 255) // 256)
+        if partial.shape != (m, slots, 2) or partial.dtype != torch.float32 or not partial.is_contiguous():
+            raise ValueError(f"ce_stats partial buffer must be fp32 ({m}, {slots}, 2)")
+        p.ce_mode, p.ce_vocab, p.ce_slots = 1, vocab, slots
+        p.ce_partial, p.ce_tgt_logit, p.ce_targets = partial.data_ptr(), tgt_logit.data_ptr(), targets.data_ptr()
+        out = partial                       # nothing is written through D in this mode
+        two_cta = False
+    elif out is None:
+        out = debug.fresh((m, n), out_dtype, a.device)
+    if ce_stats is None and (out.shape != (m, n) or out.stride(1) != 1):
+        raise ValueError("output has the wrong shape or layout")
+    if ce_grad is not None:
+        lse, targets, vocab, scale = ce_grad
+        p.ce_mode, p.ce_vocab, p.ce_scale = 2, vocab, scale
+        p.ce_lse, p.ce_targets = lse.data_ptr(), targets.data_ptr()
+        two_cta = False
+    p.D, p.ldd = out.data_ptr(), (n if ce_stats is not None else out.stride(0))
     p.bias = 0 if bias is None else bias.data_ptr()
     p.bias_fp32 = int(bias is not None and bias.dtype == torch.float32)
     if residual is not None:
@@ -698,9 +718,13 @@ def cell_embed(cells, cp_embed, pos_embed, colour, out_dtype):
 
 
 # =================================================================================================
-# LM head + cross-entropy, chunked over rows so the (rows x vocab) logits never exist at once
+# LM head + cross-entropy: chunked over rows, logits reduced inside the GEMM epilogue (reference materialises them:
+# src/main_action_model.cpp:156-175)
 # =================================================================================================
 LM_HEAD_CHUNK_ROWS = 4096
+# True: cross-entropy statistics and gradient come out of the head GEMM's epilogue (no fp32 logits in HBM);
+# False: the GEMM writes a chunk of fp32 logits and a row-wise kernel reads them back.
+FUSED_LM_HEAD_CE = True
 
 
 class _LmHeadCe(torch.autograd.Function):
@@ -716,11 +740,32 @@ class _LmHeadCe(torch.autograd.Function):
         for lo in range(0, rows, LM_HEAD_CHUNK_ROWS):
             hi = min(rows, lo + LM_HEAD_CHUNK_ROWS)
             xc = x[lo:hi]
-            logits = gemm(xc, w_head, out_dtype=torch.float32)           # (chunk, vpad) fp32 accumulators
-            dlogits = torch.empty(hi - lo, vpad, dtype=BF16, device=x.device) if need_grad else None
-            nv.check(nv.lib().fbam_ce_fwd_bwd_f32(nv.ptr(logits), nv.ptr(dlogits), nv.ptr(targets[lo:hi]),
-                                                  nv.ptr(loss), C.c_longlong(hi - lo), vocab, vpad, C.c_float(scale),
-                                                  nv.stream_ptr()), "fbam_ce_fwd_bwd_f32")
+            n = hi - lo
+            tg = targets[lo:hi]
+            if FUSED_LM_HEAD_CE:
+                # The logits never reach HBM: the head GEMM's epilogue reduces each 128 x 128 tile half, still in
+                # tensor memory, to per-row (maximum, sum of exp) pairs and picks out the target logit; a small
+                # kernel merges the pairs into the rows' log-sum-exp and the loss; for the backward the same GEMM
+                # runs again and its epilogue turns the accumulators straight into bf16 scale·(softmax − onehot).
+                slots = 2 * ((vpad + 255) // 256)
+                partial = torch.empty(n, slots, 2, dtype=torch.float32, device=x.device)
+                tgt_logit = torch.zeros(n, dtype=torch.float32, device=x.device)      # targets outside the table: 0
+                lse = torch.empty(n, dtype=torch.float32, device=x.device)
+                gemm(xc, w_head, ce_stats=(partial, tgt_logit, tg, vocab))
+                nv.check(nv.lib().fbam_ce_combine(nv.ptr(partial), nv.ptr(tgt_logit), nv.ptr(lse), nv.ptr(loss),
+                                                  C.c_longlong(n), slots, C.c_float(scale), nv.stream_ptr()),
+                         "fbam_ce_combine")
+                dlogits = None
+                if need_grad:
+                    dlogits = torch.empty(n, vpad, dtype=BF16, device=x.device)
+                    with flops.not_useful():                             # the logits are computed a second time
+                        gemm(xc, w_head, out=dlogits, ce_grad=(lse, tg, vocab, scale))
+            else:
+                logits = gemm(xc, w_head, out_dtype=torch.float32)       # (chunk, vpad) fp32 accumulators
+                dlogits = torch.empty(n, vpad, dtype=BF16, device=x.device) if need_grad else None
+                nv.check(nv.lib().fbam_ce_fwd_bwd_f32(nv.ptr(logits), nv.ptr(dlogits), nv.ptr(tg), nv.ptr(loss),
+                                                      C.c_longlong(n), vocab, vpad, C.c_float(scale),
+                                                      nv.stream_ptr()), "fbam_ce_fwd_bwd_f32")
             if need_grad:                                                # dlogits = scale·(softmax − onehot)
                 gemm_nn(dlogits, w_head, out=dx[lo:hi])
                 gemm_tn(dlogits, xc, out=dw, accumulate=nv.GEMM_ACC_RMW)
