@@ -139,6 +139,32 @@ def status_word(device: torch.device) -> torch.Tensor:
     return _status[key]
 
 
+_status_probe = {}
+
+
+def check_status_late(device: torch.device) -> None:
+    """Raises if a kernel reported a timed-out wait, without draining the device: every call queues an asynchronous
+    copy of the status word into pinned host memory and examines the copy queued by the PREVIOUS call (whose event has
+    long completed by then).  A training loop calls this once per step; an expired wait therefore stops the run one
+    step later instead of letting it train on through broken collectives."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    probe = _status_probe.get(key)
+    if probe is None:
+        probe = {"host": torch.zeros(1, dtype=torch.int32).pin_memory(), "event": None}
+        _status_probe[key] = probe
+    if probe["event"] is not None:
+        probe["event"].synchronize()
+        code = int(probe["host"][0])
+        if code != 0:
+            status_word(device).zero_()
+            probe["event"] = None
+            raise RuntimeError(f"device-side wait expired: {_ERRORS.get(code, 'error')} (code {code})")
+    probe["host"].copy_(status_word(device), non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record()
+    probe["event"] = ev
+
+
 def check_status(device: torch.device) -> None:
     """Synchronises and raises if any kernel reported a timed-out wait since the last check."""
     w = status_word(device)

@@ -283,6 +283,11 @@ class Trainer:
         committed = True
         if self.dp is not None:
             committed = self.dp.reduce_and_step(self)
+            if self._cuda and getattr(self.dp, "mode", "") == "fused" and not hasattr(self.dp, "peer"):
+                # plain (not fault-tolerant) fused data parallelism: a bounded device-side wait that ran out means
+                # a collective did not complete; fail the run (seen one step late, without a host sync per step)
+                from .ops import native as _nv
+                _nv.check_status_late(self.device)
         else:
             with gputx_range("fbamtrain::action_model_optim_step"):
                 self.optimizers["action_model"].step()
