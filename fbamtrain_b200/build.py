@@ -1,7 +1,7 @@
 """In-tree build of the native libraries.
 
-``build_all()`` compiles every ``csrc/*.cu`` for ``sm_100a`` with ``nvcc`` and links them into
-``lib/libfbam_kernels.so``; ``csrc/runtime/*.cpp`` (host-only runtime: tokenizer trie, SplitMix64,
+``build_all()`` compiles every ``csrc/*.cu`` for ``sm_100a`` with ``nvcc``, twice: with bf16 elements into
+``lib/libfbam_kernels.so`` and with ``-DFBAM_ELEM_FP16`` (IEEE half elements) into ``lib/libfbam_kernels_fp16.so``; ``csrc/runtime/*.cpp`` (host-only runtime: tokenizer trie, SplitMix64,
 safetensors, durable cursor writer, TCP rendezvous, membership master) goes into
 ``lib/libfbam_runtime.so`` with ``g++``.  Objects are rebuilt only when their source (or a header)
 is newer.  Run as ``python -m fbamtrain_b200.build``.
@@ -21,6 +21,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "lib")
 OBJ = os.path.join(LIB, "obj")
 KERNELS_SO = os.path.join(LIB, "libfbam_kernels.so")
+KERNELS_FP16_SO = os.path.join(LIB, "libfbam_kernels_fp16.so")
 RUNTIME_SO = os.path.join(LIB, "libfbam_runtime.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -62,17 +63,24 @@ def build_kernels(force: bool = False, verbose: bool = False) -> str:
     headers = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh"))
     hdr_time = _newest(headers)
     nvcc = _nvcc()
-    jobs, objs = [], []
-    for src in sources:
-        obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
-        objs.append(obj)
-        if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_time):
-            jobs.append(([nvcc] + NVCC_FLAGS + _feature_flags() + ["-I", CSRC, "-c", src, "-o", obj], obj + ".log"))
+    jobs, relinked = [], False
+    variants = ((KERNELS_SO, "", []), (KERNELS_FP16_SO, "_fp16", ["-DFBAM_ELEM_FP16"]))
+    objs_of = {}
+    for so, suffix, defs in variants:
+        objs_of[so] = []
+        for src in sources:
+            obj = os.path.join(OBJ, os.path.basename(src)[:-3] + suffix + ".o")
+            objs_of[so].append(obj)
+            if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_time):
+                jobs.append(([nvcc] + NVCC_FLAGS + _feature_flags() + defs + ["-I", CSRC, "-c", src, "-o", obj],
+                             obj + ".log"))
     if jobs:
-        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+        with ThreadPoolExecutor(max_workers=min(os.cpu_count() or 8, len(jobs))) as ex:
             list(ex.map(lambda j: _compile(*j), jobs))
-    if jobs or not os.path.exists(KERNELS_SO) or os.path.getmtime(KERNELS_SO) < _newest(objs):
-        _compile([nvcc, "-shared", "-o", KERNELS_SO] + objs + ["-lcudart"], os.path.join(OBJ, "link_kernels.log"))
+    for so, suffix, _ in variants:
+        objs = objs_of[so]
+        if jobs or not os.path.exists(so) or os.path.getmtime(so) < _newest(objs):
+            _compile([nvcc, "-shared", "-o", so] + objs + ["-lcudart"], os.path.join(OBJ, f"link_kernels{suffix}.log"))
     if verbose:
         for _, log in jobs:
             sys.stdout.write(open(log).read())
@@ -125,4 +133,4 @@ if __name__ == "__main__":
         print("LD_PRELOAD=" + sanitizer_preload())
         sys.exit(0)
     build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
-    print("built:", KERNELS_SO, RUNTIME_SO if os.path.exists(RUNTIME_SO) else "")
+    print("built:", KERNELS_SO, KERNELS_FP16_SO, RUNTIME_SO if os.path.exists(RUNTIME_SO) else "")

@@ -240,10 +240,9 @@ def main(argv=None) -> int:
             dp = FaultTolerantDataParallel(peer, expected_world=args.ddp_world_size, min_world=1,
                                            mode="fused" if ddp.grad_reduce == "fused" else "allreduce")
 
-    if cfg.model_config.dtype == "fp16" and device.type == "cuda":
-        LOG("WARN", "the native kernels compute in bf16; running the fp16 configuration as bf16")
-        cfg.model_config.dtype = "bf16"
-        cfg.model_config.use_fp16_accumulation = False
+    if cfg.model_config.dtype == "fp16" and cfg.model_config.use_fp16_accumulation and device.type == "cuda":
+        LOG("INFO", "use_fp16_accumulation: the half-precision kernels of this package accumulate in fp32 "
+                    "(tensor-memory accumulators); the flag changes nothing here")
     trainer = Trainer(cfg, parallel=par, device=device, dp=dp, frame_chunk=args.frame_chunk, working_dir=working_dir)
     if args.synthetic:
         cfg.train_data_config.recordings_directory_path = ""

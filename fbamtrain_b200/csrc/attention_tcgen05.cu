@@ -29,7 +29,6 @@
 namespace {
 
 using namespace tc05;
-typedef __nv_bfloat16 bf16;
 
 constexpr int BQ = 128;   // queries per tile (TMEM lanes)
 constexpr int BKV = 128;  // keys per block
@@ -40,7 +39,7 @@ struct AttnParams {
   int causal;
   float scale_log2;  // softmax scale * log2(e)
   float scale;
-  bf16* out;         // (B, T, H, D) contiguous
+  elem_t* out;         // (B, T, H, D) contiguous
   float* lse;        // (B, H, T), natural-log units of the scaled scores
   int* status;
 };
@@ -129,8 +128,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       };
       load_kv(0);
-      const uint32_t idesc_s = make_idesc_bf16(128, BKV, false, false);
-      const uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);   // B = V is MN-major
+      const uint32_t idesc_s = make_idesc_f16kind(128, BKV, false, false);
+      const uint32_t idesc_pv = make_idesc_f16kind(128, D, false, true);   // B = V is MN-major
       ok = mbar_wait(q_full, 0);
       for (int kb = 0; kb < nkb && ok; ++kb) {
         const int s = kb % KV_STAGES;
@@ -223,11 +222,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
 #pragma unroll
         for (int j8 = 0; j8 < 4; ++j8) {
-          __align__(16) __nv_bfloat162 hh[4];
+          __align__(16) elem2_t hh[4];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            hh[q] = __floats2bfloat162_rn(pv[j8 * 8 + 2 * q], pv[j8 * 8 + 2 * q + 1]);
-            const float2 back = __bfloat1622float2(hh[q]);   // sum what the tensor core will actually see
+            hh[q] = ff2e2(pv[j8 * 8 + 2 * q], pv[j8 * 8 + 2 * q + 1]);
+            const float2 back = e22ff(hh[q]);   // sum what the tensor core will actually see
             rs += back.x + back.y;
           }
           const int chunk = (c0 >> 3) + j8;                  // 16-byte chunk index within the 128-key row
@@ -255,12 +254,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
     if (ok && t_q < p.T) {
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-      bf16* dst = p.out + (((long long)b * p.T + t_q) * p.H + h) * D;
+      elem_t* dst = p.out + (((long long)b * p.T + t_q) * p.H + h) * D;
 #pragma unroll
       for (int d = 0; d < D; d += 8) {
-        __align__(16) __nv_bfloat162 hh[4];
+        __align__(16) elem2_t hh[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) hh[q] = __floats2bfloat162_rn(o[d + 2 * q] * inv, o[d + 2 * q + 1] * inv);
+        for (int q = 0; q < 4; ++q) hh[q] = ff2e2(o[d + 2 * q] * inv, o[d + 2 * q + 1] * inv);
         *reinterpret_cast<uint4*>(dst + d) = *reinterpret_cast<uint4*>(hh);
       }
       if (p.lse != nullptr)
@@ -367,8 +366,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
         for (int j = 0; j < DP; ++j) tma_load_attn(sV + j * BKV * 128, &map_v, v_full, j * 64, h, kb * BKV, b);
       };
-      const uint32_t idesc_s = make_idesc_bf16(128, BKV, false, false);
-      const uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);   // B = V is MN-major
+      const uint32_t idesc_s = make_idesc_f16kind(128, BKV, false, false);
+      const uint32_t idesc_pv = make_idesc_f16kind(128, D, false, true);   // B = V is MN-major
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
       auto issue_s = [&](int g) {      // S_g = Q_g · Kᵀ
         const uint32_t q_addr = smem_u32(sQ + g * kQBytes);
@@ -519,7 +518,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         tmem_ld_wait();
 #pragma unroll
         for (int j8 = 0; j8 < 4; ++j8) {
-          __align__(16) __nv_bfloat162 hh[4];
+          __align__(16) elem2_t hh[4];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const int j = j8 * 8 + 2 * q;
@@ -532,7 +531,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             const float2 e = __ffma2_rn(sv, sc2, nm2);
             const float2 pe = make_float2(fast_exp2(e.x), fast_exp2(e.y));
             if (q & 1) rs2b = __fadd2_rn(rs2b, pe); else rs2 = __fadd2_rn(rs2, pe);
-            hh[q] = __float22bfloat162_rn(pe);
+            hh[q] = f22e2(pe);
           }
           const int chunk = (c0 >> 3) + j8;
           uint8_t* dst = sPg + (chunk >> 3) * BQ * 128 + swz(row, chunk & 7);
@@ -551,7 +550,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       if (ok) {
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         const float2 inv2 = make_float2(inv, inv);
-        bf16* dst = p.out + (((long long)b * p.T + t_q) * p.H + h) * D;
+        elem_t* dst = p.out + (((long long)b * p.T + t_q) * p.H + h) * D;
 #pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 32) {
           uint32_t r[32];
@@ -560,10 +559,10 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           if (t_q < p.T) {
 #pragma unroll
             for (int d = 0; d < 32; d += 8) {
-              __align__(16) __nv_bfloat162 hh[4];
+              __align__(16) elem2_t hh[4];
 #pragma unroll
               for (int q = 0; q < 4; ++q)
-                hh[q] = __float22bfloat162_rn(__fmul2_rn(
+                hh[q] = f22e2(__fmul2_rn(
                     make_float2(__uint_as_float(r[d + 2 * q]), __uint_as_float(r[d + 2 * q + 1])), inv2));
               *reinterpret_cast<uint4*>(dst + c0 + d) = *reinterpret_cast<uint4*>(hh);
             }
@@ -584,7 +583,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 // -------------------------------------------------------------------------------------------------
 // backward pre-pass: delta[b,h,t] = sum_d dO*O
 // -------------------------------------------------------------------------------------------------
-__global__ void attn_delta_kernel(const bf16* __restrict__ o, const bf16* __restrict__ d_o, float* __restrict__ delta,
+__global__ void attn_delta_kernel(const elem_t* __restrict__ o, const elem_t* __restrict__ d_o, float* __restrict__ delta,
                                   int B, int T, int H, int D, long long do_sb, long long do_st, long long do_sh) {
   const long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);   // (b, t, h) row
   const int lane = threadIdx.x & 31;
@@ -593,12 +592,12 @@ __global__ void attn_delta_kernel(const bf16* __restrict__ o, const bf16* __rest
   const long long bt = idx / H;
   const int t = (int)(bt % T);
   const int b = (int)(bt / T);
-  const bf16* orow = o + idx * D;
-  const bf16* drow = d_o + b * do_sb + t * do_st + hh * do_sh;
+  const elem_t* orow = o + idx * D;
+  const elem_t* drow = d_o + b * do_sb + t * do_st + hh * do_sh;
   float s = 0.0f;
   for (int d = lane * 2; d < D; d += 64) {
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(orow + d));
-    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(drow + d));
+    const float2 a = e22ff(*reinterpret_cast<const elem2_t*>(orow + d));
+    const float2 g = e22ff(*reinterpret_cast<const elem2_t*>(drow + d));
     s += a.x * g.x + a.y * g.y;
   }
 #pragma unroll
@@ -616,8 +615,8 @@ struct AttnBwdParams {
   const float* lse;    // (B, H, T)
   const float* delta;  // (B, H, T)
   float* dq;           // (B, T, H, D) fp32, zero-initialised; atomically accumulated
-  bf16* dk;            // (B, T, H, D) contiguous
-  bf16* dv;
+  elem_t* dk;            // (B, T, H, D) contiguous
+  elem_t* dv;
   int* status;
 };
 
@@ -676,9 +675,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tma_load_attn(sK + j * 128 * 128, &map_k, kv_full, j * 64, h, k0, b);
         tma_load_attn(sV + j * 128 * 128, &map_v, kv_full, j * 64, h, k0, b);
       }
-      const uint32_t id_s = make_idesc_bf16(128, 128, false, false);   // S = Q Kᵀ, dP = dO Vᵀ
-      const uint32_t id_t = make_idesc_bf16(128, D, true, true);       // dV = Pᵀ dO, dK = dSᵀ Q (A, B MN-major)
-      const uint32_t id_q = make_idesc_bf16(128, D, false, true);      // dQ = dS K (B MN-major)
+      const uint32_t id_s = make_idesc_f16kind(128, 128, false, false);   // S = Q Kᵀ, dP = dO Vᵀ
+      const uint32_t id_t = make_idesc_f16kind(128, D, true, true);       // dV = Pᵀ dO, dK = dSᵀ Q (A, B MN-major)
+      const uint32_t id_q = make_idesc_f16kind(128, D, false, true);      // dQ = dS K (B MN-major)
       ok = mbar_wait(kv_full, 0);
       int it = 0;
       for (int qb = qb_begin; qb < nqb && ok; ++qb, ++it) {
@@ -751,7 +750,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tmem_ld_wait();
 #pragma unroll
         for (int j8 = 0; j8 < 4; ++j8) {
-          __align__(16) __nv_bfloat162 hp[4], hd[4];
+          __align__(16) elem2_t hp[4], hd[4];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             float pe[2], de[2];
@@ -764,8 +763,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               pe[e] = pr;
               de[e] = pr * (__uint_as_float(rd[j]) - dl) * p.scale;
             }
-            hp[q] = __floats2bfloat162_rn(pe[0], pe[1]);
-            hd[q] = __floats2bfloat162_rn(de[0], de[1]);
+            hp[q] = ff2e2(pe[0], pe[1]);
+            hd[q] = ff2e2(de[0], de[1]);
           }
           const int chunk = (c0 >> 3) + j8;
           const uint32_t off = (chunk >> 3) * 128 * 128 + swz(row, chunk & 7);
@@ -800,7 +799,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const int t_k = k0 + row;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
-        bf16* base = which == 0 ? p.dv : p.dk;
+        elem_t* base = which == 0 ? p.dv : p.dk;
         const uint32_t src = which == 0 ? tm_dv : tm_dk;
 #pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 32) {
@@ -808,13 +807,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tmem_ld_32x32(src + lane_addr + c0, r);
           tmem_ld_wait();
           if (t_k < p.T) {
-            bf16* dst = base + (((long long)b * p.T + t_k) * p.H + h) * D + c0;
+            elem_t* dst = base + (((long long)b * p.T + t_k) * p.H + h) * D + c0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
-              __align__(16) __nv_bfloat162 hh[4];
+              __align__(16) elem2_t hh[4];
 #pragma unroll
               for (int q = 0; q < 4; ++q)
-                hh[q] = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * q]), __uint_as_float(r[j + 2 * q + 1]));
+                hh[q] = ff2e2(__uint_as_float(r[j + 2 * q]), __uint_as_float(r[j + 2 * q + 1]));
               *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<uint4*>(hh);
             }
           }
@@ -868,7 +867,7 @@ int encode_bthd(CUtensorMap* map, const void* base, int B, int T, int H, int D, 
   cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)st * 2, (cuuint64_t)sb * 2};
   cuuint32_t box[4] = {64, 1, 128, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = enc(map, ELEM_TMAP, 4, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : 3;
@@ -892,7 +891,7 @@ int fbam_attn_fwd(const void* q, const void* k, const void* v, long long sb, lon
   if ((e = encode_bthd(&mq, q, B, T, H, D, sb, st, sh))) return e;
   if ((e = encode_bthd(&mk, k, B, T, H, D, sb, st, sh))) return e;
   if ((e = encode_bthd(&mv, v, B, T, H, D, sb, st, sh))) return e;
-  AttnParams p{B, T, H, D, causal, scale * 1.4426950408889634f, scale, (bf16*)out, lse, status};
+  AttnParams p{B, T, H, D, causal, scale * 1.4426950408889634f, scale, (elem_t*)out, lse, status};
   dim3 grid((T + BQ - 1) / BQ, H, B);
   const int stages = D == 64 ? 1 : 2;
   const int smem = BQ * D * 2 + 2 * stages * BKV * D * 2 + BQ * BKV * 2 + 256 + 1024;
@@ -916,7 +915,7 @@ int fbam_attn_fwd2(const void* q, const void* k, const void* v, long long sb, lo
   if ((e = encode_bthd(&mq, q, B, T, H, D, sb, st, sh))) return e;
   if ((e = encode_bthd(&mk, k, B, T, H, D, sb, st, sh))) return e;
   if ((e = encode_bthd(&mv, v, B, T, H, D, sb, st, sh))) return e;
-  AttnParams p{B, T, H, D, causal, scale * 1.4426950408889634f, scale, (bf16*)out, lse, status};
+  AttnParams p{B, T, H, D, causal, scale * 1.4426950408889634f, scale, (elem_t*)out, lse, status};
   dim3 grid((T + 2 * BQ - 1) / (2 * BQ), H, B);
   const int smem = 2 * BQ * D * 2 + 2 * BKV * D * 2 + 2 * BQ * BKV * 2 + 256 + 1024;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -939,7 +938,7 @@ int fbam_attn_bwd(const void* q, const void* k, const void* v, long long sb, lon
   if ((D != 64 && D != 128) || B < 1 || T < 1 || H < 1) return 1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const long long rows = (long long)B * T * H;
-  attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const bf16*)o, (const bf16*)d_o, delta, B, T, H, D,
+  attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const elem_t*)o, (const elem_t*)d_o, delta, B, T, H, D,
                                                                do_sb, do_st, do_sh);
   if (cudaGetLastError() != cudaSuccess) return 5;
   CUtensorMap mq, mk, mv, mdo;
@@ -948,7 +947,7 @@ int fbam_attn_bwd(const void* q, const void* k, const void* v, long long sb, lon
   if ((e = encode_bthd(&mk, k, B, T, H, D, sb, st, sh))) return e;
   if ((e = encode_bthd(&mv, v, B, T, H, D, sb, st, sh))) return e;
   if ((e = encode_bthd(&mdo, d_o, B, T, H, D, do_sb, do_st, do_sh))) return e;
-  AttnBwdParams p{B, T, H, D, causal, scale * 1.4426950408889634f, scale, lse, delta, dq, (bf16*)dk, (bf16*)dv, status};
+  AttnBwdParams p{B, T, H, D, causal, scale * 1.4426950408889634f, scale, lse, delta, dq, (elem_t*)dk, (elem_t*)dv, status};
   dim3 grid((T + BKV - 1) / BKV, H, B);
   const int smem = 4 * 128 * D * 2 + 2 * 128 * 128 * 2 + 256 + 1024;
   if (D == 64) {

@@ -23,7 +23,7 @@
 //
 // The reference reduces gradients with NCCL all-reduce calls on packed buffers and steps the optimizer afterwards
 // (reference: src/main.cpp:3572-3713, ccl/src/ccl_nccl.cpp:197-232); these kernels replace that sequence.
-#include <cuda_bf16.h>
+#include "elem16.cuh"
 #include <cuda_runtime.h>
 #include <string.h>
 #include <stdint.h>
@@ -36,7 +36,6 @@ struct PeerPtrs {
 
 namespace {
 
-typedef __nv_bfloat16 bf16;
 enum { COMM_ERR_PEER_TIMEOUT = 301 };
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
@@ -104,20 +103,20 @@ __device__ void finish_and_wait(const PeerPtrs& flags, int rank, int world, int 
   }
 }
 
-__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* f) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+__device__ __forceinline__ void unpack_elem8(const uint4& raw, float* f) {
+  const elem2_t* h = reinterpret_cast<const elem2_t*>(&raw);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(h[i]);
+    const float2 t = e22ff(h[i]);
     f[2 * i] = t.x;
     f[2 * i + 1] = t.y;
   }
 }
-__device__ __forceinline__ uint4 pack_bf16x8(const float* f) {
+__device__ __forceinline__ uint4 pack_elem8(const float* f) {
   uint4 raw;
-  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+  elem2_t* h = reinterpret_cast<elem2_t*>(&raw);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  for (int i = 0; i < 4; ++i) h[i] = ff2e2(f[2 * i], f[2 * i + 1]);
   return raw;
 }
 
@@ -127,11 +126,11 @@ struct AdamArgs {
 
 // -------------------------------------------------------------------------------------------------
 // reduce-scatter + AdamW + all-gather.  The shard [lo, hi) (element indices, multiples of 8) is this rank's.
-// BF16 = parameters/gradients are bf16 with an fp32 master copy; otherwise they are fp32 (no master).
+// ELEM16 = parameters/gradients are 16-bit (the element type) with an fp32 master copy; otherwise they are fp32 (no master).
 // MULTIMEM = gradients are summed by the switch (multimem.ld_reduce) and parameters broadcast by it
 // (multimem.st) through the multicast addresses mc_grad / mc_param.
 // -------------------------------------------------------------------------------------------------
-template <bool BF16, bool MULTIMEM>
+template <bool ELEM16, bool MULTIMEM>
 __global__ void __launch_bounds__(256)
 rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_grad, void* mc_param, float* m, float* v,
                    float* master, long long lo, long long hi, AdamArgs a, int rank, int world, unsigned epoch,
@@ -139,7 +138,7 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_gra
   // phase 0: every rank's gradients are complete (this kernel is stream-ordered after the local backward)
   if (sync && !signal_and_wait(flags, rank, world, 0, epoch, spin_limit, status)) return;
 
-  constexpr int VEC = BF16 ? 8 : 4;  // elements per 16-byte packet
+  constexpr int VEC = ELEM16 ? 8 : 4;  // elements per 16-byte packet
   const long long packets = (hi - lo) / VEC;
   for (long long pk = (long long)blockIdx.x * blockDim.x + threadIdx.x; pk < packets;
        pk += (long long)gridDim.x * blockDim.x) {
@@ -148,13 +147,13 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_gra
 #pragma unroll
     for (int j = 0; j < VEC; ++j) g[j] = 0.0f;
     if constexpr (MULTIMEM) {
-      if constexpr (BF16) {
+      if constexpr (ELEM16) {
         uint4 raw;
-        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4." ELEM_PTX "x2 {%0,%1,%2,%3}, [%4];"
                      : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
-                     : "l"(reinterpret_cast<const bf16*>(mc_grad) + i)
+                     : "l"(reinterpret_cast<const elem_t*>(mc_grad) + i)
                      : "memory");
-        unpack_bf16x8(raw, g);
+        unpack_elem8(raw, g);
       } else {
         asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
                      : "=f"(g[0]), "=f"(g[1]), "=f"(g[2]), "=f"(g[3])
@@ -169,14 +168,14 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_gra
 #pragma unroll
       for (int r = 0; r < FBAM_MAX_RANKS; ++r)
         if (r < world)
-          raw[r] = BF16 ? ld_cg_v4(reinterpret_cast<const bf16*>(grads.p[r]) + i)
+          raw[r] = ELEM16 ? ld_cg_v4(reinterpret_cast<const elem_t*>(grads.p[r]) + i)
                         : ld_cg_v4(reinterpret_cast<const float*>(grads.p[r]) + i);
 #pragma unroll
       for (int r = 0; r < FBAM_MAX_RANKS; ++r) {
         if (r < world) {
-          if constexpr (BF16) {
+          if constexpr (ELEM16) {
             float t[8];
-            unpack_bf16x8(raw[r], t);
+            unpack_elem8(raw[r], t);
 #pragma unroll
             for (int j = 0; j < 8; ++j) g[j] += t[j];
           } else {
@@ -187,7 +186,7 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_gra
       }
     }
     float w[VEC];
-    if constexpr (BF16) {
+    if constexpr (ELEM16) {
       const float4 w0 = *reinterpret_cast<const float4*>(master + i), w1 = *reinterpret_cast<const float4*>(master + i + 4);
       w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w; w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
     } else {
@@ -214,16 +213,16 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_gra
       *reinterpret_cast<float4*>(v + i + j) = make_float4(vv[j], vv[j + 1], vv[j + 2], vv[j + 3]);
     }
     uint4 out;
-    if constexpr (BF16) {
+    if constexpr (ELEM16) {
       *reinterpret_cast<float4*>(master + i) = make_float4(w[0], w[1], w[2], w[3]);
       *reinterpret_cast<float4*>(master + i + 4) = make_float4(w[4], w[5], w[6], w[7]);
-      out = pack_bf16x8(w);
+      out = pack_elem8(w);
     } else {
       out = make_uint4(__float_as_uint(w[0]), __float_as_uint(w[1]), __float_as_uint(w[2]), __float_as_uint(w[3]));
     }
     // all-gather: the updated packet goes to every rank's parameter buffer
     if constexpr (MULTIMEM) {
-      void* dst = BF16 ? static_cast<void*>(reinterpret_cast<bf16*>(mc_param) + i)
+      void* dst = ELEM16 ? static_cast<void*>(reinterpret_cast<elem_t*>(mc_param) + i)
                        : static_cast<void*>(reinterpret_cast<float*>(mc_param) + i);
       asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst),
                    "f"(__uint_as_float(out.x)), "f"(__uint_as_float(out.y)), "f"(__uint_as_float(out.z)),
@@ -233,7 +232,7 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_gra
 #pragma unroll
       for (int r = 0; r < FBAM_MAX_RANKS; ++r) {
         if (r < world) {
-          void* dst = BF16 ? static_cast<void*>(reinterpret_cast<bf16*>(params.p[r]) + i)
+          void* dst = ELEM16 ? static_cast<void*>(reinterpret_cast<elem_t*>(params.p[r]) + i)
                            : static_cast<void*>(reinterpret_cast<float*>(params.p[r]) + i);
           *reinterpret_cast<uint4*>(dst) = out;
         }
@@ -246,14 +245,14 @@ rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, PeerPtrs flags, void* mc_gra
 
 // -------------------------------------------------------------------------------------------------
 // Sum of all peers' gradients over [lo, hi) -> momentum buffer update -> bf16 update direction + Σ x².
-// buf = mu*buf + (1 - mu)*g;  u = nesterov ? (1 - mu)*g + mu*buf : buf;  out_bf16 = u;  sumsq += Σ u²
+// buf = mu*buf + (1 - mu)*g;  u = nesterov ? (1 - mu)*g + mu*buf : buf;  out_elem = u;  sumsq += Σ u²
 // (the momentum buffer is an exponential moving average, as in the reference: src/optimizers.cpp:1204-1226)
 // -------------------------------------------------------------------------------------------------
-template <bool BF16>
+template <bool ELEM16>
 __global__ void __launch_bounds__(256)
-reduce_pull_kernel(PeerPtrs grads, float* momentum_buf, bf16* out, float* sumsq, long long lo, long long hi, float mu,
+reduce_pull_kernel(PeerPtrs grads, float* momentum_buf, elem_t* out, float* sumsq, long long lo, long long hi, float mu,
                    int nesterov, float grad_scale, int world) {
-  constexpr int VEC = BF16 ? 8 : 4;
+  constexpr int VEC = ELEM16 ? 8 : 4;
   const long long packets = (hi - lo) / VEC;
   float local = 0.0f;
   for (long long pk = (long long)blockIdx.x * blockDim.x + threadIdx.x; pk < packets;
@@ -266,14 +265,14 @@ reduce_pull_kernel(PeerPtrs grads, float* momentum_buf, bf16* out, float* sumsq,
 #pragma unroll
     for (int r = 0; r < FBAM_MAX_RANKS; ++r)
       if (r < world)
-        raw[r] = BF16 ? ld_cg_v4(reinterpret_cast<const bf16*>(grads.p[r]) + i)
+        raw[r] = ELEM16 ? ld_cg_v4(reinterpret_cast<const elem_t*>(grads.p[r]) + i)
                       : ld_cg_v4(reinterpret_cast<const float*>(grads.p[r]) + i);
 #pragma unroll
     for (int r = 0; r < FBAM_MAX_RANKS; ++r) {
       if (r < world) {
-        if constexpr (BF16) {
+        if constexpr (ELEM16) {
           float t[8];
-          unpack_bf16x8(raw[r], t);
+          unpack_elem8(raw[r], t);
 #pragma unroll
           for (int j = 0; j < 8; ++j) g[j] += t[j];
         } else {
@@ -299,10 +298,10 @@ reduce_pull_kernel(PeerPtrs grads, float* momentum_buf, bf16* out, float* sumsq,
 #pragma unroll
     for (int j = 0; j < VEC; j += 4)
       *reinterpret_cast<float4*>(momentum_buf + (i - lo) + j) = make_float4(bufv[j], bufv[j + 1], bufv[j + 2], bufv[j + 3]);
-    if constexpr (BF16) {
-      *reinterpret_cast<uint4*>(out + (i - lo)) = pack_bf16x8(u);
+    if constexpr (ELEM16) {
+      *reinterpret_cast<uint4*>(out + (i - lo)) = pack_elem8(u);
     } else {
-      __align__(8) __nv_bfloat162 h[2] = {__floats2bfloat162_rn(u[0], u[1]), __floats2bfloat162_rn(u[2], u[3])};
+      __align__(8) elem2_t h[2] = {ff2e2(u[0], u[1]), ff2e2(u[2], u[3])};
       *reinterpret_cast<uint2*>(out + (i - lo)) = *reinterpret_cast<uint2*>(h);
     }
   }
@@ -368,17 +367,17 @@ reduce_slots_kernel(const uint4* __restrict__ slots, uint4* __restrict__ out, lo
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int r = 0; r < world; ++r) {
       const uint4 raw = __ldcg(slots + (long long)r * packets_per_slot + pk);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const elem2_t* h = reinterpret_cast<const elem2_t*>(&raw);
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const float2 f = __bfloat1622float2(h[q]);
+        const float2 f = e22ff(h[q]);
         acc[2 * q] += f.x;
         acc[2 * q + 1] += f.y;
       }
     }
-    __align__(16) __nv_bfloat162 o[4];
+    __align__(16) elem2_t o[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) o[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+    for (int q = 0; q < 4; ++q) o[q] = ff2e2(acc[2 * q], acc[2 * q + 1]);
     out[pk] = *reinterpret_cast<uint4*>(o);
   }
 }
@@ -405,14 +404,14 @@ int fbam_comm_max_ranks() { return FBAM_MAX_RANKS; }
 // or null (then plain peer loads/stores are used).  arrive: one zeroed unsigned in local memory.
 // sync = 0 skips the cross-rank barriers (single-process emulation of several ranks, one launch per rank).
 int fbam_rs_adamw_ag(void* const* grads, void* const* params, void* const* flags, void* mc_grad, void* mc_param,
-                     float* m, float* v, float* master, long long lo, long long hi, int is_bf16, float lr, float b1,
+                     float* m, float* v, float* master, long long lo, long long hi, int is_elem, float lr, float b1,
                      float b2, float eps, float wd, float bc1, float bc2, float grad_scale, int rank, int world,
                      unsigned epoch, int sync, unsigned spin_limit, int* status, unsigned* arrive, int max_ctas,
                      void* stream) {
   if (world < 1 || world > FBAM_MAX_RANKS || rank < 0 || rank >= world) return 1;
-  const int vec = is_bf16 ? 8 : 4;
+  const int vec = is_elem ? 8 : 4;
   if (lo % vec != 0 || hi % vec != 0 || hi < lo) return 1;
-  if (is_bf16 && master == nullptr) return 1;
+  if (is_elem && master == nullptr) return 1;
   if ((reinterpret_cast<uintptr_t>(m) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
       (reinterpret_cast<uintptr_t>(master) & 15))
     return 1;
@@ -435,29 +434,29 @@ int fbam_rs_adamw_ag(void* const* grads, void* const* params, void* const* flags
 #define LAUNCH(BF, MM)                                                                                              \
   rs_adamw_ag_kernel<BF, MM><<<grid, 256, 0, s>>>(G, P, F, mc_grad, mc_param, m, v, master, lo, hi, a, rank, world, \
                                                   epoch, sync, spin_limit, status, arrive)
-  if (is_bf16) { if (mm) LAUNCH(true, true); else LAUNCH(true, false); }
+  if (is_elem) { if (mm) LAUNCH(true, true); else LAUNCH(true, false); }
   else { if (mm) LAUNCH(false, true); else LAUNCH(false, false); }
 #undef LAUNCH
   return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 
-int fbam_reduce_pull(void* const* grads, float* momentum_buf, void* out_bf16, float* sumsq, long long lo, long long hi,
-                     int is_bf16, float mu, int nesterov, float grad_scale, int world, void* stream) {
+int fbam_reduce_pull(void* const* grads, float* momentum_buf, void* out_elem, float* sumsq, long long lo, long long hi,
+                     int is_elem, float mu, int nesterov, float grad_scale, int world, void* stream) {
   if (world < 1 || world > FBAM_MAX_RANKS) return 1;
-  const int vec = is_bf16 ? 8 : 4;
+  const int vec = is_elem ? 8 : 4;
   if (lo % vec != 0 || hi % vec != 0 || hi < lo) return 1;
-  if ((reinterpret_cast<uintptr_t>(momentum_buf) & 15) || (reinterpret_cast<uintptr_t>(out_bf16) & 15)) return 1;
+  if ((reinterpret_cast<uintptr_t>(momentum_buf) & 15) || (reinterpret_cast<uintptr_t>(out_elem) & 15)) return 1;
   PeerPtrs G{};
   for (int r = 0; r < world; ++r) G.p[r] = grads[r];
   const long long packets = (hi - lo) / vec;
   int grid = (int)((packets + 255) / 256);
   if (grid > num_sms() * 4) grid = num_sms() * 4;
   if (grid < 1) grid = 1;
-  if (is_bf16)
-    reduce_pull_kernel<true><<<grid, 256, 0, STREAM(stream)>>>(G, momentum_buf, (bf16*)out_bf16, sumsq, lo, hi, mu,
+  if (is_elem)
+    reduce_pull_kernel<true><<<grid, 256, 0, STREAM(stream)>>>(G, momentum_buf, (elem_t*)out_elem, sumsq, lo, hi, mu,
                                                                nesterov, grad_scale, world);
   else
-    reduce_pull_kernel<false><<<grid, 256, 0, STREAM(stream)>>>(G, momentum_buf, (bf16*)out_bf16, sumsq, lo, hi, mu,
+    reduce_pull_kernel<false><<<grid, 256, 0, STREAM(stream)>>>(G, momentum_buf, (elem_t*)out_elem, sumsq, lo, hi, mu,
                                                                 nesterov, grad_scale, world);
   return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }

@@ -26,7 +26,7 @@
 // of every run, which also bounds the rounding drift); the backward kernel accumulates dZ in registers per tap
 // while that tap's code point stays the same and adds the run to S with vector reductions only when it changes.
 // Frames that share nothing cost nine row loads (forward) or nine row reductions (backward) per pixel and frame.
-#include <cuda_bf16.h>
+#include "elem16.cuh"
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -34,7 +34,6 @@
 
 namespace {
 
-typedef __nv_bfloat16 bf16;
 
 struct EmbConvGeom {
   int rows, cols;        // cells per frame
@@ -42,7 +41,7 @@ struct EmbConvGeom {
   int stride, pad, dil;  // 3x3 filter geometry
 };
 
-struct alignas(16) Pack8 { __nv_bfloat162 h[4]; };
+struct alignas(16) Pack8 { elem2_t h[4]; };
 // Cell index (row-major within the frame) that output pixel (oy, ox) reads through filter tap `tap`, or -1 when the
 // tap falls into the padding.
 __device__ __forceinline__ int tap_cell(const EmbConvGeom& g, int oy, int ox, int tap) {
@@ -55,7 +54,7 @@ __device__ __forceinline__ int tap_cell(const EmbConvGeom& g, int oy, int ox, in
 // ------------------------------------------------------------------------------------------------
 // colour features: one thread per output pixel writes its 128-byte row
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) embconv_features_kernel(const int* __restrict__ cells, bf16* __restrict__ feat,
+__global__ void __launch_bounds__(256) embconv_features_kernel(const int* __restrict__ cells, elem_t* __restrict__ feat,
                                                                long long frames, EmbConvGeom g) {
   const int p_out = g.oh * g.ow;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -74,9 +73,9 @@ __global__ void __launch_bounds__(256) embconv_features_kernel(const int* __rest
       const int* cw = cells + (frame_base + cell) * 3;
       const uint32_t fg = (uint32_t)__ldg(cw + 1), bg = (uint32_t)__ldg(cw + 2);
       const float k = 1.0f / 255.0f;
-      const __nv_bfloat162 a = __floats2bfloat162_rn(((fg >> 16) & 255) * k, ((fg >> 8) & 255) * k);
-      const __nv_bfloat162 b = __floats2bfloat162_rn((fg & 255) * k, ((bg >> 16) & 255) * k);
-      const __nv_bfloat162 c = __floats2bfloat162_rn(((bg >> 8) & 255) * k, (bg & 255) * k);
+      const elem2_t a = ff2e2(((fg >> 16) & 255) * k, ((fg >> 8) & 255) * k);
+      const elem2_t b = ff2e2((fg & 255) * k, ((bg >> 16) & 255) * k);
+      const elem2_t c = ff2e2(((bg >> 8) & 255) * k, (bg & 255) * k);
       w[t * 3 + 0] = *reinterpret_cast<const uint32_t*>(&a);
       w[t * 3 + 1] = *reinterpret_cast<const uint32_t*>(&b);
       w[t * 3 + 2] = *reinterpret_cast<const uint32_t*>(&c);
@@ -96,16 +95,16 @@ constexpr int kPrefetchBwd = 16;   // same in the backward reduction (8-byte pie
 using gelu_math::f2;
 using gelu_math::gelu2;
 
-__device__ __forceinline__ void add_row(float2* acc, const bf16* row, float sign) {
+__device__ __forceinline__ void add_row(float2* acc, const elem_t* row, float sign) {
   const Pack8 r = *reinterpret_cast<const Pack8*>(row);
   const float2 s2 = f2(sign);
 #pragma unroll
-  for (int j = 0; j < 4; ++j) acc[j] = __ffma2_rn(s2, __bfloat1622float2(r.h[j]), acc[j]);
+  for (int j = 0; j < 4; ++j) acc[j] = __ffma2_rn(s2, e22ff(r.h[j]), acc[j]);
 }
 
-__global__ void __launch_bounds__(256, 3) embconv_fwd_kernel(const int* __restrict__ cells, const bf16* __restrict__ table,
-                                                             const float* __restrict__ pos, bf16* __restrict__ z,
-                                                             bf16* __restrict__ y, long long frames, int vocab, int O,
+__global__ void __launch_bounds__(256, 3) embconv_fwd_kernel(const int* __restrict__ cells, const elem_t* __restrict__ table,
+                                                             const float* __restrict__ pos, elem_t* __restrict__ z,
+                                                             elem_t* __restrict__ y, long long frames, int vocab, int O,
                                                              EmbConvGeom g, int seg_len, int nseg, int z_has_input,
                                                              int apply_gelu) {
   const unsigned full = 0xffffffffu;
@@ -131,7 +130,7 @@ __global__ void __launch_bounds__(256, 3) embconv_fwd_kernel(const int* __restri
   const long long f0 = (long long)seg * seg_len;
   const long long f1 = min(frames, f0 + seg_len);
   const long long row9 = 9ll * O;
-  const bf16* tab = table + (act ? co : 0);
+  const elem_t* tab = table + (act ? co : 0);
   const int* cell_ptr = cells + (f0 * cells_per_frame + max(cell, 0)) * 3;
   const long long cell_step = cells_per_frame * 3, z_step = (long long)p_out * O;
   long long off = (f0 * p_out + p) * O + (act ? co : 0);
@@ -181,16 +180,16 @@ __global__ void __launch_bounds__(256, 3) embconv_fwd_kernel(const int* __restri
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           v[j] = __fadd2_rn(sum[j], base[j]);
-          if (z_has_input) v[j] = __fadd2_rn(v[j], __bfloat1622float2(zin[u].h[j]));
+          if (z_has_input) v[j] = __fadd2_rn(v[j], e22ff(zin[u].h[j]));
         }
         Pack8 out;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) out.h[j] = __float22bfloat162_rn(v[j]);
+        for (int j = 0; j < 4; ++j) out.h[j] = f22e2(v[j]);
         *reinterpret_cast<Pack8*>(z + off + u * z_step) = out;
         if (y != nullptr) {
           if (apply_gelu) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) out.h[j] = __float22bfloat162_rn(gelu2(v[j]));
+            for (int j = 0; j < 4; ++j) out.h[j] = f22e2(gelu2(v[j]));
           }
           *reinterpret_cast<Pack8*>(y + off + u * z_step) = out;
         }
@@ -209,11 +208,11 @@ __global__ void __launch_bounds__(256, 3) embconv_fwd_kernel(const int* __restri
 // the difference of two prefixes, taken when the run ends.  Per frame that is four additions instead of forty; the
 // prefix at the end of the segment is the pixel's contribution to D.  (The prefix spans at most one segment, so the
 // difference loses at most log2(segment) bits of fp32 — far below the bf16 resolution of dZ.)
-struct alignas(8) Pack4 { __nv_bfloat162 h[2]; };
+struct alignas(8) Pack4 { elem2_t h[2]; };
 
 __device__ __forceinline__ void red_add4(float* dst, float4 v) { atomicAdd(reinterpret_cast<float4*>(dst), v); }
 
-__global__ void __launch_bounds__(256, 3) embconv_bwd_reduce_kernel(const int* __restrict__ cells, const bf16* __restrict__ dz,
+__global__ void __launch_bounds__(256, 3) embconv_bwd_reduce_kernel(const int* __restrict__ cells, const elem_t* __restrict__ dz,
                                                                     float* __restrict__ S, float* __restrict__ D,
                                                                     long long frames, int vocab, int O, EmbConvGeom g,
                                                                     int seg_len, int nseg) {
@@ -239,7 +238,7 @@ __global__ void __launch_bounds__(256, 3) embconv_bwd_reduce_kernel(const int* _
   const long long f0 = (long long)seg * seg_len;
   const long long f1 = min(frames, f0 + seg_len);
   const int* cell_ptr = cells + (f0 * cells_per_frame + max(cell, 0)) * 3;
-  const bf16* dz_ptr = dz + (f0 * p_out + p) * O + (act ? co : 0);
+  const elem_t* dz_ptr = dz + (f0 * p_out + p) * O + (act ? co : 0);
   const long long cell_step = cells_per_frame * 3, dz_step = (long long)p_out * O;
   float* s_base = S + (act ? co : 0);
   for (long long fb = f0; fb < f1; fb += kPrefetchBwd) {
@@ -272,8 +271,8 @@ __global__ void __launch_bounds__(256, 3) embconv_bwd_reduce_kernel(const int* _
       }
       cur = nc;
       if (act) {
-        pre[0] = __fadd2_rn(pre[0], __bfloat1622float2(din[u].h[0]));
-        pre[1] = __fadd2_rn(pre[1], __bfloat1622float2(din[u].h[1]));
+        pre[0] = __fadd2_rn(pre[0], e22ff(din[u].h[0]));
+        pre[1] = __fadd2_rn(pre[1], e22ff(din[u].h[1]));
       }
     }
   }
@@ -291,7 +290,7 @@ __global__ void __launch_bounds__(256, 3) embconv_bwd_reduce_kernel(const int* _
 // sum of split-K slabs: out[i] = sum_s work[s][i], written as fp32 or bf16
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) slab_reduce_kernel(const float* __restrict__ work, void* __restrict__ out,
-                                                          long long n, int slabs, int out_bf16) {
+                                                          long long n, int slabs, int out_elem) {
   const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i >= n) return;
   float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -299,10 +298,10 @@ __global__ void __launch_bounds__(256) slab_reduce_kernel(const float* __restric
     const float4 v = *reinterpret_cast<const float4*>(work + (long long)k * n + i);
     s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
   }
-  if (out_bf16) {
-    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<bf16*>(out) + i);
-    o[0] = __floats2bfloat162_rn(s.x, s.y);
-    o[1] = __floats2bfloat162_rn(s.z, s.w);
+  if (out_elem) {
+    elem2_t* o = reinterpret_cast<elem2_t*>(reinterpret_cast<elem_t*>(out) + i);
+    o[0] = ff2e2(s.x, s.y);
+    o[1] = ff2e2(s.z, s.w);
   } else {
     *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + i) = s;
   }
@@ -330,7 +329,7 @@ extern "C" int fbam_embconv_features(const void* cells, void* feat, long long fr
   const long long blocks = (total + 255) / 256;
   if (blocks > 0x7fffffffll) return 1;
   embconv_features_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const int*>(cells), reinterpret_cast<bf16*>(feat), frames, g);
+      reinterpret_cast<const int*>(cells), reinterpret_cast<elem_t*>(feat), frames, g);
   return launch_result();
 }
 
@@ -351,8 +350,8 @@ extern "C" int fbam_embconv_fwd(const void* cells, const void* table, const void
   if (blocks > 0x7fffffffll) return 1;
   dim3 grid((unsigned)blocks, (unsigned)((O + 255) / 256));
   embconv_fwd_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const int*>(cells), reinterpret_cast<const bf16*>(table), reinterpret_cast<const float*>(pos),
-      reinterpret_cast<bf16*>(z), reinterpret_cast<bf16*>(y), frames, vocab, O, g, seg_len, nseg, z_has_input,
+      reinterpret_cast<const int*>(cells), reinterpret_cast<const elem_t*>(table), reinterpret_cast<const float*>(pos),
+      reinterpret_cast<elem_t*>(z), reinterpret_cast<elem_t*>(y), frames, vocab, O, g, seg_len, nseg, z_has_input,
       apply_gelu);
   return launch_result();
 }
@@ -373,18 +372,18 @@ extern "C" int fbam_embconv_bwd_reduce(const void* cells, const void* dz, void* 
   if (blocks > 0x7fffffffll) return 1;
   dim3 grid((unsigned)blocks, (unsigned)((O + 127) / 128));
   embconv_bwd_reduce_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const int*>(cells), reinterpret_cast<const bf16*>(dz), reinterpret_cast<float*>(S),
+      reinterpret_cast<const int*>(cells), reinterpret_cast<const elem_t*>(dz), reinterpret_cast<float*>(S),
       reinterpret_cast<float*>(D), frames, vocab, O, g, seg_len, nseg);
   return launch_result();
 }
 
 // out[i] = sum over `slabs` fp32 slabs of n elements each (n a multiple of 4, 16-byte aligned pointers).
-extern "C" int fbam_slab_reduce(const void* work, void* out, long long n, int slabs, int out_bf16, void* stream) {
+extern "C" int fbam_slab_reduce(const void* work, void* out, long long n, int slabs, int out_elem, void* stream) {
   if (n < 0 || n % 4 != 0 || slabs < 1) return 1;
-  if (reinterpret_cast<uintptr_t>(work) % 16 != 0 || reinterpret_cast<uintptr_t>(out) % (out_bf16 ? 8 : 16) != 0) return 2;
+  if (reinterpret_cast<uintptr_t>(work) % 16 != 0 || reinterpret_cast<uintptr_t>(out) % (out_elem ? 8 : 16) != 0) return 2;
   if (n == 0) return 0;
   const long long blocks = (n / 4 + 255) / 256;
   slab_reduce_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const float*>(work), out, n, slabs, out_bf16);
+      reinterpret_cast<const float*>(work), out, n, slabs, out_elem);
   return launch_result();
 }

@@ -229,7 +229,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (rank == 0 && elect_one()) {
-      const uint32_t idesc = make_idesc_bf16(256, BN, p.a_mn_major != 0, p.b_mn_major != 0);
+      const uint32_t idesc = make_idesc_f16kind(256, BN, p.a_mn_major != 0, p.b_mn_major != 0);
       const uint32_t a_lbo = p.a_mn_major ? BK * 128 : 16, b_lbo = p.b_mn_major ? BK * 128 : 16;
       const uint32_t a_kstep = p.a_mn_major ? UMMA_K * 128 : UMMA_K * 2;
       const uint32_t b_kstep = p.b_mn_major ? UMMA_K * 128 : UMMA_K * 2;
@@ -271,18 +271,27 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       const int tile_m = (tile / tiles_n + p.tile_m_rotate) % p.tiles_m, tile_n = tile % tiles_n;
       const int half = tile_m * 2 + (int)rank;
+      // the side input of the first chunk is requested before the accumulator is waited for, and that of every
+      // later chunk before the previous one is processed
+      const long long roff = row_offset2(p, half, row);
+      const elem_t* aux_row = gemm_epi::aux_row_ptr(p, roff);
+      uint4 aux[4] = {};
+      gemm_epi::aux_prefetch(aux_row, tile_n * BN + col_half * (BN / 2), p.N, aux);
       if (!mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
       fence_after_sync();
-      const long long roff = row_offset2(p, half, row);
       const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * BN;
 #pragma unroll 1
       for (int c0 = col_half * (BN / 2); c0 < (col_half + 1) * (BN / 2); c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c0, r);
-        tmem_ld_wait();
         const int n0 = tile_n * BN + c0;
+        uint4 cur[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) cur[q] = aux[q];
+        if (c0 + 32 < (col_half + 1) * (BN / 2)) gemm_epi::aux_prefetch(aux_row, n0 + 32, p.N, aux);
+        tmem_ld_wait();
         if (roff < 0 || n0 >= p.N) continue;
-        gemm_epi::store_chunk(p, roff, n0, r);
+        gemm_epi::store_chunk<false, true>(p, roff, n0, r, cur);
       }
       fence_before_sync();
       __syncwarp();
@@ -328,7 +337,7 @@ int enc2d(CUtensorMap* map, const void* base, long long rows, long long cols, lo
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  const CUresult r = enc(map, ELEM_TMAP, 2, const_cast<void*>(base), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) g_fbam_last_driver_error = (int)r;
@@ -343,7 +352,7 @@ int enc_nhwc(CUtensorMap* map, const void* base, int n, int h, int w, int c, int
   cuuint64_t strides[3] = {(cuuint64_t)c * 2, (cuuint64_t)w * c * 2, (cuuint64_t)h * w * c * 2};
   cuuint32_t box[4] = {64, (cuuint32_t)((tw - 1) * stride + 1), (cuuint32_t)((th - 1) * stride + 1), (cuuint32_t)tn};
   cuuint32_t estr[4] = {1, (cuuint32_t)stride, (cuuint32_t)stride, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+  return enc(map, ELEM_TMAP, 4, const_cast<void*>(base), dims, strides, box, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : GEMM_ERR_TENSORMAP;
 }
@@ -373,9 +382,9 @@ int launch2(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStr
 
 }  // namespace
 
-// Same contracts as fbam_gemm_bf16 / fbam_conv_bf16 (gemm_tcgen05.cu), computed by CTA pairs.  N must be a
+// Same contracts as fbam_gemm / fbam_conv (gemm_tcgen05.cu), computed by CTA pairs.  N must be a
 // multiple of 16 with BN in {128, 256}; split-K stays on the single-CTA kernel.
-extern "C" int fbam_gemm2_bf16(const void* A, long long lda, int a_mn_major, const void* B, long long ldb,
+extern "C" int fbam_gemm2(const void* A, long long lda, int a_mn_major, const void* B, long long ldb,
                                int b_mn_major, int M, int N, int K, GemmParams* params, void* stream) {
   GemmParams p = *params;
   if (M <= 0 || N <= 0 || K <= 0 || p.splits > 1) return GEMM_ERR_SHAPE;
@@ -403,7 +412,7 @@ extern "C" int fbam_gemm2_bf16(const void* A, long long lda, int a_mn_major, con
   return bn == 128 ? launch2<128>(ma, mb, p, s) : launch2<256>(ma, mb, p, s);
 }
 
-extern "C" int fbam_conv2_bf16(const void* X, int in_h, int in_w, int C, const void* Wmat, long long ldw, int N,
+extern "C" int fbam_conv2(const void* X, int in_h, int in_w, int C, const void* Wmat, long long ldw, int N,
                                GemmParams* params, void* stream) {
   GemmParams p = *params;
   ConvGeom& g = p.conv;

@@ -2,7 +2,7 @@
 #pragma once
 #include "gemm_tcgen05.h"
 #include "gelu_math.cuh"
-#include <cuda_bf16.h>
+#include "elem16.cuh"
 
 // The row-store variant of the reduce-scatter epilogue (GemmParams::rs_row_stores) is compiled in only on request
 // (-DFBAM_RS_ROW_STORES=1, `FBAMTRAIN_RS_ROW_STORES=1 python -m fbamtrain_b200.build --force`): it raises the
@@ -28,9 +28,29 @@ __device__ __forceinline__ uint4 shfl_xor_u4(const uint4& x, int lane_mask) {
   return y;
 }
 
-// r: 32 fp32 accumulator values of output row `roff / ldd`, columns [n0, n0 + 32).
-template <bool CE = false>
-__device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff, int n0, const uint32_t (&r)[32]) {
+// The epilogue reads at most one bf16 side input per element that is worth fetching a chunk ahead: the
+// pre-activation whose GELU derivative scales the result, or else the residual.  aux_row_ptr gives that input's row
+// (null when there is none, or when it cannot be read with 16-byte loads); aux_prefetch issues the four loads of
+// columns [n0, n0 + 32) so that their latency passes while the previous chunk is converted and stored.
+__device__ __forceinline__ const elem_t* aux_row_ptr(const GemmParams& p, long long roff) {
+  if (roff < 0 || !p.vec_ok) return nullptr;
+  if (p.gelu_grad_in != nullptr) return p.gelu_grad_in + roff;
+  if (p.residual != nullptr && (p.ldr % 8 == 0)) return p.residual + roff / p.ldd * p.ldr;
+  return nullptr;
+}
+
+__device__ __forceinline__ void aux_prefetch(const elem_t* aux_row, int n0, int n_total, uint4 (&aux)[4]) {
+  if (aux_row != nullptr && n0 + 32 <= n_total) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) aux[q] = *reinterpret_cast<const uint4*>(aux_row + n0 + 8 * q);
+  }
+}
+
+// r: 32 fp32 accumulator values of output row `roff / ldd`, columns [n0, n0 + 32).  With PRE, `pre` holds what
+// aux_prefetch loaded for this chunk (valid whenever the chunk takes the vector path).
+template <bool CE = false, bool PRE = false>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff, int n0, const uint32_t (&r)[32],
+                                            const uint4 (&pre)[4]) {
           float v[32];
   #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
@@ -53,22 +73,22 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
             for (int j = 0; j < 32; ++j)
               if (n0 + j < p.N)
                 v[j] += p.bias_fp32 ? reinterpret_cast<const float*>(p.bias)[n0 + j]
-                                    : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n0 + j]);
+                                    : e2f(reinterpret_cast<const elem_t*>(p.bias)[n0 + j]);
           }
           if (p.preact_out != nullptr) {
-            __nv_bfloat16* po = p.preact_out + roff + n0;
+            elem_t* po = p.preact_out + roff + n0;
             if (full_vec) {
   #pragma unroll
               for (int j = 0; j < 32; j += 8) {
-                __align__(16) __nv_bfloat162 h[4];
+                __align__(16) elem2_t h[4];
   #pragma unroll
-                for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+                for (int q = 0; q < 4; ++q) h[q] = ff2e2(v[j + 2 * q], v[j + 2 * q + 1]);
                 *reinterpret_cast<uint4*>(po + j) = *reinterpret_cast<uint4*>(h);
               }
             } else {
   #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (n0 + j < p.N) po[j] = __float2bfloat16(v[j]);
+                if (n0 + j < p.N) po[j] = f2e(v[j]);
             }
           }
           if (p.act == GEMM_ACT_GELU) {
@@ -83,15 +103,17 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
             for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
           }
           if (p.gelu_grad_in != nullptr) {
-            const __nv_bfloat16* gi = p.gelu_grad_in + roff + n0;
+            const elem_t* gi = p.gelu_grad_in + roff + n0;
             if (full_vec) {
   #pragma unroll
               for (int j = 0; j < 32; j += 8) {
-                uint4 raw = *reinterpret_cast<const uint4*>(gi + j);
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                uint4 raw;
+                if constexpr (PRE) raw = pre[j / 8];
+                else raw = *reinterpret_cast<const uint4*>(gi + j);
+                const elem2_t* h = reinterpret_cast<const elem2_t*>(&raw);
   #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                  const float2 g = gelu_math::gelu_grad2(__bfloat1622float2(h[q]));
+                  const float2 g = gelu_math::gelu_grad2(e22ff(h[q]));
                   v[j + 2 * q] *= g.x;
                   v[j + 2 * q + 1] *= g.y;
                 }
@@ -99,19 +121,21 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
             } else {
   #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (n0 + j < p.N) v[j] *= gelu_grad_f(__bfloat162float(gi[j]));
+                if (n0 + j < p.N) v[j] *= gelu_grad_f(e2f(gi[j]));
             }
           }
           if (p.residual != nullptr) {
-            const __nv_bfloat16* ri = p.residual + roff / p.ldd * p.ldr + n0;
+            const elem_t* ri = p.residual + roff / p.ldd * p.ldr + n0;
             if (full_vec && (p.ldr % 8 == 0)) {
   #pragma unroll
               for (int j = 0; j < 32; j += 8) {
-                uint4 raw = *reinterpret_cast<const uint4*>(ri + j);
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                uint4 raw;
+                if (PRE && p.gelu_grad_in == nullptr) raw = pre[j / 8];
+                else raw = *reinterpret_cast<const uint4*>(ri + j);
+                const elem2_t* h = reinterpret_cast<const elem2_t*>(&raw);
   #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                  float2 f = __bfloat1622float2(h[q]);
+                  float2 f = e22ff(h[q]);
                   v[j + 2 * q] += f.x;
                   v[j + 2 * q + 1] += f.y;
                 }
@@ -119,7 +143,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
             } else {
   #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (n0 + j < p.N) v[j] += __bfloat162float(ri[j]);
+                if (n0 + j < p.N) v[j] += e2f(ri[j]);
             }
           }
           if (p.rs_rows_per_rank > 0 && p.rs_slot_plus1 > 0) {
@@ -127,7 +151,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
             // owner's buffer (plain 16-byte stores over NVLink)
             const int m = (int)(roff / p.ldd);
             const int owner = m / p.rs_rows_per_rank;
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.rs_out[owner]) +
+            elem_t* out = reinterpret_cast<elem_t*>(p.rs_out[owner]) +
                                  ((long long)(p.rs_slot_plus1 - 1) * p.rs_rows_per_rank + (m - owner * p.rs_rows_per_rank)) *
                                      p.ldd + n0;
 #if FBAM_RS_ROW_STORES
@@ -138,9 +162,9 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
               uint4 piece[4];
   #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                __align__(16) __nv_bfloat162 h[4];
+                __align__(16) elem2_t h[4];
   #pragma unroll
-                for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]);
+                for (int e = 0; e < 4; ++e) h[e] = ff2e2(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]);
                 piece[q] = *reinterpret_cast<uint4*>(h);
               }
               const int j = (int)(threadIdx.x & 3);
@@ -164,15 +188,15 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
             if (full_vec) {
   #pragma unroll
               for (int j = 0; j < 32; j += 8) {
-                __align__(16) __nv_bfloat162 h[4];
+                __align__(16) elem2_t h[4];
   #pragma unroll
-                for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+                for (int q = 0; q < 4; ++q) h[q] = ff2e2(v[j + 2 * q], v[j + 2 * q + 1]);
                 *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
               }
             } else {
   #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (n0 + j < p.N) out[j] = __float2bfloat16(v[j]);
+                if (n0 + j < p.N) out[j] = f2e(v[j]);
             }
             return;
           }
@@ -217,33 +241,39 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
                 if (n0 + j < p.N) out[j] = p.accumulate ? out[j] + v[j] : v[j];
             }
           } else {
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + roff + n0;
+            elem_t* out = reinterpret_cast<elem_t*>(p.D) + roff + n0;
             if (full_vec) {
   #pragma unroll
               for (int j = 0; j < 32; j += 8) {
                 if (p.accumulate) {
                   uint4 raw = *reinterpret_cast<const uint4*>(out + j);
-                  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                  const elem2_t* h = reinterpret_cast<const elem2_t*>(&raw);
   #pragma unroll
                   for (int q = 0; q < 4; ++q) {
-                    float2 f = __bfloat1622float2(h[q]);
+                    float2 f = e22ff(h[q]);
                     v[j + 2 * q] += f.x;
                     v[j + 2 * q + 1] += f.y;
                   }
                 }
-                __align__(16) __nv_bfloat162 h[4];
+                __align__(16) elem2_t h[4];
   #pragma unroll
-                for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+                for (int q = 0; q < 4; ++q) h[q] = ff2e2(v[j + 2 * q], v[j + 2 * q + 1]);
                 *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<uint4*>(h);
               }
             } else {
   #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (n0 + j < p.N)
-                  out[j] = __float2bfloat16(p.accumulate ? __bfloat162float(out[j]) + v[j] : v[j]);
+                  out[j] = f2e(p.accumulate ? e2f(out[j]) + v[j] : v[j]);
             }
           }
 
+}
+
+template <bool CE = false>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff, int n0, const uint32_t (&r)[32]) {
+  const uint4 none[4] = {};
+  store_chunk<CE, false>(p, roff, n0, r, none);
 }
 
 }  // namespace gemm_epi

@@ -236,7 +236,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      const uint32_t idesc = make_idesc_bf16(128, BN, p.a_mn_major != 0, p.b_mn_major != 0);
+      const uint32_t idesc = make_idesc_f16kind(128, BN, p.a_mn_major != 0, p.b_mn_major != 0);
       // K-major: 8-row groups are 1024 B apart (SBO); one UMMA_K step = 32 B inside the swizzle row.
       // MN-major: 64-wide column panels are BK*128 B apart (LBO), 8-row K groups 1024 B apart (SBO);
       //           one UMMA_K step = 16 rows = 2048 B.
@@ -289,9 +289,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const Work wk = decode_work(p, tile, tiles_n);
       const int tile_m = wk.tile_m, tile_n = wk.tile_n;
+      // the side input of the first chunk is requested before the accumulator is waited for, and that of every
+      // later chunk before the previous one is processed
+      const long long roff = row_offset(p, tile_m, row, BM);
+      const elem_t* aux_row = gemm_epi::aux_row_ptr(p, roff);
+      uint4 aux[4] = {};
+      gemm_epi::aux_prefetch(aux_row, tile_n * BN + c_begin, p.N, aux);
       if (!mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
       fence_after_sync();
-      const long long roff = row_offset(p, tile_m, row, BM);
       const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + (MH == 2 ? second * BN : acc * BN);
       // fused cross-entropy statistics: running (maximum, sum of exp relative to it) of this thread's row over the
       // columns of the tile half it owns, and the target column's logit when it falls into them
@@ -305,8 +310,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       for (int c0 = c_begin; c0 < c_end; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c0, r);
-        tmem_ld_wait();
         const int n0 = tile_n * BN + c0;
+        uint4 cur[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) cur[q] = aux[q];
+        if (c0 + 32 < c_end) gemm_epi::aux_prefetch(aux_row, n0 + 32, p.N, aux);
+        tmem_ld_wait();
         if (roff < 0 || n0 >= p.N) continue;
         if constexpr (CE) {
           if (p.ce_mode == 1) {
@@ -347,7 +356,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           continue;
         }
         if (wk.k_end <= wk.k_begin) continue;
-        gemm_epi::store_chunk<CE>(p, roff, n0, r);
+        gemm_epi::store_chunk<CE, true>(p, roff, n0, r, cur);
       }
       if constexpr (CE) {
         if (p.ce_mode == 1 && roff >= 0) {
@@ -406,7 +415,7 @@ int encode_2d(CUtensorMap* map, const void* base, long long rows, long long cols
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = enc(map, ELEM_TMAP, 2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) g_fbam_last_driver_error = (int)r;
@@ -423,7 +432,7 @@ int encode_nhwc(CUtensorMap* map, const void* base, int n, int h, int w, int c, 
   cuuint64_t strides[3] = {(cuuint64_t)c * 2, (cuuint64_t)w * c * 2, (cuuint64_t)h * w * c * 2};
   cuuint32_t box[4] = {64, (cuuint32_t)((tw - 1) * stride + 1), (cuuint32_t)((th - 1) * stride + 1), (cuuint32_t)tn};
   cuuint32_t estr[4] = {1, (cuuint32_t)stride, (cuuint32_t)stride, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = enc(map, ELEM_TMAP, 4, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : GEMM_ERR_TENSORMAP;
@@ -503,6 +512,9 @@ extern "C" void fbam_gemm_params_layout(long long* out) {
   out[7] = (long long)sizeof(ConvGeom);
 }
 
+// 1 when this library was compiled with IEEE half elements, 0 for bf16 (see elem16.cuh).
+extern "C" int fbam_elem_is_fp16() { return ELEM_IS_FP16; }
+
 // 1 when the row-store variant of the reduce-scatter epilogue was compiled in (see gemm_epilogue.cuh).
 extern "C" int fbam_has_rs_row_stores() { return FBAM_RS_ROW_STORES; }
 
@@ -512,7 +524,7 @@ extern "C" int fbam_set_reserved_sms(int n) {
   return old;
 }
 
-extern "C" int fbam_gemm_bf16(const void* A, long long lda, int a_mn_major, const void* B, long long ldb,
+extern "C" int fbam_gemm(const void* A, long long lda, int a_mn_major, const void* B, long long ldb,
                               int b_mn_major, int M, int N, int K, GemmParams* params, void* stream) {
   GemmParams p = *params;
   if (M <= 0 || N <= 0 || K <= 0) return GEMM_ERR_SHAPE;
@@ -564,7 +576,7 @@ extern "C" int fbam_gemm_bf16(const void* A, long long lda, int a_mn_major, cons
 
 // Implicit-GEMM convolution pass.  `X` is the gathered NHWC tensor [batch, in_h, in_w, C]; `Wmat` is the
 // filter matrix [N, taps*C] (K-major; tap-major then channel).  See ConvGeom for the tiling fields.
-extern "C" int fbam_conv_bf16(const void* X, int in_h, int in_w, int C, const void* Wmat, long long ldw, int N,
+extern "C" int fbam_conv(const void* X, int in_h, int in_w, int C, const void* Wmat, long long ldw, int N,
                               GemmParams* params, void* stream) {
   GemmParams p = *params;
   ConvGeom& g = p.conv;
@@ -597,7 +609,7 @@ extern "C" int fbam_conv_bf16(const void* X, int in_h, int in_w, int C, const vo
 //   dW[o, tap, c] += sum_pixels dY[pixel, o] * X[gather(pixel, tap), c]
 // dY: NHWC [batch, out_h, out_w, O]; X: NHWC [batch, in_h, in_w, C]; dW: fp32 [O, taps*C], must be zeroed by
 // the caller (CTAs add their partial sums atomically).  conv.{tn,th,tw} describe the 64-pixel K brick.
-extern "C" int fbam_conv_wgrad_bf16(const void* dY, int O, const void* X, int in_h, int in_w, int C,
+extern "C" int fbam_conv_wgrad(const void* dY, int O, const void* X, int in_h, int in_w, int C,
                                     GemmParams* params, void* stream) {
   GemmParams p = *params;
   ConvGeom& g = p.conv;

@@ -1,7 +1,7 @@
 // Parameter blocks of the tcgen05 GEMM / implicit-GEMM convolution entry points.  The Python side
 // mirrors these structs field for field with ctypes (fbamtrain_b200/ops/native.py).
 #pragma once
-#include <cuda_bf16.h>
+#include "elem16.cuh"
 #include <stdint.h>
 
 enum { GEMM_MODE_PLAIN = 0, GEMM_MODE_CONV = 1, GEMM_MODE_WGRAD = 2 };
@@ -31,10 +31,10 @@ struct GemmParams {
   void* D;                          // output, bf16 or fp32, row pitch ldd elements
   long long ldd;
   const void* bias;                 // [N] or null
-  const __nv_bfloat16* residual;    // [M, N] pitch ldr, added after the activation, or null
+  const elem_t* residual;    // [M, N] pitch ldr, added after the activation, or null
   long long ldr;
-  __nv_bfloat16* preact_out;        // [M, N] pitch ldd: value before the activation, or null
-  const __nv_bfloat16* gelu_grad_in;  // [M, N] pitch ldd: result is multiplied by gelu'(this), or null
+  elem_t* preact_out;        // [M, N] pitch ldd: value before the activation, or null
+  const elem_t* gelu_grad_in;  // [M, N] pitch ldd: result is multiplied by gelu'(this), or null
   int* status;                      // device word, receives an error code on a timed-out wait
   float alpha;
   int out_fp32, bias_fp32, act, accumulate;

@@ -10,7 +10,7 @@
 // positions (kernels/avg_pool2d.py:35-144, avg_pool2d_bwd.py:6-214, mean_reduce.py:30-108), column sums for bias
 // gradients (kernels/sum_reduce.py:33-140), GELU / GeGLU and their gradients (kernels/act.py:43-86), and the AdamW
 // and SGD steps (kernels/optimizer.py:6-79).
-#include <cuda_bf16.h>
+#include "elem16.cuh"
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -18,7 +18,6 @@
 
 namespace {
 
-typedef __nv_bfloat16 bf16;
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -78,11 +77,11 @@ __device__ __forceinline__ void gelu_grad8(const float* x, float* y) {
   }
 }
 
-struct alignas(16) Pack8 { __nv_bfloat162 h[4]; };
+struct alignas(16) Pack8 { elem2_t h[4]; };
 __device__ __forceinline__ void unpack8(const Pack8& p, float* f) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float2 t = __bfloat1622float2(p.h[i]);
+    float2 t = e22ff(p.h[i]);
     f[2 * i] = t.x;
     f[2 * i + 1] = t.y;
   }
@@ -90,7 +89,7 @@ __device__ __forceinline__ void unpack8(const Pack8& p, float* f) {
 __device__ __forceinline__ Pack8 pack8(const float* f) {
   Pack8 p;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) p.h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  for (int i = 0; i < 4; ++i) p.h[i] = ff2e2(f[2 * i], f[2 * i + 1]);
   return p;
 }
 
@@ -98,12 +97,12 @@ __device__ __forceinline__ Pack8 pack8(const float* f) {
 // RMSNorm: one warp per row for dim <= 2048 (kept in registers), bf16 IO, fp32 math.
 // ------------------------------------------------------------------------------------------------
 template <int VEC_PER_LANE>  // dim = VEC_PER_LANE * 32 * 8 at most
-__global__ void rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
+__global__ void rmsnorm_fwd_kernel(const elem_t* __restrict__ x, const elem_t* __restrict__ w, elem_t* __restrict__ y,
                                    float* __restrict__ rstd, long long rows, int dim, float eps) {
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
-  const bf16* xr = x + row * dim;
+  const elem_t* xr = x + row * dim;
   float v[VEC_PER_LANE][8];
   float ss = 0.0f;
 #pragma unroll
@@ -134,8 +133,8 @@ __global__ void rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __res
 // dx = rstd * (g*dy - xhat * mean(g*dy*xhat));  dgamma[c] += sum_rows dy*xhat (fp32 atomics, one per
 // column per block after an in-block reduction over the block's rows).
 template <int VEC_PER_LANE>
-__global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
-                                   const float* __restrict__ rstd, bf16* __restrict__ dx, float* __restrict__ dgamma,
+__global__ void rmsnorm_bwd_kernel(const elem_t* __restrict__ dy, const elem_t* __restrict__ x, const elem_t* __restrict__ w,
+                                   const float* __restrict__ rstd, elem_t* __restrict__ dx, float* __restrict__ dgamma,
                                    long long rows, int dim, int rows_per_warp) {
   extern __shared__ float sm_dg[];  // [dim]
   for (int c = threadIdx.x; c < dim; c += blockDim.x) sm_dg[c] = 0.0f;
@@ -198,40 +197,40 @@ __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __re
 }
 
 // LayerNorm forward (block per row).
-__global__ void layernorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ b,
-                                     bf16* __restrict__ y, int dim, float eps) {
+__global__ void layernorm_fwd_kernel(const elem_t* __restrict__ x, const elem_t* __restrict__ w, const elem_t* __restrict__ b,
+                                     elem_t* __restrict__ y, int dim, float eps) {
   __shared__ float scratch[32];
   const long long row = blockIdx.x;
-  const bf16* xr = x + row * dim;
+  const elem_t* xr = x + row * dim;
   float s = 0.0f;
-  for (int c = threadIdx.x; c < dim; c += blockDim.x) s += __bfloat162float(xr[c]);
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) s += e2f(xr[c]);
   const float mean = block_sum(s, scratch) / dim;
   float q = 0.0f;
   for (int c = threadIdx.x; c < dim; c += blockDim.x) {
-    const float d = __bfloat162float(xr[c]) - mean;
+    const float d = e2f(xr[c]) - mean;
     q += d * d;
   }
   const float r = rsqrtf(block_sum(q, scratch) / dim + eps);
   for (int c = threadIdx.x; c < dim; c += blockDim.x) {
-    float o = (__bfloat162float(xr[c]) - mean) * r * __bfloat162float(w[c]);
-    if (b != nullptr) o += __bfloat162float(b[c]);
-    y[row * dim + c] = __float2bfloat16(o);
+    float o = (e2f(xr[c]) - mean) * r * e2f(w[c]);
+    if (b != nullptr) o += e2f(b[c]);
+    y[row * dim + c] = f2e(o);
   }
 }
 
 // LayerNorm forward that also keeps the row statistics for the backward.
-__global__ void layernorm_fwd_stats_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
-                                           const bf16* __restrict__ b, bf16* __restrict__ y, float* __restrict__ mean_out,
+__global__ void layernorm_fwd_stats_kernel(const elem_t* __restrict__ x, const elem_t* __restrict__ w,
+                                           const elem_t* __restrict__ b, elem_t* __restrict__ y, float* __restrict__ mean_out,
                                            float* __restrict__ rstd_out, int dim, float eps) {
   __shared__ float scratch[32];
   const long long row = blockIdx.x;
-  const bf16* xr = x + row * dim;
+  const elem_t* xr = x + row * dim;
   float s = 0.0f;
-  for (int c = threadIdx.x; c < dim; c += blockDim.x) s += __bfloat162float(xr[c]);
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) s += e2f(xr[c]);
   const float mean = block_sum(s, scratch) / dim;
   float q = 0.0f;
   for (int c = threadIdx.x; c < dim; c += blockDim.x) {
-    const float d = __bfloat162float(xr[c]) - mean;
+    const float d = e2f(xr[c]) - mean;
     q += d * d;
   }
   const float r = rsqrtf(block_sum(q, scratch) / dim + eps);
@@ -240,9 +239,9 @@ __global__ void layernorm_fwd_stats_kernel(const bf16* __restrict__ x, const bf1
     rstd_out[row] = r;
   }
   for (int c = threadIdx.x; c < dim; c += blockDim.x) {
-    float o = (__bfloat162float(xr[c]) - mean) * r * __bfloat162float(w[c]);
-    if (b != nullptr) o += __bfloat162float(b[c]);
-    y[row * dim + c] = __float2bfloat16(o);
+    float o = (e2f(xr[c]) - mean) * r * e2f(w[c]);
+    if (b != nullptr) o += e2f(b[c]);
+    y[row * dim + c] = f2e(o);
   }
 }
 
@@ -251,9 +250,9 @@ __global__ void layernorm_fwd_stats_kernel(const bf16* __restrict__ x, const bf1
 // A block walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; a thread owns columns threadIdx.x + k * blockDim.x
 // (k < COLS) and keeps their dw / db sums in registers across its rows: one atomic per column and block at the end.
 template <int COLS>
-__global__ void __launch_bounds__(256) layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
-                                                            const bf16* __restrict__ w, const float* __restrict__ mean,
-                                                            const float* __restrict__ rstd, bf16* __restrict__ dx,
+__global__ void __launch_bounds__(256) layernorm_bwd_kernel(const elem_t* __restrict__ dy, const elem_t* __restrict__ x,
+                                                            const elem_t* __restrict__ w, const float* __restrict__ mean,
+                                                            const float* __restrict__ rstd, elem_t* __restrict__ dx,
                                                             float* __restrict__ dw, float* __restrict__ db,
                                                             long long rows, int dim) {
   __shared__ float scratch[32];
@@ -261,7 +260,7 @@ __global__ void __launch_bounds__(256) layernorm_bwd_kernel(const bf16* __restri
 #pragma unroll
   for (int k = 0; k < COLS; ++k) {
     const int c = threadIdx.x + k * blockDim.x;
-    wreg[k] = c < dim ? __bfloat162float(w[c]) : 0.0f;
+    wreg[k] = c < dim ? e2f(w[c]) : 0.0f;
     dw_acc[k] = 0.0f;
     db_acc[k] = 0.0f;
   }
@@ -275,8 +274,8 @@ __global__ void __launch_bounds__(256) layernorm_bwd_kernel(const bf16* __restri
       xh[k] = 0.0f;
       g[k] = 0.0f;
       if (c < dim) {
-        const float d = __bfloat162float(dy[row * dim + c]);
-        xh[k] = (__bfloat162float(x[row * dim + c]) - m) * r;
+        const float d = e2f(dy[row * dim + c]);
+        xh[k] = (e2f(x[row * dim + c]) - m) * r;
         g[k] = d * wreg[k];
         dw_acc[k] += d * xh[k];
         db_acc[k] += d;
@@ -289,7 +288,7 @@ __global__ void __launch_bounds__(256) layernorm_bwd_kernel(const bf16* __restri
 #pragma unroll
     for (int k = 0; k < COLS; ++k) {
       const int c = threadIdx.x + k * blockDim.x;
-      if (c < dim) dx[row * dim + c] = __float2bfloat16(r * (g[k] - mg - xh[k] * mgx));
+      if (c < dim) dx[row * dim + c] = f2e(r * (g[k] - mg - xh[k] * mgx));
     }
   }
 #pragma unroll
@@ -306,7 +305,7 @@ __global__ void __launch_bounds__(256) layernorm_bwd_kernel(const bf16* __restri
 // element-wise
 // ------------------------------------------------------------------------------------------------
 // mode 0: y = gelu(x); mode 1: dx = dy * gelu'(x)
-__global__ void gelu_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, bf16* __restrict__ out,
+__global__ void gelu_kernel(const elem_t* __restrict__ x, const elem_t* __restrict__ dy, elem_t* __restrict__ out,
                             long long n8, int mode) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n8) return;
@@ -325,7 +324,7 @@ __global__ void gelu_kernel(const bf16* __restrict__ x, const bf16* __restrict__
 }
 
 // GeGLU over the channel dimension: x [rows, 2C] -> y [rows, C] = value * gelu(gate).
-__global__ void geglu_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long rows, int c) {
+__global__ void geglu_fwd_kernel(const elem_t* __restrict__ x, elem_t* __restrict__ y, long long rows, int c) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int c8 = c / 8;
   if (i >= rows * c8) return;
@@ -339,7 +338,7 @@ __global__ void geglu_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ 
   for (int j = 0; j < 8; ++j) o[j] *= v[j];
   *reinterpret_cast<Pack8*>(y + row * c + col) = pack8(o);
 }
-__global__ void geglu_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, bf16* __restrict__ dx,
+__global__ void geglu_bwd_kernel(const elem_t* __restrict__ x, const elem_t* __restrict__ dy, elem_t* __restrict__ dx,
                                  long long rows, int c) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int c8 = c / 8;
@@ -362,7 +361,7 @@ __global__ void geglu_bwd_kernel(const bf16* __restrict__ x, const bf16* __restr
 }
 
 // 2x2 stride-2 average pool, NHWC.  bwd=1 scatters dy/4 back.
-__global__ void avgpool2x2_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, long long n, int oh, int ow,
+__global__ void avgpool2x2_kernel(const elem_t* __restrict__ in, elem_t* __restrict__ out, long long n, int oh, int ow,
                                   int c, int bwd) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int c8 = c / 8;
@@ -406,7 +405,7 @@ __global__ void avgpool2x2_kernel(const bf16* __restrict__ in, bf16* __restrict_
 
 // Global average pool over `pix` positions: x [n, pix, c] -> y [n, c].  One block per (n, 8-channel-group
 // slab of 32 groups); threads stride over positions.
-__global__ void global_avgpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, int pix, int c) {
+__global__ void global_avgpool_fwd_kernel(const elem_t* __restrict__ x, elem_t* __restrict__ y, int pix, int c) {
   __shared__ float red[8][33][8];
   const long long n = blockIdx.x;
   const int cg = blockIdx.y * 32 + (threadIdx.x & 31);  // 8-channel group
@@ -436,32 +435,49 @@ __global__ void global_avgpool_fwd_kernel(const bf16* __restrict__ x, bf16* __re
   }
 }
 // dx[n, p, :] = dy[n, :] / pix, optionally multiplied by gelu'(z[n, p, :]) (z = pre-activation of the
-// GELU that fed the pool), which folds the activation gradient into the same pass.
-__global__ void global_avgpool_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ z,
-                                          bf16* __restrict__ dx, long long n, int pix, int c) {
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const int c8 = c / 8;
-  if (i >= n * pix * c8) return;
-  const int col = (int)(i % c8) * 8;
-  const long long b = i / c8 / pix;
-  float v[8];
-  unpack8(*reinterpret_cast<const Pack8*>(dy + b * c + col), v);
-  const float inv = 1.0f / pix;
-  if (z != nullptr) {
-    float zv[8], gz[8];
-    unpack8(reinterpret_cast<const Pack8*>(z)[i], zv);
-    gelu_grad8(zv, gz);
+// GELU that fed the pool), which folds the activation gradient into the same pass.  Grid-stride over 16-byte
+// groups, four per thread and trip with all loads issued before the arithmetic; I is a 32-bit index type whenever
+// the group count fits one (64-bit division costs more than the rest of the thread's work).
+template <typename I>
+__global__ void __launch_bounds__(256) global_avgpool_bwd_kernel(const elem_t* __restrict__ dy, const elem_t* __restrict__ z,
+                                                                 elem_t* __restrict__ dx, I total, I pix, I c8) {
+  constexpr int kUnroll = 4;
+  const I stride = (I)gridDim.x * blockDim.x;
+  const I per_image = pix * c8;
+  const float inv = 1.0f / (float)pix;
+  for (I base = (I)blockIdx.x * blockDim.x + threadIdx.x; base < total; base += stride * kUnroll) {
+    Pack8 zr[kUnroll], dr[kUnroll];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] *= inv * gz[j];
-  } else {
+    for (int u = 0; u < kUnroll; ++u) {
+      const I i = base + (I)u * stride;
+      if (i < total) {
+        if (z != nullptr) zr[u] = reinterpret_cast<const Pack8*>(z)[i];
+        dr[u] = reinterpret_cast<const Pack8*>(dy)[(i / per_image) * c8 + i % c8];
+      }
+    }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] *= inv;
+    for (int u = 0; u < kUnroll; ++u) {
+      const I i = base + (I)u * stride;
+      if (i >= total) continue;
+      float v[8];
+      unpack8(dr[u], v);
+      if (z != nullptr) {
+        float zv[8], gz[8];
+        unpack8(zr[u], zv);
+        gelu_grad8(zv, gz);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] *= inv * gz[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] *= inv;
+      }
+      reinterpret_cast<Pack8*>(dx)[i] = pack8(v);
+    }
   }
-  reinterpret_cast<Pack8*>(dx)[i] = pack8(v);
 }
 
 // Column sums of a bf16 matrix [rows, cols] into fp32 (bias gradients): out[c] += sum_r x[r, c].
-__global__ void colsum_kernel(const bf16* __restrict__ x, float* __restrict__ out, long long rows, int cols,
+__global__ void colsum_kernel(const elem_t* __restrict__ x, float* __restrict__ out, long long rows, int cols,
                               int rows_per_block) {
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (c >= cols) return;
@@ -491,7 +507,7 @@ __global__ void colsum_kernel(const bf16* __restrict__ x, float* __restrict__ ou
 template <bool SMEM_TABLE>
 __global__ void __launch_bounds__(512) cell_embed_fwd_kernel(const int* __restrict__ cells, const float* __restrict__ cp_embed,
                                       const float* __restrict__ pos_embed, const float* __restrict__ colour,
-                                      bf16* __restrict__ out, long long frames, int positions, int e, int vocab,
+                                      elem_t* __restrict__ out, long long frames, int positions, int e, int vocab,
                                       int frames_per_block) {
   extern __shared__ uint4 embed_smem[];
   const int e8 = e / 8;
@@ -583,7 +599,7 @@ __global__ void __launch_bounds__(512) cell_embed_fwd_kernel(const int* __restri
 //   * code-point gradient: consecutive frames mostly show the same glyph at a position, so the thread
 //     accumulates while the code point stays the same and issues its 8 atomics only when it changes
 //     (run-length flushing); worst case (every frame differs) this degenerates to one flush per cell.
-__global__ void cell_embed_bwd_kernel(const int* __restrict__ cells, const bf16* __restrict__ dout,
+__global__ void cell_embed_bwd_kernel(const int* __restrict__ cells, const elem_t* __restrict__ dout,
                                       float* __restrict__ d_cp, float* __restrict__ d_pos,
                                       float* __restrict__ d_colour, long long frames, int positions, int e, int vocab,
                                       int frames_per_block) {
@@ -674,28 +690,28 @@ __global__ void cell_embed_bwd_kernel(const int* __restrict__ cells, const bf16*
 // ------------------------------------------------------------------------------------------------
 // logits [rows, ld] (first `vocab` columns valid).  loss_sum += scale * sum_rows (lse - logit[target]);
 // logits are overwritten with scale * (softmax - onehot); padding columns get 0.
-__global__ void ce_fwd_bwd_kernel(bf16* __restrict__ logits, const long long* __restrict__ targets,
+__global__ void ce_fwd_bwd_kernel(elem_t* __restrict__ logits, const long long* __restrict__ targets,
                                   float* __restrict__ loss_sum, int vocab, int ld, float scale, int write_grad) {
   __shared__ float scratch[32];
   const long long row = blockIdx.x;
-  bf16* lr = logits + row * ld;
+  elem_t* lr = logits + row * ld;
   float mx = -INFINITY;
-  for (int c = threadIdx.x; c < vocab; c += blockDim.x) mx = fmaxf(mx, __bfloat162float(lr[c]));
+  for (int c = threadIdx.x; c < vocab; c += blockDim.x) mx = fmaxf(mx, e2f(lr[c]));
   mx = block_max(mx, scratch);
   float s = 0.0f;
-  for (int c = threadIdx.x; c < vocab; c += blockDim.x) s += __expf(__bfloat162float(lr[c]) - mx);
+  for (int c = threadIdx.x; c < vocab; c += blockDim.x) s += __expf(e2f(lr[c]) - mx);
   s = block_sum(s, scratch);
   const int t = (int)targets[row];
   if (threadIdx.x == 0) {
-    const float lt = (t >= 0 && t < vocab) ? __bfloat162float(lr[t]) : 0.0f;
+    const float lt = (t >= 0 && t < vocab) ? e2f(lr[t]) : 0.0f;
     atomicAdd(loss_sum, scale * (logf(s) + mx - lt));
   }
   if (!write_grad) return;
   const float inv = 1.0f / s;
   for (int c = threadIdx.x; c < ld; c += blockDim.x) {
     float g = 0.0f;
-    if (c < vocab) g = scale * (__expf(__bfloat162float(lr[c]) - mx) * inv - (c == t ? 1.0f : 0.0f));
-    lr[c] = __float2bfloat16(g);
+    if (c < vocab) g = scale * (__expf(e2f(lr[c]) - mx) * inv - (c == t ? 1.0f : 0.0f));
+    lr[c] = f2e(g);
   }
 }
 
@@ -724,7 +740,7 @@ __global__ void ce_combine_kernel(const float* __restrict__ partial, const float
 
 // Same with fp32 logits in (the LM-head GEMM keeps its fp32 accumulators) and bf16 gradient out: the loss and the
 // softmax are then free of the bf16 rounding of the logits.
-__global__ void ce_fwd_bwd_f32_kernel(const float* __restrict__ logits, bf16* __restrict__ dlogits,
+__global__ void ce_fwd_bwd_f32_kernel(const float* __restrict__ logits, elem_t* __restrict__ dlogits,
                                       const long long* __restrict__ targets, float* __restrict__ loss_sum, int vocab,
                                       int ld, float scale) {
   __shared__ float scratch[32];
@@ -743,11 +759,11 @@ __global__ void ce_fwd_bwd_f32_kernel(const float* __restrict__ logits, bf16* __
   }
   if (dlogits == nullptr) return;
   const float inv = 1.0f / s;
-  bf16* dr = dlogits + row * ld;
+  elem_t* dr = dlogits + row * ld;
   for (int c = threadIdx.x; c < ld; c += blockDim.x) {
     float g = 0.0f;
     if (c < vocab) g = scale * (__expf(lr[c] - mx) * inv - (c == t ? 1.0f : 0.0f));
-    dr[c] = __float2bfloat16(g);
+    dr[c] = f2e(g);
   }
 }
 
@@ -769,8 +785,8 @@ __global__ void adamw_kernel(PT* __restrict__ param, const PT* __restrict__ grad
     vv[0] = tv.x; vv[1] = tv.y; vv[2] = tv.z; vv[3] = tv.w;
     if constexpr (sizeof(PT) == 2) {
       const uint2 raw = *reinterpret_cast<const uint2*>(grad + i0);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-      const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+      const elem2_t* h = reinterpret_cast<const elem2_t*>(&raw);
+      const float2 a = e22ff(h[0]), b = e22ff(h[1]);
       g[0] = a.x; g[1] = a.y; g[2] = b.x; g[3] = b.y;
     } else {
       const float4 tg = *reinterpret_cast<const float4*>(grad + i0);
@@ -781,8 +797,8 @@ __global__ void adamw_kernel(PT* __restrict__ param, const PT* __restrict__ grad
       w[0] = tw.x; w[1] = tw.y; w[2] = tw.z; w[3] = tw.w;
     } else if constexpr (sizeof(PT) == 2) {
       const uint2 raw = *reinterpret_cast<const uint2*>(param + i0);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-      const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+      const elem2_t* h = reinterpret_cast<const elem2_t*>(&raw);
+      const float2 a = e22ff(h[0]), b = e22ff(h[1]);
       w[0] = a.x; w[1] = a.y; w[2] = b.x; w[3] = b.y;
     } else {
       const float4 tw = *reinterpret_cast<const float4*>(param + i0);
@@ -794,9 +810,9 @@ __global__ void adamw_kernel(PT* __restrict__ param, const PT* __restrict__ grad
     const long long i = i0 + k;
     if (!vec) {
       if (i >= n) return;
-      if constexpr (sizeof(PT) == 2) g[k] = __bfloat162float(grad[i]); else g[k] = grad[i];
+      if constexpr (sizeof(PT) == 2) g[k] = e2f(grad[i]); else g[k] = grad[i];
       if (master != nullptr) w[k] = master[i];
-      else if constexpr (sizeof(PT) == 2) w[k] = __bfloat162float(param[i]); else w[k] = param[i];
+      else if constexpr (sizeof(PT) == 2) w[k] = e2f(param[i]); else w[k] = param[i];
       mm[k] = m[i];
       vv[k] = v[i];
     }
@@ -809,7 +825,7 @@ __global__ void adamw_kernel(PT* __restrict__ param, const PT* __restrict__ grad
       m[i] = mm[k];
       v[i] = vv[k];
       if (master != nullptr) master[i] = w[k];
-      if constexpr (sizeof(PT) == 2) param[i] = __float2bfloat16(w[k]); else param[i] = w[k];
+      if constexpr (sizeof(PT) == 2) param[i] = f2e(w[k]); else param[i] = w[k];
     }
   }
   if (vec) {
@@ -817,7 +833,7 @@ __global__ void adamw_kernel(PT* __restrict__ param, const PT* __restrict__ grad
     *reinterpret_cast<float4*>(v + i0) = make_float4(vv[0], vv[1], vv[2], vv[3]);
     if (master != nullptr) *reinterpret_cast<float4*>(master + i0) = make_float4(w[0], w[1], w[2], w[3]);
     if constexpr (sizeof(PT) == 2) {
-      __align__(8) __nv_bfloat162 h[2] = {__floats2bfloat162_rn(w[0], w[1]), __floats2bfloat162_rn(w[2], w[3])};
+      __align__(8) elem2_t h[2] = {ff2e2(w[0], w[1]), ff2e2(w[2], w[3])};
       *reinterpret_cast<uint2*>(param + i0) = *reinterpret_cast<uint2*>(h);
     } else {
       *reinterpret_cast<float4*>(param + i0) = make_float4(w[0], w[1], w[2], w[3]);
@@ -826,14 +842,14 @@ __global__ void adamw_kernel(PT* __restrict__ param, const PT* __restrict__ grad
 }
 
 template <int V>
-int launch_rms_fwd(const bf16* x, const bf16* w, bf16* y, float* rstd, long long rows, int dim, float eps,
+int launch_rms_fwd(const elem_t* x, const elem_t* w, elem_t* y, float* rstd, long long rows, int dim, float eps,
                    cudaStream_t s) {
   const int warps = 8;
   rmsnorm_fwd_kernel<V><<<(unsigned)((rows + warps - 1) / warps), warps * 32, 0, s>>>(x, w, y, rstd, rows, dim, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 template <int V>
-int launch_rms_bwd(const bf16* dy, const bf16* x, const bf16* w, const float* rstd, bf16* dx, float* dg, long long rows,
+int launch_rms_bwd(const elem_t* dy, const elem_t* x, const elem_t* w, const float* rstd, elem_t* dx, float* dg, long long rows,
                    int dim, cudaStream_t s) {
   const int warps = 8, rpw = 8;
   const long long blocks = (rows + warps * rpw - 1) / (warps * rpw);
@@ -852,9 +868,9 @@ __global__ void sgd_kernel(PT* __restrict__ param, const PT* __restrict__ grad, 
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float g, w;
-  if constexpr (sizeof(PT) == 2) g = __bfloat162float(grad[i]); else g = grad[i];
+  if constexpr (sizeof(PT) == 2) g = e2f(grad[i]); else g = grad[i];
   if (master != nullptr) w = master[i];
-  else if constexpr (sizeof(PT) == 2) w = __bfloat162float(param[i]); else w = param[i];
+  else if constexpr (sizeof(PT) == 2) w = e2f(param[i]); else w = param[i];
   g += wd * w;
   if (velocity != nullptr) {
     const float v = mu * velocity[i] + g;
@@ -863,7 +879,7 @@ __global__ void sgd_kernel(PT* __restrict__ param, const PT* __restrict__ grad, 
   }
   w -= lr * g;
   if (master != nullptr) master[i] = w;
-  if constexpr (sizeof(PT) == 2) param[i] = __float2bfloat16(w); else param[i] = w;
+  if constexpr (sizeof(PT) == 2) param[i] = f2e(w); else param[i] = w;
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -917,24 +933,24 @@ extern "C" {
 int fbam_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int dim, float eps,
                      void* stream) {
   if (dim % 8 != 0 || dim > 8192) return 1;
-  const bf16 *X = (const bf16*)x, *W = (const bf16*)w;
-  if (dim <= 256) return launch_rms_fwd<1>(X, W, (bf16*)y, rstd, rows, dim, eps, STREAM(stream));
-  if (dim <= 512) return launch_rms_fwd<2>(X, W, (bf16*)y, rstd, rows, dim, eps, STREAM(stream));
-  if (dim <= 1024) return launch_rms_fwd<4>(X, W, (bf16*)y, rstd, rows, dim, eps, STREAM(stream));
-  if (dim <= 2048) return launch_rms_fwd<8>(X, W, (bf16*)y, rstd, rows, dim, eps, STREAM(stream));
-  if (dim <= 4096) return launch_rms_fwd<16>(X, W, (bf16*)y, rstd, rows, dim, eps, STREAM(stream));
-  return launch_rms_fwd<32>(X, W, (bf16*)y, rstd, rows, dim, eps, STREAM(stream));
+  const elem_t *X = (const elem_t*)x, *W = (const elem_t*)w;
+  if (dim <= 256) return launch_rms_fwd<1>(X, W, (elem_t*)y, rstd, rows, dim, eps, STREAM(stream));
+  if (dim <= 512) return launch_rms_fwd<2>(X, W, (elem_t*)y, rstd, rows, dim, eps, STREAM(stream));
+  if (dim <= 1024) return launch_rms_fwd<4>(X, W, (elem_t*)y, rstd, rows, dim, eps, STREAM(stream));
+  if (dim <= 2048) return launch_rms_fwd<8>(X, W, (elem_t*)y, rstd, rows, dim, eps, STREAM(stream));
+  if (dim <= 4096) return launch_rms_fwd<16>(X, W, (elem_t*)y, rstd, rows, dim, eps, STREAM(stream));
+  return launch_rms_fwd<32>(X, W, (elem_t*)y, rstd, rows, dim, eps, STREAM(stream));
 }
 
 int fbam_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dgamma,
                      long long rows, int dim, void* stream) {
   if (dim % 8 != 0 || dim > 4096) return 1;
-  const bf16 *DY = (const bf16*)dy, *X = (const bf16*)x, *W = (const bf16*)w;
-  if (dim <= 256) return launch_rms_bwd<1>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
-  if (dim <= 512) return launch_rms_bwd<2>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
-  if (dim <= 1024) return launch_rms_bwd<4>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
-  if (dim <= 2048) return launch_rms_bwd<8>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
-  return launch_rms_bwd<16>(DY, X, W, rstd, (bf16*)dx, dgamma, rows, dim, STREAM(stream));
+  const elem_t *DY = (const elem_t*)dy, *X = (const elem_t*)x, *W = (const elem_t*)w;
+  if (dim <= 256) return launch_rms_bwd<1>(DY, X, W, rstd, (elem_t*)dx, dgamma, rows, dim, STREAM(stream));
+  if (dim <= 512) return launch_rms_bwd<2>(DY, X, W, rstd, (elem_t*)dx, dgamma, rows, dim, STREAM(stream));
+  if (dim <= 1024) return launch_rms_bwd<4>(DY, X, W, rstd, (elem_t*)dx, dgamma, rows, dim, STREAM(stream));
+  if (dim <= 2048) return launch_rms_bwd<8>(DY, X, W, rstd, (elem_t*)dx, dgamma, rows, dim, STREAM(stream));
+  return launch_rms_bwd<16>(DY, X, W, rstd, (elem_t*)dx, dgamma, rows, dim, STREAM(stream));
 }
 
 // partial: fp32 [rows][slots][2] (maximum, sum of exp) from the head GEMM's statistics epilogue; tgt_logit: fp32 [rows];
@@ -952,8 +968,8 @@ int fbam_ce_combine(const float* partial, const float* tgt_logit, float* lse, fl
 int fbam_layernorm_fwd_stats(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
                              long long rows, int dim, float eps, void* stream) {
   if (rows <= 0 || dim <= 0) return rows == 0 ? 0 : 1;
-  layernorm_fwd_stats_kernel<<<(unsigned)rows, 256, 0, STREAM(stream)>>>((const bf16*)x, (const bf16*)w, (const bf16*)b,
-                                                                        (bf16*)y, mean, rstd, dim, eps);
+  layernorm_fwd_stats_kernel<<<(unsigned)rows, 256, 0, STREAM(stream)>>>((const elem_t*)x, (const elem_t*)w, (const elem_t*)b,
+                                                                        (elem_t*)y, mean, rstd, dim, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 
@@ -966,26 +982,26 @@ int fbam_layernorm_bwd(const void* dy, const void* x, const void* w, const float
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const unsigned grid = (unsigned)(rows < 4ll * sms ? rows : 4ll * sms);
-  const bf16 *dyp = (const bf16*)dy, *xp = (const bf16*)x, *wp = (const bf16*)w;
+  const elem_t *dyp = (const elem_t*)dy, *xp = (const elem_t*)x, *wp = (const elem_t*)w;
   cudaStream_t s = STREAM(stream);
-  if (dim <= 1024) layernorm_bwd_kernel<4><<<grid, 256, 0, s>>>(dyp, xp, wp, mean, rstd, (bf16*)dx, dw, db, rows, dim);
-  else if (dim <= 2048) layernorm_bwd_kernel<8><<<grid, 256, 0, s>>>(dyp, xp, wp, mean, rstd, (bf16*)dx, dw, db, rows, dim);
-  else if (dim <= 4096) layernorm_bwd_kernel<16><<<grid, 256, 0, s>>>(dyp, xp, wp, mean, rstd, (bf16*)dx, dw, db, rows, dim);
-  else layernorm_bwd_kernel<32><<<grid, 256, 0, s>>>(dyp, xp, wp, mean, rstd, (bf16*)dx, dw, db, rows, dim);
+  if (dim <= 1024) layernorm_bwd_kernel<4><<<grid, 256, 0, s>>>(dyp, xp, wp, mean, rstd, (elem_t*)dx, dw, db, rows, dim);
+  else if (dim <= 2048) layernorm_bwd_kernel<8><<<grid, 256, 0, s>>>(dyp, xp, wp, mean, rstd, (elem_t*)dx, dw, db, rows, dim);
+  else if (dim <= 4096) layernorm_bwd_kernel<16><<<grid, 256, 0, s>>>(dyp, xp, wp, mean, rstd, (elem_t*)dx, dw, db, rows, dim);
+  else layernorm_bwd_kernel<32><<<grid, 256, 0, s>>>(dyp, xp, wp, mean, rstd, (elem_t*)dx, dw, db, rows, dim);
   return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
 
 int fbam_layernorm_fwd(const void* x, const void* w, const void* b, void* y, long long rows, int dim, float eps,
                        void* stream) {
-  layernorm_fwd_kernel<<<(unsigned)rows, 256, 0, STREAM(stream)>>>((const bf16*)x, (const bf16*)w, (const bf16*)b,
-                                                                   (bf16*)y, dim, eps);
+  layernorm_fwd_kernel<<<(unsigned)rows, 256, 0, STREAM(stream)>>>((const elem_t*)x, (const elem_t*)w, (const elem_t*)b,
+                                                                   (elem_t*)y, dim, eps);
   return CHECK_LAUNCH();
 }
 
 int fbam_gelu(const void* x, const void* dy, void* out, long long n, int mode, void* stream) {
   if (n % 8 != 0) return 1;
   const long long n8 = n / 8;
-  gelu_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16*)x, (const bf16*)dy, (bf16*)out,
+  gelu_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, STREAM(stream)>>>((const elem_t*)x, (const elem_t*)dy, (elem_t*)out,
                                                                         n8, mode);
   return CHECK_LAUNCH();
 }
@@ -993,16 +1009,16 @@ int fbam_gelu(const void* x, const void* dy, void* out, long long n, int mode, v
 int fbam_geglu(const void* x, const void* dy, void* out, long long rows, int c, int bwd, void* stream) {
   if (c % 8 != 0) return 1;
   const long long n = rows * (c / 8);
-  if (!bwd) geglu_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16*)x, (bf16*)out, rows, c);
-  else geglu_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16*)x, (const bf16*)dy,
-                                                                                (bf16*)out, rows, c);
+  if (!bwd) geglu_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, STREAM(stream)>>>((const elem_t*)x, (elem_t*)out, rows, c);
+  else geglu_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, STREAM(stream)>>>((const elem_t*)x, (const elem_t*)dy,
+                                                                                (elem_t*)out, rows, c);
   return CHECK_LAUNCH();
 }
 
 int fbam_avgpool2x2(const void* in, void* out, long long n, int oh, int ow, int c, int bwd, void* stream) {
   if (c % 8 != 0) return 1;
   const long long total = n * oh * ow * (c / 8);
-  avgpool2x2_kernel<<<(unsigned)((total + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16*)in, (bf16*)out, n, oh, ow,
+  avgpool2x2_kernel<<<(unsigned)((total + 255) / 256), 256, 0, STREAM(stream)>>>((const elem_t*)in, (elem_t*)out, n, oh, ow,
                                                                                  c, bwd);
   return CHECK_LAUNCH();
 }
@@ -1012,11 +1028,17 @@ int fbam_global_avgpool(const void* in, void* out, long long n, int pix, int c, 
   if (c % 8 != 0) return 1;
   if (!bwd) {
     dim3 grid((unsigned)n, (c / 8 + 31) / 32);
-    global_avgpool_fwd_kernel<<<grid, 256, 0, STREAM(stream)>>>((const bf16*)in, (bf16*)out, pix, c);
+    global_avgpool_fwd_kernel<<<grid, 256, 0, STREAM(stream)>>>((const elem_t*)in, (elem_t*)out, pix, c);
   } else {
     const long long total = n * pix * (c / 8);
-    global_avgpool_bwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, STREAM(stream)>>>(
-        (const bf16*)in, (const bf16*)gelu_z, (bf16*)out, n, pix, c);
+    const long long want = (total + 256 * 4 - 1) / (256 * 4);
+    const unsigned blocks = (unsigned)(want < 148 * 8 ? (want > 0 ? want : 1) : 148 * 8);
+    if (total + 4LL * blocks * 256 < (1LL << 32))
+      global_avgpool_bwd_kernel<unsigned><<<blocks, 256, 0, STREAM(stream)>>>(
+          (const elem_t*)in, (const elem_t*)gelu_z, (elem_t*)out, (unsigned)total, (unsigned)pix, (unsigned)(c / 8));
+    else
+      global_avgpool_bwd_kernel<long long><<<blocks, 256, 0, STREAM(stream)>>>(
+          (const elem_t*)in, (const elem_t*)gelu_z, (elem_t*)out, total, (long long)pix, (long long)(c / 8));
   }
   return CHECK_LAUNCH();
 }
@@ -1031,7 +1053,7 @@ int fbam_colsum(const void* x, float* out, long long rows, int cols, void* strea
   long long rpb = (rows + want_gy - 1) / want_gy;
   rpb = rpb < 32 ? 32 : (rpb > 256 ? 256 : rpb);
   dim3 grid(gx, (unsigned)((rows + rpb - 1) / rpb));
-  colsum_kernel<<<grid, threads, 0, STREAM(stream)>>>((const bf16*)x, out, rows, cols, (int)rpb);
+  colsum_kernel<<<grid, threads, 0, STREAM(stream)>>>((const elem_t*)x, out, rows, cols, (int)rpb);
   return CHECK_LAUNCH();
 }
 
@@ -1055,13 +1077,13 @@ int fbam_cell_embed_fwd(const int* cells, const float* cp_embed, const float* po
     const int big = (512 / e8 > 0 ? 512 / e8 : 1) * e8;   // one 512-thread block per SM next to the 136 KB table
     const int ppb2 = big / e8;
     dim3 grid((positions + ppb2 - 1) / ppb2, (unsigned)((frames + fpb - 1) / fpb));
-    cell_embed_fwd_kernel<true><<<grid, big, table, STREAM(stream)>>>(cells, cp_embed, pos_embed, colour, (bf16*)out,
+    cell_embed_fwd_kernel<true><<<grid, big, table, STREAM(stream)>>>(cells, cp_embed, pos_embed, colour, (elem_t*)out,
                                                                       frames, positions, e, vocab, fpb);
     return CHECK_LAUNCH();
   }
   const int fpb = 64;
   dim3 grid((positions + ppb - 1) / ppb, (unsigned)((frames + fpb - 1) / fpb));
-  cell_embed_fwd_kernel<false><<<grid, threads, 0, STREAM(stream)>>>(cells, cp_embed, pos_embed, colour, (bf16*)out,
+  cell_embed_fwd_kernel<false><<<grid, threads, 0, STREAM(stream)>>>(cells, cp_embed, pos_embed, colour, (elem_t*)out,
                                                                      frames, positions, e, vocab, fpb);
   return CHECK_LAUNCH();
 }
@@ -1073,35 +1095,35 @@ int fbam_cell_embed_bwd(const int* cells, const void* dout, float* d_cp, float* 
   const int fpb = 256;
   dim3 grid((positions + ppb - 1) / ppb, (unsigned)((frames + fpb - 1) / fpb));
   cell_embed_bwd_kernel<<<grid, threads, 6 * e * sizeof(float), STREAM(stream)>>>(
-      cells, (const bf16*)dout, d_cp, d_pos, d_colour, frames, positions, e, vocab, fpb);
+      cells, (const elem_t*)dout, d_cp, d_pos, d_colour, frames, positions, e, vocab, fpb);
   return CHECK_LAUNCH();
 }
 
 int fbam_ce_fwd_bwd(void* logits, const long long* targets, float* loss_sum, long long rows, int vocab, int ld,
                     float scale, int write_grad, void* stream) {
-  ce_fwd_bwd_kernel<<<(unsigned)rows, 256, 0, STREAM(stream)>>>((bf16*)logits, targets, loss_sum, vocab, ld, scale,
+  ce_fwd_bwd_kernel<<<(unsigned)rows, 256, 0, STREAM(stream)>>>((elem_t*)logits, targets, loss_sum, vocab, ld, scale,
                                                                 write_grad);
   return CHECK_LAUNCH();
 }
 
 int fbam_ce_fwd_bwd_f32(const float* logits, void* dlogits, const long long* targets, float* loss_sum, long long rows,
                         int vocab, int ld, float scale, void* stream) {
-  ce_fwd_bwd_f32_kernel<<<(unsigned)rows, 256, 0, STREAM(stream)>>>(logits, (bf16*)dlogits, targets, loss_sum, vocab, ld,
+  ce_fwd_bwd_f32_kernel<<<(unsigned)rows, 256, 0, STREAM(stream)>>>(logits, (elem_t*)dlogits, targets, loss_sum, vocab, ld,
                                                                     scale);
   return CHECK_LAUNCH();
 }
 
-int fbam_adamw(void* param, const void* grad, float* m, float* v, float* master, long long n, int param_bf16,
+int fbam_adamw(void* param, const void* grad, float* m, float* v, float* master, long long n, int param_elem,
                float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
                void* stream) {
   if (n <= 0) return 0;
   const unsigned blocks = (unsigned)((n + 1023) / 1024);
-  const uintptr_t pa = param_bf16 ? 7 : 15;
+  const uintptr_t pa = param_elem ? 7 : 15;
   const int vec_ok = !((reinterpret_cast<uintptr_t>(param) & pa) || (reinterpret_cast<uintptr_t>(grad) & pa) ||
                        (reinterpret_cast<uintptr_t>(m) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
                        (reinterpret_cast<uintptr_t>(master) & 15));
-  if (param_bf16)
-    adamw_kernel<bf16><<<blocks, 256, 0, STREAM(stream)>>>((bf16*)param, (const bf16*)grad, m, v, master, n, lr, b1, b2,
+  if (param_elem)
+    adamw_kernel<elem_t><<<blocks, 256, 0, STREAM(stream)>>>((elem_t*)param, (const elem_t*)grad, m, v, master, n, lr, b1, b2,
                                                            eps, wd, 1.0f / bc1, 1.0f / bc2, grad_scale, vec_ok);
   else
     adamw_kernel<float><<<blocks, 256, 0, STREAM(stream)>>>((float*)param, (const float*)grad, m, v, master, n, lr, b1,
@@ -1110,12 +1132,12 @@ int fbam_adamw(void* param, const void* grad, float* m, float* v, float* master,
 }
 
 // velocity may be null (no momentum); master may be null (fp32 parameters).
-int fbam_sgd(void* param, const void* grad, float* velocity, float* master, long long n, int param_bf16, float lr,
+int fbam_sgd(void* param, const void* grad, float* velocity, float* master, long long n, int param_elem, float lr,
              float momentum, int nesterov, float wd, void* stream) {
   if (n <= 0) return 0;
   const unsigned blocks = (unsigned)((n + 255) / 256);
-  if (param_bf16)
-    sgd_kernel<bf16><<<blocks, 256, 0, STREAM(stream)>>>((bf16*)param, (const bf16*)grad, velocity, master, n, lr,
+  if (param_elem)
+    sgd_kernel<elem_t><<<blocks, 256, 0, STREAM(stream)>>>((elem_t*)param, (const elem_t*)grad, velocity, master, n, lr,
                                                         momentum, nesterov, wd);
   else
     sgd_kernel<float><<<blocks, 256, 0, STREAM(stream)>>>((float*)param, (const float*)grad, velocity, master, n, lr,

@@ -25,13 +25,12 @@
 // around them); gate order i, f, g, o, fp32 gates and cell state as there (tanh is tanhf here; the reference
 // writes it as 2·sigmoid(2x) - 1, the same function).
 #include <cooperative_groups.h>
-#include <cuda_bf16.h>
+#include "elem16.cuh"
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace {
 
-typedef __nv_bfloat16 bf16;
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr unsigned kBarrierSpinLimit = 1u << 22;
@@ -62,7 +61,7 @@ __device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target,
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      "mma.sync.aligned.m16n8k16.row.col.f32." ELEM_PTX "." ELEM_PTX ".f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
@@ -74,13 +73,13 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __ex
 // -------------------------------------------------------------------------------------------------
 template <int MAXKS>  // k-steps (of 16) per warp: H <= MAXKS * 8 * 16
 __global__ void __launch_bounds__(kThreads, 1)
-lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const float* __restrict__ h0,
-                const float* __restrict__ c0, bf16* __restrict__ y, float* __restrict__ c_all, bf16* hbuf,
+lstm_fwd_kernel(float* __restrict__ gates, const elem_t* __restrict__ whh, const float* __restrict__ h0,
+                const float* __restrict__ c0, elem_t* __restrict__ y, float* __restrict__ c_all, elem_t* hbuf,
                 unsigned* counter, int* status, int T, int B, int H, int per_sample) {
   __shared__ float part[kWarps][2][16][8];
   __shared__ float pre[32][8];
   extern __shared__ uint4 dyn_smem[];
-  bf16* hs = reinterpret_cast<bf16*>(dyn_smem);  // [8][H + 8]: h_{t-1}, rows padded by 16 B against bank conflicts
+  elem_t* hs = reinterpret_cast<elem_t*>(dyn_smem);  // [8][H + 8]: h_{t-1}, rows padded by 16 B against bank conflicts
   const int hs_ld = H + 8;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
@@ -96,8 +95,8 @@ lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const f
       const int ks = warp + kWarps * j;
       const bool on = ks < nks;
       const int k = ks * 16 + q * 2;
-      const bf16* r_lo = whh + ((long long)(tile * 2) * H + unit0 + g) * H;      // row g   of the tile
-      const bf16* r_hi = whh + ((long long)(tile * 2 + 1) * H + unit0 + g) * H;  // row g+8 of the tile
+      const elem_t* r_lo = whh + ((long long)(tile * 2) * H + unit0 + g) * H;      // row g   of the tile
+      const elem_t* r_hi = whh + ((long long)(tile * 2 + 1) * H + unit0 + g) * H;  // row g+8 of the tile
       afrag[tile][j][0] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k) : 0u;
       afrag[tile][j][1] = on ? *reinterpret_cast<const uint32_t*>(r_hi + k) : 0u;
       afrag[tile][j][2] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k + 8) : 0u;
@@ -112,7 +111,7 @@ lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const f
     // from the previous chunk of the same sequences
     const long long si = per_sample ? (long long)min(b, B - 1) * H + unit0 + u : unit0 + u;
     c = c0[si];
-    hbuf[(long long)b * H + unit0 + u] = __float2bfloat16(h0[si]);
+    hbuf[(long long)b * H + unit0 + u] = f2e(h0[si]);
   }
   // Each of the 256 threads owns one (gate row, batch) entry of the pre-activations; the value for the next
   // step is fetched from HBM before the grid barrier so that its latency is hidden behind the wait.
@@ -126,8 +125,8 @@ lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const f
 
   for (int t = 0; t < T; ++t) {
     const float xg = xg_next;
-    const bf16* hprev = hbuf + (long long)(t & 1) * 8 * H;
-    bf16* hnext = hbuf + (long long)((t + 1) & 1) * 8 * H;
+    const elem_t* hprev = hbuf + (long long)(t & 1) * 8 * H;
+    elem_t* hnext = hbuf + (long long)((t + 1) & 1) * 8 * H;
     // h_{t-1} (8 x H bf16) -> shared memory with independent 16-byte loads (one L2 round trip in flight
     // for all of them), then the B fragments come from shared memory.
     for (int c = threadIdx.x; c < H; c += kThreads) {  // 8*H/8 packets of 8 elements
@@ -141,7 +140,7 @@ lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const f
     for (int j = 0; j < MAXKS; ++j) {
       const int ks = warp + kWarps * j;
       if (ks < nks) {
-        const bf16* hp = hs + g * hs_ld + ks * 16 + q * 2;  // B fragment: n = g (batch), k pairs
+        const elem_t* hp = hs + g * hs_ld + ks * 16 + q * 2;  // B fragment: n = g (batch), k pairs
         const uint32_t b0 = *reinterpret_cast<const uint32_t*>(hp);
         const uint32_t b1 = *reinterpret_cast<const uint32_t*>(hp + 8);
         mma_16816(acc[0][j & 1], afrag[0][j], b0, b1);
@@ -170,7 +169,7 @@ lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const f
       const float gg = tanhf(pre[16 + u][b]), og = sigmoid_f(pre[24 + u][b]);
       c = fg * c + ig * gg;
       const float h = og * tanhf(c);
-      const bf16 hb = __float2bfloat16(h);
+      const elem_t hb = f2e(h);
       if (b < B) {
         float* gt = gates + ((long long)t * B + b) * 4 * H + unit0 + u;
         gt[0] = ig; gt[H] = fg; gt[2 * (long long)H] = gg; gt[3 * (long long)H] = og;
@@ -178,7 +177,7 @@ lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const f
         c_all[((long long)t * B + b) * H + unit0 + u] = c;
         hnext[(long long)b * H + unit0 + u] = hb;
       } else {
-        hnext[(long long)b * H + unit0 + u] = __float2bfloat16(0.0f);
+        hnext[(long long)b * H + unit0 + u] = f2e(0.0f);
       }
     }
     // prefetch: the same thread wrote this location's activated gate for step t above only if it is one of
@@ -194,12 +193,12 @@ lstm_fwd_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const f
 template <int MAXKS>  // k-steps per warp: 4H <= MAXKS * 8 * 16
 __global__ void __launch_bounds__(kThreads, 1)
 lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all, const float* __restrict__ c0,
-                const bf16* __restrict__ dy, const bf16* __restrict__ whh_t, bf16* dgates, float* __restrict__ dh0,
+                const elem_t* __restrict__ dy, const elem_t* __restrict__ whh_t, elem_t* dgates, float* __restrict__ dh0,
                 float* __restrict__ dc0, const float* __restrict__ dh_last, const float* __restrict__ dc_last,
                 unsigned* counter, int* status, int T, int B, int H, int per_sample) {
   __shared__ float part[kWarps][16][8];
   extern __shared__ uint4 dyn_smem[];
-  bf16* ds = reinterpret_cast<bf16*>(dyn_smem);  // [8][4H + 8]: dGates[t], padded rows
+  elem_t* ds = reinterpret_cast<elem_t*>(dyn_smem);  // [8][4H + 8]: dGates[t], padded rows
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
   const int unit0 = blockIdx.x * 16;
@@ -213,8 +212,8 @@ lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all
     const int ks = warp + kWarps * j;
     const bool on = ks < nks;
     const int k = ks * 16 + q * 2;
-    const bf16* r_lo = whh_t + (long long)(unit0 + g) * K;
-    const bf16* r_hi = whh_t + (long long)(unit0 + g + 8) * K;
+    const elem_t* r_lo = whh_t + (long long)(unit0 + g) * K;
+    const elem_t* r_hi = whh_t + (long long)(unit0 + g + 8) * K;
     afrag[j][0] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k) : 0u;
     afrag[j][1] = on ? *reinterpret_cast<const uint32_t*>(r_hi + k) : 0u;
     afrag[j][2] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k + 8) : 0u;
@@ -238,7 +237,7 @@ lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all
     n_ig = gt[0]; n_fg = gt[H]; n_gg = gt[2 * (long long)H]; n_og = gt[3 * (long long)H];
     n_ct = c_all[((long long)t * B + b) * H + unit];
     n_cp = t > 0 ? c_all[((long long)(t - 1) * B + b) * H + unit] : c0[per_sample ? (long long)b * H + unit : unit];
-    n_dy = __bfloat162float(dy[((long long)t * B + b) * H + unit]);
+    n_dy = e2f(dy[((long long)t * B + b) * H + unit]);
   }
 
   for (int t = T - 1; t >= 0; --t) {
@@ -252,11 +251,11 @@ lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all
       const float d_f = dc * cp * fg * (1.0f - fg);
       const float d_g = dc * ig * (1.0f - gg * gg);
       dc_next = dc * fg;
-      bf16* dg = dgates + ((long long)t * B + b) * K + unit;
-      dg[0] = __float2bfloat16(d_i);
-      dg[H] = __float2bfloat16(d_f);
-      dg[2 * (long long)H] = __float2bfloat16(d_g);
-      dg[3 * (long long)H] = __float2bfloat16(d_o);
+      elem_t* dg = dgates + ((long long)t * B + b) * K + unit;
+      dg[0] = f2e(d_i);
+      dg[H] = f2e(d_f);
+      dg[2 * (long long)H] = f2e(d_g);
+      dg[3 * (long long)H] = f2e(d_o);
       if (t > 0) {
         const int tn = t - 1;
         const float* gt = gates + ((long long)tn * B + b) * K + unit;
@@ -264,12 +263,12 @@ lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all
         n_ct = cp;
         n_cp = tn > 0 ? c_all[((long long)(tn - 1) * B + b) * H + unit]
                       : c0[per_sample ? (long long)b * H + unit : unit];
-        n_dy = __bfloat162float(dy[((long long)tn * B + b) * H + unit]);
+        n_dy = e2f(dy[((long long)tn * B + b) * H + unit]);
       }
     }
     if (!grid_barrier(counter, ++bar * gridDim.x, status)) return;
     // dh_{t-1}[b, unit] = sum_k dGates[t][b, k] * W_hh[k, unit]
-    const bf16* dgt = dgates + (long long)t * B * K;
+    const elem_t* dgt = dgates + (long long)t * B * K;
     for (int c = threadIdx.x; c < B * (K / 8); c += kThreads) {
       const int row = c / (K / 8), col = (c % (K / 8)) * 8;
       *reinterpret_cast<uint4*>(ds + row * ds_ld + col) =
@@ -281,7 +280,7 @@ lstm_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_all
     for (int j = 0; j < MAXKS; ++j) {
       const int ks = warp + kWarps * j;
       if (ks < nks) {
-        const bf16* p = ds + g * ds_ld + ks * 16 + q * 2;
+        const elem_t* p = ds + g * ds_ld + ks * 16 + q * 2;
         mma_16816(acc[j & 1], afrag[j], *reinterpret_cast<const uint32_t*>(p),
                   *reinterpret_cast<const uint32_t*>(p + 8));
       }
@@ -316,12 +315,12 @@ constexpr int kBigThreads = kBigWarps * 32;
 
 template <int RKS, int SKS>  // H <= (RKS + SKS) * 16 warps * 16
 __global__ void __launch_bounds__(kBigThreads, 1)
-lstm_fwd_big_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, const float* __restrict__ h0,
-                    const float* __restrict__ c0, bf16* __restrict__ y, float* __restrict__ c_all, bf16* hbuf,
+lstm_fwd_big_kernel(float* __restrict__ gates, const elem_t* __restrict__ whh, const float* __restrict__ h0,
+                    const float* __restrict__ c0, elem_t* __restrict__ y, float* __restrict__ c_all, elem_t* hbuf,
                     unsigned* counter, int* status, int T, int B, int H, int per_sample) {
   extern __shared__ uint4 dyn_smem[];
   uint4* wsm = dyn_smem;                                                  // [SKS * 4][512] A fragments
-  bf16* hs = reinterpret_cast<bf16*>(dyn_smem + SKS * 4 * kBigThreads);   // [8][H + 8]
+  elem_t* hs = reinterpret_cast<elem_t*>(dyn_smem + SKS * 4 * kBigThreads);   // [8][H + 8]
   const int hs_ld = H + 8;
   float* part = reinterpret_cast<float*>(hs + 8 * hs_ld);                 // [16 warps][4 tiles][16][8]
   float* pre = part + kBigWarps * 4 * 128;                                // [64][8]
@@ -334,8 +333,8 @@ lstm_fwd_big_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, con
     const bool on = ks < nks;
     const int k = ks * 16 + q * 2;
     const int unit = unit0 + (tile >> 1) * 8 + g;
-    const bf16* r_lo = whh + ((long long)((tile & 1) * 2) * H + unit) * H;
-    const bf16* r_hi = whh + ((long long)((tile & 1) * 2 + 1) * H + unit) * H;
+    const elem_t* r_lo = whh + ((long long)((tile & 1) * 2) * H + unit) * H;
+    const elem_t* r_hi = whh + ((long long)((tile & 1) * 2 + 1) * H + unit) * H;
     a[0] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k) : 0u;
     a[1] = on ? *reinterpret_cast<const uint32_t*>(r_hi + k) : 0u;
     a[2] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k + 8) : 0u;
@@ -360,7 +359,7 @@ lstm_fwd_big_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, con
   if (threadIdx.x < 128) {
     const long long si = per_sample ? (long long)min(b, B - 1) * H + unit0 + u : unit0 + u;
     c = c0[si];
-    hbuf[(long long)b * H + unit0 + u] = __float2bfloat16(h0[si]);
+    hbuf[(long long)b * H + unit0 + u] = f2e(h0[si]);
   }
   // every thread owns one (gate row of 64, batch) pre-activation, fetched one step ahead of its use
   const int prow = threadIdx.x >> 3, pbb = threadIdx.x & 7;
@@ -373,8 +372,8 @@ lstm_fwd_big_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, con
 
   for (int t = 0; t < T; ++t) {
     const float xg = xg_next;
-    const bf16* hprev = hbuf + (long long)(t & 1) * 8 * H;
-    bf16* hnext = hbuf + (long long)((t + 1) & 1) * 8 * H;
+    const elem_t* hprev = hbuf + (long long)(t & 1) * 8 * H;
+    elem_t* hnext = hbuf + (long long)((t + 1) & 1) * 8 * H;
     for (int cc = threadIdx.x; cc < H; cc += kBigThreads) {
       const int row = cc / (H / 8), col = (cc % (H / 8)) * 8;
       *reinterpret_cast<uint4*>(hs + row * hs_ld + col) =
@@ -390,7 +389,7 @@ lstm_fwd_big_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, con
     for (int j = 0; j < RKS + SKS; ++j) {
       const int ks = warp + kBigWarps * j;
       if (ks < nks) {
-        const bf16* hp = hs + g * hs_ld + ks * 16 + q * 2;
+        const elem_t* hp = hs + g * hs_ld + ks * 16 + q * 2;
         const uint32_t b0 = *reinterpret_cast<const uint32_t*>(hp);
         const uint32_t b1 = *reinterpret_cast<const uint32_t*>(hp + 8);
 #pragma unroll
@@ -427,7 +426,7 @@ lstm_fwd_big_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, con
       const float gg = tanhf(pre[(base + 16) * 8 + b]), og = sigmoid_f(pre[(base + 24) * 8 + b]);
       c = fg * c + ig * gg;
       const float h = og * tanhf(c);
-      const bf16 hb = __float2bfloat16(h);
+      const elem_t hb = f2e(h);
       if (b < B) {
         float* gt = gates + ((long long)t * B + b) * 4 * H + unit0 + u;
         gt[0] = ig; gt[H] = fg; gt[2 * (long long)H] = gg; gt[3 * (long long)H] = og;
@@ -435,7 +434,7 @@ lstm_fwd_big_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, con
         c_all[((long long)t * B + b) * H + unit0 + u] = c;
         hnext[(long long)b * H + unit0 + u] = hb;
       } else {
-        hnext[(long long)b * H + unit0 + u] = __float2bfloat16(0.0f);
+        hnext[(long long)b * H + unit0 + u] = f2e(0.0f);
       }
     }
     if (pbb < B && t + 1 < T) xg_next = gates[((long long)(t + 1) * B + pbb) * 4 * H + pre_off];
@@ -449,13 +448,13 @@ lstm_fwd_big_kernel(float* __restrict__ gates, const bf16* __restrict__ whh, con
 template <int HKS>  // k-steps per warp and half: 4H <= 2 * HKS * 16 warps * 16
 __global__ void __launch_bounds__(kBigThreads, 1)
 lstm_bwd_big_kernel(const float* __restrict__ gates, const float* __restrict__ c_all, const float* __restrict__ c0,
-                    const bf16* __restrict__ dy, const bf16* __restrict__ whh_t, bf16* dgates,
+                    const elem_t* __restrict__ dy, const elem_t* __restrict__ whh_t, elem_t* dgates,
                     float* __restrict__ dh0, float* __restrict__ dc0, const float* __restrict__ dh_last,
                     const float* __restrict__ dc_last, unsigned* counter, int* status, int T, int B, int H,
                     int per_sample) {
   extern __shared__ uint4 dyn_smem[];
   uint4* wsm = dyn_smem;                                              // [HKS][512] A fragments (second half of K)
-  bf16* ds = reinterpret_cast<bf16*>(dyn_smem + HKS * kBigThreads);   // [8][K/2 + 8]: half of dGates[t]
+  elem_t* ds = reinterpret_cast<elem_t*>(dyn_smem + HKS * kBigThreads);   // [8][K/2 + 8]: half of dGates[t]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
   const int unit0 = blockIdx.x * 16;
@@ -467,8 +466,8 @@ lstm_bwd_big_kernel(const float* __restrict__ gates, const float* __restrict__ c
 
   auto load_frag = [&](int ks, bool on, uint32_t (&a)[4]) {
     const int k = ks * 16 + q * 2;
-    const bf16* r_lo = whh_t + (long long)(unit0 + g) * K;
-    const bf16* r_hi = whh_t + (long long)(unit0 + g + 8) * K;
+    const elem_t* r_lo = whh_t + (long long)(unit0 + g) * K;
+    const elem_t* r_hi = whh_t + (long long)(unit0 + g + 8) * K;
     a[0] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k) : 0u;
     a[1] = on ? *reinterpret_cast<const uint32_t*>(r_hi + k) : 0u;
     a[2] = on ? *reinterpret_cast<const uint32_t*>(r_lo + k + 8) : 0u;
@@ -500,7 +499,7 @@ lstm_bwd_big_kernel(const float* __restrict__ gates, const float* __restrict__ c
     n_ig = gt[0]; n_fg = gt[H]; n_gg = gt[2 * (long long)H]; n_og = gt[3 * (long long)H];
     n_ct = c_all[((long long)t * B + b) * H + unit];
     n_cp = t > 0 ? c_all[((long long)(t - 1) * B + b) * H + unit] : c0[per_sample ? (long long)b * H + unit : unit];
-    n_dy = __bfloat162float(dy[((long long)t * B + b) * H + unit]);
+    n_dy = e2f(dy[((long long)t * B + b) * H + unit]);
   }
 
   for (int t = T - 1; t >= 0; --t) {
@@ -514,11 +513,11 @@ lstm_bwd_big_kernel(const float* __restrict__ gates, const float* __restrict__ c
       const float d_f = dc * cp * fg * (1.0f - fg);
       const float d_g = dc * ig * (1.0f - gg * gg);
       dc_next = dc * fg;
-      bf16* dg = dgates + ((long long)t * B + b) * K + unit;
-      dg[0] = __float2bfloat16(d_i);
-      dg[H] = __float2bfloat16(d_f);
-      dg[2 * (long long)H] = __float2bfloat16(d_g);
-      dg[3 * (long long)H] = __float2bfloat16(d_o);
+      elem_t* dg = dgates + ((long long)t * B + b) * K + unit;
+      dg[0] = f2e(d_i);
+      dg[H] = f2e(d_f);
+      dg[2 * (long long)H] = f2e(d_g);
+      dg[3 * (long long)H] = f2e(d_o);
       if (t > 0) {
         const int tn = t - 1;
         const float* gt = gates + ((long long)tn * B + b) * K + unit;
@@ -526,11 +525,11 @@ lstm_bwd_big_kernel(const float* __restrict__ gates, const float* __restrict__ c
         n_ct = cp;
         n_cp = tn > 0 ? c_all[((long long)(tn - 1) * B + b) * H + unit]
                       : c0[per_sample ? (long long)b * H + unit : unit];
-        n_dy = __bfloat162float(dy[((long long)tn * B + b) * H + unit]);
+        n_dy = e2f(dy[((long long)tn * B + b) * H + unit]);
       }
     }
     if (!grid_barrier(counter, ++bar * gridDim.x, status)) return;
-    const bf16* dgt = dgates + (long long)t * B * K;
+    const elem_t* dgt = dgates + (long long)t * B * K;
     float acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -545,7 +544,7 @@ lstm_bwd_big_kernel(const float* __restrict__ gates, const float* __restrict__ c
       for (int j = 0; j < HKS; ++j) {
         const int ks = warp + kBigWarps * j;
         if (ks < kh) {
-          const bf16* p = ds + g * ds_ld + ks * 16 + q * 2;
+          const elem_t* p = ds + g * ds_ld + ks * 16 + q * 2;
           const uint32_t b0 = *reinterpret_cast<const uint32_t*>(p), b1 = *reinterpret_cast<const uint32_t*>(p + 8);
           if (half == 0) {
             mma_16816(acc[j & 1], afrag[j], b0, b1);
@@ -608,12 +607,12 @@ int fbam_lstm_fwd_ex(float* gates, const void* whh, const float* h0, const float
   if (cudaMemsetAsync(counter, 0, sizeof(unsigned), s) != cudaSuccess) return 5;
   void* args[] = {&gates, &whh, &h0, &c0, &y, &c_all, &hbuf, &counter, &status, &T, &B, &H, &per_sample};
   if (H > 1024) {  // 16 units per CTA; half of each warp's 8 k-steps in registers, half in shared memory
-    const size_t big = (size_t)4 * 4 * kBigThreads * 16 + (size_t)8 * (H + 8) * sizeof(bf16) +
+    const size_t big = (size_t)4 * 4 * kBigThreads * 16 + (size_t)8 * (H + 8) * sizeof(elem_t) +
                        (size_t)(kBigWarps * 4 * 128 + 64 * 8) * sizeof(float);
     return coop_launch(lstm_fwd_big_kernel<4, 4>, H / 16, args, big, s, kBigThreads);
   }
   const int grid = H / 8;
-  const size_t smem = (size_t)8 * (H + 8) * sizeof(bf16);
+  const size_t smem = (size_t)8 * (H + 8) * sizeof(elem_t);
   if (H <= 256) return coop_launch(lstm_fwd_kernel<2>, grid, args, smem, s);
   if (H <= 512) return coop_launch(lstm_fwd_kernel<4>, grid, args, smem, s);
   return coop_launch(lstm_fwd_kernel<8>, grid, args, smem, s);
@@ -635,12 +634,12 @@ int fbam_lstm_bwd_ex(const float* gates, const float* c_all, const float* c0, co
   void* args[] = {&gates, &c_all, &c0, &dy, &whh_t, &dgates, &dh0, &dc0, &dh_last, &dc_last, &counter, &status,
                   &T, &B, &H, &per_sample};
   if (H > 1024) {
-    const size_t big = (size_t)16 * kBigThreads * 16 + (size_t)8 * (2 * H + 8) * sizeof(bf16) +
+    const size_t big = (size_t)16 * kBigThreads * 16 + (size_t)8 * (2 * H + 8) * sizeof(elem_t) +
                        (size_t)kBigWarps * 128 * sizeof(float);
     return coop_launch(lstm_bwd_big_kernel<16>, H / 16, args, big, s, kBigThreads);
   }
   const int grid = H / 16;
-  const size_t smem = (size_t)8 * (4 * H + 8) * sizeof(bf16);
+  const size_t smem = (size_t)8 * (4 * H + 8) * sizeof(elem_t);
   if (H <= 256) return coop_launch(lstm_bwd_kernel<8>, grid, args, smem, s);
   if (H <= 512) return coop_launch(lstm_bwd_kernel<16>, grid, args, smem, s);
   return coop_launch(lstm_bwd_kernel<32>, grid, args, smem, s);
@@ -720,7 +719,7 @@ int fbam_lstm_fwd_noalloc(float* gates, const void* whh, const float* h0, const 
   int per_sample = 0;
   void* args[] = {&gates, &whh, &h0, &c0, &y, &c_all, &hbuf, &counter, &status, &T, &B, &H, &per_sample};
   const int grid = H / 8;
-  const size_t smem = (size_t)8 * (H + 8) * sizeof(bf16);
+  const size_t smem = (size_t)8 * (H + 8) * sizeof(elem_t);
   if (H <= 256) return coop_launch(lstm_fwd_kernel<2>, grid, args, smem, s);
   if (H <= 512) return coop_launch(lstm_fwd_kernel<4>, grid, args, smem, s);
   return coop_launch(lstm_fwd_kernel<8>, grid, args, smem, s);

@@ -7,7 +7,7 @@
 #pragma once
 
 #include <cuda.h>
-#include <cuda_bf16.h>
+#include "elem16.cuh"
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -152,11 +152,11 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 // ---------------------------------------------------------------------------------------------
 // descriptors
 // ---------------------------------------------------------------------------------------------
-// Instruction descriptor for kind::f16 with bf16 operands and fp32 accumulation.
-//   bits 4-5 D format (1 = f32) | 7-9 A format (1 = bf16) | 10-12 B format | 15 A is MN-major | 16 B is MN-major
+// Instruction descriptor for kind::f16 with operands of the element type (bf16 or half) and fp32 accumulation.
+//   bits 4-5 D format (1 = f32) | 7-9 A format (0 = f16, 1 = bf16) | 10-12 B format | 15 A is MN-major | 16 B is MN-major
 //   | 17-22 N>>3 | 24-28 M>>4
-__host__ __device__ constexpr uint32_t make_idesc_bf16(uint32_t m, uint32_t n, bool a_mn_major, bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) |
+__host__ __device__ constexpr uint32_t make_idesc_f16kind(uint32_t m, uint32_t n, bool a_mn_major, bool b_mn_major) {
+  return (1u << 4) | (ELEM_IDESC_FORMAT << 7) | (ELEM_IDESC_FORMAT << 10) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) |
          ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 

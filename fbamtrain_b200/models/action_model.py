@@ -57,11 +57,11 @@ class ActionModel(nn.Module):
     def forward(self, frame_embeddings: torch.Tensor, targets: torch.Tensor, loss_scale: float, state=None):
         """Returns ``loss_scale · Σ CE`` over all ``B·T`` positions."""
         if (self.streaming and state is None and frame_embeddings.is_cuda and ops.get_backend() == "auto"
-                and frame_embeddings.dtype == torch.bfloat16):
+                and frame_embeddings.dtype in (torch.bfloat16, torch.float16)):
             from ..ops.lstm import persistent_ok
             layer = self.lstm.layers[0]
             b, t, e = frame_embeddings.shape
-            if persistent_ok(b, layer.hidden) and e % 8 == 0 and frame_embeddings.dtype == torch.bfloat16:
+            if persistent_ok(b, layer.hidden) and e % 8 == 0:
                 from ..ops.streaming import streaming_lstm_head_ce
                 return streaming_lstm_head_ce(frame_embeddings.transpose(0, 1).contiguous(), layer.weights_ih,
                                               layer.weights_hh, layer.bias_ih, layer.bias_hh, layer.h0, layer.c0,

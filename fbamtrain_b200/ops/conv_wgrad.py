@@ -17,13 +17,15 @@ import torch
 from . import native as nv
 
 
-def wgrad_pass(x, dy, o: int, c: int, taps, stride: int, out_dtype=torch.bfloat16, splits: int = 0, bn: int = 0,
+def wgrad_pass(x, dy, o: int, c: int, taps, stride: int, out_dtype=None, splits: int = 0, bn: int = 0,
                bm: int = 0) -> torch.Tensor:
     """``dW[o, t, c] = Σ_pixels dY[pixel, o] · X[pixel·stride + taps[t], c]`` → ``(O, len(taps)·C)``.  ``taps`` are
     (dh, dw) offsets in input pixels; a single tap ``(0, 0)`` with stride 1 is the plain product ``dYᵀ · X`` over
     all pixels (used for reductions whose K is the number of pixels)."""
-    from .native_ops import _brick
+    from .native_ops import _brick, _need_elem
     from ..utils import debug, flops
+    elem = _need_elem(x, dy)
+    out_dtype = out_dtype or elem               # the operands' 16-bit type unless fp32 is asked for
     b, ih, iw, _ = x.shape
     _, oh, ow, _ = dy.shape
     nt = len(taps)
@@ -59,20 +61,20 @@ def wgrad_pass(x, dy, o: int, c: int, taps, stride: int, out_dtype=torch.bfloat1
     p.out_fp32 = 1
     p.splits, p.bn, p.bm = splits, bn, bm
     with debug.label(f"wgrad c{c} o{o} taps{nt}"):
-        code = nv.lib().fbam_conv_wgrad_bf16(nv.ptr(dy), o, nv.ptr(x), ih, iw, c, C.byref(p), nv.stream_ptr())
-    nv.check(code, "fbam_conv_wgrad_bf16")
+        code = nv.lib(dy).fbam_conv_wgrad(nv.ptr(dy), o, nv.ptr(x), ih, iw, c, C.byref(p), nv.stream_ptr())
+    nv.check(code, "fbam_conv_wgrad")
     flops.add(2.0 * b * oh * ow * o * nt * c)
     if splits == 1 and out_dtype == torch.float32:
         return work[0]
     out = torch.empty(o, nt * c, dtype=out_dtype, device=x.device)
-    if out_dtype not in (torch.float32, torch.bfloat16):
-        raise TypeError("weight gradients are written as fp32 or bf16")
-    nv.check(nv.lib().fbam_slab_reduce(nv.ptr(work), nv.ptr(out), C.c_longlong(o * nt * c), splits,
-                                       int(out_dtype == torch.bfloat16), nv.stream_ptr()), "fbam_slab_reduce")
+    if out_dtype not in (torch.float32, elem):
+        raise TypeError("weight gradients are written as fp32 or in the operands' 16-bit type")
+    nv.check(nv.lib(elem).fbam_slab_reduce(nv.ptr(work), nv.ptr(out), C.c_longlong(o * nt * c), splits,
+                                           int(out_dtype == elem), nv.stream_ptr()), "fbam_slab_reduce")
     return out
 
 
-def conv2d_wgrad(x, dy, w_shape, stride, padding, dilation, out_dtype=torch.bfloat16, splits: int = 0, bn: int = 0,
+def conv2d_wgrad(x, dy, w_shape, stride, padding, dilation, out_dtype=None, splits: int = 0, bn: int = 0,
                  bm: int = 0):
     o, _, _, c = w_shape
     if c % 64 != 0 or o % 8 != 0:

@@ -52,8 +52,9 @@ _warned_dtypes = set()
 
 
 def _native(t: torch.Tensor, dtype: Optional[torch.dtype] = None, family: Optional[str] = None) -> bool:
-    """The hand-written kernels compute in bf16 (fp32 accumulate).  CUDA tensors of another activation dtype
-    (the reference's fp16 mode, fp32 debugging runs) take the PyTorch definitions, i.e. the vendor libraries."""
+    """The hand-written kernels compute in bf16 or fp16 (fp32 accumulate; one library per element type).  CUDA
+    tensors of another activation dtype (fp32 debugging runs) take the PyTorch definitions, i.e. the vendor
+    libraries."""
     use = _native_inner(t, dtype, family)
     if family is not None:
         _last[family] = "native" if use else "torch"
@@ -66,13 +67,13 @@ def _native_inner(t: torch.Tensor, dtype: Optional[torch.dtype], family: Optiona
     if family is not None and _prefer.get(family, "native") == "torch":
         return False
     dtype = dtype or t.dtype
-    if dtype == torch.bfloat16:
+    if dtype in (torch.bfloat16, torch.float16):
         return True
     if dtype not in _warned_dtypes:
         _warned_dtypes.add(dtype)
         from ..utils.logging import LOG
         LOG("WARN", f"ops: {dtype} activations on a GPU run on the PyTorch / vendor-library path; the sm_100a kernels "
-                    "of this package compute in bf16")
+                    "of this package compute in bf16 or fp16")
     return False
 
 
@@ -84,7 +85,8 @@ def cell_embed(cells, cp_embed, pos_embed, colour_embed, out_dtype):
 
 
 def conv2d_nhwc(x, w_ohwi, stride: int, padding: int, dilation: int):
-    if _native(x, family="conv2d"):
+    # the implicit-GEMM kernels tile the input channels in blocks of 64; other channel counts take the library
+    if x.shape[3] % 64 == 0 and _native(x, family="conv2d"):
         from .native_ops import conv2d_nhwc as f
         return f(x, w_ohwi, stride, padding, dilation)
     return ref.conv2d_nhwc(x, w_ohwi, stride, padding, dilation)
@@ -193,7 +195,7 @@ def attention_qkv(qkv, causal: bool):
 
 
 def lstm_sequence(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype):
-    if _native(x, compute_dtype) and x.dtype == torch.bfloat16:
+    if _native(x, compute_dtype) and x.dtype == compute_dtype:
         from .native_ops import lstm_sequence as f
         return f(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype)
     if x.is_cuda and h0.dim() == 1:

@@ -120,12 +120,13 @@ def _geom_args(rows, cols, stride, pad, dil):
     return rows, cols, oh, ow, stride, pad, dil
 
 
-def features_native(cells: torch.Tensor, rows: int, cols: int, stride: int, pad: int, dil: int) -> torch.Tensor:
+def features_native(cells: torch.Tensor, rows: int, cols: int, stride: int, pad: int, dil: int,
+                    dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     from . import native as nv
     oh, ow = out_hw(rows, cols, stride, pad, dil)
     n = cells.shape[0]
-    out = torch.empty(n, oh * ow, FEATURES, dtype=torch.bfloat16, device=cells.device)
-    nv.check(nv.lib().fbam_embconv_features(nv.ptr(cells), nv.ptr(out), C.c_longlong(n),
+    out = torch.empty(n, oh * ow, FEATURES, dtype=dtype, device=cells.device)
+    nv.check(nv.lib(dtype).fbam_embconv_features(nv.ptr(cells), nv.ptr(out), C.c_longlong(n),
                                             *_geom_args(rows, cols, stride, pad, dil), nv.stream_ptr()),
              "fbam_embconv_features")
     return out
@@ -137,7 +138,7 @@ def forward_native(cells, table, pos, z, y, rows, cols, stride, pad, dil, z_has_
     return; ``y`` receives ``GELU(z)``."""
     from . import native as nv
     vocab, _, o = table.shape
-    nv.check(nv.lib().fbam_embconv_fwd(nv.ptr(cells), nv.ptr(table), nv.ptr(pos), nv.ptr(z), nv.ptr(y),
+    nv.check(nv.lib(table).fbam_embconv_fwd(nv.ptr(cells), nv.ptr(table), nv.ptr(pos), nv.ptr(z), nv.ptr(y),
                                        C.c_longlong(cells.shape[0]), vocab, o, *_geom_args(rows, cols, stride, pad, dil),
                                        seg_len, int(z_has_input), int(apply_gelu), nv.stream_ptr()),
              "fbam_embconv_fwd")
@@ -147,7 +148,7 @@ def reduce_native(cells, dz, s, d, rows, cols, stride, pad, dil, seg_len: int = 
     """Adds into ``s`` (fp32, at least ``(V, 9, O)``; rows past ``vocab`` are left alone) and ``d`` (fp32 ``(P_out, O)``)."""
     from . import native as nv
     o = dz.shape[-1]
-    nv.check(nv.lib().fbam_embconv_bwd_reduce(nv.ptr(cells), nv.ptr(dz), nv.ptr(s), nv.ptr(d),
+    nv.check(nv.lib(dz).fbam_embconv_bwd_reduce(nv.ptr(cells), nv.ptr(dz), nv.ptr(s), nv.ptr(d),
                                               C.c_longlong(cells.shape[0]), s.shape[0], o,
                                               *_geom_args(rows, cols, stride, pad, dil), seg_len, nv.stream_ptr()),
              "fbam_embconv_bwd_reduce")
@@ -180,7 +181,7 @@ def _tables_native(cp_embed, pos_embed, colour, w, rows, cols, stride, pad, dil)
         return _table_cache[key]
     o, _, _, c = w.shape
     v = cp_embed.shape[0]
-    bf = torch.bfloat16
+    bf = w.dtype                                                      # the 16-bit type of the filter: bf16 or fp16
     ext = torch.cat([cp_embed, colour], 0).to(bf)
     w_p = w.permute(1, 2, 0, 3).reshape(9 * o, c).contiguous()
     prod = no.gemm(ext, w_p)                                          # (V + 6, 9·O)
@@ -208,7 +209,7 @@ def first_layer_forward_native(cells, cp_embed, pos_embed, colour, w, rows, cols
     n = cells.shape[0]
     oh, ow = out_hw(rows, cols, stride, pad, dil)
     _ext, _w_p, table, cc_t, pos_out, _pos_img = _tables_native(cp_embed, pos_embed, colour, w, rows, cols, stride, pad, dil)
-    feat = features_native(cells, rows, cols, stride, pad, dil)
+    feat = features_native(cells, rows, cols, stride, pad, dil, w.dtype)
     # colour term: K = 64 makes this GEMM all epilogue; single CTAs with 256 x 256 tiles measured fastest for it
     z = no.gemm(feat.view(n * oh * ow, FEATURES), cc_t, bm=256, bn=256, two_cta=False)
     y = torch.empty_like(z)
@@ -225,7 +226,7 @@ def first_layer_backward_native(cells, feat, dz, cp_embed, pos_embed, colour, w,
     v = cp_embed.shape[0]
     n = cells.shape[0]
     oh, ow = out_hw(rows, cols, stride, pad, dil)
-    bf = torch.bfloat16
+    bf = w.dtype
     ext, w_p, _table, _cc_t, _pos_out, pos_img = _tables_native(cp_embed, pos_embed, colour, w, rows, cols, stride, pad, dil)
     dz = dz.contiguous()
     s = torch.zeros(v + 6, 9, o, dtype=torch.float32, device=dz.device)
@@ -289,13 +290,13 @@ def first_layer_backward_torch(cells, feat, dz, cp_embed, pos_embed, colour, w, 
 
 
 class CellConvGelu(torch.autograd.Function):
-    """``GELU(conv3x3(cell_embed(cells)))`` through the table decomposition.  CUDA bf16 parameters take the native
+    """``GELU(conv3x3(cell_embed(cells)))`` through the table decomposition.  CUDA bf16 / fp16 parameters take the native
     kernels; anything else the PyTorch form (which is how the decomposition is tested on the CPU)."""
 
     @staticmethod
     def forward(ctx, cells, cp_embed, pos_embed, colour, w, rows, cols, stride, pad, dil):
         cells = cells.contiguous()
-        native = cells.is_cuda and w.dtype == torch.bfloat16 and supported(cells, cp_embed, w)
+        native = cells.is_cuda and w.dtype in (torch.bfloat16, torch.float16) and supported(cells, cp_embed, w)
         geom = (rows, cols, stride, pad, dil)
         if native:
             y, z, feat = first_layer_forward_native(cells, cp_embed, pos_embed, colour, w, *geom)

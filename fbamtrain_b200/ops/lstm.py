@@ -22,7 +22,7 @@ from ..utils import flops
 
 from . import native as nv
 from . import reference as ref
-from .native_ops import BF16, gemm, gemm_nn, gemm_tn
+from .native_ops import gemm, gemm_nn, gemm_tn
 
 _scratch = {}
 
@@ -45,15 +45,15 @@ class _LstmSequence(torch.autograd.Function):
         h = w_hh.shape[1]
         dev = x.device
         x2 = x.reshape(t_len * b, i_dim).contiguous()
-        wi, wh = w_ih.to(BF16), w_hh.to(BF16)
+        wi, wh = w_ih.to(x.dtype), w_hh.to(x.dtype)
         bias = (b_ih.float() + b_hh.float()).contiguous()
         gates = gemm(x2, wi, bias=bias, out_dtype=torch.float32).view(t_len, b, 4 * h)
-        y = torch.empty(t_len, b, h, dtype=BF16, device=dev)
+        y = torch.empty(t_len, b, h, dtype=x.dtype, device=dev)
         c_all = torch.empty(t_len, b, h, dtype=torch.float32, device=dev)
-        hbuf = torch.empty(2 * 8 * h, dtype=BF16, device=dev)
+        hbuf = torch.empty(2 * 8 * h, dtype=x.dtype, device=dev)
         h0f, c0f = h0.float().contiguous(), c0.float().contiguous()
         per_sample = int(h0.dim() == 2)
-        nv.check(nv.lib().fbam_lstm_fwd_ex(nv.ptr(gates), nv.ptr(wh), nv.ptr(h0f), nv.ptr(c0f), nv.ptr(y),
+        nv.check(nv.lib(wh).fbam_lstm_fwd_ex(nv.ptr(gates), nv.ptr(wh), nv.ptr(h0f), nv.ptr(c0f), nv.ptr(y),
                                            nv.ptr(c_all), nv.ptr(hbuf), nv.ptr(_counter(dev)),
                                            nv.ptr(nv.status_word(dev)), t_len, b, h, per_sample, nv.stream_ptr()),
                  "fbam_lstm_fwd")
@@ -70,12 +70,12 @@ class _LstmSequence(torch.autograd.Function):
         dev = dy.device
         dy = dy.contiguous()
         wh_t = wh.t().contiguous()
-        dgates = torch.empty(t_len, b, 4 * h, dtype=BF16, device=dev)
+        dgates = torch.empty(t_len, b, 4 * h, dtype=wh.dtype, device=dev)
         dh0 = torch.empty(b, h, dtype=torch.float32, device=dev)
         dc0 = torch.empty(b, h, dtype=torch.float32, device=dev)
         dhl = None if dh_last is None else dh_last.float().contiguous()
         dcl = None if dc_last is None else dc_last.float().contiguous()
-        nv.check(nv.lib().fbam_lstm_bwd_ex(nv.ptr(gates), nv.ptr(c_all), nv.ptr(c0f), nv.ptr(dy), nv.ptr(wh_t),
+        nv.check(nv.lib(wh).fbam_lstm_bwd_ex(nv.ptr(gates), nv.ptr(c_all), nv.ptr(c0f), nv.ptr(dy), nv.ptr(wh_t),
                                            nv.ptr(dgates), nv.ptr(dh0), nv.ptr(dc0), nv.ptr(dhl), nv.ptr(dcl),
                                            nv.ptr(_counter(dev)), nv.ptr(nv.status_word(dev)), t_len, b, h,
                                            ctx.per_sample, nv.stream_ptr()), "fbam_lstm_bwd")
@@ -83,7 +83,7 @@ class _LstmSequence(torch.autograd.Function):
         dg2 = dgates.view(t_len * b, 4 * h)
         dx = gemm_nn(dg2, wi).view(t_len, b, i_dim) if ctx.needs_input_grad[0] else None
         dw_ih = gemm_tn(dg2, x2, out_dtype=torch.float32)
-        h_first = h0f.to(BF16).view(1, b, h) if ctx.per_sample else h0f.to(BF16).expand(1, b, h)
+        h_first = h0f.to(y.dtype).view(1, b, h) if ctx.per_sample else h0f.to(y.dtype).expand(1, b, h)
         h_prev = torch.cat([h_first, y[:-1]], 0).reshape(t_len * b, h)
         dw_hh = gemm_tn(dg2, h_prev, out_dtype=torch.float32)
         from .native_ops import _colsum
@@ -98,22 +98,23 @@ def _stepwise(x, w_ih, w_hh, b_ih, b_hh, h0, c0):
     from .native_ops import linear
     t_len, b, _ = x.shape
     hdim = w_hh.shape[1]
-    wi, wh = w_ih.to(BF16), w_hh.to(BF16)
+    wi, wh = w_ih.to(x.dtype), w_hh.to(x.dtype)
     bias = b_ih.float() + b_hh.float()
     xg = linear(x.reshape(t_len * b, -1), wi).float().view(t_len, b, 4 * hdim)
-    h = h0.to(BF16).unsqueeze(0).expand(b, hdim).contiguous()
+    h = h0.to(x.dtype).unsqueeze(0).expand(b, hdim).contiguous()
     c = c0.float().unsqueeze(0).expand(b, hdim)
     ys = []
     for t in range(t_len):
         hf, c = ref.lstm_cell(xg[t] + linear(h, wh).float() + bias, c)
-        h = hf.to(BF16)
+        h = hf.to(x.dtype)
         ys.append(h)
     return torch.stack(ys, 0), h, c
 
 
 def lstm_sequence(x, w_ih, w_hh, b_ih, b_hh, h0, c0, compute_dtype):
-    if compute_dtype != BF16:
-        raise TypeError("native LSTM computes in bf16")
+    if compute_dtype not in nv.ELEM_DTYPES:
+        raise TypeError("native LSTM computes in bf16 or fp16")
+    x = x.to(compute_dtype)
     if not persistent_ok(x.shape[1], w_hh.shape[1]) or x.shape[2] % 8 != 0:
         return _stepwise(x, w_ih, w_hh, b_ih, b_hh, h0, c0)
-    return _LstmSequence.apply(x.to(BF16), w_ih, w_hh, b_ih, b_hh, h0, c0)
+    return _LstmSequence.apply(x, w_ih, w_hh, b_ih, b_hh, h0, c0)

@@ -1,9 +1,11 @@
-"""ctypes binding of ``lib/libfbam_kernels.so`` (hand-written sm_100a kernels).
+"""ctypes binding of ``lib/libfbam_kernels.so`` and ``lib/libfbam_kernels_fp16.so`` (hand-written sm_100a kernels).
 
-The library exports plain C entry points that take device pointers, sizes and a CUDA stream; this
-module loads it, mirrors its parameter structs, and converts non-zero return codes and device-side
-status words into Python exceptions.  If the library is absent on a machine that has a GPU, loading
-raises — CUDA tensors never fall back to a PyTorch implementation silently.
+The kernel sources are compiled twice, once per 16-bit element type (bf16, IEEE half; fp32 accumulation in both);
+the two libraries export the same plain C entry points that take device pointers, sizes and a CUDA stream.
+``lib(like)`` returns the library for the dtype of ``like``.  This module loads them, mirrors their parameter
+structs, and converts non-zero return codes and device-side status words into Python exceptions.  If a library is
+absent on a machine that has a GPU, loading raises — CUDA tensors never fall back to a PyTorch implementation
+silently.
 """
 from __future__ import annotations
 
@@ -18,7 +20,10 @@ from ..utils import plan as _plan
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libfbam_kernels.so")
+LIB_PATH_FP16 = os.path.join(os.path.dirname(_HERE), "lib", "libfbam_kernels_fp16.so")
 _lib: Optional[C.CDLL] = None
+_lib_fp16: Optional[C.CDLL] = None
+ELEM_DTYPES = (torch.bfloat16, torch.float16)
 
 GEMM_ACT = {"none": 0, "gelu": 1, "relu": 2}
 GEMM_ACC_NONE, GEMM_ACC_RMW, GEMM_ACC_ATOMIC = 0, 1, 2
@@ -61,11 +66,11 @@ class GemmParams(C.Structure):
                 ("conv", ConvGeom)]
 
 
-def available() -> bool:
-    return os.path.exists(LIB_PATH)
+def available(dtype: torch.dtype = torch.bfloat16) -> bool:
+    return os.path.exists(LIB_PATH_FP16 if dtype == torch.float16 else LIB_PATH)
 
 
-def _check_struct_layout(library: C.CDLL) -> None:
+def _check_struct_layout(library: C.CDLL, path: str) -> None:
     """The parameter struct is mirrored by hand above: refuse a library whose layout differs (a stale build)."""
     got = (C.c_longlong * 8)()
     library.fbam_gemm_params_layout.restype = None
@@ -74,25 +79,37 @@ def _check_struct_layout(library: C.CDLL) -> None:
             GemmParams.rs_out.offset, GemmParams.rs_row_stores.offset, GemmParams.mode.offset,
             GemmParams.conv.offset, C.sizeof(ConvGeom)]
     if list(got) != mine:
-        raise RuntimeError(f"{LIB_PATH} was built from different sources than this binding (GemmParams layout "
+        raise RuntimeError(f"{path} was built from different sources than this binding (GemmParams layout "
                            f"{list(got)} vs {mine}); run `python -m fbamtrain_b200.build`")
 
 
-def lib() -> C.CDLL:
-    global _lib
+def _load(path: str) -> C.CDLL:
+    if not os.path.exists(path):
+        raise RuntimeError(f"native kernel library missing: {path} (run `python -m fbamtrain_b200.build`)")
+    library = C.CDLL(path)
+    _check_struct_layout(library, path)
+    for name in ("fbam_gemm", "fbam_conv", "fbam_conv_wgrad", "fbam_gemm2", "fbam_conv2",
+                 "fbam_lstm_persistent_max_hidden", "fbam_lstm_fwd_ex", "fbam_lstm_bwd_ex", "fbam_elem_is_fp16"):
+        getattr(library, name).restype = C.c_int
+    return library
+
+
+def lib(like=None) -> C.CDLL:
+    """The kernel library for the 16-bit element type of ``like`` (a tensor or a dtype): the half-precision build
+    for ``torch.float16``, the bf16 build for everything else (bf16, and calls whose operands are all fp32 or
+    integer, which are the same code in both)."""
+    global _lib, _lib_fp16
+    dtype = like.dtype if isinstance(like, torch.Tensor) else like
+    if dtype == torch.float16:
+        if _lib_fp16 is None:
+            _lib_fp16 = _load(LIB_PATH_FP16)
+            if _lib_fp16.fbam_elem_is_fp16() != 1:
+                raise RuntimeError(f"{LIB_PATH_FP16} was not built with half-precision elements")
+        return _lib_fp16
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
-            raise RuntimeError(f"native kernel library missing: {LIB_PATH} (run `python -m fbamtrain_b200.build`)")
-        _lib = C.CDLL(LIB_PATH)
-        _check_struct_layout(_lib)
-        _lib.fbam_gemm_bf16.restype = C.c_int
-        _lib.fbam_conv_bf16.restype = C.c_int
-        _lib.fbam_conv_wgrad_bf16.restype = C.c_int
-        _lib.fbam_gemm2_bf16.restype = C.c_int
-        _lib.fbam_conv2_bf16.restype = C.c_int
-        _lib.fbam_lstm_persistent_max_hidden.restype = C.c_int
-        _lib.fbam_lstm_fwd_ex.restype = C.c_int
-        _lib.fbam_lstm_bwd_ex.restype = C.c_int
+        _lib = _load(LIB_PATH)
+        if _lib.fbam_elem_is_fp16() != 0:
+            raise RuntimeError(f"{LIB_PATH} was not built with bf16 elements")
     return _lib
 
 
@@ -108,9 +125,11 @@ def check(code: int, what: str) -> None:
     global _launches
     if code != 0:
         detail = ""
-        if code in (3, 5) and _lib is not None and hasattr(_lib, "fbam_last_driver_error"):
-            detail = (f"; driver result {_lib.fbam_last_driver_error()}, pending runtime error "
-                      f"{_lib.fbam_pending_runtime_error()}")
+        if code in (3, 5):
+            for loaded in (_lib, _lib_fp16):
+                if loaded is not None and hasattr(loaded, "fbam_last_driver_error") and loaded.fbam_last_driver_error():
+                    detail = (f"; driver result {loaded.fbam_last_driver_error()}, pending runtime error "
+                              f"{loaded.fbam_pending_runtime_error()}")
         raise RuntimeError(f"{what}: {_ERRORS.get(code, 'error')} (code {code}){detail}")
     _launches += 1
     if _debug.BREAK_ON_LAUNCH and _debug.break_requested(_launches, what):

@@ -30,17 +30,25 @@ TWO_CTA = "auto"
 USE_MN_MAJOR = True
 
 
-def _need_bf16(*ts):
+def _need_elem(*ts) -> torch.dtype:
+    """All given tensors must share one 16-bit element type (bf16 or half); returns it."""
+    dtype = None
     for t in ts:
-        if t is not None and t.dtype != BF16:
-            raise TypeError(f"native kernels take bf16 tensors, got {t.dtype}")
+        if t is None:
+            continue
+        if t.dtype not in nv.ELEM_DTYPES:
+            raise TypeError(f"native kernels take bf16 or fp16 tensors, got {t.dtype}")
+        if dtype is not None and t.dtype != dtype:
+            raise TypeError(f"native kernels take operands of one 16-bit type, got {dtype} and {t.dtype}")
+        dtype = t.dtype
+    return dtype
 
 
 # =================================================================================================
 # GEMM
 # =================================================================================================
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
-         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = BF16, bias: Optional[torch.Tensor] = None,
+         out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, bias: Optional[torch.Tensor] = None,
          act: str = "none", residual: Optional[torch.Tensor] = None, preact_out: Optional[torch.Tensor] = None,
          gelu_grad_in: Optional[torch.Tensor] = None, accumulate: int = 0, alpha: float = 1.0,
          bn: int = 0, bm: int = 0, max_ctas: int = 0, ready_flags: Optional[torch.Tensor] = None,
@@ -50,7 +58,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     """``D[M, N] = epilogue(A · Bᵀ)``.
 
     ``a``: ``(M, K)`` (or ``(K, M)`` when ``a_mn``); ``b``: ``(N, K)`` (or ``(K, N)`` when ``b_mn``).
-    Operands must be bf16 with unit inner stride, 16-byte aligned rows.  ``accumulate``: 0 overwrite,
+    Operands must be bf16 or fp16 (both the same) with unit inner stride; ``out_dtype`` defaults to theirs.  ``accumulate``: 0 overwrite,
     1 read-modify-write ``D +=``, 2 atomic adds (fp32 output only).
 
     ``ready_flags`` (int32 tensor in local memory, written by peers) gates the loads of A (or B with
@@ -67,7 +75,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     leaves per-row (maximum, sum of exp) pairs of every tile half in ``partial`` ``(M, 2·⌈N/256⌉, 2)`` fp32 and the
     target logits in ``tgt_logit``; ``ce_grad = (lse, targets, vocab, scale)`` writes ``scale·(softmax − onehot)``
     computed from the accumulators and the rows' log-sum-exp instead of the logits."""
-    _need_bf16(a, b)
+    _need_elem(a, b)
     if a.stride(-1) != 1 or b.stride(-1) != 1:
         raise ValueError("GEMM operands need unit inner stride")
     a, b = _tma_pitch(a), _tma_pitch(b)
@@ -92,7 +100,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         out = partial                       # nothing is written through D in this mode
         two_cta = False
     elif out is None:
-        out = debug.fresh((m, n), out_dtype, a.device)
+        out = debug.fresh((m, n), out_dtype or a.dtype, a.device)
     if ce_stats is None and (out.shape != (m, n) or out.stride(1) != 1):
         raise ValueError("output has the wrong shape or layout")
     if ce_grad is not None:
@@ -104,7 +112,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     p.bias = 0 if bias is None else bias.data_ptr()
     p.bias_fp32 = int(bias is not None and bias.dtype == torch.float32)
     if residual is not None:
-        _need_bf16(residual)
+        _need_elem(residual)
         p.residual, p.ldr = residual.data_ptr(), residual.stride(0)
     if preact_out is not None:
         if preact_out.stride(0) != out.stride(0):
@@ -134,11 +142,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if pair == "auto":
         pair = (n >= 256 and n % 16 == 0 and bm != 128 and
                 ((m + 255) // 256) * ((n + 255) // 256) >= 148)
-    fn = nv.lib().fbam_gemm2_bf16 if pair else nv.lib().fbam_gemm_bf16
+    fn = nv.lib(a).fbam_gemm2 if pair else nv.lib(a).fbam_gemm
     with debug.label(f"gemm{'2' if pair else ''} m{m} n{n} k{k} {'T' if a_mn else 'N'}{'T' if b_mn else 'N'}"):
         code = fn(nv.ptr(a), C.c_longlong(a.stride(0)), int(a_mn), nv.ptr(b), C.c_longlong(b.stride(0)), int(b_mn),
                   m, n, k, C.byref(p), nv.stream_ptr())
-    nv.check(code, "fbam_gemm_bf16")
+    nv.check(code, "fbam_gemm")
     flops.add(2.0 * m * n * k)
     debug.after_launch("gemm", a, b, out)
     return out
@@ -184,14 +192,14 @@ def gemm_tn(a_km, b_kn, **kw):
 
 def _colsum(x2d: torch.Tensor) -> torch.Tensor:
     out = torch.zeros(x2d.shape[1], dtype=torch.float32, device=x2d.device)
-    nv.check(nv.lib().fbam_colsum(nv.ptr(x2d), nv.ptr(out), C.c_longlong(x2d.shape[0]), x2d.shape[1],
+    nv.check(nv.lib(x2d).fbam_colsum(nv.ptr(x2d), nv.ptr(out), C.c_longlong(x2d.shape[0]), x2d.shape[1],
                                   nv.stream_ptr()), "fbam_colsum")
     return out
 
 
 def _gelu_bwd(preact: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
     out = torch.empty_like(dy)
-    nv.check(nv.lib().fbam_gelu(nv.ptr(preact), nv.ptr(dy), nv.ptr(out), C.c_longlong(dy.numel()), 1,
+    nv.check(nv.lib(preact).fbam_gelu(nv.ptr(preact), nv.ptr(dy), nv.ptr(out), C.c_longlong(dy.numel()), 1,
                                 nv.stream_ptr()), "fbam_gelu")
     return out
 
@@ -204,7 +212,7 @@ class _Linear(torch.autograd.Function):
             x2 = x2.contiguous()
         preact = None
         if act == "gelu" and (x.requires_grad or weight.requires_grad):
-            preact = torch.empty((x2.shape[0], weight.shape[0]), dtype=BF16, device=x.device)
+            preact = torch.empty((x2.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
         res2 = None
         if residual is not None:            # added in the GEMM epilogue, after the activation
             res2 = residual.reshape(-1, weight.shape[0])
@@ -233,13 +241,13 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = gemm_tn(dy2, x2)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = _colsum(dy2).to(BF16)
+            db = _colsum(dy2).to(dy2.dtype)
         d_res = dy if len(ctx.needs_input_grad) > 4 and ctx.needs_input_grad[4] else None
         return dx, dw, db, None, d_res
 
 
 def linear(x, weight, bias=None, act="none", residual=None):
-    _need_bf16(x, weight, bias, residual)
+    _need_elem(x, weight, bias, residual)
     return _Linear.apply(x, weight, bias, act, residual)
 
 
@@ -266,8 +274,8 @@ def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor
               out_mul=1, out_off=(0, 0), accumulate=0, bn: int = 0, act: str = "none",
               preact_out: Optional[torch.Tensor] = None, gelu_grad_in: Optional[torch.Tensor] = None,
               tile_rows: int = 0, two_cta=None) -> None:
-    """One implicit-GEMM pass (see ``ConvGeom`` in csrc/gemm_tcgen05.h).  ``x`` NHWC bf16, ``wmat``
-    ``(n_out, taps·C)`` bf16, ``out`` NHWC with ``n_out`` channels."""
+    """One implicit-GEMM pass (see ``ConvGeom`` in csrc/gemm_tcgen05.h).  ``x`` NHWC bf16 or fp16, ``wmat``
+    ``(n_out, taps·C)`` of the same type, ``out`` NHWC with ``n_out`` channels."""
     b, ih, iw, c = x.shape
     if bn == 0 and tile_rows == 0 and two_cta is None:
         tuned = tuning.lookup(tuning.conv_key(b, grid_hw[0], grid_hw[1], c, n_out, len(taps), in_mul, out_mul),
@@ -309,11 +317,11 @@ def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor
         p.preact_out = preact_out.data_ptr()
     if gelu_grad_in is not None:
         p.gelu_grad_in = gelu_grad_in.data_ptr()
-    fn = nv.lib().fbam_conv2_bf16 if pair else nv.lib().fbam_conv_bf16
+    fn = nv.lib(x).fbam_conv2 if pair else nv.lib(x).fbam_conv
     with debug.label(f"conv{'2' if pair else ''} c{c} n{n_out} taps{len(taps)} in_mul{in_mul} out_mul{out_mul} {act}"):
         code = fn(nv.ptr(x), ih, iw, c, nv.ptr(wmat), C.c_longlong(wmat.stride(0)), n_out, C.byref(p),
                   nv.stream_ptr())
-    nv.check(code, "fbam_conv_bf16")
+    nv.check(code, "fbam_conv")
     flops.add(2.0 * b * grid_hw[0] * grid_hw[1] * n_out * len(taps) * c)
     debug.after_launch("conv_pass", x, wmat, out)
 
@@ -323,7 +331,7 @@ def conv2d_fprop(x, w_ohwi, stride, padding, dilation, act: str = "none", preact
     o = w_ohwi.shape[0]
     oh = (ih + 2 * padding - 2 * dilation - 1) // stride + 1
     ow = (iw + 2 * padding - 2 * dilation - 1) // stride + 1
-    out = debug.fresh((b, oh, ow, o), BF16, x.device)
+    out = debug.fresh((b, oh, ow, o), x.dtype, x.device)
     taps = [(r * dilation - padding, s * dilation - padding) for r in range(3) for s in range(3)]
     conv_pass(x, w_ohwi.reshape(o, 9 * c), o, out, grid_hw=(oh, ow), in_mul=stride, taps=taps, act=act,
               preact_out=preact_out)
@@ -341,7 +349,7 @@ def conv2d_dgrad(dy, w_ohwi, in_hw, stride, padding, dilation, gelu_grad_in=None
     b, oh, ow, o = dy.shape
     c = w_ohwi.shape[3]
     ih, iw = in_hw
-    dx = debug.fresh((b, ih, iw, c), BF16, dy.device)
+    dx = debug.fresh((b, ih, iw, c), dy.dtype, dy.device)
     covered = 0
     for ph in range(stride):
         for pw in range(stride):
@@ -380,13 +388,13 @@ class _ConvGeluStackPool(torch.autograd.Function):
         ys, zs = [x], []
         for w, pad, dil in zip(weights, paddings, dilations):
             oh, ow = conv_out_hw(ys[-1].shape[1], ys[-1].shape[2], stride, pad, dil)
-            z = debug.fresh((x.shape[0], oh, ow, w.shape[0]), BF16, x.device)
+            z = debug.fresh((x.shape[0], oh, ow, w.shape[0]), x.dtype, x.device)
             ys.append(conv2d_fprop(ys[-1], w, stride, pad, dil, act="gelu", preact_out=z))
             zs.append(z)
         last = ys[-1]
         n, h, wd, c = last.shape
-        vec = torch.empty(n, c, dtype=BF16, device=x.device)
-        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(last), nv.ptr(vec), C.c_longlong(n), h * wd, c, 0, None,
+        vec = torch.empty(n, c, dtype=last.dtype, device=x.device)
+        nv.check(nv.lib(last).fbam_global_avgpool(nv.ptr(last), nv.ptr(vec), C.c_longlong(n), h * wd, c, 0, None,
                                               nv.stream_ptr()), "fbam_global_avgpool")
         ctx.save_for_backward(*ys[:-1], *zs, *weights)
         ctx.cfg = (stride, tuple(paddings), tuple(dilations), len(weights))
@@ -401,7 +409,7 @@ class _ConvGeluStackPool(torch.autograd.Function):
         z_last = zs[-1]
         n, h, wd, c = z_last.shape
         dz = torch.empty_like(z_last)
-        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(dvec.contiguous()), nv.ptr(dz), C.c_longlong(n), h * wd, c, 1,
+        nv.check(nv.lib(dvec).fbam_global_avgpool(nv.ptr(dvec.contiguous()), nv.ptr(dz), C.c_longlong(n), h * wd, c, 1,
                                               nv.ptr(z_last), nv.stream_ptr()), "fbam_global_avgpool")
         dws = [None] * nb
         for i in range(nb - 1, -1, -1):
@@ -431,13 +439,13 @@ class _CellConvGeluStackPool(torch.autograd.Function):
         ys, zs = [y1], [z1]
         for w, pad, dil in zip(weights[1:], paddings[1:], dilations[1:]):
             oh, ow = conv_out_hw(ys[-1].shape[1], ys[-1].shape[2], stride, pad, dil)
-            z = debug.fresh((cells.shape[0], oh, ow, w.shape[0]), BF16, cells.device)
+            z = debug.fresh((cells.shape[0], oh, ow, w.shape[0]), y1.dtype, cells.device)
             ys.append(conv2d_fprop(ys[-1], w, stride, pad, dil, act="gelu", preact_out=z))
             zs.append(z)
         last = ys[-1]
         n, h, wd, c = last.shape
-        vec = torch.empty(n, c, dtype=BF16, device=cells.device)
-        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(last), nv.ptr(vec), C.c_longlong(n), h * wd, c, 0, None,
+        vec = torch.empty(n, c, dtype=last.dtype, device=cells.device)
+        nv.check(nv.lib(last).fbam_global_avgpool(nv.ptr(last), nv.ptr(vec), C.c_longlong(n), h * wd, c, 0, None,
                                               nv.stream_ptr()), "fbam_global_avgpool")
         ctx.save_for_backward(cells, feat, cp_embed, pos_embed, colour, *ys[:-1], *zs, *weights)
         ctx.cfg = (rows, cols, stride, tuple(paddings), tuple(dilations), len(weights))
@@ -455,7 +463,7 @@ class _CellConvGeluStackPool(torch.autograd.Function):
         z_last = zs[-1]
         n, h, wd, c = z_last.shape
         dz = torch.empty_like(z_last)
-        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(dvec.contiguous()), nv.ptr(dz), C.c_longlong(n), h * wd, c, 1,
+        nv.check(nv.lib(dvec).fbam_global_avgpool(nv.ptr(dvec.contiguous()), nv.ptr(dz), C.c_longlong(n), h * wd, c, 1,
                                               nv.ptr(z_last), nv.stream_ptr()), "fbam_global_avgpool")
         dws = [None] * nb
         for i in range(nb - 1, 0, -1):
@@ -471,13 +479,13 @@ class _CellConvGeluStackPool(torch.autograd.Function):
 
 
 def cell_conv_gelu_stack_pool(cells, cp_embed, pos_embed, colour, rows, cols, weights, stride, paddings, dilations):
-    _need_bf16(*weights)
+    _need_elem(*weights)
     return _CellConvGeluStackPool.apply(cells, cp_embed, pos_embed, colour, rows, cols, stride, tuple(paddings),
                                         tuple(dilations), *weights)
 
 
 def conv_gelu_stack_pool(x, weights, stride, paddings, dilations):
-    _need_bf16(x, *weights)
+    _need_elem(x, *weights)
     return _ConvGeluStackPool.apply(x.contiguous(), stride, tuple(paddings), tuple(dilations), *weights)
 
 
@@ -507,7 +515,7 @@ class _Conv2d(torch.autograd.Function):
 
 
 def conv2d_nhwc(x, w_ohwi, stride, padding, dilation):
-    _need_bf16(x, w_ohwi)
+    _need_elem(x, w_ohwi)
     if x.shape[3] % 64 != 0:
         raise ValueError("native convolution needs input channels in multiples of 64")
     return _Conv2d.apply(x.contiguous(), w_ohwi, stride, padding, dilation)
@@ -522,7 +530,7 @@ class _RmsNorm(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
         y = torch.empty_like(x2)
         rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
-        nv.check(nv.lib().fbam_rmsnorm_fwd(nv.ptr(x2), nv.ptr(weight), nv.ptr(y), nv.ptr(rstd),
+        nv.check(nv.lib(x2).fbam_rmsnorm_fwd(nv.ptr(x2), nv.ptr(weight), nv.ptr(y), nv.ptr(rstd),
                                            C.c_longlong(x2.shape[0]), x2.shape[1], C.c_float(eps), nv.stream_ptr()),
                  "fbam_rmsnorm_fwd")
         ctx.save_for_backward(x2, weight, rstd)
@@ -534,13 +542,13 @@ class _RmsNorm(torch.autograd.Function):
         dy2 = dy.reshape(x2.shape).contiguous()
         dx = torch.empty_like(x2)
         dg = torch.zeros(x2.shape[1], dtype=torch.float32, device=x2.device)
-        nv.check(nv.lib().fbam_rmsnorm_bwd(nv.ptr(dy2), nv.ptr(x2), nv.ptr(weight), nv.ptr(rstd), nv.ptr(dx), nv.ptr(dg),
+        nv.check(nv.lib(dy2).fbam_rmsnorm_bwd(nv.ptr(dy2), nv.ptr(x2), nv.ptr(weight), nv.ptr(rstd), nv.ptr(dx), nv.ptr(dg),
                                            C.c_longlong(x2.shape[0]), x2.shape[1], nv.stream_ptr()), "fbam_rmsnorm_bwd")
         return dx.view(dy.shape), dg.to(weight.dtype), None
 
 
 def rms_norm(x, weight, eps):
-    _need_bf16(x, weight)
+    _need_elem(x, weight)
     return _RmsNorm.apply(x, weight, eps)
 
 
@@ -554,7 +562,7 @@ class _LayerNorm(torch.autograd.Function):
         y = torch.empty_like(x2)
         mean = torch.empty(rows, dtype=torch.float32, device=x.device)
         rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
-        nv.check(nv.lib().fbam_layernorm_fwd_stats(nv.ptr(x2), nv.ptr(weight), nv.ptr(bias), nv.ptr(y), nv.ptr(mean),
+        nv.check(nv.lib(x2).fbam_layernorm_fwd_stats(nv.ptr(x2), nv.ptr(weight), nv.ptr(bias), nv.ptr(y), nv.ptr(mean),
                                                    nv.ptr(rstd), C.c_longlong(rows), dim, C.c_float(eps),
                                                    nv.stream_ptr()), "fbam_layernorm_fwd_stats")
         ctx.save_for_backward(x2, weight, mean, rstd)
@@ -569,14 +577,14 @@ class _LayerNorm(torch.autograd.Function):
         dx = torch.empty_like(x2)
         dw = torch.zeros(dim, dtype=torch.float32, device=x2.device)
         db = torch.zeros(dim, dtype=torch.float32, device=x2.device) if ctx.has_bias else None
-        nv.check(nv.lib().fbam_layernorm_bwd(nv.ptr(dy2), nv.ptr(x2), nv.ptr(weight), nv.ptr(mean), nv.ptr(rstd),
+        nv.check(nv.lib(dy2).fbam_layernorm_bwd(nv.ptr(dy2), nv.ptr(x2), nv.ptr(weight), nv.ptr(mean), nv.ptr(rstd),
                                              nv.ptr(dx), nv.ptr(dw), nv.ptr(db), C.c_longlong(rows), dim,
                                              nv.stream_ptr()), "fbam_layernorm_bwd")
         return dx.view(dy.shape), dw.to(weight.dtype), (db.to(weight.dtype) if db is not None else None), None
 
 
 def layer_norm(x, weight, bias, eps):
-    _need_bf16(x, weight, bias)
+    _need_elem(x, weight, bias)
     if x.shape[-1] > 8192:
         raise ValueError("native LayerNorm handles rows of up to 8192 elements")
     return _LayerNorm.apply(x, weight, bias, eps)
@@ -587,7 +595,7 @@ class _Gelu(torch.autograd.Function):
     def forward(ctx, x):
         x = x.contiguous()
         y = torch.empty_like(x)
-        nv.check(nv.lib().fbam_gelu(nv.ptr(x), None, nv.ptr(y), C.c_longlong(x.numel()), 0, nv.stream_ptr()), "fbam_gelu")
+        nv.check(nv.lib(x).fbam_gelu(nv.ptr(x), None, nv.ptr(y), C.c_longlong(x.numel()), 0, nv.stream_ptr()), "fbam_gelu")
         ctx.save_for_backward(x)
         return y
 
@@ -598,7 +606,7 @@ class _Gelu(torch.autograd.Function):
 
 
 def gelu(x):
-    _need_bf16(x)
+    _need_elem(x)
     return _Gelu.apply(x)
 
 
@@ -608,8 +616,8 @@ class _Geglu(torch.autograd.Function):
         x = x.contiguous()
         c = x.shape[-1] // 2
         rows = x.numel() // (2 * c)
-        y = torch.empty(*x.shape[:-1], c, dtype=BF16, device=x.device)
-        nv.check(nv.lib().fbam_geglu(nv.ptr(x), None, nv.ptr(y), C.c_longlong(rows), c, 0, nv.stream_ptr()), "fbam_geglu")
+        y = torch.empty(*x.shape[:-1], c, dtype=x.dtype, device=x.device)
+        nv.check(nv.lib(x).fbam_geglu(nv.ptr(x), None, nv.ptr(y), C.c_longlong(rows), c, 0, nv.stream_ptr()), "fbam_geglu")
         ctx.save_for_backward(x)
         return y
 
@@ -618,13 +626,13 @@ class _Geglu(torch.autograd.Function):
         (x,) = ctx.saved_tensors
         c = x.shape[-1] // 2
         dx = torch.empty_like(x)
-        nv.check(nv.lib().fbam_geglu(nv.ptr(x), nv.ptr(dy.contiguous()), nv.ptr(dx), C.c_longlong(x.numel() // (2 * c)),
+        nv.check(nv.lib(x).fbam_geglu(nv.ptr(x), nv.ptr(dy.contiguous()), nv.ptr(dx), C.c_longlong(x.numel() // (2 * c)),
                                      c, 1, nv.stream_ptr()), "fbam_geglu")
         return dx
 
 
 def geglu(x):
-    _need_bf16(x)
+    _need_elem(x)
     return _Geglu.apply(x)
 
 
@@ -632,8 +640,8 @@ class _AvgPool2x2(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x):
         n, h, w, c = x.shape
-        y = torch.empty(n, h // 2, w // 2, c, dtype=BF16, device=x.device)
-        nv.check(nv.lib().fbam_avgpool2x2(nv.ptr(x.contiguous()), nv.ptr(y), C.c_longlong(n), h // 2, w // 2, c, 0,
+        y = torch.empty(n, h // 2, w // 2, c, dtype=x.dtype, device=x.device)
+        nv.check(nv.lib(x).fbam_avgpool2x2(nv.ptr(x.contiguous()), nv.ptr(y), C.c_longlong(n), h // 2, w // 2, c, 0,
                                           nv.stream_ptr()), "fbam_avgpool2x2")
         ctx.shape = x.shape
         return y
@@ -641,15 +649,15 @@ class _AvgPool2x2(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         n, h, w, c = ctx.shape
-        dx = torch.zeros(ctx.shape, dtype=BF16, device=dy.device) if (h % 2 or w % 2) else \
-            torch.empty(ctx.shape, dtype=BF16, device=dy.device)
-        nv.check(nv.lib().fbam_avgpool2x2(nv.ptr(dy.contiguous()), nv.ptr(dx), C.c_longlong(n), h // 2, w // 2, c, 1,
+        dx = torch.zeros(ctx.shape, dtype=dy.dtype, device=dy.device) if (h % 2 or w % 2) else \
+            torch.empty(ctx.shape, dtype=dy.dtype, device=dy.device)
+        nv.check(nv.lib(dy).fbam_avgpool2x2(nv.ptr(dy.contiguous()), nv.ptr(dx), C.c_longlong(n), h // 2, w // 2, c, 1,
                                           nv.stream_ptr()), "fbam_avgpool2x2")
         return dx
 
 
 def avg_pool2x2_nhwc(x):
-    _need_bf16(x)
+    _need_elem(x)
     if x.shape[1] % 2 or x.shape[2] % 2:
         raise ValueError("2x2 pooling needs even height and width")
     return _AvgPool2x2.apply(x)
@@ -659,8 +667,8 @@ class _GlobalAvgPool(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x):
         n, h, w, c = x.shape
-        y = torch.empty(n, c, dtype=BF16, device=x.device)
-        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(x.contiguous()), nv.ptr(y), C.c_longlong(n), h * w, c, 0, None,
+        y = torch.empty(n, c, dtype=x.dtype, device=x.device)
+        nv.check(nv.lib(x).fbam_global_avgpool(nv.ptr(x.contiguous()), nv.ptr(y), C.c_longlong(n), h * w, c, 0, None,
                                               nv.stream_ptr()), "fbam_global_avgpool")
         ctx.shape = x.shape
         return y
@@ -668,14 +676,14 @@ class _GlobalAvgPool(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         n, h, w, c = ctx.shape
-        dx = torch.empty(ctx.shape, dtype=BF16, device=dy.device)
-        nv.check(nv.lib().fbam_global_avgpool(nv.ptr(dy.contiguous()), nv.ptr(dx), C.c_longlong(n), h * w, c, 1, None,
+        dx = torch.empty(ctx.shape, dtype=dy.dtype, device=dy.device)
+        nv.check(nv.lib(dy).fbam_global_avgpool(nv.ptr(dy.contiguous()), nv.ptr(dx), C.c_longlong(n), h * w, c, 1, None,
                                               nv.stream_ptr()), "fbam_global_avgpool")
         return dx
 
 
 def global_avg_pool_nhwc(x):
-    _need_bf16(x)
+    _need_elem(x)
     return _GlobalAvgPool.apply(x)
 
 
@@ -684,12 +692,12 @@ def global_avg_pool_nhwc(x):
 # =================================================================================================
 class _CellEmbed(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, cells, cp_embed, pos_embed, colour):
+    def forward(ctx, cells, cp_embed, pos_embed, colour, out_dtype):
         n, p, _ = cells.shape
         e = cp_embed.shape[1]
         cells = cells.contiguous()
-        out = debug.fresh((n, p, e), BF16, cells.device)
-        nv.check(nv.lib().fbam_cell_embed_fwd(nv.ptr(cells), nv.ptr(cp_embed), nv.ptr(pos_embed), nv.ptr(colour),
+        out = debug.fresh((n, p, e), out_dtype, cells.device)
+        nv.check(nv.lib(out_dtype).fbam_cell_embed_fwd(nv.ptr(cells), nv.ptr(cp_embed), nv.ptr(pos_embed), nv.ptr(colour),
                                               nv.ptr(out), C.c_longlong(n), p, e, cp_embed.shape[0],
                                               nv.stream_ptr()), "fbam_cell_embed_fwd")
         ctx.save_for_backward(cells)
@@ -703,18 +711,18 @@ class _CellEmbed(torch.autograd.Function):
         d_cp = torch.zeros(vocab, e, dtype=torch.float32, device=dout.device)
         d_pos = torch.zeros(p, e, dtype=torch.float32, device=dout.device)
         d_col = torch.zeros(6, e, dtype=torch.float32, device=dout.device)
-        nv.check(nv.lib().fbam_cell_embed_bwd(nv.ptr(cells), nv.ptr(dout.contiguous()), nv.ptr(d_cp), nv.ptr(d_pos),
+        nv.check(nv.lib(dout).fbam_cell_embed_bwd(nv.ptr(cells), nv.ptr(dout.contiguous()), nv.ptr(d_cp), nv.ptr(d_pos),
                                               nv.ptr(d_col), C.c_longlong(n), p, e, vocab, nv.stream_ptr()),
                  "fbam_cell_embed_bwd")
-        return None, d_cp, d_pos, d_col
+        return None, d_cp, d_pos, d_col, None
 
 
 def cell_embed(cells, cp_embed, pos_embed, colour, out_dtype):
-    if out_dtype != BF16:
-        raise TypeError("native cell embedding writes bf16")
+    if out_dtype not in nv.ELEM_DTYPES:
+        raise TypeError("native cell embedding writes bf16 or fp16")
     if pos_embed.shape[0] != cells.shape[1]:
         raise ValueError("position table must have one row per cell")
-    return _CellEmbed.apply(cells, cp_embed, pos_embed, colour)
+    return _CellEmbed.apply(cells, cp_embed.float(), pos_embed.float(), colour.float(), out_dtype)
 
 
 # =================================================================================================
@@ -746,24 +754,24 @@ class _LmHeadCe(torch.autograd.Function):
                 # The logits never reach HBM: the head GEMM's epilogue reduces each 128 x 128 tile half, still in
                 # tensor memory, to per-row (maximum, sum of exp) pairs and picks out the target logit; a small
                 # kernel merges the pairs into the rows' log-sum-exp and the loss; for the backward the same GEMM
-                # runs again and its epilogue turns the accumulators straight into bf16 scale·(softmax − onehot).
+                # runs again and its epilogue turns the accumulators straight into 16-bit scale·(softmax − onehot).
                 slots = 2 * ((vpad + 255) // 256)
                 partial = torch.empty(n, slots, 2, dtype=torch.float32, device=x.device)
                 tgt_logit = torch.zeros(n, dtype=torch.float32, device=x.device)      # targets outside the table: 0
                 lse = torch.empty(n, dtype=torch.float32, device=x.device)
                 gemm(xc, w_head, ce_stats=(partial, tgt_logit, tg, vocab))
-                nv.check(nv.lib().fbam_ce_combine(nv.ptr(partial), nv.ptr(tgt_logit), nv.ptr(lse), nv.ptr(loss),
+                nv.check(nv.lib(partial).fbam_ce_combine(nv.ptr(partial), nv.ptr(tgt_logit), nv.ptr(lse), nv.ptr(loss),
                                                   C.c_longlong(n), slots, C.c_float(scale), nv.stream_ptr()),
                          "fbam_ce_combine")
                 dlogits = None
                 if need_grad:
-                    dlogits = torch.empty(n, vpad, dtype=BF16, device=x.device)
+                    dlogits = torch.empty(n, vpad, dtype=x.dtype, device=x.device)
                     with flops.not_useful():                             # the logits are computed a second time
                         gemm(xc, w_head, out=dlogits, ce_grad=(lse, tg, vocab, scale))
             else:
                 logits = gemm(xc, w_head, out_dtype=torch.float32)       # (chunk, vpad) fp32 accumulators
-                dlogits = torch.empty(n, vpad, dtype=BF16, device=x.device) if need_grad else None
-                nv.check(nv.lib().fbam_ce_fwd_bwd_f32(nv.ptr(logits), nv.ptr(dlogits), nv.ptr(tg), nv.ptr(loss),
+                dlogits = torch.empty(n, vpad, dtype=x.dtype, device=x.device) if need_grad else None
+                nv.check(nv.lib(x).fbam_ce_fwd_bwd_f32(nv.ptr(logits), nv.ptr(dlogits), nv.ptr(tg), nv.ptr(loss),
                                                       C.c_longlong(n), vocab, vpad, C.c_float(scale),
                                                       nv.stream_ptr()), "fbam_ce_fwd_bwd_f32")
             if need_grad:                                                # dlogits = scale·(softmax − onehot)
@@ -775,11 +783,11 @@ class _LmHeadCe(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dloss):
         dx, dw = ctx.saved_tensors
-        return (dx * dloss.to(dx.dtype)), (dw * dloss).to(BF16), None, None, None
+        return (dx * dloss.to(dx.dtype)), (dw * dloss).to(dx.dtype), None, None, None
 
 
 def lm_head_ce(x, w_head, targets, vocab, scale):
-    _need_bf16(x, w_head)
+    _need_elem(x, w_head)
     return _LmHeadCe.apply(x.contiguous(), w_head, targets, vocab, scale)
 
 
@@ -790,11 +798,13 @@ def adamw_flat(param, grad, m, v, master, lo, hi, lr, b1, b2, eps, wd, bc1, bc2,
     n = hi - lo
     if n <= 0:
         return
-    is_bf16 = param.dtype == BF16
-    if not is_bf16 and param.dtype != torch.float32:
-        raise TypeError("fused AdamW handles bf16 and fp32 parameters")
-    nv.check(nv.lib().fbam_adamw(nv.ptr(param[lo:hi]), nv.ptr(grad[lo:hi]), nv.ptr(m[lo:hi]), nv.ptr(v[lo:hi]),
-                                 nv.ptr(None if master is None else master[lo:hi]), C.c_longlong(n), int(is_bf16),
+    is_elem = param.dtype in nv.ELEM_DTYPES
+    if not is_elem and param.dtype != torch.float32:
+        raise TypeError("fused AdamW handles bf16, fp16 and fp32 parameters")
+    if grad.dtype != param.dtype:
+        raise TypeError("fused AdamW needs gradients of the parameters' type")
+    nv.check(nv.lib(param).fbam_adamw(nv.ptr(param[lo:hi]), nv.ptr(grad[lo:hi]), nv.ptr(m[lo:hi]), nv.ptr(v[lo:hi]),
+                                 nv.ptr(None if master is None else master[lo:hi]), C.c_longlong(n), int(is_elem),
                                  C.c_float(lr), C.c_float(b1), C.c_float(b2), C.c_float(eps), C.c_float(wd),
                                  C.c_float(bc1), C.c_float(bc2), C.c_float(grad_scale), nv.stream_ptr()), "fbam_adamw")
 

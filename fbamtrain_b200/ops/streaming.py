@@ -26,15 +26,15 @@ from ..utils import flops
 
 from ..utils.stream_io import TensorStreamIterator, TensorStreamPopulator
 from . import native as nv
-from .native_ops import BF16, _colsum, gemm, gemm_nn, gemm_tn
+from .native_ops import _colsum, gemm, gemm_nn, gemm_tn
 
 
 def _fwd_chunk(x2, wi, wh, bias, h_state, c_state, t_len, b, h, dev, counter):
     gates = gemm(x2, wi, bias=bias, out_dtype=torch.float32).view(t_len, b, 4 * h)
-    y = torch.empty(t_len, b, h, dtype=BF16, device=dev)
+    y = torch.empty(t_len, b, h, dtype=wh.dtype, device=dev)
     c_all = torch.empty(t_len, b, h, dtype=torch.float32, device=dev)
-    hbuf = torch.empty(2 * 8 * h, dtype=BF16, device=dev)
-    nv.check(nv.lib().fbam_lstm_fwd_ex(nv.ptr(gates), nv.ptr(wh), nv.ptr(h_state), nv.ptr(c_state), nv.ptr(y),
+    hbuf = torch.empty(2 * 8 * h, dtype=wh.dtype, device=dev)
+    nv.check(nv.lib(wh).fbam_lstm_fwd_ex(nv.ptr(gates), nv.ptr(wh), nv.ptr(h_state), nv.ptr(c_state), nv.ptr(y),
                                        nv.ptr(c_all), nv.ptr(hbuf), nv.ptr(counter), nv.ptr(nv.status_word(dev)),
                                        t_len, b, h, 1, nv.stream_ptr()), "fbam_lstm_fwd")
     return gates, y, c_all
@@ -46,7 +46,8 @@ class _StreamingLstmHeadCe(torch.autograd.Function):
         t_total, b, i_dim = x.shape
         h = w_hh.shape[1]
         dev = w_ih.device
-        wi, wh = w_ih.to(BF16), w_hh.to(BF16)
+        elem = w_head.dtype                       # the model's 16-bit compute type
+        wi, wh = w_ih.to(elem), w_hh.to(elem)
         bias = (b_ih.float() + b_hh.float()).contiguous()
         counter = torch.zeros(1, dtype=torch.int32, device=dev)
         h_state = h0.float().unsqueeze(0).expand(b, h).contiguous()
@@ -54,7 +55,7 @@ class _StreamingLstmHeadCe(torch.autograd.Function):
         loss = torch.zeros(1, dtype=torch.float32, device=dev)
         dw_head = torch.zeros(w_head.shape, dtype=torch.float32, device=dev)
         vpad = w_head.shape[0]
-        dy_store = torch.empty((t_total, b, h), dtype=BF16, device="cpu" if offload else dev,
+        dy_store = torch.empty((t_total, b, h), dtype=elem, device="cpu" if offload else dev,
                                pin_memory=offload and dev.type == "cuda")
         populator = TensorStreamPopulator(dy_store) if offload else None
         boundary: List[tuple] = []
@@ -63,7 +64,7 @@ class _StreamingLstmHeadCe(torch.autograd.Function):
         for lo, hi, x_c in TensorStreamIterator(x, chunk, dev):
             n = hi - lo
             boundary.append((h_state, c_state))
-            x2 = x_c.to(BF16).reshape(n * b, i_dim)
+            x2 = x_c.to(elem).reshape(n * b, i_dim)
             _, y, c_all = _fwd_chunk(x2, wi, wh, bias, h_state, c_state, n, b, h, dev, counter)
             h_state, c_state = y[-1].float(), c_all[-1].clone()
             # per-chunk hook on its own stream: LM head + CE forward/backward for this chunk
@@ -71,7 +72,7 @@ class _StreamingLstmHeadCe(torch.autograd.Function):
             with torch.cuda.stream(ce_stream):
                 y2 = y.view(n * b, h)
                 logits = gemm(y2, w_head)
-                nv.check(nv.lib().fbam_ce_fwd_bwd(nv.ptr(logits), nv.ptr(targets[lo:hi].reshape(-1).contiguous()),
+                nv.check(nv.lib(logits).fbam_ce_fwd_bwd(nv.ptr(logits), nv.ptr(targets[lo:hi].reshape(-1).contiguous()),
                                                   nv.ptr(loss), C.c_longlong(n * b), vocab, vpad, C.c_float(scale), 1,
                                                   nv.stream_ptr()), "fbam_ce_fwd_bwd")
                 dy_c = gemm_nn(logits, w_head).view(n, b, h)
@@ -101,7 +102,7 @@ class _StreamingLstmHeadCe(torch.autograd.Function):
         dw_ih = torch.zeros(4 * h, i_dim, dtype=torch.float32, device=dev)
         dw_hh = torch.zeros(4 * h, h, dtype=torch.float32, device=dev)
         db = torch.zeros(4 * h, dtype=torch.float32, device=dev)
-        dx = torch.empty((t_total, b, i_dim), dtype=BF16, device="cpu" if x.device.type == "cpu" and offload else dev,
+        dx = torch.empty((t_total, b, i_dim), dtype=wi.dtype, device="cpu" if x.device.type == "cpu" and offload else dev,
                          pin_memory=offload and x.device.type == "cpu" and dev.type == "cuda")
         dx_pop = TensorStreamPopulator(dx) if not dx.is_cuda else None
         dh_carry = dc_carry = None
@@ -111,13 +112,13 @@ class _StreamingLstmHeadCe(torch.autograd.Function):
             _, _, dy_c = next(dy_iter)
             n = hi - lo
             h_start, c_start = ctx.boundary[k]
-            x2 = x_c.to(BF16).reshape(n * b, i_dim)
+            x2 = x_c.to(wi.dtype).reshape(n * b, i_dim)
             with flops.not_useful():                  # recomputation of what a resident run would have kept
                 gates, y, c_all = _fwd_chunk(x2, wi, wh, bias, h_start, c_start, n, b, h, dev, counter)
-            dgates = torch.empty(n, b, 4 * h, dtype=BF16, device=dev)
+            dgates = torch.empty(n, b, 4 * h, dtype=wi.dtype, device=dev)
             dh0 = torch.empty(b, h, dtype=torch.float32, device=dev)
             dc0 = torch.empty(b, h, dtype=torch.float32, device=dev)
-            nv.check(nv.lib().fbam_lstm_bwd_ex(nv.ptr(gates), nv.ptr(c_all), nv.ptr(c_start), nv.ptr(dy_c.contiguous()),
+            nv.check(nv.lib(wh_t).fbam_lstm_bwd_ex(nv.ptr(gates), nv.ptr(c_all), nv.ptr(c_start), nv.ptr(dy_c.contiguous()),
                                                nv.ptr(wh_t), nv.ptr(dgates), nv.ptr(dh0), nv.ptr(dc0),
                                                nv.ptr(dh_carry), nv.ptr(dc_carry), nv.ptr(counter),
                                                nv.ptr(nv.status_word(dev)), n, b, h, 1, nv.stream_ptr()),
@@ -130,7 +131,7 @@ class _StreamingLstmHeadCe(torch.autograd.Function):
             else:
                 dx[lo:hi].copy_(dx_c)
             gemm_tn(dg2, x2, out=dw_ih, accumulate=nv.GEMM_ACC_RMW)
-            h_prev = torch.cat([h_start.to(BF16).view(1, b, h), y[:-1]], 0).reshape(n * b, h)
+            h_prev = torch.cat([h_start.to(y.dtype).view(1, b, h), y[:-1]], 0).reshape(n * b, h)
             gemm_tn(dg2, h_prev, out=dw_hh, accumulate=nv.GEMM_ACC_RMW)
             db += _colsum(dg2)
         if dx_pop is not None:

@@ -79,7 +79,7 @@ class AdamwOptimizer(Optimizer):
                 lo, hi = rank * per, (rank + 1) * per
             if g.data.is_cuda:
                 from ..ops import dispatch
-                if dispatch.get_backend() == "auto" and g.data.dtype in (torch.bfloat16, torch.float32):
+                if dispatch.get_backend() == "auto" and g.data.dtype in (torch.bfloat16, torch.float16, torch.float32):
                     from ..ops.native_ops import adamw_flat
                     adamw_flat(g.data, g.grad, fs["m"], fs["v"], fs.get("master"), lo, hi, self.lr, self.beta1,
                                self.beta2, self.eps, self.weight_decay, bc1, bc2, grad_scale)

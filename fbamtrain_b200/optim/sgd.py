@@ -42,8 +42,8 @@ class SgdOptimizer(Optimizer):
             self._publish(name, p)
 
     def _native_step(self, name: str, p: torch.Tensor) -> bool:
-        """One fused kernel per tensor on a GPU (bf16 parameters with an fp32 master, or fp32 parameters)."""
-        if not p.is_cuda or p.dtype not in (torch.bfloat16, torch.float32) or p.grad.dtype != p.dtype:
+        """One fused kernel per tensor on a GPU (bf16 / fp16 parameters with an fp32 master, or fp32 parameters)."""
+        if not p.is_cuda or p.dtype not in (torch.bfloat16, torch.float16, torch.float32) or p.grad.dtype != p.dtype:
             return False
         from ..ops import dispatch
         if dispatch.get_backend() != "auto" or not p.is_contiguous() or not p.grad.is_contiguous():
@@ -52,10 +52,10 @@ class SgdOptimizer(Optimizer):
         from ..ops import native as nv
         st = self.state[name]
         master = st.get("master")
-        if p.dtype == torch.bfloat16 and master is None:
+        if p.dtype != torch.float32 and master is None:
             return False
-        nv.check(nv.lib().fbam_sgd(nv.ptr(p.data), nv.ptr(p.grad), nv.ptr(st.get("velocity")), nv.ptr(master),
-                                   C.c_longlong(p.numel()), int(p.dtype == torch.bfloat16), C.c_float(self.lr),
+        nv.check(nv.lib(p).fbam_sgd(nv.ptr(p.data), nv.ptr(p.grad), nv.ptr(st.get("velocity")), nv.ptr(master),
+                                   C.c_longlong(p.numel()), int(p.dtype != torch.float32), C.c_float(self.lr),
                                    C.c_float(self.momentum), int(self.nesterov), C.c_float(self.weight_decay),
                                    nv.stream_ptr()), "fbam_sgd")
         return True

@@ -244,15 +244,15 @@ class DataParallel:
             g, off = by_param[name]
             wg, wp = self._windows[g.name]
             n = p.numel()
-            is_bf16 = g.dtype == torch.bfloat16
-            esize = 2 if is_bf16 else 4
-            if (not is_bf16 and g.dtype != torch.float32) or n % (16 // esize) != 0:
-                raise ValueError(f"fused Muon needs bf16/fp32 matrices whose size is a multiple of 16 bytes ('{name}')")
+            is_elem = g.dtype in nv.ELEM_DTYPES
+            esize = 2 if is_elem else 4
+            if (not is_elem and g.dtype != torch.float32) or n % (16 // esize) != 0:
+                raise ValueError(f"fused Muon needs bf16/fp16/fp32 matrices whose size is a multiple of 16 bytes ('{name}')")
             buf = muon.state[name]["momentum"].view(-1)
-            u = torch.empty(n, dtype=torch.bfloat16, device=dev)
+            u = torch.empty(n, dtype=g.dtype if is_elem else torch.bfloat16, device=dev)
             sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
-            nv.check(nv.lib().fbam_reduce_pull(wg.c_ptrs, nv.ptr(buf), nv.ptr(u), nv.ptr(sumsq), C.c_longlong(off),
-                                               C.c_longlong(off + n), int(is_bf16), C.c_float(muon.momentum),
+            nv.check(nv.lib(g.dtype).fbam_reduce_pull(wg.c_ptrs, nv.ptr(buf), nv.ptr(u), nv.ptr(sumsq), C.c_longlong(off),
+                                               C.c_longlong(off + n), int(is_elem), C.c_float(muon.momentum),
                                                int(muon.nesterov), C.c_float(self.grad_scale), self.world_size,
                                                nv.stream_ptr()),
                      "fbam_reduce_pull")
@@ -303,14 +303,14 @@ class DataParallel:
         per = g.numel // self.world_size
         lo, hi = self.rank * per, (self.rank + 1) * per
         epoch = self.peers.next_epoch()
-        is_bf16 = g.dtype == torch.bfloat16
-        if not is_bf16 and g.dtype != torch.float32:
-            raise TypeError("fused buckets are bf16 or fp32")
+        is_elem = g.dtype in nv.ELEM_DTYPES
+        if not is_elem and g.dtype != torch.float32:
+            raise TypeError("fused buckets are bf16, fp16 or fp32")
         master = fs.get("master")
-        code = nv.lib().fbam_rs_adamw_ag(
+        code = nv.lib(g.dtype).fbam_rs_adamw_ag(
             wg.c_ptrs, wp.c_ptrs, self.peers.flags.c_ptrs,
             C.c_void_p(wg.multicast_ptr), C.c_void_p(wp.multicast_ptr),
-            nv.ptr(fs["m"]), nv.ptr(fs["v"]), nv.ptr(master), C.c_longlong(lo), C.c_longlong(hi), int(is_bf16),
+            nv.ptr(fs["m"]), nv.ptr(fs["v"]), nv.ptr(master), C.c_longlong(lo), C.c_longlong(hi), int(is_elem),
             C.c_float(opt.lr), C.c_float(opt.beta1), C.c_float(opt.beta2), C.c_float(opt.eps),
             C.c_float(opt.weight_decay), C.c_float(bc1), C.c_float(bc2), C.c_float(self.grad_scale), self.rank,
             self.world_size,

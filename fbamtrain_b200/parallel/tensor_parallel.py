@@ -119,26 +119,26 @@ class TpContext:
         """``reduce_scatter_rows(h · wᵀ)``: the GEMM epilogue stores every bf16 partial tile straight into this
         rank's slot of the buffer of the rank that owns the rows (plain vector stores over NVLink, remote owners
         first and in a different order on every rank so that no owner is written by two peers at once); one more
-        kernel waits for all peers' tiles and sums the slots.  Returns this rank's bf16 rows."""
+        kernel waits for all peers' tiles and sums the slots.  Returns this rank's rows in the operands' 16-bit type."""
         from ..ops import native as nv
         from ..ops import native_ops as no
         m, n = h.shape[0], w.shape[0]
         rows = m // self.world
         self._rs_round = getattr(self, "_rs_round", 0) + 1
         # two buffers in turn: a peer may still be summing the previous call's slots while this call's tiles arrive
-        win = self._window(f"rs{self._rs_round & 1}", self.world * rows * n, torch.bfloat16)
+        win = self._window(f"rs{self._rs_round & 1}", self.world * rows * n, h.dtype)
         if self.rs_mode == "chunked":
             return self._gemm_rs_chunked(h, w, win, rows, n)
         pair = n >= 256 and n % 16 == 0 and ((m + 255) // 256) * ((n + 255) // 256) >= 148
         tile_rows = 256 if pair else 128
         first = ((self.rank + 1) % self.world) * rows
         rotate = first // tile_rows if rows % tile_rows == 0 else 0
-        no.gemm(h, w, out=_RsShape((m, n), torch.bfloat16, n, win.local.data_ptr()), rs_out=list(win.ptrs),
+        no.gemm(h, w, out=_RsShape((m, n), h.dtype, n, win.local.data_ptr()), rs_out=list(win.ptrs),
                 rs_rows_per_rank=rows, rs_slot=self.rank, tile_m_rotate=rotate, two_cta=pair, bm=tile_rows,
                 rs_row_stores=self.rs_row_stores)
-        out = torch.empty(rows, n, dtype=torch.bfloat16, device=h.device)
+        out = torch.empty(rows, n, dtype=h.dtype, device=h.device)
         epoch = self.peers.next_epoch()
-        nv.check(nv.lib().fbam_reduce_slots(nv.ptr(win.local), nv.ptr(out), C.c_longlong(rows * n), self.world,
+        nv.check(nv.lib(h).fbam_reduce_slots(nv.ptr(win.local), nv.ptr(out), C.c_longlong(rows * n), self.world,
                                             self.peers.flags.c_ptrs, self.rank, 5, C.c_uint(epoch),
                                             C.c_uint(self.spin_limit), nv.ptr(nv.status_word(self.device)),
                                             nv.stream_ptr()), "fbam_reduce_slots")
@@ -171,9 +171,9 @@ class TpContext:
                                               C.c_void_p(self._copy_stream.cuda_stream)), "fbam_copy_async")
             part.record_stream(self._copy_stream)
         main.wait_stream(self._copy_stream)
-        out = torch.empty(rows, n, dtype=torch.bfloat16, device=h.device)
+        out = torch.empty(rows, n, dtype=h.dtype, device=h.device)
         epoch = self.peers.next_epoch()
-        nv.check(nv.lib().fbam_reduce_slots(nv.ptr(win.local), nv.ptr(out), C.c_longlong(slot_elems), self.world,
+        nv.check(nv.lib(h).fbam_reduce_slots(nv.ptr(win.local), nv.ptr(out), C.c_longlong(slot_elems), self.world,
                                             self.peers.flags.c_ptrs, self.rank, 5, C.c_uint(epoch),
                                             C.c_uint(self.spin_limit), nv.ptr(nv.status_word(self.device)),
                                             nv.stream_ptr()), "fbam_reduce_slots")

@@ -21,7 +21,7 @@ from typing import Dict, Iterator, List, Optional, Tuple
 @dataclass
 class PlanEntry:
     index: int
-    name: str            # native entry point, e.g. fbam_gemm_bf16
+    name: str            # native entry point, e.g. fbam_gemm
     phase: str           # innermost phase range open on the launching thread ("" outside any)
     backward: bool       # launched from an autograd worker thread
     flops: float = 0.0

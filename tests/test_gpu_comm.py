@@ -19,7 +19,7 @@ def _nv():
     return native
 
 
-@pytest.mark.parametrize("dtype", [BF, torch.float32])
+@pytest.mark.parametrize("dtype", [BF, torch.float16, torch.float32])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_rs_adamw_ag_emulated_ranks(dtype, world):
     from fbamtrain_b200.parallel.peer_window import LocalPeerGroup
@@ -41,7 +41,7 @@ def test_rs_adamw_ag_emulated_ranks(dtype, world):
     v = [torch.rand(n, device=DEV) * 0.01 for _ in range(world)]
     m[1:] = [m[0].clone() for _ in range(world - 1)]
     v[1:] = [v[0].clone() for _ in range(world - 1)]
-    masters = [master0.to(dtype).float().clone() if dtype == BF else None for _ in range(world)]
+    masters = [master0.to(dtype).float().clone() if dtype != torch.float32 else None for _ in range(world)]
     em, ev = m[0].clone(), v[0].clone()
     ew = master0.to(dtype).float().clone()
     lr, b1, b2, eps, wd, step = 1e-2, 0.9, 0.99, 1e-8, 0.1, 2
@@ -49,9 +49,9 @@ def test_rs_adamw_ag_emulated_ranks(dtype, world):
     per = n // world
     status = nv.status_word(torch.device(DEV))
     for r in range(world):
-        code = nv.lib().fbam_rs_adamw_ag(
+        code = nv.lib(dtype).fbam_rs_adamw_ag(
             grads[r].c_ptrs, params[r].c_ptrs, None, None, None, nv.ptr(m[r]), nv.ptr(v[r]), nv.ptr(masters[r]),
-            C.c_longlong(r * per), C.c_longlong((r + 1) * per), int(dtype == BF), C.c_float(lr), C.c_float(b1),
+            C.c_longlong(r * per), C.c_longlong((r + 1) * per), int(dtype != torch.float32), C.c_float(lr), C.c_float(b1),
             C.c_float(b2), C.c_float(eps), C.c_float(wd), C.c_float(bc1), C.c_float(bc2), C.c_float(1.0), r, world,
             C.c_uint(1), 0, C.c_uint(1000), nv.ptr(status), nv.ptr(peers.arrive), 0, nv.stream_ptr())
         nv.check(code, "fbam_rs_adamw_ag")
@@ -62,7 +62,7 @@ def test_rs_adamw_ag_emulated_ranks(dtype, world):
     ew.addcdiv_(em / bc1, (ev / bc2).sqrt() + eps, value=-lr)
     expect = ew.to(dtype)
     for r in range(world):
-        assert torch.allclose(params[r].local.float(), expect.float(), atol=1e-5 if dtype != BF else 8e-3), r
+        assert torch.allclose(params[r].local.float(), expect.float(), atol=1e-5 if dtype == torch.float32 else 8e-3), r
         assert torch.equal(params[r].local, params[0].local)
         sl = slice(r * per, (r + 1) * per)
         assert torch.allclose(m[r][sl], em[sl], atol=1e-6) and torch.allclose(v[r][sl], ev[sl], atol=1e-6)

@@ -38,7 +38,7 @@ def test_colour_features_kernel(rows, cols, stride, pad, dil):
     from fbamtrain_b200.ops import embconv
     cells = _cells(37, rows, cols, 50, 1)
     taps = embconv.tap_cells(rows, cols, stride, pad, dil, DEV)
-    got = embconv.features_native(cells, rows, cols, stride, pad, dil)
+    got = embconv.features_native(cells, rows, cols, stride, pad, dil, BF)
     want = embconv.features_torch(cells, taps, BF)
     assert torch.equal(got, want)
 

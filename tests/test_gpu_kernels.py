@@ -550,11 +550,14 @@ def test_device_fingerprint_detects_single_bit_changes():
 
 
 @pytest.mark.parametrize("dtype", ["fp16", "fp32"])
-def test_non_bf16_models_train_on_the_library_path(dtype):
-    """fp16 (the reference's default dtype) and fp32 configurations run on a GPU through the PyTorch definitions."""
+def test_fp16_models_train_on_the_native_kernels_and_fp32_on_the_library_path(dtype):
+    """fp16 (the reference's default dtype, ``src/config.cpp:43-51``) runs on the half-precision build of the sm_100a
+    kernels; fp32 configurations run on a GPU through the PyTorch definitions."""
     from fbamtrain_b200 import RunConfiguration, Trainer, presets
     from fbamtrain_b200.data import SyntheticBatchSource
+    from fbamtrain_b200.ops import dispatch
     d = presets.tiny(dtype)
+    d["model_config"].update({"cell_embed_dim": 64, "downsample_channels": [64], "n_embed": 64})
     cfg = RunConfiguration.from_json(d)
     src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=3, pin=False)
     cells, tg = src.next_batch(2, cfg.train_sequence_length)
@@ -562,6 +565,8 @@ def test_non_bf16_models_train_on_the_library_path(dtype):
     losses = [float(tr.train_step(cells, tg)) for _ in range(4)]
     tr.close()
     assert all(math.isfinite(x) for x in losses) and losses[-1] < losses[0]
+    expected = "native" if dtype == "fp16" else "torch"
+    assert dispatch.last_backend("gemm") == expected and dispatch.last_backend("conv2d") == expected
 
 
 def test_frame_head_recompute_gives_the_same_gradients():
@@ -591,7 +596,7 @@ def test_frame_head_recompute_gives_the_same_gradients():
 
 
 def test_expected_backends_are_chosen_on_gpu():
-    """bf16 CUDA tensors must reach the sm_100a kernels (no silent library fallback), other dtypes the library."""
+    """16-bit CUDA tensors must reach the sm_100a kernels (no silent library fallback), fp32 the library."""
     _nops()
     from fbamtrain_b200 import ops
     from fbamtrain_b200.ops import dispatch

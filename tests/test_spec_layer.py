@@ -268,14 +268,14 @@ def test_step_plan_records_launches_phases_and_flops():
     nv.check(0, "fbam_before")                                         # outside a recording: no effect
     with plan.record() as p:
         with gputx_range("fbamtrain::frame_head_fwd"):
-            nv.check(0, "fbam_gemm_bf16")
+            nv.check(0, "fbam_gemm")
             flops.add(2e9)
             with flops.not_useful():
-                nv.check(0, "fbam_conv_bf16")
+                nv.check(0, "fbam_conv")
                 flops.add(1e9)
 
         def backward_thread():
-            nv.check(0, "fbam_gemm_bf16")
+            nv.check(0, "fbam_gemm")
             flops.add(4e9)
         t = threading.Thread(target=backward_thread)
         t.start()
@@ -286,12 +286,12 @@ def test_step_plan_records_launches_phases_and_flops():
                 pass
     assert plan.active() is None
     assert [(e.name, e.phase, e.backward, e.flops, e.useful_flops) for e in p.entries] == [
-        ("fbam_gemm_bf16", "fbamtrain::frame_head_fwd", False, 2e9, 2e9),
-        ("fbam_conv_bf16", "fbamtrain::frame_head_fwd", False, 1e9, 0.0),
-        ("fbam_gemm_bf16", "", True, 4e9, 4e9),
+        ("fbam_gemm", "fbamtrain::frame_head_fwd", False, 2e9, 2e9),
+        ("fbam_conv", "fbamtrain::frame_head_fwd", False, 1e9, 0.0),
+        ("fbam_gemm", "", True, 4e9, 4e9),
         ("fbam_adamw", "", False, 0.0, 0.0)]
     assert p.total_flops() == 7e9 and p.total_useful_flops() == 6e9
-    assert p.by("name")["fbam_gemm_bf16"] == (2, 6e9)
+    assert p.by("name")["fbam_gemm"] == (2, 6e9)
     text = p.listing()
     assert text.startswith("# 4 launches") and "(recompute)" in text and "fbamtrain::frame_head_fwd" in text
 
