@@ -142,6 +142,7 @@ def run_ours(args) -> dict:
 
     micro = args.micro_batch
     cfg = RunConfiguration.from_json(presets.PRESETS[args.model](micro, world))
+    cfg.model_config.dtype = args.dtype
     if args.seq:
         cfg.train_sequence_length = args.seq
     seq = cfg.train_sequence_length
@@ -231,7 +232,7 @@ def run_ours(args) -> dict:
         "metric": "train frames/sec", "value": value, "unit": "frames/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": (value / BASELINE_FRAMES_PER_SEC) if BASELINE_FRAMES_PER_SEC else None,
-        "dtype": "bf16", "data": "synthetic seeded frames/actions, random-init weights",
+        "dtype": args.dtype, "data": "synthetic seeded frames/actions, random-init weights",
         "impl": "ours",
         "mfu": flops / step_s / peak,
         "mfu_of_measured_sustained_cublas": flops / step_s / (meas["bf16_tflops_sustained"] * 1e12),
@@ -273,6 +274,8 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--frame-chunk", type=int, default=1024)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"],
+                    help="model / compute dtype (fp32 accumulation in both; the headline number is bf16)")
     ap.add_argument("--dp-mode", default="fused", choices=["allreduce", "zero1", "fused"])
     args = ap.parse_args()
     if args.warmup < 3:

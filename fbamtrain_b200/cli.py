@@ -11,7 +11,8 @@ Role resolution: with a parallel configuration whose ``ddp_parallel.use_ddp_para
 is the data-parallel rank and ``--ddp-world-size`` the world size; transport ``ccl`` rendezvouses at
 ``ccl_rendezvous`` and reduces gradients as ``grad_reduce`` says (all-reduce, ZeRO-1 or the fused peer-memory
 kernels); transport ``ftccl`` joins the membership master at ``ftccl_master``.  ``frame_head_parallel`` maps to
-the two-stage pipeline over ``--world-size`` ranks.  Under ``torch.distributed.run`` the RANK / WORLD_SIZE
+the two-stage pipeline over ``--world-size`` ranks; together with transport ``ftccl`` every pipeline is a job of its
+own that joins the membership master (``--replica-id`` tells pipelines started by hand apart).  Under ``torch.distributed.run`` the RANK / WORLD_SIZE
 environment takes the place of the flags.
 """
 from __future__ import annotations
@@ -35,6 +36,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--worker_id", "--worker-id", type=int, default=None)
     ap.add_argument("--world-size", type=int, default=1)
     ap.add_argument("--ddp-world-size", type=int, default=1)
+    ap.add_argument("--replica-id", type=int, default=None,
+                    help="frame_head_parallel with transport ftccl, processes started by hand: which pipeline this "
+                         "process belongs to (its pipeline rendezvouses at the configured port + this number)")
     ap.add_argument("--validation-dump", action="store_true")
     ap.add_argument("--validation-dump-file", default="validation_dump.safetensors")
     ap.add_argument("--validation-dump-steps", type=int, default=1)
@@ -72,16 +76,28 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
     from .parallel import rendezvous
     from .parallel.pipeline import PipelineLayout, PipelineTrainer
     env_rank = os.environ.get("RANK")
+    ddp = par.ddp_parallel
+    dynamic = ddp.use_ddp_parallel and ddp.transport == "ftccl"
+    if dynamic:
+        # pipelines come and go: ranks may vanish while their memory is mapped by peers, so nothing in this job binds
+        # memory to NVLink multicast objects
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     if env_rank is not None:
         rank, world = int(env_rank), int(os.environ["WORLD_SIZE"])
         kwargs = {"device_id": device} if device.type == "cuda" else {}
         dist.init_process_group("nccl" if device.type == "cuda" else "gloo", **kwargs)
+    elif dynamic:
+        # every pipeline is a job of its own: --world-size ranks, --worker_id counts inside the pipeline
+        rank, world = (args.worker_id or 0), args.world_size
+        ep = par.frame_head_parallel.ccl_rendezvous
+        rendezvous.perform_ccl_rendezvous(ep.ip, ep.port + (args.replica_id or 0), rank, world, device)
     else:
         # --world-size ranks per pipeline, --ddp-world-size pipelines side by side; --worker_id counts over all
         rank, world = (args.worker_id or 0), args.world_size * max(1, args.ddp_world_size)
         ep = par.frame_head_parallel.ccl_rendezvous
         rendezvous.perform_ccl_rendezvous(ep.ip, ep.port, rank, world, device)
-    replicas = max(1, args.ddp_world_size)
+    replicas = 1 if dynamic else max(1, args.ddp_world_size)
     if world % replicas or (world // replicas) % 2:
         LOG("FATAL", f"{world} ranks do not split into {replicas} pipelines of an even number of ranks")
     per = world // replicas
@@ -94,7 +110,16 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
         vocab = len(Tokenizer.from_file(os.path.join(os.path.dirname(os.path.abspath(args.config)),
                                                      cfg.tokenizer_file_path)))
     fused_tp = device.type == "cuda" and per // 2 > 1        # peer-memory kernels need at least two TP ranks
-    trainer = PipelineTrainer(cfg, device, vocab, tp_transport="fused" if fused_tp else "nccl", replicas=replicas)
+    ft = None
+    if dynamic:
+        # Data parallelism over pipelines with dynamic membership: this process group is one pipeline; its leader
+        # talks to the membership master, same-position ranks of the pipelines that are present exchange gradients.
+        # A pipeline started while the job runs receives the state from the others (the highest revision wins).
+        from .parallel.ft_pipeline import FaultTolerantPipelineReplicas
+        ft = FaultTolerantPipelineReplicas(ddp.ftccl_master.ip, ddp.ftccl_master.port, device,
+                                           expected_replicas=max(1, args.ddp_world_size), min_replicas=1)
+    trainer = PipelineTrainer(cfg, device, vocab, tp_transport="fused" if fused_tp else "nccl", replicas=replicas,
+                              ft=ft)
     working_dir = os.path.dirname(os.path.abspath(args.config))
     rec_dir = cfg.train_data_config.recordings_directory_path
     if rec_dir and not args.synthetic:
@@ -168,6 +193,8 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
         iterator.close()
     if hasattr(next_batch, "close"):
         next_batch.close()
+    if ft is not None:
+        ft.leave()               # orderly departure: the remaining pipelines re-form their groups at the next gate
     dist.destroy_process_group()
     return 0
 
@@ -206,9 +233,6 @@ def main(argv=None) -> int:
 
     fhp = par.frame_head_parallel if par is not None else None
     if fhp is not None and fhp.use_frame_head_parallel:
-        if par.ddp_parallel.use_ddp_parallel and par.ddp_parallel.transport == "ftccl":
-            LOG("WARN", "data parallelism over pipelines runs on static process groups; the fault-tolerant transport "
-                        "(dynamic membership) applies to plain data parallelism")
         return _run_pipeline(cfg, par, args, device)
 
     dp = None

@@ -18,6 +18,11 @@ the same surface on top of plain TCP (control plane) and ``torch.distributed`` (
 Failures are detected on the host — a missed heartbeat at the master, or an exception from a collective — and
 every device-side wait in the fused kernels is bounded, so a lost peer costs a dropped step, never a hung GPU.
 ``FtPeer.on_topology_change`` callbacks let owners of peer-memory windows rebuild them for the new group.
+
+A peer normally owns the process's default ``torch.distributed`` group (one group per epoch).  A process that
+already has a static default group (the ranks of one pipeline) keeps it: its leader only votes
+(:meth:`FtPeer.vote_topology`) and every rank builds a :class:`ScopedGroup` — a stand-alone communicator over the
+epoch's bootstrap store — for its own position (``parallel/ft_pipeline.py``).
 """
 from __future__ import annotations
 
@@ -428,10 +433,125 @@ def tensor_hashes(tensors: Sequence[torch.Tensor]) -> List[str]:
     return out
 
 
+class _DefaultGroupComm:
+    """The process's default ``torch.distributed`` group behind the small interface the shared-state exchange needs."""
+
+    def __init__(self, rank: int, world_size: int):
+        self.rank, self.world_size = rank, world_size
+
+    def all_gather_object(self, obj) -> list:
+        out: List[Optional[object]] = [None] * self.world_size
+        dist.all_gather_object(out, obj)
+        return out
+
+    def broadcast(self, tensor: torch.Tensor, src: int) -> None:
+        dist.broadcast(tensor, src=src)
+
+
+class ScopedGroup:
+    """A communicator of its own, next to whatever default group the process has: the members rendezvous through a
+    TCP store at a known address (one member hosts it) under a prefix that names the group.  Gloo on CPU tensors,
+    NCCL on CUDA tensors.  Used for the same-position ranks of pipelines that come and go
+    (``parallel/ft_pipeline.py``); torn down and rebuilt at every topology epoch."""
+
+    def __init__(self, store_ip: str, store_port: int, host_store: bool, prefix: str, rank: int, world_size: int,
+                 device: torch.device, timeout_s: float = 30.0):
+        self.rank, self.world_size, self.device = rank, world_size, device
+        timeout = datetime.timedelta(seconds=timeout_s)
+        self._store = dist.TCPStore(store_ip, store_port, None, host_store, timeout=timeout, wait_for_workers=False)
+        scoped = dist.PrefixStore(prefix, self._store)
+        if device.type == "cuda":
+            self._pg = dist.ProcessGroupNCCL(scoped, rank, world_size, timeout)
+        else:
+            self._pg = dist.ProcessGroupGloo(scoped, rank, world_size, timeout=timeout)
+
+    def all_reduce(self, tensor: torch.Tensor) -> None:
+        self._pg.allreduce([tensor]).wait()
+
+    def broadcast(self, tensor: torch.Tensor, src: int) -> None:
+        opts = dist.BroadcastOptions()
+        opts.rootRank, opts.rootTensor = src, 0
+        self._pg.broadcast([tensor], opts).wait()
+
+    def all_gather_object(self, obj) -> list:
+        import pickle
+        raw = pickle.dumps(obj)
+        size = torch.tensor([len(raw)], dtype=torch.int64, device=self.device)
+        sizes = [torch.zeros_like(size) for _ in range(self.world_size)]
+        self._pg.allgather([sizes], [size]).wait()
+        longest = max(int(t.item()) for t in sizes)
+        mine = torch.zeros(longest, dtype=torch.uint8, device=self.device)
+        mine[:len(raw)] = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(self.device)
+        everyone = [torch.zeros_like(mine) for _ in range(self.world_size)]
+        self._pg.allgather([everyone], [mine]).wait()
+        return [pickle.loads(bytes(t[:int(n.item())].cpu().numpy().tobytes())) for t, n in zip(everyone, sizes)]
+
+    def close(self) -> None:
+        pg, self._pg = self._pg, None
+        if pg is not None and hasattr(pg, "abort") and self.device.type == "cuda":
+            try:
+                pg.abort()          # do not wait for members that are gone
+            except Exception:  # noqa: BLE001
+                pass
+        del pg
+        self._store = None
+
+
+def synchronize_shared_state(comm, revision: int, infos: Sequence[TensorInfo],
+                             strategy: SharedStateSyncStrategy = SharedStateSyncStrategy.ENFORCE_POPULAR
+                             ) -> Tuple[Result, SharedStateSyncInfo]:
+    """Makes every member of ``comm`` (``rank``, ``world_size``, ``all_gather_object``, ``broadcast``) hold the same
+    content for the named tensors.  Members exchange (revision, hash of all tensors); the donor is a member with the
+    highest revision whose hash is the most common one at that revision (lowest rank on ties); every member whose
+    hash differs receives the donor's tensors."""
+    out = SharedStateSyncInfo(revision=revision)
+    if comm.world_size <= 1:
+        return Result.SUCCESS, out
+    h = hashlib.blake2b(digest_size=16)
+    compared = [ti for ti in infos if not ti.allow_content_inequality]
+    for ti, digest in zip(compared, tensor_hashes([ti.tensor for ti in compared])):
+        h.update(ti.name.encode())
+        h.update(digest.encode())
+    mine = (int(revision), h.hexdigest(), strategy.value)
+    try:
+        everyone = comm.all_gather_object(mine)
+        candidates = [(r, rev, hh) for r, (rev, hh, st) in enumerate(everyone)
+                      if st != SharedStateSyncStrategy.RECEIVE_ONLY.value]
+        if not candidates:
+            return Result.INVALID_USAGE, out
+        top = max(rev for _, rev, _ in candidates)
+        counts: Dict[str, int] = {}
+        for _, rev, hh in candidates:
+            if rev == top:
+                counts[hh] = counts.get(hh, 0) + 1
+        popular = max(counts.items(), key=lambda kv: (kv[1], ))[0]
+        donor = min(r for r, rev, hh in candidates if rev == top and hh == popular)
+        differs = [(rev, hh) != (top, popular) for (rev, hh, _) in everyone]
+        out.revision = top
+        if any(differs):
+            for ti in infos:
+                buf = ti.tensor if ti.tensor.is_contiguous() else ti.tensor.contiguous()
+                comm.broadcast(buf, donor)
+                if buf is not ti.tensor:
+                    ti.tensor.copy_(buf)
+                nbytes = buf.numel() * buf.element_size()
+                if comm.rank == donor:
+                    out.tx_bytes += nbytes * sum(differs)
+                elif differs[comm.rank]:
+                    out.rx_bytes += nbytes
+    except Exception as ex:  # noqa: BLE001
+        LOG("WARN", f"ftccl: shared-state synchronisation failed: {ex}")
+        return Result.RANK_CONNECTION_LOST, out
+    return Result.SUCCESS, out
+
+
 class FtPeer:
     def __init__(self, master_ip: str, master_port: int, device: torch.device, peer_group: int = 0,
                  my_ip: str = "127.0.0.1", heartbeat_interval_s: float = 0.25, collective_timeout_s: float = 30.0,
-                 p2p_connection_pool_size: int = 16):
+                 p2p_connection_pool_size: int = 16, owns_default_group: bool = True):
+        """``owns_default_group=False``: the process has a default ``torch.distributed`` group of its own that this
+        peer must leave alone (it then only connects, heartbeats, gates and votes; see :meth:`vote_topology`)."""
+        self.owns_default_group = owns_default_group
         self.master_addr = (master_ip, master_port)
         self.device, self.peer_group, self.my_ip = device, peer_group, my_ip
         self.heartbeat_interval_s, self.collective_timeout_s = heartbeat_interval_s, collective_timeout_s
@@ -523,22 +643,36 @@ class FtPeer:
         return (not v.get("ok", True)) or v.get("pending", 0) > 0 or (
             self.world_size > 0 and v.get("world", self.world_size) != self.world_size)
 
-    def update_topology(self, min_world: int = 1, timeout_s: float = 30.0) -> Result:
-        """Votes for a topology update and, once all accepted peers have voted, re-rendezvouses: the old
-        process group is destroyed and the new epoch's group initialised with the ranks the master assigned."""
+    def vote_topology(self, min_world: int = 1, timeout_s: float = 30.0) -> Optional[dict]:
+        """Votes for a topology update and returns the master's answer once all accepted peers have voted (None when
+        the round failed): ``epoch``, ``world``, ``ranks`` (uid → rank), ``groups`` (uid → peer group) and ``store``
+        (address of the epoch's bootstrap store, a free port on the peer with rank 0).  Takes the new epoch, world
+        size and rank but leaves process groups alone — :meth:`update_topology` builds the default group from the
+        answer; a caller with its own communicators builds those."""
         try:
             res = self._rpc({"op": "vote", "free_port": _free_port(self.my_ip), "min_world": min_world,
                              "timeout": timeout_s}, timeout=timeout_s + 10.0)
         except (OSError, ConnectionError) as ex:
             LOG("ERR", f"ftccl: topology vote failed: {ex}")
-            return Result.UPDATE_TOPOLOGY_FAILED
+            return None
         if not res.get("ok"):
-            return Result.UPDATE_TOPOLOGY_FAILED
-        self._teardown_group()
+            return None
         self.epoch = int(res["epoch"])
         self.world_size = int(res["world"])
         self.rank = int(res["ranks"][str(self.uid)])
         self._groups = res.get("groups", {})
+        self._master_view = dict(self._master_view, world=self.world_size, pending=0, ok=True)
+        return res
+
+    def update_topology(self, min_world: int = 1, timeout_s: float = 30.0) -> Result:
+        """Votes for a topology update and, once all accepted peers have voted, re-rendezvouses: the old
+        process group is destroyed and the new epoch's group initialised with the ranks the master assigned."""
+        if not self.owns_default_group:
+            return Result.INVALID_USAGE
+        res = self.vote_topology(min_world, timeout_s)
+        if res is None:
+            return Result.UPDATE_TOPOLOGY_FAILED
+        self._teardown_group()
         store = res["store"]
         backend = "nccl" if self.device.type == "cuda" else "gloo"
         kwargs = {"device_id": self.device} if self.device.type == "cuda" else {}
@@ -576,7 +710,7 @@ class FtPeer:
         return max(sizes.values()) if sizes else 0
 
     def _teardown_group(self) -> None:
-        if dist.is_initialized():
+        if self.owns_default_group and dist.is_initialized():
             try:
                 dist.destroy_process_group()
             except Exception:  # noqa: BLE001
@@ -665,49 +799,8 @@ class FtPeer:
     def synchronize_shared_state(self, revision: int, infos: Sequence[TensorInfo],
                                  strategy: SharedStateSyncStrategy = SharedStateSyncStrategy.ENFORCE_POPULAR
                                  ) -> Tuple[Result, SharedStateSyncInfo]:
-        """Makes every peer hold the same content for the named tensors.  Peers exchange (revision, hash of
-        all tensors); the donor is a peer with the highest revision whose hash is the most common one at that
-        revision (lowest rank on ties); every peer whose hash differs receives the donor's tensors."""
-        out = SharedStateSyncInfo(revision=revision)
-        if self.world_size <= 1:
-            return Result.SUCCESS, out
-        h = hashlib.blake2b(digest_size=16)
-        compared = [ti for ti in infos if not ti.allow_content_inequality]
-        for ti, digest in zip(compared, tensor_hashes([ti.tensor for ti in compared])):
-            h.update(ti.name.encode())
-            h.update(digest.encode())
-        mine = (int(revision), h.hexdigest(), strategy.value)
-        try:
-            everyone: List[Optional[tuple]] = [None] * self.world_size
-            dist.all_gather_object(everyone, mine)
-            candidates = [(r, rev, hh) for r, (rev, hh, st) in enumerate(everyone)
-                          if st != SharedStateSyncStrategy.RECEIVE_ONLY.value]
-            if not candidates:
-                return Result.INVALID_USAGE, out
-            top = max(rev for _, rev, _ in candidates)
-            counts: Dict[str, int] = {}
-            for _, rev, hh in candidates:
-                if rev == top:
-                    counts[hh] = counts.get(hh, 0) + 1
-            popular = max(counts.items(), key=lambda kv: (kv[1], ))[0]
-            donor = min(r for r, rev, hh in candidates if rev == top and hh == popular)
-            differs = [(rev, hh) != (top, popular) for (rev, hh, _) in everyone]
-            out.revision = top
-            if any(differs):
-                for ti in infos:
-                    buf = ti.tensor if ti.tensor.is_contiguous() else ti.tensor.contiguous()
-                    dist.broadcast(buf, src=donor)
-                    if buf is not ti.tensor:
-                        ti.tensor.copy_(buf)
-                    nbytes = buf.numel() * buf.element_size()
-                    if self.rank == donor:
-                        out.tx_bytes += nbytes * sum(differs)
-                    elif differs[self.rank]:
-                        out.rx_bytes += nbytes
-        except Exception as ex:  # noqa: BLE001
-            LOG("WARN", f"ftccl: shared-state synchronisation failed: {ex}")
-            return Result.RANK_CONNECTION_LOST, out
-        return Result.SUCCESS, out
+        """:func:`synchronize_shared_state` over this peer's process group."""
+        return synchronize_shared_state(_DefaultGroupComm(self.rank, self.world_size), revision, infos, strategy)
 
     # -- leaving / failure injection ----------------------------------------------------------
     def leave(self) -> None:

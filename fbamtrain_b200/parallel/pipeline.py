@@ -262,21 +262,30 @@ class PipelineTrainer:
     ``src/main.cpp:3119-3123, 3204-3273, 3368-3414, 3588-3598``)."""
 
     def __init__(self, cfg, device: torch.device, vocab: int, layout: Optional[PipelineLayout] = None,
-                 tp_transport: str = "nccl", replicas: int = 1):
+                 tp_transport: str = "nccl", replicas: int = 1, ft=None):
         """``replicas`` > 1 runs that many pipelines side by side (data parallelism over pipelines: the reference's
         combination of ``ddp_parallel`` with ``frame_head_parallel``, ``src/main.cpp:2563-2588``): consecutive
         blocks of ``world / replicas`` ranks form one pipeline each, every replica takes its share of the batch
-        and the gradients of ranks in the same position are summed across replicas."""
+        and the gradients of ranks in the same position are summed across replicas.
+
+        ``ft`` (a :class:`~.ft_pipeline.FaultTolerantPipelineReplicas`): this process group is ONE pipeline of a job
+        whose pipelines come and go; the batch is divided by ``ft.expected_replicas``, the pipeline takes the share
+        of its current index, gradients are summed over the pipelines that are present, and a step is applied only
+        when every position's exchange succeeded."""
         from ..optim import create_optimizer
         self.cfg, self.device = cfg, device
+        self.ft = ft
         world, rank = dist.get_world_size(), dist.get_rank()
+        if ft is not None and replicas != 1:
+            raise ValueError("with dynamic membership every pipeline is a process group of its own (replicas = 1)")
         if replicas < 1 or world % replicas or (world // replicas) % 2:
             raise ValueError("the world must split into `replicas` pipelines with an even number of ranks each")
-        if cfg.total_batch_size % (cfg.micro_batch_size * replicas):
+        shares = replicas if ft is None else ft.expected_replicas
+        if cfg.total_batch_size % (cfg.micro_batch_size * shares):
             raise ValueError("total_batch_size must be a multiple of micro_batch_size x replicas")
         self.replicas, self.per_replica = replicas, world // replicas
         self.replica = rank // self.per_replica
-        self.micro_batches = cfg.total_batch_size // (cfg.micro_batch_size * replicas)
+        self.micro_batches = cfg.total_batch_size // (cfg.micro_batch_size * shares)
         self.seq = cfg.train_sequence_length
         torch.manual_seed(cfg.model_config.model_init_seed)
         self.model = FbamModel(cfg.model_config, vocab).to(device)
@@ -306,6 +315,8 @@ class PipelineTrainer:
         self.optimizer = create_optimizer(cfg.optimizer_config, named, prefix)
         self.loss_scale = 1.0 / (self.seq * cfg.total_batch_size)
         self.step_count = 0
+        if ft is not None:
+            ft.attach(self)
 
     # -- checkpoints ---------------------------------------------------------------------------------------
     # One model file in the single-process layout (every mode can load it) written by global rank 0, plus one
@@ -388,8 +399,9 @@ class PipelineTrainer:
             p.grad = None
         mb = self.cfg.micro_batch_size
         per = self.micro_batches * mb                      # sequences of this replica
-        cells, targets = cells[self.replica * per:(self.replica + 1) * per], \
-            targets[self.replica * per:(self.replica + 1) * per]
+        share_index = self.replica if self.ft is None else self.ft.replica_index
+        cells, targets = cells[share_index * per:(share_index + 1) * per], \
+            targets[share_index * per:(share_index + 1) * per]
         c5 = cells.view(self.micro_batches, mb, *cells.shape[1:]) if self.pipe.is_frame else None
         t3 = targets.view(self.micro_batches, mb, targets.shape[1]) if not self.pipe.is_frame else None
         share = self.pipe.run_step(c5, t3, self.loss_scale)
@@ -397,8 +409,20 @@ class PipelineTrainer:
             for _, p in self.named:
                 if p.grad is not None:
                     dist.all_reduce(p.grad, group=self.cross_group)
-        self.optimizer.step()
-        self.step_count += 1
         total = torch.tensor([share], dtype=torch.float64, device=self.device)
         dist.all_reduce(total)
+        if self.ft is not None:
+            # the loss of the whole job rides along with the leader's gradients (zero from the other positions)
+            extra = total.float() if self.ft.is_leader else torch.zeros(1, device=self.device)
+            if not self.ft.reduce(self, extra=extra):
+                return float("nan")                        # dropped: no update, the step is not counted
+            total = self._job_loss(extra)
+        self.optimizer.step()
+        self.step_count += 1
         return float(total.item())
+
+    def _job_loss(self, leader_sum: torch.Tensor) -> torch.Tensor:
+        """The leader holds the loss summed over the pipelines; everyone in the pipeline gets it."""
+        t = leader_sum.double()
+        dist.broadcast(t, src=0)
+        return t

@@ -385,3 +385,52 @@ def test_fault_tolerant_cli_survives_a_killed_rank(tmp_path):
     assert all(p.returncode == 0 for p in procs[:2]), outs
     for out in outs:
         assert "finished 10 steps" in out, out
+
+
+def test_cli_pipelines_with_dynamic_membership(tmp_path):
+    """``frame_head_parallel`` together with ``ddp_parallel`` on transport ``ftccl``: the membership master and two
+    pipelines of two CPU processes each, every pipeline started by hand as a job of its own (``--replica-id``).  The
+    pipeline that forms the group first takes the other in at its step gate; afterwards both report the same
+    committed losses."""
+    import socket
+    cfg = presets.tiny()
+    cfg["model_config"].update({"action_heads": 2, "lstm_layers": 1})
+    cfg["micro_batch_size"], cfg["total_batch_size"] = 1, 2
+    run = tmp_path / "run.json"
+    run.write_text(json.dumps(cfg))
+    ports = []
+    for _ in range(2):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            ports.append(s.getsockname()[1])
+    # the two pipelines rendezvous at ports[0] and ports[0] + 1; keep the second one free as well
+    par = {"frame_head_parallel": {"use_frame_head_parallel": True, "transport": "ccl",
+                                   "ccl_rendezvous": {"ip": "127.0.0.1", "port": ports[0]}},
+           "ddp_parallel": {"use_ddp_parallel": True, "transport": "ftccl",
+                            "ftccl_master": {"ip": "127.0.0.1", "port": ports[1]}}}
+    parallel = tmp_path / "parallel.json"
+    parallel.write_text(json.dumps(par))
+    env = dict(os.environ, PYTHONPATH=ROOT, FBAMTRAIN_LOG_LEVEL="INFO", FBAMTRAIN_METRICS_JSON="1")
+    master = subprocess.Popen([sys.executable, "-m", "fbamtrain_b200.cli", "--parallel-config", str(parallel),
+                               "--ftccl-master"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
+    try:
+        base = [sys.executable, "-m", "fbamtrain_b200.cli", "-c", str(run), "--parallel-config", str(parallel),
+                "--synthetic", "--steps", "6", "--device", "cpu", "--world-size", "2", "--ddp-world-size", "2"]
+        procs = []
+        for replica in (0, 1):
+            for worker, extra in ((0, []), (1, ["--master"])):
+                procs.append(subprocess.Popen(base + ["--replica-id", str(replica), "--worker_id", str(worker)] + extra,
+                                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env))
+        outs = [p.communicate(timeout=400)[0] for p in procs]
+        assert all(p.returncode == 0 for p in procs), outs
+    finally:
+        master.terminate()
+        master.communicate(timeout=30)
+
+    def losses(out):
+        rows = [json.loads(line) for line in out.splitlines() if line.startswith("{") and "loss/train" in line]
+        return {r["step"]: r["loss/train"] for r in rows}
+    first, second = losses(outs[1]), losses(outs[3])         # the recurrence masters report
+    both = sorted(set(first) & set(second))
+    assert len(both) >= 3
+    assert all(abs(first[k] - second[k]) < 1e-6 for k in both[-3:])      # in lockstep once both are in the group

@@ -261,3 +261,17 @@ def test_reduce_scatter_row_stores_single_gpu(pair):
     got = results[1][:, 1].float()
     assert float((got - expect).norm() / expect.norm()) < 1e-2
     assert float(results[1][:, 0].abs().max()) == 0.0 and float(results[1][:, 2].abs().max()) == 0.0
+
+
+def test_scoped_group_next_to_the_default_group_on_two_gpus(tmp_path):
+    """The stand-alone NCCL communicator that pipelines with dynamic membership build per position
+    (``parallel/ft_pipeline.py``): collectives, object exchange and the shared-state comparison on two GPUs."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = tmp_path / "result.txt"
+    worker = os.path.join(os.path.dirname(__file__), "workers", "scoped_group_worker.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), worker, str(out), str(_free_port())]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, _tail(r)
+    assert out.read_text() == "ok"
