@@ -104,7 +104,7 @@ __device__ __forceinline__ void mma2_commit_both(uint64_t* bar) {
 }
 
 // Row of this CTA's 128-row half -> element offset in D (or -1).  `half_tile` indexes 128-row tiles / bricks.
-__device__ __forceinline__ long long row_offset2(const GemmParams& p, int half_tile, int row) {
+__device__ __forceinline__ long long row_offset2(const GemmParams& p, int half_tile, int row, int off_h, int off_w) {
   if (p.mode != GEMM_MODE_CONV) {
     const int m = half_tile * BM + row;
     return m < p.M ? (long long)m * p.ldd : -1;
@@ -116,10 +116,20 @@ __device__ __forceinline__ long long row_offset2(const GemmParams& p, int half_t
   const int wl = row % g.tw, hl = (row / g.tw) % g.th, nl = row / (g.tw * g.th);
   const int n = nb * g.tn + nl, h = hb * g.th + hl, w = wb * g.tw + wl;
   if (n >= g.batch || h >= g.grid_h || w >= g.grid_w) return -1;
-  const int oh = h * g.out_mul + g.out_off_h, ow = w * g.out_mul + g.out_off_w;
+  const int oh = h * g.out_mul + off_h, ow = w * g.out_mul + off_w;
   if (oh >= g.out_h || ow >= g.out_w) return -1;
   return (((long long)n * g.out_h + oh) * g.out_w + ow) * p.ldd;
 }
+
+// Work items of one CTA pair: tile `cluster_id + j * num_clusters` for j = 0, 1, ..., each visited once per parity
+// class (all classes of a tile back to back).  The three roles walk the same sequence.
+struct WorkIter {
+  int tile, cls;
+  __device__ __forceinline__ WorkIter(int first) : tile(first), cls(0) {}
+  __device__ __forceinline__ void next(int ncls, int stride) {
+    if (++cls >= ncls) { cls = 0; tile += stride; }
+  }
+};
 
 // p.tiles_m counts PAIR tiles (256 rows); K is never split in this variant.
 template <int BN>
@@ -139,7 +149,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   const int cluster_id = blockIdx.x / 2, num_clusters = gridDim.x / 2;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = p.tiles_m * tiles_n;
-  const int k_blocks = p.k_blocks;
+  const int ncls = p.num_classes > 0 ? p.num_classes : 1;
   constexpr uint32_t kTmemCols = 2 * BN;
 
   if (threadIdx.x == 0) {
@@ -171,10 +181,14 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      for (WorkIter it(cluster_id); it.tile < num_tiles && ok; it.next(ncls, num_clusters)) {
+        const int tile = it.tile;
         const int tile_m = (tile / tiles_n + p.tile_m_rotate) % p.tiles_m, tile_n = tile % tiles_n;
         const int half = tile_m * 2 + (int)rank;              // this CTA's 128-row tile / brick
         const int b_row0 = tile_n * BN + (int)rank * (BN / 2);   // this CTA's half of the B tile
+        const bool classes = p.num_classes > 0;
+        const int k_blocks = classes ? p.cls[it.cls].num_taps * p.conv.c_blocks : p.k_blocks;
+        const int kb_base = classes ? p.cls[it.cls].k_block_base : 0;
         int cn = 0, ch = 0, cw = 0;
         if (p.mode == GEMM_MODE_CONV) {
           const ConvGeom& g = p.conv;
@@ -207,7 +221,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
           if (p.mode == GEMM_MODE_CONV) {
             const ConvGeom& g = p.conv;
             const int tap = kb / g.c_blocks, cb = kb % g.c_blocks;
-            tma2_load_4d(sa, &map_a, leader_full, cb * BK, cw + g.tap_dw[tap], ch + g.tap_dh[tap], cn);
+            const int dw = classes ? p.cls[it.cls].tap_dw[tap] : g.tap_dw[tap];
+            const int dh = classes ? p.cls[it.cls].tap_dh[tap] : g.tap_dh[tap];
+            tma2_load_4d(sa, &map_a, leader_full, cb * BK, cw + dw, ch + dh, cn);
           } else if (p.a_mn_major) {
             tma2_load_2d(sa, &map_a, leader_full, half * BM, kb * BK);
             tma2_load_2d(sa + BK * 128, &map_a, leader_full, half * BM + 64, kb * BK);
@@ -217,9 +233,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
           if (p.b_mn_major) {
 #pragma unroll
             for (int j = 0; j < BN / 128; ++j)
-              tma2_load_2d(sb + j * BK * 128, &map_b, leader_full, b_row0 + j * 64, kb * BK);
+              tma2_load_2d(sb + j * BK * 128, &map_b, leader_full, b_row0 + j * 64, (kb_base + kb) * BK);
           } else {
-            tma2_load_2d(sb, &map_b, leader_full, kb * BK, b_row0);
+            tma2_load_2d(sb, &map_b, leader_full, (kb_base + kb) * BK, b_row0);
           }
           if (++stage == L::kStages) { stage = 0; phase ^= 1; }
         }
@@ -236,7 +252,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      for (WorkIter it(cluster_id); it.tile < num_tiles && ok; it.next(ncls, num_clusters)) {
+        const int k_blocks = p.num_classes > 0 ? p.cls[it.cls].num_taps * p.conv.c_blocks : p.k_blocks;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { ok = false; break; }
         fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -268,12 +285,15 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+    for (WorkIter it(cluster_id); it.tile < num_tiles && ok; it.next(ncls, num_clusters)) {
+      const int tile = it.tile;
       const int tile_m = (tile / tiles_n + p.tile_m_rotate) % p.tiles_m, tile_n = tile % tiles_n;
       const int half = tile_m * 2 + (int)rank;
+      const int off_h = p.num_classes > 0 ? p.cls[it.cls].out_off_h : p.conv.out_off_h;
+      const int off_w = p.num_classes > 0 ? p.cls[it.cls].out_off_w : p.conv.out_off_w;
       // the side input of the first chunk is requested before the accumulator is waited for, and that of every
       // later chunk before the previous one is processed
-      const long long roff = row_offset2(p, half, row);
+      const long long roff = row_offset2(p, half, row, off_h, off_w);
       const elem_t* aux_row = gemm_epi::aux_row_ptr(p, roff);
       uint4 aux[4] = {};
       gemm_epi::aux_prefetch(aux_row, tile_n * BN + col_half * (BN / 2), p.N, aux);
@@ -417,6 +437,13 @@ extern "C" int fbam_conv2(const void* X, int in_h, int in_w, int C, const void* 
   GemmParams p = *params;
   ConvGeom& g = p.conv;
   if (C % 64 != 0 || g.tn * g.th * g.tw != BM || g.num_taps < 1 || g.num_taps > 9) return GEMM_ERR_SHAPE;
+  if (p.num_classes < 0 || p.num_classes > 4) return GEMM_ERR_SHAPE;
+  int class_taps = 0;
+  for (int c = 0; c < p.num_classes; ++c) {
+    if (p.cls[c].num_taps < 1 || p.cls[c].num_taps > 4 || p.cls[c].k_block_base != class_taps * (C / 64)) return GEMM_ERR_SHAPE;
+    class_taps += p.cls[c].num_taps;
+  }
+  if (p.num_classes > 0 && class_taps != g.num_taps) return GEMM_ERR_SHAPE;   // conv.num_taps = all classes' taps
   p.mode = GEMM_MODE_CONV;
   p.a_mn_major = 0; p.b_mn_major = 0;
   g.c_blocks = C / 64;

@@ -579,6 +579,7 @@ extern "C" int fbam_gemm(const void* A, long long lda, int a_mn_major, const voi
 extern "C" int fbam_conv(const void* X, int in_h, int in_w, int C, const void* Wmat, long long ldw, int N,
                               GemmParams* params, void* stream) {
   GemmParams p = *params;
+  if (p.num_classes != 0) return GEMM_ERR_SHAPE;   // fused parity classes exist in the CTA-pair kernel only
   ConvGeom& g = p.conv;
   const int BM = g.tn * g.th * g.tw;
   if (C % 64 != 0 || (BM != 128 && BM != 256) || g.num_taps < 1 || g.num_taps > 9) return GEMM_ERR_SHAPE;

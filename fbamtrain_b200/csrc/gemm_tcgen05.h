@@ -27,6 +27,15 @@ struct ConvGeom {
   int c_blocks, tiles_w, tiles_h;
 };
 
+// One parity class of a strided data-gradient convolution run by the CTA-pair kernel as part of a fused pass: its own
+// taps, its own output offset, and where its filter columns start in the shared filter matrix (in 64-column blocks).
+struct ConvClass {
+  int num_taps;
+  int tap_dh[4], tap_dw[4];
+  int out_off_h, out_off_w;
+  int k_block_base;
+};
+
 struct GemmParams {
   void* D;                          // output, bf16 or fp32, row pitch ldd elements
   long long ldd;
@@ -82,6 +91,12 @@ struct GemmParams {
   // filled by the launcher
   int mode, M, N, K, tiles_m, k_blocks, a_mn_major, b_mn_major, vec_ok;
   ConvGeom conv;
+  // Fused parity classes (CTA-pair convolution only; 0 = a single pass with conv's own taps and offset).  Every
+  // 256-row tile is computed num_classes times in a row by the same CTA pair, once per class, each time with that
+  // class's taps, filter columns and output offset: the input tile is fetched from DRAM once and found in L2 by the
+  // other classes, instead of being streamed again by a separate launch per class.
+  int num_classes;
+  ConvClass cls[4];
 };
 
 // Driver entry points (tensor-map encoding) need a context that is current on the CALLING thread.  A thread that

@@ -43,6 +43,11 @@ class ConvGeom(C.Structure):
                 ("c_blocks", C.c_int), ("tiles_w", C.c_int), ("tiles_h", C.c_int)]
 
 
+class ConvClass(C.Structure):
+    _fields_ = [("num_taps", C.c_int), ("tap_dh", C.c_int * 4), ("tap_dw", C.c_int * 4),
+                ("out_off_h", C.c_int), ("out_off_w", C.c_int), ("k_block_base", C.c_int)]
+
+
 class GemmParams(C.Structure):
     _fields_ = [("D", C.c_void_p), ("ldd", C.c_longlong),
                 ("bias", C.c_void_p),
@@ -63,7 +68,8 @@ class GemmParams(C.Structure):
                 ("ce_targets", C.c_void_p),
                 ("mode", C.c_int), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("tiles_m", C.c_int),
                 ("k_blocks", C.c_int), ("a_mn_major", C.c_int), ("b_mn_major", C.c_int), ("vec_ok", C.c_int),
-                ("conv", ConvGeom)]
+                ("conv", ConvGeom),
+                ("num_classes", C.c_int), ("cls", ConvClass * 4)]
 
 
 def available(dtype: torch.dtype = torch.bfloat16) -> bool:

@@ -273,11 +273,18 @@ def _brick(n: int, h: int, w: int, total: int = 128) -> Tuple[int, int, int]:
 def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor, *, grid_hw, in_mul, taps,
               out_mul=1, out_off=(0, 0), accumulate=0, bn: int = 0, act: str = "none",
               preact_out: Optional[torch.Tensor] = None, gelu_grad_in: Optional[torch.Tensor] = None,
-              tile_rows: int = 0, two_cta=None) -> None:
+              tile_rows: int = 0, two_cta=None, classes=None) -> None:
     """One implicit-GEMM pass (see ``ConvGeom`` in csrc/gemm_tcgen05.h).  ``x`` NHWC bf16 or fp16, ``wmat``
-    ``(n_out, taps·C)`` of the same type, ``out`` NHWC with ``n_out`` channels."""
+    ``(n_out, taps·C)`` of the same type, ``out`` NHWC with ``n_out`` channels.
+
+    ``classes`` (CTA-pair kernel only): a list of ``(taps, out_off)`` — parity classes of a strided data gradient
+    that share the iteration grid.  ``taps`` is then the concatenation of the classes' taps and ``wmat`` holds the
+    classes' filter columns side by side in that order; every tile is computed once per class by the same CTA pair,
+    so the input tile is read from DRAM once for all classes."""
     b, ih, iw, c = x.shape
-    if bn == 0 and tile_rows == 0 and two_cta is None:
+    if classes is not None:
+        two_cta, tile_rows, bn = True, 0, 0
+    elif bn == 0 and tile_rows == 0 and two_cta is None:
         tuned = tuning.lookup(tuning.conv_key(b, grid_hw[0], grid_hw[1], c, n_out, len(taps), in_mul, out_mul),
                               {"batch": b, "in_h": ih, "in_w": iw, "c": c, "n_out": n_out, "grid_hw": list(grid_hw),
                                "in_mul": in_mul, "out_mul": out_mul, "taps": [list(t) for t in taps],
@@ -306,6 +313,15 @@ def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor
     g.num_taps = len(taps)
     for i, (dh, dw) in enumerate(taps):
         g.tap_dh[i], g.tap_dw[i] = dh, dw
+    if classes is not None:
+        p.num_classes = len(classes)
+        base = 0
+        for k, (ctaps, coff) in enumerate(classes):
+            cl = p.cls[k]
+            cl.num_taps, cl.out_off_h, cl.out_off_w, cl.k_block_base = len(ctaps), coff[0], coff[1], base * (c // 64)
+            for i, (dh, dw) in enumerate(ctaps):
+                cl.tap_dh[i], cl.tap_dw[i] = dh, dw
+            base += len(ctaps)
     p.D, p.ldd = out.data_ptr(), out.shape[3]
     p.status = nv.status_word(x.device).data_ptr()
     p.alpha = 1.0
@@ -318,7 +334,8 @@ def conv_pass(x: torch.Tensor, wmat: torch.Tensor, n_out: int, out: torch.Tensor
     if gelu_grad_in is not None:
         p.gelu_grad_in = gelu_grad_in.data_ptr()
     fn = nv.lib(x).fbam_conv2 if pair else nv.lib(x).fbam_conv
-    with debug.label(f"conv{'2' if pair else ''} c{c} n{n_out} taps{len(taps)} in_mul{in_mul} out_mul{out_mul} {act}"):
+    with debug.label(f"conv{'2' if pair else ''} c{c} n{n_out} taps{len(taps)} in_mul{in_mul} out_mul{out_mul} {act}"
+                     + (f" classes{len(classes)}" if classes is not None else "")):
         code = fn(nv.ptr(x), ih, iw, c, nv.ptr(wmat), C.c_longlong(wmat.stride(0)), n_out, C.byref(p),
                   nv.stream_ptr())
     nv.check(code, "fbam_conv")
@@ -350,7 +367,7 @@ def conv2d_dgrad(dy, w_ohwi, in_hw, stride, padding, dilation, gelu_grad_in=None
     c = w_ohwi.shape[3]
     ih, iw = in_hw
     dx = debug.fresh((b, ih, iw, c), dy.dtype, dy.device)
-    covered = 0
+    parts = []                                  # (taps, filter matrix (C, taps·O), grid, output offset) per class
     for ph in range(stride):
         for pw in range(stride):
             taps, mats = [], []
@@ -370,11 +387,37 @@ def conv2d_dgrad(dy, w_ohwi, in_hw, stride, padding, dilation, gelu_grad_in=None
                 continue
             # (gelu_grad_in multiplies every written element, so zero-tap classes stay zero)
             # filter matrix for this class: (C, taps·O), K ordered tap-major then output channel
-            wmat = torch.stack(mats, 0).permute(2, 0, 1).reshape(c, len(taps) * o).contiguous()
-            conv_pass(dy, wmat, c, dx, grid_hw=(gh, gw), in_mul=1, taps=taps, out_mul=stride, out_off=(ph, pw),
-                      gelu_grad_in=gelu_grad_in)
-            covered += 1
+            wmat = torch.stack(mats, 0).permute(2, 0, 1).reshape(c, len(taps) * o)
+            parts.append((taps, wmat, (gh, gw), (ph, pw)))
+    if _fuse_dgrad_classes(parts, b, c, stride):
+        # all parity classes in one launch: a CTA pair runs the classes of a tile back to back, so the gradient tile
+        # is streamed from DRAM once instead of once per class (heaviest class first: it touches every shifted tile)
+        parts.sort(key=lambda part: -len(part[0]))
+        wall = torch.cat([part[1] for part in parts], 1).contiguous()
+        conv_pass(dy, wall, c, dx, grid_hw=parts[0][2], in_mul=1, taps=[t for part in parts for t in part[0]],
+                  out_mul=stride, gelu_grad_in=gelu_grad_in, classes=[(part[0], part[3]) for part in parts])
+        return dx
+    for taps, wmat, grid, off in parts:
+        conv_pass(dy, wmat.contiguous(), c, dx, grid_hw=grid, in_mul=1, taps=taps, out_mul=stride, out_off=off,
+                  gelu_grad_in=gelu_grad_in)
     return dx
+
+
+FUSE_DGRAD_CLASSES = True
+
+
+def _fuse_dgrad_classes(parts, batch: int, n_out: int, stride: int) -> bool:
+    """The fused form needs every class on the same grid with one to four taps, nine taps in all at most, and a
+    problem that the CTA-pair kernel would be chosen for anyway."""
+    if not FUSE_DGRAD_CLASSES or TWO_CTA is False or len(parts) < 2 or len(parts) > 4 or n_out < 256 or n_out % 16:
+        return False
+    if any(part[2] != parts[0][2] or not 1 <= len(part[0]) <= 4 for part in parts):
+        return False
+    if sum(len(part[0]) for part in parts) > 9:
+        return False
+    gh, gw = parts[0][2]
+    tn, th, tw = _brick(batch, gh, gw, 256)
+    return math.ceil(batch / tn) * math.ceil(gh / th) * math.ceil(gw / tw) >= 148
 
 
 class _ConvGeluStackPool(torch.autograd.Function):

@@ -531,6 +531,42 @@ def test_conv_cta_pairs(stride, pad, dil):
     assert _rel_err(y, expect) < 5e-3
 
 
+@pytest.mark.parametrize("with_gelu_grad", [False, True])
+@pytest.mark.parametrize("shape", [(160, 24, 40, 256, 64), (300, 16, 32, 320, 128), (40, 23, 41, 256, 64)])
+def test_strided_dgrad_with_fused_parity_classes(shape, with_gelu_grad, monkeypatch):
+    """Stride-2 data gradient with all four parity classes in one launch of the CTA-pair kernel (every tile computed
+    once per class by the same pair), against the one-launch-per-class form and against fp32 autograd.  The last
+    shape has odd sides: its classes have different grids, which keeps the per-class form."""
+    nv, no = _nops()
+    n, h, w, c, o = shape
+    torch.manual_seed(5)
+    wt = (torch.randn(o, 3, 3, c, device=DEV) / math.sqrt(9 * c)).to(BF)
+    oh, ow = no.conv_out_hw(h, w, 2, 1, 1)
+    dy = torch.randn(n, oh, ow, o, device=DEV).to(BF)
+    z = torch.randn(n, h, w, c, device=DEV).to(BF) if with_gelu_grad else None
+    launches = []
+    real = no.conv_pass
+    monkeypatch.setattr(no, "conv_pass", lambda *a, **k: (launches.append(k.get("classes")), real(*a, **k))[1])
+    fused = no.conv2d_dgrad(dy, wt, (h, w), 2, 1, 1, gelu_grad_in=z)
+    fused_launches = list(launches)
+    monkeypatch.setattr(no, "FUSE_DGRAD_CLASSES", False)
+    separate = no.conv2d_dgrad(dy, wt, (h, w), 2, 1, 1, gelu_grad_in=z)
+    nv.check_status(dy.device)
+    if h % 2 == 0 and w % 2 == 0:
+        assert len(fused_launches) == 1 and len(fused_launches[0]) == 4
+    else:
+        assert len(fused_launches) == 4 and all(cl is None for cl in fused_launches)
+    assert torch.equal(fused, separate)
+    xf = torch.zeros(n, h, w, c, device=DEV, requires_grad=True)
+    ref.conv2d_nhwc(xf, wt.float(), 2, 1, 1).backward(dy.float())
+    expect = xf.grad
+    if with_gelu_grad:
+        zf = z.float().requires_grad_(True)
+        torch.nn.functional.gelu(zf).sum().backward()
+        expect = expect * zf.grad
+    assert _rel_err(fused, expect) < 6e-3
+
+
 def test_device_fingerprint_detects_single_bit_changes():
     _nops()
     from fbamtrain_b200.parallel.ftccl import tensor_hashes

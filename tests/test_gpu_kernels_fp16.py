@@ -24,6 +24,7 @@ from test_gpu_kernels import (  # noqa: E402,F401  (collected here, with this mo
     test_layernorm_gelu_geglu_pools, test_layernorm_fwd_bwd, test_cell_embed_fwd_bwd, test_lm_head_ce_fwd_bwd,
     test_persistent_lstm_fwd_bwd, test_conv_wgrad, test_conv_gelu_stack_pool_matches_unfused_reference,
     test_flash_attention_fwd_bwd, test_gemm_cta_pairs, test_conv_cta_pairs, test_linear_relu_fwd_bwd,
+    test_strided_dgrad_with_fused_parity_classes,
     test_expected_backends_are_chosen_on_gpu)
 from test_gpu_embconv import (  # noqa: E402,F401
     test_colour_features_kernel, test_forward_gather_kernel, test_backward_reduce_kernel,
