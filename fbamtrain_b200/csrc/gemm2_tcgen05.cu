@@ -16,7 +16,10 @@
 // Same operation set as gemm_tcgen05.cu (reference kernel families: cutlass_codegen/gemm_cutlass_kernel.cu:198-330,
 // cutlass_codegen/conv2d_cutlass_kernel.cu).
 #include "gemm_epilogue.cuh"
+#include <cstring>
+
 #include "gemm_tcgen05.h"
+#include "gemm_out_maps.h"
 #include "tc05.cuh"
 
 extern int g_fbam_reserved_sms;        // defined in gemm_tcgen05.cu
@@ -38,7 +41,8 @@ struct Smem2 {
   static constexpr int kBBytes = (BN / 2) * BK * 2;   // this CTA's half of the B tile
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (200 * 1024 / kStageBytes) > 8 ? 8 : (200 * 1024 / kStageBytes);
-  static constexpr int kTotal = kStages * kStageBytes + 512 + 1024;
+  static constexpr int kEpiStage = kEpiWarps * 2 * 2048;   // per epilogue warp: two 32-row x 64-byte buffers for TMA stores
+  static constexpr int kTotal = kStages * kStageBytes + kEpiStage + 512 + 1024;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -134,11 +138,13 @@ struct WorkIter {
 // p.tiles_m counts PAIR tiles (256 rows); K is never split in this variant.
 template <int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+             const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_pre, const GemmParams p) {
   using L = Smem2<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);
+  uint8_t* epi_stage = smem + L::kStages * L::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + L::kEpiStage);
   uint64_t* empty_bar = full_bar + L::kStages;
   uint64_t* tmem_full = empty_bar + L::kStages;
   uint64_t* tmem_empty = tmem_full + 2;
@@ -155,6 +161,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   if (threadIdx.x == 0) {
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
+    if (p.tma_store >= 1) prefetch_tensormap(&map_d);
+    if (p.tma_store >= 2) prefetch_tensormap(&map_pre);
     for (int s = 0; s < L::kStages; ++s) {
       mbar_init(&full_bar[s], 1);    // leader: one arrive.expect_tx covering both CTAs' bytes
       mbar_init(&empty_bar[s], 1);   // one multicast commit per use
@@ -291,26 +299,78 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       const int half = tile_m * 2 + (int)rank;
       const int off_h = p.num_classes > 0 ? p.cls[it.cls].out_off_h : p.conv.out_off_h;
       const int off_w = p.num_classes > 0 ? p.cls[it.cls].out_off_w : p.conv.out_off_w;
-      // the side input of the first chunk is requested before the accumulator is waited for, and that of every
-      // later chunk before the previous one is processed
       const long long roff = row_offset2(p, half, row, off_h, off_w);
+      // TMA stores: where in the output this warp's 32 rows start (a box of st_bn x st_bh x st_bw output positions of
+      // the brick for a convolution, 32 matrix rows otherwise); a box that starts outside the output is skipped,
+      // one that reaches over its edge is clipped by the copy.
+      int sx1 = 0, sx2 = 0, sx3 = 0;
+      bool box_in = true;
+      if (p.tma_store) {
+        if (p.mode == GEMM_MODE_CONV) {
+          const ConvGeom& g = p.conv;
+          const int r0 = lane_group * 32;
+          const int w = (half % g.tiles_w) * g.tw + r0 % g.tw;
+          const int h = ((half / g.tiles_w) % g.tiles_h) * g.th + (r0 / g.tw) % g.th;
+          const int n = (half / (g.tiles_w * g.tiles_h)) * g.tn + r0 / (g.tw * g.th);
+          sx1 = w * g.out_mul + off_w;
+          sx2 = h * g.out_mul + off_h;
+          sx3 = n;
+          box_in = n < g.batch && h < g.grid_h && w < g.grid_w && sx1 < g.out_w && sx2 < g.out_h;
+        } else {
+          sx1 = half * BM + lane_group * 32;
+          box_in = sx1 < p.M;
+        }
+      }
+      uint8_t* stage_pre = epi_stage + (warp - 2) * 4096;
+      uint8_t* stage_out = stage_pre + 2048;
+      // the side input (gelu_grad_in or residual) of the first chunk is requested before the accumulator is waited
+      // for, and that of every later chunk before the previous one is processed
+      const int c_first = col_half * (BN / 2), c_last = (col_half + 1) * (BN / 2);
       const elem_t* aux_row = gemm_epi::aux_row_ptr(p, roff);
       uint4 aux[4] = {};
-      gemm_epi::aux_prefetch(aux_row, tile_n * BN + col_half * (BN / 2), p.N, aux);
+      gemm_epi::aux_prefetch(aux_row, tile_n * BN + c_first, p.N, aux);
       if (!mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
       fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c0 = col_half * (BN / 2); c0 < (col_half + 1) * (BN / 2); c0 += 32) {
+      for (int c0 = c_first; c0 < c_last; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c0, r);
         const int n0 = tile_n * BN + c0;
         uint4 cur[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) cur[q] = aux[q];
-        if (c0 + 32 < (col_half + 1) * (BN / 2)) gemm_epi::aux_prefetch(aux_row, n0 + 32, p.N, aux);
+        if (c0 + 32 < c_last) gemm_epi::aux_prefetch(aux_row, n0 + 32, p.N, aux);
         tmem_ld_wait();
-        if (roff < 0 || n0 >= p.N) continue;
+        if (n0 >= p.N) continue;                               // the same for the whole warp
+        if (p.tma_store && n0 + 32 <= p.N) {
+          // A staging buffer is free once the copy that read it is done (tracked by lane 0, which issued it).  Without
+          // preact_out the two buffers take turns, so only the copy before the previous one has to be done.
+          const bool both = p.tma_store >= 2;
+          uint8_t* out_buf = (both || ((c0 >> 5) & 1)) ? stage_out : stage_pre;
+          if (lane == 0) {
+            if (both) bulk_wait_group_read<0>();
+            else bulk_wait_group_read<1>();
+          }
+          __syncwarp();
+          gemm_epi::store_chunk<false, true, true>(p, roff, n0, r, cur, stage_pre, out_buf);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (box_in) {
+              if (p.mode == GEMM_MODE_CONV) {
+                if (both) tma_store_4d(&map_pre, stage_pre, n0, sx1, sx2, sx3);
+                tma_store_4d(&map_d, out_buf, n0, sx1, sx2, sx3);
+              } else {
+                if (both) tma_store_2d(&map_pre, stage_pre, n0, sx1);
+                tma_store_2d(&map_d, out_buf, n0, sx1);
+              }
+            }
+            bulk_commit_group();      // also when nothing was stored: the group count paces the buffers
+          }
+          continue;
+        }
+        if (roff < 0) continue;
         gemm_epi::store_chunk<false, true>(p, roff, n0, r, cur);
       }
       fence_before_sync();
@@ -322,6 +382,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (!ok && lane == 0) atomicExch(p.status, GEMM_ERR_EPILOGUE_TIMEOUT);
+    if (lane == 0) bulk_wait_group_all();     // this warp's TMA stores have left shared memory and reached global memory
   }
 
   fence_before_sync();
@@ -396,7 +457,10 @@ int launch2(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStr
   const int usable = sms - g_fbam_reserved_sms > 2 ? sms - g_fbam_reserved_sms : 2;
   int clusters = tiles < usable / 2 ? tiles : usable / 2;
   if (p.max_ctas > 1 && clusters > p.max_ctas / 2) clusters = p.max_ctas / 2;
-  gemm2_kernel<BN><<<2 * clusters, kThreads, L::kTotal, stream>>>(ma, mb, p);
+  CUtensorMap md, mpre;
+  const int e = fbam_encode_out_maps(encode_fn2(), &md, &mpre, p);
+  if (e) return e;
+  gemm2_kernel<BN><<<2 * clusters, kThreads, L::kTotal, stream>>>(ma, mb, md, mpre, p);
   return cudaGetLastError() == cudaSuccess ? 0 : GEMM_ERR_LAUNCH;
 }
 

@@ -46,16 +46,38 @@ __device__ __forceinline__ void aux_prefetch(const elem_t* aux_row, int n0, int 
   }
 }
 
+// Staging for TMA stores: a lane writes the four 16-byte pieces of its row's 64-byte chunk into a 32-row x 64-byte
+// buffer in the layout of CU_TENSOR_MAP_SWIZZLE_64B (piece index XOR bits 1-2 of the row), which also keeps the
+// writes of a warp free of bank conflicts.  The buffer must be 512-byte aligned.
+__device__ __forceinline__ void stage_row64(uint8_t* buffer, const float (&v)[32]) {
+  const int lane = threadIdx.x & 31;
+  uint4* row = reinterpret_cast<uint4*>(buffer + lane * 64);
+  const int sw = (lane >> 1) & 3;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __align__(16) elem2_t h[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) h[q] = ff2e2(v[8 * j + 2 * q], v[8 * j + 2 * q + 1]);
+    row[j ^ sw] = *reinterpret_cast<uint4*>(h);
+  }
+}
+
 // r: 32 fp32 accumulator values of output row `roff / ldd`, columns [n0, n0 + 32).  With PRE, `pre` holds what
-// aux_prefetch loaded for this chunk (valid whenever the chunk takes the vector path).
-template <bool CE = false, bool PRE = false>
+// aux_prefetch loaded for this chunk (valid whenever the chunk takes the vector path).  With STAGE (16-bit output
+// without accumulation, a full 32-column chunk; every lane of the warp calls, lanes whose row is outside the output
+// with roff < 0) nothing is stored to global memory: the result goes to `stage_out` and the pre-activation, if
+// requested, to `stage_pre`, for the caller's TMA stores (which clip rows outside the output).
+template <bool CE = false, bool PRE = false, bool STAGE = false>
 __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff, int n0, const uint32_t (&r)[32],
-                                            const uint4 (&pre)[4]) {
+                                            const uint4 (&pre)[4], uint8_t* stage_pre = nullptr,
+                                            uint8_t* stage_out = nullptr) {
+          const bool valid = roff >= 0;
+          if (!STAGE && !valid) return;
           float v[32];
   #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
           if constexpr (CE) {
-            if (p.ce_mode == 2) {   // logits -> scale * (softmax - onehot), straight from the accumulators
+            if (p.ce_mode == 2 && valid) {   // logits -> scale * (softmax - onehot), straight from the accumulators
               const long long m = roff / p.ldd;
               const float lse = p.ce_lse[m];
               const int tgt = (int)p.ce_targets[m];
@@ -77,7 +99,9 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
           }
           if (p.preact_out != nullptr) {
             elem_t* po = p.preact_out + roff + n0;
-            if (full_vec) {
+            if constexpr (STAGE) {
+              stage_row64(stage_pre, v);
+            } else if (full_vec) {
   #pragma unroll
               for (int j = 0; j < 32; j += 8) {
                 __align__(16) elem2_t h[4];
@@ -109,7 +133,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
               for (int j = 0; j < 32; j += 8) {
                 uint4 raw;
                 if constexpr (PRE) raw = pre[j / 8];
-                else raw = *reinterpret_cast<const uint4*>(gi + j);
+                else raw = valid ? *reinterpret_cast<const uint4*>(gi + j) : make_uint4(0, 0, 0, 0);
                 const elem2_t* h = reinterpret_cast<const elem2_t*>(&raw);
   #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -131,7 +155,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
               for (int j = 0; j < 32; j += 8) {
                 uint4 raw;
                 if (PRE && p.gelu_grad_in == nullptr) raw = pre[j / 8];
-                else raw = *reinterpret_cast<const uint4*>(ri + j);
+                else raw = valid ? *reinterpret_cast<const uint4*>(ri + j) : make_uint4(0, 0, 0, 0);
                 const elem2_t* h = reinterpret_cast<const elem2_t*>(&raw);
   #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -143,8 +167,12 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
             } else {
   #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (n0 + j < p.N) v[j] += e2f(ri[j]);
+                if (valid && n0 + j < p.N) v[j] += e2f(ri[j]);
             }
+          }
+          if constexpr (STAGE) {
+            stage_row64(stage_out, v);
+            return;
           }
           if (p.rs_rows_per_rank > 0 && p.rs_slot_plus1 > 0) {
             // GEMM -> reduce-scatter, slot form: this rank's partial tile goes, as bf16, into its slot of the

@@ -32,6 +32,7 @@
 // accumulation (cutlass_codegen/conv2d_cutlass_kernel.cu, kernels/conv2d.py:72-190, kernels/conv2d_bwd.py:6-232;
 // dispatch in src/passes/conv2d_pass.cpp).
 #include "gemm_tcgen05.h"
+#include "gemm_out_maps.h"
 #include <cstddef>
 #include "gemm_epilogue.cuh"
 #include "tc05.cuh"
@@ -61,7 +62,8 @@ struct SmemLayout {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024: manual alignment slack
+  static constexpr int kEpiStage = 8 * 2 * 2048;   // per epilogue warp: two 32-row x 64-byte buffers for TMA stores
+  static constexpr int kTotal = kStages * kStageBytes + kEpiStage + kBarrierBytes + 1024;  // +1024: manual alignment slack
 };
 
 // Row of the output tile -> element offset of that row in D (or -1 when the row is out of range).
@@ -110,12 +112,13 @@ __device__ __forceinline__ Work decode_work(const GemmParams& p, int item, int t
 template <int BM, int BN, bool CE = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-            const GemmParams p) {
+            const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_pre, const GemmParams p) {
   using L = SmemLayout<BM, BN>;
   constexpr int MH = BM / 128;  // M = 128 halves per tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);
+  uint8_t* epi_stage = smem + L::kStages * L::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + L::kEpiStage);
   uint64_t* empty_bar = full_bar + L::kStages;
   uint64_t* tmem_full = empty_bar + L::kStages;
   uint64_t* tmem_empty = tmem_full + 2;
@@ -130,6 +133,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   if (threadIdx.x == 0) {
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
+    if (p.tma_store >= 1) prefetch_tensormap(&map_d);
+    if (p.tma_store >= 2) prefetch_tensormap(&map_pre);
     for (int s = 0; s < L::kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -295,6 +300,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const elem_t* aux_row = gemm_epi::aux_row_ptr(p, roff);
       uint4 aux[4] = {};
       gemm_epi::aux_prefetch(aux_row, tile_n * BN + c_begin, p.N, aux);
+      // TMA stores: where in the output this warp's 32 rows start (a box of st_bn x st_bh x st_bw output positions of
+      // the brick for a convolution, 32 matrix rows otherwise); a box that starts outside the output is skipped,
+      // one that reaches over its edge is clipped by the copy.
+      int sx1 = 0, sx2 = 0, sx3 = 0;
+      bool box_in = true;
+      if (!CE && p.tma_store) {
+        const int r0 = (MH == 2 ? second * 128 : 0) + lane_group * 32;
+        if (p.mode == GEMM_MODE_CONV) {
+          const ConvGeom& g = p.conv;
+          const int w = (tile_m % g.tiles_w) * g.tw + r0 % g.tw;
+          const int h = ((tile_m / g.tiles_w) % g.tiles_h) * g.th + (r0 / g.tw) % g.th;
+          const int n = (tile_m / (g.tiles_w * g.tiles_h)) * g.tn + r0 / (g.tw * g.th);
+          sx1 = w * g.out_mul + g.out_off_w;
+          sx2 = h * g.out_mul + g.out_off_h;
+          sx3 = n;
+          box_in = n < g.batch && h < g.grid_h && w < g.grid_w && sx1 < g.out_w && sx2 < g.out_h;
+        } else {
+          sx1 = tile_m * BM + r0;
+          box_in = sx1 < p.M;
+        }
+      }
+      uint8_t* stage_pre = epi_stage + (warp - 2) * 4096;
+      uint8_t* stage_out = stage_pre + 2048;
       if (!mbar_wait(&tmem_full[acc], acc_phase)) { ok = false; break; }
       fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + (MH == 2 ? second * BN : acc * BN);
@@ -316,7 +344,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         for (int q = 0; q < 4; ++q) cur[q] = aux[q];
         if (c0 + 32 < c_end) gemm_epi::aux_prefetch(aux_row, n0 + 32, p.N, aux);
         tmem_ld_wait();
-        if (roff < 0 || n0 >= p.N) continue;
+        if (n0 >= p.N) continue;                               // the same for the whole warp
+        const bool tma_chunk = !CE && p.tma_store != 0 && n0 + 32 <= p.N;   // (the launcher rules out split-K here)
+        if (!tma_chunk && roff < 0) continue;
         if constexpr (CE) {
           if (p.ce_mode == 1) {
             float cm = -INFINITY;
@@ -356,6 +386,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           continue;
         }
         if (wk.k_end <= wk.k_begin) continue;
+        if constexpr (!CE) {
+          if (tma_chunk) {
+            // A staging buffer is free once the copy that read it is done (tracked by lane 0, which issued it).
+            // Without preact_out the two buffers take turns, so only the copy before the previous one has to be done.
+            const bool both = p.tma_store >= 2;
+            uint8_t* out_buf = (both || ((c0 >> 5) & 1)) ? stage_out : stage_pre;
+            if (lane == 0) {
+              if (both) bulk_wait_group_read<0>();
+              else bulk_wait_group_read<1>();
+            }
+            __syncwarp();
+            gemm_epi::store_chunk<false, true, true>(p, roff, n0, r, cur, stage_pre, out_buf);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (box_in) {
+                if (p.mode == GEMM_MODE_CONV) {
+                  if (both) tma_store_4d(&map_pre, stage_pre, n0, sx1, sx2, sx3);
+                  tma_store_4d(&map_d, out_buf, n0, sx1, sx2, sx3);
+                } else {
+                  if (both) tma_store_2d(&map_pre, stage_pre, n0, sx1);
+                  tma_store_2d(&map_d, out_buf, n0, sx1);
+                }
+              }
+              bulk_commit_group();      // also when nothing was stored: the group count paces the buffers
+            }
+            continue;
+          }
+        }
         gemm_epi::store_chunk<CE, true>(p, roff, n0, r, cur);
       }
       if constexpr (CE) {
@@ -375,6 +434,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       else if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (!ok && lane == 0) atomicExch(p.status, GEMM_ERR_EPILOGUE_TIMEOUT);
+    if (lane == 0) bulk_wait_group_all();     // this warp's TMA stores have left shared memory and reached global memory
   }
 
   fence_before_sync();
@@ -459,7 +519,15 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, cudaStre
   const int usable = g_num_sms - g_fbam_reserved_sms > 0 ? g_num_sms - g_fbam_reserved_sms : 1;
   int grid = tiles < usable ? tiles : usable;
   if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
-  gemm_kernel<BM, BN, CE><<<grid, kThreads, L::kTotal, stream>>>(ma, mb, p);
+  CUtensorMap md, mpre;
+  p.tma_store = 0;
+  std::memset(&md, 0, sizeof(md));
+  std::memset(&mpre, 0, sizeof(mpre));
+  if (!CE && p.ce_mode == 0 && p.splits <= 1 && p.split_workspace == nullptr && p.mode != GEMM_MODE_WGRAD) {
+    const int e = fbam_encode_out_maps(get_encode_fn(), &md, &mpre, p);
+    if (e) return e;
+  }
+  gemm_kernel<BM, BN, CE><<<grid, kThreads, L::kTotal, stream>>>(ma, mb, md, mpre, p);
   return cudaGetLastError() == cudaSuccess ? 0 : GEMM_ERR_LAUNCH;
 }
 

@@ -97,6 +97,11 @@ struct GemmParams {
   // other classes, instead of being streamed again by a separate launch per class.
   int num_classes;
   ConvClass cls[4];
+  // Filled by the CTA-pair launchers.  tma_store: 0 = the epilogue stores from registers; 1 = 16-bit results leave
+  // through shared memory and TMA tiled stores (D only); 2 = D and preact_out.  st_bw / st_bh / st_bn: the 32 rows
+  // that one epilogue warp owns, as a box of output positions (w, h, n) of a convolution brick (1, 1, 32 rows of a
+  // plain matrix).
+  int tma_store, st_bw, st_bh, st_bn;
 };
 
 // Driver entry points (tensor-map encoding) need a context that is current on the CALLING thread.  A thread that

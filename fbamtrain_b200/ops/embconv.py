@@ -210,8 +210,8 @@ def first_layer_forward_native(cells, cp_embed, pos_embed, colour, w, rows, cols
     oh, ow = out_hw(rows, cols, stride, pad, dil)
     _ext, _w_p, table, cc_t, pos_out, _pos_img = _tables_native(cp_embed, pos_embed, colour, w, rows, cols, stride, pad, dil)
     feat = features_native(cells, rows, cols, stride, pad, dil, w.dtype)
-    # colour term: K = 64 makes this GEMM all epilogue; single CTAs with 256 x 256 tiles measured fastest for it
-    z = no.gemm(feat.view(n * oh * ow, FEATURES), cc_t, bm=256, bn=256, two_cta=False)
+    # colour term: K = 64 makes this GEMM all epilogue; the CTA-pair kernel writes its tiles with TMA stores
+    z = no.gemm(feat.view(n * oh * ow, FEATURES), cc_t, two_cta=True)
     y = torch.empty_like(z)
     forward_native(cells, table, pos_out, z, y, rows, cols, stride, pad, dil)
     return y.view(n, oh, ow, o), z.view(n, oh, ow, o), feat

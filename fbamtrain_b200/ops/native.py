@@ -69,7 +69,8 @@ class GemmParams(C.Structure):
                 ("mode", C.c_int), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("tiles_m", C.c_int),
                 ("k_blocks", C.c_int), ("a_mn_major", C.c_int), ("b_mn_major", C.c_int), ("vec_ok", C.c_int),
                 ("conv", ConvGeom),
-                ("num_classes", C.c_int), ("cls", ConvClass * 4)]
+                ("num_classes", C.c_int), ("cls", ConvClass * 4),
+                ("tma_store", C.c_int), ("st_bw", C.c_int), ("st_bh", C.c_int), ("st_bn", C.c_int)]
 
 
 def available(dtype: torch.dtype = torch.bfloat16) -> bool:
