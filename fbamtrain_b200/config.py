@@ -130,6 +130,7 @@ class FbamModelConfiguration:
     action_mlp_dim: int = 0            # 0 -> 4 * n_embed
     action_vocab: int = 0              # 0 -> tokenizer size (reference)
     frame_head_recompute: bool = False  # recompute the frame head's activations in the backward, chunk by chunk
+    frame_replay: bool = False          # frames stay in host memory; chunks are uploaded again for the backward
 
     @staticmethod
     def from_json(o: Dict[str, Any]) -> "FbamModelConfiguration":
@@ -165,7 +166,7 @@ class FbamModelConfiguration:
                     "action_blocks", "action_heads", "action_mlp_dim", "action_vocab"):
             if key in o:
                 kw[key] = _uint(o, key, ctx)
-        for key in ("downsample_norm", "frame_proj", "frame_head_recompute"):
+        for key in ("downsample_norm", "frame_proj", "frame_head_recompute", "frame_replay"):
             if key in o:
                 kw[key] = _bool(o, key, ctx)
         if "downsample_channels" in o:

@@ -191,6 +191,8 @@ class Trainer:
     def _forward_backward(self, cells: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         loss_scale = 1.0 / (cells.shape[1] * cfg.total_batch_size)
+        if self.model.cfg.frame_replay and not cells.is_cuda:
+            return self._forward_backward_replayed(cells, targets, loss_scale)
         dev_cells, dev_targets, events, chunk = self._upload(cells, targets)
         b, t, p, _ = dev_cells.shape
         progress = log_enabled("INFO")          # per-chunk progress lines cost two events per chunk: only when shown
@@ -239,6 +241,28 @@ class Trainer:
             done = torch.cuda.Event()
             done.record()
             self._slot_free[self._slot_in_use] = done
+        return loss.detach()
+
+    def _forward_backward_replayed(self, cells: torch.Tensor, targets: torch.Tensor, loss_scale: float) -> torch.Tensor:
+        """Model key ``frame_replay``: the frames stay in host memory, the frame head sees one chunk at a time and
+        every chunk is uploaded and run again in the backward (``utils/frame_replay.py``)."""
+        from .utils.frame_replay import FrameReplay, ReplayedFrameHead
+        b, t, p, _ = cells.shape
+        chunk = self.frame_chunk or b * t
+        replay = FrameReplay(cells.reshape(b * t, p, 3), chunk, self.device,
+                             self.h2d_stream if self._cuda else None)
+        self.last_replay = replay
+        anchor = next(self.model.frame_head.parameters())
+        dev_targets = targets.to(self.device, non_blocking=True)
+        with gputx_range("fbamtrain::forward"):
+            with gputx_range("fbamtrain::frame_head_fwd"):
+                parts = [ReplayedFrameHead.apply(anchor, self.model.frame_head, replay, i)
+                         for i in range(replay.num_chunks)]
+            emb = (parts[0] if len(parts) == 1 else torch.cat(parts, 0)).view(b, t, -1)
+            with gputx_range("fbamtrain::action_model_fwd_bwd"):
+                loss = self.model.action_model(emb, dev_targets, loss_scale)
+        with gputx_range("fbamtrain::backward"):
+            loss.backward()
         return loss.detach()
 
     def train_step(self, cells: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:

@@ -631,6 +631,37 @@ def test_frame_head_recompute_gives_the_same_gradients():
         assert _rel_err(results[True][1][name], g) < 2e-2, name
 
 
+def test_frame_replay_matches_resident_frames_on_gpu():
+    """``frame_replay``: the frames stay in pinned host memory, chunks are copied in for the forward and again for the
+    backward on the copy stream (the reference re-decodes and recomputes: ``src/main.cpp:3354-3483``): same loss and
+    gradients as with the whole micro-batch resident, twice the chunk uploads."""
+    from fbamtrain_b200 import RunConfiguration, Trainer, presets
+    from fbamtrain_b200.data import SyntheticBatchSource
+    results = {}
+    for replay in (False, True):
+        d = presets.tiny("bf16")
+        d["model_config"].update({"cell_embed_dim": 64, "downsample_channels": [64, 128], "downsample_blocks": 2,
+                                  "n_embed": 64, "frame_rows": 16, "frame_cols": 24, "frame_replay": replay})
+        d["frame_rows"], d["frame_cols"] = 16, 24
+        cfg = RunConfiguration.from_json(d)
+        tr = Trainer(cfg, device=torch.device(DEV), frame_chunk=8)
+        src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, cfg.model_config.max_code_point, tr.vocab, seed=3,
+                                   pin=True)
+        cells, tg = src.next_batch(cfg.micro_batch_size, cfg.train_sequence_length)
+        tr.zero_grad()
+        loss = tr._forward_backward(cells, tg)
+        torch.cuda.synchronize()
+        results[replay] = (float(loss), {n: p.grad.detach().float().clone()
+                                         for n, p in tr.model.frame_head.named_parameters()})
+        if replay:
+            chunks = (cells.shape[0] * cells.shape[1] + 7) // 8
+            assert tr.last_replay.uploads == 2 * chunks
+        tr.close()
+    assert results[True][0] == pytest.approx(results[False][0], abs=1e-3)
+    for name, g in results[False][1].items():
+        assert _rel_err(results[True][1][name], g) < 2e-2, name
+
+
 def test_expected_backends_are_chosen_on_gpu():
     """16-bit CUDA tensors must reach the sm_100a kernels (no silent library fallback), fp32 the library."""
     _nops()

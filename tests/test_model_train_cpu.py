@@ -598,3 +598,29 @@ def test_scaled_down_reference_sample_configuration_trains(opt, mode, reduction)
     losses = [float(tr.train_step(cells, targets)) for _ in range(4)]
     tr.close()
     assert all(math.isfinite(x) for x in losses) and losses[-1] < losses[0]
+
+
+def test_frame_replay_gives_the_same_loss_and_gradients():
+    """Model key ``frame_replay``: frames stay on the host, every chunk is fetched twice (forward and backward) and the
+    frame head runs again in the backward — same loss, same gradients as keeping everything."""
+    import torch
+    from fbamtrain_b200 import RunConfiguration, Trainer, presets
+    from fbamtrain_b200.data import SyntheticBatchSource
+    results = {}
+    for replay in (False, True):
+        d = presets.tiny()
+        d["model_config"]["frame_replay"] = replay
+        cfg = RunConfiguration.from_json(d)
+        tr = Trainer(cfg, device=torch.device("cpu"), frame_chunk=5)
+        src = SyntheticBatchSource(cfg.frame_rows, cfg.frame_cols, 256, 32, seed=3, pin=False)
+        cells, tg = src.next_batch(cfg.micro_batch_size, cfg.train_sequence_length)
+        tr.zero_grad()
+        loss = tr._forward_backward(cells, tg)
+        results[replay] = (float(loss), {n: p.grad.detach().clone() for n, p in tr.model.named_parameters()})
+        if replay:
+            chunks = (cells.shape[0] * cells.shape[1] + 4) // 5
+            assert tr.last_replay.num_chunks == chunks and tr.last_replay.uploads == 2 * chunks
+        tr.close()
+    assert results[True][0] == results[False][0]
+    for name, g in results[False][1].items():
+        assert torch.allclose(results[True][1][name], g, atol=1e-7), name
