@@ -91,11 +91,37 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, long long roff,
           }
           const bool full_vec = (n0 + 32 <= p.N) && p.vec_ok;
           if (p.bias != nullptr) {
+            // every lane of the warp needs the same 32 bias values: 16-byte loads (served by L1 after the first tile)
+            // instead of 32 scalar ones, whenever the chunk is whole and the vector is 16-byte aligned
+            if (n0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) {
+              if (p.bias_fp32) {
+                const float4* b4 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + n0);
   #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N)
-                v[j] += p.bias_fp32 ? reinterpret_cast<const float*>(p.bias)[n0 + j]
-                                    : e2f(reinterpret_cast<const elem_t*>(p.bias)[n0 + j]);
+                for (int q = 0; q < 8; ++q) {
+                  const float4 t = __ldg(b4 + q);
+                  v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
+                }
+              } else {
+                const uint4* b4 = reinterpret_cast<const uint4*>(reinterpret_cast<const elem_t*>(p.bias) + n0);
+  #pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const uint4 raw = __ldg(b4 + q);
+                  const elem2_t* h = reinterpret_cast<const elem2_t*>(&raw);
+  #pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 f = e22ff(h[e]);
+                    v[8 * q + 2 * e] += f.x;
+                    v[8 * q + 2 * e + 1] += f.y;
+                  }
+                }
+              }
+            } else {
+  #pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + j < p.N)
+                  v[j] += p.bias_fp32 ? reinterpret_cast<const float*>(p.bias)[n0 + j]
+                                      : e2f(reinterpret_cast<const elem_t*>(p.bias)[n0 + j]);
+            }
           }
           if (p.preact_out != nullptr) {
             elem_t* po = p.preact_out + roff + n0;
