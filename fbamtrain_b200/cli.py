@@ -224,6 +224,8 @@ def main(argv=None) -> int:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.device:
         device = torch.device(args.device)
+        if device.type == "cuda" and device.index is not None:
+            torch.cuda.set_device(device)
     elif torch.cuda.is_available():
         device = torch.device("cuda", local_rank if env_rank is not None else (args.worker_id or 0) % max(
             1, torch.cuda.device_count()))

@@ -275,3 +275,63 @@ def test_scoped_group_next_to_the_default_group_on_two_gpus(tmp_path):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, _tail(r)
     assert out.read_text() == "ok"
+
+
+def test_cli_pipelines_with_dynamic_membership_on_four_gpus(tmp_path):
+    """Two one-plus-one pipelines, each a job of its own on its own pair of GPUs, under the membership master
+    (``frame_head_parallel`` + ``ddp_parallel.transport = "ftccl"``): same-position ranks exchange gradients over their
+    stand-alone NCCL communicators, and once both pipelines are in the group they report the same committed losses."""
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs four GPUs")
+    import json
+    from fbamtrain_b200 import presets
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = presets.tiny("bf16")
+    cfg["model_config"].update({"action_heads": 2, "lstm_layers": 1, "cell_embed_dim": 64, "downsample_channels": [64],
+                                "n_embed": 64})
+    cfg["micro_batch_size"], cfg["total_batch_size"] = 1, 2
+    run = tmp_path / "run.json"
+    run.write_text(json.dumps(cfg))
+    ports = [_free_port(), _free_port()]
+    par = {"frame_head_parallel": {"use_frame_head_parallel": True, "transport": "ccl",
+                                   "ccl_rendezvous": {"ip": "127.0.0.1", "port": ports[0]}},
+           "ddp_parallel": {"use_ddp_parallel": True, "transport": "ftccl",
+                            "ftccl_master": {"ip": "127.0.0.1", "port": ports[1]}}}
+    parallel = tmp_path / "parallel.json"
+    parallel.write_text(json.dumps(par))
+    env = dict(os.environ, PYTHONPATH=root, FBAMTRAIN_LOG_LEVEL="INFO", FBAMTRAIN_METRICS_JSON="1",
+               NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    master = subprocess.Popen([sys.executable, "-m", "fbamtrain_b200.cli", "--parallel-config", str(parallel),
+                               "--ftccl-master"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
+    procs = []
+    try:
+        base = [sys.executable, "-m", "fbamtrain_b200.cli", "-c", str(run), "--parallel-config", str(parallel),
+                "--synthetic", "--steps", "8", "--world-size", "2", "--ddp-world-size", "2"]
+        for replica in (0, 1):
+            for worker, extra in ((0, []), (1, ["--master"])):
+                procs.append(subprocess.Popen(
+                    base + ["--replica-id", str(replica), "--worker_id", str(worker), "--device",
+                            f"cuda:{2 * replica + worker}"] + extra,
+                    stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env))
+        outs = []
+        for p in procs:
+            try:
+                outs.append(p.communicate(timeout=420)[0])
+            except subprocess.TimeoutExpired:
+                p.kill()                                   # this very process, by its handle
+                outs.append(p.communicate()[0])
+        assert all(p.returncode == 0 for p in procs), [o[-1500:] for o in outs]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+        master.terminate()
+        master.communicate(timeout=30)
+
+    def losses(out):
+        rows = [json.loads(line) for line in out.splitlines() if line.startswith("{") and "loss/train" in line]
+        return {r["step"]: r["loss/train"] for r in rows}
+    first, second = losses(outs[1]), losses(outs[3])
+    both = sorted(set(first) & set(second))
+    assert len(both) >= 3
+    assert all(abs(first[k] - second[k]) < 1e-5 for k in both[-3:])
