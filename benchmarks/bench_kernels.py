@@ -71,9 +71,19 @@ def bench_gemm(a):
     w = torch.randn(a.n, a.k, device="cuda").bfloat16()
     out = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
     flops = 2.0 * a.m * a.n * a.k
-    report(f"gemm_tcgen05 {a.m}x{a.n}x{a.k}", timeit(lambda: no.gemm(x, w, out=out)), flops)
+    bias = torch.randn(a.n, device="cuda").bfloat16() if a.bias or a.gelu else None
+    pre = torch.empty_like(out) if a.gelu else None
+    tag = f"{a.m}x{a.n}x{a.k}" + (" +bias" if bias is not None else "") + (" +gelu +preact" if a.gelu else "")
+    report("gemm_tcgen05 " + tag, timeit(lambda: no.gemm(x, w, out=out, bias=bias, act="gelu" if a.gelu else "none",
+                                                         preact_out=pre)), flops)
     if a.library:
-        report(f"gemm_cublas {a.m}x{a.n}x{a.k}", timeit(lambda: torch.matmul(x, w.t(), out=out)), flops)
+        if a.gelu:
+            lib = lambda: torch.nn.functional.gelu(torch.addmm(bias, x, w.t()))
+        elif bias is not None:
+            lib = lambda: torch.addmm(bias, x, w.t(), out=out)
+        else:
+            lib = lambda: torch.matmul(x, w.t(), out=out)
+        report("gemm_cublas " + tag, timeit(lib), flops)
 
 
 def bench_conv(a):
@@ -269,6 +279,8 @@ def main():
     g.add_argument("--n", type=int, default=4096)
     g.add_argument("--k", type=int, default=4096)
     g.add_argument("--library", action="store_true")
+    g.add_argument("--bias", action="store_true")
+    g.add_argument("--gelu", action="store_true", help="bias + GELU + pre-activation store (the MLP's first layer)")
     c = sub.add_parser("conv")
     for name, default in (("batch", 32), ("h", 48), ("w", 160), ("cin", 1024), ("cout", 1024), ("stride", 1),
                           ("dilation", 2)):

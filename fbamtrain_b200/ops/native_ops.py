@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -54,7 +55,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          bn: int = 0, bm: int = 0, max_ctas: int = 0, ready_flags: Optional[torch.Tensor] = None,
          flag_rows: int = 0, flag_on_b: bool = False, flag_epoch: int = 0, flag_spin_limit: int = 0,
          rs_out=None, rs_rows_per_rank: int = 0, tile_m_rotate: int = 0, two_cta=None,
-         rs_slot: int = -1, rs_row_stores: bool = False, ce_stats=None, ce_grad=None) -> torch.Tensor:
+         rs_slot: int = -1, rs_row_stores: bool = False, ce_stats=None, ce_grad=None, splits: int = 0) -> torch.Tensor:
     """``D[M, N] = epilogue(A · Bᵀ)``.
 
     ``a``: ``(M, K)`` (or ``(K, M)`` when ``a_mn``); ``b``: ``(N, K)`` (or ``(K, N)`` when ``b_mn``).
@@ -71,6 +72,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     of a row instead of 16 bytes of 32 rows (needs ``M`` and ``rs_rows_per_rank`` in multiples of 32).
     ``two_cta`` selects the CTA-pair kernel (default: automatically for large problems).
 
+    ``splits`` > 1: split-K over that many CTAs per tile (single-CTA kernel); every split writes its fp32 partial tile
+    to a slab of a workspace with plain stores and one reduction sums the slabs into the output (no atomics, fixed
+    summation order) — for small outputs with a long K, which otherwise occupy a fraction of the SMs.
+
     Fused LM head + cross-entropy: ``ce_stats = (partial, tgt_logit, targets, vocab)`` stores nothing per element and
     leaves per-row (maximum, sum of exp) pairs of every tile half in ``partial`` ``(M, 2·⌈N/256⌉, 2)`` fp32 and the
     target logits in ``tgt_logit``; ``ce_grad = (lse, targets, vocab, scale)`` writes ``scale·(softmax − onehot)``
@@ -83,6 +88,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     n, kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
     if k != kb:
         raise ValueError(f"inner dimensions differ: {k} vs {kb}")
+    if splits > 1:
+        if (bias is not None or act != "none" or residual is not None or preact_out is not None or accumulate or
+                gelu_grad_in is not None or rs_out is not None or ready_flags is not None or ce_stats or ce_grad
+                or alpha != 1.0):
+            raise ValueError("split-K takes no epilogue options")
+        return _gemm_split_k(a, b, a_mn, b_mn, m, n, k, out, out_dtype or a.dtype, splits, bm, bn)
     if (bm == 0 and bn == 0 and max_ctas == 0 and two_cta is None and ready_flags is None and rs_out is None and
             ce_stats is None and ce_grad is None):
         tuned = tuning.lookup(tuning.gemm_key(m, n, k, a_mn, b_mn), {"m": m, "n": n, "k": k, "a_mn": a_mn, "b_mn": b_mn})
@@ -150,6 +161,42 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     flops.add(2.0 * m * n * k)
     debug.after_launch("gemm", a, b, out)
     return out
+
+
+def _gemm_split_k(a, b, a_mn, b_mn, m, n, k, out, out_dtype, splits, bm, bn) -> torch.Tensor:
+    splits = max(1, min(splits, (k + 63) // 64))
+    work = torch.empty(splits, m, n, dtype=torch.float32, device=a.device)
+    p = nv.GemmParams()
+    p.D, p.ldd = work.data_ptr(), n
+    p.split_workspace, p.split_stride = work.data_ptr(), m * n
+    p.status = nv.status_word(a.device).data_ptr()
+    p.alpha, p.out_fp32, p.splits, p.bn, p.bm = 1.0, 1, splits, bn, bm
+    with debug.label(f"gemm m{m} n{n} k{k} {'T' if a_mn else 'N'}{'T' if b_mn else 'N'} split{splits}"):
+        code = nv.lib(a).fbam_gemm(nv.ptr(a), C.c_longlong(a.stride(0)), int(a_mn), nv.ptr(b), C.c_longlong(b.stride(0)),
+                                   int(b_mn), m, n, k, C.byref(p), nv.stream_ptr())
+    nv.check(code, "fbam_gemm")
+    flops.add(2.0 * m * n * k)
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    if not out.is_contiguous() or out.dtype not in (torch.float32, a.dtype) or (m * n) % 8:
+        out.copy_(work.sum(0))
+        return out
+    nv.check(nv.lib(a).fbam_slab_reduce(nv.ptr(work), nv.ptr(out), C.c_longlong(m * n), splits,
+                                        int(out.dtype != torch.float32), nv.stream_ptr()), "fbam_slab_reduce")
+    return out
+
+
+# FBAMTRAIN_WGRAD_SPLIT_K=0 keeps the weight gradients of the linear layers on single launches without split-K.
+WEIGHT_GRAD_SPLIT_K = os.environ.get("FBAMTRAIN_WGRAD_SPLIT_K", "1") != "0"
+
+
+def weight_grad_splits(m: int, n: int, k: int) -> int:
+    """Split-K factor for ``dW = dYᵀ·X`` products whose output is small and whose K (the number of rows of the batch)
+    is long: a 1024 x 1024 output is 16 tiles of 256 x 256 — a tenth of the SMs — unless K is divided."""
+    tiles = ((m + 255) // 256) * ((n + 255) // 256)
+    if not WEIGHT_GRAD_SPLIT_K or k < 4096 or tiles > 48:
+        return 0
+    return max(1, min(8, 148 // tiles, k // 1024))
 
 
 def _tma_pitch(t: torch.Tensor) -> torch.Tensor:
@@ -239,7 +286,8 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm_nn(dy2, weight).view(ctx.in_shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm_tn(dy2, x2)
+            n_out, n_in = dy2.shape[1], x2.shape[1]
+            dw = gemm_tn(dy2, x2, splits=weight_grad_splits(n_out, n_in, dy2.shape[0]) if USE_MN_MAJOR else 0)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = _colsum(dy2).to(dy2.dtype)
         d_res = dy if len(ctx.needs_input_grad) > 4 and ctx.needs_input_grad[4] else None

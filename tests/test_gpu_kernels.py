@@ -67,6 +67,23 @@ def test_gemm_operands_without_16_byte_pitch(m, n, k, a_mn, b_mn):
     nv.check_status(a.device)
 
 
+@pytest.mark.parametrize("out_dtype", ["elem", "fp32"])
+@pytest.mark.parametrize("m,n,k,splits", [(1024, 1024, 8192, 8), (3072, 1024, 8192, 3), (200, 136, 1000, 4)])
+def test_gemm_split_k_with_slab_reduction(m, n, k, splits, out_dtype):
+    """Split-K for small outputs with a long K (weight gradients of the linear layers): every split writes its fp32
+    partial tile to its own slab, one reduction sums the slabs — against the fp32 product."""
+    nv, no = _nops()
+    torch.manual_seed(2)
+    a = torch.randn(k, m, device=DEV).to(BF)          # dY (rows x out features), read as A^T
+    b = torch.randn(k, n, device=DEV).to(BF)          # X  (rows x in features)
+    dtype = BF if out_dtype == "elem" else torch.float32
+    got = no.gemm(a, b, a_mn=True, b_mn=True, out_dtype=dtype, splits=splits)
+    nv.check_status(a.device)
+    expect = a.float().t() @ b.float()
+    assert got.dtype == dtype and _rel_err(got, expect) < (5e-3 if out_dtype == "elem" else 1e-4)
+    assert no.weight_grad_splits(1024, 1024, 8192) == 8 and no.weight_grad_splits(4096, 4096, 8192) == 0
+
+
 @pytest.mark.parametrize("bm", [128, 256])
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, True)])
 def test_gemm_tall_tiles(bm, a_mn, b_mn):

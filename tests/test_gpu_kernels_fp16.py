@@ -19,7 +19,7 @@ def _half_elements(monkeypatch):
 
 
 from test_gpu_kernels import (  # noqa: E402,F401  (collected here, with this module's fixture)
-    test_gemm_k_major, test_gemm_mn_major_operands, test_gemm_operands_without_16_byte_pitch, test_gemm_tall_tiles,
+    test_gemm_k_major, test_gemm_split_k_with_slab_reduction, test_gemm_mn_major_operands, test_gemm_operands_without_16_byte_pitch, test_gemm_tall_tiles,
     test_gemm_epilogues, test_conv_fprop_and_dgrad, test_linear_autograd_matches_reference, test_rmsnorm_fwd_bwd,
     test_layernorm_gelu_geglu_pools, test_layernorm_fwd_bwd, test_cell_embed_fwd_bwd, test_lm_head_ce_fwd_bwd,
     test_persistent_lstm_fwd_bwd, test_conv_wgrad, test_conv_gelu_stack_pool_matches_unfused_reference,
