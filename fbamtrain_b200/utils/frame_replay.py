@@ -5,7 +5,8 @@ CPU thread and running the frame head on them again in the backward (``src/main.
 Here the decoded frames of the batch already sit in pinned host memory (the loader's output); :class:`FrameReplay`
 uploads chunk ``i`` for the forward, and uploads it AGAIN for the backward, where :class:`ReplayedFrameHead` runs the
 frame head on it a second time (not counted as useful FLOPs).  Two chunk-sized device buffers take turns and the
-neighbouring chunk is copied on the host→device stream while the current one computes, in both directions.  Device
+neighbouring chunk is copied on the host→device stream while the current one computes, in both directions (the last
+two chunks of the forward are still in the buffers when the backward starts and are not copied again).  Device
 memory for the frames and the frame head's activations is then one chunk's worth whatever B·T is.
 """
 from __future__ import annotations

@@ -672,7 +672,9 @@ def test_frame_replay_matches_resident_frames_on_gpu():
                                          for n, p in tr.model.frame_head.named_parameters()})
         if replay:
             chunks = (cells.shape[0] * cells.shape[1] + 7) // 8
-            assert tr.last_replay.uploads == 2 * chunks
+            # every chunk is copied in twice, except the last two, which are still in the two buffers when the
+            # backward starts
+            assert tr.last_replay.uploads == 2 * chunks - 2
         tr.close()
     assert results[True][0] == pytest.approx(results[False][0], abs=1e-3)
     for name, g in results[False][1].items():
