@@ -326,3 +326,22 @@ def test_prefetching_source_keeps_order_and_reports_errors():
     with pytest.raises(OSError, match="no data"):
         bad.next_batch(1, 1)
     bad.close()
+
+
+def test_launch_rules_for_split_k_and_fused_parity_classes():
+    """Pure launch rules (no GPU): which weight gradients are split over K, and when the four parity classes of a
+    strided data gradient share one launch."""
+    from fbamtrain_b200.ops import native_ops as no
+    # small output, long K: divided so that the tiles fill the machine; large outputs and short K are left alone
+    assert no.weight_grad_splits(1024, 1024, 8192) == 8
+    assert no.weight_grad_splits(3072, 1024, 8192) == 3
+    assert no.weight_grad_splits(4096, 4096, 8192) == 0
+    assert no.weight_grad_splits(1024, 1024, 2048) == 0
+    taps = {1: [(0, 0)], 2: [(0, 0), (0, 1)], 4: [(0, 0), (0, 1), (1, 0), (1, 1)]}
+    parts = [(taps[1], None, (12, 40), (0, 0)), (taps[2], None, (12, 40), (0, 1)), (taps[2], None, (12, 40), (1, 0)),
+             (taps[4], None, (12, 40), (1, 1))]
+    assert no._fuse_dgrad_classes(parts, 1024, 256, 2)                     # the benchmark model's second layer
+    assert not no._fuse_dgrad_classes(parts, 1024, 128, 2)                 # too few output channels for CTA pairs
+    assert not no._fuse_dgrad_classes(parts, 16, 256, 2)                   # too few tiles
+    odd = [(taps[1], None, (12, 41), (0, 0))] + parts[1:]
+    assert not no._fuse_dgrad_classes(odd, 1024, 256, 2)                   # classes on different grids
