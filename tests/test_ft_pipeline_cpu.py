@@ -129,3 +129,41 @@ def test_pipelines_join_and_leave_a_running_job():
     for p in static:
         p.join(60)
     assert [info_a["losses"][k] for k in range(3)] == pytest.approx(curves[0], abs=2e-5)
+
+
+def _scoped_rank(rank, world, port, q):
+    from fbamtrain_b200.parallel.ftccl import (Result, ScopedGroup, SharedStateSyncStrategy, TensorInfo,
+                                               synchronize_shared_state)
+    group = ScopedGroup("127.0.0.1", port, host_store=rank == 0, prefix="test/1/0", rank=rank, world_size=world,
+                        device=torch.device("cpu"), timeout_s=60.0)
+    x = torch.full((1000,), float(rank + 1))
+    group.all_reduce(x)
+    y = torch.full((10,), float(rank))
+    group.broadcast(y, src=world - 1)
+    objs = group.all_gather_object({"rank": rank, "pad": "x" * (5 * rank)})
+    # shared state: the highest revision wins; among equal revisions the most common content
+    t = torch.full((64,), float(rank >= 1))
+    res, info = synchronize_shared_state(group, 7 if rank >= 1 else 3, [TensorInfo("t", t)],
+                                         SharedStateSyncStrategy.ENFORCE_POPULAR)
+    q.put((rank, float(x[0]), float(y[0]), [o["rank"] for o in objs], len(objs[-1]["pad"]), res == Result.SUCCESS,
+           info.revision, float(t.mean()), info.rx_bytes))
+    group.close()
+
+
+def test_scoped_group_collectives_and_shared_state_on_gloo():
+    """The stand-alone communicator of a pipeline position (no default process group involved): sum, broadcast,
+    object exchange, and the shared-state comparison in which the member that is behind receives the others' tensor."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_scoped_rank, args=(r, 3, port, q)) for r in range(3)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=120) for _ in range(3))
+    for p in procs:
+        p.join(30)
+        assert p.exitcode == 0
+    for rank, total, bcast, ranks, pad, ok, revision, mean, rx in results:
+        assert total == 6.0 and bcast == 2.0 and ranks == [0, 1, 2] and pad == 10
+        assert ok and revision == 7 and mean == 1.0
+        assert (rx > 0) == (rank == 0)                  # only the member that was behind received anything
