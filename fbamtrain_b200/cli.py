@@ -162,6 +162,8 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
                 iterator.restore(restored)
             elif iterator is None:
                 src.seek(trainer.step_count)
+    if ft is not None and iterator is None and trainer.step_count > 0:
+        src.seek(trainer.step_count)     # a pipeline admitted to a running job continues at the job's position
     limit = cfg.max_training_steps if args.steps is None else min(cfg.max_training_steps,
                                                                   trainer.step_count + args.steps)
     interval = cfg.checkpointing.checkpoint_interval

@@ -5,6 +5,8 @@ non-zero exit code.
     python -m fbamtrain_b200.launch --nproc 8 -- -c run.json --parallel-config configs/parallel/dp_ccl_fused.json
     python -m fbamtrain_b200.launch --nproc 8 --pipelines 1 -- -c run.json --parallel-config \
         configs/parallel/frame_head_parallel.json
+    python -m fbamtrain_b200.launch --nproc 8 --pipelines 2 -- -c run.json --parallel-config \
+        configs/parallel/pipelines_ftccl.json        # two pipelines under the membership master
 
 When a rank fails, the others get ``--grace`` seconds to finish and are then stopped (ranks of a fault-tolerant job
 carry on instead).  Everything after ``--`` goes to ``fbamtrain_b200.cli`` unchanged; the launcher adds ``--worker_id``, ``--world-size`` /
@@ -66,10 +68,22 @@ def main(argv=None) -> int:
             raise SystemExit("--nproc must split into --pipelines pipelines with an even number of ranks each")
         per = a.nproc // a.pipelines
         for r in range(a.nproc):
-            extra = ["--worker_id", str(r), "--world-size", str(per), "--ddp-world-size", str(a.pipelines)]
+            if master is not None:
+                # pipelines with dynamic membership: every pipeline is a job of its own (its ranks count from 0 and
+                # rendezvous at the configured port + the pipeline's number); one GPU per process unless told otherwise
+                extra = ["--worker_id", str(r % per), "--replica-id", str(r // per), "--world-size", str(per),
+                         "--ddp-world-size", str(a.pipelines)]
+                if "--device" not in cli_args:
+                    import torch
+                    if torch.cuda.is_available():
+                        extra += ["--device", f"cuda:{r % torch.cuda.device_count()}"]
+                tag = f"pipeline {r // per} rank {r % per}"
+            else:
+                extra = ["--worker_id", str(r), "--world-size", str(per), "--ddp-world-size", str(a.pipelines)]
+                tag = f"rank {r}"
             if r % per == per // 2:
                 extra.append("--master")
-            start(extra, f"rank {r}")
+            start(extra, tag)
     else:
         for r in range(a.nproc):
             start(["--worker_id", str(r), "--ddp-world-size", str(a.nproc)], f"rank {r}")

@@ -434,3 +434,32 @@ def test_cli_pipelines_with_dynamic_membership(tmp_path):
     both = sorted(set(first) & set(second))
     assert len(both) >= 3
     assert all(abs(first[k] - second[k]) < 1e-6 for k in both[-3:])      # in lockstep once both are in the group
+
+
+def test_launcher_starts_pipelines_with_dynamic_membership(tmp_path):
+    """``launch --pipelines 2`` with ``frame_head_parallel`` + transport ``ftccl``: the launcher starts the membership
+    master and two pipelines of two CPU ranks, each pipeline as a job of its own (ranks numbered inside the pipeline,
+    ``--replica-id`` per pipeline)."""
+    import socket
+    cfg = presets.tiny()
+    cfg["model_config"].update({"action_heads": 2, "lstm_layers": 1})
+    cfg["micro_batch_size"], cfg["total_batch_size"] = 1, 2
+    run = tmp_path / "run.json"
+    run.write_text(json.dumps(cfg))
+    ports = []
+    for _ in range(2):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            ports.append(s.getsockname()[1])
+    par = {"frame_head_parallel": {"use_frame_head_parallel": True, "transport": "ccl",
+                                   "ccl_rendezvous": {"ip": "127.0.0.1", "port": ports[0]}},
+           "ddp_parallel": {"use_ddp_parallel": True, "transport": "ftccl",
+                            "ftccl_master": {"ip": "127.0.0.1", "port": ports[1]}}}
+    parallel = tmp_path / "parallel.json"
+    parallel.write_text(json.dumps(par))
+    r = _run(["fbamtrain_b200.launch", "--nproc", "4", "--pipelines", "2", "--", "-c", str(run), "--parallel-config",
+              str(parallel), "--synthetic", "--steps", "4", "--device", "cpu", "-v"])
+    assert r.returncode == 0, r.stdout + r.stderr
+    for pipeline in (0, 1):
+        assert f"[pipeline {pipeline} rank 1]" in r.stdout
+    assert r.stdout.count("Step 3 took") == 2          # the recurrence master of each pipeline reports
