@@ -291,7 +291,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     const int col_half = (warp - 2) / 4;
     const int row = lane_group * 32 + lane;
     int acc = 0;
-    uint32_t acc_phase = 0;
+    uint32_t acc_phase = 0, stage_turn = 0;
     bool ok = true;
     for (WorkIter it(cluster_id); it.tile < num_tiles && ok; it.next(ncls, num_clusters)) {
       const int tile = it.tile;
@@ -345,9 +345,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         if (n0 >= p.N) continue;                               // the same for the whole warp
         if (p.tma_store && n0 + 32 <= p.N) {
           // A staging buffer is free once the copy that read it is done (tracked by lane 0, which issued it).  Without
-          // preact_out the two buffers take turns, so only the copy before the previous one has to be done.
+          // preact_out the two buffers take turns (stage_turn counts this warp's stored chunks across tiles), so only
+          // the copy before the previous one has to be done.
           const bool both = p.tma_store >= 2;
-          uint8_t* out_buf = (both || ((c0 >> 5) & 1)) ? stage_out : stage_pre;
+          uint8_t* out_buf = (both || (stage_turn++ & 1)) ? stage_out : stage_pre;
           if (lane == 0) {
             if (both) bulk_wait_group_read<0>();
             else bulk_wait_group_read<1>();

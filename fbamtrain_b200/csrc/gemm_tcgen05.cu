@@ -289,7 +289,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const int row = (MH == 2 ? second * 128 : 0) + lane_group * 32 + lane;
     const int c_begin = MH == 2 ? 0 : second * (BN / 2), c_end = MH == 2 ? BN : (second + 1) * (BN / 2);
     int acc = 0;
-    uint32_t acc_phase = 0;
+    uint32_t acc_phase = 0, stage_turn = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const Work wk = decode_work(p, tile, tiles_n);
@@ -389,9 +389,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if constexpr (!CE) {
           if (tma_chunk) {
             // A staging buffer is free once the copy that read it is done (tracked by lane 0, which issued it).
-            // Without preact_out the two buffers take turns, so only the copy before the previous one has to be done.
+            // Without preact_out the two buffers take turns (stage_turn counts this warp's stored chunks across tiles), so
+            // only the copy before the previous one has to be done.
             const bool both = p.tma_store >= 2;
-            uint8_t* out_buf = (both || ((c0 >> 5) & 1)) ? stage_out : stage_pre;
+            uint8_t* out_buf = (both || (stage_turn++ & 1)) ? stage_out : stage_pre;
             if (lane == 0) {
               if (both) bulk_wait_group_read<0>();
               else bulk_wait_group_read<1>();
