@@ -359,9 +359,11 @@ class PipelineTrainer:
         from ..utils import safetensors_io as st
         self.gather_model()
         path = manager.path_for(self.step_count)
-        if dist.get_rank() == 0:
+        # with dynamic membership every pipeline holds the same state: the one with index 0 writes the files
+        writer = self.ft is None or self.ft.replica_index == 0
+        if dist.get_rank() == 0 and writer:
             manager.save(self.step_count, self.model, {}, dataset_state)
-        if self.replica == 0:
+        if self.replica == 0 and writer:
             import os
             os.makedirs(manager.directory, exist_ok=True)
             st.save_file({k: v.detach().cpu() for k, v in self.optimizer.state_tensors().items()},
