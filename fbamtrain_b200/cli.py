@@ -164,11 +164,21 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
                 src.seek(trainer.step_count)
     if ft is not None and iterator is None and trainer.step_count > 0:
         src.seek(trainer.step_count)     # a pipeline admitted to a running job continues at the job's position
+    if ft is not None and iterator is not None:
+        valid, rng_state = (int(v) for v in trainer.data_state.tolist())
+        if valid:                        # ... and on recordings it adopts the job's iterator state
+            from .data.iterator import DatasetIteratorState
+            iterator.restore(DatasetIteratorState(rng_state=rng_state & ((1 << 64) - 1), batch_size=cfg.total_batch_size))
+            LOG("INFO", "adopted the job's dataset iterator state")
     limit = cfg.max_training_steps if args.steps is None else min(cfg.max_training_steps,
                                                                   trainer.step_count + args.steps)
     interval = cfg.checkpointing.checkpoint_interval
     while trainer.step_count < limit:
         step = trainer.step_count
+        if ft is not None and iterator is not None:
+            rng_now = iterator.cursor_checkpoint().rng_state
+            trainer.data_state.copy_(torch.tensor([1, rng_now - (1 << 64) if rng_now >= (1 << 63) else rng_now],
+                                                  dtype=torch.int64))
         cells, targets = next_batch()
         t0 = time.perf_counter()
         loss = trainer.train_step(cells.to(device), targets.to(device))
@@ -192,6 +202,7 @@ def _run_pipeline(cfg: RunConfiguration, par: ParallelConfiguration, args, devic
         if interval > 0 and trainer.step_count % interval == 0:
             trainer.save_checkpoint(manager, iterator.checkpoint() if iterator is not None else None)
     if iterator is not None:
+        LOG("INFO", f"dataset iterator state at the end: {iterator.cursor_checkpoint().rng_state}")
         iterator.close()
     if hasattr(next_batch, "close"):
         next_batch.close()

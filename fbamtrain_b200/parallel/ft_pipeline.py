@@ -83,6 +83,10 @@ class FaultTolerantPipelineReplicas:
         for name, t in sorted(trainer.optimizer.state_tensors().items()):
             if not name.endswith("__optimizer/step"):
                 infos.append(TensorInfo(name, t))
+        if getattr(trainer, "data_state", None) is not None:
+            # where the job's dataset iterator stands: travels with the rest to a pipeline that receives the state,
+            # but a difference in it alone is no reason for a transfer
+            infos.append(TensorInfo("data/iterator_state", trainer.data_state, allow_content_inequality=True))
         return infos
 
     def _retopologize(self, trainer, joining: bool = False) -> bool:

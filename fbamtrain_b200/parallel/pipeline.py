@@ -315,6 +315,9 @@ class PipelineTrainer:
         self.optimizer = create_optimizer(cfg.optimizer_config, named, prefix)
         self.loss_scale = 1.0 / (self.seq * cfg.total_batch_size)
         self.step_count = 0
+        # (valid, RNG state of the dataset iterator at the start of the current step): part of the state a pipeline
+        # receives when it is admitted to a running job, so that it continues the job's data order
+        self.data_state = torch.zeros(2, dtype=torch.int64, device=device) if ft is not None else None
         if ft is not None:
             ft.attach(self)
 

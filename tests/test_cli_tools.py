@@ -463,3 +463,75 @@ def test_launcher_starts_pipelines_with_dynamic_membership(tmp_path):
     for pipeline in (0, 1):
         assert f"[pipeline {pipeline} rank 1]" in r.stdout
     assert r.stdout.count("Step 3 took") == 2          # the recurrence master of each pipeline reports
+
+
+def test_pipelines_with_dynamic_membership_share_the_data_order_on_recordings(tmp_path):
+    """Two pipelines under the membership master on a recordings folder, the second started after the first has
+    trained for a while: it adopts the job's step AND the dataset iterator's state, so both end on the same iterator
+    state (same data order from the step of admission on)."""
+    import socket
+    import time
+    import numpy as np
+    from fbamtrain_b200.data import ArrayRecording, SyntheticRecording
+    from fbamtrain_b200.tokenizer import Tokenizer
+    rec_dir = tmp_path / "rec"
+    rec_dir.mkdir()
+    for i in range(2):
+        r = SyntheticRecording(8, 16, 50, seed=i)
+        cells = np.stack([r.frame(t)[0] for t in range(50)])
+        ArrayRecording(cells, [r.frame(t)[1] for t in range(50)]).save(str(rec_dir / f"r{i}.fbrec.npz"))
+    Tokenizer(list("abcdefghijklmnopqrstuvwxyz") + ["ab", "th"]).save(str(tmp_path / "tok.txt"))
+    cfg = presets.tiny()
+    cfg["model_config"].update({"action_heads": 2, "lstm_layers": 1, "action_vocab": 0})
+    cfg["micro_batch_size"], cfg["total_batch_size"] = 1, 2
+    cfg["tokenizer_file_path"] = "tok.txt"
+    cfg["train_data_config"]["recordings_directory_path"] = "rec"
+    cfg["max_training_steps"] = 240
+    run = tmp_path / "run.json"
+    run.write_text(json.dumps(cfg))
+    ports = []
+    for _ in range(2):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            ports.append(s.getsockname()[1])
+    par = {"frame_head_parallel": {"use_frame_head_parallel": True, "transport": "ccl",
+                                   "ccl_rendezvous": {"ip": "127.0.0.1", "port": ports[0]}},
+           "ddp_parallel": {"use_ddp_parallel": True, "transport": "ftccl",
+                            "ftccl_master": {"ip": "127.0.0.1", "port": ports[1]}}}
+    parallel = tmp_path / "parallel.json"
+    parallel.write_text(json.dumps(par))
+    env = dict(os.environ, PYTHONPATH=ROOT, FBAMTRAIN_LOG_LEVEL="INFO", OMP_NUM_THREADS="1")   # five processes share the cores
+    master = subprocess.Popen([sys.executable, "-m", "fbamtrain_b200.cli", "--parallel-config", str(parallel),
+                               "--ftccl-master"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
+    procs = []
+    try:
+        base = [sys.executable, "-m", "fbamtrain_b200.cli", "-c", str(run), "--parallel-config", str(parallel),
+                "--device", "cpu", "--world-size", "2", "--ddp-world-size", "2"]
+
+        logs = []
+
+        def start(replica):
+            for worker, extra in ((0, []), (1, ["--master"])):
+                log = tmp_path / f"out_{replica}_{worker}.log"
+                logs.append(log)
+                procs.append(subprocess.Popen(base + ["--replica-id", str(replica), "--worker_id", str(worker)] + extra,
+                                              stdout=open(log, "w"), stderr=subprocess.STDOUT, env=env))
+        start(0)
+        deadline = time.time() + 120
+        while "Step 2 took" not in logs[1].read_text() and time.time() < deadline:
+            time.sleep(0.2)                    # the first pipeline is training: now start the second
+        start(1)
+        for p in procs:
+            p.wait(timeout=500)
+        outs = [log.read_text() for log in logs]
+        assert all(p.returncode == 0 for p in procs), [o[-2000:] for o in outs]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+        master.terminate()
+        master.communicate(timeout=30)
+    assert "adopted the job's dataset iterator state" in outs[2] + outs[3]
+    assert "Step 0 took" not in outs[3]                                  # the late pipeline joined mid-run
+    ends = [line.split("end: ")[1] for o in outs for line in o.splitlines() if "iterator state at the end" in line]
+    assert len(ends) == 4 and len(set(ends)) == 1                         # one data order for the whole job
