@@ -41,7 +41,10 @@ _CONTROL_WORDS = 8
 class FaultTolerantPipelineReplicas:
     def __init__(self, master_ip: str, master_port: int, device: torch.device, expected_replicas: int,
                  min_replicas: int = 1, late_joiner: bool = False, heartbeat_interval_s: float = 0.25,
-                 collective_timeout_s: float = 30.0, gate_timeout_s: float = 30.0):
+                 collective_timeout_s: float = 30.0, gate_timeout_s: float = 30.0, stall_timeout_s: float = 300.0):
+        """``stall_timeout_s``: when the leader has not reached its step gate for this long (it waits in a collective
+        of the pipeline's own process group because another rank of the pipeline is gone), it stops heartbeating, so
+        that the other pipelines drop this one instead of waiting for it at every gate (0 = never)."""
         if not dist.is_initialized():
             raise RuntimeError("the pipeline's own process group must be initialised first")
         self.device = device
@@ -53,7 +56,8 @@ class FaultTolerantPipelineReplicas:
         self.peer: Optional[FtPeer] = None
         if self.is_leader:
             self.peer = FtPeer(master_ip, master_port, device, heartbeat_interval_s=heartbeat_interval_s,
-                               collective_timeout_s=collective_timeout_s, owns_default_group=False)
+                               collective_timeout_s=collective_timeout_s, owns_default_group=False,
+                               progress_deadline_s=stall_timeout_s)
         self.group: Optional[ScopedGroup] = None
         self.epoch = 0
         self.replicas = 0                  # pipelines in the current topology
@@ -155,6 +159,7 @@ class FaultTolerantPipelineReplicas:
             words = None
             if self.is_leader:
                 peer = self.peer
+                peer.note_progress()
                 if peer.world_size > 1:
                     aligned = peer.gate(trainer.step_count, timeout_s=self.gate_timeout_s)
                 else:

@@ -548,10 +548,19 @@ def synchronize_shared_state(comm, revision: int, infos: Sequence[TensorInfo],
 class FtPeer:
     def __init__(self, master_ip: str, master_port: int, device: torch.device, peer_group: int = 0,
                  my_ip: str = "127.0.0.1", heartbeat_interval_s: float = 0.25, collective_timeout_s: float = 30.0,
-                 p2p_connection_pool_size: int = 16, owns_default_group: bool = True):
+                 p2p_connection_pool_size: int = 16, owns_default_group: bool = True,
+                 progress_deadline_s: float = 0.0):
         """``owns_default_group=False``: the process has a default ``torch.distributed`` group of its own that this
-        peer must leave alone (it then only connects, heartbeats, gates and votes; see :meth:`vote_topology`)."""
+        peer must leave alone (it then only connects, heartbeats, gates and votes; see :meth:`vote_topology`).
+
+        ``progress_deadline_s`` > 0: the heartbeat thread vouches for the training thread only while that thread
+        keeps calling :meth:`note_progress`; after this many seconds without a call the peer stops heartbeating and
+        closes its connection, so the master evicts it like a process that died.  For peers whose training thread can
+        block for a long time in something the master cannot see (the leader of a pipeline waits in a collective of
+        its own process group when another rank of the pipeline has died)."""
         self.owns_default_group = owns_default_group
+        self.progress_deadline_s = progress_deadline_s
+        self._last_progress = time.monotonic()
         self.master_addr = (master_ip, master_port)
         self.device, self.peer_group, self.my_ip = device, peer_group, my_ip
         self.heartbeat_interval_s, self.collective_timeout_s = heartbeat_interval_s, collective_timeout_s
@@ -597,8 +606,24 @@ class FtPeer:
         LOG("ERR", f"ftccl: cannot reach the master at {self.master_addr}: {last}")
         return Result.MASTER_CONNECTION_FAILED
 
+    def note_progress(self) -> None:
+        """The training thread is alive and moving (see ``progress_deadline_s``)."""
+        self._last_progress = time.monotonic()
+
     def _heartbeat_loop(self) -> None:
         while not self._hb_stop.wait(self.heartbeat_interval_s):
+            if self.progress_deadline_s > 0 and time.monotonic() - self._last_progress > self.progress_deadline_s:
+                LOG("ERR", f"ftccl: no progress for {self.progress_deadline_s:.0f} s; this peer stops vouching for "
+                           "its training thread and leaves the group")
+                self._master_view = dict(self._master_view, ok=False)
+                with self._io:
+                    if self._sock is not None:
+                        try:
+                            self._sock.close()
+                        except OSError:
+                            pass
+                        self._sock = None
+                return
             try:
                 self._master_view = self._rpc({"op": "heartbeat"}, timeout=5.0)
             except (OSError, ConnectionError, json.JSONDecodeError):

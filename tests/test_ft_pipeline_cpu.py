@@ -167,3 +167,31 @@ def test_scoped_group_collectives_and_shared_state_on_gloo():
         assert total == 6.0 and bcast == 2.0 and ranks == [0, 1, 2] and pad == 10
         assert ok and revision == 7 and mean == 1.0
         assert (rx > 0) == (rank == 0)                  # only the member that was behind received anything
+
+
+def test_peer_that_makes_no_progress_stops_vouching_for_itself():
+    """``progress_deadline_s``: the heartbeat thread of a peer whose training thread is stuck (it does not call
+    ``note_progress``) stops after the deadline, and the master evicts the peer like a dead process; a peer that keeps
+    reporting progress stays."""
+    from fbamtrain_b200.parallel.ftccl import FtPeer, Result
+    master = create_master(heartbeat_timeout_s=0.6).start()
+    try:
+        stuck = FtPeer("127.0.0.1", master.port, torch.device("cpu"), heartbeat_interval_s=0.1,
+                       owns_default_group=False, progress_deadline_s=0.5)
+        moving = FtPeer("127.0.0.1", master.port, torch.device("cpu"), heartbeat_interval_s=0.1,
+                        owns_default_group=False, progress_deadline_s=0.5)
+        assert stuck.connect() == Result.SUCCESS and moving.connect() == Result.SUCCESS
+        deadline = time.time() + 6.0
+        while time.time() < deadline:
+            moving.note_progress()
+            snap = master.snapshot()
+            known = set(snap["accepted"]) | set(snap["pending"])
+            if stuck.uid not in known:
+                break
+            time.sleep(0.1)
+        snap = master.snapshot()
+        known = set(snap["accepted"]) | set(snap["pending"])
+        assert stuck.uid not in known and moving.uid in known
+        moving.leave()
+    finally:
+        master.interrupt()
