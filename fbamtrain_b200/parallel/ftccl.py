@@ -596,6 +596,7 @@ class FtPeer:
                 self._reader = _LineReader(self._sock)
                 res = self._rpc({"op": "connect", "peer_group": self.peer_group, "ip": self.my_ip})
                 self.uid = int(res["uid"])
+                self._last_progress = time.monotonic()
                 self._hb_stop.clear()
                 self._hb_thread = threading.Thread(target=self._heartbeat_loop, name="ftccl-heartbeat", daemon=True)
                 self._hb_thread.start()
