@@ -99,6 +99,7 @@ class FaultTolerantPipelineReplicas:
         if self.is_leader:
             res = None
             for _ in range(50):
+                self.peer.note_progress()              # waiting for the others' votes is not a stall of this pipeline
                 res = self.peer.vote_topology(min_world=self.min_replicas)
                 if res is not None:
                     break
